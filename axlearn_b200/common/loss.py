@@ -1,0 +1,228 @@
+"""Loss functions.
+
+Parity targets in the reference (axlearn/common/loss.py): ``cross_entropy`` (:89),
+``binary_cross_entropy`` (:176), stable CE custom VJP (:234-327), ``mean_squared_error``
+(:360), ``l1_loss`` (:419), contrastive losses (:442-720), ``focal_loss`` (:760),
+``huber_loss`` (:810), ``flops_loss`` (:843), ``large_margin_cosine_loss`` (:887),
+``giou_loss`` (:940), ``kl_divergence`` (:1052), ``koleo_loss`` (:1091),
+``pairwise_loss``/``ranking_pairwise_loss`` (:1135, :1164).
+
+The LM cross entropy runs through ``axlearn_b200.ops`` (fused softmax-CE kernels on GPU).
+"""
+
+from __future__ import annotations
+
+import enum
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from axlearn_b200 import ops
+
+Tensor = torch.Tensor
+
+
+class ReductionMethod(enum.Enum):
+    NONE = None
+    MEAN = "mean"
+    SUM = "sum"
+
+
+def _reduce(loss: Tensor, *, reduction: ReductionMethod, sample_weight: Optional[Tensor], eps: float = 0.0) -> Tensor:
+    if reduction in (ReductionMethod.NONE, None):
+        return loss
+    if sample_weight is not None:
+        w = sample_weight.to(loss.dtype)
+        while w.dim() < loss.dim():
+            w = w.unsqueeze(-1)
+        loss = loss * w
+        if reduction == ReductionMethod.MEAN:
+            denom = w.expand_as(loss).sum()
+            return loss.sum() / (denom + eps).clamp_min(eps or 1e-12)
+    return loss.mean() if reduction == ReductionMethod.MEAN else loss.sum()
+
+
+def cross_entropy(
+    logits: Tensor,
+    target_labels: Tensor,
+    *,
+    live_targets: Optional[Tensor] = None,
+    z_loss_scale: float = 0.0,
+    label_smoothing: float = 0.0,
+    soft_target_labels: Optional[Tensor] = None,
+    denominator: Optional[Tensor] = None,
+) -> tuple[Tensor, dict]:
+    """Softmax cross entropy + ``z_loss_scale * logsumexp^2``, averaged over live targets.
+
+    Returns ``(loss, aux)`` with aux keys ``cross_entropy_loss``, ``z_loss``, ``accuracy``,
+    ``num_live`` (and ``per_token_loss`` on the unfused path).
+    """
+    num_classes = logits.shape[-1]
+    if live_targets is None:
+        live_targets = (target_labels >= 0) & (target_labels < num_classes)
+    if label_smoothing or soft_target_labels is not None:
+        lf = logits.float()
+        logp = torch.log_softmax(lf, dim=-1)
+        if soft_target_labels is None:
+            onehot = F.one_hot(target_labels.clamp(0, num_classes - 1).long(), num_classes).float()
+            soft_target_labels = onehot * (1 - label_smoothing) + label_smoothing / num_classes
+        live = live_targets.float()
+        denom = live.sum().clamp_min(1.0) if denominator is None else denominator
+        per = -(soft_target_labels * logp).sum(-1)
+        lse = torch.logsumexp(lf, dim=-1)
+        ce = (per * live).sum() / denom
+        z = (lse * lse * live).sum() / denom
+        acc = ((lf.argmax(-1) == target_labels).float() * live).sum() / denom
+        return ce + z_loss_scale * z, {
+            "cross_entropy_loss": ce, "z_loss": z, "accuracy": acc,
+            "per_token_loss": per * live, "num_live": live.sum(),
+        }
+    return ops.cross_entropy(
+        logits, target_labels, live_targets=live_targets, z_loss_scale=z_loss_scale, denominator=denominator
+    )
+
+
+def binary_cross_entropy(
+    logits: Tensor, *, target_labels: Tensor, live_targets: Optional[Tensor] = None
+) -> tuple[Tensor, dict]:
+    if live_targets is None:
+        live_targets = (target_labels == 0) | (target_labels == 1)
+    live = live_targets.float()
+    per = F.binary_cross_entropy_with_logits(logits.float(), target_labels.clamp(0, 1).float(), reduction="none")
+    denom = live.sum().clamp_min(1.0)
+    loss = (per * live).sum() / denom
+    return loss, {"binary_cross_entropy_loss": loss, "per_target_loss": per * live}
+
+
+def mean_squared_error(preds: Tensor, targets: Tensor, sample_weight: Optional[Tensor] = None,
+                       reduction: ReductionMethod = ReductionMethod.MEAN, eps: float = 0.0) -> Tensor:
+    return _reduce((preds.float() - targets.float()) ** 2, reduction=reduction, sample_weight=sample_weight, eps=eps)
+
+
+def l1_loss(preds: Tensor, targets: Tensor, sample_weight: Optional[Tensor] = None,
+            reduction: ReductionMethod = ReductionMethod.MEAN, eps: float = 0.0) -> Tensor:
+    return _reduce((preds.float() - targets.float()).abs(), reduction=reduction, sample_weight=sample_weight, eps=eps)
+
+
+def huber_loss(*, predictions: Tensor, targets: Tensor, delta: float = 1.0,
+               reduce_axis: Optional[int] = None, sample_weight: Optional[Tensor] = None,
+               reduction: ReductionMethod = ReductionMethod.MEAN) -> Tensor:
+    err = (predictions.float() - targets.float()).abs()
+    quad = torch.clamp(err, max=delta)
+    loss = 0.5 * quad**2 + delta * (err - quad)
+    if reduce_axis is not None:
+        loss = loss.mean(dim=reduce_axis)
+    return _reduce(loss, reduction=reduction, sample_weight=sample_weight)
+
+
+def focal_loss(logits: Tensor, *, targets: Tensor, alpha: float = 0.25, gamma: float = 2.0,
+               sample_weight: Optional[Tensor] = None, reduction: ReductionMethod = ReductionMethod.MEAN) -> Tensor:
+    lf = logits.float()
+    t = targets.float()
+    bce = F.binary_cross_entropy_with_logits(lf, t, reduction="none")
+    p = torch.sigmoid(lf)
+    pt = p * t + (1 - p) * (1 - t)
+    w = (1 - pt) ** gamma
+    if alpha >= 0:
+        w = w * (alpha * t + (1 - alpha) * (1 - t))
+    return _reduce(w * bce, reduction=reduction, sample_weight=sample_weight)
+
+
+def kl_divergence(log_predictions: Tensor, targets: Tensor, is_log_targets: bool = False) -> tuple[Tensor, dict]:
+    lp = log_predictions.float()
+    if is_log_targets:
+        per = (targets.float().exp() * (targets.float() - lp)).sum(-1)
+    else:
+        t = targets.float()
+        per = torch.where(t > 0, t * (t.clamp_min(1e-30).log() - lp), torch.zeros_like(t)).sum(-1)
+    loss = per.mean()
+    return loss, {"per_example_loss": per}
+
+
+def contrastive_logits(x: Tensor, y: Tensor) -> Tensor:
+    """Pairwise similarities ``x @ y^T`` of L2-normalised embeddings."""
+    return x @ y.t()
+
+
+def symmetric_contrastive_loss_from_logits(
+    x_y_logits: Tensor, y_x_logits: Tensor, *, temperature: float = 1.0,
+    y_as_key_weight: float = 0.5,
+) -> Tensor:
+    n = x_y_logits.shape[0]
+    labels = torch.arange(n, device=x_y_logits.device)
+    l_xy = F.cross_entropy(x_y_logits.float() / temperature, labels)
+    l_yx = F.cross_entropy(y_x_logits.float() / temperature, labels)
+    return y_as_key_weight * l_xy + (1 - y_as_key_weight) * l_yx
+
+
+def asymmetric_contrastive_loss_from_logits(logits: Tensor, *, key_paddings: Optional[Tensor] = None,
+                                            temperature: float = 1.0, soft_labels: Optional[Tensor] = None) -> Tensor:
+    lf = logits.float() / temperature
+    if key_paddings is not None:
+        lf = lf + key_paddings.float()[None, :] * (-1e9)
+    n = lf.shape[0]
+    if soft_labels is None:
+        return F.cross_entropy(lf, torch.arange(n, device=lf.device))
+    return -(soft_labels * torch.log_softmax(lf, -1)).sum(-1).mean()
+
+
+def flops_loss(embeddings: Tensor, paddings: Optional[Tensor] = None, sparsity_threshold: float = 0.0):
+    """FLOPs regulariser of sparse embeddings: sum_j (mean_i |e_ij|)^2."""
+    e = embeddings.float().abs()
+    if paddings is not None:
+        w = (1 - paddings.float()).unsqueeze(-1)
+        mean = (e * w).sum(tuple(range(e.dim() - 1))) / w.sum().clamp_min(1.0)
+    else:
+        mean = e.reshape(-1, e.shape[-1]).mean(0)
+    sparsity = (e <= sparsity_threshold).float().mean()
+    return (mean**2).sum(), sparsity
+
+
+def large_margin_cosine_loss(logits: Tensor, *, labels: Tensor, alpha: float = 1.0, margin: float = 0.0):
+    num_classes = logits.shape[-1]
+    onehot = F.one_hot(labels.long(), num_classes).float()
+    adj = alpha * (logits.float() - margin * onehot)
+    return cross_entropy(adj, labels)
+
+
+def giou_loss(*, predictions: Tensor, targets: Tensor, eps: float = 1e-7,
+              reduction: ReductionMethod = ReductionMethod.MEAN, sample_weight=None) -> Tensor:
+    """Generalised IoU loss on boxes ``[..., (y1, x1, y2, x2)]``."""
+    p, t = predictions.float(), targets.float()
+    area = lambda b: (b[..., 2] - b[..., 0]).clamp_min(0) * (b[..., 3] - b[..., 1]).clamp_min(0)
+    iy1, ix1 = torch.max(p[..., 0], t[..., 0]), torch.max(p[..., 1], t[..., 1])
+    iy2, ix2 = torch.min(p[..., 2], t[..., 2]), torch.min(p[..., 3], t[..., 3])
+    inter = (iy2 - iy1).clamp_min(0) * (ix2 - ix1).clamp_min(0)
+    union = area(p) + area(t) - inter
+    iou = inter / (union + eps)
+    ey1, ex1 = torch.min(p[..., 0], t[..., 0]), torch.min(p[..., 1], t[..., 1])
+    ey2, ex2 = torch.max(p[..., 2], t[..., 2]), torch.max(p[..., 3], t[..., 3])
+    enclose = (ey2 - ey1).clamp_min(0) * (ex2 - ex1).clamp_min(0)
+    giou = iou - (enclose - union) / (enclose + eps)
+    return _reduce(1 - giou, reduction=reduction, sample_weight=sample_weight)
+
+
+def koleo_loss(embeddings: Tensor, *, eps: float = 1e-8, normalize_embedding: bool = True) -> Tensor:
+    """Kozachenko-Leonenko differential-entropy regulariser (spreads embeddings)."""
+    e = embeddings.float()
+    if normalize_embedding:
+        e = F.normalize(e, dim=-1, eps=eps)
+    d = torch.cdist(e, e)
+    d = d + torch.eye(d.shape[0], device=d.device) * 1e9
+    return -torch.log(d.min(dim=-1).values + eps).mean()
+
+
+def pairwise_loss(*, logits: Tensor, pair_weights: Tensor, loss_scale: float = 1.0) -> Tensor:
+    diff = logits.float()[..., :, None] - logits.float()[..., None, :]
+    per = F.softplus(-diff) * pair_weights.float()
+    return loss_scale * per.sum() / pair_weights.float().sum().clamp_min(1.0)
+
+
+def ranking_pairwise_loss(*, logits: Tensor, ranks: Tensor, loss_scale: float = 1.0) -> Tensor:
+    """Pairs (i, j) with rank_i < rank_j (and both ranked, rank > 0) should have
+    logit_i > logit_j."""
+    r = ranks.float()
+    valid = (r[..., :, None] > 0) & (r[..., None, :] > 0)
+    w = ((r[..., :, None] < r[..., None, :]) & valid).float()
+    return pairwise_loss(logits=logits, pair_weights=w, loss_scale=loss_scale)

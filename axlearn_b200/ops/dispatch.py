@@ -1,0 +1,151 @@
+"""Backend selection for the hot ops.
+
+Rule: CUDA tensors in bf16 (fp32 where a kernel supports it) go to the sm_100a kernels in
+``axlearn_b200.ops.cuda_ops``; everything else runs the PyTorch statements in
+``axlearn_b200.ops.reference``.  ``use_reference_ops()`` forces the reference path (tests
+use it to produce oracles on the GPU).
+"""
+
+from __future__ import annotations
+
+import contextlib
+import threading
+from typing import Optional
+
+import torch
+
+from axlearn_b200.ops import reference
+
+
+class _Flags(threading.local):
+    force_reference = 0
+
+
+_flags = _Flags()
+
+
+@contextlib.contextmanager
+def use_reference_ops():
+    _flags.force_reference += 1
+    try:
+        yield
+    finally:
+        _flags.force_reference -= 1
+
+
+def _cuda(*tensors: torch.Tensor) -> bool:
+    if _flags.force_reference:
+        return False
+    return all(t is None or t.is_cuda for t in tensors) and any(t is not None for t in tensors)
+
+
+def _ops():
+    from axlearn_b200.ops import cuda_ops
+
+    return cuda_ops
+
+
+def rms_norm(x, scale, eps: float, *, upcast: bool = False):
+    if _cuda(x, scale) and x.dtype in (torch.bfloat16, torch.float32) and x.shape[-1] % 8 == 0:
+        return _ops().rms_norm(x, scale, eps)
+    return reference.rms_norm(x, scale, eps, upcast=upcast)
+
+
+def swiglu(gate, up):
+    if _cuda(gate, up) and gate.dtype == torch.bfloat16:
+        return _ops().swiglu(gate, up)
+    return reference.swiglu(gate, up)
+
+
+def rope(x, positions, theta: float = 10000.0):
+    if _cuda(x) and x.dtype == torch.bfloat16 and positions.dim() == 1:
+        return _ops().rope(x, positions, theta)
+    return reference.rope(x, positions, theta)
+
+
+def linear(x, w):
+    """``x[..., K] @ w[K, N]`` with fp32 accumulation."""
+    if _cuda(x, w) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        return _ops().linear(x, w)
+    return torch.matmul(x, w)
+
+
+def attention(
+    q,
+    k,
+    v,
+    *,
+    bias=None,
+    causal: bool = False,
+    softmax_scale: Optional[float] = None,
+    segment_ids=None,
+    sliding_window: Optional[int] = None,
+    logit_cap: Optional[float] = None,
+    dropout_mask=None,
+):
+    if (
+        _cuda(q, k, v)
+        and q.dtype == torch.bfloat16
+        and bias is None
+        and logit_cap is None
+        and dropout_mask is None
+        and sliding_window is None
+        and _ops().flash_supported(q, k, v, segment_ids)
+    ):
+        return _ops().flash_attention(
+            q, k, v, causal=causal, softmax_scale=softmax_scale, segment_ids=segment_ids
+        )
+    return reference.attention(
+        q,
+        k,
+        v,
+        bias=bias,
+        causal=causal,
+        softmax_scale=softmax_scale,
+        segment_ids=segment_ids,
+        sliding_window=sliding_window,
+        logit_cap=logit_cap,
+        dropout_mask=dropout_mask,
+    )
+
+
+def cross_entropy(logits, targets, *, live_targets=None, z_loss_scale: float = 0.0, denominator=None):
+    if _cuda(logits) and logits.dtype in (torch.bfloat16, torch.float32) and logits.dim() >= 2:
+        return _ops().cross_entropy(
+            logits, targets, live_targets=live_targets, z_loss_scale=z_loss_scale, denominator=denominator
+        )
+    return reference.cross_entropy(
+        logits, targets, live_targets=live_targets, z_loss_scale=z_loss_scale, denominator=denominator
+    )
+
+
+def lm_head_cross_entropy(
+    hidden,
+    weight,
+    targets,
+    *,
+    live_targets=None,
+    z_loss_scale: float = 0.0,
+    denominator=None,
+    chunk_tokens: int = 8192,
+    weight_is_vocab_major: bool = True,
+):
+    """Fused LM head + cross entropy over token chunks: logits ``[chunk, V]`` exist only for
+    one chunk at a time, in forward and in backward (the analogue of the reference's
+    ``scan_chunk`` at axlearn/common/causal_lm.py:637-806).
+
+    hidden: [..., D]; weight: [V, D] (vocab-major) or [D, V]; targets: [...].
+    Returns ``(loss, aux)`` like ``cross_entropy``.
+    """
+    from axlearn_b200.ops.chunked_ce import chunked_lm_head_cross_entropy
+
+    return chunked_lm_head_cross_entropy(
+        hidden,
+        weight,
+        targets,
+        live_targets=live_targets,
+        z_loss_scale=z_loss_scale,
+        denominator=denominator,
+        chunk_tokens=chunk_tokens,
+        weight_is_vocab_major=weight_is_vocab_major,
+    )

@@ -1,0 +1,271 @@
+"""Autograd-aware collectives on mesh axes.
+
+Every function takes mesh axis names, looks up the process group on the mesh in scope and
+degenerates to the identity when that group is trivial — so the same layer code runs on one
+device, on CPU/gloo ranks in tests, and on NCCL ranks.  These are the *baseline* collectives
+(one library call each); the fused peer-memory kernels in ``axlearn_b200.ops`` replace the
+hot ones and are validated against these.
+
+The reference never spells these out: XLA's SPMD partitioner inserts them from sharding
+annotations (axlearn/common/utils.py:637-700 ``with_sharding_constraint``/``maybe_shard``);
+the explicit ones it does write are in axlearn/common/mixture_of_experts.py:2139-2210,
+2670-2726.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from axlearn_b200.parallel.mesh import AxisSpec, Mesh, current_mesh
+
+
+def _group(axes: AxisSpec, mesh: Optional[Mesh] = None):
+    mesh = mesh or current_mesh()
+    if mesh is None:
+        return None, 1, 0
+    present = mesh.present_axes(axes)
+    if not present:
+        return None, 1, 0
+    return mesh.group(present), mesh.axis_size(present), mesh.axis_index(present)
+
+
+def axis_size(axes: AxisSpec) -> int:
+    return _group(axes)[1]
+
+
+def axis_index(axes: AxisSpec) -> int:
+    return _group(axes)[2]
+
+
+# ------------------------------------------------------------------------------------------
+# Raw (non-differentiable) helpers.
+# ------------------------------------------------------------------------------------------
+
+
+def all_gather_raw(x: torch.Tensor, group, world: int, dim: int = 0) -> torch.Tensor:
+    x = x.contiguous()
+    out = torch.empty((world,) + tuple(x.shape), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(out, x, group=group)
+    if dim == 0:
+        return out.reshape((world * x.shape[0],) + tuple(x.shape[1:]))
+    # [W, ..., d, ...] -> [..., W*d, ...]
+    out = out.movedim(0, dim)
+    shape = list(x.shape)
+    shape[dim] *= world
+    return out.reshape(shape)
+
+
+def reduce_scatter_raw(x: torch.Tensor, group, world: int, dim: int = 0) -> torch.Tensor:
+    if dim != 0:
+        shape = list(x.shape)
+        x = x.reshape(shape[:dim] + [world, shape[dim] // world] + shape[dim + 1 :]).movedim(dim, 0)
+    else:
+        x = x.reshape((world, x.shape[0] // world) + tuple(x.shape[1:]))
+    x = x.contiguous()
+    out = torch.empty(x.shape[1:], dtype=x.dtype, device=x.device)
+    dist.reduce_scatter_tensor(out, x, group=group)
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+# Differentiable collectives.
+# ------------------------------------------------------------------------------------------
+
+
+class _AllReduce(torch.autograd.Function):
+    """y = sum over group; dy passes through (the "g" operator of tensor parallelism)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        x = x.contiguous().clone()
+        dist.all_reduce(x, group=group)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+class _IdentityFwdAllReduceBwd(torch.autograd.Function):
+    """y = x; dx = sum over group of dy (the "f" operator of tensor parallelism)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous().clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+class _AllGather(torch.autograd.Function):
+    """Concatenate shards on ``dim``; backward reduce-scatters (sums) the gradient."""
+
+    @staticmethod
+    def forward(ctx, x, group, world, dim):
+        ctx.group, ctx.world, ctx.dim = group, world, dim
+        return all_gather_raw(x, group, world, dim)
+
+    @staticmethod
+    def backward(ctx, g):
+        return reduce_scatter_raw(g, ctx.group, ctx.world, ctx.dim), None, None, None
+
+
+class _ReduceScatter(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group, world, dim):
+        ctx.group, ctx.world, ctx.dim = group, world, dim
+        return reduce_scatter_raw(x, group, world, dim)
+
+    @staticmethod
+    def backward(ctx, g):
+        return all_gather_raw(g, ctx.group, ctx.world, ctx.dim), None, None, None
+
+
+class _AllToAll(torch.autograd.Function):
+    """Splits ``split_dim`` into ``world`` pieces, sends piece r to rank r, concatenates what
+    arrives on ``concat_dim``."""
+
+    @staticmethod
+    def forward(ctx, x, group, world, split_dim, concat_dim):
+        ctx.args = (group, world, split_dim, concat_dim)
+        return _all_to_all_raw(x, group, world, split_dim, concat_dim)
+
+    @staticmethod
+    def backward(ctx, g):
+        group, world, split_dim, concat_dim = ctx.args
+        return _all_to_all_raw(g, group, world, concat_dim, split_dim), None, None, None, None
+
+
+def _all_to_all_raw(x, group, world, split_dim, concat_dim):
+    parts = [p.contiguous() for p in x.chunk(world, dim=split_dim)]
+    outs = [torch.empty_like(parts[0]) for _ in range(world)]
+    dist.all_to_all(outs, parts, group=group)
+    return torch.cat(outs, dim=concat_dim)
+
+
+def psum(x: torch.Tensor, axes: AxisSpec) -> torch.Tensor:
+    """Sum over ``axes``; gradient passes through unchanged."""
+    group, world, _ = _group(axes)
+    if world == 1:
+        return x
+    return _AllReduce.apply(x, group)
+
+
+def psum_grad(x: torch.Tensor, axes: AxisSpec) -> torch.Tensor:
+    """Identity whose *gradient* is summed over ``axes``."""
+    group, world, _ = _group(axes)
+    if world == 1:
+        return x
+    return _IdentityFwdAllReduceBwd.apply(x, group)
+
+
+def all_gather(x: torch.Tensor, axes: AxisSpec, *, dim: int = 0) -> torch.Tensor:
+    group, world, _ = _group(axes)
+    if world == 1:
+        return x
+    return _AllGather.apply(x, group, world, dim % x.dim())
+
+
+def reduce_scatter(x: torch.Tensor, axes: AxisSpec, *, dim: int = 0) -> torch.Tensor:
+    group, world, _ = _group(axes)
+    if world == 1:
+        return x
+    return _ReduceScatter.apply(x, group, world, dim % x.dim())
+
+
+def all_to_all(x: torch.Tensor, axes: AxisSpec, *, split_dim: int, concat_dim: int) -> torch.Tensor:
+    group, world, _ = _group(axes)
+    if world == 1:
+        return x
+    return _AllToAll.apply(x, group, world, split_dim % x.dim(), concat_dim % x.dim())
+
+
+def all_reduce_scalar(x: torch.Tensor, axes: AxisSpec, op: str = "sum") -> torch.Tensor:
+    """Non-differentiable reduction of a small tensor (counts, norms, metrics)."""
+    group, world, _ = _group(axes)
+    if world == 1:
+        return x
+    y = x.detach().clone()
+    dist.all_reduce(y, op={"sum": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN}[op], group=group)
+    return y
+
+
+def barrier(name: str = "") -> None:
+    """Cross-process barrier (no-op without an initialised process group)."""
+    del name
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+
+
+def process_index() -> int:
+    return dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
+
+
+def process_count() -> int:
+    return dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+
+
+# ------------------------------------------------------------------------------------------
+# Parameter un-sharding (FSDP) by partition spec.
+# ------------------------------------------------------------------------------------------
+
+# Axes that shard *parameters for storage only*: a layer gathers over them before use.
+# "model" (and "pipeline") shard the computation itself and are never gathered.
+_COMPUTE_AXES = ("model", "pipeline")
+
+
+def storage_axes(entry: AxisSpec, mesh: Optional[Mesh] = None) -> tuple[str, ...]:
+    mesh = mesh or current_mesh()
+    if mesh is None or entry is None:
+        return ()
+    names = (entry,) if isinstance(entry, str) else tuple(entry)
+    return tuple(a for a in mesh.present_axes(names) if a not in _COMPUTE_AXES)
+
+
+def unshard_param(
+    w: torch.Tensor, mesh_axes: Optional[Sequence[AxisSpec]], *, compute_shape: Optional[Sequence[int]] = None
+) -> torch.Tensor:
+    """Gathers ``w`` over its storage (FSDP) axes; the gradient is reduce-scattered back.
+
+    If ``w`` already has ``compute_shape`` (a prefetcher gathered it ahead of time) it is
+    returned as is.
+    """
+    mesh = current_mesh()
+    if mesh is None or mesh_axes is None or mesh.size == 1:
+        return w
+    if compute_shape is not None and tuple(w.shape) == tuple(compute_shape):
+        return w
+    for dim, entry in enumerate(mesh_axes):
+        axes = storage_axes(entry, mesh)
+        if axes:
+            w = all_gather(w, axes, dim=dim)
+    return w
+
+
+def compute_shape(shape: Sequence[int], mesh_axes: Optional[Sequence[AxisSpec]]) -> tuple[int, ...]:
+    """Shape a parameter has when used in computation: split only over compute axes."""
+    mesh = current_mesh()
+    if mesh is None or mesh_axes is None:
+        return tuple(shape)
+    out = []
+    for d, entry in zip(shape, mesh_axes):
+        names = () if entry is None else ((entry,) if isinstance(entry, str) else tuple(entry))
+        comp = tuple(a for a in mesh.present_axes(names) if a in _COMPUTE_AXES)
+        out.append(d // mesh.axis_size(comp))
+    return tuple(out)
+
+
+def has_axis(entry: AxisSpec, axis: str) -> bool:
+    """True when ``axis`` is named by the spec entry and has extent > 1 on the mesh."""
+    mesh = current_mesh()
+    if mesh is None or entry is None:
+        return False
+    names = (entry,) if isinstance(entry, str) else tuple(entry)
+    return axis in mesh.present_axes(names)
