@@ -359,6 +359,17 @@ class SpmdTrainer(Module):
         return "\n".join(lines)
 
     # ------------------------------------------------------------------ step
+    def train_step(self, host_batch: dict) -> dict:
+        """One optimisation step on a per-process host batch: asynchronous host→device copy of
+        the inputs, forward, backward, update.  Returns ``{"loss", "aux", "summaries"}`` with
+        ``loss`` still on the device (reading it is the caller's device→host sync).  The
+        trainer must have been initialised (``init`` or ``restore_checkpoint``)."""
+        with self._mesh, use_device(self._device):
+            batch = tree_map(
+                lambda t: t.to(self._device, non_blocking=True) if isinstance(t, Tensor) else t, host_batch)
+            self._step += 1
+            return self._train_step(batch)
+
     def _run_step(self, host_batch: dict) -> dict:
         cfg = self._config
         batch = tree_map(lambda t: t.to(self._device, non_blocking=True) if isinstance(t, Tensor) else t, host_batch)

@@ -1,0 +1,434 @@
+"""Python side of the sm_100a kernels: library loading, launch wrappers, autograd Functions.
+
+The kernels live in ``axlearn_b200/csrc`` and are linked into ``axlearn_b200/lib/libaxb200.so``
+with plain C entry points.  They are called through ``ctypes`` with raw device pointers and the
+current CUDA stream, so a launch costs a few microseconds of host time and nothing here
+depends on a PyTorch C++ ABI.  If the library is missing it is built on first use (``nvcc``
+cross-compiles without a GPU); if that is impossible, the first GPU op raises — there is no
+silent fallback to library kernels.
+
+Kernels that wait on hardware barriers do so with a bounded number of polls and report a
+timeout in a per-device status word instead of hanging; ``check_status()`` raises if it is set.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+import threading
+from typing import Optional, Sequence, Union
+
+import torch
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libaxb200.so")
+_lib_lock = threading.Lock()
+_lib_handle: Optional[ctypes.CDLL] = None
+launch_count = 0  # Kernels launched through this module (bench.py reports it).
+
+c_void_p, c_int, c_int64, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
+
+
+def lib() -> ctypes.CDLL:
+    global _lib_handle
+    if _lib_handle is not None:
+        return _lib_handle
+    with _lib_lock:
+        if _lib_handle is None:
+            if not os.path.exists(_LIB_PATH):
+                from axlearn_b200.csrc import build as _build
+
+                _build.build()
+            h = ctypes.CDLL(_LIB_PATH)
+            for name in dir(_Sigs):
+                if name.startswith("axb_"):
+                    fn = getattr(h, name)
+                    fn.argtypes = getattr(_Sigs, name)
+                    fn.restype = c_int
+            _lib_handle = h
+    return _lib_handle
+
+
+class _Sigs:
+    axb_gemm_bf16 = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
+                     c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
+    axb_rmsnorm_fwd = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p]
+    axb_rmsnorm_bwd_ctas = [c_int64]
+    axb_rmsnorm_bwd = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                       c_void_p, c_int64, c_int, c_void_p]
+    axb_swiglu_fwd = [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]
+    axb_swiglu_bwd = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]
+    axb_rope = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_float, c_int, c_void_p]
+    axb_ce_fwd_bwd = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                      c_float, c_int64, c_int, c_int, c_void_p]
+    axb_adamw = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float,
+                 c_float, c_float, c_float, c_float, c_float, c_float, c_void_p]
+    axb_sumsq_ctas = []
+    axb_sumsq = [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_float, c_int, c_void_p]
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _check(rc: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
+    if rc != 0:
+        raise RuntimeError(f"{what}: launcher returned {rc}")
+
+
+# ------------------------------------------------------------------------------------------
+# Status word.
+# ------------------------------------------------------------------------------------------
+
+_status: dict[int, torch.Tensor] = {}
+
+_STATUS_TEXT = {
+    1: "TMA producer gave up waiting for a free stage",
+    2: "MMA issuer gave up waiting for operands / accumulator",
+    3: "epilogue gave up waiting for an accumulator",
+    4: "gave up waiting for a peer flag",
+    5: "bad argument detected on device",
+}
+
+
+def status_word(device: Optional[torch.device] = None) -> torch.Tensor:
+    idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+    if idx not in _status:
+        _status[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+    return _status[idx]
+
+
+def check_status(device: Optional[torch.device] = None, *, clear: bool = True) -> None:
+    """Raises if any kernel on ``device`` reported a bounded-wait timeout (synchronises)."""
+    w = status_word(device)
+    code = int(w.item())
+    if code != 0:
+        if clear:
+            w.zero_()
+        raise RuntimeError(f"device kernel reported status {code}: {_STATUS_TEXT.get(code, 'unknown')}")
+
+
+# ------------------------------------------------------------------------------------------
+# GEMM.
+# ------------------------------------------------------------------------------------------
+
+
+def _operand(t: torch.Tensor, contraction_dim: int) -> tuple[torch.Tensor, int, int]:
+    """Returns (tensor, mn_major flag, leading dim) for a 2-D bf16 operand whose contraction
+    dim is ``contraction_dim``; copies only if the layout is unusable."""
+    other = 1 - contraction_dim
+
+    def usable(x):
+        if x.stride(contraction_dim) == 1 and x.stride(other) % 8 == 0 and x.stride(other) >= x.shape[contraction_dim]:
+            return 0, x.stride(other)
+        if x.stride(other) == 1 and x.stride(contraction_dim) % 8 == 0 and x.stride(contraction_dim) >= x.shape[other]:
+            return 1, x.stride(contraction_dim)
+        return None
+
+    # Degenerate dims (size 1) can make both strides look contiguous; prefer K-major.
+    u = usable(t) if t.data_ptr() % 16 == 0 else None
+    if u is None:
+        t = t.contiguous()
+        u = usable(t)
+        if u is None:
+            raise ValueError(f"GEMM operand of shape {tuple(t.shape)} needs dims that are multiples of 8")
+    return t, u[0], u[1]
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = None,
+         out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False,
+         max_ctas: int = 0) -> torch.Tensor:
+    """``a[M, K] @ b[K, N]`` on the tcgen05 kernel; operands may be transposed views."""
+    assert a.dim() == 2 and b.dim() == 2 and a.shape[1] == b.shape[0], (a.shape, b.shape)
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    m, k = a.shape
+    n = b.shape[1]
+    a, a_mn, lda = _operand(a, 1)
+    b, b_mn, ldb = _operand(b, 0)
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    else:
+        assert out.shape == (m, n) and out.stride(1) == 1
+    if m == 0 or n == 0:
+        return out
+    if k == 0:
+        return out if accumulate else out.zero_()
+    rc = lib().axb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k, lda, ldb, out.stride(0),
+                             a_mn, b_mn, 1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0,
+                             status_word(a.device).data_ptr(), max_ctas, _stream())
+    _check(rc, "axb_gemm_bf16")
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w):  # x: [..., K], w: [K, N] (any strides)
+        ctx.save_for_backward(x, w)
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm(x2, w)
+        return y.reshape(x.shape[:-1] + (w.shape[1],))
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w.t()).reshape(x.shape)
+        if ctx.needs_input_grad[1]:
+            if w.stride(0) == 1 and w.stride(1) != 1:
+                # w is a transposed view of a row-major [N, K] tensor: produce the gradient
+                # directly in that layout so the view's backward is free.
+                dw = gemm(dy2.t(), x2).t()
+            else:
+                dw = gemm(x2.t(), dy2)
+        return dx, dw
+
+
+def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    if x.shape[-1] % 8 or w.shape[1] % 8:
+        return torch.matmul(x, w)
+    return _Linear.apply(x, w)
+
+
+# ------------------------------------------------------------------------------------------
+# RMSNorm.
+# ------------------------------------------------------------------------------------------
+
+
+class _RmsNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, scale, eps):
+        d = x.shape[-1]
+        x2 = x.reshape(-1, d)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        scale_b = scale.to(torch.bfloat16).contiguous()
+        rows = x2.shape[0]
+        y = torch.empty_like(x2)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        _check(lib().axb_rmsnorm_fwd(x2.data_ptr(), None, scale_b.data_ptr(), y.data_ptr(), None,
+                                     rstd.data_ptr(), rows, d, eps, _stream()), "axb_rmsnorm_fwd")
+        ctx.save_for_backward(x2, scale_b, rstd)
+        ctx.scale_dtype = scale.dtype
+        ctx.x_shape = x.shape
+        return y.reshape(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, scale_b, rstd = ctx.saved_tensors
+        d = x2.shape[-1]
+        rows = x2.shape[0]
+        dy2 = dy.reshape(-1, d)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = torch.empty_like(x2)
+        ctas = lib().axb_rmsnorm_bwd_ctas(rows)
+        partial = torch.empty((ctas, d), dtype=torch.float32, device=x2.device)
+        dscale = torch.empty(d, dtype=torch.float32, device=x2.device)
+        _check(lib().axb_rmsnorm_bwd(x2.data_ptr(), scale_b.data_ptr(), rstd.data_ptr(), dy2.data_ptr(),
+                                     None, dx.data_ptr(), partial.data_ptr(), None, dscale.data_ptr(),
+                                     rows, d, _stream()), "axb_rmsnorm_bwd")
+        return dx.reshape(ctx.x_shape), dscale.to(ctx.scale_dtype), None
+
+
+def rms_norm(x: torch.Tensor, scale: torch.Tensor, eps: float) -> torch.Tensor:
+    if x.dtype != torch.bfloat16:
+        from axlearn_b200.ops import reference
+
+        return reference.rms_norm(x, scale, eps, upcast=True)
+    return _RmsNorm.apply(x, scale, float(eps))
+
+
+# ------------------------------------------------------------------------------------------
+# SwiGLU / RoPE.
+# ------------------------------------------------------------------------------------------
+
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate, up):
+        gate, up = gate.contiguous(), up.contiguous()
+        out = torch.empty_like(gate)
+        _check(lib().axb_swiglu_fwd(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(), _stream()),
+               "axb_swiglu_fwd")
+        ctx.save_for_backward(gate, up)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        gate, up = ctx.saved_tensors
+        dout = dout.contiguous()
+        dg, du = torch.empty_like(gate), torch.empty_like(up)
+        _check(lib().axb_swiglu_bwd(gate.data_ptr(), up.data_ptr(), dout.data_ptr(), dg.data_ptr(),
+                                    du.data_ptr(), gate.numel(), _stream()), "axb_swiglu_bwd")
+        return dg, du
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    if gate.numel() % 8:
+        from axlearn_b200.ops import reference
+
+        return reference.swiglu(gate, up)
+    return _SwiGLU.apply(gate, up)
+
+
+class _Rope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, positions, theta):
+        x = x.contiguous()
+        b, t, n, h = x.shape
+        pos = positions.to(device=x.device, dtype=torch.int64).contiguous()
+        y = torch.empty_like(x)
+        _check(lib().axb_rope(x.data_ptr(), y.data_ptr(), pos.data_ptr(), b, t, n, h, theta, 0, _stream()), "axb_rope")
+        ctx.save_for_backward(pos)
+        ctx.theta = theta
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (pos,) = ctx.saved_tensors
+        dy = dy.contiguous()
+        b, t, n, h = dy.shape
+        dx = torch.empty_like(dy)
+        _check(lib().axb_rope(dy.data_ptr(), dx.data_ptr(), pos.data_ptr(), b, t, n, h, ctx.theta, 1, _stream()), "axb_rope")
+        return dx, None, None
+
+
+def rope(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor:
+    return _Rope.apply(x, positions, float(theta))
+
+
+# ------------------------------------------------------------------------------------------
+# Cross entropy.
+# ------------------------------------------------------------------------------------------
+
+
+def ce_chunk(logits: torch.Tensor, targets: torch.Tensor, live: torch.Tensor, z_loss_scale: float,
+             inv_denom: torch.Tensor, need_grad: bool):
+    """Statistics of one ``[n, V]`` chunk; with ``need_grad`` the logits buffer is overwritten by
+    d(loss)/d(logits).  Returns ``(sum_ce, sum_z, sum_correct, dlogits | None)``."""
+    assert logits.dim() == 2 and logits.is_contiguous()
+    n, v = logits.shape
+    tg = targets.to(torch.int64).contiguous()
+    lv = live.to(torch.uint8).contiguous()
+    stats = torch.empty((3, n), dtype=torch.float32, device=logits.device)
+    inv = inv_denom.reshape(1).to(device=logits.device, dtype=torch.float32)
+    _check(lib().axb_ce_fwd_bwd(logits.data_ptr(), 1 if logits.dtype == torch.float32 else 0, tg.data_ptr(),
+                                lv.data_ptr(), stats[0].data_ptr(), stats[1].data_ptr(), stats[2].data_ptr(),
+                                inv.data_ptr(), float(z_loss_scale), n, v, 1 if need_grad else 0, _stream()),
+           "axb_ce_fwd_bwd")
+    sums = stats.sum(dim=1)
+    return sums[0], sums[1], sums[2], (logits if need_grad else None)
+
+
+class _CrossEntropy(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, targets, live, z_loss_scale, denom):
+        v = logits.shape[-1]
+        work = logits.reshape(-1, v).clone()  # The kernel writes the gradient in place.
+        inv = (1.0 / denom).to(torch.float32)
+        need = ctx.needs_input_grad[0]
+        ce, z, correct, dl = ce_chunk(work, targets.reshape(-1), live.reshape(-1), z_loss_scale, inv, need)
+        if need:
+            ctx.save_for_backward(dl)
+            ctx.shape = logits.shape
+        loss = (ce + z_loss_scale * z) * inv
+        ctx.mark_non_differentiable(ce, z, correct)
+        return loss, ce * inv, z * inv, correct * inv
+
+    @staticmethod
+    def backward(ctx, g, *_):
+        (dl,) = ctx.saved_tensors
+        return (dl * g.to(dl.dtype)).reshape(ctx.shape), None, None, None, None
+
+
+def cross_entropy(logits, targets, *, live_targets=None, z_loss_scale: float = 0.0, denominator=None):
+    v = logits.shape[-1]
+    if live_targets is None:
+        live_targets = (targets >= 0) & (targets < v)
+    num_live = live_targets.sum().to(torch.float32)
+    denom = num_live.clamp_min(1.0) if denominator is None else denominator.to(torch.float32)
+    loss, ce, z, acc = _CrossEntropy.apply(logits, targets, live_targets, float(z_loss_scale), denom)
+    return loss, {"cross_entropy_loss": ce, "z_loss": z, "accuracy": acc, "num_live": num_live}
+
+
+# ------------------------------------------------------------------------------------------
+# Optimizer.
+# ------------------------------------------------------------------------------------------
+
+_scale_one: dict[int, torch.Tensor] = {}
+
+
+def multi_tensor_adamw(params, grads, mus, nus, shadows, wd_scales, *, step: int, lr: float,
+                       weight_decay: float, b1: float, b2: float, eps: float,
+                       grad_scale: Union[float, torch.Tensor] = 1.0) -> None:
+    dev = params[0].device
+    if isinstance(grad_scale, torch.Tensor):
+        gs = grad_scale.reshape(1).to(device=dev, dtype=torch.float32)
+    else:
+        gs = torch.full((1,), float(grad_scale), dtype=torch.float32, device=dev)
+    bc1, bc2 = 1.0 - b1**step, 1.0 - b2**step
+    h = lib()
+    stream = _stream()
+    for p, g, m, v, sh, ws in zip(params, grads, mus, nus, shadows, wd_scales):
+        assert p.is_contiguous() and m.is_contiguous() and v.is_contiguous()
+        g = g.contiguous()
+        if g.dtype not in (torch.bfloat16, torch.float32):
+            g = g.float()
+        shadow_ptr = None
+        if sh is not None and sh is not p:
+            assert sh.dtype == torch.bfloat16 and sh.is_contiguous()
+            shadow_ptr = sh.data_ptr()
+        _check(h.axb_adamw(p.data_ptr(), g.data_ptr(), 1 if g.dtype == torch.bfloat16 else 0, m.data_ptr(),
+                           v.data_ptr(), shadow_ptr, gs.data_ptr(), p.numel(), lr, weight_decay * ws, b1, b2,
+                           eps, bc1, bc2, stream), "axb_adamw")
+
+
+def sum_of_squares(tensors: Sequence[torch.Tensor], weights: Optional[Sequence[float]] = None) -> torch.Tensor:
+    """Deterministic ``sum_i w_i * ||t_i||^2`` as a 0-d fp32 device tensor."""
+    dev = tensors[0].device
+    h = lib()
+    out = torch.zeros(1, dtype=torch.float32, device=dev)
+    partial = torch.empty(h.axb_sumsq_ctas(), dtype=torch.float32, device=dev)
+    stream = _stream()
+    for i, t in enumerate(tensors):
+        if t.dtype not in (torch.bfloat16, torch.float32):
+            t = t.float()
+        t = t.contiguous()
+        w = 1.0 if weights is None else float(weights[i])
+        _check(h.axb_sumsq(t.data_ptr(), 1 if t.dtype == torch.bfloat16 else 0, t.numel(), partial.data_ptr(),
+                           out.data_ptr(), w, 1, stream), "axb_sumsq")
+    return out[0]
+
+
+# ------------------------------------------------------------------------------------------
+# Attention and KV-cache kernels are wired in axlearn_b200/ops/attention_ops.py.
+# ------------------------------------------------------------------------------------------
+
+
+def flash_supported(q, k, v, segment_ids) -> bool:
+    from axlearn_b200.ops import attention_ops
+
+    return attention_ops.flash_supported(q, k, v, segment_ids)
+
+
+def flash_attention(q, k, v, *, causal: bool, softmax_scale: Optional[float], segment_ids=None):
+    from axlearn_b200.ops import attention_ops
+
+    return attention_ops.flash_attention(q, k, v, causal=causal, softmax_scale=softmax_scale, segment_ids=segment_ids)
+
+
+def paged_kv_append(pages, new, page_ids, offsets):
+    from axlearn_b200.ops import attention_ops
+
+    return attention_ops.paged_kv_append(pages, new, page_ids, offsets)

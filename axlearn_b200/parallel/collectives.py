@@ -45,27 +45,34 @@ def axis_index(axes: AxisSpec) -> int:
 # ------------------------------------------------------------------------------------------
 
 
+@torch.no_grad()
 def all_gather_raw(x: torch.Tensor, group, world: int, dim: int = 0) -> torch.Tensor:
+    """Concatenation over the group's ranks along ``dim``."""
     x = x.contiguous()
-    out = torch.empty((world,) + tuple(x.shape), dtype=x.dtype, device=x.device)
-    dist.all_gather_into_tensor(out, x, group=group)
+    if x.dim() == 0:
+        x = x.reshape(1)
+    flat = torch.empty((world * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(flat, x, group=group)
     if dim == 0:
-        return out.reshape((world * x.shape[0],) + tuple(x.shape[1:]))
-    # [W, ..., d, ...] -> [..., W*d, ...]
-    out = out.movedim(0, dim)
+        return flat
+    # [W*d0, ...] -> [W, d0, ..., d, ...] -> [d0, ..., W*d, ...]
+    out = flat.reshape((world,) + tuple(x.shape)).movedim(0, dim)
     shape = list(x.shape)
     shape[dim] *= world
     return out.reshape(shape)
 
 
+@torch.no_grad()
 def reduce_scatter_raw(x: torch.Tensor, group, world: int, dim: int = 0) -> torch.Tensor:
+    """Sum over the group, each rank keeping its slice along ``dim``."""
     if dim != 0:
+        # [..., W*d, ...] -> [W, ..., d, ...] -> [W * d0, ...] (rank-major rows).
         shape = list(x.shape)
         x = x.reshape(shape[:dim] + [world, shape[dim] // world] + shape[dim + 1 :]).movedim(dim, 0)
-    else:
-        x = x.reshape((world, x.shape[0] // world) + tuple(x.shape[1:]))
+        x = x.contiguous()
+        x = x.reshape((-1,) + tuple(x.shape[2:]))
     x = x.contiguous()
-    out = torch.empty(x.shape[1:], dtype=x.dtype, device=x.device)
+    out = torch.empty((x.shape[0] // world,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
     dist.reduce_scatter_tensor(out, x, group=group)
     return out
 

@@ -66,18 +66,24 @@ def sharded_sum_of_squares(tree: Any, *, specs: Optional[Any] = None, mesh: Opti
     if not leaves:
         return torch.zeros(())
     device = leaves[0][1].device
-    total = torch.zeros((), dtype=torch.float32, device=device)
-    if mesh is None or mesh.size == 1:
-        sq = torch._foreach_norm([t for _, t in leaves])  # pylint: disable=protected-access
-        return torch.stack([s.float() ** 2 for s in sq]).sum()
-    spec_list = _spec_list(dict(leaves) if False else tree, specs)
-    for (path, t), spec in zip(flatten_items(tree), spec_list):
-        if not isinstance(t, torch.Tensor):
-            continue
-        used = _axes_in_spec(spec.mesh_axes if spec is not None else None)
-        shard_ways = mesh.axis_size(mesh.present_axes(tuple(used)))
-        replication = mesh.size // max(1, shard_ways)
-        total = total + t.float().pow(2).sum() / replication
-    if mesh._real:  # pylint: disable=protected-access
+    from axlearn_b200.ops import dispatch
+
+    use_kernel = device.type == "cuda" and not dispatch._flags.force_reference  # pylint: disable=protected-access
+    weights = [1.0] * len(leaves)
+    if mesh is not None and mesh.size > 1:
+        spec_map = dict(zip([p for p, _ in flatten_items(tree)], _spec_list(tree, specs)))
+        for i, (path, _) in enumerate(leaves):
+            spec = spec_map.get(path)
+            used = _axes_in_spec(spec.mesh_axes if spec is not None else None)
+            shard_ways = mesh.axis_size(mesh.present_axes(tuple(used)))
+            weights[i] = 1.0 / (mesh.size // max(1, shard_ways))
+    if use_kernel:
+        total = dispatch._ops().sum_of_squares([t for _, t in leaves], weights)  # pylint: disable=protected-access
+    else:
+        total = torch.zeros((), dtype=torch.float32, device=device)
+        for (_, t), w in zip(leaves, weights):
+            total = total + t.float().pow(2).sum() * w
+    if mesh is not None and mesh.size > 1 and mesh._real:  # pylint: disable=protected-access
+        total = total.clone()
         dist.all_reduce(total)
     return total

@@ -1,0 +1,280 @@
+"""Headline benchmark: Fuji-7B training throughput (tokens/s) on N B200 GPUs of one node.
+
+Config (BASELINE.json config 2): 32 layers, d_model 4096, 32 heads (MHA), SwiGLU hidden 11008,
+vocab 32768, RoPE, RMSNorm; sequence length 4096; 4 sequences per GPU (32 at 8 GPUs, weak
+scaling); mesh fsdp=N; bf16 compute with fp32 master weights and AdamW moments; full
+rematerialisation per layer; synthetic uniform-random tokens from seed 0; random-init weights.
+
+Two measurements per run:
+  * ``value``: K steps of the trainer's step function on device-resident batches, timed with
+    CUDA events between barriers, max over ranks.
+  * ``e2e``: the same K steps through the public ``SpmdTrainer.train_step(host_batch)`` with a
+    pinned-host → device copy of every batch and a device → host read of every loss.
+
+``--impl reference`` would run the unmodified reference (apple/axlearn, JAX/XLA); it cannot be
+installed offline here (no ``hatchling`` build backend, no ``jax``/``jaxlib``/``tensorstore``
+wheels), so that arm reports ``unavailable``.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+PUBLISHED_TOKENS_PER_S = 65536 / 1.54  # fuji-7B-v2 single host, 8xH100 (fuji.py:1214-1216)
+
+
+def _args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="7B", help="Fuji size (7B is the benchmark; others for debugging)")
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--per_gpu_batch", type=int, default=4)
+    ap.add_argument("--layers", type=int, default=None, help="debug only: override layer count")
+    ap.add_argument("--skip_e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self._idx = gpu_index
+        self._proc = None
+        self._lines: list[str] = []
+        self._thread = None
+
+    def start(self):
+        try:
+            self._proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self._idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self._proc = None
+            return
+        self._thread = threading.Thread(target=self._read, daemon=True)
+        self._thread.start()
+
+    def _read(self):
+        for line in self._proc.stdout:
+            self._lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self._proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self._proc.terminate()
+        try:
+            self._proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self._proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self._lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(sm) if sm else None,
+            "sm_max_mhz": max(mx) if mx else None,
+            "samples": len(sm),
+            "reasons": sorted(reasons),
+        }
+
+
+def main():
+    args = _args()
+    if args.impl == "reference":
+        print(json.dumps({
+            "impl": "reference",
+            "unavailable": "apple/axlearn needs jax/jaxlib(cuda12)/tensorstore/absl/optax wheels and the hatchling "
+                           "build backend; none are in the offline wheelhouse, so it cannot be installed",
+        }))
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    use_cuda = torch.cuda.is_available()  # CPU is only for dry-running this script's plumbing.
+    if use_cuda:
+        torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if use_cuda:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        else:
+            dist.init_process_group("gloo")
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+
+    from axlearn_b200.common import prng
+    from axlearn_b200.common.base_layer import RematSpec, nothing_saveable
+    from axlearn_b200.experiments.text.gpt import fuji
+    from axlearn_b200.experiments.text.gpt.common import (
+        MESH_AXIS_NAMES,
+        adamw_decoupled_learner_config,
+        get_trainer_config_fn,
+        mesh_shape_from_axes,
+    )
+    from axlearn_b200.ops import cuda_ops
+
+    kw = fuji.get_trainer_kwargs(args.model, vocab_size=32768, version=fuji.Version.V2)
+    mk = dict(kw["model_kwargs"])
+    if args.layers:
+        mk["num_layers"] = args.layers
+    model_cfg = fuji.model_config(scan_chunk=8192, **mk)
+    # Full remat per layer: only each layer's input is kept.
+    model_cfg.decoder.transformer.layer.remat_spec = RematSpec(prevent_cse=False, policy=nothing_saveable)
+    global_batch = args.per_gpu_batch * world
+    cfg = get_trainer_config_fn(
+        model_cfg=model_cfg,
+        learner_cfg=adamw_decoupled_learner_config(max_step=kw["max_step"], **kw["learner_kwargs"]),
+        max_step=kw["max_step"], train_batch_size=global_batch, max_sequence_length=args.seq,
+        vocab_size=32768, mesh_shape=mesh_shape_from_axes(fsdp=world), mesh_axis_names=MESH_AXIS_NAMES,
+        train_dtype=torch.bfloat16)()
+    cfg.dir = tempfile.mkdtemp(prefix="axb200_bench_")
+    cfg.device = f"cuda:{local_rank}" if use_cuda else "cpu"
+    trainer = cfg.instantiate(parent=None)
+    trainer.init(prng.PRNGKey(0))
+    num_params = sum(t.numel() for t in _leaves(trainer.trainer_state["model"]))
+    data = iter(trainer.input.dataset())
+    dev = torch.device("cuda", local_rank) if use_cuda else torch.device("cpu")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        if use_cuda:
+            torch.cuda.synchronize()
+
+    class _WallEvent:
+        def __init__(self, enable_timing=True):
+            self.t = 0.0
+
+        def record(self):
+            self.t = time.perf_counter()
+
+        def elapsed_time(self, other):
+            return (other.t - self.t) * 1e3
+
+    Event = torch.cuda.Event if use_cuda else _WallEvent
+
+    tokens_per_step = global_batch * args.seq
+
+    # ----------------------------------------------------------------- device-timed region
+    device_batches = [
+        {k: v.to(dev) for k, v in next(data).items()} for _ in range(min(4, args.warmup + args.steps))]
+    step_fn = trainer._train_step  # pylint: disable=protected-access
+    with trainer.mesh():
+        for i in range(args.warmup):
+            out = step_fn(device_batches[i % len(device_batches)])
+        barrier()
+        if use_cuda:
+            cuda_ops.check_status()
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        launches0 = cuda_ops.launch_count
+        start, end = Event(enable_timing=True), Event(enable_timing=True)
+        barrier()
+        start.record()
+        for i in range(args.steps):
+            out = step_fn(device_batches[(args.warmup + i) % len(device_batches)])
+        end.record()
+        barrier()
+        clocks = sampler.stop()
+        launches = cuda_ops.launch_count - launches0
+        ms = start.elapsed_time(end)
+    loss_value = float(out["loss"])
+    if use_cuda:
+        cuda_ops.check_status()
+    t = torch.tensor([ms], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = t.item() / args.steps
+    value = tokens_per_step / (ms_per_step / 1e3)
+
+    # ----------------------------------------------------------------- end-to-end region
+    e2e = None
+    if not args.skip_e2e:
+        host_batches = [next(data) for _ in range(args.steps)]
+        h2d = sum(v.numel() * v.element_size() for v in host_batches[0].values())
+        barrier()
+        t0 = time.perf_counter()
+        for hb in host_batches:
+            out = trainer.train_step(hb)
+            _ = out["loss"].item()  # device -> host read of the step's result
+        barrier()
+        dt = torch.tensor([time.perf_counter() - t0], device=dev)
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        e2e = {
+            "value": tokens_per_step * args.steps / dt.item(), "unit": "tokens/s",
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+        }
+
+    if rank == 0:
+        # 6 * params * tokens (fwd+bwd) + attention; remat adds one more forward (reported
+        # MFU counts model FLOPs only, i.e. without the recompute).
+        layers, d, heads = mk["num_layers"], mk["hidden_dim"], mk["num_heads"]
+        dense_params = layers * (4 * d * d + 3 * d * 11008) + 32768 * d
+        flops_per_token = 6 * dense_params + 6 * layers * d * args.seq  # causal attention: 12*L*d*T/2
+        peak = 2.25e15
+        result = {
+            "metric": "Fuji-7B train tokens/sec (max over ranks)",
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": value / PUBLISHED_TOKENS_PER_S, "dtype": "bf16", "data": "synthetic",
+            "impl": "ours",
+            "config": {
+                "model": f"fuji-{args.model}-v2" + (f"-{args.layers}layers-DEBUG" if args.layers else ""),
+                "global_batch": global_batch, "seq_len": args.seq, "parallelism": f"fsdp{world}",
+                "remat": "full per layer", "optimizer": "clip_by_global_norm(1)+adamw_decoupled, fp32 master+moments",
+                "l2": "per-step working set (>100 GB of parameters, moments and activations) exceeds the 126 MB L2",
+            },
+            "clocks": clocks,
+            "e2e": e2e,
+            "gpu_launches": launches,
+            "loss": loss_value,
+            "mfu_model_flops_nominal_peak": value * flops_per_token / (peak * world),
+            "local_params": num_params,
+        }
+        print(json.dumps(result))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _leaves(tree):
+    if isinstance(tree, dict):
+        for v in tree.values():
+            yield from _leaves(v)
+    elif tree is not None and hasattr(tree, "numel"):
+        yield tree
+
+
+if __name__ == "__main__":
+    main()

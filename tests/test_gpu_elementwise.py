@@ -1,0 +1,128 @@
+"""Memory-bound kernels vs fp32 PyTorch references."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(a, b, tol):
+    err = (a.float() - b.float()).abs().max().item()
+    scale = b.float().abs().max().item() + 1e-6
+    assert err / scale < tol, f"err {err} scale {scale}"
+
+
+@pytest.mark.parametrize("rows,d", [(64, 128), (1000, 4096), (37, 1024)])
+def test_rmsnorm_fwd_bwd(rows, d):
+    from axlearn_b200.ops import cuda_ops
+
+    torch.manual_seed(0)
+    x = torch.randn(rows, d, device="cuda").bfloat16().requires_grad_()
+    scale = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16().requires_grad_()
+    y = cuda_ops.rms_norm(x, scale, 1e-5)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf, sf = x.detach().float().requires_grad_(), scale.detach().float().requires_grad_()
+    yr = xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + 1e-5) * sf
+    yr.backward(g.float())
+    _close(y, yr, 2e-2)
+    _close(x.grad, xf.grad, 3e-2)
+    _close(scale.grad, sf.grad, 3e-2)
+
+
+def test_swiglu_fwd_bwd():
+    from axlearn_b200.ops import cuda_ops
+
+    torch.manual_seed(0)
+    a = torch.randn(333, 1024, device="cuda").bfloat16().requires_grad_()
+    b = torch.randn(333, 1024, device="cuda").bfloat16().requires_grad_()
+    y = cuda_ops.swiglu(a, b)
+    g = torch.randn_like(y)
+    y.backward(g)
+    af, bf = a.detach().float().requires_grad_(), b.detach().float().requires_grad_()
+    yr = torch.nn.functional.silu(af) * bf
+    yr.backward(g.float())
+    _close(y, yr, 2e-2)
+    _close(a.grad, af.grad, 2e-2)
+    _close(b.grad, bf.grad, 2e-2)
+
+
+def test_rope_fwd_bwd():
+    from axlearn_b200.ops import cuda_ops, reference
+
+    torch.manual_seed(0)
+    x = torch.randn(2, 300, 4, 128, device="cuda").bfloat16().requires_grad_()
+    pos = torch.arange(300, device="cuda")
+    y = cuda_ops.rope(x, pos, 5e5)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf = x.detach().float().requires_grad_()
+    yr = reference.rope(xf, pos, 5e5)
+    yr.backward(g.float())
+    _close(y, yr, 2e-2)
+    _close(x.grad, xf.grad, 2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_cross_entropy_fwd_bwd(dtype):
+    from axlearn_b200.ops import cuda_ops, reference
+
+    torch.manual_seed(0)
+    n, v = 300, 32768
+    logits = (3 * torch.randn(n, v, device="cuda")).to(dtype).requires_grad_()
+    targets = torch.randint(0, v, (n,), device="cuda")
+    targets[::7] = -1
+    live = targets >= 0
+    loss, aux = cuda_ops.cross_entropy(logits, targets, live_targets=live, z_loss_scale=1e-4)
+    loss.backward()
+    lf = logits.detach().float().requires_grad_()
+    loss_r, aux_r = reference.cross_entropy(lf, targets, live_targets=live, z_loss_scale=1e-4)
+    loss_r.backward()
+    assert abs(loss.item() - loss_r.item()) < 2e-3 * abs(loss_r.item())
+    assert abs(aux["accuracy"].item() - aux_r["accuracy"].item()) < 1e-6
+    _close(logits.grad, lf.grad, 2e-2)
+
+
+def test_chunked_lm_head_ce_matches_unfused():
+    from axlearn_b200 import ops
+    from axlearn_b200.ops import reference
+
+    torch.manual_seed(0)
+    n, d, v = 700, 256, 4096
+    h = torch.randn(n, d, device="cuda").bfloat16().requires_grad_()
+    w = (0.05 * torch.randn(v, d, device="cuda")).bfloat16().requires_grad_()
+    t = torch.randint(0, v, (n,), device="cuda")
+    loss, _ = ops.lm_head_cross_entropy(h, w, t, z_loss_scale=1e-4, chunk_tokens=256)
+    loss.backward()
+    hf, wf = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    loss_r, _ = reference.cross_entropy(hf @ wf.t(), t, z_loss_scale=1e-4)
+    loss_r.backward()
+    assert abs(loss.item() - loss_r.item()) < 5e-3 * abs(loss_r.item())
+    _close(h.grad, hf.grad, 5e-2)
+    _close(w.grad, wf.grad, 5e-2)
+
+
+def test_adamw_and_sumsq():
+    from axlearn_b200.ops import cuda_ops, reference
+
+    torch.manual_seed(0)
+    n = 1_000_003
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda").bfloat16()
+    m = torch.randn(n, device="cuda") * 0.1
+    v = torch.rand(n, device="cuda") * 0.1
+    shadow = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    pr, mr, vr = p.clone(), m.clone(), v.clone()
+    scale = torch.tensor(0.5, device="cuda")
+    cuda_ops.multi_tensor_adamw([p], [g], [m], [v], [shadow], [2.0], step=3, lr=1e-2, weight_decay=0.1,
+                                b1=0.9, b2=0.95, eps=1e-8, grad_scale=scale)
+    reference.adamw_step(pr, g, mr, vr, step=3, lr=1e-2, b1=0.9, b2=0.95, eps=1e-8, weight_decay=0.2,
+                         update_scale=1.0, grad_scale=0.5)
+    _close(p, pr, 1e-5)
+    _close(m, mr, 1e-5)
+    _close(v, vr, 1e-5)
+    assert torch.equal(shadow, p.bfloat16())
+    ss = cuda_ops.sum_of_squares([g, p], [1.0, 0.5])
+    ref = g.float().pow(2).sum() + 0.5 * p.pow(2).sum()
+    assert abs(ss.item() - ref.item()) < 1e-4 * ref.item()
+    assert ss.item() == cuda_ops.sum_of_squares([g, p], [1.0, 0.5]).item()

@@ -1,0 +1,77 @@
+"""tcgen05 GEMM vs an fp32 PyTorch reference, over operand layouts, shapes and outputs."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b):
+    return a.float() @ b.float()
+
+
+def _close(out, ref, tol=2e-2):
+    err = (out.float() - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    assert err / scale < tol, f"max err {err} vs scale {scale}"
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (256, 256, 256), (384, 512, 192), (200, 264, 72), (1024, 4096, 1024), (2048, 11008, 512)])
+@pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, False), (True, True)])
+def test_gemm_layouts(m, n, k, a_t, b_t):
+    from axlearn_b200.ops import cuda_ops
+
+    torch.manual_seed(0)
+    dev = "cuda"
+    a = torch.randn(k, m, device=dev).bfloat16().t() if a_t else torch.randn(m, k, device=dev).bfloat16()
+    b = torch.randn(n, k, device=dev).bfloat16().t() if b_t else torch.randn(k, n, device=dev).bfloat16()
+    out = cuda_ops.gemm(a, b)
+    torch.cuda.synchronize()
+    cuda_ops.check_status()
+    _close(out, _ref(a, b))
+
+
+def test_gemm_fp32_out_and_accumulate():
+    from axlearn_b200.ops import cuda_ops
+
+    torch.manual_seed(1)
+    a = torch.randn(256, 320, device="cuda").bfloat16()
+    b = torch.randn(320, 384, device="cuda").bfloat16()
+    out = cuda_ops.gemm(a, b, out_dtype=torch.float32)
+    _close(out, _ref(a, b), tol=1e-3)
+    base = torch.randn(256, 384, device="cuda")
+    acc = base.clone()
+    cuda_ops.gemm(a, b, out=acc, accumulate=True)
+    _close(acc, base + _ref(a, b), tol=1e-3)
+    cuda_ops.check_status()
+
+
+def test_linear_autograd_matches_reference():
+    from axlearn_b200.ops import cuda_ops
+
+    torch.manual_seed(2)
+    x = torch.randn(4, 96, 256, device="cuda").bfloat16().requires_grad_()
+    w = torch.randn(256, 512, device="cuda").bfloat16().requires_grad_()
+    wt = torch.randn(384, 256, device="cuda").bfloat16().requires_grad_()  # used as x @ wt.t()
+    y = cuda_ops.linear(x, w)
+    z = cuda_ops.linear(x, wt.t())
+    g1, g2 = torch.randn_like(y), torch.randn_like(z)
+    (y * g1).sum().backward(retain_graph=True)
+    (z * g2).sum().backward()
+    xf, wf, wtf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_(), wt.detach().float().requires_grad_()
+    yr, zr = xf @ wf, xf @ wtf.t()
+    ((yr * g1.float()).sum() + (zr * g2.float()).sum()).backward()
+    _close(y, yr)
+    _close(z, zr)
+    _close(x.grad, xf.grad)
+    _close(w.grad, wf.grad)
+    _close(wt.grad, wtf.grad)
+    cuda_ops.check_status()
+
+
+def test_gemm_deterministic():
+    from axlearn_b200.ops import cuda_ops
+
+    a = torch.randn(512, 1024, device="cuda").bfloat16()
+    b = torch.randn(1024, 768, device="cuda").bfloat16()
+    assert torch.equal(cuda_ops.gemm(a, b), cuda_ops.gemm(a, b))
