@@ -83,10 +83,14 @@ class FakeLmInput(Input):
         if cfg.global_batch_size % feeds:
             raise ValueError(f"global batch {cfg.global_batch_size} not divisible by {feeds} feeds")
         local = cfg.global_batch_size // feeds
-        base = prng.fold_in(prng.PRNGKey(cfg.seed), index)
+        base = prng.PRNGKey(cfg.seed)
         while cfg.total_num_batches is None or self._batch_index < cfg.total_num_batches:
+            # The global batch is a function of (seed, batch index) only; each feed takes its
+            # rows, so the data does not depend on how many ranks share the batch.
             key = prng.fold_in(base, self._batch_index)
-            tokens = prng.randint(key, (local, cfg.source_length + 1), 0, cfg.vocab_size, dtype=torch.int32)
+            tokens = prng.randint(
+                key, (cfg.global_batch_size, cfg.source_length + 1), 0, cfg.vocab_size, dtype=torch.int32)
+            tokens = tokens[index * local:(index + 1) * local]
             self._batch_index += 1
             yield {
                 "input_ids": _pin(tokens[:, :-1].contiguous()),

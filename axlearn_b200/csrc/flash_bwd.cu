@@ -234,24 +234,30 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       }
       const bool need_mask = (p.causal && s0 + 127 > t0 + p.q_offset) || (s0 + 128 > p.S);
 #pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
-        uint32_t rs[32], rd[32];
-        tmem_ld_32x32(tm_s + lane_base + c, rs);
-        tmem_ld_32x32(tm_dp + lane_base + c, rd);
+      for (int c = 0; c < 128; c += 64) {
+        // 64 score columns and 64 dP columns per TMEM round trip.
+        uint32_t rs[2][32], rd[2][32];
+        tmem_ld_32x32(tm_s + lane_base + c, rs[0]);
+        tmem_ld_32x32(tm_s + lane_base + c + 32, rs[1]);
+        tmem_ld_32x32(tm_dp + lane_base + c, rd[0]);
+        tmem_ld_32x32(tm_dp + lane_base + c + 32, rd[1]);
         tmem_ld_wait();
-        float pv[32], dsv[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float e = exp2f(__uint_as_float(rs[j]) * p.scale_log2 - lse_l2);
-          if (need_mask) {
-            const int col = s0 + c + j;
-            if (col >= p.S || (p.causal && col > row_pos)) e = 0.f;
+        for (int h2 = 0; h2 < 2; ++h2) {
+          float pv[32], dsv[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float e = exp2f(__uint_as_float(rs[h2][j]) * p.scale_log2 - lse_l2);
+            if (need_mask) {
+              const int col = s0 + c + h2 * 32 + j;
+              if (col >= p.S || (p.causal && col > row_pos)) e = 0.f;
+            }
+            pv[j] = e;
+            dsv[j] = e * (__uint_as_float(rd[h2][j]) - delta) * p.scale;
           }
-          pv[j] = e;
-          dsv[j] = e * (__uint_as_float(rd[j]) - delta) * p.scale;
+          store_row_chunk(smem + L::kP, r_in, c + h2 * 32, pv);
+          store_row_chunk(smem + L::kDS, r_in, c + h2 * 32, dsv);
         }
-        store_row_chunk(smem + L::kP, r_in, c, pv);
-        store_row_chunk(smem + L::kDS, r_in, c, dsv);
       }
       fence_proxy_async();
       tc_fence_before_sync();
@@ -460,22 +466,27 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
       const bool need_mask = (p.causal && s0 + 127 > t0 + p.q_offset) || (s0 + 128 > p.S);
 #pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
-        uint32_t rs[32], rd[32];
-        tmem_ld_32x32(tm_s + lane_base + c, rs);
-        tmem_ld_32x32(tm_dp + lane_base + c, rd);
+      for (int c = 0; c < 128; c += 64) {
+        uint32_t rs[2][32], rd[2][32];
+        tmem_ld_32x32(tm_s + lane_base + c, rs[0]);
+        tmem_ld_32x32(tm_s + lane_base + c + 32, rs[1]);
+        tmem_ld_32x32(tm_dp + lane_base + c, rd[0]);
+        tmem_ld_32x32(tm_dp + lane_base + c + 32, rd[1]);
         tmem_ld_wait();
-        float dsv[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float e = exp2f(__uint_as_float(rs[j]) * p.scale_log2 - lse_l2);
-          if (need_mask) {
-            const int col = s0 + c + j;
-            if (col >= p.S || (p.causal && col > row_pos)) e = 0.f;
+        for (int h2 = 0; h2 < 2; ++h2) {
+          float dsv[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float e = exp2f(__uint_as_float(rs[h2][j]) * p.scale_log2 - lse_l2);
+            if (need_mask) {
+              const int col = s0 + c + h2 * 32 + j;
+              if (col >= p.S || (p.causal && col > row_pos)) e = 0.f;
+            }
+            dsv[j] = e * (__uint_as_float(rd[h2][j]) - delta) * p.scale;
           }
-          dsv[j] = e * (__uint_as_float(rd[j]) - delta) * p.scale;
+          store_row_chunk(smem + L::kDS, r_in, c + h2 * 32, dsv);
         }
-        store_row_chunk(smem + L::kDS, r_in, c, dsv);
       }
       fence_proxy_async();
       tc_fence_before_sync();

@@ -9,8 +9,11 @@ import torch
 
 from axlearn_b200.ops import cuda_ops
 
+import os
+
 c_void_p, c_int, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 _configured = False
+FORWARD_VARIANT = os.environ.get("AXB200_FLASH_FWD", "v2")
 
 
 def _lib():
@@ -19,6 +22,8 @@ def _lib():
     if not _configured:
         h.axb_flash_fwd.argtypes = [c_void_p] * 5 + [c_int] * 6 + [c_float, c_int, c_void_p, c_void_p]
         h.axb_flash_fwd.restype = c_int
+        h.axb_flash_fwd_v2.argtypes = h.axb_flash_fwd.argtypes
+        h.axb_flash_fwd_v2.restype = c_int
         h.axb_flash_bwd.argtypes = [c_void_p] * 10 + [c_int] * 6 + [c_float, c_int, c_void_p, c_void_p]
         h.axb_flash_bwd.restype = c_int
         _configured = True
@@ -31,7 +36,11 @@ def forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool, 
     s, nkv = k.shape[1], k.shape[2]
     out = torch.empty_like(q)
     lse = torch.empty((b, n, t), dtype=torch.float32, device=q.device)
-    rc = _lib().axb_flash_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+    h_lib = _lib()
+    # "v2" (two query tiles per CTA, probabilities in tensor memory) is the default;
+    # "v1" (one query tile, probabilities through shared memory) is kept as a cross-check.
+    fn = h_lib.axb_flash_fwd if FORWARD_VARIANT == "v1" else h_lib.axb_flash_fwd_v2
+    rc = fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
                               b, t, s, n, nkv, h, scale, 1 if causal else 0,
                               cuda_ops.status_word(q.device).data_ptr(), cuda_ops._stream())  # pylint: disable=protected-access
     cuda_ops._check(rc, "axb_flash_fwd")  # pylint: disable=protected-access

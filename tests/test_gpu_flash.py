@@ -22,13 +22,17 @@ CASES = [
     (2, 200, 200, 2, 1, 64, True),
     (1, 128, 320, 2, 2, 128, False),
     (1, 1024, 1024, 2, 2, 128, True),
+    (1, 640, 640, 2, 1, 128, True),
+    (2, 300, 300, 2, 2, 64, False),
 ]
 
 
+@pytest.mark.parametrize("variant", ["v2", "v1"])
 @pytest.mark.parametrize("b,t,s,n,nkv,h,causal", CASES)
-def test_flash_fwd_bwd(b, t, s, n, nkv, h, causal):
-    from axlearn_b200.ops import attention_ops, cuda_ops, reference
+def test_flash_fwd_bwd(b, t, s, n, nkv, h, causal, variant, monkeypatch):
+    from axlearn_b200.ops import attention_ops, cuda_ops, flash_sm100, reference
 
+    monkeypatch.setattr(flash_sm100, "FORWARD_VARIANT", variant)
     torch.manual_seed(0)
     q = torch.randn(b, t, n, h, device="cuda").bfloat16().requires_grad_()
     k = torch.randn(b, s, nkv, h, device="cuda").bfloat16().requires_grad_()
@@ -48,10 +52,12 @@ def test_flash_fwd_bwd(b, t, s, n, nkv, h, causal):
     _close(v.grad, vf.grad, 3e-2)
 
 
-def test_flash_large_scores_trigger_rescale():
+@pytest.mark.parametrize("variant", ["v2", "v1"])
+def test_flash_large_scores_trigger_rescale(variant, monkeypatch):
     """Scores that grow along the key axis force the running-max rescale path."""
-    from axlearn_b200.ops import attention_ops, reference
+    from axlearn_b200.ops import attention_ops, flash_sm100, reference
 
+    monkeypatch.setattr(flash_sm100, "FORWARD_VARIANT", variant)
     torch.manual_seed(0)
     b, t, n, h = 1, 512, 1, 128
     q = torch.randn(b, t, n, h, device="cuda").bfloat16()
