@@ -412,7 +412,10 @@ class SpmdTrainer(Module):
                 param_specs=self._model_param_specs, state_updates=oc.state_updates, shadows=self._shadows)
         summaries["learner"] = learner_oc.summaries
         state["prng_key"] = new_key
-        return {"loss": loss.detach(), "aux": aux, "summaries": summaries}
+        # Each rank's loss is its share of the global mean (normalised by the global number of
+        # live targets); the reported loss is the sum of the shares over the batch axes.
+        global_loss = coll.all_reduce_scalar(loss.detach().float(), ("data", "expert", "fsdp"))
+        return {"loss": global_loss, "aux": aux, "summaries": summaries}
 
     def _zero_grads(self) -> None:
         def visit(node, stacked):
