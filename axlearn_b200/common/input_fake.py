@@ -66,12 +66,16 @@ class FakeLmInput(Input):
     def __init__(self, cfg, *, parent=None):
         super().__init__(cfg, parent=parent)
         self._batch_index = 0
+        # The mesh in scope at construction (the trainer builds its children inside its mesh)
+        # decides which rows of the global batch this process feeds; iterating the dataset
+        # later, outside any mesh context, must not change that.
+        self._mesh = current_mesh()
 
     def _feeds(self) -> tuple[int, int]:
         cfg = self._config
         if cfg.num_feeds is not None:
             return cfg.num_feeds, cfg.feed_index or 0
-        mesh = current_mesh()
+        mesh = self._mesh or current_mesh()
         if mesh is None:
             return 1, 0
         axes = mesh.present_axes(("data", "expert", "fsdp"))

@@ -584,6 +584,14 @@ extern "C" int axb_adamw(float* p, const void* g, int g_is_bf16, float* m, float
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
+// The CUDA runtime's current device as seen by this library (diagnostic: it must equal the
+// framework's current device, or launches would land on the wrong GPU).
+extern "C" int axb_current_device() {
+  int dev = -1;
+  cudaGetDevice(&dev);
+  return dev;
+}
+
 // out (+)= weight * sum(x^2). `partial` is an fp32 workspace of axb_sumsq_ctas() entries.
 extern "C" int axb_sumsq_ctas() { return 148 * 4; }
 

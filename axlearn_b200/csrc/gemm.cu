@@ -17,6 +17,8 @@
 // Reference behaviour being replaced: every jnp.einsum of the dense layers lowers to a cuBLAS
 // GEMM in the reference (axlearn/common/layers.py:715-770, axlearn/common/attention.py:536-562,
 // 864-1060).
+#include <string.h>
+
 #include "host_utils.cuh"
 #include "sm100.cuh"
 
@@ -44,10 +46,149 @@ struct GemmParams {
   int accumulate;  // C += A*B (read-modify-write in the epilogue)
 };
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, typename OutT>
+constexpr int kMaxPeers = 8;
+
+// Extra arguments of the fused compute+collective variants (FUSED = true).
+//
+// All-gather of the B operand (FSDP weights) inside the GEMM.  Every rank stores a contiguous
+// row-slab of the operand (`ag_shard_bytes` bytes; `ag_shard_extent` rows).  `ag_copy_ctas`
+// CTAs of this kernel pull each rank's slab from `ag_src[r]` (a peer pointer; the own slab
+// first, then peers in ring order) into this GPU's full-size operand buffer `ag_dst` (slab r at
+// byte offset r * ag_shard_bytes) with bulk asynchronous copies, and publish `ag_epoch` in
+// `ag_flags[r]` when slab r is complete.  The GEMM CTAs read B from `ag_dst` through TMA;
+// before loading a tile they wait (bounded) for the flags of the slabs it touches, and they
+// visit their own slab's tiles first.  `ag_along_k` says whether the slab rows are B's
+// contraction dim (B stored [K, N]) or its N dim (B stored [N, K]).
+//
+// Reduce-scatter of C (weight gradients) out of the epilogue: row m of C belongs to rank
+// m / rs_rows_per_rank and is stored into that rank's staging buffer at slot `rs_rank`
+// (`rs_dst[owner] + (rs_rank * rs_rows_per_rank + m % rs_rows_per_rank) * ldc`), i.e. every
+// rank ends up holding one partial per peer, which it later reduces in a fixed order.
+struct FusedParams {
+  // all-gather of B
+  const void* ag_src[kMaxPeers];
+  void* ag_dst;
+  int* ag_flags;  // [ag_world], this GPU's memory
+  int* ag_cnt;    // [ag_world], zero-initialised arrival counters of the copy CTAs
+  int64_t ag_shard_bytes;
+  int ag_world, ag_rank, ag_epoch, ag_copy_ctas, ag_along_k;
+  int ag_shard_extent;  // rows of the split dim (K or N) per slab
+  // reduce-scatter of C
+  void* rs_dst[kMaxPeers];
+  int rs_world, rs_rank, rs_rows_per_rank;
+};
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Bounded wait until *flag == epoch. Returns false (and records a status) on timeout.
+__device__ __forceinline__ bool wait_flag(const int* flag, int epoch, int* status) {
+  for (uint32_t i = 0; i < (1u << 24); ++i) {
+    if (ld_acquire_sys(flag) == epoch) return true;
+    __nanosleep(64);
+  }
+  if (status != nullptr) atomicCAS(status, 0, kStatusWaitTimeoutPeer);
+  return false;
+}
+
+// Bulk (non-tensor) asynchronous copies used by the copy CTAs of the fused all-gather.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(
+                   reinterpret_cast<uint64_t>(gdst)),
+               "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+
+constexpr int kCopyBufs = 8;
+constexpr uint32_t kCopyChunk = 16384;
+
+// Copy CTA of the fused all-gather: pulls every rank's shard (own first, then ring order) into
+// the local full-size buffer with bulk asynchronous copies staged through shared memory, and
+// publishes a flag per shard once all copy CTAs have finished it.
+__device__ void ag_copy_cta(uint8_t* smem, uint64_t* copy_full, uint64_t* copy_empty, const FusedParams& f,
+                            int* status) {
+  const int warp = threadIdx.x >> 5;
+  const int c = blockIdx.x, num_c = f.ag_copy_ctas;
+  const int64_t shard_bytes = f.ag_shard_bytes;
+  const int64_t chunks_per_shard = (shard_bytes + kCopyChunk - 1) / kCopyChunk;
+  if (warp == 0) {
+    if (elect_one()) {
+      int64_t n = 0;
+      for (int s = 0; s < f.ag_world; ++s) {
+        const int r = (f.ag_rank + s) % f.ag_world;
+        const uint8_t* src = static_cast<const uint8_t*>(f.ag_src[r]);
+        for (int64_t q = c; q < chunks_per_shard; q += num_c, ++n) {
+          const int b = static_cast<int>(n % kCopyBufs);
+          const uint32_t ph = static_cast<uint32_t>((n / kCopyBufs) & 1);
+          if (!mbar_wait(&copy_empty[b], ph ^ 1, status, kStatusWaitTimeoutProducer)) return;
+          const int64_t off = q * kCopyChunk;
+          const int64_t left = shard_bytes - off;
+          const uint32_t bytes = left < static_cast<int64_t>(kCopyChunk) ? static_cast<uint32_t>(left) : kCopyChunk;
+          mbar_arrive_expect_tx(&copy_full[b], bytes);
+          bulk_load(smem + b * kCopyChunk, src + off, bytes, &copy_full[b]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      int64_t n = 0;
+      for (int s = 0; s < f.ag_world; ++s) {
+        const int r = (f.ag_rank + s) % f.ag_world;
+        uint8_t* dst = static_cast<uint8_t*>(f.ag_dst) + r * shard_bytes;
+        int64_t first_unreleased = n;
+        for (int64_t q = c; q < chunks_per_shard; q += num_c, ++n) {
+          const int b = static_cast<int>(n % kCopyBufs);
+          const uint32_t ph = static_cast<uint32_t>((n / kCopyBufs) & 1);
+          if (!mbar_wait(&copy_full[b], ph, status, kStatusWaitTimeoutProducer)) return;
+          const int64_t off = q * kCopyChunk;
+          const int64_t left = shard_bytes - off;
+          const uint32_t bytes = left < static_cast<int64_t>(kCopyChunk) ? static_cast<uint32_t>(left) : kCopyChunk;
+          bulk_store(dst + off, smem + b * kCopyChunk, bytes);
+          tma_store_commit();
+          // Keep up to 4 stores in flight; older ones have released their buffer.
+          tma_store_wait_read<4>();
+          while (first_unreleased + 4 <= n) {
+            mbar_arrive(&copy_empty[first_unreleased % kCopyBufs]);
+            ++first_unreleased;
+          }
+        }
+        // Shard done for this CTA: all of its stores must be complete before the flag.
+        tma_store_wait<0>();
+        while (first_unreleased < n) {
+          mbar_arrive(&copy_empty[first_unreleased % kCopyBufs]);
+          ++first_unreleased;
+        }
+        __threadfence();
+        if (atomicAdd(&f.ag_cnt[r], 1) == num_c - 1) {
+          f.ag_cnt[r] = 0;
+          __threadfence();
+          st_release_sys(&f.ag_flags[r], f.ag_epoch);
+        }
+      }
+    }
+  }
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, typename OutT, bool FUSED>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                 const __grid_constant__ CUtensorMap tmap_b, GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmap_b, GemmParams p,
+                 const __grid_constant__ FusedParams f) {
   using S = GemmSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment is required by the 128B swizzle pattern.
@@ -90,6 +231,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  // CTA roles: with a fused all-gather the first `ag_copy_ctas` CTAs only move data.
+  const bool ag_on = FUSED && f.ag_world > 1;
+  const int copy_ctas = ag_on ? f.ag_copy_ctas : 0;
+  const int cta = static_cast<int>(blockIdx.x) - copy_ctas;   // index among the GEMM CTAs
+  const int num_ctas = static_cast<int>(gridDim.x) - copy_ctas;
+  // Rotation that makes every rank start on its own (already local) slab.
+  const int n_rot = (ag_on && !f.ag_along_k) ? (f.ag_rank * f.ag_shard_extent) / BN : 0;
+  const int kb_rot = (ag_on && f.ag_along_k) ? (f.ag_rank * f.ag_shard_extent) / kBlockK : 0;
+
   auto tile_coords = [&](int t, int& m_blk, int& n_blk) {
     const int per_group = kGroupM * n_blocks;
     const int g = t / per_group;
@@ -98,19 +248,55 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int r = t % per_group;
     m_blk = first_m + r % gsize;
     n_blk = r / gsize;
+    if (FUSED && n_rot) n_blk = (n_blk + n_rot) % n_blocks;
   };
 
-  if (warp == 0) {
+  if (cta < 0) {
+    if constexpr (FUSED) {
+      uint64_t* copy_full = reinterpret_cast<uint64_t*>(bar_base + 256);
+      uint64_t* copy_empty = copy_full + kCopyBufs;
+      if (threadIdx.x == 0) {
+        for (int b = 0; b < kCopyBufs; ++b) {
+          mbar_init(&copy_full[b], 1);
+          mbar_init(&copy_empty[b], 1);
+        }
+        fence_barrier_init();
+        fence_proxy_async();
+      }
+      __syncthreads();
+      ag_copy_cta(smem, copy_full, copy_empty, f, p.status);
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ producer
     if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      uint32_t slab_ready = 0;  // bit r: slab r of the gathered operand has landed
+      auto need_slab = [&](int r) -> bool {
+        if (slab_ready >> r & 1u) return true;
+        if (!wait_flag(&f.ag_flags[r], f.ag_epoch, p.status)) return false;
+        // Later TMA reads (async proxy) must observe the copy CTAs' writes.
+        asm volatile("fence.proxy.async;" ::: "memory");
+        slab_ready |= 1u << r;
+        return true;
+      };
+      for (int t = cta; t < num_tiles && ok; t += num_ctas) {
         int m_blk, n_blk;
         tile_coords(t, m_blk, n_blk);
         const int m0 = m_blk * kBlockM, n0 = n_blk * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        if (FUSED && ag_on && !f.ag_along_k) {
+          const int last = min(n0 + BN, p.N) - 1;
+          for (int r = n0 / f.ag_shard_extent; r <= last / f.ag_shard_extent && ok; ++r) ok = need_slab(r);
+          if (!ok) break;
+        }
+        for (int kbi = 0; kbi < num_kb; ++kbi) {
+          const int kb = FUSED ? (kbi + kb_rot) % num_kb : kbi;
+          if (FUSED && ag_on && f.ag_along_k) {
+            const int k_lo = kb * kBlockK, k_hi = min(k_lo + kBlockK, p.K) - 1;
+            for (int r = k_lo / f.ag_shard_extent; r <= k_hi / f.ag_shard_extent && ok; ++r) ok = need_slab(r);
+            if (!ok) break;
+          }
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kStatusWaitTimeoutProducer)) {
             ok = false;
             break;
@@ -149,7 +335,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = cta; t < num_tiles && ok; t += num_ctas) {
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.status, kStatusWaitTimeoutMma)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -190,7 +376,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int acc = 0;
     uint32_t acc_phase = 0;
     OutT* C = reinterpret_cast<OutT*>(p.C);
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    for (int t = cta; t < num_tiles; t += num_ctas) {
       int m_blk, n_blk;
       tile_coords(t, m_blk, n_blk);
       if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, kStatusWaitTimeoutEpilogue)) break;
@@ -199,6 +385,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int n0 = n_blk * BN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       OutT* crow = C + static_cast<int64_t>(row) * p.ldc + n0;
+      if (FUSED && f.rs_world > 1 && row < p.M) {
+        // Reduce-scatter epilogue: this row goes to its owner's staging slot for this rank
+        // (a store to peer memory over NVLink when the owner is another GPU).
+        const int owner = row / f.rs_rows_per_rank;
+        const int local_row = row - owner * f.rs_rows_per_rank;
+        crow = reinterpret_cast<OutT*>(f.rs_dst[owner]) +
+               (static_cast<int64_t>(f.rs_rank) * f.rs_rows_per_rank + local_row) * p.ldc + n0;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
@@ -270,10 +464,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, typename OutT>
+template <int BN, int STAGES, bool A_MN, bool B_MN, typename OutT, bool FUSED = false>
 static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda,
                        int64_t ldb, int64_t ldc, int accumulate, int* status, int max_ctas,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const FusedParams* fused = nullptr) {
   CUtensorMap ta, tb;
   int rc;
   if (!A_MN) {
@@ -305,7 +499,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   }
   if (rc != 0) return rc;
   using S = GemmSmem<BN, STAGES>;
-  auto kernel = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, OutT>;
+  auto kernel = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, OutT, FUSED>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e =
@@ -320,9 +514,16 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   const int n_blocks = (N + BN - 1) / BN;
   int grid = m_blocks * n_blocks;
   int cap = max_ctas > 0 ? max_ctas : sm_count();
-  if (grid > cap) grid = cap;
+  FusedParams fp;
+  memset(&fp, 0, sizeof(fp));
+  if (FUSED && fused != nullptr) fp = *fused;
+  const int copy_ctas = (FUSED && fp.ag_world > 1) ? fp.ag_copy_ctas : 0;
+  // All CTAs (copy + GEMM) must be co-resident: GEMM CTAs wait on flags the copy CTAs set.
+  if (grid > cap - copy_ctas) grid = cap - copy_ctas;
+  if (grid < 1) return -12;
+  grid += copy_ctas;
   GemmParams p{M, N, K, C, ldc, status, accumulate};
-  kernel<<<grid, kNumThreads, S::kTotal, stream>>>(ta, tb, p);
+  kernel<<<grid, kNumThreads, S::kTotal, stream>>>(ta, tb, p, fp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     fprintf(stderr, "axb gemm: launch failed: %s\n", cudaGetErrorString(e));
@@ -346,6 +547,37 @@ static int dispatch_bn(const void* A, const void* B, void* C, int M, int N, int 
 }
 
 }  // namespace axb
+
+// Fused compute+collective GEMM (bf16 out). `fused` points to a host copy of axb::FusedParams
+// (see the struct for the all-gather-of-B and reduce-scatter-of-C contracts). With
+// ag_world > 1, B must be the local full-size buffer `fused->ag_dst`.
+extern "C" int axb_gemm_bf16_fused(const void* A, const void* B, void* C, int M, int N, int K,
+                                   int64_t lda, int64_t ldb, int64_t ldc, int a_mn_major,
+                                   int b_mn_major, int* status, int max_ctas,
+                                   const void* fused, cudaStream_t stream) {
+  using namespace axb;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const FusedParams* fp = static_cast<const FusedParams*>(fused);
+  if ((lda % 8) || (ldb % 8) || (ldc % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
+      (reinterpret_cast<uintptr_t>(B) & 15))
+    return -10;
+  if (fp->ag_world > 1) {
+    if (fp->ag_world > kMaxPeers || fp->ag_copy_ctas < 1 || (fp->ag_shard_bytes % 16) ||
+        (fp->ag_shard_extent % 256))
+      return -13;
+  }
+  if (fp->rs_world > 1 && (fp->rs_world > kMaxPeers || fp->rs_rows_per_rank * fp->rs_world != M)) return -14;
+#define AXB_FUSED_CASE(AM, BM)                                                                     \
+  if (a_mn_major == (AM ? 1 : 0) && b_mn_major == (BM ? 1 : 0))                                    \
+    return launch_gemm<256, 4, AM, BM, __nv_bfloat16, true>(A, B, C, M, N, K, lda, ldb, ldc, 0,    \
+                                                            status, max_ctas, stream, fp);
+  AXB_FUSED_CASE(false, false)
+  AXB_FUSED_CASE(false, true)
+  AXB_FUSED_CASE(true, false)
+  AXB_FUSED_CASE(true, true)
+#undef AXB_FUSED_CASE
+  return -11;
+}
 
 // C[M,N] (bf16 or fp32, row-major with leading dim ldc) = A * B (+ C when accumulate).
 //   a_mn_major = 0: A is [M, K] row-major (lda = row pitch);  1: A is stored [K, M] row-major.

@@ -25,6 +25,15 @@ _LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file_
 _lib_lock = threading.Lock()
 _lib_handle: Optional[ctypes.CDLL] = None
 launch_count = 0  # Kernels launched through this module (bench.py reports it).
+# SMs left free for communication kernels that run concurrently with compute (NCCL or the
+# peer-memory copy kernels). The persistent GEMM launches at most (SM count - this) CTAs, so
+# that all of its CTAs stay resident and its static tile schedule has no second wave.
+COMM_RESERVED_SMS = int(os.environ.get("AXB200_COMM_SMS", "0"))
+
+
+def reserve_sms_for_comm(n: int) -> None:
+    global COMM_RESERVED_SMS
+    COMM_RESERVED_SMS = max(COMM_RESERVED_SMS, int(n))
 
 c_void_p, c_int, c_int64, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
 
@@ -119,6 +128,16 @@ def check_status(device: Optional[torch.device] = None, *, clear: bool = True) -
 # ------------------------------------------------------------------------------------------
 
 
+_sm_counts: dict[int, int] = {}
+
+
+def _sm_count(device: torch.device) -> int:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _sm_counts:
+        _sm_counts[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _sm_counts[idx]
+
+
 def _operand(t: torch.Tensor, contraction_dim: int) -> tuple[torch.Tensor, int, int]:
     """Returns (tensor, mn_major flag, leading dim) for a 2-D bf16 operand whose contraction
     dim is ``contraction_dim``; copies only if the layout is unusable."""
@@ -159,6 +178,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = None
         return out
     if k == 0:
         return out if accumulate else out.zero_()
+    if max_ctas == 0 and COMM_RESERVED_SMS:
+        max_ctas = max(8, _sm_count(a.device) - COMM_RESERVED_SMS)
     rc = lib().axb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k, lda, ldb, out.stride(0),
                              a_mn, b_mn, 1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0,
                              status_word(a.device).data_ptr(), max_ctas, _stream())

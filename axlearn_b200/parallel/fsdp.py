@@ -14,6 +14,7 @@ the correctness oracle and the fallback of the fused peer-memory path.
 
 from __future__ import annotations
 
+import os
 from typing import Any, Optional, Sequence
 
 import torch
@@ -21,6 +22,11 @@ import torch.distributed as dist
 
 from axlearn_b200.parallel import collectives as coll
 from axlearn_b200.parallel.mesh import Mesh, current_mesh
+
+
+# SMs reserved for communication kernels while a sharded layer stack runs (see
+# cuda_ops.reserve_sms_for_comm); the launcher caps the library collectives to the same number.
+COMM_SMS = int(os.environ.get("AXB200_COMM_SMS", "16"))
 
 
 class _CommStream:
@@ -131,6 +137,11 @@ class LayerParamGatherer:
         dev = self._leaves[0].device if self._leaves else torch.device("cpu")
         self._stream = comm_stream(dev) if self.sharded else None
         self._device = dev
+        if self.sharded and dev.type == "cuda":
+            # Collectives run beside compute: keep a few SMs free for them.
+            from axlearn_b200.ops import cuda_ops
+
+            cuda_ops.reserve_sms_for_comm(COMM_SMS)
 
     def prefetch(self, i: int) -> None:
         if not self.sharded or i in self._ready or not 0 <= i < self._num_layers:

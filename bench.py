@@ -127,6 +127,8 @@ def main():
         torch.cuda.set_device(local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # Collectives share the GPU with persistent compute kernels: cap their CTA count.
+        os.environ.setdefault("NCCL_MAX_CTAS", os.environ.get("AXB200_COMM_SMS", "16"))
         if use_cuda:
             dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         else:
