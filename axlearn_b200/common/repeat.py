@@ -158,16 +158,25 @@ class Repeat(BaseLayer):
         return {"layer": VDict(unflatten_items(list((stacked or {}).items())))}
 
     # ------------------------------------------------------------------ execution
-    def _gatherer(self, stacked_params: Any) -> fsdp.LayerParamGatherer:
+    def _gatherer(self, stacked_params: Any, *, remat: bool = False):
         leaves = [t for _, t in flatten_items(stacked_params)]
-        key = hash(tuple(id(t) for t in leaves))
+        key = hash(tuple(id(t) for t in leaves)) ^ int(remat)
         g = self._gatherer_cache.get(key)
         if g is None:
             mesh = current_mesh()
             specs = self.layer.create_parameter_specs_recursively()
             plans = tree_map(lambda s: fsdp.LeafPlan(mesh, s.mesh_axes), specs, is_leaf=_is_spec)
-            g = fsdp.LayerParamGatherer(stacked_params, plans, self._config.num_layers)
-            self._gatherer_cache = {key: g}
+            from axlearn_b200.parallel import fsdp_fused
+
+            plan_list = [p for _, p in flatten_items(plans, is_leaf=lambda x: isinstance(x, fsdp.LeafPlan))]
+            # The fused path shares one gather buffer per leaf across layers, so it needs the
+            # layer to be replayed (remat) rather than kept for backward.
+            if remat and leaves and fsdp_fused.supported(leaves, plan_list):
+                g = fsdp_fused.FusedLayerGatherer(stacked_params, plans, self._config.num_layers)
+                fsdp_fused.register(g)
+            else:
+                g = fsdp.LayerParamGatherer(stacked_params, plans, self._config.num_layers)
+            self._gatherer_cache[key] = g
         return g
 
     def _run(self, fn: Callable, *, carry: Any, xs: Any = None, collect: bool = False):
@@ -182,11 +191,11 @@ class Repeat(BaseLayer):
         param_items = flatten_items(stacked_params)
         param_paths = [p for p, _ in param_items]
         param_leaves = [t for _, t in param_items]
-        gatherer = self._gatherer(stacked_params)
         layer_cfg = cfg.layer
         remat_spec = getattr(layer_cfg, "remat_spec", None)
         training = ctx.is_training and torch.is_grad_enabled()
         use_remat = bool(training and remat_spec is not None and not remat_spec.saves_everything())
+        gatherer = self._gatherer(stacked_params, remat=use_remat or not training)
         needs_param_grads = training and any(t.requires_grad for t in param_leaves)
         via_function = needs_param_grads and (use_remat or gatherer.sharded or True)
 

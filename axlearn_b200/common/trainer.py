@@ -250,6 +250,36 @@ class SpmdTrainer(Module):
         from axlearn_b200.common.utils import tree_paths
 
         self._shadows = tree_map(lambda t, p: mk(p, t), self._trainer_state["model"], tree_paths(self._trainer_state["model"]))
+        self._place_sharded_shadows_in_symmetric_memory()
+
+    def _place_sharded_shadows_in_symmetric_memory(self) -> None:
+        """Storage-sharded stacked shadows are moved into peer-mapped memory so that the fused
+        FSDP kernels of the other ranks can read this rank's shards over NVLink."""
+        from axlearn_b200.parallel import fsdp_fused
+
+        mesh = self._mesh
+        if self._device.type != "cuda" or mesh.size == 1 or not mesh._real or not fsdp_fused.ENABLED:  # pylint: disable=protected-access
+            return
+        specs = dict(flatten_items(self._model_param_specs, is_leaf=_is_spec))
+
+        def visit(node, prefix, stacked):
+            if isinstance(node, dict):
+                for k in list(node.keys()):
+                    path = f"{prefix}/{k}" if prefix else str(k)
+                    v = node[k]
+                    if isinstance(v, Tensor):
+                        spec = specs.get(path)
+                        if not (stacked or isinstance(node, VDict)) or spec is None or spec.mesh_axes is None:
+                            continue
+                        if v.dtype != torch.bfloat16 or not v.requires_grad:
+                            continue
+                        plan = fsdp.LeafPlan(mesh, tuple(spec.mesh_axes)[1:])
+                        if plan.world > 1 and plan.world <= 8:
+                            node[k] = fsdp_fused.make_symmetric(v.detach(), plan).requires_grad_(True)
+                    else:
+                        visit(v, path, stacked or isinstance(node, VDict))
+
+        visit(self._shadows, "", False)
 
     def restore_checkpoint(self, restore_step: Optional[int] = None) -> Optional[int]:
         """Restores the latest (or given) checkpoint into this trainer; returns its step or
@@ -394,6 +424,10 @@ class SpmdTrainer(Module):
         new_key, _noise_key, fwd_key, _learner_key = prng.split(state["prng_key"], 4)
         batch = self.input.dispatch_global_batch(batch)
         self._zero_grads()
+        if self._device.type == "cuda":
+            from axlearn_b200.parallel import fsdp_fused
+
+            fsdp_fused.begin_step_all()
         (loss, aux), oc = functional(
             self.model, fwd_key, self._shadows, [batch], is_training=True, method="forward")
         loss.backward()
@@ -420,7 +454,11 @@ class SpmdTrainer(Module):
     def _zero_grads(self) -> None:
         def visit(node, stacked):
             if isinstance(node, Tensor):
-                if stacked and node.grad is not None:
+                if stacked and node.requires_grad:
+                    # Stacked leaves keep one persistent gradient buffer that the layer loop
+                    # fills slice by slice.
+                    if node.grad is None:
+                        node.grad = torch.empty_like(node)
                     fsdp.reset_grad_slices(node)
                 else:
                     node.grad = None

@@ -563,7 +563,7 @@ extern "C" int axb_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
     return -10;
   if (fp->ag_world > 1) {
     if (fp->ag_world > kMaxPeers || fp->ag_copy_ctas < 1 || (fp->ag_shard_bytes % 16) ||
-        (fp->ag_shard_extent % 256))
+        fp->ag_shard_extent < 1)
       return -13;
   }
   if (fp->rs_world > 1 && (fp->rs_world > kMaxPeers || fp->rs_rows_per_rank * fp->rs_world != M)) return -14;

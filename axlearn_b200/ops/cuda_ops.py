@@ -187,12 +187,34 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = None
     return out
 
 
+def _fused_fsdp_info(w: torch.Tensor):
+    """The pending-gather record of ``w`` when it is a weight matrix managed by the fused FSDP
+    runtime (gather fused into the forward GEMM, gradient scatter into the weight-gradient GEMM)."""
+    from axlearn_b200.parallel import fsdp_fused
+
+    return fsdp_fused.lookup(w)
+
+
+def _is_nk_view(w: torch.Tensor) -> bool:
+    """True when ``w [K, N]`` is a transposed view of a row-major ``[N, K]`` tensor."""
+    return w.stride(0) == 1 and w.stride(1) != 1
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w):  # x: [..., K], w: [K, N] (any strides)
         ctx.save_for_backward(x, w)
         x2 = x.reshape(-1, x.shape[-1])
-        y = gemm(x2, w)
+        info = _fused_fsdp_info(w)
+        if info is not None and not info.gathered:
+            from axlearn_b200.ops import fused_comm
+            from axlearn_b200.parallel import fsdp_fused
+
+            y = fused_comm.ag_gemm(x2, shard_ptrs=info.shard_ptrs, state=info.state, rank=info.rank,
+                                   weight_is_nk=_is_nk_view(w), copy_ctas=fsdp_fused.COPY_CTAS)
+            info.gathered = True
+        else:
+            y = gemm(x2, w)
         return y.reshape(x.shape[:-1] + (w.shape[1],))
 
     @staticmethod
@@ -206,7 +228,16 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, w.t()).reshape(x.shape)
         if ctx.needs_input_grad[1]:
-            if w.stride(0) == 1 and w.stride(1) != 1:
+            info = _fused_fsdp_info(w)
+            if info is not None:
+                # Rows of the weight gradient go straight to the staging slots of their owners.
+                from axlearn_b200.ops import fused_comm
+
+                if _is_nk_view(w):
+                    fused_comm.gemm_rs(dy2.t(), x2, staging_ptrs=info.staging_ptrs, rank=info.rank)
+                else:
+                    fused_comm.gemm_rs(x2.t(), dy2, staging_ptrs=info.staging_ptrs, rank=info.rank)
+            elif _is_nk_view(w):
                 # w is a transposed view of a row-major [N, K] tensor: produce the gradient
                 # directly in that layout so the view's backward is free.
                 dw = gemm(dy2.t(), x2).t()

@@ -1,0 +1,83 @@
+"""Fused compute+collective kernels on one GPU with local stand-ins for the peers.
+
+All "ranks" are emulated in one process: peer pointers are addresses of other local tensors, and
+each rank's kernel is launched in turn on one stream.  No kernel waits on another launch: the
+all-gather GEMM waits only on flags set by its own copy CTAs, and the flag wait of the
+reduce-scatter runs after the launches that set the flags.
+"""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(a, b, tol=2e-2):
+    err = (a.float() - b.float()).abs().max().item()
+    scale = b.float().abs().max().item() + 1e-6
+    assert err / scale < tol, (err, scale)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("weight_is_nk", [False, True])
+def test_ag_gemm_matches_gather_then_matmul(world, weight_is_nk):
+    from axlearn_b200.ops import cuda_ops, fused_comm
+
+    torch.manual_seed(0)
+    m, k, n = 1024, 2048, 4096
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    w = (torch.randn(n, k, device="cuda") if weight_is_nk else torch.randn(k, n, device="cuda")).bfloat16()
+    shards = [s.contiguous() for s in w.chunk(world, dim=0)]
+    ref = x.float() @ (w.float().t() if weight_is_nk else w.float())
+    for rank in range(world):
+        state = fused_comm.GatherState(w.shape, world, "cuda")
+        state.full.fill_(float("nan"))  # Anything the copy CTAs fail to write would poison the result.
+        for rep in range(2):  # Second call reuses the buffer with a new epoch.
+            out = fused_comm.ag_gemm(x, shard_ptrs=[s.data_ptr() for s in shards], state=state, rank=rank,
+                                     weight_is_nk=weight_is_nk, copy_ctas=4)
+            torch.cuda.synchronize()
+            cuda_ops.check_status()
+            _close(out, ref)
+        assert torch.equal(state.full, w)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_gemm_rs_and_reduce_match_matmul_then_reduce_scatter(world):
+    from axlearn_b200.ops import cuda_ops, fused_comm
+
+    torch.manual_seed(1)
+    m, k, n = 2048, 1024, 512   # dW[m, n] = x^T dy with m rows scattered over `world` owners
+    xs = [torch.randn(k, m, device="cuda").bfloat16() for _ in range(world)]   # per-rank x (tokens x m)
+    dys = [torch.randn(k, n, device="cuda").bfloat16() for _ in range(world)]
+    staging = [torch.full((world, m // world, n), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    flags = [torch.zeros(world, dtype=torch.int32, device="cuda") for _ in range(world)]
+    flag_ptrs = torch.tensor([f.data_ptr() for f in flags], dtype=torch.int64, device="cuda")
+    for rank in range(world):
+        fused_comm.gemm_rs(xs[rank].t(), dys[rank], staging_ptrs=[s.data_ptr() for s in staging], rank=rank)
+        fused_comm.signal_peers(flag_ptrs, world, slot=rank, value=7)
+    total = sum(x.float().t() @ dy.float() for x, dy in zip(xs, dys))
+    for owner in range(world):
+        fused_comm.wait_flags(flags[owner], world, 7)
+        out = torch.empty(m // world, n, device="cuda", dtype=torch.bfloat16)
+        partial = torch.zeros(64, device="cuda")
+        fused_comm.reduce_slots(staging[owner], out, sumsq_partial=partial)
+        torch.cuda.synchronize()
+        cuda_ops.check_status()
+        _close(out, total[owner * (m // world):(owner + 1) * (m // world)])
+        ss = partial.sum().item()
+        ref_ss = out.float().pow(2).sum().item()
+        assert abs(ss - ref_ss) < 1e-3 * ref_ss
+
+
+def test_wait_flags_times_out_cleanly():
+    """A flag nobody sets: the waiter gives up after its poll budget, reports status 4, and the
+    context stays usable."""
+    from axlearn_b200.ops import cuda_ops, fused_comm
+
+    flags = torch.zeros(2, dtype=torch.int32, device="cuda")
+    fused_comm.wait_flags(flags, 2, 1)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="peer flag"):
+        cuda_ops.check_status()
+    cuda_ops.check_status()  # cleared
+    assert torch.ones(4, device="cuda").sum().item() == 4.0
