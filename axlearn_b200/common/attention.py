@@ -1499,9 +1499,16 @@ def set_double_shard_weights_config(
         )
         attn_cfg.output_linear.param_partition_spec = (fsdp_axis_names, tp_axis_names, None)
 
+    def _as_tuple(a):
+        return (a,) if isinstance(a, str) else tuple(a)
+
     def set_ffn(ff_cfg):
         ff_cfg.linear1.param_partition_spec = (fsdp_axis_names, tp_axis_names)
-        ff_cfg.linear2.param_partition_spec = (tp_axis_names, fsdp_axis_names)
+        # The reference shards linear2 as (model, fsdp), i.e. storage-sharded on its *output*
+        # columns.  Here every storage shard is a contiguous row-slab (what the in-kernel
+        # all-gather and the reduce-scatter epilogue move), so linear2's rows are split over
+        # model (major) and then the storage axes; the global shape is unchanged.
+        ff_cfg.linear2.param_partition_spec = (_as_tuple(tp_axis_names) + _as_tuple(fsdp_axis_names), None)
 
     for layer_cfg in cfg if isinstance(cfg, (list, tuple)) else [cfg]:
         set_attn(layer_cfg.self_attention.attention)

@@ -449,6 +449,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         acc_phase ^= 1;
       }
     }
+    // Stores to peer memory are posted: make each writer's rows visible system-wide before the
+    // kernel can complete, so the flag raised by the next launch cannot overtake them.
+    if (FUSED && f.rs_world > 1) __threadfence_system();
   }
 
   // ---------------------------------------------------------------------- tear-down

@@ -126,10 +126,11 @@ class FusedLayerGatherer:
             (num_layers * self._world,), torch.int32, group, dev)
         self._flags.zero_()
         self._flag_ptrs = symm.device_pointer_array(self._flags_sym.peer_ptrs, dev)
-        self._epoch = 0
-        from axlearn_b200.ops import cuda_ops
-
-        cuda_ops.reserve_sms_for_comm(fsdp.COMM_SMS)
+        # The gatherer is built lazily inside the first step, after that step's `begin_step_all`:
+        # start at 1 so that the zero-initialised flags never read as "already signalled".
+        self._epoch = 1
+        # No SMs are set aside here: the copy CTAs are part of the GEMM launch itself, and the
+        # small reduction kernels fit beside resident GEMM CTAs.
         self._flags_sym.barrier()
 
     # ------------------------------------------------------------------ step protocol

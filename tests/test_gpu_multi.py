@@ -1,0 +1,98 @@
+"""Two-GPU checks of the fused FSDP path against the library-collective path.
+
+Needs two visible GPUs (skipped otherwise).  Each case spawns one process per GPU over NCCL on
+127.0.0.1, trains a small Fuji for two steps on both paths from the same initial state, and
+compares losses and the per-layer gradient shards after the first backward.
+"""
+
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _run(rank, world, port, directory, fused, queue):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), AXB200_FUSED_FSDP="1" if fused else "0", NCCL_NVLS_ENABLE="0")
+    sys.path.insert(0, REPO)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from axlearn_b200.common import prng
+        from axlearn_b200.common.base_layer import RematSpec, nothing_saveable
+        from axlearn_b200.common.utils import flatten_items
+        from axlearn_b200.experiments.text.gpt.common import mesh_shape_from_axes
+        from axlearn_b200.ops import cuda_ops
+        from tests.helpers import tiny_fuji_trainer_config
+
+        cfg = tiny_fuji_trainer_config(
+            os.path.join(directory, f"{'fused' if fused else 'nccl'}_{rank}"), max_step=4, save_every_n_steps=1000,
+            train_dtype=torch.bfloat16, device=f"cuda:{rank}", mesh_shape=mesh_shape_from_axes(fsdp=world),
+            hidden=512, heads=4, ffn=1024, vocab=4096, seq=256, batch=4 * world, layers=3, scan_chunk=512,
+            shared_lm_head=True)
+        cfg.model.decoder.transformer.layer.remat_spec = RematSpec(prevent_cse=False, policy=nothing_saveable)
+        trainer = cfg.instantiate(parent=None)
+        trainer.init(prng.PRNGKey(0))
+        data = iter(trainer.input.dataset())
+        losses, grads = [], None
+        for step in range(2):
+            out = trainer.train_step(next(data))
+            losses.append(out["loss"].item())
+            if step == 0:
+                stacked = trainer._shadows["decoder"]["transformer"]["repeat"]["layer"]  # pylint: disable=protected-access
+                grads = {p: t.grad.float().cpu() for p, t in flatten_items(stacked)}
+        torch.cuda.synchronize()
+        cuda_ops.check_status()
+        queue.put((rank, losses, grads, cuda_ops.launch_count))
+    finally:
+        dist.destroy_process_group()
+
+
+def _launch(tmp_path, fused):
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_run, args=(r, world, port, str(tmp_path), fused, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = {}
+    for _ in range(world):
+        rank, losses, grads, launches = q.get(timeout=600)
+        results[rank] = (losses, grads, launches)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    return results
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_fsdp_matches_library_collectives(tmp_path):
+    ref = _launch(tmp_path, fused=False)
+    got = _launch(tmp_path, fused=True)
+    assert got[0][2] > ref[0][2], "the fused path must launch its own signal/reduce kernels"
+    for rank in (0, 1):
+        for a, b in zip(got[rank][0], ref[rank][0]):
+            assert abs(a - b) < 5e-3 * abs(b), (got[rank][0], ref[rank][0])
+        bad = []
+        for path, g in got[rank][1].items():
+            r = ref[rank][1][path]
+            scale = r.abs().max().item() + 1e-8
+            # Per-layer errors make it obvious which slice of a stacked gradient is off.
+            per_layer = [round((g[i] - r[i]).abs().max().item() / scale, 4) for i in range(g.shape[0])]
+            if max(per_layer) >= 3e-2:
+                bad.append((path, per_layer))
+        assert not bad, (rank, bad)

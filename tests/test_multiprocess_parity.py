@@ -50,13 +50,14 @@ def _worker(rank, world, port, directory, mesh_axes, steps, out_queue):
         from axlearn_b200.parallel import collectives as coll
 
         w = trainer.trainer_state["model"]["decoder"]["transformer"]["repeat"]["layer"]["feed_forward"]["linear2"]["weight"]
-        spec = ("model", ("expert", "fsdp", "seq"))
+        spec = (("model", "expert", "fsdp", "seq"), None)
         with trainer.mesh():
             full = w
             for dim, entry in enumerate(spec):
-                axes = trainer.mesh().present_axes(entry)
-                if axes:
-                    full = coll.all_gather_raw(full, trainer.mesh().group(axes), trainer.mesh().axis_size(axes), dim + 1)
+                # A dim split over several axes is major-to-minor: undo the minor axis first.
+                for axis in reversed(trainer.mesh().present_axes(entry)):
+                    full = coll.all_gather_raw(
+                        full, trainer.mesh().group(axis), trainer.mesh().axis_size(axis), dim + 1)
         if rank == 0:
             out_queue.put((losses, full.clone()))
     finally:
