@@ -445,6 +445,8 @@ class SpmdTrainer(Module):
                 model_params=state["model"], gradients=grads, state=state["learner"],
                 param_specs=self._model_param_specs, state_updates=oc.state_updates, shadows=self._shadows)
         summaries["learner"] = learner_oc.summaries
+        if self._device.type == "cuda":
+            fsdp_fused.invalidate_all()  # the shards changed: gather buffers are stale
         state["prng_key"] = new_key
         # Each rank's loss is its share of the global mean (normalised by the global number of
         # live targets); the reported loss is the sum of the shares over the batch axes.

@@ -50,29 +50,39 @@ constexpr int kMaxPeers = 8;
 
 // Extra arguments of the fused compute+collective variants (FUSED = true).
 //
-// All-gather of the B operand (FSDP weights) inside the GEMM.  Every rank stores a contiguous
-// row-slab of the operand (`ag_shard_bytes` bytes; `ag_shard_extent` rows).  `ag_copy_ctas`
-// CTAs of this kernel pull each rank's slab from `ag_src[r]` (a peer pointer; the own slab
-// first, then peers in ring order) into this GPU's full-size operand buffer `ag_dst` (slab r at
-// byte offset r * ag_shard_bytes) with bulk asynchronous copies, and publish `ag_epoch` in
-// `ag_flags[r]` when slab r is complete.  The GEMM CTAs read B from `ag_dst` through TMA;
-// before loading a tile they wait (bounded) for the flags of the slabs it touches, and they
-// visit their own slab's tiles first.  `ag_along_k` says whether the slab rows are B's
-// contraction dim (B stored [K, N]) or its N dim (B stored [N, K]).
+// All-gather of FSDP weights inside the GEMM (a `GatherJob`).  Every rank stores a contiguous
+// row-slab of the weight (`shard_bytes` bytes).  One extra warp in every CTA of this kernel pulls
+// its share of each rank's slab from `src[r]` (peers in ring order, the own slab last) into this
+// GPU's full-size buffer `dst` (slab r at byte offset r * shard_bytes) with bulk asynchronous
+// copies, and `epoch` is published in `flags[r]` when slab r is complete.  Two uses:
+//   carried         the gathered weight is NOT this GEMM's operand (it is the operand of a later
+//                   launch, typically the same matrix of the next layer): the copy simply rides
+//                   along and is complete, by stream order, when this kernel ends;
+//   ag_consume = 1  B is `ag[0].dst` itself: tiles inside the own slab are read straight from the
+//                   shard, other tiles wait (bounded) for the flags of the slabs they touch, and
+//                   every rank starts on its own slab (`ag_shard_extent` rows per slab).
+//                   `ag_along_k` says whether the slab rows are B's contraction dim (B stored
+//                   [K, N]) or its N dim (B stored [N, K]).
 //
 // Reduce-scatter of C (weight gradients) out of the epilogue: row m of C belongs to rank
 // m / rs_rows_per_rank and is stored into that rank's staging buffer at slot `rs_rank`
 // (`rs_dst[owner] + (rs_rank * rs_rows_per_rank + m % rs_rows_per_rank) * ldc`), i.e. every
 // rank ends up holding one partial per peer, which it later reduces in a fixed order.
+struct GatherJob {
+  const void* src[kMaxPeers];  // every rank's slab (peer pointers; the own shard at [rank])
+  void* dst;                   // this GPU's full-size buffer
+  int* flags;                  // [world], this GPU's memory: epoch once slab r is complete
+  int* cnt;                    // [world], zero-initialised arrival counters of the copy warps
+  int64_t shard_bytes;
+  int world, rank, epoch, reserved;
+};
+
 struct FusedParams {
-  // all-gather of B
-  const void* ag_src[kMaxPeers];
-  void* ag_dst;
-  int* ag_flags;  // [ag_world], this GPU's memory
-  int* ag_cnt;    // [ag_world], zero-initialised arrival counters of the copy CTAs
-  int64_t ag_shard_bytes;
-  int ag_world, ag_rank, ag_epoch, ag_copy_ctas, ag_along_k;
-  int ag_shard_extent;  // rows of the split dim (K or N) per slab
+  // Up to two gathers per launch; with ag_consume, ag[0] is the gather of this GEMM's B.
+  GatherJob ag[2];
+  int ag_consume, ag_along_k;
+  int ag_shard_extent;  // consume mode: rows of the split dim (K or N) per slab
+  int reserved;
   // reduce-scatter of C
   void* rs_dst[kMaxPeers];
   int rs_world, rs_rank, rs_rows_per_rank;
@@ -98,7 +108,7 @@ __device__ __forceinline__ bool wait_flag(const int* flag, int epoch, int* statu
   return false;
 }
 
-// Bulk (non-tensor) asynchronous copies used by the copy CTAs of the fused all-gather.
+// Bulk (non-tensor) asynchronous copies used by the copy warps of the fused all-gather.
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
@@ -114,80 +124,93 @@ __device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uin
                : "memory");
 }
 
-constexpr int kCopyBufs = 8;
+constexpr int kCopyBufs = 2;
 constexpr uint32_t kCopyChunk = 16384;
+constexpr int kFusedThreads = kNumThreads + 32;  // + one copy warp per CTA
 
-// Copy CTA of the fused all-gather: pulls every rank's shard (own first, then ring order) into
-// the local full-size buffer with bulk asynchronous copies staged through shared memory, and
-// publishes a flag per shard once all copy CTAs have finished it.
-__device__ void ag_copy_cta(uint8_t* smem, uint64_t* copy_full, uint64_t* copy_empty, const FusedParams& f,
-                            int* status) {
-  const int warp = threadIdx.x >> 5;
-  const int c = blockIdx.x, num_c = f.ag_copy_ctas;
-  const int64_t shard_bytes = f.ag_shard_bytes;
+// Copy warp of the fused all-gather (one per CTA, one elected thread): CTA c moves chunks
+// c, c + G, ... of every slab (peers in ring order, the own slab last) into the local full-size
+// buffer with bulk asynchronous copies staged through two shared-memory buffers, and the last
+// CTA to finish a slab publishes its flag.  No SM is taken away from the GEMM: the copies ride
+// on the otherwise idle bulk-copy path of every CTA.
+__device__ bool ag_copy_warp(uint8_t* bufs, uint64_t* copy_full, const GatherJob& f, int64_t& seq, int* status) {
+  const int c = blockIdx.x, num_c = gridDim.x;
+  const int64_t shard_bytes = f.shard_bytes;
   const int64_t chunks_per_shard = (shard_bytes + kCopyChunk - 1) / kCopyChunk;
-  if (warp == 0) {
-    if (elect_one()) {
-      int64_t n = 0;
-      for (int s = 0; s < f.ag_world; ++s) {
-        const int r = (f.ag_rank + s) % f.ag_world;
-        const uint8_t* src = static_cast<const uint8_t*>(f.ag_src[r]);
-        for (int64_t q = c; q < chunks_per_shard; q += num_c, ++n) {
-          const int b = static_cast<int>(n % kCopyBufs);
-          const uint32_t ph = static_cast<uint32_t>((n / kCopyBufs) & 1);
-          if (!mbar_wait(&copy_empty[b], ph ^ 1, status, kStatusWaitTimeoutProducer)) return;
-          const int64_t off = q * kCopyChunk;
-          const int64_t left = shard_bytes - off;
-          const uint32_t bytes = left < static_cast<int64_t>(kCopyChunk) ? static_cast<uint32_t>(left) : kCopyChunk;
-          mbar_arrive_expect_tx(&copy_full[b], bytes);
-          bulk_load(smem + b * kCopyChunk, src + off, bytes, &copy_full[b]);
-        }
-      }
+  const int64_t mine = c < chunks_per_shard ? (chunks_per_shard - c + num_c - 1) / num_c : 0;  // per slab
+  const int64_t total = mine * f.world;
+  auto locate = [&](int64_t n, const uint8_t*& src, uint8_t*& dst, uint32_t& bytes) {
+    const int s = static_cast<int>(n / mine);
+    const int r = (f.rank + 1 + s) % f.world;  // peers first, own slab last
+    const int64_t off = (c + (n % mine) * num_c) * static_cast<int64_t>(kCopyChunk);
+    const int64_t left = shard_bytes - off;
+    bytes = left < static_cast<int64_t>(kCopyChunk) ? static_cast<uint32_t>(left) : kCopyChunk;
+    src = static_cast<const uint8_t*>(f.src[r]) + off;
+    dst = static_cast<uint8_t*>(f.dst) + r * shard_bytes + off;
+  };
+  auto issue_load = [&](int64_t n) {
+    const uint8_t* src;
+    uint8_t* dst;
+    uint32_t bytes;
+    locate(n, src, dst, bytes);
+    const int b = static_cast<int>((seq + n) % kCopyBufs);
+    mbar_arrive_expect_tx(&copy_full[b], bytes);
+    bulk_load(bufs + b * kCopyChunk, src, bytes, &copy_full[b]);
+  };
+  bool ok = true;
+  tma_store_wait_read<0>();  // a previous job's last stores may still be reading the buffers
+  if (total > 0) issue_load(0);
+  for (int64_t n = 0; n < total && ok; ++n) {
+    if (n + 1 < total) {
+      // Buffer (n+1) % 2 was read by store n-1: wait until that read is over, then refill it.
+      tma_store_wait_read<0>();
+      issue_load(n + 1);
     }
-  } else if (warp == 1) {
-    if (elect_one()) {
-      int64_t n = 0;
-      for (int s = 0; s < f.ag_world; ++s) {
-        const int r = (f.ag_rank + s) % f.ag_world;
-        uint8_t* dst = static_cast<uint8_t*>(f.ag_dst) + r * shard_bytes;
-        int64_t first_unreleased = n;
-        for (int64_t q = c; q < chunks_per_shard; q += num_c, ++n) {
-          const int b = static_cast<int>(n % kCopyBufs);
-          const uint32_t ph = static_cast<uint32_t>((n / kCopyBufs) & 1);
-          if (!mbar_wait(&copy_full[b], ph, status, kStatusWaitTimeoutProducer)) return;
-          const int64_t off = q * kCopyChunk;
-          const int64_t left = shard_bytes - off;
-          const uint32_t bytes = left < static_cast<int64_t>(kCopyChunk) ? static_cast<uint32_t>(left) : kCopyChunk;
-          bulk_store(dst + off, smem + b * kCopyChunk, bytes);
-          tma_store_commit();
-          // Keep up to 4 stores in flight; older ones have released their buffer.
-          tma_store_wait_read<4>();
-          while (first_unreleased + 4 <= n) {
-            mbar_arrive(&copy_empty[first_unreleased % kCopyBufs]);
-            ++first_unreleased;
-          }
-        }
-        // Shard done for this CTA: all of its stores must be complete before the flag.
-        tma_store_wait<0>();
-        while (first_unreleased < n) {
-          mbar_arrive(&copy_empty[first_unreleased % kCopyBufs]);
-          ++first_unreleased;
-        }
+    const int b = static_cast<int>((seq + n) % kCopyBufs);
+    const uint32_t ph = static_cast<uint32_t>(((seq + n) / kCopyBufs) & 1);
+    if (!mbar_wait(&copy_full[b], ph, status, kStatusWaitTimeoutProducer)) {
+      ok = false;
+      break;
+    }
+    const uint8_t* src;
+    uint8_t* dst;
+    uint32_t bytes;
+    locate(n, src, dst, bytes);
+    bulk_store(dst, bufs + b * kCopyChunk, bytes);
+    tma_store_commit();
+    if ((n + 1) % mine == 0) {
+      // Slab done for this CTA: its stores must be complete before the arrival is counted.
+      const int r = (f.rank + 1 + static_cast<int>(n / mine)) % f.world;
+      tma_store_wait<0>();
+      __threadfence();
+      if (atomicAdd(&f.cnt[r], 1) == num_c - 1) {
+        f.cnt[r] = 0;
         __threadfence();
-        if (atomicAdd(&f.ag_cnt[r], 1) == num_c - 1) {
-          f.ag_cnt[r] = 0;
-          __threadfence();
-          st_release_sys(&f.ag_flags[r], f.ag_epoch);
-        }
+        st_release_sys(&f.flags[r], f.epoch);
       }
     }
   }
+  if (ok && mine == 0) {
+    // Nothing to copy (more CTAs than chunks): still count this CTA's arrival for every slab.
+    for (int s = 0; s < f.world; ++s) {
+      const int r = (f.rank + 1 + s) % f.world;
+      if (atomicAdd(&f.cnt[r], 1) == num_c - 1) {
+        f.cnt[r] = 0;
+        __threadfence();
+        st_release_sys(&f.flags[r], f.epoch);
+      }
+    }
+  }
+  tma_store_wait<0>();
+  seq += total;
+  return ok;
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN, typename OutT, bool FUSED>
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__(FUSED ? kFusedThreads : kNumThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                 const __grid_constant__ CUtensorMap tmap_b, GemmParams p,
+                 const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_b_local, GemmParams p,
                  const __grid_constant__ FusedParams f) {
   using S = GemmSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
@@ -208,9 +231,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int num_tiles = m_blocks * n_blocks;
   const int num_kb = (p.K + kBlockK - 1) / kBlockK;
 
+  // Fused all-gather: two barriers and two chunk buffers behind the pipeline's own.
+  uint64_t* copy_full = reinterpret_cast<uint64_t*>(bar_base + 256);
+  uint8_t* copy_bufs = bar_base + S::kBarrierBytes;
+
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if constexpr (FUSED) {
+      tma_prefetch_desc(&tmap_b_local);
+      for (int b = 0; b < kCopyBufs; ++b) mbar_init(&copy_full[b], 1);
+    }
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -231,14 +262,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  // CTA roles: with a fused all-gather the first `ag_copy_ctas` CTAs only move data.
-  const bool ag_on = FUSED && f.ag_world > 1;
-  const int copy_ctas = ag_on ? f.ag_copy_ctas : 0;
-  const int cta = static_cast<int>(blockIdx.x) - copy_ctas;   // index among the GEMM CTAs
-  const int num_ctas = static_cast<int>(gridDim.x) - copy_ctas;
-  // Rotation that makes every rank start on its own (already local) slab.
-  const int n_rot = (ag_on && !f.ag_along_k) ? (f.ag_rank * f.ag_shard_extent) / BN : 0;
-  const int kb_rot = (ag_on && f.ag_along_k) ? (f.ag_rank * f.ag_shard_extent) / kBlockK : 0;
+  const bool copy_on = FUSED && (f.ag[0].world > 1 || f.ag[1].world > 1);  // carries gathers
+  const bool ag_on = FUSED && f.ag_consume && f.ag[0].world > 1;           // ... one of its own B
+  const int cta = static_cast<int>(blockIdx.x);
+  const int num_ctas = static_cast<int>(gridDim.x);
+  // Rows [own_lo, own_hi) of the split dim are this rank's own slab: tiles inside it are read
+  // straight from the shard (`tmap_b_local`), without waiting for any copy.
+  const int own_lo = ag_on ? f.ag[0].rank * f.ag_shard_extent : 0;
+  const int own_hi = own_lo + (ag_on ? f.ag_shard_extent : 0);
+  // Rotation that makes every rank start on the first tile fully inside its own slab.
+  const int n_rot = (ag_on && !f.ag_along_k) ? ((own_lo + BN - 1) / BN) % n_blocks : 0;
+  const int kb_rot = (ag_on && f.ag_along_k) ? ((own_lo + kBlockK - 1) / kBlockK) % num_kb : 0;
 
   auto tile_coords = [&](int t, int& m_blk, int& n_blk) {
     const int per_group = kGroupM * n_blocks;
@@ -251,20 +285,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (FUSED && n_rot) n_blk = (n_blk + n_rot) % n_blocks;
   };
 
-  if (cta < 0) {
+  if (warp == 6) {
+    // ------------------------------------------------------------------ copy warp (fused only)
     if constexpr (FUSED) {
-      uint64_t* copy_full = reinterpret_cast<uint64_t*>(bar_base + 256);
-      uint64_t* copy_empty = copy_full + kCopyBufs;
-      if (threadIdx.x == 0) {
-        for (int b = 0; b < kCopyBufs; ++b) {
-          mbar_init(&copy_full[b], 1);
-          mbar_init(&copy_empty[b], 1);
-        }
-        fence_barrier_init();
-        fence_proxy_async();
+      if (copy_on && elect_one()) {
+        int64_t seq = 0;
+        bool ok = true;
+        for (int j = 0; j < 2 && ok; ++j)
+          if (f.ag[j].world > 1) ok = ag_copy_warp(copy_bufs, copy_full, f.ag[j], seq, p.status);
       }
-      __syncthreads();
-      ag_copy_cta(smem, copy_full, copy_empty, f, p.status);
     }
   } else if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -275,7 +304,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t slab_ready = 0;  // bit r: slab r of the gathered operand has landed
       auto need_slab = [&](int r) -> bool {
         if (slab_ready >> r & 1u) return true;
-        if (!wait_flag(&f.ag_flags[r], f.ag_epoch, p.status)) return false;
+        if (!wait_flag(&f.ag[0].flags[r], f.ag[0].epoch, p.status)) return false;
         // Later TMA reads (async proxy) must observe the copy CTAs' writes.
         asm volatile("fence.proxy.async;" ::: "memory");
         slab_ready |= 1u << r;
@@ -285,16 +314,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         int m_blk, n_blk;
         tile_coords(t, m_blk, n_blk);
         const int m0 = m_blk * kBlockM, n0 = n_blk * BN;
+        bool local = false;  // read this B tile from the own shard
         if (FUSED && ag_on && !f.ag_along_k) {
           const int last = min(n0 + BN, p.N) - 1;
-          for (int r = n0 / f.ag_shard_extent; r <= last / f.ag_shard_extent && ok; ++r) ok = need_slab(r);
+          local = n0 >= own_lo && last < own_hi;
+          for (int r = n0 / f.ag_shard_extent; !local && r <= last / f.ag_shard_extent && ok; ++r)
+            ok = need_slab(r);
           if (!ok) break;
         }
         for (int kbi = 0; kbi < num_kb; ++kbi) {
           const int kb = FUSED ? (kbi + kb_rot) % num_kb : kbi;
           if (FUSED && ag_on && f.ag_along_k) {
             const int k_lo = kb * kBlockK, k_hi = min(k_lo + kBlockK, p.K) - 1;
-            for (int r = k_lo / f.ag_shard_extent; r <= k_hi / f.ag_shard_extent && ok; ++r) ok = need_slab(r);
+            local = k_lo >= own_lo && k_hi < own_hi;
+            for (int r = k_lo / f.ag_shard_extent; !local && r <= k_hi / f.ag_shard_extent && ok; ++r)
+              ok = need_slab(r);
             if (!ok) break;
           }
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kStatusWaitTimeoutProducer)) {
@@ -312,7 +346,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
             for (int j = 0; j < kBlockM / 64; ++j)
               tma_load_2d(sa + j * 8192, &tmap_a, &full_bar[stage], m0 + j * 64, k0);
           }
-          if constexpr (!B_MN) {
+          if (FUSED && local) {
+            // B_MN: slabs split K (rows of the stored [K, N]); otherwise they split N.
+            if constexpr (!B_MN) {
+              tma_load_2d(sb, &tmap_b_local, &full_bar[stage], k0, n0 - own_lo);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(sb + j * 8192, &tmap_b_local, &full_bar[stage], n0 + j * 64, k0 - own_lo);
+            }
+          } else if constexpr (!B_MN) {
             tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
           } else {
 #pragma unroll
@@ -502,11 +545,33 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   }
   if (rc != 0) return rc;
   using S = GemmSmem<BN, STAGES>;
+  FusedParams fp;
+  memset(&fp, 0, sizeof(fp));
+  if (FUSED && fused != nullptr) fp = *fused;
+  // The own shard as a tensor of its own (consume mode): same row pitch, one slab of rows.
+  CUtensorMap tl = tb;
+  if (FUSED && fp.ag[0].world > 1 && fp.ag_consume) {
+    const void* own = fp.ag[0].src[fp.ag[0].rank];
+    const uint64_t ext = static_cast<uint64_t>(fp.ag_shard_extent);
+    uint64_t strides[1] = {static_cast<uint64_t>(ldb) * 2};
+    if (!B_MN) {
+      uint64_t dims[2] = {static_cast<uint64_t>(K), ext};
+      uint32_t box[2] = {kBlockK, BN};
+      rc = make_tensor_map(&tl, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, own, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_128B);
+    } else {
+      uint64_t dims[2] = {static_cast<uint64_t>(N), ext};
+      uint32_t box[2] = {64, kBlockK};
+      rc = make_tensor_map(&tl, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, own, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_128B);
+    }
+    if (rc != 0) return rc;
+  }
+  constexpr int kSmem = S::kTotal + (FUSED ? kCopyBufs * static_cast<int>(kCopyChunk) : 0);
   auto kernel = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, OutT, FUSED>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e =
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
     if (e != cudaSuccess) {
       fprintf(stderr, "axb gemm: cudaFuncSetAttribute: %s\n", cudaGetErrorString(e));
       return -3;
@@ -516,17 +581,13 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   const int m_blocks = (M + kBlockM - 1) / kBlockM;
   const int n_blocks = (N + BN - 1) / BN;
   int grid = m_blocks * n_blocks;
-  int cap = max_ctas > 0 ? max_ctas : sm_count();
-  FusedParams fp;
-  memset(&fp, 0, sizeof(fp));
-  if (FUSED && fused != nullptr) fp = *fused;
-  const int copy_ctas = (FUSED && fp.ag_world > 1) ? fp.ag_copy_ctas : 0;
-  // All CTAs (copy + GEMM) must be co-resident: GEMM CTAs wait on flags the copy CTAs set.
-  if (grid > cap - copy_ctas) grid = cap - copy_ctas;
+  int cap = max_ctas > 0 && max_ctas < sm_count() ? max_ctas : sm_count();
+  // All CTAs must be co-resident (one per SM): tiles may wait on flags that every CTA's copy
+  // warp contributes to.
+  if (grid > cap) grid = cap;
   if (grid < 1) return -12;
-  grid += copy_ctas;
   GemmParams p{M, N, K, C, ldc, status, accumulate};
-  kernel<<<grid, kNumThreads, S::kTotal, stream>>>(ta, tb, p, fp);
+  kernel<<<grid, FUSED ? kFusedThreads : kNumThreads, kSmem, stream>>>(ta, tb, tl, p, fp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     fprintf(stderr, "axb gemm: launch failed: %s\n", cudaGetErrorString(e));
@@ -564,11 +625,12 @@ extern "C" int axb_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
   if ((lda % 8) || (ldb % 8) || (ldc % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
       (reinterpret_cast<uintptr_t>(B) & 15))
     return -10;
-  if (fp->ag_world > 1) {
-    if (fp->ag_world > kMaxPeers || fp->ag_copy_ctas < 1 || (fp->ag_shard_bytes % 16) ||
-        fp->ag_shard_extent < 1)
+  for (int j = 0; j < 2; ++j) {
+    const GatherJob& g = fp->ag[j];
+    if (g.world > 1 && (g.world > kMaxPeers || (g.shard_bytes % 16) || g.rank < 0 || g.rank >= g.world))
       return -13;
   }
+  if (fp->ag_consume && fp->ag[0].world > 1 && fp->ag_shard_extent < 1) return -13;
   if (fp->rs_world > 1 && (fp->rs_world > kMaxPeers || fp->rs_rows_per_rank * fp->rs_world != M)) return -14;
 #define AXB_FUSED_CASE(AM, BM)                                                                     \
   if (a_mn_major == (AM ? 1 : 0) && b_mn_major == (BM ? 1 : 0))                                    \

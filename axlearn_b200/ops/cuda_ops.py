@@ -206,13 +206,17 @@ class _Linear(torch.autograd.Function):
         ctx.save_for_backward(x, w)
         x2 = x.reshape(-1, x.shape[-1])
         info = _fused_fsdp_info(w)
-        if info is not None and not info.gathered:
+        if info is not None and not (info.gathered and info.carry is None):
             from axlearn_b200.ops import fused_comm
-            from axlearn_b200.parallel import fsdp_fused
 
-            y = fused_comm.ag_gemm(x2, shard_ptrs=info.shard_ptrs, state=info.state, rank=info.rank,
-                                   weight_is_nk=_is_nk_view(w), copy_ctas=fsdp_fused.COPY_CTAS)
-            info.gathered = True
+            carry = info.take_carry()  # the same matrix of the neighbouring layer, if not there yet
+            if not info.gathered:
+                y = fused_comm.ag_gemm(x2, shard_ptrs=info.shard_ptrs, state=info.state, rank=info.rank,
+                                       weight_is_nk=_is_nk_view(w), carry=carry)
+                info.gathered = True
+                info.state.holds = info.layer
+            else:
+                y = fused_comm.gemm_carrying_gather(x2, w, shard_ptrs=carry[0], state=carry[1], rank=info.rank)
         else:
             y = gemm(x2, w)
         return y.reshape(x.shape[:-1] + (w.shape[1],))

@@ -1,11 +1,13 @@
 """Fused compute+collective ops over NVLink peer memory.
 
-* ``ag_gemm``: ``x @ W`` where ``W`` is stored as one contiguous row-slab per rank (FSDP).  A few
-  CTAs of the GEMM kernel pull the peers' slabs into a local full-size buffer with bulk
-  asynchronous copies while the remaining CTAs start on the rank's own slab; tiles that need a
-  remote slab wait on a per-slab flag (bounded).  This is the reference's "all-gather the bf16
-  parameters, then matmul" (axlearn/common/attention.py:3803-3850 shardings, collectives
-  inserted by XLA) as one kernel.
+* ``ag_gemm``: ``x @ W`` where ``W`` is stored as one contiguous row-slab per rank (FSDP).  One
+  extra warp in every CTA of the GEMM kernel pulls its share of the peers' slabs into a local
+  full-size buffer with bulk asynchronous copies while the GEMM starts on the rank's own slab
+  (read in place); tiles that need a remote slab wait on a per-slab flag (bounded).  This is the
+  reference's "all-gather the bf16 parameters, then matmul" (axlearn/common/attention.py:3803-3850
+  shardings, collectives inserted by XLA) as one kernel.
+* ``gemm_carrying_gather``: a GEMM on complete operands whose copy warps gather a *different*
+  weight (the next layer's) for a later launch, so that in steady state no GEMM ever waits.
 * ``gemm_rs``: weight-gradient GEMM whose epilogue stores each output row into the staging slot
   of the rank that owns it (a peer store when the owner is another GPU); ``reduce_slots`` then
   sums the per-rank partials in a fixed order.  Together they replace "matmul, then
@@ -28,21 +30,31 @@ MAX_PEERS = 8
 c_void_p, c_int, c_int64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
 
 
+class GatherJob(ctypes.Structure):
+    """Host mirror of ``axb::GatherJob`` (csrc/gemm.cu)."""
+
+    _fields_ = [
+        ("src", c_void_p * MAX_PEERS),
+        ("dst", c_void_p),
+        ("flags", c_void_p),
+        ("cnt", c_void_p),
+        ("shard_bytes", c_int64),
+        ("world", c_int),
+        ("rank", c_int),
+        ("epoch", c_int),
+        ("reserved", c_int),
+    ]
+
+
 class FusedParams(ctypes.Structure):
     """Host mirror of ``axb::FusedParams`` (csrc/gemm.cu)."""
 
     _fields_ = [
-        ("ag_src", c_void_p * MAX_PEERS),
-        ("ag_dst", c_void_p),
-        ("ag_flags", c_void_p),
-        ("ag_cnt", c_void_p),
-        ("ag_shard_bytes", c_int64),
-        ("ag_world", c_int),
-        ("ag_rank", c_int),
-        ("ag_epoch", c_int),
-        ("ag_copy_ctas", c_int),
+        ("ag", GatherJob * 2),
+        ("ag_consume", c_int),
         ("ag_along_k", c_int),
         ("ag_shard_extent", c_int),
+        ("reserved", c_int),
         ("rs_dst", c_void_p * MAX_PEERS),
         ("rs_world", c_int),
         ("rs_rank", c_int),
@@ -83,37 +95,46 @@ class GatherState:
         self.epoch = 0
 
 
+def _fill_gather(job: GatherJob, shard_ptrs: Sequence[int], state, rank: int) -> None:
+    world = len(shard_ptrs)
+    rows, cols = state.full.shape
+    assert rows % world == 0 and 1 < world <= MAX_PEERS
+    state.epoch += 1
+    for r, p in enumerate(shard_ptrs):
+        job.src[r] = p
+    job.dst = state.full.data_ptr()
+    job.flags = state.flags.data_ptr()
+    job.cnt = state.cnt.data_ptr()
+    job.shard_bytes = (rows // world) * cols * 2
+    job.world, job.rank, job.epoch = world, rank, state.epoch
+
+
 def ag_gemm(x: torch.Tensor, *, shard_ptrs: Sequence[int], state: GatherState, rank: int,
-            weight_is_nk: bool = False, copy_ctas: int = 8, out: Optional[torch.Tensor] = None,
+            weight_is_nk: bool = False, carry: Optional[tuple] = None, out: Optional[torch.Tensor] = None,
             max_ctas: int = 0) -> torch.Tensor:
-    """``x[M, K] @ W`` with W gathered inside the kernel.
+    """``x[M, K] @ W`` with W gathered inside the kernel that consumes it.
 
     ``shard_ptrs[r]`` is the address of rank r's slab (``W[r*rows/R:(r+1)*rows/R]``), its own for
     ``r == rank``.  ``state.full`` has W's full shape: ``[K, N]`` (slabs split the contraction
     dim) or, with ``weight_is_nk``, ``[N, K]`` used as ``x @ W^T`` (slabs split the output dim).
-    After the call ``state.full`` holds the whole of W and can be reused (e.g. by the backward).
+    Tiles inside the rank's own slab are read from the shard itself; the rest wait for the
+    slabs as they land.  After the call ``state.full`` holds the whole of W.  ``carry`` =
+    ``(shard_ptrs, state)`` of a second, unrelated matrix to gather in the same launch (see
+    ``gemm_carrying_gather``).
     """
-    world = len(shard_ptrs)
     full = state.full
     rows, cols = full.shape
     x2 = x.reshape(-1, x.shape[-1])
     m, k = x2.shape
     n = rows if weight_is_nk else cols
     assert (cols if weight_is_nk else rows) == k, (full.shape, x2.shape)
-    assert rows % world == 0
     if out is None:
         out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
-    state.epoch += 1
     fp = FusedParams()
-    for r, p in enumerate(shard_ptrs):
-        fp.ag_src[r] = p
-    fp.ag_dst = full.data_ptr()
-    fp.ag_flags = state.flags.data_ptr()
-    fp.ag_cnt = state.cnt.data_ptr()
-    fp.ag_shard_bytes = (rows // world) * cols * 2
-    fp.ag_world, fp.ag_rank, fp.ag_epoch, fp.ag_copy_ctas = world, rank, state.epoch, copy_ctas
-    fp.ag_along_k = 0 if weight_is_nk else 1
-    fp.ag_shard_extent = rows // world
+    _fill_gather(fp.ag[0], shard_ptrs, state, rank)
+    fp.ag_consume, fp.ag_along_k, fp.ag_shard_extent = 1, 0 if weight_is_nk else 1, rows // len(shard_ptrs)
+    if carry is not None:
+        _fill_gather(fp.ag[1], carry[0], carry[1], rank)
     fp.rs_world = 1
     x2c, a_mn, lda = cuda_ops._operand(x2, 1)  # pylint: disable=protected-access
     # B as the kernel sees it: [K, N]. weight_is_nk: stored [N, K] -> K-major B (b_mn = 0).
@@ -123,6 +144,33 @@ def ag_gemm(x: torch.Tensor, *, shard_ptrs: Sequence[int], state: GatherState, r
                                     out.stride(0), a_mn, b_mn, cuda_ops.status_word(x.device).data_ptr(), cap,
                                     ctypes.addressof(fp), cuda_ops._stream())  # pylint: disable=protected-access
     cuda_ops._check(rc, "axb_gemm_bf16_fused(ag)")  # pylint: disable=protected-access
+    return out.reshape(x.shape[:-1] + (n,))
+
+
+def gemm_carrying_gather(x: torch.Tensor, w: torch.Tensor, *, shard_ptrs: Sequence[int], state: GatherState,
+                         rank: int, out: Optional[torch.Tensor] = None, max_ctas: int = 0) -> torch.Tensor:
+    """``x[M, K] @ w[K, N]`` (``w`` complete and local) while the same kernel's copy warps gather
+    *another* matrix -- ``shard_ptrs`` into ``state.full`` -- for a later launch.
+
+    Nothing in this kernel waits for the copy: it hides under the GEMM and is complete, by
+    stream order, when the kernel ends (this is how layer i+1's weights arrive during layer i).
+    """
+    x2 = x.reshape(-1, x.shape[-1])
+    m, k = x2.shape
+    n = w.shape[1]
+    assert w.shape[0] == k
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    fp = FusedParams()
+    _fill_gather(fp.ag[0], shard_ptrs, state, rank)
+    fp.rs_world = 1
+    x2c, a_mn, lda = cuda_ops._operand(x2, 1)  # pylint: disable=protected-access
+    w2, b_mn, ldb = cuda_ops._operand(w, 0)  # pylint: disable=protected-access
+    cap = max_ctas or (cuda_ops._sm_count(x.device) - cuda_ops.COMM_RESERVED_SMS)  # pylint: disable=protected-access
+    rc = _lib().axb_gemm_bf16_fused(x2c.data_ptr(), w2.data_ptr(), out.data_ptr(), m, n, k, lda, ldb,
+                                    out.stride(0), a_mn, b_mn, cuda_ops.status_word(x.device).data_ptr(), cap,
+                                    ctypes.addressof(fp), cuda_ops._stream())  # pylint: disable=protected-access
+    cuda_ops._check(rc, "axb_gemm_bf16_fused(carry)")  # pylint: disable=protected-access
     return out.reshape(x.shape[:-1] + (n,))
 
 
@@ -136,7 +184,6 @@ def gemm_rs(a: torch.Tensor, b: torch.Tensor, *, staging_ptrs: Sequence[int], ra
     a2, a_mn, lda = cuda_ops._operand(a, 1)  # pylint: disable=protected-access
     b2, b_mn, ldb = cuda_ops._operand(b, 0)  # pylint: disable=protected-access
     fp = FusedParams()
-    fp.ag_world = 1
     for r, p in enumerate(staging_ptrs):
         fp.rs_dst[r] = p
     fp.rs_world, fp.rs_rank, fp.rs_rows_per_rank = world, rank, m // world

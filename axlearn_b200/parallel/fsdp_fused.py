@@ -3,11 +3,17 @@
 Drop-in alternative to ``fsdp.LayerParamGatherer`` for stacked layers whose storage-sharded
 leaves live in symmetric (peer-mapped) memory:
 
-* **No gather step.**  ``get(i)`` hands the layer full-shape *views* of per-leaf scratch buffers
-  that are still empty, and registers each weight matrix in them as a pending gather.  The first
-  ``linear`` that consumes a matrix runs ``fused_comm.ag_gemm``: copy CTAs of the GEMM kernel
-  pull the peers' row-slabs into the buffer while the other CTAs start on the local slab.  Later
-  users of the same matrix in that layer (the data-gradient GEMM) find it complete.
+* **No gather step.**  ``get(i)`` hands the layer full-shape *views* of per-leaf gather buffers
+  (two per leaf, alternating with the layer's parity).  Each weight matrix in them is gathered
+  by copy warps that ride inside a GEMM kernel (``ops/fused_comm.py``):
+
+  - in steady state the matrix of layer ``i +/- 1`` is gathered by the GEMM that uses the same
+    matrix of layer ``i`` (``gemm_carrying_gather``): the transfer hides under that GEMM, is
+    complete by stream order when the next layer starts, and no kernel ever waits on a flag;
+  - a matrix that nobody gathered ahead of time (the first layer of a step) is gathered by the
+    very GEMM that consumes it (``ag_gemm``): tiles of the rank's own slab are read in place
+    while the peers' slabs arrive, later tiles wait on per-slab flags (bounded).
+
 * **No reduce-scatter step.**  The weight-gradient GEMM of a registered matrix stores each
   output row into the owning rank's staging slot (``fused_comm.gemm_rs``); after the layer's
   backward every rank signals its peers, and on the side stream the owner waits for all
@@ -34,22 +40,33 @@ import torch
 from axlearn_b200.parallel import fsdp, symm
 
 ENABLED = os.environ.get("AXB200_FUSED_FSDP", "1") != "0"
-COPY_CTAS = int(os.environ.get("AXB200_AG_COPY_CTAS", "8"))
 
 
 class PendingMatrix:
-    """One 2-D weight matrix inside a gather buffer."""
+    """One 2-D weight matrix of one layer inside a gather buffer."""
 
-    __slots__ = ("full", "shard_ptrs", "state", "rank", "world", "gathered", "staging_ptrs", "rows", "cols")
+    __slots__ = ("full", "shard_ptrs", "state", "rank", "world", "layer", "gathered", "staging_ptrs", "carry")
 
-    def __init__(self, full, shard_ptrs, state, rank, world, staging_ptrs):
+    def __init__(self, full, shard_ptrs, state, rank, world, layer, gathered, staging_ptrs):
         self.full = full                # [rows, cols] view of the gather buffer
-        self.shard_ptrs = shard_ptrs    # address of every rank's row-slab
-        self.state = state              # fused_comm.GatherState-like (flags, cnt, epoch)
+        self.shard_ptrs = shard_ptrs    # address of every rank's row-slab of this layer's matrix
+        self.state = state              # _MatrixState of the buffer (flags, cnt, epoch, holds)
         self.rank, self.world = rank, world
-        self.gathered = False
+        self.layer = layer
+        self.gathered = gathered        # the buffer already holds this layer's matrix
         self.staging_ptrs = staging_ptrs  # every rank's staging buffer [R, rows/R, cols]
-        self.rows, self.cols = full.shape
+        # (shard_ptrs, _MatrixState, layer) of the matrix to gather for the neighbouring layer
+        # inside this matrix's forward GEMM.
+        self.carry = None
+
+    def take_carry(self):
+        """The pending neighbour gather, marked as issued (call right before launching it)."""
+        c, self.carry = self.carry, None
+        if c is None:
+            return None
+        ptrs, state, layer = c
+        state.holds = layer
+        return ptrs, state
 
 
 # Weight matrices whose gather / gradient scatter is fused into the GEMMs, keyed by address.
@@ -68,6 +85,7 @@ class _MatrixState:
         self.flags = torch.zeros(world, dtype=torch.int32, device=full2d.device)
         self.cnt = torch.zeros(world, dtype=torch.int32, device=full2d.device)
         self.epoch = 0
+        self.holds = -1  # layer whose matrix the buffer holds (or will, by stream order)
 
 
 class _Leaf:
@@ -83,14 +101,23 @@ class _Leaf:
         self.world = plan.world
         self.full_shape = shape[:d] + (self.rows_local * self.world,) + shape[d + 1:]
         dev = stacked.device
-        self.buffer = torch.empty(self.full_shape, dtype=stacked.dtype, device=dev)
         rows = self.rows_local * self.world
+        # Two gather buffers: layer i lives in buffer i % 2 while its neighbour arrives in the other.
+        self.buffers = [torch.empty(self.full_shape, dtype=stacked.dtype, device=dev) for _ in range(2)]
         self.mats = [
-            _MatrixState(self.buffer.reshape(self.nb, rows, self.cols)[j], self.world) for j in range(self.nb)
+            [_MatrixState(buf.reshape(self.nb, rows, self.cols)[j], self.world) for j in range(self.nb)]
+            for buf in self.buffers
         ]
         # Staging for the gradient partials of every layer: [L, nb, R, rows/R, cols].
         self.staging, self.staging_sym = symm.symmetric_empty_like_sharded(
             (num_layers, self.nb, self.world, self.rows_local, self.cols), stacked.dtype, plan.group, dev)
+
+    def shard_ptrs(self, i: int) -> list[list[int]]:
+        """Per matrix of layer ``i``: the address of every rank's slab."""
+        shard = self.stacked[i]
+        peer_base = self.sym.peer_addresses(shard)
+        mat_bytes = self.rows_local * self.cols * shard.element_size()
+        return [[p + j * mat_bytes for p in peer_base] for j in range(self.nb)]
 
 
 class FusedLayerGatherer:
@@ -129,8 +156,8 @@ class FusedLayerGatherer:
         # The gatherer is built lazily inside the first step, after that step's `begin_step_all`:
         # start at 1 so that the zero-initialised flags never read as "already signalled".
         self._epoch = 1
-        # No SMs are set aside here: the copy CTAs are part of the GEMM launch itself, and the
-        # small reduction kernels fit beside resident GEMM CTAs.
+        self._current: Optional[int] = None
+        self._current_records: list[list[PendingMatrix]] = []
         self._flags_sym.barrier()
 
     # ------------------------------------------------------------------ step protocol
@@ -138,28 +165,47 @@ class FusedLayerGatherer:
         """Cross-rank barrier: peers' parameter shards are final, and their reductions of the
         previous step no longer read the staging buffers."""
         self._epoch += 1
+        self.invalidate()
         self._flags_sym.barrier()
 
-    def prefetch(self, i: int) -> None:
-        del i  # Gathers are fused into the consuming GEMMs.
+    def invalidate(self) -> None:
+        """Forgets what the gather buffers hold (the shards changed, e.g. after an update)."""
+        self._current = None
+        for leaf in self._fused:
+            if leaf is not None:
+                for mats in leaf.mats:
+                    for ms in mats:
+                        ms.holds = -1
 
     def get(self, i: int) -> list[torch.Tensor]:
         out = []
+        self._current, self._current_records = i, []
         for t, leaf in zip(self._leaves, self._fused):
             if leaf is None:
                 out.append(t[i])
+                self._current_records.append([])
                 continue
-            shard = t[i]  # [batch..., rows/R, cols...]
-            peer_base = leaf.sym.peer_addresses(shard)
-            mat_bytes = leaf.rows_local * leaf.cols * shard.element_size()
-            for j, ms in enumerate(leaf.mats):
-                shard_ptrs = [p + j * mat_bytes for p in peer_base]
-                staging_local = leaf.staging[i, j]
-                staging_ptrs = leaf.staging_sym.peer_addresses(staging_local)
-                _pending[ms.full.data_ptr()] = PendingMatrix(
-                    ms.full, shard_ptrs, ms, self._rank, self._world, staging_ptrs)
-            out.append(leaf.buffer)
+            records = []
+            for j, (ms, ptrs) in enumerate(zip(leaf.mats[i % 2], leaf.shard_ptrs(i))):
+                staging_ptrs = leaf.staging_sym.peer_addresses(leaf.staging[i, j])
+                rec = PendingMatrix(ms.full, ptrs, ms, self._rank, self._world, i, ms.holds == i, staging_ptrs)
+                _pending[ms.full.data_ptr()] = rec
+                records.append(rec)
+            self._current_records.append(records)
+            out.append(leaf.buffers[i % 2])
         return out
+
+    def prefetch(self, i: int) -> None:
+        """Layer ``i`` comes next: let the current layer's GEMMs carry its gathers."""
+        cur = self._current
+        if cur is None or not 0 <= i < self._num_layers or abs(i - cur) != 1:
+            return
+        for leaf, records in zip(self._fused, self._current_records):
+            if leaf is None:
+                continue
+            for rec, ms, ptrs in zip(records, leaf.mats[i % 2], leaf.shard_ptrs(i)):
+                if ms.holds != i:
+                    rec.carry = (ptrs, ms, i)
 
     def scatter_grads(self, i: int, full_grads: Sequence[Optional[torch.Tensor]]) -> None:
         from axlearn_b200.ops import fused_comm
@@ -199,6 +245,12 @@ def begin_step_all() -> None:
     """Called by the trainer at the start of every step (after the previous optimizer update)."""
     for g in _active:
         g.begin_step()
+
+
+def invalidate_all() -> None:
+    """Called after anything rewrites the parameter shards (optimizer update, restore)."""
+    for g in _active:
+        g.invalidate()
 
 
 def make_symmetric(stacked: torch.Tensor, plan: fsdp.LeafPlan) -> torch.Tensor:

@@ -2,7 +2,7 @@
 
 All "ranks" are emulated in one process: peer pointers are addresses of other local tensors, and
 each rank's kernel is launched in turn on one stream.  No kernel waits on another launch: the
-all-gather GEMM waits only on flags set by its own copy CTAs, and the flag wait of the
+all-gather GEMM waits only on flags set by its own copy warps, and the flag wait of the
 reduce-scatter runs after the launches that set the flags.
 """
 
@@ -31,14 +31,39 @@ def test_ag_gemm_matches_gather_then_matmul(world, weight_is_nk):
     ref = x.float() @ (w.float().t() if weight_is_nk else w.float())
     for rank in range(world):
         state = fused_comm.GatherState(w.shape, world, "cuda")
-        state.full.fill_(float("nan"))  # Anything the copy CTAs fail to write would poison the result.
+        state.full.fill_(float("nan"))  # Anything the copy warps fail to write would poison the result.
         for rep in range(2):  # Second call reuses the buffer with a new epoch.
             out = fused_comm.ag_gemm(x, shard_ptrs=[s.data_ptr() for s in shards], state=state, rank=rank,
-                                     weight_is_nk=weight_is_nk, copy_ctas=4)
+                                     weight_is_nk=weight_is_nk)
             torch.cuda.synchronize()
             cuda_ops.check_status()
             _close(out, ref)
         assert torch.equal(state.full, w)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_gemm_carrying_gather_computes_and_gathers(world):
+    """The GEMM result is that of a plain matmul and the unrelated gathered matrix is complete
+    when the kernel ends (nothing waits inside the kernel)."""
+    from axlearn_b200.ops import cuda_ops, fused_comm
+
+    torch.manual_seed(2)
+    m, k, n = 2048, 1024, 768
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    w = torch.randn(k, n, device="cuda").bfloat16()
+    other = torch.randn(4096, 1000 + 8 * world, device="cuda").bfloat16()  # slab size not a multiple of the chunk
+    shards = [s.contiguous() for s in other.chunk(world, dim=0)]
+    for rank in (0, world - 1):
+        state = fused_comm.GatherState(other.shape, world, "cuda")
+        state.full.fill_(float("nan"))
+        for weight in (w, w.t().contiguous().t()):  # both operand layouts
+            out = fused_comm.gemm_carrying_gather(x, weight, shard_ptrs=[s.data_ptr() for s in shards],
+                                                  state=state, rank=rank)
+            torch.cuda.synchronize()
+            cuda_ops.check_status()
+            _close(out, x.float() @ w.float())
+            assert torch.equal(state.full, other)
+            assert state.flags.tolist() == [state.epoch] * world
 
 
 @pytest.mark.parametrize("world", [2, 8])
