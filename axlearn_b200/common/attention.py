@@ -1392,7 +1392,7 @@ class _TransformerRepeat(Repeat):
             return (carry if out is None else out.data), st
 
         data_out, states = self._run(body, carry=data, collect=True)
-        return states, (None if time_step is None else data_out)
+        return _as_vdict(states), (None if time_step is None else data_out)
 
     def extend_step(self, cached_states, data, **kwargs):
         def body(carry, st_i, layer):
@@ -1400,7 +1400,13 @@ class _TransformerRepeat(Repeat):
             return out.data, st
 
         data, states = self._run(body, carry=data, xs=cached_states, collect=True)
-        return states, data
+        return _as_vdict(states), data
+
+
+def _as_vdict(states):
+    """Stacked per-layer states carry the layer dim in front of the batch dim: mark them so that
+    batch-wise tree operations (decoding) map over layers."""
+    return VDict(states) if isinstance(states, dict) and not isinstance(states, VDict) else states
 
 
 class RepeatedTransformerLayer(BaseStackedTransformerLayer):

@@ -219,6 +219,31 @@ class VDict(dict):
         return [(k, self[k]) for k in sorted(self.keys())]
 
 
+def vectorized_tree_map(fn: Callable, tree: Nested) -> Nested:
+    """``tree_map`` that applies ``fn`` per index of the leading dim for leaves under a VDict
+    (reference: axlearn/common/utils.py ``vectorized_tree_map``), so that ``fn`` always sees
+    the per-layer shape (e.g. batch-leading cache tensors of stacked layers)."""
+
+    def walk(node, depth):
+        if node is None:
+            return None
+        if isinstance(node, dict):
+            d = depth + 1 if isinstance(node, VDict) else depth
+            return type(node)((k, walk(v, d)) for k, v in node.items())
+        if _is_namedtuple(node):
+            return type(node)(*[walk(v, depth) for v in node])
+        if isinstance(node, (list, tuple)):
+            return type(node)(walk(v, depth) for v in node)
+        return apply(node, depth)
+
+    def apply(x, depth):
+        if depth == 0 or not isinstance(x, torch.Tensor):
+            return fn(x)
+        return torch.stack([apply(x[i], depth - 1) for i in range(x.shape[0])], dim=0)
+
+    return walk(tree, 0)
+
+
 def expand_vdicts(tree: Nested) -> Nested:
     """Replaces every VDict by a list of per-index plain dicts."""
 
