@@ -118,3 +118,132 @@ extern "C" int axb_reduce_slots(const void* staging, void* out, int slots, int64
       static_cast<const __nv_bfloat16*>(staging), static_cast<__nv_bfloat16*>(out), slots, n, sumsq_partial);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+// ---------------------------------------------------------------------------------------------
+// One-shot all-reduce for small, latency-bound messages (tensor-parallel decode).
+//
+//   axb_allreduce_push    copies this rank's partial vector into slot `rank` of every peer's
+//                         staging buffer (plain peer stores), and the last CTA to finish raises
+//                         flag [site * world + rank] on every peer to the current epoch;
+//   axb_allreduce_finish  every CTA waits (bounded) until the `world` local flags of the site
+//                         equal the epoch, then writes out = (residual +) sum of the slots for
+//                         its share of the vector.
+//
+// The epoch lives in device memory (`epoch_ptr`) so that both launches can sit in a captured
+// CUDA graph and still see a new value every replay; the caller bumps it once per step.
+// Staging and flags are per call site, so a rank that runs ahead never overwrites data that a
+// slower peer has not reduced yet (see DecodeEngine in axlearn_b200/inference).
+namespace axb {
+
+__global__ void allreduce_push_kernel(const uint4* __restrict__ src, uint4* const* peer_staging,
+                                      int* const* peer_flags, int* done_counter, const int* epoch_ptr,
+                                      int world, int rank, int site, int64_t nvec) {
+  for (int r = 0; r < world; ++r) {
+    uint4* dst = peer_staging[r] + static_cast<int64_t>(rank) * nvec;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+      dst[i] = src[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(done_counter, 1) == static_cast<int>(gridDim.x) - 1) {
+      *done_counter = 0;
+      __threadfence_system();
+      const int epoch = *epoch_ptr;
+      for (int r = 0; r < world; ++r)
+        asm volatile("st.release.sys.global.b32 [%0], %1;" ::"l"(peer_flags[r] + site * world + rank), "r"(epoch)
+                     : "memory");
+    }
+  }
+}
+
+__global__ void allreduce_finish_kernel(const __nv_bfloat16* staging,
+                                        const __nv_bfloat16* __restrict__ residual,
+                                        __nv_bfloat16* __restrict__ out, const int* flags, const int* epoch_ptr,
+                                        int world, int site, int64_t n, int* status) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    const int epoch = *epoch_ptr;
+    bool ok = false;
+    for (uint32_t it = 0; it < (1u << 22); ++it) {
+      int v;
+      asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(flags + site * world + threadIdx.x) : "memory");
+      if (v == epoch) {
+        ok = true;
+        break;
+      }
+      __nanosleep(100);
+    }
+    if (!ok) {
+      s_ok = 0;
+      if (status != nullptr) atomicCAS(status, 0, 4);
+    }
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const int64_t nvec = n / 8;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float acc[8];
+    if (residual != nullptr) {
+      const V8 a = reinterpret_cast<const V8*>(residual)[i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(a.v[j]);
+        acc[2 * j] = f.x;
+        acc[2 * j + 1] = f.y;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    }
+    for (int r = 0; r < world; ++r) {
+      // Written by peers while this kernel may already be resident: L2-coherent loads.
+      const uint4 u = __ldcg(reinterpret_cast<const uint4*>(staging + r * n) + i);
+      const __nv_bfloat162* av = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(av[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    V8 o;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o.v[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    reinterpret_cast<V8*>(out)[i] = o;
+  }
+}
+
+}  // namespace axb
+
+// n (elements, bf16) must be a multiple of 8; `peer_staging_dev[r]` points at rank r's staging
+// buffer [world, n] for this site; `peer_flags_dev[r]` at rank r's flag array [sites, world].
+extern "C" int axb_allreduce_push(const void* src, void* const* peer_staging_dev, int* const* peer_flags_dev,
+                                  int* done_counter, const int* epoch_ptr, int world, int rank, int site,
+                                  int64_t n, cudaStream_t stream) {
+  if (n % 8 || world > 32) return -10;
+  const int64_t nvec = n / 8;
+  int ctas = static_cast<int>((nvec + 255) / 256);
+  if (ctas > 32) ctas = 32;
+  axb::allreduce_push_kernel<<<ctas, 256, 0, stream>>>(
+      static_cast<const uint4*>(src), reinterpret_cast<uint4* const*>(peer_staging_dev), peer_flags_dev,
+      done_counter, epoch_ptr, world, rank, site, nvec);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int axb_allreduce_finish(const void* staging, const void* residual, void* out, const int* flags,
+                                    const int* epoch_ptr, int world, int site, int64_t n, int* status,
+                                    cudaStream_t stream) {
+  if (n % 8 || world > 32) return -10;
+  const int64_t nvec = n / 8;
+  int ctas = static_cast<int>((nvec + 255) / 256);
+  if (ctas > 32) ctas = 32;
+  axb::allreduce_finish_kernel<<<ctas, 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(staging), static_cast<const __nv_bfloat16*>(residual),
+      static_cast<__nv_bfloat16*>(out), flags, epoch_ptr, world, site, n, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

@@ -1,0 +1,197 @@
+"""Python entry points of the decode-time kernels (``csrc/decode_attn.cu``, ``csrc/peer_sync.cu``).
+
+* ``paged_decode_attention``: one query token per sequence over a paged KV cache.
+* ``rope_append_paged``: RoPE on q/k of the new token + store of k/v into its page slot.
+* ``swiglu_packed``: SwiGLU on a ``[rows, 2F]`` (gate | up) GEMM output.
+* ``OneShotAllReduce``: push-based all-reduce over peer memory for latency-bound messages.
+
+A torch reference of the attention (``reference_paged_attention``) is the oracle in tests; it
+gathers the pages like the reference's ``PagedKVCache`` does
+(axlearn/common/kv_cache/paged_kv_cache.py:22-35).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional
+
+import torch
+
+from axlearn_b200.ops import cuda_ops
+
+c_void_p, c_int, c_int64, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
+_configured = False
+
+
+def _lib():
+    global _configured
+    h = cuda_ops.lib()
+    if not _configured:
+        h.axb_decode_attn_scratch_floats.argtypes = [c_int, c_int, c_int]
+        h.axb_decode_attn_scratch_floats.restype = c_int64
+        h.axb_decode_attn.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                      c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+        h.axb_decode_attn.restype = c_int
+        h.axb_rope_append_paged.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                            c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]
+        h.axb_rope_append_paged.restype = c_int
+        h.axb_swiglu_packed.argtypes = [c_void_p, c_void_p, c_int64, c_int, c_void_p]
+        h.axb_swiglu_packed.restype = c_int
+        h.axb_allreduce_push.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                         c_int64, c_void_p]
+        h.axb_allreduce_push.restype = c_int
+        h.axb_allreduce_finish.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64,
+                                           c_void_p, c_void_p]
+        h.axb_allreduce_finish.restype = c_int
+        _configured = True
+    return h
+
+
+def default_splits(batch: int, num_kv_heads: int, group: int, max_len: int, page_size: int, sms: int = 148) -> int:
+    """KV splits so that the grid has a few CTAs per SM without splitting below 8 pages."""
+    gt = 4 if group % 4 == 0 else 2 if group % 2 == 0 else 1
+    ctas = batch * num_kv_heads * (group // gt)
+    want = max(1, (4 * sms + ctas - 1) // ctas)
+    pages = max(1, max_len // page_size)
+    return max(1, min(want, pages // 8 if pages >= 8 else 1, 32))
+
+
+def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
+                           lengths: torch.Tensor, *, softmax_scale: Optional[float] = None, splits: int = 1,
+                           out: Optional[torch.Tensor] = None, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q ``[B, Nq, H]``; pools ``[num_pages, page_size, Nkv, H]``; page_table ``[B, max_pages]`` int32;
+    lengths ``[B]`` int32 (valid tokens per sequence).  Returns ``[B, Nq, H]``."""
+    b, nq, h = q.shape
+    _, page_size, nkv, _ = k_pool.shape
+    assert q.is_contiguous() and k_pool.is_contiguous() and v_pool.is_contiguous()
+    assert page_table.dtype == torch.int32 and lengths.dtype == torch.int32 and page_table.is_contiguous()
+    if out is None:
+        out = torch.empty_like(q)
+    if splits > 1 and scratch is None:
+        scratch = torch.empty(_lib().axb_decode_attn_scratch_floats(b, nq, splits), dtype=torch.float32, device=q.device)
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(h)
+    rc = _lib().axb_decode_attn(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr(),
+                                lengths.data_ptr(), out.data_ptr(), None if scratch is None else scratch.data_ptr(),
+                                b, nq, nkv, h, page_size, page_table.shape[1], splits, scale,
+                                cuda_ops._stream())  # pylint: disable=protected-access
+    cuda_ops._check(rc, "axb_decode_attn")  # pylint: disable=protected-access
+    return out
+
+
+def reference_paged_attention(q, k_pool, v_pool, page_table, lengths, *, softmax_scale=None):
+    """fp32 torch oracle: gather each sequence's pages, mask beyond its length, softmax, PV."""
+    b, nq, h = q.shape
+    _, page_size, nkv, _ = k_pool.shape
+    g = nq // nkv
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(h)
+    k = k_pool[page_table.long()].reshape(b, -1, nkv, h).float()
+    v = v_pool[page_table.long()].reshape(b, -1, nkv, h).float()
+    qf = q.float().reshape(b, nkv, g, h)
+    logits = torch.einsum("bkgh,bskh->bkgs", qf, k) * scale
+    mask = torch.arange(k.shape[1], device=q.device)[None] < lengths[:, None]
+    logits = logits.masked_fill(~mask[:, None, None, :], float("-inf"))
+    p = torch.softmax(logits, dim=-1)
+    return torch.einsum("bkgs,bskh->bkgh", p, v).reshape(b, nq, h)
+
+
+def rope_append_paged(qkv: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
+                      lengths: torch.Tensor, *, num_q_heads: int, theta: float, apply_rope: bool = True,
+                      q_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """qkv ``[B, (Nq + 2 Nkv) * H]`` of the token at position ``lengths - 1``: returns rotated q
+    ``[B, Nq, H]`` and stores rotated k / plain v into the pools."""
+    b = qkv.shape[0]
+    _, page_size, nkv, h = k_pool.shape
+    assert qkv.is_contiguous() and qkv.shape[1] == (num_q_heads + 2 * nkv) * h
+    if q_out is None:
+        q_out = torch.empty((b, num_q_heads, h), dtype=qkv.dtype, device=qkv.device)
+    rc = _lib().axb_rope_append_paged(qkv.data_ptr(), q_out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+                                      page_table.data_ptr(), lengths.data_ptr(), b, num_q_heads, nkv, h, page_size,
+                                      page_table.shape[1], theta, 1 if apply_rope else 0,
+                                      cuda_ops._stream())  # pylint: disable=protected-access
+    cuda_ops._check(rc, "axb_rope_append_paged")  # pylint: disable=protected-access
+    return q_out
+
+
+def swiglu_packed(gu: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    rows, two_f = gu.shape
+    f = two_f // 2
+    assert gu.is_contiguous()
+    if out is None:
+        out = torch.empty((rows, f), dtype=gu.dtype, device=gu.device)
+    rc = _lib().axb_swiglu_packed(gu.data_ptr(), out.data_ptr(), rows, f, cuda_ops._stream())  # pylint: disable=protected-access
+    cuda_ops._check(rc, "axb_swiglu_packed")  # pylint: disable=protected-access
+    return out
+
+
+class OneShotAllReduce:
+    """All-reduce of small bf16 vectors over peer memory: every rank stores its partial into
+    slot ``rank`` of every peer's staging buffer and raises a flag; every rank then sums its
+    slots (optionally on top of a residual).  One instance serves ``sites`` call sites per
+    step, each with its own staging and flags, so that no buffer is reused within a step; the
+    epoch in ``self.epoch`` (device memory) must be bumped once per step (``begin_step``),
+    which also works inside a captured CUDA graph."""
+
+    def __init__(self, numel: int, sites: int, *, group=None, device=None, peers: Optional[list] = None,
+                 rank: int = 0):
+        from axlearn_b200.parallel import symm
+
+        self.numel, self.sites = numel, sites
+        if peers is not None:
+            # Single-process emulation: `peers[r]` is another instance whose buffers stand in
+            # for rank r's memory.
+            self.world, self.rank = len(peers) if peers else 1, rank
+            self.staging = torch.zeros((sites, max(self.world, 1), numel), dtype=torch.bfloat16, device=device)
+            self.flags = torch.zeros((sites, max(self.world, 1)), dtype=torch.int32, device=device)
+            self._sym = None
+        else:
+            import torch.distributed as dist
+
+            self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+            self.staging, self._sym = symm.symmetric_empty_like_sharded(
+                (sites, self.world, numel), torch.bfloat16, group, device)
+            self.flags, self._flags_sym = symm.symmetric_empty_like_sharded(
+                (sites, self.world), torch.int32, group, device)
+            self.flags.zero_()
+            self._staging_ptrs = [
+                symm.device_pointer_array([p + s * self.world * numel * 2 for p in self._sym.peer_ptrs], device)
+                for s in range(sites)
+            ]
+            self._flag_ptrs = symm.device_pointer_array(self._flags_sym.peer_ptrs, device)
+            self._flags_sym.barrier()
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self.counter = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def connect(self, peers: list["OneShotAllReduce"]) -> None:
+        """Emulation only: wire the pointer tables to the stand-in peers."""
+        dev = self.staging.device
+        self._staging_ptrs = [
+            torch.tensor([p.staging[s].data_ptr() for p in peers], dtype=torch.int64, device=dev)
+            for s in range(self.sites)
+        ]
+        self._flag_ptrs = torch.tensor([p.flags.data_ptr() for p in peers], dtype=torch.int64, device=dev)
+        self.world = len(peers)
+
+    def begin_step(self) -> None:
+        self.epoch.add_(1)
+
+    def push(self, x: torch.Tensor, site: int) -> None:
+        assert x.is_contiguous() and x.numel() == self.numel and x.dtype == torch.bfloat16
+        rc = _lib().axb_allreduce_push(x.data_ptr(), self._staging_ptrs[site].data_ptr(), self._flag_ptrs.data_ptr(),
+                                       self.counter.data_ptr(), self.epoch.data_ptr(), self.world, self.rank, site,
+                                       self.numel, cuda_ops._stream())  # pylint: disable=protected-access
+        cuda_ops._check(rc, "axb_allreduce_push")  # pylint: disable=protected-access
+
+    def finish(self, site: int, *, residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None):
+        if out is None:
+            out = torch.empty(self.numel, dtype=torch.bfloat16, device=self.staging.device)
+        rc = _lib().axb_allreduce_finish(
+            self.staging[site].data_ptr(), None if residual is None else residual.data_ptr(), out.data_ptr(),
+            self.flags.data_ptr(), self.epoch.data_ptr(), self.world, site, self.numel,
+            cuda_ops.status_word(self.staging.device).data_ptr(), cuda_ops._stream())  # pylint: disable=protected-access
+        cuda_ops._check(rc, "axb_allreduce_finish")  # pylint: disable=protected-access
+        return out
+
+    def all_reduce(self, x: torch.Tensor, site: int, *, residual=None, out=None) -> torch.Tensor:
+        self.push(x, site)
+        return self.finish(site, residual=residual, out=out)
