@@ -129,9 +129,15 @@ class AuxLossMetrics(BaseLossMetrics):
             zero = torch.zeros((), device=input_batch["target_labels"].device)
             return WeightedSummary(zero, 1), {"aux_loss": zero}
         aux = sum(h.float().mean() for h in hits)
+        # Like the cross entropy, the returned loss is this rank's share of the global mean
+        # (ranks are weighted by their live targets), so that summing shares over the batch
+        # axes gives the mean auxiliary loss and gradients can simply be summed.
         num = _live_targets(input_batch, input_batch["target_labels"]).sum().float()
-        self.add_summary("aux_loss", WeightedSummary(aux.detach(), num))
-        return WeightedSummary(aux, num), {"aux_loss": aux}
+        num_global = coll.all_reduce_scalar(num, BATCH_AXES)
+        share = aux * (num / num_global.clamp_min(1.0))
+        total = coll.all_reduce_scalar(share.detach(), BATCH_AXES)
+        self.add_summary("aux_loss", WeightedSummary(total, num_global))
+        return WeightedSummary(share, num_global), {"aux_loss": total}
 
 
 class CompositeLossMetrics(BaseLossMetrics):

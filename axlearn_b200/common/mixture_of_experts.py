@@ -1,0 +1,502 @@
+"""Mixture-of-experts feed-forward layers with capacity-based top-k routing.
+
+Parity targets in the reference (axlearn/common/mixture_of_experts.py): ``_router_z_loss`` (:158),
+``_compute_expert_capacity`` (:224), ``AdaptiveLoadBalanceLoss`` (:307), ``BaseGating`` (:365),
+``Top2Gating`` (:461-725), ``TopKGating`` (:727-1098) and ``TransformerFeedForwardMoE`` (:1443-1800),
+including the routing semantics: tokens are grouped ``[outer_batch, groups, group_size]``; within
+a group experts fill up in priority order (every token's first choice before any second choice,
+tokens in sequence order), assignments beyond ``expert_capacity`` are dropped, gate weights are
+renormalised over the chosen experts, and the load-balance loss is
+``mean(density * density_proxy) * E^2`` (``/ k`` for top-k).
+
+Representation.  The reference materialises one-hot ``[O, G, S, E, C]`` dispatch / combine
+tensors and moves tokens with einsums.  Here routing is kept as indices -- for every
+(token, choice): expert id, slot in that expert's buffer (or "dropped") and weight -- and tokens
+move by gather / scatter (``dispatch`` / ``combine``), which is O(tokens * k * model_dim) memory
+traffic instead of O(tokens * E * C).  The dense tensors are still available
+(``Routing.combine_tensor()`` / ``dispatch_tensor()``) for parity checks.
+
+Expert parallelism.  Expert weights are sharded over the ``expert`` mesh axis on their leading
+dim (marked ``ComputeAxis``: never gathered).  Each rank routes its own tokens, an all-to-all
+over the ``expert`` axis brings every expert the tokens of all ranks, the expert FFN runs as
+per-expert GEMMs, and a second all-to-all returns the outputs to the ranks that own the tokens.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+import math
+from typing import Any, Optional, Sequence, Union
+
+import torch
+
+from axlearn_b200 import ops
+from axlearn_b200.common.base_layer import BaseLayer, FanAxes, ParameterSpec
+from axlearn_b200.common.config import REQUIRED, InstantiableConfig, Required, config_class
+from axlearn_b200.common.layers import Dropout, LayerNorm, StochasticDepth, get_activation_fn
+from axlearn_b200.common.module import Module, nowrap
+from axlearn_b200.common.param_init import constant_initializer
+from axlearn_b200.parallel import collectives as coll
+from axlearn_b200.parallel.mesh import current_mesh
+
+Tensor = torch.Tensor
+
+
+def _router_z_loss(logits: Tensor) -> Tensor:
+    """``mean(logsumexp(logits)^2)``: keeps router logits small."""
+    return torch.logsumexp(logits.float(), dim=-1).square().mean()
+
+
+def _cap_logits(logits: Tensor, cap: float) -> Tensor:
+    return cap * torch.tanh(logits / cap) if cap > 0 else logits
+
+
+def _compute_expert_capacity(*, group_size: int, num_experts: int, expert_capacity: Optional[int],
+                             capacity_factor: Optional[float]) -> int:
+    if not (capacity_factor or expert_capacity):
+        raise ValueError("At least one of `capacity_factor` or `expert_capacity` needs to be set.")
+    if capacity_factor:
+        auto = int(group_size * capacity_factor / num_experts)
+        if expert_capacity is None:
+            expert_capacity = 1
+        expert_capacity = max(expert_capacity, auto)
+    return expert_capacity
+
+
+@dataclasses.dataclass
+class Routing:
+    """Index form of a routing decision for tokens ``[O, G, S]`` and ``K`` choices each."""
+
+    expert_index: Tensor   # int64 [O, G, S, K]
+    slot: Tensor           # int64 [O, G, S, K]: position in the expert's buffer, -1 = dropped
+    weight: Tensor         # float32 [O, G, S, K]: combine weight (0 for dropped assignments)
+    num_experts: int
+    expert_capacity: int
+    load_balance_loss: Optional[Tensor] = None
+    router_z_loss: Optional[Tensor] = None
+
+    def dispatch_tensor(self) -> Tensor:
+        """Dense bool ``[O, G, S, E, C]`` (the reference's representation)."""
+        return self.combine_tensor(weights=False) > 0
+
+    def combine_tensor(self, weights: bool = True) -> Tensor:
+        o, g, s, k = self.expert_index.shape
+        out = torch.zeros((o, g, s, self.num_experts * self.expert_capacity + 1), dtype=torch.float32,
+                          device=self.expert_index.device)
+        flat = torch.where(self.slot >= 0, self.expert_index * self.expert_capacity + self.slot,
+                           torch.full_like(self.slot, self.num_experts * self.expert_capacity))
+        vals = self.weight if weights else (self.slot >= 0).float()
+        out.scatter_add_(3, flat, vals)
+        return out[..., :-1].reshape(o, g, s, self.num_experts, self.expert_capacity)
+
+
+def _slots_in_priority_order(expert_index: Tensor, num_experts: int, capacity: int) -> Tensor:
+    """Position of each (token, choice) in its expert's buffer: all first choices in sequence
+    order, then all second choices, ...; -1 where the expert is already full."""
+    o, g, s, k = expert_index.shape
+    # [O, G, K*S] choice-major, as the reference flattens it.
+    flat = expert_index.permute(0, 1, 3, 2).reshape(o, g, k * s)
+    onehot = torch.nn.functional.one_hot(flat, num_experts)                 # [O, G, K*S, E]
+    pos = (onehot.cumsum(dim=2) * onehot).sum(dim=-1) - 1                   # [O, G, K*S]
+    pos = torch.where(pos < capacity, pos, torch.full_like(pos, -1))
+    return pos.reshape(o, g, k, s).permute(0, 1, 3, 2).contiguous()
+
+
+class AdaptiveLoadBalanceLoss(BaseLayer):
+    """Scales the load-balance loss up (down) when the moving average of the over-capacity
+    ratio is above ``max_value`` (below ``min_value``); the scale lives in log space."""
+
+    @config_class
+    class Config(BaseLayer.Config):
+        moving_average_weight: float = 0.99
+        max_value: Required[float] = REQUIRED
+        min_value: float = 1e-3
+        log_step: float = 0.01
+
+    def _create_layer_parameter_specs(self):
+        zero = constant_initializer(0.0)
+        return {
+            "value_average": ParameterSpec(shape=(), dtype=torch.float32, initializer=zero, weight_decay_scale=0.0),
+            "log_scale": ParameterSpec(shape=(), dtype=torch.float32, initializer=zero, weight_decay_scale=0.0),
+        }
+
+    def forward(self, value: Tensor) -> Tensor:
+        cfg = self._config
+        avg = self.parameters["value_average"].detach()
+        log_scale = self.parameters["log_scale"].detach()
+        new_avg = cfg.moving_average_weight * avg + (1 - cfg.moving_average_weight) * value.detach().float()
+        inc = (new_avg > cfg.max_value).float() - (new_avg < cfg.min_value).float()
+        new_log_scale = log_scale + inc * cfg.log_step
+        self.add_state_update("value_average", new_avg)
+        self.add_state_update("log_scale", new_log_scale)
+        self.add_summary("value_average", new_avg)
+        self.add_summary("log_scale", new_log_scale)
+        return torch.exp(new_log_scale)
+
+
+class BaseGating(BaseLayer):
+    """Turns router logits ``[O, G, S, E]`` into a ``Routing``."""
+
+    @config_class
+    class Config(BaseLayer.Config):
+        num_experts: Required[int] = REQUIRED
+
+    Output = Routing
+
+    def forward(self, logits: Tensor) -> Routing:
+        raise NotImplementedError(type(self))
+
+    @nowrap
+    def dispatch(self, x: Tensor, routing: Routing) -> Tensor:
+        """``x [O, G, S, M] -> [O, E, G, C, M]``: every kept (token, choice) lands in its
+        expert's slot; unfilled slots are zero."""
+        o, g, s, m = x.shape
+        e, c, k = routing.num_experts, routing.expert_capacity, routing.expert_index.shape[-1]
+        dest, _ = _flat_destinations(routing)
+        src = torch.arange(o * g * s, device=x.device).repeat_interleave(k)
+        buf = torch.zeros((o * e * g * c + 1, m), dtype=x.dtype, device=x.device)
+        buf = buf.index_add(0, dest.reshape(-1), x.reshape(o * g * s, m)[src])
+        return buf[:-1].reshape(o, e, g, c, m)
+
+    @nowrap
+    def combine(self, y: Tensor, routing: Routing, *, dtype=None) -> Tensor:
+        """``y [O, E, G, C, M] -> [O, G, S, M]``: weighted sum of each token's expert outputs."""
+        o, e, g, c, m = y.shape
+        s, k = routing.expert_index.shape[2:]
+        dest, _ = _flat_destinations(routing)
+        padded = torch.cat([y.reshape(o * e * g * c, m), y.new_zeros((1, m))], dim=0)
+        gathered = padded[dest.reshape(-1)].reshape(o, g, s, k, m)
+        out = (gathered.float() * routing.weight[..., None]).sum(dim=3)
+        return out.to(dtype or y.dtype)
+
+
+def _flat_destinations(routing: Routing) -> tuple[Tensor, Tensor]:
+    """Row of ``[O, E, G, C]`` (flattened) for every (token, choice); dropped ones point at the
+    extra trailing row."""
+    o, g, s, k = routing.expert_index.shape
+    e, c = routing.num_experts, routing.expert_capacity
+    dev = routing.expert_index.device
+    oo = torch.arange(o, device=dev).view(o, 1, 1, 1)
+    gg = torch.arange(g, device=dev).view(1, g, 1, 1)
+    valid = routing.slot >= 0
+    dest = ((oo * e + routing.expert_index) * g + gg) * c + routing.slot.clamp(min=0)
+    dest = torch.where(valid, dest, torch.full_like(dest, o * e * g * c))
+    return dest, valid
+
+
+class Top2Gating(BaseGating):
+    """Top-2 routing with capacity (GShard).  The second choice is the best expert other than
+    the first; gate weights are renormalised over the two."""
+
+    @config_class
+    class Config(BaseGating.Config):
+        gating_logit_cap: float = 0.0
+        train_capacity_factor: float = 2.0
+        eval_capacity_factor: float = 2.0
+        expert_capacity: Optional[int] = None
+        adaptive_load_balance_loss: Optional[InstantiableConfig] = None
+
+    def __init__(self, cfg, *, parent=None):
+        super().__init__(cfg, parent=parent)
+        if cfg.adaptive_load_balance_loss is not None:
+            self._add_child("adaptive_load_balance_loss", cfg.adaptive_load_balance_loss)
+
+    def _compute_index(self, raw_gates: Tensor, *, k: int) -> Tensor:
+        return raw_gates.topk(k, dim=-1).indices
+
+    def forward(self, logits: Tensor) -> Routing:
+        cfg = self._config
+        logits = _cap_logits(logits.float(), cfg.gating_logit_cap)
+        raw_gates = torch.softmax(logits, dim=-1)
+        e = cfg.num_experts
+        capacity = _compute_expert_capacity(
+            expert_capacity=cfg.expert_capacity,
+            capacity_factor=cfg.train_capacity_factor if self.is_training else cfg.eval_capacity_factor,
+            group_size=logits.shape[-2], num_experts=e)
+        index = self._compute_index(raw_gates, k=2)                          # [O, G, S, 2]
+        gate_1 = torch.gather(raw_gates, -1, index[..., :1]).squeeze(-1)
+        gate_2 = torch.gather(raw_gates, -1, index[..., 1:]).squeeze(-1)
+        gate_2 = torch.where(index[..., 0] == index[..., 1], torch.zeros_like(gate_2), gate_2)
+        denom = gate_1 + gate_2 + 1e-9
+        weights = torch.stack([gate_1 / denom, gate_2 / denom], dim=-1)
+        # Load balance: fraction of tokens whose first choice is e, times the mean gate of e.
+        density_1 = torch.nn.functional.one_hot(index[..., 0], e).float().mean(dim=-2)
+        density_proxy = raw_gates.mean(dim=-2)
+        aux = (density_1 * density_proxy).mean() * e * e
+        slot = _slots_in_priority_order(index, e, capacity)
+        kept = slot >= 0
+        weights = weights * kept.float()
+        first = torch.nn.functional.one_hot(index[..., 0], e).sum(dim=-2)    # [O, G, E]
+        over_1 = (first - capacity).clamp(min=0).sum() / first.sum().clamp(min=1)
+        second_total = torch.nn.functional.one_hot(index[..., 1], e).sum(dim=-2) + first
+        over_2 = (second_total - capacity).clamp(min=0).sum() / second_total.sum().clamp(min=1)
+        z = _router_z_loss(logits)
+        counts = kept.sum(dim=-1)
+        for i in range(3):
+            self.add_summary(f"dispatch_{i}", (counts == i).sum())
+        self.add_summary("router_z_loss", z.detach())
+        self.add_summary("over_capacity_1", over_1)
+        self.add_summary("over_capacity_2", over_2)
+        if "adaptive_load_balance_loss" in self._children:
+            self.add_summary("load_balance_loss_original", aux.detach())
+            aux = aux * self.adaptive_load_balance_loss(torch.maximum(over_1, over_2))
+        self.add_summary("load_balance_loss", aux.detach())
+        self.add_module_output("gate_assignment", index)
+        return Routing(expert_index=index, slot=slot, weight=weights, num_experts=e, expert_capacity=capacity,
+                       load_balance_loss=aux, router_z_loss=z)
+
+
+class TopKGating(BaseGating):
+    """Top-k routing with capacity; weights are the raw gates renormalised over the k chosen
+    experts (dropped assignments simply vanish from the sum)."""
+
+    @config_class
+    class Config(BaseGating.Config):
+        num_experts_per_token: int = 2
+        gating_logit_cap: float = 0.0
+        train_capacity_factor: Optional[float] = None
+        eval_capacity_factor: Optional[float] = None
+        expert_capacity: Optional[int] = None
+        adaptive_load_balance_loss: Optional[InstantiableConfig] = None
+        noisy_gating: Optional[str] = None   # "gumbel"
+        score_fn: Optional[Any] = None       # None = softmax; "sigmoid" or a callable(logits, dim)
+
+    def __init__(self, cfg, *, parent=None):
+        super().__init__(cfg, parent=parent)
+        if cfg.adaptive_load_balance_loss is not None:
+            self._add_child("adaptive_load_balance_loss", cfg.adaptive_load_balance_loss)
+
+    def _score(self, logits: Tensor) -> Tensor:
+        fn = self._config.score_fn
+        if fn is None:
+            return torch.softmax(logits, dim=-1)
+        if fn == "sigmoid":
+            return torch.sigmoid(logits)
+        return fn(logits, -1)
+
+    def _compute_index(self, raw_gates: Tensor, *, k: int) -> Tensor:
+        return raw_gates.topk(k, dim=-1).indices
+
+    def _expert_capacity(self, group_size: int) -> int:
+        cfg = self._config
+        factor = cfg.train_capacity_factor if self.is_training else cfg.eval_capacity_factor
+        if factor is None:
+            factor = float(cfg.num_experts_per_token)
+        return _compute_expert_capacity(expert_capacity=cfg.expert_capacity, capacity_factor=factor,
+                                        group_size=group_size, num_experts=cfg.num_experts)
+
+    def forward(self, logits: Tensor) -> Routing:
+        cfg = self._config
+        e, k = cfg.num_experts, cfg.num_experts_per_token
+        logits = logits.float()
+        self.add_summary("router_logit_rms", logits.detach().square().mean().sqrt())
+        logits = _cap_logits(logits, cfg.gating_logit_cap)
+        if cfg.noisy_gating is not None:
+            if cfg.noisy_gating != "gumbel":
+                raise NotImplementedError(cfg.noisy_gating)
+            from axlearn_b200.common import prng
+
+            u = prng.uniform(self.prng_key, logits.shape, device=logits.device).clamp(1e-20, 1.0)
+            logits = logits - torch.log(-torch.log(u))
+        z = _router_z_loss(logits)
+        raw_gates = self._score(logits)
+        capacity = self._expert_capacity(logits.shape[-2])
+        index = self._compute_index(raw_gates, k=k)
+        gate_w = torch.gather(raw_gates, -1, index)
+        normalized = raw_gates if cfg.score_fn is None else raw_gates / raw_gates.sum(dim=-1, keepdim=True)
+        assigned = torch.nn.functional.one_hot(index, e).amax(dim=-2).float()  # [O, G, S, E]
+        aux = (assigned.mean(dim=-2) * normalized.mean(dim=-2)).mean() * e * e / k
+        slot = _slots_in_priority_order(index, e, capacity)
+        kept = slot >= 0
+        weights = gate_w / gate_w.sum(dim=-1, keepdim=True) * kept.float()
+        totals = torch.nn.functional.one_hot(index, e).sum(dim=(-3, -2))      # [O, G, E]
+        over = (totals - capacity).clamp(min=0).sum() / totals.sum().clamp(min=1)
+        self.add_summary("over_capacity_ratio", over)
+        self.add_summary("router_z_loss", z.detach())
+        counts = kept.sum(dim=-1)
+        for i in range(k + 1):
+            self.add_summary(f"dispatch_{i}", (counts == i).sum())
+        if "adaptive_load_balance_loss" in self._children:
+            self.add_summary("load_balance_loss_original", aux.detach())
+            aux = aux * self.adaptive_load_balance_loss(over)
+        self.add_summary("load_balance_loss", aux.detach())
+        self.add_module_output("gate_assignment", index)
+        return Routing(expert_index=index, slot=slot, weight=weights, num_experts=e, expert_capacity=capacity,
+                       load_balance_loss=aux, router_z_loss=z)
+
+
+class TransformerFeedForwardMoE(BaseLayer):
+    """Drop-in replacement of the dense transformer feed-forward layer with ``num_experts``
+    expert FFNs and a learned router (``gate_weight [M, E]``)."""
+
+    @config_class
+    class Config(BaseLayer.Config):
+        input_dim: Required[int] = REQUIRED
+        hidden_dim: Required[Union[int, InstantiableConfig]] = REQUIRED
+        outer_batch: int = 1
+        norm: InstantiableConfig = LayerNorm.default_config()
+        activation: Union[str, tuple] = "nn.relu"
+        dropout: InstantiableConfig = Dropout.default_config()
+        stochastic_depth: InstantiableConfig = StochasticDepth.default_config()
+        structure: str = "prenorm"
+        residual_weight: float = 1.0
+        num_experts: Required[int] = REQUIRED
+        num_groups: Required[int] = REQUIRED
+        gating: InstantiableConfig = Top2Gating.default_config()
+        load_balance_loss_weight: float = 0.01
+        router_z_loss_weight: float = 0.0
+        # Logical dim name -> mesh axes, as in the reference ("e" = experts, "m" = model dim,
+        # "h" = hidden dim).
+        dim_to_mesh_axis_map: dict = {}
+
+    @classmethod
+    def default_config(cls):
+        cfg = super().default_config()
+        cfg.dim_to_mesh_axis_map = {
+            "me": (None, None),
+            "emh": (coll.ComputeAxis("expert"), None, "model"),
+            "ehm": (coll.ComputeAxis("expert"), "model", None),
+        }
+        return cfg
+
+    def __init__(self, cfg, *, parent=None):
+        super().__init__(cfg, parent=parent)
+        self._add_child("gating", cfg.gating.clone(num_experts=cfg.num_experts))
+        self._add_child("stochastic_depth", cfg.stochastic_depth)
+        if cfg.structure in ("prenorm", "postnorm"):
+            self._add_child("norm", cfg.norm.clone(input_dim=cfg.input_dim))
+        elif cfg.structure == "hybridnorm":
+            self._add_child("prenorm", cfg.norm.clone(input_dim=cfg.input_dim))
+            self._add_child("postnorm", cfg.norm.clone(input_dim=cfg.input_dim))
+        elif cfg.structure != "nonorm":
+            raise NotImplementedError(cfg.structure)
+        if cfg.structure in ("prenorm", "hybridnorm", "nonorm"):
+            self._add_child("dropout1", cfg.dropout)
+            self._add_child("dropout2", cfg.dropout)
+        else:
+            self._add_child("dropout", cfg.dropout)
+
+    @nowrap
+    def hidden_dim(self) -> int:
+        cfg = self._config
+        if isinstance(cfg.hidden_dim, int):
+            return cfg.hidden_dim
+        return cfg.hidden_dim.clone(input_dim=cfg.input_dim).instantiate()
+
+    def _create_layer_parameter_specs(self):
+        cfg = self._config
+        h = self.hidden_dim()
+        axes = cfg.dim_to_mesh_axis_map
+        params = {
+            "gate_weight": ParameterSpec(shape=(cfg.input_dim, cfg.num_experts), mesh_axes=axes.get("me")),
+            "wo_weight": ParameterSpec(shape=(cfg.num_experts, h, cfg.input_dim), mesh_axes=axes.get("ehm"),
+                                       fan_axes=FanAxes(in_axis=-2, out_axis=-1, batch_axis=0)),
+        }
+        names = [f"wi_{i}_weight" for i in range(len(cfg.activation))] if isinstance(cfg.activation, tuple) else ["wi_weight"]
+        for n in names:
+            params[n] = ParameterSpec(shape=(cfg.num_experts, cfg.input_dim, h), mesh_axes=axes.get("emh"),
+                                      fan_axes=FanAxes(in_axis=-2, out_axis=-1, batch_axis=0))
+        return params
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, inputs: Tensor) -> Tensor:
+        cfg = self._config
+        s = cfg.structure
+        if s == "prenorm":
+            x = self._dispatch_and_combine(self.norm(inputs))
+            x = self.stochastic_depth(self.dropout2(x))
+            if cfg.residual_weight != 1:
+                x = x * cfg.residual_weight
+            return x + inputs
+        if s == "postnorm":
+            x = self.stochastic_depth(self.dropout(self._dispatch_and_combine(inputs)))
+            if cfg.residual_weight != 1:
+                x = x * cfg.residual_weight
+            return self.norm(x + inputs)
+        if s == "hybridnorm":
+            x = self.postnorm(self._dispatch_and_combine(self.prenorm(inputs)))
+            x = self.stochastic_depth(self.dropout2(x))
+            if cfg.residual_weight != 1:
+                x = x * cfg.residual_weight
+            return x + inputs
+        x = self.stochastic_depth(self.dropout2(self._dispatch_and_combine(inputs)))
+        return x * cfg.residual_weight if cfg.residual_weight != 1 else x
+
+    def _expert_weight(self, name: str, logical: str) -> Tensor:
+        cfg = self._config
+        spec = cfg.dim_to_mesh_axis_map.get(logical)
+        w = self.parameters[name]
+        shape = {"emh": (cfg.num_experts, cfg.input_dim, self.hidden_dim()),
+                 "ehm": (cfg.num_experts, self.hidden_dim(), cfg.input_dim)}[logical]
+        return coll.unshard_param(w, spec, compute_shape=coll.compute_shape(shape, spec))
+
+    def _dispatch_and_combine(self, x: Tensor) -> Tensor:
+        cfg = self._config
+        in_dtype = x.dtype
+        token_shape = x.shape[:-1]
+        o = cfg.outer_batch
+        if x.shape[0] % o:
+            raise ValueError(f"batch_size {x.shape[0]} has to be divisible by outer_batch {o}.")
+        tokens = math.prod(token_shape) // o
+        if tokens % cfg.num_groups:
+            raise ValueError(f"{tokens} tokens per outer batch must be divisible by num_groups({cfg.num_groups}).")
+        x = x.reshape(o, cfg.num_groups, tokens // cfg.num_groups, cfg.input_dim)
+        logits = torch.einsum("ogsm,me->ogse", x.float(), self.parameters["gate_weight"].float())
+        routing = self.gating(logits)
+        aux = routing.load_balance_loss * cfg.load_balance_loss_weight
+        if cfg.router_z_loss_weight:
+            aux = aux + routing.router_z_loss * cfg.router_z_loss_weight
+        self.add_module_output("aux_loss", aux)
+        expert_in = self.gating.dispatch(x, routing)                          # [O, E, G, C, M]
+        expert_out = self._experts(expert_in)
+        out = self.gating.combine(expert_out, routing, dtype=in_dtype)
+        return out.reshape(*token_shape, cfg.input_dim)
+
+    def _experts(self, x: Tensor) -> Tensor:
+        """``[O, E, G, C, M] -> [O, E, G, C, M]`` through the expert FFNs, with the all-to-all
+        pair around it when experts are sharded over the ``expert`` mesh axis."""
+        cfg = self._config
+        o, e, g, c, m = x.shape
+        mesh = current_mesh()
+        ep = mesh.axis_size("expert") if mesh is not None and "expert" in mesh.shape else 1
+        ep = ep if coll.has_axis((cfg.dim_to_mesh_axis_map.get("emh") or (None,))[0], "expert") else 1
+        xe = x.permute(1, 0, 2, 3, 4).reshape(e, o * g * c, m)                # expert-major
+        if ep > 1:
+            # [E, T, M] -> every rank keeps E/ep experts and receives their tokens from all ranks.
+            xe = coll.all_to_all(xe.reshape(ep, e // ep, o * g * c, m), "expert", split_dim=0, concat_dim=2)
+            xe = xe.reshape(e // ep, ep * o * g * c, m)
+        ye = self._expert_ffn(xe)
+        if ep > 1:
+            ye = ye.reshape(1, e // ep, ep, o * g * c, m)
+            ye = coll.all_to_all(ye, "expert", split_dim=2, concat_dim=0).reshape(e, o * g * c, m)
+        return ye.reshape(e, o, g, c, m).permute(1, 0, 2, 3, 4)
+
+    def _expert_ffn(self, xe: Tensor) -> Tensor:
+        """``[E_local, T, M]`` through each local expert's FFN (one GEMM per expert and
+        projection; the tensor-parallel ``model`` split of the hidden dim is summed at the end)."""
+        cfg = self._config
+        act = cfg.activation
+        outs = []
+        wo = self._expert_weight("wo_weight", "ehm")
+        if isinstance(act, tuple):
+            wis = [self._expert_weight(f"wi_{i}_weight", "emh") for i in range(len(act))]
+        else:
+            wis = [self._expert_weight("wi_weight", "emh")]
+        acts = list(act) if isinstance(act, tuple) else [act]
+        x_in = coll.psum_grad(xe, "model") if coll.has_axis((cfg.dim_to_mesh_axis_map.get("emh") or (None,) * 3)[2], "model") else xe
+        for i in range(xe.shape[0]):
+            xi = x_in[i]
+            hs = [ops.linear(xi, w[i].to(xi.dtype)) for w in wis]
+            if len(hs) == 2 and acts == ["nn.silu", "linear"]:
+                h = ops.swiglu(hs[0], hs[1])
+            else:
+                h = None
+                for hv, a in zip(hs, acts):
+                    hv = get_activation_fn(a)(hv)
+                    h = hv if h is None else h * hv
+            h = self.dropout1(h) if "dropout1" in self._children else h
+            outs.append(ops.linear(h, wo[i].to(h.dtype)))
+        y = torch.stack(outs, dim=0)
+        if coll.has_axis((cfg.dim_to_mesh_axis_map.get("ehm") or (None,) * 3)[1], "model"):
+            y = coll.psum(y, "model")
+        return y

@@ -1,0 +1,95 @@
+"""Envy: decoder-only LMs with mixture-of-experts feed-forward layers.
+
+Parity target in the reference: axlearn/experiments/text/gpt/envy.py (MoE model family: sparse
+and dense layers interleaved by ``ffn_layer_types``, Top2 gating, aux loss collected through
+``aux_loss_regex``).  ``MODEL_PRESETS["Mixtral-8x7B"]`` is the Mixtral-style configuration used as
+the MoE training benchmark: 32 layers, d_model 4096, 32 query / 8 KV heads, 8 SwiGLU experts of
+hidden 14336, top-2 softmax router, capacity factor 2.0, load-balance loss weight 0.01.
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+from axlearn_b200.common import causal_lm
+from axlearn_b200.common.attention import (
+    FusedGroupedQKVLinear,
+    FusedQKVLinear,
+    GroupedQueryAttention,
+    MultiheadAttention,
+    RepeatedTransformerLayer,
+    RoFormerQKVLinear,
+)
+from axlearn_b200.common.config import InstantiableConfig
+from axlearn_b200.common.decoder import LmHead
+from axlearn_b200.common.embedding import TransformerTextEmbeddings
+from axlearn_b200.common.layers import RMSNorm
+from axlearn_b200.common.mixture_of_experts import Top2Gating, TopKGating, TransformerFeedForwardMoE
+from axlearn_b200.experiments.text.gpt.common import model_config as common_model_config
+
+MODEL_PRESETS = {
+    "test": dict(num_layers=2, hidden_dim=64, num_heads=4, num_kv_heads=2, num_experts=4, moe_ffn_dim=128,
+                 vocab_size=512, num_groups=2),
+    "Mixtral-8x7B": dict(num_layers=32, hidden_dim=4096, num_heads=32, num_kv_heads=8, num_experts=8,
+                         moe_ffn_dim=14336, vocab_size=32768, num_groups=1),
+}
+
+
+def model_config(
+    *,
+    num_layers: int,
+    hidden_dim: int,
+    num_heads: int,
+    num_kv_heads: Optional[int],
+    num_experts: int,
+    moe_ffn_dim: int,
+    vocab_size: int,
+    num_groups: int = 1,
+    outer_batch: int = 1,
+    rope_theta: float = 1e6,
+    capacity_factor: float = 2.0,
+    num_experts_per_token: int = 2,
+    load_balance_loss_weight: float = 0.01,
+    router_z_loss_weight: float = 0.0,
+    ffn_layer_types: Sequence[str] = ("sparse",),
+    dense_ffn_dim: Optional[int] = None,
+    shared_lm_head: bool = False,
+    stack_cfg: Optional[InstantiableConfig] = None,
+    scan_chunk: Optional[int] = None,
+) -> causal_lm.Model.Config:
+    """RMSNorm / RoPE / SwiGLU decoder whose feed-forward layers follow ``ffn_layer_types``
+    (cycled over the stack): "sparse" = MoE, "dense" = ordinary FFN."""
+    if num_kv_heads:
+        atten_cfg = GroupedQueryAttention.default_config()
+        input_linear = FusedGroupedQKVLinear.default_config().set(num_kv_heads=num_kv_heads)
+    else:
+        atten_cfg = MultiheadAttention.default_config()
+        input_linear = FusedQKVLinear.default_config()
+    qkv = RoFormerQKVLinear.default_config().set(input_linear=input_linear, rotary_value=False)
+    qkv.rope_pos_emb_layer.theta = rope_theta
+    if num_experts_per_token == 2:
+        gating = Top2Gating.default_config().set(
+            train_capacity_factor=capacity_factor, eval_capacity_factor=capacity_factor)
+    else:
+        gating = TopKGating.default_config().set(
+            num_experts_per_token=num_experts_per_token, train_capacity_factor=capacity_factor,
+            eval_capacity_factor=capacity_factor)
+    expert_cfg = TransformerFeedForwardMoE.default_config().set(
+        num_experts=num_experts, num_groups=num_groups, outer_batch=outer_batch, gating=gating,
+        load_balance_loss_weight=load_balance_loss_weight, router_z_loss_weight=router_z_loss_weight)
+    cfg = common_model_config(
+        num_layers=num_layers, hidden_dim=hidden_dim, num_heads=num_heads, vocab_size=vocab_size,
+        stack_cfg=stack_cfg if stack_cfg is not None else RepeatedTransformerLayer.default_config(),
+        activation_fn=("nn.silu", "linear"), ffn_dim=dense_ffn_dim or moe_ffn_dim,
+        normalization=RMSNorm.default_config().set(eps=1e-5, forward_dtype=None),
+        emb_cfg=TransformerTextEmbeddings.default_config().set(pos_emb=None),
+        lm_head_cfg=LmHead.default_config() if not shared_lm_head else None,
+        attention_cfg=atten_cfg, attention_qkv_linear=qkv, ffn_layer_types=tuple(ffn_layer_types),
+        expert_cfg=expert_cfg, moe_ffn_dim=moe_ffn_dim, scan_chunk=scan_chunk)
+    cfg.aux_loss_regex = ".*/aux_loss"
+    cfg.metrics = causal_lm.metrics_config(aux_loss_regex=cfg.aux_loss_regex)
+    return cfg
+
+
+def preset(name: str, **overrides) -> causal_lm.Model.Config:
+    return model_config(**{**MODEL_PRESETS[name], **overrides})

@@ -153,7 +153,15 @@ class _AllToAll(torch.autograd.Function):
 def _all_to_all_raw(x, group, world, split_dim, concat_dim):
     parts = [p.contiguous() for p in x.chunk(world, dim=split_dim)]
     outs = [torch.empty_like(parts[0]) for _ in range(world)]
-    dist.all_to_all(outs, parts, group=group)
+    if dist.get_backend(group) == "gloo":
+        # gloo has no all-to-all: gather everything and keep the pieces addressed to this rank.
+        stacked = torch.stack(parts, dim=0)
+        everyone = [torch.empty_like(stacked) for _ in range(world)]
+        dist.all_gather(everyone, stacked, group=group)
+        me = dist.get_rank(group)
+        outs = [everyone[r][me] for r in range(world)]
+    else:
+        dist.all_to_all(outs, parts, group=group)
     return torch.cat(outs, dim=concat_dim)
 
 
@@ -228,12 +236,23 @@ def process_count() -> int:
 _COMPUTE_AXES = ("model", "pipeline")
 
 
+class ComputeAxis(str):
+    """A mesh-axis name that, in this partition-spec entry, shards the *computation* and is
+    never gathered: e.g. ``ComputeAxis("expert")`` on the expert dim of MoE weights (experts
+    live on their rank; tokens travel), while plain ``"expert"`` elsewhere remains a storage
+    axis that FSDP gathers."""
+
+
+def _is_compute_axis(a: str) -> bool:
+    return a in _COMPUTE_AXES or isinstance(a, ComputeAxis)
+
+
 def storage_axes(entry: AxisSpec, mesh: Optional[Mesh] = None) -> tuple[str, ...]:
     mesh = mesh or current_mesh()
     if mesh is None or entry is None:
         return ()
     names = (entry,) if isinstance(entry, str) else tuple(entry)
-    return tuple(a for a in mesh.present_axes(names) if a not in _COMPUTE_AXES)
+    return tuple(a for a in mesh.present_axes(names) if not _is_compute_axis(a))
 
 
 def unshard_param(
@@ -264,7 +283,7 @@ def compute_shape(shape: Sequence[int], mesh_axes: Optional[Sequence[AxisSpec]])
     out = []
     for d, entry in zip(shape, mesh_axes):
         names = () if entry is None else ((entry,) if isinstance(entry, str) else tuple(entry))
-        comp = tuple(a for a in mesh.present_axes(names) if a in _COMPUTE_AXES)
+        comp = tuple(a for a in mesh.present_axes(names) if _is_compute_axis(a))
         out.append(d // mesh.axis_size(comp))
     return tuple(out)
 
