@@ -184,8 +184,12 @@ class _Remat(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, run, *tensors):  # pylint: disable=arguments-differ
+        from axlearn_b200.parallel.mesh import current_mesh
+
         ctx.run = run
         ctx.needs = [t.requires_grad for t in tensors]
+        # The replay runs on an autograd worker thread, whose thread-local mesh stack is empty.
+        ctx.mesh = current_mesh()
         ctx.save_for_backward(*tensors)
         with torch.no_grad():
             outs = run(tensors, first_pass=True)
@@ -193,6 +197,15 @@ class _Remat(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, *grads):  # pylint: disable=arguments-differ
+        from axlearn_b200.parallel.mesh import current_mesh
+
+        if ctx.mesh is not None and current_mesh() is not ctx.mesh:
+            with ctx.mesh:
+                return _Remat._backward(ctx, *grads)
+        return _Remat._backward(ctx, *grads)
+
+    @staticmethod
+    def _backward(ctx, *grads):
         tensors = ctx.saved_tensors
         replay = [
             t.detach().requires_grad_(need) if t.is_floating_point() else t.detach()

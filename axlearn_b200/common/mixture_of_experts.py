@@ -92,14 +92,31 @@ class Routing:
 
 def _slots_in_priority_order(expert_index: Tensor, num_experts: int, capacity: int) -> Tensor:
     """Position of each (token, choice) in its expert's buffer: all first choices in sequence
-    order, then all second choices, ...; -1 where the expert is already full."""
+    order, then all second choices, ...; -1 where the expert is already full.
+
+    One stable sort of the (group, expert) keys in choice-major order: the rank of an entry
+    among equal keys is its position (the reference takes a cumulative sum over a one-hot
+    ``[.., K*S, E]`` tensor instead)."""
     o, g, s, k = expert_index.shape
-    # [O, G, K*S] choice-major, as the reference flattens it.
-    flat = expert_index.permute(0, 1, 3, 2).reshape(o, g, k * s)
-    onehot = torch.nn.functional.one_hot(flat, num_experts)                 # [O, G, K*S, E]
-    pos = (onehot.cumsum(dim=2) * onehot).sum(dim=-1) - 1                   # [O, G, K*S]
+    flat = expert_index.permute(0, 1, 3, 2).reshape(o * g, k * s)           # choice-major
+    group = torch.arange(o * g, device=flat.device)[:, None]
+    keys = (group * num_experts + flat).reshape(-1)
+    order = torch.sort(keys, stable=True).indices
+    counts = torch.bincount(keys, minlength=o * g * num_experts)
+    starts = counts.cumsum(0) - counts
+    ranks = torch.arange(keys.numel(), device=keys.device) - starts[keys[order]]
+    pos = torch.empty_like(keys)
+    pos[order] = ranks
     pos = torch.where(pos < capacity, pos, torch.full_like(pos, -1))
     return pos.reshape(o, g, k, s).permute(0, 1, 3, 2).contiguous()
+
+
+def _expert_counts(index: Tensor, num_experts: int) -> Tensor:
+    """``index [O, G, S]`` of expert ids -> how many tokens chose each expert ``[O, G, E]``."""
+    o, g, s = index.shape
+    group = torch.arange(o * g, device=index.device)[:, None]
+    keys = (group * num_experts + index.reshape(o * g, s)).reshape(-1)
+    return torch.bincount(keys, minlength=o * g * num_experts).reshape(o, g, num_experts)
 
 
 class AdaptiveLoadBalanceLoss(BaseLayer):
@@ -150,38 +167,35 @@ class BaseGating(BaseLayer):
     def dispatch(self, x: Tensor, routing: Routing) -> Tensor:
         """``x [O, G, S, M] -> [O, E, G, C, M]``: every kept (token, choice) lands in its
         expert's slot; unfilled slots are zero."""
+        from axlearn_b200.ops import moe_ops
+
         o, g, s, m = x.shape
-        e, c, k = routing.num_experts, routing.expert_capacity, routing.expert_index.shape[-1]
-        dest, _ = _flat_destinations(routing)
-        src = torch.arange(o * g * s, device=x.device).repeat_interleave(k)
-        buf = torch.zeros((o * e * g * c + 1, m), dtype=x.dtype, device=x.device)
-        buf = buf.index_add(0, dest.reshape(-1), x.reshape(o * g * s, m)[src])
-        return buf[:-1].reshape(o, e, g, c, m)
+        e, c = routing.num_experts, routing.expert_capacity
+        out = moe_ops.dispatch(x.reshape(o * g * s, m), _flat_destinations(routing), o * e * g * c)
+        return out.reshape(o, e, g, c, m)
 
     @nowrap
     def combine(self, y: Tensor, routing: Routing, *, dtype=None) -> Tensor:
         """``y [O, E, G, C, M] -> [O, G, S, M]``: weighted sum of each token's expert outputs."""
+        from axlearn_b200.ops import moe_ops
+
         o, e, g, c, m = y.shape
         s, k = routing.expert_index.shape[2:]
-        dest, _ = _flat_destinations(routing)
-        padded = torch.cat([y.reshape(o * e * g * c, m), y.new_zeros((1, m))], dim=0)
-        gathered = padded[dest.reshape(-1)].reshape(o, g, s, k, m)
-        out = (gathered.float() * routing.weight[..., None]).sum(dim=3)
-        return out.to(dtype or y.dtype)
+        out = moe_ops.combine(y.reshape(o * e * g * c, m), routing.weight.reshape(o * g * s, k),
+                              _flat_destinations(routing))
+        return out.reshape(o, g, s, m).to(dtype or y.dtype)
 
 
-def _flat_destinations(routing: Routing) -> tuple[Tensor, Tensor]:
-    """Row of ``[O, E, G, C]`` (flattened) for every (token, choice); dropped ones point at the
-    extra trailing row."""
+def _flat_destinations(routing: Routing) -> Tensor:
+    """``[T, K]``: row of the flattened ``[O, E, G, C]`` expert buffer for every (token, choice),
+    -1 for dropped assignments."""
     o, g, s, k = routing.expert_index.shape
     e, c = routing.num_experts, routing.expert_capacity
     dev = routing.expert_index.device
     oo = torch.arange(o, device=dev).view(o, 1, 1, 1)
     gg = torch.arange(g, device=dev).view(1, g, 1, 1)
-    valid = routing.slot >= 0
-    dest = ((oo * e + routing.expert_index) * g + gg) * c + routing.slot.clamp(min=0)
-    dest = torch.where(valid, dest, torch.full_like(dest, o * e * g * c))
-    return dest, valid
+    dest = ((oo * e + routing.expert_index) * g + gg) * c + routing.slot
+    return torch.where(routing.slot >= 0, dest, torch.full_like(dest, -1)).reshape(o * g * s, k)
 
 
 class Top2Gating(BaseGating):
@@ -220,15 +234,15 @@ class Top2Gating(BaseGating):
         denom = gate_1 + gate_2 + 1e-9
         weights = torch.stack([gate_1 / denom, gate_2 / denom], dim=-1)
         # Load balance: fraction of tokens whose first choice is e, times the mean gate of e.
-        density_1 = torch.nn.functional.one_hot(index[..., 0], e).float().mean(dim=-2)
+        first = _expert_counts(index[..., 0], e)                            # [O, G, E]
+        density_1 = first.float() / index.shape[2]
         density_proxy = raw_gates.mean(dim=-2)
         aux = (density_1 * density_proxy).mean() * e * e
         slot = _slots_in_priority_order(index, e, capacity)
         kept = slot >= 0
         weights = weights * kept.float()
-        first = torch.nn.functional.one_hot(index[..., 0], e).sum(dim=-2)    # [O, G, E]
         over_1 = (first - capacity).clamp(min=0).sum() / first.sum().clamp(min=1)
-        second_total = torch.nn.functional.one_hot(index[..., 1], e).sum(dim=-2) + first
+        second_total = _expert_counts(index[..., 1], e) + first
         over_2 = (second_total - capacity).clamp(min=0).sum() / second_total.sum().clamp(min=1)
         z = _router_z_loss(logits)
         counts = kept.sum(dim=-1)
@@ -304,12 +318,12 @@ class TopKGating(BaseGating):
         index = self._compute_index(raw_gates, k=k)
         gate_w = torch.gather(raw_gates, -1, index)
         normalized = raw_gates if cfg.score_fn is None else raw_gates / raw_gates.sum(dim=-1, keepdim=True)
-        assigned = torch.nn.functional.one_hot(index, e).amax(dim=-2).float()  # [O, G, S, E]
-        aux = (assigned.mean(dim=-2) * normalized.mean(dim=-2)).mean() * e * e / k
+        # top-k indices of a token are distinct, so "assigned" counts are plain counts.
+        totals = sum(_expert_counts(index[..., j], e) for j in range(k))      # [O, G, E]
+        aux = (totals.float() / index.shape[2] * normalized.mean(dim=-2)).mean() * e * e / k
         slot = _slots_in_priority_order(index, e, capacity)
         kept = slot >= 0
         weights = gate_w / gate_w.sum(dim=-1, keepdim=True) * kept.float()
-        totals = torch.nn.functional.one_hot(index, e).sum(dim=(-3, -2))      # [O, G, E]
         over = (totals - capacity).clamp(min=0).sum() / totals.sum().clamp(min=1)
         self.add_summary("over_capacity_ratio", over)
         self.add_summary("router_z_loss", z.detach())

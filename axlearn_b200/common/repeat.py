@@ -63,6 +63,8 @@ class _LayerCall(torch.autograd.Function):
     @staticmethod
     def forward(ctx, run, gatherer, i, n_inputs, remat, *tensors):  # pylint: disable=arguments-differ
         ctx.run, ctx.gatherer, ctx.i, ctx.n_inputs, ctx.remat = run, gatherer, i, n_inputs, remat
+        # Backward runs on an autograd worker thread, where the thread-local mesh stack is empty.
+        ctx.mesh = current_mesh()
         inputs = tensors[:n_inputs]
         ctx.needs = [t.requires_grad for t in inputs]
         ctx.param_needs = [t.requires_grad for t in tensors[n_inputs:]]
@@ -83,6 +85,13 @@ class _LayerCall(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, *grads):  # pylint: disable=arguments-differ
+        if ctx.mesh is not None and current_mesh() is not ctx.mesh:
+            with ctx.mesh:
+                return _LayerCall._backward(ctx, *grads)
+        return _LayerCall._backward(ctx, *grads)
+
+    @staticmethod
+    def _backward(ctx, *grads):
         gatherer, i = ctx.gatherer, ctx.i
         if ctx.remat:
             inputs = ctx.saved_tensors

@@ -40,7 +40,9 @@ def _args():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", default="7B", help="Fuji size (7B is the benchmark; others for debugging)")
+    ap.add_argument("--model", default="7B", help="Fuji size (7B is the benchmark; others for debugging), or an "
+                    "envy preset with --family envy (Mixtral-8x7B: the MoE training configuration)")
+    ap.add_argument("--family", default="fuji", choices=["fuji", "envy"])
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--per_gpu_batch", type=int, default=4)
     ap.add_argument("--layers", type=int, default=None, help="debug only: override layer count")
@@ -146,11 +148,20 @@ def main():
     )
     from axlearn_b200.ops import cuda_ops
 
-    kw = fuji.get_trainer_kwargs(args.model, vocab_size=32768, version=fuji.Version.V2)
-    mk = dict(kw["model_kwargs"])
-    if args.layers:
-        mk["num_layers"] = args.layers
-    model_cfg = fuji.model_config(scan_chunk=8192, **mk)
+    moe = args.family == "envy"
+    kw = fuji.get_trainer_kwargs("7B" if moe else args.model, vocab_size=32768, version=fuji.Version.V2)
+    if moe:
+        from axlearn_b200.experiments.text.gpt import envy
+
+        mk = dict(envy.MODEL_PRESETS[args.model])
+        if args.layers:
+            mk["num_layers"] = args.layers
+        model_cfg = envy.model_config(scan_chunk=8192, **mk)
+    else:
+        mk = dict(kw["model_kwargs"])
+        if args.layers:
+            mk["num_layers"] = args.layers
+        model_cfg = fuji.model_config(scan_chunk=8192, **mk)
     # Full remat per layer: only each layer's input is kept.
     model_cfg.decoder.transformer.layer.remat_spec = RematSpec(prevent_cse=False, policy=nothing_saveable)
     global_batch = args.per_gpu_batch * world
@@ -158,7 +169,9 @@ def main():
         model_cfg=model_cfg,
         learner_cfg=adamw_decoupled_learner_config(max_step=kw["max_step"], **kw["learner_kwargs"]),
         max_step=kw["max_step"], train_batch_size=global_batch, max_sequence_length=args.seq,
-        vocab_size=32768, mesh_shape=mesh_shape_from_axes(fsdp=world), mesh_axis_names=MESH_AXIS_NAMES,
+        vocab_size=mk.get("vocab_size", 32768),
+        mesh_shape=mesh_shape_from_axes(**({"expert": world} if moe else {"fsdp": world})),
+        mesh_axis_names=MESH_AXIS_NAMES,
         train_dtype=torch.bfloat16)()
     cfg.dir = tempfile.mkdtemp(prefix="axb200_bench_")
     cfg.device = f"cuda:{local_rank}" if use_cuda else "cpu"
@@ -243,18 +256,25 @@ def main():
         # 6 * params * tokens (fwd+bwd) + attention; remat adds one more forward (reported
         # MFU counts model FLOPs only, i.e. without the recompute).
         layers, d, heads = mk["num_layers"], mk["hidden_dim"], mk["num_heads"]
-        dense_params = layers * (4 * d * d + 3 * d * 11008) + 32768 * d
+        if moe:
+            kvd = d * mk["num_kv_heads"] // heads
+            # Active parameters per token: attention + 2 of the experts.
+            dense_params = layers * (2 * d * d + 2 * d * kvd + 2 * 3 * d * mk["moe_ffn_dim"]) + mk["vocab_size"] * d
+        else:
+            dense_params = layers * (4 * d * d + 3 * d * 11008) + 32768 * d
         flops_per_token = 6 * dense_params + 6 * layers * d * args.seq  # causal attention: 12*L*d*T/2
         peak = 2.25e15
         result = {
-            "metric": "Fuji-7B train tokens/sec (max over ranks)",
+            "metric": ("MoE train tokens/sec (max over ranks)" if moe else "Fuji-7B train tokens/sec (max over ranks)"),
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": value / PUBLISHED_TOKENS_PER_S, "dtype": "bf16", "data": "synthetic",
+            "vs_baseline": None if moe else value / PUBLISHED_TOKENS_PER_S, "dtype": "bf16", "data": "synthetic",
             "impl": "ours",
             "config": {
-                "model": f"fuji-{args.model}-v2" + (f"-{args.layers}layers-DEBUG" if args.layers else ""),
-                "global_batch": global_batch, "seq_len": args.seq, "parallelism": f"fsdp{world}",
+                "model": (f"envy-{args.model}" if moe else f"fuji-{args.model}-v2") + (
+                    f"-{args.layers}layers-DEBUG" if args.layers else ""),
+                "global_batch": global_batch, "seq_len": args.seq,
+                "parallelism": f"expert{world} (dense parameters sharded over the same axis)" if moe else f"fsdp{world}",
                 "remat": "full per layer", "optimizer": "clip_by_global_norm(1)+adamw_decoupled, fp32 master+moments",
                 "l2": "per-step working set (>100 GB of parameters, moments and activations) exceeds the 126 MB L2",
             },
