@@ -75,6 +75,26 @@ def bench_gemm(args) -> dict:
             "flops": flops}
 
 
+def bench_gemm_fp8(args) -> dict:
+    """Block-scaled fp8 GEMM (1x128 activation scales, 128x128 weight scales); the library
+    column is the bf16 library GEMM of the same shape."""
+    from axlearn_b200.ops import fp8_ops
+
+    m, n, k = args.m, args.n, args.k
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    b = torch.randn(n, k, device="cuda").bfloat16()
+    aq, sa = fp8_ops.quantize_rows(a)
+    bq, sb = fp8_ops.quantize_blocks(b)
+    ours = _time(lambda: fp8_ops.gemm_fp8(aq, bq, sa, sb, a_gran=1), args.iters)
+    out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+    lib = _time(lambda: torch.matmul(a, b.t(), out=out), args.iters)
+    quant = _time(lambda: fp8_ops.quantize_rows(a), args.iters)
+    cuda_ops.check_status()
+    flops = 2.0 * m * n * k
+    return {"ms": ours, "tflops": flops / ours / 1e9, "library_ms": lib, "library_tflops": flops / lib / 1e9,
+            "flops": flops, "quantize_rows_ms": quant, "quantize_rows_gbs": 3.0 * m * k / quant / 1e6}
+
+
 def bench_flash(args, backward: bool) -> dict:
     b, t, n, nkv, h = args.batch, args.seq, args.heads, args.kv_heads or args.heads, args.head_dim
     q = torch.randn(b, t, n, h, device="cuda").bfloat16()
@@ -151,7 +171,7 @@ def bench_memory_bound(args) -> dict:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", required=True,
-                    choices=["gemm", "flash_fwd", "flash_bwd", "rmsnorm", "swiglu", "rope", "ce", "adamw"])
+                    choices=["gemm", "gemm_fp8", "flash_fwd", "flash_bwd", "rmsnorm", "swiglu", "rope", "ce", "adamw"])
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -167,6 +187,8 @@ def main() -> None:
     peaks = _peaks()
     if args.op == "gemm":
         r = bench_gemm(args)
+    elif args.op == "gemm_fp8":
+        r = bench_gemm_fp8(args)
     elif args.op in ("flash_fwd", "flash_bwd"):
         r = bench_flash(args, backward=args.op == "flash_bwd")
     else:
