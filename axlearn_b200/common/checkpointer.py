@@ -180,6 +180,17 @@ def read_state_spec(ckpt_dir: str) -> dict:
 # ------------------------------------------------------------------------------------------
 
 
+def read_state_tensors(ckpt_dir: str) -> dict[str, torch.Tensor]:
+    """Reads every array of a committed checkpoint in full: ``{path: tensor}`` (offline
+    inspection, tests, conversion tools)."""
+    out = {}
+    for path, value in read_index_file(ckpt_dir):
+        if isinstance(value, dict) and "shape" in value and "dtype" in value:
+            shape = tuple(ast.literal_eval(value["shape"])) if isinstance(value["shape"], str) else tuple(value["shape"])
+            out[path] = _read_array(ckpt_dir, path, want=tuple(slice(0, d) for d in shape), dtype=None)
+    return out
+
+
 class _Shard(NamedTuple):
     path: str
     host: torch.Tensor  # CPU copy of this rank's shard.

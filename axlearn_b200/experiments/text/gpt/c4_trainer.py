@@ -12,12 +12,7 @@ from axlearn_b200.experiments.text.gpt import fuji
 def named_trainer_configs() -> dict:
     configs = {}
     configs.update(fuji.trainer_configs())
-    try:
-        from axlearn_b200.experiments.text.gpt import envy, gspmd, qwen  # pylint: disable=import-outside-toplevel
+    from axlearn_b200.experiments.text.gpt import envy  # pylint: disable=import-outside-toplevel
 
-        configs.update(envy.trainer_configs())
-        configs.update(qwen.trainer_configs())
-        configs.update(gspmd.trainer_configs())
-    except ImportError:
-        pass
+    configs.update(envy.trainer_configs())
     return configs

@@ -93,3 +93,32 @@ def model_config(
 
 def preset(name: str, **overrides) -> causal_lm.Model.Config:
     return model_config(**{**MODEL_PRESETS[name], **overrides})
+
+
+def trainer_configs() -> dict:
+    """Named MoE trainer configs: ``envy-{preset}`` (synthetic input unless a source is wired)."""
+    from axlearn_b200.experiments.text.gpt.common import (
+        MESH_AXIS_NAMES,
+        adamw_decoupled_learner_config,
+        get_trainer_config_fn,
+        mesh_shape_from_axes,
+    )
+
+    def make(name):
+        def fn():
+            mk = dict(MODEL_PRESETS[name])
+            small = name == "test"
+            max_step = 50 if small else 250_000
+            return get_trainer_config_fn(
+                model_cfg=model_config(scan_chunk=None if small else 8192, **mk),
+                learner_cfg=adamw_decoupled_learner_config(
+                    peak_lr=3e-4 if not small else 3e-3, max_step=max_step, weight_decay=0.1,
+                    lr_warmup_steps=2 if small else 2000),
+                max_step=max_step, train_batch_size=8 if small else 16,
+                max_sequence_length=64 if small else 4096, vocab_size=mk["vocab_size"],
+                mesh_shape=mesh_shape_from_axes(expert=-1) if not small else mesh_shape_from_axes(),
+                mesh_axis_names=MESH_AXIS_NAMES)()
+
+        return fn
+
+    return {f"envy-{name}": make(name) for name in MODEL_PRESETS}
