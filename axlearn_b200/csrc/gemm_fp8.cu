@@ -8,16 +8,16 @@
 // (ga = 128); sB has one scale per 128x128 block (the weight recipe).  K and N are multiples
 // of 128.
 //
-// Each K block is one group of four tcgen05.mma.kind::f8f6f4 (128x128x32) into a tensor-memory
+// Each K block is one group of four tcgen05.mma.kind::f8f6f4 (128x256x32) into a tensor-memory
 // buffer with fp32 accumulation *within* the block; the scaling and the accumulation *across*
 // blocks happen in fp32 registers of the four accumulator warps, which read every finished
-// block with tcgen05.ld while the tensor core already works on the next block in the second
+// block with tcgen05.ld while the tensor core already works on the next block in the other
 // buffer.  This is the "promote every 128 K" scheme that block scaling needs, with the tensor
-// memory double buffer turning the promotion into a pipeline stage instead of a stall.
+// memory ring turning the promotion into a pipeline stage instead of a stall.
 //
-// Warp roles (320 threads, persistent over output tiles): warp 0 TMA producer (6 stages of
-// 128x128 A + 128x128 B bytes, 128-byte swizzle), warp 1 MMA issuer, warps 2-9 accumulate /
-// scale / store (thread = one output row x 64 columns, fp32 accumulators in registers).
+// Warp roles (320 threads, persistent over output tiles): warp 0 TMA producer (4 stages of
+// 128x128 A + 256x128 B bytes, 128-byte swizzle), warp 1 MMA issuer, warps 2-9 accumulate /
+// scale / store (thread = one output row x 128 columns, fp32 accumulators in registers).
 //
 // Quantisers: `quantize_rows` (1x128 blocks along the contiguous dim), `quantize_blocks`
 // (128x128 blocks, optionally writing the transposed matrix) produce the byte matrices and
@@ -34,8 +34,9 @@
 
 namespace axb {
 
-constexpr int kF8BM = 128, kF8BN = 128, kF8BK = 128;
-constexpr int kF8Stages = 6;
+constexpr int kF8BM = 128, kF8BN = 256, kF8BK = 128;
+constexpr int kF8Stages = 4;
+constexpr int kF8AccBufs = 2;  // tensor-memory accumulator ring (2 x 256 columns = all of TMEM)
 constexpr int kF8Threads = 320;  // producer, MMA issuer, 8 accumulator warps
 constexpr int kF8StageBytes = kF8BM * kF8BK + kF8BN * kF8BK;  // 32 KB
 constexpr int kF8Smem = kF8Stages * kF8StageBytes + 1024 + 1024;
@@ -61,12 +62,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_base);
   uint64_t* empty_bar = full_bar + kF8Stages;
   uint64_t* acc_full = empty_bar + kF8Stages;
-  uint64_t* acc_empty = acc_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* acc_empty = acc_full + kF8AccBufs;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kF8AccBufs);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_blocks = (p.M + kF8BM - 1) / kF8BM;
-  const int n_blocks = p.N / kF8BN;
+  const int n_blocks = (p.N + kF8BN - 1) / kF8BN;
   const int num_tiles = m_blocks * n_blocks;
   const int num_kb = p.K / kF8BK;
 
@@ -77,7 +78,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < kF8AccBufs; ++a) {
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 8);
     }
@@ -85,7 +86,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     fence_proxy_async();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 256);
+    tmem_alloc(tmem_slot, kF8AccBufs * kF8BN);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -128,12 +129,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
-      uint32_t it = 0;  // K blocks issued so far: buffer = it & 1
+      uint32_t it = 0;  // K blocks issued so far: buffer = it % kF8AccBufs
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int buf = it & 1;
-          if (!mbar_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1, p.status, kStatusWaitTimeoutMma) ||
+          const int buf = it % kF8AccBufs;
+          if (!mbar_wait(&acc_empty[buf], ((it / kF8AccBufs) & 1) ^ 1, p.status, kStatusWaitTimeoutMma) ||
               !mbar_wait(&full_bar[stage], phase, p.status, kStatusWaitTimeoutMma)) {
             ok = false;
             break;
@@ -172,37 +173,40 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const int row = m_blk * kF8BM + quarter * 32 + lane;
       const int srow = min(row, p.M - 1) / p.a_gran;
       const float* sa_row = p.sa + static_cast<int64_t>(srow) * num_kb;
-      const float* sb_row = p.sb + static_cast<int64_t>(n_blk) * num_kb;
+      // One weight scale per 128 columns: this warp's half of the 256-wide tile is one block.
+      const int sb_blk = min(n_blk * 2 + half, p.N / 128 - 1);
+      const float* sb_row = p.sb + static_cast<int64_t>(sb_blk) * num_kb;
       float acc[kCols];
 #pragma unroll
       for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
       float scale_next = sa_row[0] * sb_row[0];
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        const int buf = it & 1;
+        const int buf = it % kF8AccBufs;
         const float scale = scale_next;
         if (kb + 1 < num_kb) scale_next = sa_row[kb + 1] * sb_row[kb + 1];
-        if (!mbar_wait(&acc_full[buf], (it >> 1) & 1, p.status, kStatusWaitTimeoutEpilogue)) {
+        if (!mbar_wait(&acc_full[buf], (it / kF8AccBufs) & 1, p.status, kStatusWaitTimeoutEpilogue)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
         const uint32_t taddr =
             tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kF8BN + half * kCols;
-        uint32_t r0[32], r1[32];
-        tmem_ld_32x32(taddr, r0);
-        tmem_ld_32x32(taddr + 32, r1);
-        tmem_ld_wait();
-        // This warp's part of the buffer is in registers: hand it back to the tensor core.
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[buf]);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          acc[j] = fmaf(__uint_as_float(r0[j]), scale, acc[j]);
-          acc[32 + j] = fmaf(__uint_as_float(r1[j]), scale, acc[32 + j]);
+        for (int c = 0; c < kCols; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c, r);
+          tmem_ld_wait();
+          if (c + 32 == kCols) {
+            // This warp's part of the buffer is in registers: hand it back to the tensor core.
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[c + j] = fmaf(__uint_as_float(r[j]), scale, acc[c + j]);
         }
       }
-      if (ok && row < p.M) {
+      if (ok && row < p.M && n_blk * kF8BN + half * kCols < p.N) {
         OutT* crow = C + static_cast<int64_t>(row) * p.ldc + n_blk * kF8BN + half * kCols;
         if constexpr (sizeof(OutT) == 2) {
 #pragma unroll
@@ -231,7 +235,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     }
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 256);
+    tmem_dealloc(tmem_base, kF8AccBufs * kF8BN);
   }
 }
 
@@ -353,7 +357,7 @@ extern "C" int axb_gemm_fp8(const void* A, const void* B, void* C, const float* 
       return -3;
     configured = true;
   }
-  const int tiles = ((M + kF8BM - 1) / kF8BM) * (N / kF8BN);
+  const int tiles = ((M + kF8BM - 1) / kF8BM) * ((N + kF8BN - 1) / kF8BN);
   int cap = max_ctas > 0 && max_ctas < sm_count() ? max_ctas : sm_count();
   const int grid = tiles < cap ? tiles : cap;
   Fp8GemmParams p{M, N, K, C, ldc, sa, sb, a_gran, status};
