@@ -43,6 +43,7 @@ def _args():
     ap.add_argument("--model", default="7B", help="Fuji size (7B is the benchmark; others for debugging), or an "
                     "envy preset with --family envy (Mixtral-8x7B: the MoE training configuration)")
     ap.add_argument("--family", default="fuji", choices=["fuji", "envy"])
+    ap.add_argument("--fp8", action="store_true", help="block-scaled fp8 projection GEMMs (FP8ConfigModifier)")
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--per_gpu_batch", type=int, default=4)
     ap.add_argument("--layers", type=int, default=None, help="debug only: override layer count")
@@ -173,6 +174,10 @@ def main():
         mesh_shape=mesh_shape_from_axes(**({"expert": world} if moe else {"fsdp": world})),
         mesh_axis_names=MESH_AXIS_NAMES,
         train_dtype=torch.bfloat16)()
+    if args.fp8:
+        from axlearn_b200.common.trainer_config_modifier import FP8ConfigModifier
+
+        cfg = FP8ConfigModifier.default_config().set(scaling="block").instantiate()(cfg)
     cfg.dir = tempfile.mkdtemp(prefix="axb200_bench_")
     cfg.device = f"cuda:{local_rank}" if use_cuda else "cpu"
     trainer = cfg.instantiate(parent=None)
@@ -268,7 +273,7 @@ def main():
             "metric": ("MoE train tokens/sec (max over ranks)" if moe else "Fuji-7B train tokens/sec (max over ranks)"),
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None if moe else value / PUBLISHED_TOKENS_PER_S, "dtype": "bf16", "data": "synthetic",
+            "vs_baseline": None if moe else value / PUBLISHED_TOKENS_PER_S, "dtype": "fp8 (block-scaled projections) + bf16" if args.fp8 else "bf16", "data": "synthetic",
             "impl": "ours",
             "config": {
                 "model": (f"envy-{args.model}" if moe else f"fuji-{args.model}-v2") + (
