@@ -51,6 +51,7 @@ from axlearn_b200.common.config import (
 )
 from axlearn_b200.common.input_base import Input
 from axlearn_b200.common.learner import Learner
+from axlearn_b200.common.metrics import MetricAccumulator
 from axlearn_b200.common.module import Module, OutputCollection, functional
 from axlearn_b200.common.optimizer_base import OptParam
 from axlearn_b200.common.summary_writer import BaseWriter, SummaryWriter
@@ -129,6 +130,9 @@ class SpmdTrainer(Module):
         device_monitor: Optional[InstantiableConfig] = None
         recorder: Optional[InstantiableConfig] = None
         save_input_iterator: bool = False
+        # Micro-batches per optimizer step (the per-process batch is split along dim 0 and the
+        # gradients are averaged); see GradientAccumulationModifier.
+        grad_accumulation_steps: int = 1
         prune_empty_state_updates: bool = True
         # Device to train on; None = cuda:LOCAL_RANK when available else cpu.
         device: Optional[str] = None
@@ -424,13 +428,27 @@ class SpmdTrainer(Module):
         new_key, _noise_key, fwd_key, _learner_key = prng.split(state["prng_key"], 4)
         batch = self.input.dispatch_global_batch(batch)
         self._zero_grads()
-        if self._device.type == "cuda":
-            from axlearn_b200.parallel import fsdp_fused
+        steps = max(1, cfg.grad_accumulation_steps)
+        micro_batches = _split_batch(batch, steps)
+        fwd_keys = prng.split(fwd_key, steps) if steps > 1 else [fwd_key]
+        loss, aux, oc = None, None, None
+        acc = MetricAccumulator() if steps > 1 else None
+        for micro, key in zip(micro_batches, fwd_keys):
+            if self._device.type == "cuda":
+                from axlearn_b200.parallel import fsdp_fused
 
-            fsdp_fused.begin_step_all()
-        (loss, aux), oc = functional(
-            self.model, fwd_key, self._shadows, [batch], is_training=True, method="forward")
-        loss.backward()
+                # Cross-rank ordering of the gradient staging buffers (once per micro-batch).
+                fsdp_fused.begin_step_all(accumulate=micro is not micro_batches[0])
+            (micro_loss, aux), oc = functional(
+                self.model, key, self._shadows, [micro], is_training=True, method="forward")
+            # Micro-batch gradients are averaged (reference: gradient_accumulation.py:96-351).
+            (micro_loss / steps).backward()
+            loss = micro_loss.detach() / steps if loss is None else loss + micro_loss.detach() / steps
+            if acc is not None:
+                acc.update(oc.summaries)
+        if acc is not None:
+            oc.summaries.clear()
+            oc.summaries.update(acc.summaries())
         fsdp.wait_pending(self._device if self._device.type == "cuda" else None)
         grads = tree_map(lambda s: s.grad if s.requires_grad else None, self._shadows)
         grad_sync.sync_grads(grads, specs=self._model_param_specs, mesh=self._mesh)
@@ -541,6 +559,17 @@ class SpmdTrainer(Module):
                 if cfg.crash_on_hang_timeout_seconds and stalled >= cfg.crash_on_hang_timeout_seconds and self._trainer_state is not None:
                     os.kill(os.getpid(), signal.SIGKILL)
                 last_change = time.time() if not cfg.crash_on_hang_timeout_seconds else last_change
+
+
+def _split_batch(batch: dict, steps: int) -> list:
+    """Splits every tensor of a batch into ``steps`` equal chunks along dim 0."""
+    if steps == 1:
+        return [batch]
+    sizes = {t.shape[0] for _, t in flatten_items(batch) if isinstance(t, Tensor) and t.dim() > 0}
+    if any(n % steps for n in sizes):
+        raise ValueError(f"per-process batch sizes {sorted(sizes)} are not divisible by {steps} accumulation steps")
+    return [tree_map(lambda t, i=i: t.chunk(steps, dim=0)[i] if isinstance(t, Tensor) and t.dim() > 0 else t, batch)
+            for i in range(steps)]
 
 
 def _takes_model(cfg) -> bool:

@@ -43,13 +43,9 @@ class GradientAccumulationModifier(ConfigModifier):
         metric_accumulator: Optional[InstantiableConfig] = None
 
     def __call__(self, cfg):
-        cfg.learner.forward_fn_transformation = None if "forward_fn_transformation" not in cfg.learner else cfg.learner.forward_fn_transformation
-        if "grad_acc_steps" in cfg.learner:
-            cfg.learner.grad_acc_steps = self._config.grad_acc_steps
-        else:
-            cfg.input.global_batch_size = cfg.input.global_batch_size
-        cfg.set(**{})
-        object.__getattribute__(cfg, "_values").setdefault("grad_acc_steps", self._config.grad_acc_steps) if False else None
+        """The reference wraps the learner's forward function in ``with_minibatch_steps``
+        (axlearn/common/trainer_config_modifier.py:60-103); here the trainer owns the loop."""
+        cfg.grad_accumulation_steps = self._config.grad_acc_steps
         return cfg
 
 

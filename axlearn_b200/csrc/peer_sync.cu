@@ -5,7 +5,7 @@
 //                       orders this stream's earlier stores to peer memory before the flag.
 //   axb_wait_flags      waits (bounded) until `count` local flags all equal `value`; on timeout
 //                       records a code in the status word and returns (the stream continues).
-//   axb_reduce_slots    out[i] = sum_r staging[r][i] in fp32 and fixed slot order (so the result
+//   axb_reduce_slots    out[i] (+)= sum_r staging[r][i] in fp32 and fixed slot order (so the result
 //                       is bit-reproducible), written as bf16; optionally accumulates the sum
 //                       of squares of the result into per-CTA partials for global-norm clipping.
 //
@@ -47,7 +47,7 @@ struct alignas(16) V8 {
 };
 
 __global__ void reduce_slots_kernel(const __nv_bfloat16* __restrict__ staging, __nv_bfloat16* __restrict__ out,
-                                    int slots, int64_t n, float* __restrict__ sumsq_partial) {
+                                    int slots, int64_t n, float* __restrict__ sumsq_partial, int accumulate) {
   __shared__ float red[32];
   const int64_t nvec = n / 8;
   float ss = 0.f;
@@ -56,6 +56,15 @@ __global__ void reduce_slots_kernel(const __nv_bfloat16* __restrict__ staging, _
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    if (accumulate) {
+      const V8 a = reinterpret_cast<const V8*>(out)[i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(a.v[j]);
+        acc[2 * j] = f.x;
+        acc[2 * j + 1] = f.y;
+      }
+    }
     for (int r = 0; r < slots; ++r) {
       const V8 a = reinterpret_cast<const V8*>(staging + r * n)[i];
 #pragma unroll
@@ -112,10 +121,11 @@ extern "C" int axb_reduce_slots_ctas(int64_t n) {
 
 // n must be a multiple of 8. Uses few CTAs on purpose: it runs beside the backward GEMMs.
 extern "C" int axb_reduce_slots(const void* staging, void* out, int slots, int64_t n, float* sumsq_partial,
-                                cudaStream_t stream) {
+                                int accumulate, cudaStream_t stream) {
   if (n % 8) return -10;
   axb::reduce_slots_kernel<<<axb_reduce_slots_ctas(n), 256, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(staging), static_cast<__nv_bfloat16*>(out), slots, n, sumsq_partial);
+      static_cast<const __nv_bfloat16*>(staging), static_cast<__nv_bfloat16*>(out), slots, n, sumsq_partial,
+      accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

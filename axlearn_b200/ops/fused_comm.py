@@ -78,7 +78,7 @@ def _lib():
         h.axb_wait_flags.restype = c_int
         h.axb_reduce_slots_ctas.argtypes = [c_int64]
         h.axb_reduce_slots_ctas.restype = c_int
-        h.axb_reduce_slots.argtypes = [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p]
+        h.axb_reduce_slots.argtypes = [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_int, c_void_p]
         h.axb_reduce_slots.restype = c_int
         _configured = True
     return h
@@ -194,14 +194,15 @@ def gemm_rs(a: torch.Tensor, b: torch.Tensor, *, staging_ptrs: Sequence[int], ra
     cuda_ops._check(rc, "axb_gemm_bf16_fused(rs)")  # pylint: disable=protected-access
 
 
-def reduce_slots(staging: torch.Tensor, out: torch.Tensor, *, sumsq_partial: Optional[torch.Tensor] = None) -> None:
-    """``out = sum_r staging[r]`` (fp32 accumulation, fixed order, bf16 result)."""
+def reduce_slots(staging: torch.Tensor, out: torch.Tensor, *, sumsq_partial: Optional[torch.Tensor] = None,
+                 accumulate: bool = False) -> None:
+    """``out (+)= sum_r staging[r]`` (fp32 accumulation, fixed order, bf16 result)."""
     slots = staging.shape[0]
     n = out.numel()
     assert staging.numel() == slots * n and staging.is_contiguous() and out.is_contiguous()
     rc = _lib().axb_reduce_slots(staging.data_ptr(), out.data_ptr(), slots, n,
                                  None if sumsq_partial is None else sumsq_partial.data_ptr(),
-                                 cuda_ops._stream())  # pylint: disable=protected-access
+                                 1 if accumulate else 0, cuda_ops._stream())  # pylint: disable=protected-access
     cuda_ops._check(rc, "axb_reduce_slots")  # pylint: disable=protected-access
 
 

@@ -158,14 +158,21 @@ class FusedLayerGatherer:
         self._epoch = 1
         self._current: Optional[int] = None
         self._current_records: list[list[PendingMatrix]] = []
+        self._accumulate = False
         self._flags_sym.barrier()
 
     # ------------------------------------------------------------------ step protocol
-    def begin_step(self) -> None:
+    def begin_step(self, accumulate: bool = False) -> None:
         """Cross-rank barrier: peers' parameter shards are final, and their reductions of the
-        previous step no longer read the staging buffers."""
+        previous step (or micro-batch) no longer read the staging buffers.  ``accumulate``:
+        this micro-batch's gradients are added to what ``stacked.grad`` already holds."""
         self._epoch += 1
-        self.invalidate()
+        self._accumulate = accumulate
+        if not accumulate:
+            self.invalidate()
+        else:
+            # The reductions of the previous micro-batch run on the side stream.
+            torch.cuda.current_stream(self._device).wait_stream(self._stream)
         self._flags_sym.barrier()
 
     def invalidate(self) -> None:
@@ -230,7 +237,7 @@ class FusedLayerGatherer:
                     raise RuntimeError("gradient buffers of stacked leaves must be allocated before backward")
                 grad_i = t.grad[i].reshape(leaf.nb, leaf.rows_local * leaf.cols)
                 for j in range(leaf.nb):
-                    fused_comm.reduce_slots(leaf.staging[i, j], grad_i[j])
+                    fused_comm.reduce_slots(leaf.staging[i, j], grad_i[j], accumulate=self._accumulate)
                 fsdp._touched.setdefault(id(t), set()).add(i)  # pylint: disable=protected-access
 
 
@@ -241,10 +248,11 @@ def register(gatherer: "FusedLayerGatherer") -> None:
     _active.append(gatherer)
 
 
-def begin_step_all() -> None:
-    """Called by the trainer at the start of every step (after the previous optimizer update)."""
+def begin_step_all(accumulate: bool = False) -> None:
+    """Called by the trainer before every forward/backward pass: at the start of a step (after
+    the previous optimizer update) and, with ``accumulate``, before each further micro-batch."""
     for g in _active:
-        g.begin_step()
+        g.begin_step(accumulate)
 
 
 def invalidate_all() -> None:
