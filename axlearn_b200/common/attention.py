@@ -739,8 +739,13 @@ class MultiheadAttention(BaseLayer):
         b, t = query.shape[:2]
         dev = query.device
         default_positions = query_positions is None
+        # Ulysses sequence parallelism: activations hold this rank's contiguous slice of the
+        # sequence; attention itself runs on whole sequences with a slice of the heads.
+        sp = _seq_parallel_size() if (mode == ForwardMode.FORWARD and is_self_attention) else 1
         if query_positions is None:
             query_positions = torch.arange(t, device=dev)[None]
+            if sp > 1:
+                query_positions = query_positions + coll.axis_index("seq") * t
         elif query_positions.dim() == 1:
             query_positions = query_positions[None]
         key_positions = (
@@ -768,6 +773,15 @@ class MultiheadAttention(BaseLayer):
             else:
                 k_proj = self.scale_key(k_proj)
 
+        if sp > 1:
+            if not default_positions:
+                raise NotImplementedError("sequence parallelism needs default (contiguous) positions")
+            q_proj, k_proj, v_proj = (_seq_to_heads(x, sp) for x in (q_proj, k_proj, v_proj))
+            t = t * sp
+            query_positions = key_positions = torch.arange(t, device=dev)[None]
+            if segment_ids is not None:
+                segment_ids = coll.all_gather_raw(
+                    segment_ids.contiguous(), coll.current_group("seq"), sp, 1)
         new_cached_states = None
         live_kv: Optional[KVState] = None
         if mode == ForwardMode.FORWARD:
@@ -840,6 +854,8 @@ class MultiheadAttention(BaseLayer):
                 q_proj=q_proj, k_proj=dense_kv.k_proj, v_proj=dense_kv.v_proj,
                 bias=bias_val, softmax_scale=softmax_scale, want_probs=want_probs,
             )
+        if sp > 1:
+            context = coll.all_to_all(context, "seq", split_dim=1, concat_dim=2)
         context = self._remat_name(context, "context")
         o = self.o_proj(context)
         o = self._remat_name(o, "o_proj")
@@ -966,6 +982,25 @@ class MultiheadAttention(BaseLayer):
             attention_logit_biases=attention_logit_biases, cached_states=cached_states,
             return_aux=return_aux, page_pool=page_pool,
         )
+
+
+def _seq_parallel_size() -> int:
+    from axlearn_b200.parallel.mesh import current_mesh
+
+    mesh = current_mesh()
+    return mesh.shape.get("seq", 1) if mesh is not None else 1
+
+
+def _seq_to_heads(x: Tensor, sp: int) -> Tensor:
+    """``[B, T/sp, N, H] -> [B, T, N/sp, H]`` by an all-to-all over the ``seq`` axis; KV heads are
+    repeated first when there are fewer of them than ranks (reference:
+    axlearn/common/flash_attention/layer.py:204-216)."""
+    n = x.shape[2]
+    if n % sp:
+        if sp % n:
+            raise ValueError(f"{n} heads cannot be split over a seq axis of {sp}")
+        x = x.repeat_interleave(sp // n, dim=2)
+    return coll.all_to_all(x.contiguous(), "seq", split_dim=2, concat_dim=1)
 
 
 class GroupedQueryAttention(MultiheadAttention):

@@ -46,7 +46,9 @@ from axlearn_b200.parallel import collectives as coll
 Tensor = torch.Tensor
 
 # Mesh axes over which the batch dimension is split.
-BATCH_AXES = ("data", "expert", "fsdp")
+# Axes over which tokens are split: the batch axes, plus "seq" when sequences are sharded
+# (Ulysses-style sequence parallelism).
+BATCH_AXES = ("data", "expert", "fsdp", "seq")
 
 
 def _live_targets(input_batch: dict, target_labels: Tensor) -> Tensor:

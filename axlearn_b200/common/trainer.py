@@ -426,7 +426,7 @@ class SpmdTrainer(Module):
         cfg = self._config
         state = self._trainer_state
         new_key, _noise_key, fwd_key, _learner_key = prng.split(state["prng_key"], 4)
-        batch = self.input.dispatch_global_batch(batch)
+        batch = _shard_sequence(self.input.dispatch_global_batch(batch), self._mesh)
         self._zero_grads()
         steps = max(1, cfg.grad_accumulation_steps)
         micro_batches = _split_batch(batch, steps)
@@ -468,7 +468,7 @@ class SpmdTrainer(Module):
         state["prng_key"] = new_key
         # Each rank's loss is its share of the global mean (normalised by the global number of
         # live targets); the reported loss is the sum of the shares over the batch axes.
-        global_loss = coll.all_reduce_scalar(loss.detach().float(), ("data", "expert", "fsdp"))
+        global_loss = coll.all_reduce_scalar(loss.detach().float(), ("data", "expert", "fsdp", "seq"))
         return {"loss": global_loss, "aux": aux, "summaries": summaries}
 
     def _zero_grads(self) -> None:
@@ -559,6 +559,24 @@ class SpmdTrainer(Module):
                 if cfg.crash_on_hang_timeout_seconds and stalled >= cfg.crash_on_hang_timeout_seconds and self._trainer_state is not None:
                     os.kill(os.getpid(), signal.SIGKILL)
                 last_change = time.time() if not cfg.crash_on_hang_timeout_seconds else last_change
+
+
+def _shard_sequence(batch: dict, mesh) -> dict:
+    """Sequence parallelism (``seq`` mesh axis): every rank of a ``seq`` group receives the same
+    rows and keeps its contiguous slice of the time dim of each ``[B, T, ...]`` tensor."""
+    if mesh is None or "seq" not in mesh.shape or mesh.shape["seq"] == 1:
+        return batch
+    s, r = mesh.shape["seq"], mesh.coords["seq"]
+
+    def cut(t):
+        if not isinstance(t, Tensor) or t.dim() < 2:
+            return t
+        if t.shape[1] % s:
+            raise ValueError(f"sequence length {t.shape[1]} is not divisible by the seq axis ({s})")
+        n = t.shape[1] // s
+        return t[:, r * n:(r + 1) * n].contiguous()
+
+    return tree_map(cut, batch)
 
 
 def _split_batch(batch: dict, steps: int) -> list:

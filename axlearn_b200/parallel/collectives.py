@@ -40,6 +40,11 @@ def axis_index(axes: AxisSpec) -> int:
     return _group(axes)[2]
 
 
+def current_group(axes: AxisSpec):
+    """Process group of ``axes`` on the current mesh (None when the axes have extent 1)."""
+    return _group(axes)[0]
+
+
 # ------------------------------------------------------------------------------------------
 # Raw (non-differentiable) helpers.
 # ------------------------------------------------------------------------------------------

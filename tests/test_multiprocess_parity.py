@@ -64,7 +64,7 @@ def _worker(rank, world, port, directory, mesh_axes, steps, out_queue):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mesh_axes", [dict(fsdp=2), dict(model=2), dict(fsdp=2, model=2), dict(data=2)])
+@pytest.mark.parametrize("mesh_axes", [dict(fsdp=2), dict(model=2), dict(fsdp=2, model=2), dict(data=2), dict(seq=2)])
 def test_sharded_matches_single_process(tmp_path, mesh_axes):
     steps = 3
     world = 1
