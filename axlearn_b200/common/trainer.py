@@ -433,6 +433,7 @@ class SpmdTrainer(Module):
         fwd_keys = prng.split(fwd_key, steps) if steps > 1 else [fwd_key]
         loss, aux, oc = None, None, None
         acc = MetricAccumulator() if steps > 1 else None
+        pipeline_scale = 1.0 / self._mesh.shape.get("pipeline", 1) if self._mesh is not None else 1.0
         for micro, key in zip(micro_batches, fwd_keys):
             if self._device.type == "cuda":
                 from axlearn_b200.parallel import fsdp_fused
@@ -442,7 +443,8 @@ class SpmdTrainer(Module):
             (micro_loss, aux), oc = functional(
                 self.model, key, self._shadows, [micro], is_training=True, method="forward")
             # Micro-batch gradients are averaged (reference: gradient_accumulation.py:96-351).
-            (micro_loss / steps).backward()
+            # Pipeline ranks each hold 1/num_stages of the loss gradient (see common/pipeline.py).
+            (micro_loss * (pipeline_scale / steps)).backward()
             loss = micro_loss.detach() / steps if loss is None else loss + micro_loss.detach() / steps
             if acc is not None:
                 acc.update(oc.summaries)
@@ -450,6 +452,11 @@ class SpmdTrainer(Module):
             oc.summaries.clear()
             oc.summaries.update(acc.summaries())
         fsdp.wait_pending(self._device if self._device.type == "cuda" else None)
+        if self._mesh is not None and self._mesh.shape.get("pipeline", 1) > 1:
+            # A stage that does not touch a replicated parameter still takes part in its reduction.
+            for _, sh in flatten_items(self._shadows):
+                if isinstance(sh, Tensor) and sh.requires_grad and sh.grad is None:
+                    sh.grad = torch.zeros_like(sh)
         grads = tree_map(lambda s: s.grad if s.requires_grad else None, self._shadows)
         grad_sync.sync_grads(grads, specs=self._model_param_specs, mesh=self._mesh)
         summaries = {"model": oc.summaries}

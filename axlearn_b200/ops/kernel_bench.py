@@ -123,6 +123,33 @@ def bench_flash(args, backward: bool) -> dict:
             "flops": flops}
 
 
+def bench_decode_attn(args) -> dict:
+    """Paged decode attention: ``--batch`` sequences of ``--seq`` cached tokens, ``--heads`` query /
+    ``--kv_heads`` KV heads, 16-token pages; the library column is SDPA over the gathered dense cache."""
+    from axlearn_b200.ops import decode_ops
+
+    b, t, nq, nkv, h, ps = args.batch, args.seq, args.heads, args.kv_heads or args.heads, args.head_dim, 16
+    pages = t // ps
+    k = torch.randn(b * pages, ps, nkv, h, device="cuda").bfloat16()
+    v = torch.randn(b * pages, ps, nkv, h, device="cuda").bfloat16()
+    table = torch.randperm(b * pages, device="cuda").to(torch.int32).reshape(b, pages).contiguous()
+    lengths = torch.full((b,), t, dtype=torch.int32, device="cuda")
+    q = torch.randn(b, nq, h, device="cuda").bfloat16()
+    splits = decode_ops.default_splits(b, nkv, nq // nkv, t, ps)
+    scratch = torch.empty(decode_ops._lib().axb_decode_attn_scratch_floats(b, nq, splits), device="cuda")  # pylint: disable=protected-access
+    out = torch.empty_like(q)
+    ours = _time(lambda: decode_ops.paged_decode_attention(q, k, v, table, lengths, splits=splits, out=out,
+                                                           scratch=scratch), args.iters)
+    kd = k.reshape(b, t, nkv, h).transpose(1, 2)
+    vd = v.reshape(b, t, nkv, h).transpose(1, 2)
+    qd = q[:, :, None, :]
+    lib = _time(lambda: torch.nn.functional.scaled_dot_product_attention(qd, kd, vd, enable_gqa=nkv != nq), args.iters)
+    cuda_ops.check_status()
+    nbytes = 2 * k.numel() * 2
+    return {"ms": ours, "gbs": nbytes / ours / 1e6, "library_ms": lib, "library_gbs": nbytes / lib / 1e6,
+            "bytes": nbytes, "kv_splits": splits}
+
+
 def bench_memory_bound(args) -> dict:
     rows, d = args.m, args.n
     x = torch.randn(rows, d, device="cuda").bfloat16()
@@ -171,7 +198,8 @@ def bench_memory_bound(args) -> dict:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", required=True,
-                    choices=["gemm", "gemm_fp8", "flash_fwd", "flash_bwd", "rmsnorm", "swiglu", "rope", "ce", "adamw"])
+                    choices=["gemm", "gemm_fp8", "flash_fwd", "flash_bwd", "decode_attn", "rmsnorm", "swiglu", "rope", "ce",
+                             "adamw"])
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -189,6 +217,8 @@ def main() -> None:
         r = bench_gemm(args)
     elif args.op == "gemm_fp8":
         r = bench_gemm_fp8(args)
+    elif args.op == "decode_attn":
+        r = bench_decode_attn(args)
     elif args.op in ("flash_fwd", "flash_bwd"):
         r = bench_flash(args, backward=args.op == "flash_bwd")
     else:

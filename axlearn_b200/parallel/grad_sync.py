@@ -23,6 +23,9 @@ from axlearn_b200.common.utils import TensorSpec, flatten_items
 from axlearn_b200.parallel.mesh import Mesh, current_mesh
 
 BATCH_AXES = ("data", "expert", "fsdp", "seq")
+# Parameters replicated over the pipeline axis (embeddings, final norm, head) receive a part of
+# their gradient on every stage (see common/pipeline.py), so it is summed over that axis too.
+REDUCE_AXES = BATCH_AXES + ("pipeline",)
 
 
 def _axes_in_spec(mesh_axes: Optional[Sequence[Any]]) -> set:
@@ -51,7 +54,7 @@ def sync_grads(grads: Any, *, specs: Any, mesh: Optional[Mesh] = None, skip_stor
         if g is None:
             continue
         used = _axes_in_spec(spec.mesh_axes if spec is not None else None)
-        missing = tuple(a for a in mesh.present_axes(BATCH_AXES) if a not in used)
+        missing = tuple(a for a in mesh.present_axes(REDUCE_AXES) if a not in used)
         if not missing:
             continue
         group = mesh.group(missing)

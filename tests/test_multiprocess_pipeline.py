@@ -1,0 +1,75 @@
+"""Pipeline parallelism on gloo ranks must reproduce the same model run on one process."""
+
+import os
+import socket
+import sys
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _train(directory, mesh_axes: dict, steps: int):
+    sys.path.insert(0, REPO)
+    from axlearn_b200.common import prng
+    from axlearn_b200.common.pipeline import PipelinedTransformerLayer
+    from axlearn_b200.experiments.text.gpt.common import mesh_shape_from_axes
+    from tests.helpers import tiny_fuji_trainer_config
+
+    stack = PipelinedTransformerLayer.default_config().set(num_stages=2, num_microbatches=2)
+    cfg = tiny_fuji_trainer_config(
+        directory, max_step=steps, save_every_n_steps=1000, mesh_shape=mesh_shape_from_axes(**mesh_axes),
+        hidden=32, heads=2, ffn=64, vocab=128, seq=16, batch=4, layers=4, stack_cfg=stack)
+    trainer = cfg.instantiate(parent=None)
+    trainer.init(prng.PRNGKey(0))
+    losses = []
+    data = iter(trainer.input.dataset())
+    for _ in range(steps):
+        losses.append(trainer.train_step(next(data))["loss"].item())
+    stages = trainer.trainer_state["model"]["decoder"]["transformer"]["pipeline"]["layer"]
+    w = stages["layer1"]["feed_forward"]["linear2"]["weight"]
+    emb = trainer.trainer_state["model"]["decoder"]["emb"]["token_emb"]["weight"]
+    return losses, w.clone(), emb.clone()
+
+
+def _worker(rank, world, port, directory, steps, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        q.put((rank,) + _train(os.path.join(directory, f"r{rank}"), dict(pipeline=2), steps))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_stage_pipeline_matches_single_process(tmp_path):
+    steps, world = 3, 2
+    ref_losses, ref_w, ref_emb = _train(tmp_path / "single", {}, steps)
+    assert ref_w.shape[0] == 2       # both stages live on the one rank
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, str(tmp_path), steps, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in range(world):
+        rank, losses, w, emb = q.get(timeout=120)
+        got[rank] = (losses, w, emb)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for r in range(world):
+        for a, b in zip(got[r][0], ref_losses):
+            assert abs(a - b) < 1e-4 * abs(b), (got[r][0], ref_losses)
+        # Rank r holds stage r only.
+        assert got[r][1].shape[0] == 1
+        assert torch.allclose(got[r][1][0], ref_w[r], atol=3e-5, rtol=1e-3)
+        assert torch.allclose(got[r][2], ref_emb, atol=3e-5, rtol=1e-3)
