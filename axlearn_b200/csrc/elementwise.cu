@@ -223,6 +223,46 @@ __global__ void swiglu_bwd_kernel(const bf16* __restrict__ gate, const bf16* __r
 // ------------------------------------------------------------------------------ RoPE
 // x: [B, T, N, H] contiguous, interleaved pairs (x[2i], x[2i+1]); angle = pos[t] * theta^(-2i/H).
 // sign = +1 forward, -1 backward (rotation by the negative angle). In-place safe.
+//
+// The angles depend on (t, i) only, so a first tiny kernel fills a [T, H/2] table of (sin, cos)
+// -- T * H/2 evaluations instead of B * T * N * H/2 -- and the main kernel is a pure streaming
+// pass: 16-byte loads of x, the table row from L2, 16-byte stores.
+__global__ void rope_table_kernel(const int64_t* __restrict__ pos, float2* __restrict__ table, int T, int hp,
+                                  int H, float log2_theta) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= T * hp) return;
+  const int i = idx % hp, t = idx / hp;
+  const float inv_freq = exp2f(-(2.f * i / H) * log2_theta);
+  float s, c;
+  sincosf(static_cast<float>(pos[t]) * inv_freq, &s, &c);
+  table[idx] = make_float2(s, c);
+}
+
+__global__ void rope_apply_kernel(const Bf16x8* __restrict__ x, Bf16x8* __restrict__ y,
+                                  const float2* __restrict__ table, int64_t total_vec, int T, int N, int hp,
+                                  float sign) {
+  const int vec_per_head = hp / 4;  // 4 pairs (8 elements) per 16-byte vector
+  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total_vec;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int pv = idx % vec_per_head;
+    const int64_t bt = idx / (static_cast<int64_t>(vec_per_head) * N);
+    const int t = bt % T;
+    const float4* tab = reinterpret_cast<const float4*>(table + static_cast<int64_t>(t) * hp + pv * 4);
+    const float4 sc0 = __ldg(tab), sc1 = __ldg(tab + 1);  // (s0, c0, s1, c1), (s2, c2, s3, c3)
+    const float sn[4] = {sc0.x * sign, sc0.z * sign, sc1.x * sign, sc1.z * sign};
+    const float cs[4] = {sc0.y, sc0.w, sc1.y, sc1.w};
+    const Bf16x8 v = x[idx];
+    Bf16x8 o;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(v.v[j]);
+      o.v[j] = __floats2bfloat162_rn(f.x * cs[j] - f.y * sn[j], f.y * cs[j] + f.x * sn[j]);
+    }
+    y[idx] = o;
+  }
+}
+
+// Fallback without a table (H/2 not a multiple of 4, or no scratch given).
 __global__ void rope_kernel(const bf16* __restrict__ x, bf16* __restrict__ y,
                             const int64_t* __restrict__ pos, int64_t B, int T, int N, int H,
                             float log2_theta, float sign) {
@@ -351,6 +391,109 @@ __global__ void ce_fwd_bwd_kernel(T* __restrict__ logits, const int64_t* __restr
         float d = coef * __expf(v - lse);
         if (i == tgt) d -= g;
         lr[i] = from_f<T>(d);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// bf16 rows with V % 8 == 0: the same three passes with 16-byte accesses, the row staged in shared
+// memory as bf16 (V * 2 bytes, so three CTAs of 512 threads fit on an SM for V = 32768) and the
+// gradient written back with 16-byte stores.  Ties in the arg-max resolve to the lowest index.
+__global__ void __launch_bounds__(512)
+ce_fwd_bwd_bf16_vec_kernel(bf16* __restrict__ logits, const int64_t* __restrict__ targets,
+                           const uint8_t* __restrict__ live, float* __restrict__ ce_out,
+                           float* __restrict__ z_out, float* __restrict__ correct_out,
+                           const float* __restrict__ inv_denom_ptr, float z_scale, int64_t n, int V,
+                           int write_grad) {
+  __shared__ float red[32];
+  __shared__ int red_idx[32];
+  extern __shared__ __align__(16) unsigned char ce_smem[];
+  Bf16x8* cache = reinterpret_cast<Bf16x8*>(ce_smem);
+  const int nvec = V / 8;
+  const float inv_denom = *inv_denom_ptr;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int64_t row = blockIdx.x; row < n; row += gridDim.x) {
+    Bf16x8* lr = reinterpret_cast<Bf16x8*>(logits + row * V);
+    float m = -INFINITY;
+    int mi = 0x7fffffff;
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      const Bf16x8 v = lr[i];
+      cache[i] = v;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(v.v[j]);
+        if (f.x > m) {
+          m = f.x;
+          mi = i * 8 + 2 * j;
+        }
+        if (f.y > m) {
+          m = f.y;
+          mi = i * 8 + 2 * j + 1;
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, m, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, mi, o);
+      if (om > m || (om == m && oi < mi)) {
+        m = om;
+        mi = oi;
+      }
+    }
+    __syncthreads();
+    if (lane == 0) {
+      red[warp] = m;
+      red_idx[warp] = mi;
+    }
+    __syncthreads();
+    m = (lane < nw) ? red[lane] : -INFINITY;
+    mi = (lane < nw) ? red_idx[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, m, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, mi, o);
+      if (om > m || (om == m && oi < mi)) {
+        m = om;
+        mi = oi;
+      }
+    }
+    float se = 0.f;
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      const Bf16x8 v = cache[i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(v.v[j]);
+        se += __expf(f.x - m) + __expf(f.y - m);
+      }
+    }
+    se = block_sum(se, red);
+    const float lse = m + logf(se);
+    const int64_t tgt_raw = targets[row];
+    const bool is_live = live[row] != 0;
+    const int tgt = static_cast<int>(tgt_raw < 0 ? 0 : (tgt_raw >= V ? V - 1 : tgt_raw));
+    if (threadIdx.x == 0) {
+      const float picked = __bfloat162float(reinterpret_cast<const bf16*>(cache)[tgt]);
+      ce_out[row] = is_live ? (lse - picked) : 0.f;
+      z_out[row] = is_live ? lse * lse : 0.f;
+      correct_out[row] = (is_live && mi == tgt) ? 1.f : 0.f;
+    }
+    if (write_grad) {
+      const float g = is_live ? inv_denom : 0.f;
+      const float coef = g * (1.f + 2.f * z_scale * lse);
+      for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+        const Bf16x8 v = cache[i];
+        Bf16x8 o;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(v.v[j]);
+          float d0 = coef * __expf(f.x - lse), d1 = coef * __expf(f.y - lse);
+          if (i * 8 + 2 * j == tgt) d0 -= g;
+          if (i * 8 + 2 * j + 1 == tgt) d1 -= g;
+          o.v[j] = __floats2bfloat162_rn(d0, d1);
+        }
+        lr[i] = o;
       }
     }
     __syncthreads();
@@ -533,13 +676,26 @@ extern "C" int axb_swiglu_bwd(const void* gate, const void* up, const void* dout
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
+// `table`: optional scratch of T * H floats (sin/cos pairs); with it (and H % 8 == 0) the
+// table-driven streaming kernel runs, otherwise every element evaluates its own angle.
 extern "C" int axb_rope(const void* x, void* y, const int64_t* positions, int64_t B, int T, int N,
-                        int H, float theta, int backward, cudaStream_t stream) {
+                        int H, float theta, int backward, float* table, cudaStream_t stream) {
   if (H % 2) return -10;
-  const int64_t total = B * T * static_cast<int64_t>(N) * (H / 2);
-  rope_kernel<<<grid_for(total, 256, 148 * 16), 256, 0, stream>>>(
-      static_cast<const bf16*>(x), static_cast<bf16*>(y), positions, B, T, N, H, log2f(theta),
-      backward ? -1.f : 1.f);
+  const int hp = H / 2;
+  const int64_t total = B * T * static_cast<int64_t>(N) * hp;
+  if (total <= 0) return 0;
+  if (table != nullptr && hp % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
+    rope_table_kernel<<<(T * hp + 255) / 256, 256, 0, stream>>>(positions, reinterpret_cast<float2*>(table), T, hp,
+                                                                H, log2f(theta));
+    rope_apply_kernel<<<grid_for(total / 4, 256, 148 * 16), 256, 0, stream>>>(
+        static_cast<const Bf16x8*>(x), static_cast<Bf16x8*>(y), reinterpret_cast<const float2*>(table), total / 4, T,
+        N, hp, backward ? -1.f : 1.f);
+  } else {
+    rope_kernel<<<grid_for(total, 256, 148 * 16), 256, 0, stream>>>(
+        static_cast<const bf16*>(x), static_cast<bf16*>(y), positions, B, T, N, H, log2f(theta),
+        backward ? -1.f : 1.f);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -547,6 +703,18 @@ extern "C" int axb_ce_fwd_bwd(void* logits, int is_fp32, const int64_t* targets,
                               const uint8_t* live, float* ce_out, float* z_out, float* correct_out,
                               const float* inv_denom, float z_scale, int64_t n, int V,
                               int write_grad, cudaStream_t stream) {
+  if (!is_fp32 && V % 8 == 0 && static_cast<size_t>(V) * 2 <= 72 * 1024 &&
+      (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+    static bool vec_configured = false;
+    if (!vec_configured) {
+      cudaFuncSetAttribute(ce_fwd_bwd_bf16_vec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
+      vec_configured = true;
+    }
+    const int vgrid = static_cast<int>(n < 148 * 3 ? n : 148 * 3);
+    ce_fwd_bwd_bf16_vec_kernel<<<vgrid, 512, static_cast<size_t>(V) * 2, stream>>>(
+        static_cast<bf16*>(logits), targets, live, ce_out, z_out, correct_out, inv_denom, z_scale, n, V, write_grad);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  }
   const int grid = static_cast<int>(n < 148 * 4 ? n : 148 * 4);
   const size_t cache = static_cast<size_t>(V) * sizeof(float);
   const bool stage = cache <= 200 * 1024;

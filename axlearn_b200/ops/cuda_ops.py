@@ -67,7 +67,7 @@ class _Sigs:
                        c_void_p, c_int64, c_int, c_void_p]
     axb_swiglu_fwd = [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]
     axb_swiglu_bwd = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]
-    axb_rope = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_float, c_int, c_void_p]
+    axb_rope = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p]
     axb_ce_fwd_bwd = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                       c_float, c_int64, c_int, c_int, c_void_p]
     axb_adamw = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float,
@@ -338,6 +338,20 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return _SwiGLU.apply(gate, up)
 
 
+_rope_tables: dict = {}
+
+
+def _rope_table(device: torch.device, floats: int) -> torch.Tensor:
+    """Per-device scratch for the (sin, cos) table of one RoPE call (T * H floats).  Calls on
+    one stream run in order, so the table of a finished call may be overwritten by the next."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    t = _rope_tables.get(key)
+    if t is None or t.numel() < floats:
+        t = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+        _rope_tables[key] = t
+    return t
+
+
 class _Rope(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, positions, theta):
@@ -345,7 +359,8 @@ class _Rope(torch.autograd.Function):
         b, t, n, h = x.shape
         pos = positions.to(device=x.device, dtype=torch.int64).contiguous()
         y = torch.empty_like(x)
-        _check(lib().axb_rope(x.data_ptr(), y.data_ptr(), pos.data_ptr(), b, t, n, h, theta, 0, _stream()), "axb_rope")
+        _check(lib().axb_rope(x.data_ptr(), y.data_ptr(), pos.data_ptr(), b, t, n, h, theta, 0,
+                              _rope_table(x.device, t * h).data_ptr(), _stream()), "axb_rope")
         ctx.save_for_backward(pos)
         ctx.theta = theta
         return y
@@ -356,7 +371,8 @@ class _Rope(torch.autograd.Function):
         dy = dy.contiguous()
         b, t, n, h = dy.shape
         dx = torch.empty_like(dy)
-        _check(lib().axb_rope(dy.data_ptr(), dx.data_ptr(), pos.data_ptr(), b, t, n, h, ctx.theta, 1, _stream()), "axb_rope")
+        _check(lib().axb_rope(dy.data_ptr(), dx.data_ptr(), pos.data_ptr(), b, t, n, h, ctx.theta, 1,
+                              _rope_table(dy.device, t * h).data_ptr(), _stream()), "axb_rope")
         return dx, None, None
 
 
