@@ -22,7 +22,7 @@ namespace axb {
 
 int make_bthd_map(CUtensorMap* map, const void* base, int B, int L, int N, int H, int box_rows);
 
-constexpr int kBwdThreads = 192;
+constexpr int kBwdThreads = 320;  // TMA producer, MMA issuer, 8 softmax / dS warps
 constexpr int kSubTile = 16384;  // [128 x 64] bf16
 
 struct FlashBwdParams {
@@ -133,7 +133,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     mbar_init(qdo_full, 1);
     mbar_init(qdo_empty, 1);
     mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 4);
+    mbar_init(pds_full, 8);
     mbar_init(pds_free, 1);
     mbar_init(acc_done, 1);
     fence_barrier_init();
@@ -212,7 +212,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       }
     }
   } else {
+    // Two warps per TMEM lane quarter: each takes one half (64 columns) of the score tile.
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r_in = quarter * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     bool ok = true;
@@ -233,9 +235,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         if (!mbar_wait(pds_free, (it - 1) & 1, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
       }
       const bool need_mask = (p.causal && s0 + 127 > t0 + p.q_offset) || (s0 + 128 > p.S);
-#pragma unroll 1
-      for (int c = 0; c < 128; c += 64) {
+      {
         // 64 score columns and 64 dP columns per TMEM round trip.
+        const int c = half * 64;
         uint32_t rs[2][32], rd[2][32];
         tmem_ld_32x32(tm_s + lane_base + c, rs[0]);
         tmem_ld_32x32(tm_s + lane_base + c + 32, rs[1]);
@@ -278,7 +280,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
         const uint32_t src = (which == 0 ? tm_dk : tm_dv) + lane_base;
         __nv_bfloat16* dst = which == 0 ? dk_row : dv_row;
 #pragma unroll 1
-        for (int c = 0; c < H; c += 32) {
+        for (int c = half * (H / 2); c < (half + 1) * (H / 2); c += 32) {
           uint32_t r[32];
           if (n_iters > 0) {
             tmem_ld_32x32(src + c, r);
@@ -366,7 +368,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       mbar_init(&kv_empty[i], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(ds_full, 4);
+    mbar_init(ds_full, 8);
     mbar_init(ds_free, 1);
     mbar_init(acc_done, 1);
     fence_barrier_init();
@@ -446,6 +448,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
   } else {
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r_in = quarter * 32 + lane;
     const int row = t0 + r_in;
     const int row_pos = row + p.q_offset;
@@ -465,8 +468,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         if (!mbar_wait(ds_free, (it - 1) & 1, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
       }
       const bool need_mask = (p.causal && s0 + 127 > t0 + p.q_offset) || (s0 + 128 > p.S);
-#pragma unroll 1
-      for (int c = 0; c < 128; c += 64) {
+      {
+        const int c = half * 64;
         uint32_t rs[2][32], rd[2][32];
         tmem_ld_32x32(tm_s + lane_base + c, rs[0]);
         tmem_ld_32x32(tm_s + lane_base + c + 32, rs[1]);
@@ -499,7 +502,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       __nv_bfloat16* dq_row = reinterpret_cast<__nv_bfloat16*>(p.dq) +
                               ((static_cast<int64_t>(batch) * p.T + row) * p.N + head) * H;
 #pragma unroll 1
-      for (int c = 0; c < H; c += 32) {
+      for (int c = half * (H / 2); c < (half + 1) * (H / 2); c += 32) {
         uint32_t r[32];
         if (n_tiles > 0) {
           tmem_ld_32x32(tm_dq + lane_base + c, r);
