@@ -68,6 +68,8 @@ constexpr int kMaxPeers = 8;
 // m / rs_rows_per_rank and is stored into that rank's staging buffer at slot `rs_rank`
 // (`rs_dst[owner] + (rs_rank * rs_rows_per_rank + m % rs_rows_per_rank) * ldc`), i.e. every
 // rank ends up holding one partial per peer, which it later reduces in a fixed order.
+// With rs_mode = 1 the same epilogue implements the first half of a small-message all-reduce
+// (tensor-parallel decode): rows go to every peer and the kernel itself raises the flags.
 struct GatherJob {
   const void* src[kMaxPeers];  // every rank's slab (peer pointers; the own shard at [rank])
   void* dst;                   // this GPU's full-size buffer
@@ -86,6 +88,13 @@ struct FusedParams {
   // reduce-scatter of C
   void* rs_dst[kMaxPeers];
   int rs_world, rs_rank, rs_rows_per_rank;
+  // rs_mode 1 ("all-reduce push"): every row is stored into slot `rs_rank` of EVERY peer's
+  // staging buffer [rs_world, M, N], and the last CTA to finish raises flag
+  // [rs_site * rs_world + rs_rank] = *rs_epoch_ptr in every peer's flag array.
+  int rs_mode, rs_site;
+  int* rs_counter;             // zero-initialised arrival counter of the CTAs (this GPU)
+  const int* rs_epoch_ptr;     // device memory, so that captured graphs see a new epoch each replay
+  int* rs_flags[kMaxPeers];
 };
 
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
@@ -428,7 +437,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int n0 = n_blk * BN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       OutT* crow = C + static_cast<int64_t>(row) * p.ldc + n0;
-      if (FUSED && f.rs_world > 1 && row < p.M) {
+      const int n_dst = (FUSED && f.rs_world > 1 && f.rs_mode == 1) ? f.rs_world : 1;
+      if (FUSED && f.rs_world > 1 && f.rs_mode == 0 && row < p.M) {
         // Reduce-scatter epilogue: this row goes to its owner's staging slot for this rank
         // (a store to peer memory over NVLink when the owner is another GPU).
         const int owner = row / f.rs_rows_per_rank;
@@ -450,14 +460,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (row < p.M) {
           if constexpr (sizeof(OutT) == 2) {
             if (n0 + c + 32 <= p.N && !p.accumulate) {
+              uint4 o[4];
 #pragma unroll
               for (int v = 0; v < 4; ++v) {
-                uint4 o;
-                o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-                o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-                o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-                o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-                *reinterpret_cast<uint4*>(crow + c + 8 * v) = o;
+                o[v].x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                o[v].y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                o[v].z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                o[v].w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+              }
+              for (int d = 0; d < n_dst; ++d) {
+                OutT* cr = crow;
+                if (FUSED && n_dst > 1)
+                  cr = reinterpret_cast<OutT*>(f.rs_dst[d]) +
+                       (static_cast<int64_t>(f.rs_rank) * p.M + row) * p.ldc + n0;
+#pragma unroll
+                for (int v = 0; v < 4; ++v) *reinterpret_cast<uint4*>(cr + c + 8 * v) = o[v];
               }
             } else {
               for (int j = 0; j < 32; ++j) {
@@ -495,6 +512,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     // Stores to peer memory are posted: make each writer's rows visible system-wide before the
     // kernel can complete, so the flag raised by the next launch cannot overtake them.
     if (FUSED && f.rs_world > 1) __threadfence_system();
+    if (FUSED && f.rs_world > 1 && f.rs_mode == 1) {
+      // All four epilogue warps of this CTA are past their fences; the last CTA raises the flags.
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) {
+        if (atomicAdd(f.rs_counter, 1) == static_cast<int>(gridDim.x) - 1) {
+          *f.rs_counter = 0;
+          __threadfence_system();
+          const int epoch = *reinterpret_cast<const volatile int*>(f.rs_epoch_ptr);
+          for (int r = 0; r < f.rs_world; ++r)
+            st_release_sys(f.rs_flags[r] + f.rs_site * f.rs_world + f.rs_rank, epoch);
+        }
+      }
+    }
   }
 
   // ---------------------------------------------------------------------- tear-down
@@ -631,7 +661,12 @@ extern "C" int axb_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
       return -13;
   }
   if (fp->ag_consume && fp->ag[0].world > 1 && fp->ag_shard_extent < 1) return -13;
-  if (fp->rs_world > 1 && (fp->rs_world > kMaxPeers || fp->rs_rows_per_rank * fp->rs_world != M)) return -14;
+  if (fp->rs_world > 1 && fp->rs_mode == 0 &&
+      (fp->rs_world > kMaxPeers || fp->rs_rows_per_rank * fp->rs_world != M))
+    return -14;
+  if (fp->rs_world > 1 && fp->rs_mode == 1 &&
+      (fp->rs_world > kMaxPeers || (N % 32) || fp->rs_counter == nullptr || fp->rs_epoch_ptr == nullptr))
+    return -14;
 #define AXB_FUSED_CASE(AM, BM)                                                                     \
   if (a_mn_major == (AM ? 1 : 0) && b_mn_major == (BM ? 1 : 0))                                    \
     return launch_gemm<256, 4, AM, BM, __nv_bfloat16, true>(A, B, C, M, N, K, lda, ldb, ldc, 0,    \

@@ -11,9 +11,11 @@ persistent buffers, so the engine:
 * runs attention over the pages with the split-KV decode kernel (``paged_decode_attention``);
 * packs the projections so that a layer is four GEMMs on the tcgen05 kernel (QKV, output,
   gate|up, down); the residual adds are the GEMMs' accumulate epilogues on one GPU;
-* under tensor parallelism (heads and FFN columns split over the ``model`` group) replaces the
-  two all-reduces per layer with the one-shot peer-memory all-reduce (``OneShotAllReduce``),
-  whose finish kernel also adds the residual;
+* under tensor parallelism (heads and FFN columns split over the ``model`` group) fuses the two
+  all-reduces per layer with the GEMMs that feed them: the row-parallel GEMM's epilogue stores
+  its rows straight into every peer's staging slot and raises the flags
+  (``OneShotAllReduce.gemm_push``), and one finish kernel per all-reduce sums the slots and adds
+  the residual;
 * captures one decode step (all layers, head, greedy pick, length bump) in a CUDA graph and
   replays it per token.
 
@@ -153,10 +155,14 @@ class DecodeEngine:
         self.launches_per_step = 0
 
     # ------------------------------------------------------------------ shared pieces
-    def _reduce(self, partial: Tensor, residual: Tensor, site: int) -> Tensor:
-        """residual + sum over ranks of ``partial`` (decode path, fixed shapes)."""
-        return self._allreduce.all_reduce(partial.reshape(-1), site, residual=residual.reshape(-1)).reshape(
-            residual.shape)
+    def _gemm_reduce(self, a: Tensor, w: Tensor, residual: Tensor, site: int) -> Tensor:
+        """``residual + sum over ranks of (a @ w)``: the GEMM's epilogue stores its rows into every
+        peer's staging slot and raises the flags; the finish kernel sums the slots."""
+        if w.shape[1] % 32 == 0:
+            self._allreduce.gemm_push(a, w, site)
+        else:
+            self._allreduce.push(cuda_ops.gemm(a, w).reshape(-1), site)
+        return self._allreduce.finish(site, residual=residual.reshape(-1)).reshape(residual.shape)
 
     # ------------------------------------------------------------------ prefill
     @torch.no_grad()
@@ -228,13 +234,13 @@ class DecodeEngine:
                 softmax_scale=self._softmax_scale, splits=self.splits, scratch=self._scratch)
             attn2 = attn.reshape(self.batch, self.nq_l * d.head_dim)
             if self.world > 1:
-                x = self._reduce(cuda_ops.gemm(attn2, lw.wo), x, 2 * li)
+                x = self._gemm_reduce(attn2, lw.wo, x, 2 * li)
             else:
                 cuda_ops.gemm(attn2, lw.wo, out=x, accumulate=True)           # x += attn @ Wo
             hn = cuda_ops.rms_norm(x, lw.ffn_norm, d.norm_eps)
             act = decode_ops.swiglu_packed(cuda_ops.gemm(hn, lw.wgu))
             if self.world > 1:
-                x = self._reduce(cuda_ops.gemm(act, lw.wdown), x, 2 * li + 1)
+                x = self._gemm_reduce(act, lw.wdown, x, 2 * li + 1)
             else:
                 cuda_ops.gemm(act, lw.wdown, out=x, accumulate=True)
         logits = self._logits(x)

@@ -153,11 +153,10 @@ class OneShotAllReduce:
             self.flags, self._flags_sym = symm.symmetric_empty_like_sharded(
                 (sites, self.world), torch.int32, group, device)
             self.flags.zero_()
-            self._staging_ptrs = [
-                symm.device_pointer_array([p + s * self.world * numel * 2 for p in self._sym.peer_ptrs], device)
-                for s in range(sites)
-            ]
-            self._flag_ptrs = symm.device_pointer_array(self._flags_sym.peer_ptrs, device)
+            self._staging_lists = [[p + s * self.world * numel * 2 for p in self._sym.peer_ptrs] for s in range(sites)]
+            self._flag_list = list(self._flags_sym.peer_ptrs)
+            self._staging_ptrs = [symm.device_pointer_array(l, device) for l in self._staging_lists]
+            self._flag_ptrs = symm.device_pointer_array(self._flag_list, device)
             self._flags_sym.barrier()
         self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
         self.counter = torch.zeros(1, dtype=torch.int32, device=device)
@@ -165,11 +164,10 @@ class OneShotAllReduce:
     def connect(self, peers: list["OneShotAllReduce"]) -> None:
         """Emulation only: wire the pointer tables to the stand-in peers."""
         dev = self.staging.device
-        self._staging_ptrs = [
-            torch.tensor([p.staging[s].data_ptr() for p in peers], dtype=torch.int64, device=dev)
-            for s in range(self.sites)
-        ]
-        self._flag_ptrs = torch.tensor([p.flags.data_ptr() for p in peers], dtype=torch.int64, device=dev)
+        self._staging_lists = [[p.staging[s].data_ptr() for p in peers] for s in range(self.sites)]
+        self._flag_list = [p.flags.data_ptr() for p in peers]
+        self._staging_ptrs = [torch.tensor(l, dtype=torch.int64, device=dev) for l in self._staging_lists]
+        self._flag_ptrs = torch.tensor(self._flag_list, dtype=torch.int64, device=dev)
         self.world = len(peers)
 
     def begin_step(self) -> None:
@@ -181,6 +179,15 @@ class OneShotAllReduce:
                                        self.counter.data_ptr(), self.epoch.data_ptr(), self.world, self.rank, site,
                                        self.numel, cuda_ops._stream())  # pylint: disable=protected-access
         cuda_ops._check(rc, "axb_allreduce_push")  # pylint: disable=protected-access
+
+    def gemm_push(self, a: torch.Tensor, b: torch.Tensor, site: int) -> None:
+        """``a @ b`` (``[M, K] @ [K, N]``, ``M * N == numel``) with the push half of the all-reduce
+        fused into the GEMM's epilogue: rows go straight from the accumulator to every peer."""
+        from axlearn_b200.ops import fused_comm
+
+        assert a.shape[0] * b.shape[1] == self.numel
+        fused_comm.gemm_allreduce_push(a, b, staging_ptrs=self._staging_lists[site], flag_ptrs=self._flag_list,
+                                       counter=self.counter, epoch=self.epoch, rank=self.rank, site=site)
 
     def finish(self, site: int, *, residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None):
         if out is None:

@@ -59,6 +59,12 @@ class FusedParams(ctypes.Structure):
         ("rs_world", c_int),
         ("rs_rank", c_int),
         ("rs_rows_per_rank", c_int),
+        ("rs_mode", c_int),
+        ("rs_site", c_int),
+        ("reserved2", c_int),
+        ("rs_counter", c_void_p),
+        ("rs_epoch_ptr", c_void_p),
+        ("rs_flags", c_void_p * MAX_PEERS),
     ]
 
 
@@ -192,6 +198,33 @@ def gemm_rs(a: torch.Tensor, b: torch.Tensor, *, staging_ptrs: Sequence[int], ra
                                     cuda_ops.status_word(a.device).data_ptr(), cap, ctypes.addressof(fp),
                                     cuda_ops._stream())  # pylint: disable=protected-access
     cuda_ops._check(rc, "axb_gemm_bf16_fused(rs)")  # pylint: disable=protected-access
+
+
+def gemm_allreduce_push(a: torch.Tensor, b: torch.Tensor, *, staging_ptrs: Sequence[int], flag_ptrs: Sequence[int],
+                        counter: torch.Tensor, epoch: torch.Tensor, rank: int, site: int, max_ctas: int = 0) -> None:
+    """``a[M, K] @ b[K, N]`` whose epilogue is the first half of a small-message all-reduce: every
+    row is stored into slot ``rank`` of every peer's staging buffer ``[R, M, N]``
+    (``staging_ptrs[r]``), and the last CTA raises flag ``[site * R + rank]`` (= the value in
+    ``epoch``, device memory) in every peer's flag array (``flag_ptrs[r]``).  The sum is taken by
+    ``OneShotAllReduce.finish`` on every rank."""
+    world = len(staging_ptrs)
+    m, k = a.shape
+    n = b.shape[1]
+    assert n % 32 == 0
+    a2, a_mn, lda = cuda_ops._operand(a, 1)  # pylint: disable=protected-access
+    b2, b_mn, ldb = cuda_ops._operand(b, 0)  # pylint: disable=protected-access
+    fp = FusedParams()
+    for r in range(world):
+        fp.rs_dst[r] = staging_ptrs[r]
+        fp.rs_flags[r] = flag_ptrs[r]
+    fp.rs_world, fp.rs_rank, fp.rs_rows_per_rank, fp.rs_mode, fp.rs_site = world, rank, m, 1, site
+    fp.rs_counter = counter.data_ptr()
+    fp.rs_epoch_ptr = epoch.data_ptr()
+    cap = max_ctas or (cuda_ops._sm_count(a.device) - cuda_ops.COMM_RESERVED_SMS)  # pylint: disable=protected-access
+    rc = _lib().axb_gemm_bf16_fused(a2.data_ptr(), b2.data_ptr(), None, m, n, k, lda, ldb, n, a_mn, b_mn,
+                                    cuda_ops.status_word(a.device).data_ptr(), cap, ctypes.addressof(fp),
+                                    cuda_ops._stream())  # pylint: disable=protected-access
+    cuda_ops._check(rc, "axb_gemm_bf16_fused(allreduce push)")  # pylint: disable=protected-access
 
 
 def reduce_slots(staging: torch.Tensor, out: torch.Tensor, *, sumsq_partial: Optional[torch.Tensor] = None,

@@ -93,6 +93,31 @@ def test_one_shot_all_reduce_emulated():
     cuda_ops.check_status()
 
 
+def test_gemm_with_all_reduce_push_epilogue_emulated():
+    """Two emulated ranks: each rank's GEMM stores its rows into both staging buffers and raises
+    the flags itself; the finish kernels then see residual + the sum of both products."""
+    from axlearn_b200.ops import cuda_ops, decode_ops
+
+    world, m, k, n = 2, 64, 256, 512
+    ranks = [decode_ops.OneShotAllReduce(m * n, 1, device="cuda", peers=[None] * world, rank=r) for r in range(world)]
+    for r in ranks:
+        r.connect(ranks)
+    a = [torch.randn(m, k, device="cuda").bfloat16() for _ in range(world)]
+    b = [(torch.randn(k, n, device="cuda") * 0.1).bfloat16() for _ in range(world)]
+    res = torch.randn(m * n, device="cuda").bfloat16()
+    for step in range(2):
+        for r in ranks:
+            r.begin_step()
+        for r in range(world):
+            ranks[r].gemm_push(a[r], b[r], 0)
+        ref = res.float() + sum((x.float() @ y.float()).reshape(-1) for x, y in zip(a, b))
+        for r in ranks:
+            out = r.finish(0, residual=res)
+            assert (out.float() - ref).abs().max() < 3e-2 * ref.abs().max(), step
+    torch.cuda.synchronize()
+    cuda_ops.check_status()
+
+
 def _tiny_model(num_kv_heads):
     from axlearn_b200.common import prng
     from axlearn_b200.experiments.text.gpt import fuji
