@@ -630,9 +630,14 @@ template <bool A_MN, bool B_MN, typename OutT>
 static int dispatch_bn(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda,
                        int64_t ldb, int64_t ldc, int accumulate, int* status, int max_ctas,
                        cudaStream_t stream) {
-  // 128x256 tiles when they fill the machine, 128x128 otherwise (more CTAs for small problems).
+  // 128x256 tiles when they fill the machine, 128x128 otherwise (more CTAs for small problems),
+  // and 128x64 for skinny decode-time GEMMs (M <= 128), which are weight-streaming problems: the
+  // more CTAs pull weight columns concurrently, the closer they get to the HBM rate.
   const int m_blocks = (M + kBlockM - 1) / kBlockM;
   const int tiles256 = m_blocks * ((N + 255) / 256);
+  if (m_blocks == 1 && (N + 127) / 128 < sm_count() / 2)
+    return launch_gemm<64, 8, A_MN, B_MN, OutT>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, status,
+                                                max_ctas, stream);
   if (N >= 256 && tiles256 >= sm_count() / 2)
     return launch_gemm<256, 4, A_MN, B_MN, OutT>(A, B, C, M, N, K, lda, ldb, ldc, accumulate,
                                                   status, max_ctas, stream);
@@ -668,9 +673,13 @@ extern "C" int axb_gemm_bf16_fused(const void* A, const void* B, void* C, int M,
       (fp->rs_world > kMaxPeers || (N % 32) || fp->rs_counter == nullptr || fp->rs_epoch_ptr == nullptr))
     return -14;
 #define AXB_FUSED_CASE(AM, BM)                                                                     \
-  if (a_mn_major == (AM ? 1 : 0) && b_mn_major == (BM ? 1 : 0))                                    \
+  if (a_mn_major == (AM ? 1 : 0) && b_mn_major == (BM ? 1 : 0)) {                                  \
+    if (M <= kBlockM && fp->ag[0].world <= 1 && fp->ag[1].world <= 1)                              \
+      return launch_gemm<64, 8, AM, BM, __nv_bfloat16, true>(A, B, C, M, N, K, lda, ldb, ldc, 0,   \
+                                                             status, max_ctas, stream, fp);        \
     return launch_gemm<256, 4, AM, BM, __nv_bfloat16, true>(A, B, C, M, N, K, lda, ldb, ldc, 0,    \
-                                                            status, max_ctas, stream, fp);
+                                                            status, max_ctas, stream, fp);         \
+  }
   AXB_FUSED_CASE(false, false)
   AXB_FUSED_CASE(false, true)
   AXB_FUSED_CASE(true, false)
