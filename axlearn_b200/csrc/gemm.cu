@@ -44,6 +44,12 @@ struct GemmParams {
   int64_t ldc;
   int* status;
   int accumulate;  // C += A*B (read-modify-write in the epilogue)
+  // Split-K (skinny problems): `split_k` CTAs share one output tile, each over a slice of the
+  // k-blocks; fp32 partials go to `ws [split_k, M, N]` and the CTA that arrives last on
+  // `counters[tile]` sums them into C (and leaves the counter at zero for the next launch).
+  int split_k;
+  float* ws;
+  int* counters;
 };
 
 constexpr int kMaxPeers = 8;
@@ -239,6 +245,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int n_blocks = (p.N + BN - 1) / BN;
   const int num_tiles = m_blocks * n_blocks;
   const int num_kb = (p.K + kBlockK - 1) / kBlockK;
+  const int split = (!FUSED && p.split_k > 1) ? p.split_k : 1;
+  const int num_items = num_tiles * split;  // item = (k slice, tile); slices of a tile run on different CTAs
 
   // Fused all-gather: two barriers and two chunk buffers behind the pipeline's own.
   uint64_t* copy_full = reinterpret_cast<uint64_t*>(bar_base + 256);
@@ -319,9 +327,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         slab_ready |= 1u << r;
         return true;
       };
-      for (int t = cta; t < num_tiles && ok; t += num_ctas) {
+      for (int t = cta; t < num_items && ok; t += num_ctas) {
         int m_blk, n_blk;
-        tile_coords(t, m_blk, n_blk);
+        const int ks = t / num_tiles;
+        tile_coords(t - ks * num_tiles, m_blk, n_blk);
+        const int kb_lo = ks * num_kb / split, kb_hi = (ks + 1) * num_kb / split;
         const int m0 = m_blk * kBlockM, n0 = n_blk * BN;
         bool local = false;  // read this B tile from the own shard
         if (FUSED && ag_on && !f.ag_along_k) {
@@ -331,7 +341,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ok = need_slab(r);
           if (!ok) break;
         }
-        for (int kbi = 0; kbi < num_kb; ++kbi) {
+        for (int kbi = kb_lo; kbi < kb_hi; ++kbi) {
           const int kb = FUSED ? (kbi + kb_rot) % num_kb : kbi;
           if (FUSED && ag_on && f.ag_along_k) {
             const int k_lo = kb * kBlockK, k_hi = min(k_lo + kBlockK, p.K) - 1;
@@ -387,11 +397,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = cta; t < num_tiles && ok; t += num_ctas) {
+      for (int t = cta; t < num_items && ok; t += num_ctas) {
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.status, kStatusWaitTimeoutMma)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int ks = t / num_tiles;
+        const int kb_lo = ks * num_kb / split, kb_hi = (ks + 1) * num_kb / split;
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, p.status, kStatusWaitTimeoutMma)) {
             ok = false;
             break;
@@ -407,7 +419,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                      : umma_smem_desc(sa + k * 32, 16, 1024);
             const uint64_t db = B_MN ? umma_smem_desc(sb + k * 2048, 8192, 1024)
                                      : umma_smem_desc(sb + k * 32, 16, 1024);
-            tc_mma_f16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            tc_mma_f16(d_tmem, da, db, idesc, (kb > kb_lo || k > 0) ? 1u : 0u);
           }
           tc_commit(&empty_bar[stage]);  // stage reusable once these MMAs retire
           if (++stage == STAGES) {
@@ -428,15 +440,121 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int acc = 0;
     uint32_t acc_phase = 0;
     OutT* C = reinterpret_cast<OutT*>(p.C);
-    for (int t = cta; t < num_tiles; t += num_ctas) {
+    for (int t = cta; t < num_items; t += num_ctas) {
       int m_blk, n_blk;
-      tile_coords(t, m_blk, n_blk);
+      const int ks = t / num_tiles;
+      const int tile = t - ks * num_tiles;
+      tile_coords(tile, m_blk, n_blk);
       if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, kStatusWaitTimeoutEpilogue)) break;
       tc_fence_after_sync();
       const int row = m_blk * kBlockM + quarter * 32 + lane;
       const int n0 = n_blk * BN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       OutT* crow = C + static_cast<int64_t>(row) * p.ldc + n0;
+      if (split > 1) {
+        // Split-K: park the fp32 partial, then the last of the tile's `split` CTAs reduces.
+        // (N is a multiple of 32 here, so a 32-column chunk is entirely inside or outside.)
+        float* wrow = p.ws + (static_cast<int64_t>(ks) * p.M + row) * p.N + n0;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c, r);
+          tmem_ld_wait();
+          if (c + 32 >= BN) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+          }
+          if (row < p.M && n0 + c < p.N) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              __stcg(reinterpret_cast<uint4*>(wrow + c + 4 * v),
+                     make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]));
+          }
+        }
+        __threadfence();
+        int* last_flag = reinterpret_cast<int*>(bar_base + 512);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          const int prev = atomicAdd(&p.counters[tile], 1);
+          if (prev == split - 1) p.counters[tile] = 0;
+          *last_flag = prev == split - 1;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const bool is_last = *last_flag != 0;
+        if (is_last) {
+          __threadfence();
+          // The 128 epilogue threads sum the tile's partials with coalesced 16-byte accesses,
+          // two vectors per thread and round so that 2 * split loads are in flight at once.
+          const int m0 = m_blk * kBlockM;
+          const int rows_valid = min(kBlockM, p.M - m0);
+          const int vec_per_row = min(BN, p.N - n0) / 4;
+          const int total_vec = rows_valid * vec_per_row;
+          const int et = (warp - 2) * 32 + lane;
+          const int64_t slice = static_cast<int64_t>(p.M) * p.N;
+          for (int idx = et; idx < total_vec; idx += 256) {
+            float4 part[2][8];
+            int64_t off[2];
+            bool on[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int i = idx + u * 128;
+              on[u] = i < total_vec;
+              const int r = on[u] ? i / vec_per_row : 0;
+              const int c4 = on[u] ? i - r * vec_per_row : 0;
+              off[u] = static_cast<int64_t>(m0 + r) * p.N + n0 + c4 * 4;
+#pragma unroll
+              for (int sidx = 0; sidx < 8; ++sidx) {
+                part[u][sidx] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (on[u] && sidx < split)
+                  part[u][sidx] = __ldcg(reinterpret_cast<const float4*>(p.ws + sidx * slice + off[u]));
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              if (!on[u]) continue;
+              float4 sum = part[u][0];
+#pragma unroll
+              for (int sidx = 1; sidx < 8; ++sidx) {
+                sum.x += part[u][sidx].x;
+                sum.y += part[u][sidx].y;
+                sum.z += part[u][sidx].z;
+                sum.w += part[u][sidx].w;
+              }
+              const int i = idx + u * 128;
+              const int r = i / vec_per_row;
+              const int c4 = i - r * vec_per_row;
+              OutT* dst = C + static_cast<int64_t>(m0 + r) * p.ldc + n0 + c4 * 4;
+              if constexpr (sizeof(OutT) == 2) {
+                if (p.accumulate) {
+                  const uint2 old = *reinterpret_cast<const uint2*>(dst);
+                  sum.x += __uint_as_float(old.x << 16);
+                  sum.y += __uint_as_float(old.x & 0xffff0000u);
+                  sum.z += __uint_as_float(old.y << 16);
+                  sum.w += __uint_as_float(old.y & 0xffff0000u);
+                }
+                *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(sum.x, sum.y), pack_bf16x2(sum.z, sum.w));
+              } else {
+                if (p.accumulate) {
+                  const float4 old = *reinterpret_cast<const float4*>(dst);
+                  sum.x += old.x;
+                  sum.y += old.y;
+                  sum.z += old.z;
+                  sum.w += old.w;
+                }
+                *reinterpret_cast<float4*>(dst) = sum;
+              }
+            }
+          }
+        }
+        // `last_flag` is rewritten by the next item: everyone must have read it first.
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+        continue;
+      }
       const int n_dst = (FUSED && f.rs_world > 1 && f.rs_mode == 1) ? f.rs_world : 1;
       if (FUSED && f.rs_world > 1 && f.rs_mode == 0 && row < p.M) {
         // Reduce-scatter epilogue: this row goes to its owner's staging slot for this rank
@@ -543,7 +661,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
 template <int BN, int STAGES, bool A_MN, bool B_MN, typename OutT, bool FUSED = false>
 static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda,
                        int64_t ldb, int64_t ldc, int accumulate, int* status, int max_ctas,
-                       cudaStream_t stream, const FusedParams* fused = nullptr) {
+                       cudaStream_t stream, const FusedParams* fused = nullptr, int split_k = 1,
+                       float* ws = nullptr, int* counters = nullptr) {
   CUtensorMap ta, tb;
   int rc;
   if (!A_MN) {
@@ -610,13 +729,13 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   }
   const int m_blocks = (M + kBlockM - 1) / kBlockM;
   const int n_blocks = (N + BN - 1) / BN;
-  int grid = m_blocks * n_blocks;
+  int grid = m_blocks * n_blocks * (split_k > 1 ? split_k : 1);
   int cap = max_ctas > 0 && max_ctas < sm_count() ? max_ctas : sm_count();
   // All CTAs must be co-resident (one per SM): tiles may wait on flags that every CTA's copy
   // warp contributes to.
   if (grid > cap) grid = cap;
   if (grid < 1) return -12;
-  GemmParams p{M, N, K, C, ldc, status, accumulate};
+  GemmParams p{M, N, K, C, ldc, status, accumulate, split_k, ws, counters};
   kernel<<<grid, FUSED ? kFusedThreads : kNumThreads, kSmem, stream>>>(ta, tb, tl, p, fp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -645,7 +764,60 @@ static int dispatch_bn(const void* A, const void* B, void* C, int M, int N, int 
                                                 max_ctas, stream);
 }
 
+// Split-K plan for a skinny problem (one row block): how many CTAs share an output tile so that
+// the weight stream is pulled by (nearly) every SM.  1 = no split.
+static int splitk_plan(int M, int N, int K) {
+  if (M > kBlockM || (N % 32) != 0) return 1;
+  const int tiles = (N + 63) / 64;
+  const int num_kb = (K + kBlockK - 1) / kBlockK;
+  if ((N + 127) / 128 >= sm_count() / 2) return 1;
+  int split = sm_count() / tiles;
+  if (split > num_kb / 4) split = num_kb / 4;  // at least four k-blocks per slice
+  if (split > 8) split = 8;
+  // The hand-over (fence, counter, reduction by the last CTA) costs about as much as two dozen
+  // k-blocks of streaming: split only when it takes more than that off every CTA's loop.
+  if (split < 2 || num_kb - num_kb / split < 24) return 1;
+  return split;
+}
+
 }  // namespace axb
+
+extern "C" int axb_gemm_splitk_plan(int M, int N, int K) { return axb::splitk_plan(M, N, K); }
+
+// Skinny GEMM (M <= 128, N a multiple of 32) with split-K: `ws` holds split * M * N floats and
+// `counters` ceil(N / 64) ints that are zero on entry (the kernel leaves them zero).  The caller
+// owns both and must not share them between launches that may overlap in time.
+extern "C" int axb_gemm_bf16_splitk(const void* A, const void* B, void* C, int M, int N, int K,
+                                    int64_t lda, int64_t ldb, int64_t ldc, int a_mn_major,
+                                    int b_mn_major, int out_fp32, int accumulate, int split,
+                                    void* ws, void* counters, int* status, int max_ctas,
+                                    cudaStream_t stream) {
+  using namespace axb;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
+      (reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(C) & 15) ||
+      (ldc % (out_fp32 ? 4 : 8)) || (reinterpret_cast<uintptr_t>(ws) & 15))
+    return -10;
+  if (M > kBlockM || (N % 32) || split < 2 || split > (K + kBlockK - 1) / kBlockK || ws == nullptr ||
+      counters == nullptr)
+    return -15;
+#define AXB_SPLITK_CASE(AM, BM)                                                                    \
+  if (a_mn_major == (AM ? 1 : 0) && b_mn_major == (BM ? 1 : 0)) {                                  \
+    if (out_fp32)                                                                                  \
+      return launch_gemm<64, 8, AM, BM, float>(A, B, C, M, N, K, lda, ldb, ldc, accumulate,       \
+                                               status, max_ctas, stream, nullptr, split,          \
+                                               static_cast<float*>(ws), static_cast<int*>(counters)); \
+    return launch_gemm<64, 8, AM, BM, __nv_bfloat16>(A, B, C, M, N, K, lda, ldb, ldc, accumulate,  \
+                                                     status, max_ctas, stream, nullptr, split,     \
+                                                     static_cast<float*>(ws), static_cast<int*>(counters)); \
+  }
+  AXB_SPLITK_CASE(false, false)
+  AXB_SPLITK_CASE(false, true)
+  AXB_SPLITK_CASE(true, false)
+  AXB_SPLITK_CASE(true, true)
+#undef AXB_SPLITK_CASE
+  return -11;
+}
 
 // Fused compute+collective GEMM (bf16 out). `fused` points to a host copy of axb::FusedParams
 // (see the struct for the all-gather-of-B and reduce-scatter-of-C contracts). With

@@ -61,6 +61,9 @@ def lib() -> ctypes.CDLL:
 class _Sigs:
     axb_gemm_bf16 = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
                      c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
+    axb_gemm_splitk_plan = [c_int, c_int, c_int]
+    axb_gemm_bf16_splitk = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
+                            c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     axb_rmsnorm_fwd = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p]
     axb_rmsnorm_bwd_ctas = [c_int64]
     axb_rmsnorm_bwd = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -160,6 +163,31 @@ def _operand(t: torch.Tensor, contraction_dim: int) -> tuple[torch.Tensor, int, 
     return t, u[0], u[1]
 
 
+_splitk_plans: dict[tuple, int] = {}
+_splitk_ws: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def _splitk_plan(m: int, n: int, k: int) -> int:
+    key = (m > 0, n, k)
+    if key not in _splitk_plans:
+        _splitk_plans[key] = lib().axb_gemm_splitk_plan(m, n, k)
+    return _splitk_plans[key]
+
+
+def _splitk_workspace(device: torch.device, floats: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """fp32 partials + tile counters of the split-K skinny GEMM, one pair per (device, stream):
+    launches on one stream are ordered, so they can share it.  (Allocated through torch, so a
+    first use during CUDA-graph capture lands in the graph's pool.)"""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream())
+    have = _splitk_ws.get(key)
+    if have is None or have[0].numel() < floats:
+        ws = torch.empty(max(floats, 1 << 21), dtype=torch.float32, device=device)
+        counters = have[1] if have is not None else torch.zeros(4096, dtype=torch.int32, device=device)
+        have = (ws, counters)
+        _splitk_ws[key] = have
+    return have
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = None,
          out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False,
          max_ctas: int = 0) -> torch.Tensor:
@@ -180,6 +208,16 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = None
         return out if accumulate else out.zero_()
     if max_ctas == 0 and COMM_RESERVED_SMS:
         max_ctas = max(8, _sm_count(a.device) - COMM_RESERVED_SMS)
+    if m <= 128 and n % 32 == 0:
+        split = _splitk_plan(m, n, k)
+        if split > 1:
+            ws, counters = _splitk_workspace(a.device, split * m * n)
+            rc = lib().axb_gemm_bf16_splitk(
+                a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k, lda, ldb, out.stride(0), a_mn, b_mn,
+                1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0, split, ws.data_ptr(),
+                counters.data_ptr(), status_word(a.device).data_ptr(), max_ctas, _stream())
+            _check(rc, "axb_gemm_bf16_splitk")
+            return out
     rc = lib().axb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k, lda, ldb, out.stride(0),
                              a_mn, b_mn, 1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0,
                              status_word(a.device).data_ptr(), max_ctas, _stream())

@@ -75,3 +75,27 @@ def test_gemm_deterministic():
     a = torch.randn(512, 1024, device="cuda").bfloat16()
     b = torch.randn(1024, 768, device="cuda").bfloat16()
     assert torch.equal(cuda_ops.gemm(a, b), cuda_ops.gemm(a, b))
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 1536, 4096), (16, 2752, 4096), (8, 4096, 1376), (128, 4096, 11008), (1, 1536, 512)])
+@pytest.mark.parametrize("b_t", [False, True])
+def test_skinny_gemm_split_k(m, n, k, b_t):
+    """Decode-shaped problems (one row block): 64-column tiles, split over K where the plan says
+    so; bf16 and fp32 outputs, with and without accumulation, repeated to exercise the counters."""
+    from axlearn_b200.ops import cuda_ops
+
+    torch.manual_seed(2)
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    b = torch.randn(n, k, device="cuda").bfloat16().t() if b_t else torch.randn(k, n, device="cuda").bfloat16()
+    ref = _ref(a, b)
+    for _ in range(3):
+        _close(cuda_ops.gemm(a, b), ref)
+    _close(cuda_ops.gemm(a, b, out_dtype=torch.float32), ref, tol=1e-3)
+    base = torch.randn(m, n, device="cuda").bfloat16()
+    acc = base.clone()
+    cuda_ops.gemm(a, b, out=acc, accumulate=True)
+    _close(acc, base.float() + ref)
+    torch.cuda.synchronize()
+    cuda_ops.check_status()
+    if n * 2 <= 148 * 64 and k >= 4096:
+        assert cuda_ops.lib().axb_gemm_splitk_plan(m, n, k) > 1
