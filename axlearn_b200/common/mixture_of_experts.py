@@ -514,3 +514,224 @@ class TransformerFeedForwardMoE(BaseLayer):
         if coll.has_axis((cfg.dim_to_mesh_axis_map.get("ehm") or (None,) * 3)[1], "model"):
             y = coll.psum(y, "model")
         return y
+
+
+# ------------------------------------------------------------------------------------------
+# Drop-free routing: every (token, choice) is served; experts see variable-length runs of rows.
+# ------------------------------------------------------------------------------------------
+
+
+@dataclasses.dataclass
+class DropFreeRouting:
+    gate_assignment: Tensor                 # [B, S, K] expert ids
+    expert_weights: Tensor                  # [B, S, K] fp32, renormalised over the K choices
+    load_balance_loss: Optional[Tensor] = None
+    router_z_loss: Optional[Tensor] = None
+    seq_load_balance_loss: Optional[Tensor] = None
+
+
+class TopKDropFreeGating(TopKGating):
+    """Top-k routing without capacity (reference: axlearn/common/mixture_of_experts.py:1101-1240):
+    returns the chosen experts and their renormalised weights; the load-balance loss is
+    ``mean(density * density_proxy) * E^2`` with the density counted over all K choices, and the
+    optional per-sequence variant follows DeepSeek-V3 (eq. 17-20)."""
+
+    def _normalized_gates(self, raw_gates: Tensor) -> Tensor:
+        if self._config.score_fn is None:
+            return raw_gates
+        return raw_gates / raw_gates.sum(dim=-1, keepdim=True)
+
+    def _load_balance_loss(self, raw_gates: Tensor, assignment: Tensor) -> Tensor:
+        e = raw_gates.shape[-1]
+        density = torch.bincount(assignment.reshape(-1), minlength=e).float() / assignment.numel()
+        proxy = self._normalized_gates(raw_gates).reshape(-1, e).mean(dim=0)
+        return (density * proxy).mean() * e * e
+
+    def _seq_load_balance_loss(self, raw_gates: Tensor, assignment: Tensor) -> Tensor:
+        b, s, e = raw_gates.shape
+        k = assignment.shape[-1]
+        one_hot_counts = torch.zeros((b, e), dtype=torch.float32, device=raw_gates.device)
+        one_hot_counts.scatter_add_(1, assignment.reshape(b, -1), torch.ones((b, s * k), device=raw_gates.device))
+        density = one_hot_counts * e / (s * k)
+        proxy = self._normalized_gates(raw_gates).mean(dim=1)
+        return (density * proxy).sum(dim=1).mean()
+
+    def _process_logits(self, logits: Tensor) -> Tensor:
+        cfg = self._config
+        logits = _cap_logits(logits.float(), cfg.gating_logit_cap)
+        if cfg.noisy_gating is not None:
+            if cfg.noisy_gating != "gumbel":
+                raise NotImplementedError(cfg.noisy_gating)
+            from axlearn_b200.common import prng
+
+            u = prng.uniform(self.prng_key, logits.shape, device=logits.device).clamp(1e-20, 1.0)
+            logits = logits - torch.log(-torch.log(u))
+        return logits
+
+    def _select(self, raw_gates: Tensor, k: int) -> Tensor:
+        return self._compute_index(raw_gates, k=k)
+
+    def forward(self, logits: Tensor, seq_load_balance_loss_weight: Optional[float] = None) -> DropFreeRouting:
+        cfg = self._config
+        logits = self._process_logits(logits)                                   # [B, S, E]
+        z = _router_z_loss(logits)
+        self.add_summary("router_z_loss", z.detach())
+        raw_gates = self._score(logits)
+        assignment = self._select(raw_gates, cfg.num_experts_per_token)
+        gate_w = torch.gather(raw_gates, -1, assignment)
+        lb = self._load_balance_loss(raw_gates, assignment)
+        self.add_summary("load_balance_loss", lb.detach())
+        seq_lb = None
+        if seq_load_balance_loss_weight:
+            seq_lb = self._seq_load_balance_loss(raw_gates, assignment)
+            self.add_summary("seq_load_balance_loss", seq_lb.detach())
+        weights = gate_w / gate_w.sum(dim=-1, keepdim=True)
+        self.add_module_output("gate_assignment", assignment)
+        return DropFreeRouting(gate_assignment=assignment, expert_weights=weights, load_balance_loss=lb,
+                               router_z_loss=z, seq_load_balance_loss=seq_lb)
+
+
+class TopKBiasGating(TopKDropFreeGating):
+    """Auxiliary-loss-free balancing (reference: :1243-1440, after DeepSeek-V3): a per-expert bias
+    is added to the scores for *selection only* and nudged after every training step towards
+    under-used experts (``+rate`` when an expert got fewer tokens than average, ``-rate`` when
+    more); chosen weights are scaled by ``routed_scaling_factor``.  With ``num_group_of_experts >
+    1`` only the ``topk_group`` best groups (by the sum of each group's two best adjusted scores)
+    are eligible."""
+
+    @config_class
+    class Config(TopKDropFreeGating.Config):
+        gating_update_rate: float = 1e-3
+        routed_scaling_factor: float = 2.5
+        num_group_of_experts: int = 1
+        topk_group: int = 1
+
+    def _create_layer_parameter_specs(self):
+        cfg = self._config
+        return {"gate_bias": ParameterSpec(shape=(cfg.num_experts,), dtype=torch.float32,
+                                           initializer=constant_initializer(0.0))}
+
+    def _select(self, raw_gates: Tensor, k: int) -> Tensor:
+        cfg = self._config
+        adjusted = raw_gates + self.parameters["gate_bias"].float().detach()
+        g = cfg.num_group_of_experts
+        if g > 1:
+            b, s, e = adjusted.shape
+            per_group = adjusted.reshape(b, s, g, e // g)
+            group_score = per_group.topk(min(2, e // g), dim=-1).values.sum(dim=-1)      # [B, S, G]
+            keep = torch.zeros_like(group_score, dtype=torch.bool)
+            keep.scatter_(-1, group_score.topk(cfg.topk_group, dim=-1).indices, True)
+            adjusted = per_group.masked_fill(~keep[..., None], float("-inf")).reshape(b, s, e)
+        index = adjusted.topk(k, dim=-1).indices
+        if self.is_training:
+            counts = torch.bincount(index.reshape(-1), minlength=cfg.num_experts).float()
+            delta = torch.sign(counts.mean() - counts)
+            self.add_state_update("gate_bias", (self.parameters["gate_bias"].float()
+                                                + cfg.gating_update_rate * delta).detach())
+        return index
+
+    def forward(self, logits: Tensor, seq_load_balance_loss_weight: Optional[float] = None) -> DropFreeRouting:
+        out = super().forward(logits, seq_load_balance_loss_weight)
+        out.expert_weights = out.expert_weights * self._config.routed_scaling_factor
+        return out
+
+
+class TransformerFeedForwardDropFreeMoE(TransformerFeedForwardMoE):
+    """Mixture of experts without token dropping (reference: :2321-2751).
+
+    The (token, choice) pairs are sorted by expert -- choice-major, so that every token's first
+    choice precedes any second choice inside an expert's run, as in the reference -- and laid
+    out in one ``[R, M]`` buffer in which each expert's run starts on a 128-row boundary.  The
+    three projections are then grouped GEMMs over that buffer (one tcgen05 kernel launch each;
+    the expert of every 128-row block selects the weight matrix), the activation is the usual
+    fused elementwise kernel, and the outputs are gathered back and summed over the K choices
+    with the routing weights in fp32.  Nothing synchronises with the host: ``R`` is the static
+    bound ``pairs + E * 127`` rounded up to 128.
+    """
+
+    @config_class
+    class Config(TransformerFeedForwardMoE.Config):
+        seq_load_balance_loss_weight: Optional[float] = None
+        # Accepted for config compatibility with the reference (Pallas tile sizes / backend
+        # choice); the grouped kernel has one tiling.
+        tiling: Any = None
+        gmm_backend: Any = None
+
+    @classmethod
+    def default_config(cls):
+        cfg = super().default_config()
+        cfg.gating = TopKDropFreeGating.default_config()
+        cfg.num_groups = 1
+        return cfg
+
+    def _dispatch_and_combine(self, x: Tensor) -> Tensor:
+        from axlearn_b200.ops import moe_ops
+
+        cfg = self._config
+        in_dtype = x.dtype
+        token_shape = x.shape[:-1]
+        m = cfg.input_dim
+        x3 = x.reshape(x.shape[0], -1, m)                                        # [B, S, M]
+        logits = torch.einsum("bsm,me->bse", x3.float(), self.parameters["gate_weight"].float())
+        routing = self.gating(logits, cfg.seq_load_balance_loss_weight)
+        aux = routing.load_balance_loss * cfg.load_balance_loss_weight
+        if cfg.router_z_loss_weight:
+            aux = aux + routing.router_z_loss * cfg.router_z_loss_weight
+        if cfg.seq_load_balance_loss_weight and routing.seq_load_balance_loss is not None:
+            aux = aux + routing.seq_load_balance_loss * cfg.seq_load_balance_loss_weight
+        self.add_module_output("aux_loss", aux)
+
+        k = routing.gate_assignment.shape[-1]
+        tokens = x3.shape[0] * x3.shape[1]
+        assignment = routing.gate_assignment.reshape(tokens, k)
+        # Choice-major pair order decides the order inside an expert's run.
+        dest_km, offsets, block_expert, rows = moe_ops.padded_group_layout(
+            assignment.t().contiguous(), cfg.num_experts)
+        dest = dest_km.reshape(k, tokens).t().contiguous()                        # [T, K]
+        xs = moe_ops.dispatch(x3.reshape(tokens, m), dest, rows)                 # [R, M]
+        ys = self._grouped_ffn(xs, offsets, block_expert)
+        out = moe_ops.combine(ys, routing.expert_weights.reshape(tokens, k), dest)
+        return out.to(in_dtype).reshape(*token_shape, m)
+
+    def _grouped_ffn(self, xs: Tensor, offsets: Tensor, block_expert: Tensor) -> Tensor:
+        from axlearn_b200.ops import moe_ops
+
+        cfg = self._config
+        act = cfg.activation
+        acts = list(act) if isinstance(act, tuple) else [act]
+        names = [f"wi_{i}_weight" for i in range(len(acts))] if isinstance(act, tuple) else ["wi_weight"]
+        wis = [self._expert_weight(n, "emh").to(xs.dtype) for n in names]
+        wo = self._expert_weight("wo_weight", "ehm").to(xs.dtype)
+        hs = [moe_ops.grouped_linear(xs, w, offsets, block_expert) for w in wis]
+        if len(hs) == 2 and acts == ["nn.silu", "linear"]:
+            h = ops.swiglu(hs[0], hs[1])
+        else:
+            h = None
+            for hv, a in zip(hs, acts):
+                hv = get_activation_fn(a)(hv)
+                h = hv if h is None else h * hv
+        h = self.dropout1(h) if "dropout1" in self._children else h
+        return moe_ops.grouped_linear(h, wo, offsets, block_expert)
+
+
+def convert_dense_to_moe_parameters(dense_params: dict, *, num_experts: int, activation: Union[str, tuple],
+                                    gate_std: float = 0.02, generator: Optional[torch.Generator] = None) -> dict:
+    """Parameters of a ``TransformerFeedForwardMoE`` initialised from a dense
+    ``TransformerFeedForwardLayer`` ("sparse upcycling"; reference: :1843-2001): every expert
+    starts as a copy of the dense FFN (``linear1[_i].weight -> wi[_i]_weight``,
+    ``linear2.weight -> wo_weight``), the router is drawn at random, the norm is carried over."""
+    out = {}
+    names = [f"linear1_{i}" for i in range(len(activation))] if isinstance(activation, tuple) else ["linear1"]
+    targets = [f"wi_{i}_weight" for i in range(len(activation))] if isinstance(activation, tuple) else ["wi_weight"]
+    for src, dst in zip(names, targets):
+        w = dense_params[src]["weight"]
+        out[dst] = w.unsqueeze(0).repeat(num_experts, 1, 1).clone()
+    w2 = dense_params["linear2"]["weight"]
+    out["wo_weight"] = w2.unsqueeze(0).repeat(num_experts, 1, 1).clone()
+    model_dim = w2.shape[1]
+    out["gate_weight"] = torch.randn((model_dim, num_experts), generator=generator, dtype=w2.dtype) \
+        .to(w2.device) * gate_std
+    for key in ("norm", "prenorm", "postnorm"):
+        if key in dense_params:
+            out[key] = dense_params[key]
+    return out

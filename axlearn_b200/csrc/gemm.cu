@@ -50,6 +50,17 @@ struct GemmParams {
   int split_k;
   float* ws;
   int* counters;
+  // Grouped problems (mixture-of-experts), rows sorted by group and every group padded to whole
+  // 128-row blocks.  Mode 1: row block m uses B matrix number `group_index[m]` (-1 = unused
+  // block, skipped); the B tensor map stacks the groups along its outer dim, `b_group_rows`
+  // apart.  Mode 2: one output [M, N] per group g (`c_group_stride` elements apart), contracting
+  // rows [group_index[g], group_index[g + 1]) of the (MN-major) operands; an empty group's
+  // output is zero.
+  int group_mode;
+  int num_groups;
+  const int* group_index;
+  int b_group_rows;
+  int64_t c_group_stride;
 };
 
 constexpr int kMaxPeers = 8;
@@ -246,7 +257,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int num_tiles = m_blocks * n_blocks;
   const int num_kb = (p.K + kBlockK - 1) / kBlockK;
   const int split = (!FUSED && p.split_k > 1) ? p.split_k : 1;
-  const int num_items = num_tiles * split;  // item = (k slice, tile); slices of a tile run on different CTAs
+  const int gmode = FUSED ? 0 : p.group_mode;
+  // item = (k slice or group, tile); the slices / groups of a tile run as separate items.
+  const int num_items = num_tiles * (gmode == 2 ? p.num_groups : split);
+  // k-block range of an item.
+  auto kb_range = [&](int ks, int& kb_lo, int& kb_hi) {
+    if (gmode == 2) {
+      kb_lo = p.group_index[ks] / kBlockK;
+      kb_hi = p.group_index[ks + 1] / kBlockK;
+    } else {
+      kb_lo = ks * num_kb / split;
+      kb_hi = (ks + 1) * num_kb / split;
+    }
+  };
 
   // Fused all-gather: two barriers and two chunk buffers behind the pipeline's own.
   uint64_t* copy_full = reinterpret_cast<uint64_t*>(bar_base + 256);
@@ -331,7 +354,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         int m_blk, n_blk;
         const int ks = t / num_tiles;
         tile_coords(t - ks * num_tiles, m_blk, n_blk);
-        const int kb_lo = ks * num_kb / split, kb_hi = (ks + 1) * num_kb / split;
+        int kb_lo, kb_hi;
+        kb_range(ks, kb_lo, kb_hi);
+        int b_off = 0;  // grouped mode 1: outer-dim offset of this row block's B matrix
+        if (gmode == 1) {
+          const int g = p.group_index[m_blk];
+          if (g < 0) continue;
+          b_off = g * p.b_group_rows;
+        }
         const int m0 = m_blk * kBlockM, n0 = n_blk * BN;
         bool local = false;  // read this B tile from the own shard
         if (FUSED && ag_on && !f.ag_along_k) {
@@ -375,11 +405,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 tma_load_2d(sb + j * 8192, &tmap_b_local, &full_bar[stage], n0 + j * 64, k0 - own_lo);
             }
           } else if constexpr (!B_MN) {
-            tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0 + b_off);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sb + j * 8192, &tmap_b, &full_bar[stage], n0 + j * 64, k0);
+              tma_load_2d(sb + j * 8192, &tmap_b, &full_bar[stage], n0 + j * 64, k0 + b_off);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -398,11 +428,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int t = cta; t < num_items && ok; t += num_ctas) {
+        const int ks = t / num_tiles;
+        if (gmode == 1) {
+          int m_blk, n_blk;
+          tile_coords(t - ks * num_tiles, m_blk, n_blk);
+          if (p.group_index[m_blk] < 0) continue;
+        }
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.status, kStatusWaitTimeoutMma)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        const int ks = t / num_tiles;
-        const int kb_lo = ks * num_kb / split, kb_hi = (ks + 1) * num_kb / split;
+        int kb_lo, kb_hi;
+        kb_range(ks, kb_lo, kb_hi);
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, p.status, kStatusWaitTimeoutMma)) {
             ok = false;
@@ -445,12 +481,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int ks = t / num_tiles;
       const int tile = t - ks * num_tiles;
       tile_coords(tile, m_blk, n_blk);
+      if (gmode == 1 && p.group_index[m_blk] < 0) continue;
       if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, kStatusWaitTimeoutEpilogue)) break;
       tc_fence_after_sync();
       const int row = m_blk * kBlockM + quarter * 32 + lane;
       const int n0 = n_blk * BN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       OutT* crow = C + static_cast<int64_t>(row) * p.ldc + n0;
+      bool empty_group = false;  // grouped mode 2: nothing was accumulated, the result is zero
+      if (gmode == 2) {
+        crow += static_cast<int64_t>(ks) * p.c_group_stride;
+        empty_group = p.group_index[ks] / kBlockK == p.group_index[ks + 1] / kBlockK;
+      }
       if (split > 1) {
         // Split-K: park the fp32 partial, then the last of the tile's `split` CTAs reduces.
         // (N is a multiple of 32 here, so a 32-column chunk is entirely inside or outside.)
@@ -569,6 +611,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t r[32];
         tmem_ld_32x32(taddr + c, r);
         tmem_ld_wait();
+        if (empty_group) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
         if (c + 32 >= BN) {
           // All of this warp's reads of the accumulator are done: hand it back early.
           tc_fence_before_sync();
@@ -662,7 +708,11 @@ template <int BN, int STAGES, bool A_MN, bool B_MN, typename OutT, bool FUSED = 
 static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda,
                        int64_t ldb, int64_t ldc, int accumulate, int* status, int max_ctas,
                        cudaStream_t stream, const FusedParams* fused = nullptr, int split_k = 1,
-                       float* ws = nullptr, int* counters = nullptr) {
+                       float* ws = nullptr, int* counters = nullptr, int group_mode = 0,
+                       int num_groups = 1, const int* group_index = nullptr,
+                       int64_t c_group_stride = 0) {
+  // Grouped mode 1 stacks the groups' B matrices along the outer dim of one tensor map.
+  const uint64_t b_stack = group_mode == 1 ? static_cast<uint64_t>(num_groups) : 1;
   CUtensorMap ta, tb;
   int rc;
   if (!A_MN) {
@@ -680,13 +730,13 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   }
   if (rc != 0) return rc;
   if (!B_MN) {
-    uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+    uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N) * b_stack};
     uint64_t strides[1] = {static_cast<uint64_t>(ldb) * 2};
     uint32_t box[2] = {kBlockK, BN};
     rc = make_tensor_map(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, dims, strides, box,
                          CU_TENSOR_MAP_SWIZZLE_128B);
   } else {
-    uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
+    uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K) * b_stack};
     uint64_t strides[1] = {static_cast<uint64_t>(ldb) * 2};
     uint32_t box[2] = {64, kBlockK};
     rc = make_tensor_map(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, dims, strides, box,
@@ -729,13 +779,14 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   }
   const int m_blocks = (M + kBlockM - 1) / kBlockM;
   const int n_blocks = (N + BN - 1) / BN;
-  int grid = m_blocks * n_blocks * (split_k > 1 ? split_k : 1);
+  int grid = m_blocks * n_blocks * (group_mode == 2 ? num_groups : (split_k > 1 ? split_k : 1));
   int cap = max_ctas > 0 && max_ctas < sm_count() ? max_ctas : sm_count();
   // All CTAs must be co-resident (one per SM): tiles may wait on flags that every CTA's copy
   // warp contributes to.
   if (grid > cap) grid = cap;
   if (grid < 1) return -12;
-  GemmParams p{M, N, K, C, ldc, status, accumulate, split_k, ws, counters};
+  GemmParams p{M, N, K, C, ldc, status, accumulate, split_k, ws, counters,
+               group_mode, num_groups, group_index, B_MN ? K : N, c_group_stride};
   kernel<<<grid, FUSED ? kFusedThreads : kNumThreads, kSmem, stream>>>(ta, tb, tl, p, fp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -816,6 +867,46 @@ extern "C" int axb_gemm_bf16_splitk(const void* A, const void* B, void* C, int M
   AXB_SPLITK_CASE(true, false)
   AXB_SPLITK_CASE(true, true)
 #undef AXB_SPLITK_CASE
+  return -11;
+}
+
+// Grouped GEMMs for mixture-of-experts layers whose token rows are sorted by expert, each expert's
+// run padded to a whole number of 128-row blocks.
+//   mode 1: C[M, N] = A[M, K] * B[g(m)]  with B stacked [G, K, N] (b_mn_major = 1) or [G, N, K]
+//           (b_mn_major = 0) and `group_index[M / 128]` = the group of each row block (-1 = unused
+//           block: its rows of C are not written).  With b_mn_major = 1, K must be a multiple of 64.
+//   mode 2: C[g] [M, N] = sum over rows r in [group_index[g], group_index[g + 1]) of
+//           A[r, :M]^T * B[r, :N]  (both operands stored row-major over the token rows, i.e.
+//           a_mn_major = b_mn_major = 1; K = total rows); offsets are multiples of 128.
+extern "C" int axb_gemm_bf16_grouped(const void* A, const void* B, void* C, int M, int N, int K,
+                                     int64_t lda, int64_t ldb, int64_t ldc, int a_mn_major,
+                                     int b_mn_major, int out_fp32, int mode, int num_groups,
+                                     const int* group_index, int64_t c_group_stride, int* status,
+                                     int max_ctas, cudaStream_t stream) {
+  using namespace axb;
+  if (M <= 0 || N <= 0 || K <= 0 || num_groups <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
+      (reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(C) & 15) ||
+      (ldc % (out_fp32 ? 4 : 8)) || group_index == nullptr)
+    return -10;
+  if (mode == 1 && (a_mn_major || (M % kBlockM) || (b_mn_major && (K % kBlockK)))) return -16;
+  if (mode == 2 && (!a_mn_major || !b_mn_major || (c_group_stride % 8))) return -16;
+  if (mode != 1 && mode != 2) return -16;
+#define AXB_GROUPED_CASE(AM, BM, T)                                                                \
+  if (a_mn_major == (AM ? 1 : 0) && b_mn_major == (BM ? 1 : 0) && out_fp32 == (sizeof(T) == 4)) { \
+    if (N >= 256)                                                                                  \
+      return launch_gemm<256, 4, AM, BM, T>(A, B, C, M, N, K, lda, ldb, ldc, 0, status, max_ctas,  \
+                                            stream, nullptr, 1, nullptr, nullptr, mode,           \
+                                            num_groups, group_index, c_group_stride);              \
+    return launch_gemm<128, 6, AM, BM, T>(A, B, C, M, N, K, lda, ldb, ldc, 0, status, max_ctas,    \
+                                          stream, nullptr, 1, nullptr, nullptr, mode, num_groups, \
+                                          group_index, c_group_stride);                            \
+  }
+  AXB_GROUPED_CASE(false, false, __nv_bfloat16)
+  AXB_GROUPED_CASE(false, true, __nv_bfloat16)
+  AXB_GROUPED_CASE(true, true, __nv_bfloat16)
+  AXB_GROUPED_CASE(true, true, float)
+#undef AXB_GROUPED_CASE
   return -11;
 }
 

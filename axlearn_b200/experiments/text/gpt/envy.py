@@ -24,7 +24,13 @@ from axlearn_b200.common.config import InstantiableConfig
 from axlearn_b200.common.decoder import LmHead
 from axlearn_b200.common.embedding import TransformerTextEmbeddings
 from axlearn_b200.common.layers import RMSNorm
-from axlearn_b200.common.mixture_of_experts import Top2Gating, TopKGating, TransformerFeedForwardMoE
+from axlearn_b200.common.mixture_of_experts import (
+    Top2Gating,
+    TopKDropFreeGating,
+    TopKGating,
+    TransformerFeedForwardDropFreeMoE,
+    TransformerFeedForwardMoE,
+)
 from axlearn_b200.experiments.text.gpt.common import model_config as common_model_config
 
 MODEL_PRESETS = {
@@ -56,9 +62,17 @@ def model_config(
     shared_lm_head: bool = False,
     stack_cfg: Optional[InstantiableConfig] = None,
     scan_chunk: Optional[int] = None,
+    drop_free: bool = False,
+    atten_hidden_dim: Optional[int] = None,
+    qk_norm: bool = False,
+    norm_eps: float = 1e-5,
+    z_loss_scale: float = 0.0,
 ) -> causal_lm.Model.Config:
     """RMSNorm / RoPE / SwiGLU decoder whose feed-forward layers follow ``ffn_layer_types``
-    (cycled over the stack): "sparse" = MoE, "dense" = ordinary FFN."""
+    (cycled over the stack): "sparse" = MoE, "dense" = ordinary FFN.  ``drop_free`` selects the
+    sorted grouped-GEMM experts with capacity-free top-k routing; ``atten_hidden_dim`` decouples
+    the attention width (heads x head dim) from the model width; ``qk_norm`` adds per-head
+    RMSNorm on queries and keys."""
     if num_kv_heads:
         atten_cfg = GroupedQueryAttention.default_config()
         input_linear = FusedGroupedQKVLinear.default_config().set(num_kv_heads=num_kv_heads)
@@ -67,27 +81,36 @@ def model_config(
         input_linear = FusedQKVLinear.default_config()
     qkv = RoFormerQKVLinear.default_config().set(input_linear=input_linear, rotary_value=False)
     qkv.rope_pos_emb_layer.theta = rope_theta
-    if num_experts_per_token == 2:
+    if atten_hidden_dim is not None:
+        atten_cfg.hidden_dim = atten_hidden_dim
+    if qk_norm:
+        head_norm = RMSNorm.default_config().set(eps=norm_eps, forward_dtype=None)
+        atten_cfg.query_scale.norm = head_norm
+        atten_cfg.key_scale.norm = head_norm.clone()
+    if drop_free:
+        gating = TopKDropFreeGating.default_config().set(num_experts_per_token=num_experts_per_token)
+    elif num_experts_per_token == 2:
         gating = Top2Gating.default_config().set(
             train_capacity_factor=capacity_factor, eval_capacity_factor=capacity_factor)
     else:
         gating = TopKGating.default_config().set(
             num_experts_per_token=num_experts_per_token, train_capacity_factor=capacity_factor,
             eval_capacity_factor=capacity_factor)
-    expert_cfg = TransformerFeedForwardMoE.default_config().set(
+    moe_cls = TransformerFeedForwardDropFreeMoE if drop_free else TransformerFeedForwardMoE
+    expert_cfg = moe_cls.default_config().set(
         num_experts=num_experts, num_groups=num_groups, outer_batch=outer_batch, gating=gating,
         load_balance_loss_weight=load_balance_loss_weight, router_z_loss_weight=router_z_loss_weight)
     cfg = common_model_config(
         num_layers=num_layers, hidden_dim=hidden_dim, num_heads=num_heads, vocab_size=vocab_size,
         stack_cfg=stack_cfg if stack_cfg is not None else RepeatedTransformerLayer.default_config(),
         activation_fn=("nn.silu", "linear"), ffn_dim=dense_ffn_dim or moe_ffn_dim,
-        normalization=RMSNorm.default_config().set(eps=1e-5, forward_dtype=None),
+        normalization=RMSNorm.default_config().set(eps=norm_eps, forward_dtype=None),
         emb_cfg=TransformerTextEmbeddings.default_config().set(pos_emb=None),
         lm_head_cfg=LmHead.default_config() if not shared_lm_head else None,
         attention_cfg=atten_cfg, attention_qkv_linear=qkv, ffn_layer_types=tuple(ffn_layer_types),
         expert_cfg=expert_cfg, moe_ffn_dim=moe_ffn_dim, scan_chunk=scan_chunk)
     cfg.aux_loss_regex = ".*/aux_loss"
-    cfg.metrics = causal_lm.metrics_config(aux_loss_regex=cfg.aux_loss_regex)
+    cfg.metrics = causal_lm.metrics_config(aux_loss_regex=cfg.aux_loss_regex, z_loss_scale=z_loss_scale)
     return cfg
 
 

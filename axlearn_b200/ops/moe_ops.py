@@ -130,3 +130,121 @@ def combine(y: torch.Tensor, weight: torch.Tensor, dest: torch.Tensor) -> torch.
     padded = torch.cat([y, y.new_zeros((1, y.shape[1]))], dim=0)
     gathered = padded[torch.where(flat >= 0, flat, torch.full_like(flat, y.shape[0]))].reshape(t, k, -1)
     return (gathered.float() * weight[..., None].float()).sum(dim=1).to(y.dtype)
+
+
+# ------------------------------------------------------------------------------------------
+# Grouped GEMM over expert-sorted, block-padded rows (drop-free mixture of experts).
+# ------------------------------------------------------------------------------------------
+
+GROUP_BLOCK = 128  # every expert's run of rows starts on a multiple of this
+
+
+def padded_group_layout(expert_of_pair: torch.Tensor, num_experts: int):
+    """Sorted, block-padded placement of ``P`` (token, choice) pairs.
+
+    Returns ``(dest [P] int32, offsets [E + 1] int32, block_expert [R / 128] int32, R)``: pair
+    ``p`` goes to row ``dest[p]`` of an ``[R, M]`` buffer in which expert ``e`` owns rows
+    ``[offsets[e], offsets[e + 1])`` (a multiple of 128 each, its pairs first -- in pair order --
+    and zero rows after them); ``block_expert`` names the owner of every 128-row block (-1 for
+    the unused tail).  ``R`` is a static bound, so nothing here synchronises with the host.
+    """
+    p = expert_of_pair.numel()
+    flat = expert_of_pair.reshape(-1).long()
+    counts = torch.bincount(flat, minlength=num_experts)
+    padded = (counts + GROUP_BLOCK - 1) // GROUP_BLOCK * GROUP_BLOCK
+    offsets = torch.zeros(num_experts + 1, dtype=torch.long, device=flat.device)
+    offsets[1:] = torch.cumsum(padded, 0)
+    order = torch.argsort(flat, stable=True)
+    start_unpadded = torch.cumsum(counts, 0) - counts
+    sorted_expert = flat[order]
+    rank_in_expert = torch.arange(p, device=flat.device) - start_unpadded[sorted_expert]
+    dest = torch.empty(p, dtype=torch.long, device=flat.device)
+    dest[order] = offsets[:-1][sorted_expert] + rank_in_expert
+    rows = (p + num_experts * (GROUP_BLOCK - 1) + GROUP_BLOCK - 1) // GROUP_BLOCK * GROUP_BLOCK
+    block_start = torch.arange(rows // GROUP_BLOCK, device=flat.device) * GROUP_BLOCK
+    block_expert = torch.searchsorted(offsets[1:].contiguous(), block_start, right=True)
+    block_expert = torch.where(block_start < offsets[-1], block_expert, torch.full_like(block_expert, -1))
+    return dest.to(torch.int32), offsets.to(torch.int32), block_expert.to(torch.int32), rows
+
+
+def _grouped_argtypes():
+    h = _lib()
+    if not getattr(h, "_axb_grouped_configured", False):
+        h.axb_gemm_bf16_grouped.argtypes = [
+            c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int,
+            c_int, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p]
+        h.axb_gemm_bf16_grouped.restype = c_int
+        h._axb_grouped_configured = True  # pylint: disable=protected-access
+    return h
+
+
+def _gmm_kernel(x, w, block_expert, transpose_w: bool):
+    """``out[r] = x[r] @ (w[g(r)]^T if transpose_w else w[g(r)])`` on the tcgen05 kernel."""
+    rows, k = x.shape
+    e = w.shape[0]
+    n = w.shape[1] if transpose_w else w.shape[2]
+    out = torch.zeros((rows, n), dtype=torch.bfloat16, device=x.device)
+    rc = _grouped_argtypes().axb_gemm_bf16_grouped(
+        x.data_ptr(), w.data_ptr(), out.data_ptr(), rows, n, k, x.stride(0), w.stride(1), out.stride(0),
+        0, 0 if transpose_w else 1, 0, 1, e, block_expert.data_ptr(), 0,
+        cuda_ops.status_word(x.device).data_ptr(), 0, cuda_ops._stream())  # pylint: disable=protected-access
+    cuda_ops._check(rc, "axb_gemm_bf16_grouped")  # pylint: disable=protected-access
+    return out
+
+
+def _tgmm_kernel(x, dy, offsets, num_experts: int):
+    """``dw[e] = x[rows of e]^T @ dy[rows of e]`` (bf16 out, fp32 accumulation)."""
+    rows, k = x.shape
+    n = dy.shape[1]
+    dw = torch.empty((num_experts, k, n), dtype=torch.bfloat16, device=x.device)
+    rc = _grouped_argtypes().axb_gemm_bf16_grouped(
+        x.data_ptr(), dy.data_ptr(), dw.data_ptr(), k, n, rows, x.stride(0), dy.stride(0), n,
+        1, 1, 0, 2, num_experts, offsets.data_ptr(), k * n,
+        cuda_ops.status_word(x.device).data_ptr(), 0, cuda_ops._stream())  # pylint: disable=protected-access
+    cuda_ops._check(rc, "axb_gemm_bf16_grouped")  # pylint: disable=protected-access
+    return dw
+
+
+def _grouped_kernel_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (_use_kernels(x) and w.dtype == torch.bfloat16 and x.shape[0] % GROUP_BLOCK == 0
+            and w.shape[1] % 64 == 0 and w.shape[2] % 64 == 0)
+
+
+class _GroupedLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, offsets, block_expert):
+        x = x.contiguous()
+        w = w.contiguous()
+        ctx.save_for_backward(x, w, offsets, block_expert)
+        return _gmm_kernel(x, w, block_expert, transpose_w=False)
+
+    @staticmethod
+    def backward(ctx, g):
+        x, w, offsets, block_expert = ctx.saved_tensors
+        g = g.contiguous()
+        dx = _gmm_kernel(g, w, block_expert, transpose_w=True) if ctx.needs_input_grad[0] else None
+        dw = _tgmm_kernel(x, g, offsets, w.shape[0]) if ctx.needs_input_grad[1] else None
+        return dx, dw, None, None
+
+
+def grouped_linear_reference(x: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:
+    """Per-expert matmuls over the row ranges (synchronises to read the offsets): the oracle of
+    the grouped kernel and the path for CPU / non-bf16 inputs."""
+    out = x.new_zeros((x.shape[0], w.shape[2]))
+    bounds = offsets.tolist()
+    pieces = []
+    for e in range(w.shape[0]):
+        lo, hi = bounds[e], bounds[e + 1]
+        pieces.append(x[lo:hi] @ w[e].to(x.dtype))
+    used = torch.cat(pieces, dim=0) if pieces else out[:0]
+    return torch.cat([used, out[used.shape[0]:]], dim=0)
+
+
+def grouped_linear(x: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor,
+                   block_expert: torch.Tensor) -> torch.Tensor:
+    """``x [R, K]`` (rows laid out by ``padded_group_layout``) times ``w [E, K, N]`` -> ``[R, N]``:
+    the reference's ``gmm(lhs, rhs, group_sizes)`` (axlearn/common/megablock/ops.py:15-105) with
+    its transposed / per-group-transposed variants as the backward pass."""
+    if _grouped_kernel_ok(x, w):
+        return _GroupedLinear.apply(x, w, offsets, block_expert)
+    return grouped_linear_reference(x, w, offsets)
