@@ -461,19 +461,56 @@ class TransformerFeedForwardMoE(BaseLayer):
         if cfg.router_z_loss_weight:
             aux = aux + routing.router_z_loss * cfg.router_z_loss_weight
         self.add_module_output("aux_loss", aux)
+        fused = self._peer_exchange(x, routing)
+        if fused is not None:
+            return fused.to(in_dtype).reshape(*token_shape, cfg.input_dim)
         expert_in = self.gating.dispatch(x, routing)                          # [O, E, G, C, M]
         expert_out = self._experts(expert_in)
         out = self.gating.combine(expert_out, routing, dtype=in_dtype)
         return out.reshape(*token_shape, cfg.input_dim)
+
+    def _expert_parallel_size(self) -> int:
+        cfg = self._config
+        mesh = current_mesh()
+        ep = mesh.axis_size("expert") if mesh is not None and "expert" in mesh.shape else 1
+        return ep if coll.has_axis((cfg.dim_to_mesh_axis_map.get("emh") or (None,))[0], "expert") else 1
+
+    def _peer_exchange(self, x: Tensor, routing: Routing) -> Optional[Tensor]:
+        """Expert parallelism over peer memory: token rows are stored straight into the memory of
+        the GPU that owns their expert and expert outputs are read straight out of it, so the two
+        all-to-alls are fused into the dispatch gather and the combine sum.  Returns None when the
+        path does not apply (no expert axis, CPU / non-bf16 activations, more than 8 ranks)."""
+        import os
+
+        from axlearn_b200.ops import moe_ops
+
+        cfg = self._config
+        ep = self._expert_parallel_size()
+        forced = os.environ.get("AXB_MOE_PEER_EXCHANGE") == "force"
+        if not moe_ops.peer_exchange_ok(x) or ep > 8 or (ep == 1 and not forced):
+            return None
+        o, g, s, m = x.shape
+        e, c = routing.num_experts, routing.expert_capacity
+        k = routing.expert_index.shape[-1]
+        slots = o * g * c
+        dev = x.device
+        oo = torch.arange(o, device=dev).view(o, 1, 1, 1)
+        gg = torch.arange(g, device=dev).view(1, g, 1, 1)
+        dest = routing.expert_index * slots + (oo * g + gg) * c + routing.slot   # expert-major rows
+        dest = torch.where(routing.slot >= 0, dest, torch.full_like(dest, -1)).reshape(o * g * s, k)
+        group = current_mesh().group("expert") if ep > 1 else None
+        ex = moe_ops.expert_exchange(e // ep, slots, m, group, dev)
+        xe = moe_ops.ep_dispatch(x.reshape(o * g * s, m), dest, ex)             # [E_local, ep * slots, M]
+        ye = self._expert_ffn(xe)
+        out = moe_ops.ep_combine(ye, routing.weight.reshape(o * g * s, k), dest, ex)
+        return out.reshape(o, g, s, m)
 
     def _experts(self, x: Tensor) -> Tensor:
         """``[O, E, G, C, M] -> [O, E, G, C, M]`` through the expert FFNs, with the all-to-all
         pair around it when experts are sharded over the ``expert`` mesh axis."""
         cfg = self._config
         o, e, g, c, m = x.shape
-        mesh = current_mesh()
-        ep = mesh.axis_size("expert") if mesh is not None and "expert" in mesh.shape else 1
-        ep = ep if coll.has_axis((cfg.dim_to_mesh_axis_map.get("emh") or (None,))[0], "expert") else 1
+        ep = self._expert_parallel_size()
         xe = x.permute(1, 0, 2, 3, 4).reshape(e, o * g * c, m)                # expert-major
         if ep > 1:
             # [E, T, M] -> every rank keeps E/ep experts and receives their tokens from all ranks.

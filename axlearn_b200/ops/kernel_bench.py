@@ -8,6 +8,7 @@ the same measurement for the PyTorch library op for context.  The small default 
 also the ones used for ``ncu`` captures.
 
 Ops: gemm (``--layout nn|nt|tn``: forward, data-gradient and weight-gradient operand forms),
+gemm_fp8, grouped_gemm, decode_attn,
 flash_fwd, flash_bwd, rmsnorm, swiglu, rope, ce, adamw.
 """
 
@@ -93,6 +94,36 @@ def bench_gemm_fp8(args) -> dict:
     flops = 2.0 * m * n * k
     return {"ms": ours, "tflops": flops / ours / 1e9, "library_ms": lib, "library_tflops": flops / lib / 1e9,
             "flops": flops, "quantize_rows_ms": quant, "quantize_rows_gbs": 3.0 * m * k / quant / 1e6}
+
+
+def bench_grouped_gemm(args) -> dict:
+    """Grouped GEMM of a drop-free MoE projection: ``--m`` (token, choice) pairs spread unevenly
+    over ``--experts`` experts, ``[K, N]`` weights per expert; forward form and (``--layout tn``)
+    the per-expert weight-gradient form.  The library column runs one matmul per expert over the
+    same row ranges (offsets already on the host)."""
+    from axlearn_b200.ops import moe_ops
+
+    m, n, k, e = args.m, args.n, args.k, args.experts
+    torch.manual_seed(0)
+    probs = torch.softmax(torch.randn(e) * 0.5, 0)
+    experts = torch.multinomial(probs, m, replacement=True).cuda()
+    dest, offsets, block_expert, rows = moe_ops.padded_group_layout(experts, e)
+    x = torch.zeros(rows, k, device="cuda", dtype=torch.bfloat16)
+    x[dest.long()] = torch.randn(m, k, device="cuda").bfloat16()
+    w = torch.randn(e, k, n, device="cuda").bfloat16()
+    dy = torch.zeros(rows, n, device="cuda", dtype=torch.bfloat16)
+    dy[dest.long()] = torch.randn(m, n, device="cuda").bfloat16()
+    bounds = offsets.tolist()
+    if args.layout == "tn":
+        ours = _time(lambda: moe_ops._tgmm_kernel(x, dy, offsets, e), args.iters)  # pylint: disable=protected-access
+        lib = _time(lambda: [x[bounds[i]:bounds[i + 1]].t() @ dy[bounds[i]:bounds[i + 1]] for i in range(e)], args.iters)
+    else:
+        ours = _time(lambda: moe_ops._gmm_kernel(x, w, block_expert, False), args.iters)  # pylint: disable=protected-access
+        lib = _time(lambda: [x[bounds[i]:bounds[i + 1]] @ w[i] for i in range(e)], args.iters)
+    cuda_ops.check_status()
+    flops = 2.0 * bounds[-1] * n * k
+    return {"ms": ours, "tflops": flops / ours / 1e9, "library_ms": lib, "library_tflops": flops / lib / 1e9,
+            "flops": flops, "padded_rows": bounds[-1], "pairs": m}
 
 
 def bench_flash(args, backward: bool) -> dict:
@@ -198,12 +229,13 @@ def bench_memory_bound(args) -> dict:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", required=True,
-                    choices=["gemm", "gemm_fp8", "flash_fwd", "flash_bwd", "decode_attn", "rmsnorm", "swiglu", "rope", "ce",
+                    choices=["gemm", "gemm_fp8", "grouped_gemm", "flash_fwd", "flash_bwd", "decode_attn", "rmsnorm", "swiglu", "rope", "ce",
                              "adamw"])
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--layout", default="nn", choices=["nn", "nt", "tn"])
+    ap.add_argument("--experts", type=int, default=8)
     ap.add_argument("--batch", type=int, default=2)
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--heads", type=int, default=32)
@@ -217,6 +249,8 @@ def main() -> None:
         r = bench_gemm(args)
     elif args.op == "gemm_fp8":
         r = bench_gemm_fp8(args)
+    elif args.op == "grouped_gemm":
+        r = bench_grouped_gemm(args)
     elif args.op == "decode_attn":
         r = bench_decode_attn(args)
     elif args.op in ("flash_fwd", "flash_bwd"):

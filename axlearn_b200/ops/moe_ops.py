@@ -15,6 +15,7 @@ the oracle in tests.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -248,3 +249,213 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor,
     if _grouped_kernel_ok(x, w):
         return _GroupedLinear.apply(x, w, offsets, block_expert)
     return grouped_linear_reference(x, w, offsets)
+
+
+# ------------------------------------------------------------------------------------------
+# Expert-parallel exchange over peer memory: dispatch pushes rows into the owners' memory,
+# combine pulls rows out of it (the all-to-all pair fused into the token gather / weighted sum).
+# ------------------------------------------------------------------------------------------
+
+_IN_READY, _IN_FREE, _OUT_READY, _OUT_FREE = range(4)
+
+
+def _peer_argtypes():
+    h = _lib()
+    if not getattr(h, "_axb_peer_moe_configured", False):
+        h.axb_moe_push_rows.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                        c_int64, c_int, c_void_p]
+        h.axb_moe_pull_combine.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                           c_int64, c_int, c_int, c_void_p]
+        h.axb_moe_pull_row_dots.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                            c_int64, c_int, c_int, c_void_p]
+        for f in (h.axb_moe_push_rows, h.axb_moe_pull_combine, h.axb_moe_pull_row_dots):
+            f.restype = c_int
+        h._axb_peer_moe_configured = True  # pylint: disable=protected-access
+    return h
+
+
+class ExpertExchange:
+    """Symmetric in/out boxes ``[E_local, world, slots, M]`` (bf16) of one expert-parallel group
+    plus the four flag sets of the hand-shake:
+
+    * push: wait until the owners have emptied their in-boxes of my previous rows (``IN_FREE``),
+      store my rows into the owners' in-boxes, raise ``IN_READY`` there, wait for everybody's
+      ``IN_READY`` here, copy the in-box out, raise ``IN_FREE`` at the senders;
+    * pull: wait until everybody has read my previous out-box (``OUT_FREE``), fill it, raise
+      ``OUT_READY`` at the readers, wait for the owners' ``OUT_READY``, read rows out of the
+      owners' out-boxes, raise ``OUT_FREE`` at the owners.
+
+    Every wait is a bounded device-side wait that reports through the status word.  All ranks
+    must issue the same sequence of pushes and pulls (true for SPMD training steps).  With
+    ``group=None`` the "group" is this GPU alone (the kernels and the protocol still run: used by
+    single-GPU tests)."""
+
+    def __init__(self, experts_per_rank: int, slots: int, model_dim: int, group, device: torch.device):
+        from axlearn_b200.parallel import symm
+
+        self.experts_per_rank, self.slots, self.model_dim = experts_per_rank, slots, model_dim
+        if group is None:
+            self.world, self.rank = 1, 0
+            shape = (experts_per_rank, 1, slots, model_dim)
+            self.inbox = torch.empty(shape, dtype=torch.bfloat16, device=device)
+            self.outbox = torch.empty(shape, dtype=torch.bfloat16, device=device)
+            self.flags = torch.zeros(4, dtype=torch.int32, device=device)
+            in_ptrs, out_ptrs, flag_ptrs = [self.inbox.data_ptr()], [self.outbox.data_ptr()], [self.flags.data_ptr()]
+        else:
+            import torch.distributed as dist
+
+            self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+            shape = (experts_per_rank, self.world, slots, model_dim)
+            self.inbox, in_sym = symm.symmetric_empty_like_sharded(shape, torch.bfloat16, group, device)
+            self.outbox, out_sym = symm.symmetric_empty_like_sharded(shape, torch.bfloat16, group, device)
+            self.flags, flag_sym = symm.symmetric_empty_like_sharded((4 * self.world,), torch.int32, group, device)
+            self.flags.zero_()
+            torch.cuda.synchronize(device)
+            flag_sym.barrier()
+            in_ptrs, out_ptrs, flag_ptrs = in_sym.peer_ptrs, out_sym.peer_ptrs, flag_sym.peer_ptrs
+            self._keep = (in_sym, out_sym, flag_sym)
+        arr = ctypes.c_void_p * self.world
+        self._in_bases, self._out_bases = arr(*in_ptrs), arr(*out_ptrs)
+        self._flag_ptrs = symm.device_pointer_array(flag_ptrs, device)
+        self._push_epoch = 0
+        self._pull_epoch = 0
+
+    # -------------------------------------------------------------- hand-shake helpers
+    def _signal(self, kind: int, value: int) -> None:
+        from axlearn_b200.ops import fused_comm
+
+        fused_comm.signal_peers(self._flag_ptrs, self.world, kind * self.world + self.rank, value)
+
+    def _wait(self, kind: int, value: int) -> None:
+        from axlearn_b200.ops import fused_comm
+
+        fused_comm.wait_flags(self.flags[kind * self.world:(kind + 1) * self.world], self.world, value)
+
+    # -------------------------------------------------------------- push
+    def push(self, src: torch.Tensor, row_source: torch.Tensor, scale) -> torch.Tensor:
+        """``src [T, M]``; ``row_source [E * slots]`` = the row of ``src`` that fills each flat
+        (expert, slot) row, -1 for an empty slot (filled with zeros); optional per-row scale.
+        Returns this rank's experts' input ``[E_local, world * slots, M]``."""
+        self._push_epoch += 1
+        p = self._push_epoch
+        if p > 1:
+            self._wait(_IN_FREE, p - 1)
+        rows = self.world * self.experts_per_rank * self.slots
+        assert row_source.numel() == rows and src.shape[1] == self.model_dim
+        rc = _peer_argtypes().axb_moe_push_rows(
+            src.data_ptr(), row_source.data_ptr(), None if scale is None else scale.data_ptr(), self._in_bases,
+            self.world, self.rank, self.slots, self.experts_per_rank, rows, self.model_dim,
+            cuda_ops._stream())  # pylint: disable=protected-access
+        cuda_ops._check(rc, "axb_moe_push_rows")  # pylint: disable=protected-access
+        self._signal(_IN_READY, p)
+        self._wait(_IN_READY, p)
+        out = self.inbox.clone().reshape(self.experts_per_rank, self.world * self.slots, self.model_dim)
+        self._signal(_IN_FREE, p)
+        return out
+
+    # -------------------------------------------------------------- pull
+    def _pull_begin(self, y: torch.Tensor) -> None:
+        self._pull_epoch += 1
+        q = self._pull_epoch
+        if q > 1:
+            self._wait(_OUT_FREE, q - 1)
+        self.outbox.copy_(y.reshape(self.outbox.shape))
+        # The copy is an ordinary kernel / copy engine write to local memory: the release store
+        # of the flag kernel (after a system fence) orders it before the flag.
+        self._signal(_OUT_READY, q)
+        self._wait(_OUT_READY, q)
+
+    def _pull_end(self) -> None:
+        self._signal(_OUT_FREE, self._pull_epoch)
+
+    def pull_combine(self, y: torch.Tensor, dest: torch.Tensor, weight) -> torch.Tensor:
+        """``y [E_local, world * slots, M]`` (this rank's experts' outputs) ->
+        ``out[t] = sum_k weight[t, k] * row dest[t, k]`` of the owners' outputs."""
+        self._pull_begin(y)
+        tokens, k = dest.shape
+        out = torch.empty((tokens, self.model_dim), dtype=torch.bfloat16, device=y.device)
+        rc = _peer_argtypes().axb_moe_pull_combine(
+            self._out_bases, self.world, self.rank, self.slots, self.experts_per_rank, dest.data_ptr(),
+            None if weight is None else weight.data_ptr(), out.data_ptr(), tokens, k, self.model_dim,
+            cuda_ops._stream())  # pylint: disable=protected-access
+        cuda_ops._check(rc, "axb_moe_pull_combine")  # pylint: disable=protected-access
+        self._pull_end()
+        return out
+
+    def pull_row_dots(self, a: torch.Tensor, y: torch.Tensor, dest: torch.Tensor) -> torch.Tensor:
+        """``out[t, k] = <a[t], row dest[t, k] of the owners' y>`` (gradient of the gate weights)."""
+        self._pull_begin(y)
+        tokens, k = dest.shape
+        out = torch.empty((tokens, k), dtype=torch.float32, device=a.device)
+        rc = _peer_argtypes().axb_moe_pull_row_dots(
+            a.data_ptr(), self._out_bases, self.world, self.rank, self.slots, self.experts_per_rank,
+            dest.data_ptr(), out.data_ptr(), tokens, k, self.model_dim, cuda_ops._stream())  # pylint: disable=protected-access
+        cuda_ops._check(rc, "axb_moe_pull_row_dots")  # pylint: disable=protected-access
+        self._pull_end()
+        return out
+
+
+_exchanges: dict[tuple, ExpertExchange] = {}
+
+
+def expert_exchange(experts_per_rank: int, slots: int, model_dim: int, group, device) -> ExpertExchange:
+    key = (experts_per_rank, slots, model_dim, None if group is None else id(group), str(device))
+    if key not in _exchanges:
+        _exchanges[key] = ExpertExchange(experts_per_rank, slots, model_dim, group, device)
+    return _exchanges[key]
+
+
+class _EpDispatch(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, dest, inv, ex):
+        k = dest.shape[1]
+        row_source = torch.where(inv >= 0, inv // k, inv).contiguous()
+        ctx.save_for_backward(dest)
+        ctx.ex = ex
+        return ex.push(x.contiguous(), row_source, None)
+
+    @staticmethod
+    def backward(ctx, g):
+        (dest,) = ctx.saved_tensors
+        return ctx.ex.pull_combine(g.contiguous(), dest, None), None, None, None
+
+
+class _EpCombine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, weight, dest, inv, ex):
+        y = y.contiguous()
+        weight = weight.float().contiguous()
+        ctx.save_for_backward(y, weight, dest, inv)
+        ctx.ex = ex
+        return ex.pull_combine(y, dest, weight)
+
+    @staticmethod
+    def backward(ctx, g):
+        y, weight, dest, inv = ctx.saved_tensors
+        ex = ctx.ex
+        g = g.contiguous()
+        k = dest.shape[1]
+        dw = ex.pull_row_dots(g, y, dest)
+        row_source = torch.where(inv >= 0, inv // k, inv).contiguous()
+        w_of_row = weight.reshape(-1)[inv.clamp(min=0).long()].contiguous()
+        dy = ex.push(g, row_source, w_of_row)
+        return dy, dw, None, None, None
+
+
+def peer_exchange_ok(x: torch.Tensor) -> bool:
+    return _use_kernels(x) and os.environ.get("AXB_MOE_PEER_EXCHANGE", "1") != "0"
+
+
+def ep_dispatch(x: torch.Tensor, dest: torch.Tensor, ex: ExpertExchange) -> torch.Tensor:
+    """``x [T, M]``, ``dest [T, K]`` (expert-major flat rows ``e * slots + slot``, -1 = dropped)
+    -> this rank's experts' inputs ``[E_local, world * slots, M]``."""
+    dest = dest.to(torch.int32).contiguous()
+    rows = ex.world * ex.experts_per_rank * ex.slots
+    return _EpDispatch.apply(x, dest, inverse_pairs(dest, rows), ex)
+
+
+def ep_combine(y: torch.Tensor, weight: torch.Tensor, dest: torch.Tensor, ex: ExpertExchange) -> torch.Tensor:
+    """``y [E_local, world * slots, M]`` -> ``[T, M]`` (weighted sum over each token's choices)."""
+    dest = dest.to(torch.int32).contiguous()
+    rows = ex.world * ex.experts_per_rank * ex.slots
+    return _EpCombine.apply(y, weight, dest, inverse_pairs(dest, rows), ex)

@@ -74,3 +74,44 @@ def test_dispatch_combine_kernels_match_torch_formulation():
     assert (c.float() - c_ref.float()).abs().max() < 3e-2
     for a, b in zip(g, g_ref):
         assert (a.float() - b.float()).abs().max() < 5e-2 * max(1.0, b.float().abs().max().item())
+
+
+def test_peer_exchange_on_one_gpu_matches_local_dispatch(monkeypatch):
+    """The push / pull kernels and their hand-shake with a group of one (this GPU is its own
+    peer) must reproduce the local gather / combine path, forward and backward."""
+    from axlearn_b200.common import prng
+    from axlearn_b200.common.mixture_of_experts import Top2Gating, TransformerFeedForwardMoE
+    from axlearn_b200.common.module import functional
+    from axlearn_b200.common.utils import tree_map
+    from axlearn_b200.ops import cuda_ops
+
+    cfg = TransformerFeedForwardMoE.default_config().set(
+        name="moe", input_dim=256, hidden_dim=512, num_experts=4, num_groups=2, activation=("nn.silu", "linear"),
+        structure="nonorm", gating=Top2Gating.default_config().set(train_capacity_factor=1.0))
+    layer = cfg.instantiate(parent=None)
+    params = tree_map(lambda t: t.cuda().bfloat16(), layer.initialize_parameters_recursively(prng.PRNGKey(0)))
+    x = torch.randn(4, 64, 256, device="cuda").bfloat16()
+
+    def run():
+        p = tree_map(lambda t: t.detach().clone().requires_grad_(True), params)
+        xin = x.clone().requires_grad_(True)
+        outs = []
+        for _ in range(2):   # twice: the second round exercises the "box is free again" waits
+            out, oc = functional(layer, prng.PRNGKey(1), p, [xin], is_training=True, drop_output_collections=())
+            (out.float().square().mean() + oc.module_outputs["aux_loss"]).backward()
+            outs.append(out.detach().float())
+        return outs, p, xin.grad.float()
+
+    monkeypatch.setenv("AXB_MOE_PEER_EXCHANGE", "0")
+    ref_outs, ref_p, ref_dx = run()
+    monkeypatch.setenv("AXB_MOE_PEER_EXCHANGE", "force")
+    before = cuda_ops.launch_count
+    outs, p, dx = run()
+    torch.cuda.synchronize()
+    cuda_ops.check_status()
+    assert cuda_ops.launch_count - before > 20
+    for a, b in zip(outs, ref_outs):
+        assert torch.equal(a, b)
+    assert torch.equal(dx, ref_dx)
+    for name in ("wi_0_weight", "wo_weight", "gate_weight"):
+        assert torch.equal(p[name].grad, ref_p[name].grad), name
