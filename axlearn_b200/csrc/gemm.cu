@@ -17,6 +17,7 @@
 // Reference behaviour being replaced: every jnp.einsum of the dense layers lowers to a cuBLAS
 // GEMM in the reference (axlearn/common/layers.py:715-770, axlearn/common/attention.py:536-562,
 // 864-1060).
+#include <stdlib.h>
 #include <string.h>
 
 #include "host_utils.cuh"
@@ -796,6 +797,17 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   return 0;
 }
 
+// AXB_GEMM_SKINNY selects the treatment of skinny problems (one row block): 0 = the general tiles,
+// 1 = 64-column tiles, 2 (default) = 64-column tiles and split-K.
+static int skinny_mode() {
+  static int mode = -1;
+  if (mode < 0) {
+    const char* e = getenv("AXB_GEMM_SKINNY");
+    mode = (e != nullptr && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 2;
+  }
+  return mode;
+}
+
 template <bool A_MN, bool B_MN, typename OutT>
 static int dispatch_bn(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda,
                        int64_t ldb, int64_t ldc, int accumulate, int* status, int max_ctas,
@@ -805,7 +817,7 @@ static int dispatch_bn(const void* A, const void* B, void* C, int M, int N, int 
   // more CTAs pull weight columns concurrently, the closer they get to the HBM rate.
   const int m_blocks = (M + kBlockM - 1) / kBlockM;
   const int tiles256 = m_blocks * ((N + 255) / 256);
-  if (m_blocks == 1 && (N + 127) / 128 < sm_count() / 2)
+  if (m_blocks == 1 && (N + 127) / 128 < sm_count() / 2 && skinny_mode() >= 1)
     return launch_gemm<64, 8, A_MN, B_MN, OutT>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, status,
                                                 max_ctas, stream);
   if (N >= 256 && tiles256 >= sm_count() / 2)
@@ -818,7 +830,7 @@ static int dispatch_bn(const void* A, const void* B, void* C, int M, int N, int 
 // Split-K plan for a skinny problem (one row block): how many CTAs share an output tile so that
 // the weight stream is pulled by (nearly) every SM.  1 = no split.
 static int splitk_plan(int M, int N, int K) {
-  if (M > kBlockM || (N % 32) != 0) return 1;
+  if (M > kBlockM || (N % 32) != 0 || skinny_mode() < 2) return 1;
   const int tiles = (N + 63) / 64;
   const int num_kb = (K + kBlockK - 1) / kBlockK;
   if ((N + 127) / 128 >= sm_count() / 2) return 1;

@@ -29,6 +29,7 @@ from __future__ import annotations
 
 import dataclasses
 import math
+import os
 from typing import Any, Optional
 
 import torch
@@ -156,9 +157,17 @@ class DecodeEngine:
 
     # ------------------------------------------------------------------ shared pieces
     def _gemm_reduce(self, a: Tensor, w: Tensor, residual: Tensor, site: int) -> Tensor:
-        """``residual + sum over ranks of (a @ w)``: the GEMM's epilogue stores its rows into every
-        peer's staging slot and raises the flags; the finish kernel sums the slots."""
-        if w.shape[1] % 32 == 0:
+        """``residual + sum over ranks of (a @ w)``; the finish kernel sums the peers' slots.
+
+        With two ranks the GEMM's epilogue stores its rows into the peer's staging slot and raises
+        the flags itself (one launch less per all-reduce; measured 5.63 vs 5.89 ms per token on two
+        GPUs).  With more ranks the epilogue's row-per-lane 16-byte stores to seven peers are a
+        poor fit for NVLink (8 GPUs, batch 64: 7.55 ms per token against 6.72 ms with the separate
+        push kernel, whose stores are coalesced), so the push stays a kernel of its own there;
+        ``AXB_DECODE_FUSED_PUSH=0/1`` overrides the choice."""
+        fused = os.environ.get("AXB_DECODE_FUSED_PUSH")
+        use_fused = (self._allreduce.world <= 2) if fused is None else fused == "1"
+        if use_fused and w.shape[1] % 32 == 0:
             self._allreduce.gemm_push(a, w, site)
         else:
             self._allreduce.push(cuda_ops.gemm(a, w).reshape(-1), site)
