@@ -5,8 +5,9 @@ Parity targets in the reference (axlearn/common/elastic_input.py): ``ElasticSpmd
 
 A job is configured for ``num_max_slices`` slices (a slice = one node's worth of feeds).  When it
 runs on fewer, the feeds of the missing slices ("elastic feeds") are shared out among the
-processes that are left: and ``num_mini_batches`` consecutive surviving processes read one piece each on top of their own
-feed.  Every surviving process therefore steps on ``feed_logical_batch_size +
+processes that are left: the missing feeds' rows are laid end to end and cut into as many
+contiguous shares as there are surviving feeds, and every survivor reads its share on top of its
+own feed.  Every surviving process therefore steps on ``feed_logical_batch_size +
 elastic_feed_mini_batch_size`` rows and the union over processes is exactly the batch the full
 job would have seen.  The runtime facts (how many slices are alive, which one this is) come from
 the launcher through the config or the ``AXB_NUM_SLICES`` / ``AXB_SLICE_INDEX`` environment.
@@ -14,7 +15,6 @@ the launcher through the config or the ``AXB_NUM_SLICES`` / ``AXB_SLICE_INDEX`` 
 
 from __future__ import annotations
 
-import math
 import os
 from typing import Any, Iterator, Optional
 
