@@ -464,6 +464,90 @@ def lion_optimizer(learning_rate: schedule.Schedule, *, b1: float = 0.9, b2: flo
     return chain(*links)
 
 
+class AdastarState(NamedTuple):
+    count: Tensor
+    gradient_ema: Any           # None when gradient_ema_decay is None
+    gradient_square_ema: Any
+    update_ema: Any             # None when update_ema_decay is None
+
+
+def adastar_optimizer(learning_rate: float, *, gradient_ema_decay: Optional[float], gradient_ema_debias: bool,
+                      gradient_square_ema_decay: float, gradient_square_ema_debias: bool, eps: float,
+                      eps_square: float, raw_update_clipping_threshold: Optional[float],
+                      update_ema_decay: Optional[float], update_ema_debias: bool,
+                      adam_update_transformation: Optional[Any] = None, weight_decay: float = 0.0,
+                      weight_decay_per_param_scale: Optional[Callable] = None,
+                      update_schedule: schedule.Schedule = 1.0, verbosity: int = 0):
+    """The generalisation of decoupled AdamW and unfactored Adafactor (reference:
+    axlearn/common/optimizers.py:1760-2090)::
+
+        g_s   = ema(g, gradient_ema_decay)                   (optional, optionally debiased)
+        g2_s  = ema(g^2 + eps_square, gradient_square_ema_decay)
+        raw   = g_s / (sqrt(g2_s) + eps);  clipped to raw_update_clipping_threshold (block RMS)
+        u     = ema(raw, update_ema_decay)                    (optional)
+        u     = adam_update_transformation(u)                 (optional)
+        delta = -update_schedule(t) * (learning_rate * u + weight_decay * scale_p * p)
+    """
+    sched = schedule.as_schedule_fn(update_schedule)
+    inner = maybe_instantiate(adam_update_transformation) if adam_update_transformation is not None else None
+    clip = clip_by_block_rms(raw_update_clipping_threshold)
+
+    def zeros(params):
+        return tree_map(lambda p: torch.zeros_like(p.value, dtype=torch.float32), params, is_leaf=_is_opt_param)
+
+    def init(params):
+        state = AdastarState(
+            _count0(), None if gradient_ema_decay is None else zeros(params), zeros(params),
+            None if update_ema_decay is None else zeros(params))
+        return (state, inner.init(params)) if inner is not None else state
+
+    def moment(x, acc, decay, debias, t):
+        if decay is None:
+            return x
+        acc.mul_(decay).add_(x, alpha=1 - decay)
+        return acc / (1 - decay ** t) if debias else acc.clone()
+
+    def update(updates, state, params=None):
+        if params is None:
+            raise ValueError("adastar requires params")
+        inner_state = None
+        if inner is not None:
+            state, inner_state = state
+        count = _inc(state.count)
+        t = int(count)
+        g_ema = state.gradient_ema if state.gradient_ema is not None else tree_map(lambda _: None, state.gradient_square_ema)
+        u_ema = state.update_ema if state.update_ema is not None else tree_map(lambda _: None, state.gradient_square_ema)
+
+        def raw(g, m, v):
+            g = g.float()
+            gs = moment(g, m, gradient_ema_decay, gradient_ema_debias, t)
+            g2 = moment(g * g + eps_square, v, gradient_square_ema_decay, gradient_square_ema_debias, t)
+            return gs / (g2.sqrt() + eps)
+
+        raw_updates = _map_updates(raw, updates, g_ema, state.gradient_square_ema)
+        raw_updates, _ = clip.update(raw_updates, None, params)
+        if verbosity > 0:
+            _summary("raw_update_norm", global_norm(raw_updates))
+        smoothed = _map_updates(lambda u, acc: moment(u, acc, update_ema_decay, update_ema_debias, t), raw_updates, u_ema)
+        if inner is not None:
+            smoothed, inner_state = inner.update(smoothed, inner_state, params)
+        scales = _weight_decay_scales(params, weight_decay_per_param_scale)
+        s = sched(t)
+        _summary("schedule_scale", s)
+        out = _map_updates(
+            lambda u, p, ws: -s * (learning_rate * u + (weight_decay * ws) * p.value.float()), smoothed, params, scales)
+        new_state = AdastarState(count, state.gradient_ema, state.gradient_square_ema, state.update_ema)
+        return out, ((new_state, inner_state) if inner is not None else new_state)
+
+    def partition(specs):
+        st = AdastarState(_count_spec(), None if gradient_ema_decay is None else _copy_specs(specs, torch.float32),
+                          _copy_specs(specs, torch.float32),
+                          None if update_ema_decay is None else _copy_specs(specs, torch.float32))
+        return (st, inner.partition(specs)) if inner is not None else st
+
+    return PartitionedGradientTransformation(init, update, partition)
+
+
 def scale_by_param_block_rms(threshold: float = 1e-3) -> PartitionedGradientTransformation:
     """Scales each update by ``max(rms(param), threshold)``."""
 
