@@ -239,8 +239,9 @@ class Conv2DWith1DPadding(Conv2D):
         y = super().forward(x * (1 - paddings[:, :, None, None]).to(x.dtype))
         (lo, hi) = self._pad()[0]
         p = F.pad(paddings.float(), (lo, hi), value=1.0)
-        eff = (cfg.window[0] - 1) * (cfg.dilation[0] if cfg.dilation else 1) + 1
-        anchor = eff - 1 if cfg.padding == "CAUSAL" else (eff - 1) // 2 if cfg.padding == "SAME" else 0
+        # The anchor of a window is the frame that sits where the first real frame sits in the
+        # first window: `lo` frames in (0 for VALID, the centre for SAME, the last for CAUSAL).
+        anchor = lo
         out_p = p[:, anchor::cfg.strides[0]][:, :y.shape[1]]
         return y * (1 - out_p[:, :, None, None]).to(y.dtype), out_p
 

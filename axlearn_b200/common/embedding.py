@@ -99,3 +99,29 @@ class TransformerTextEmbeddings(BaseEmbedding):
         if cap:
             logits = cap * torch.tanh(logits / cap)
         return logits
+
+
+class SinusoidalPositionalEmbedding(BaseLayer):
+    """Fixed sinusoidal position embeddings (reference: axlearn/common/layers.py
+    ``SinusoidalPositionalEmbedding``): ``[sin(p / s_i) | cos(p / s_i)]`` with timescales ``s_i``
+    spaced geometrically between ``min_timescale`` and ``max_timescale``."""
+
+    @config_class
+    class Config(BaseLayer.Config):
+        dim: Required[int] = REQUIRED
+        min_timescale: float = 1.0
+        max_timescale: float = 10000.0
+
+    def forward(self, positions: torch.Tensor) -> torch.Tensor:
+        """``positions [...]`` -> ``[..., dim]``."""
+        import math
+
+        cfg = self._config
+        half = cfg.dim // 2
+        log_inc = math.log(cfg.max_timescale / cfg.min_timescale) / max(1, half - 1)
+        inv = cfg.min_timescale * torch.exp(-log_inc * torch.arange(half, device=positions.device, dtype=torch.float32))
+        scaled = positions.float()[..., None] * inv
+        emb = torch.cat([torch.sin(scaled), torch.cos(scaled)], dim=-1)
+        if cfg.dim % 2:
+            emb = torch.nn.functional.pad(emb, (0, 1))
+        return emb
