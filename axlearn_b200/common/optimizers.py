@@ -190,6 +190,8 @@ def _weight_decay_scales(params: Any, per_param_scale: Optional[Callable]) -> An
 
 
 def scale_update_per_param(per_param_scale: Callable[[Any], Any]) -> PartitionedGradientTransformation:
+    per_param_scale = maybe_instantiate(per_param_scale)
+
     def fn(updates, params):
         scales = per_param_scale(params)
         return _map_updates(lambda g, s: g * s, updates, scales)

@@ -171,6 +171,46 @@ def adamw_decoupled_learner_config(
     return learner.Learner.default_config().set(optimizer=optimizer_cfg)
 
 
+def mup_simple_adam_update_transformation(scale_factor: float) -> InstantiableConfig:
+    """Scales the Adam update of the transformer's matrices by ``scale_factor`` ("mup-simple",
+    arXiv:2309.14322 section 3.2.4): with the base width ``w0`` and the model width ``w`` the
+    factor is ``w0 / w``, which keeps a learning rate tuned on the small model valid."""
+    return config_for_function(optimizers.scale_update_per_param).set(
+        per_param_scale=config_for_function(optimizers.per_param_scale_by_path).set(
+            scale_by_path=[
+                (".*attention/o_proj/weight", scale_factor),
+                (".*attention/i_proj/i_proj/qkv_proj/weight", scale_factor),
+                (".*feed_forward/linear1_0/weight", scale_factor),
+                (".*feed_forward/linear1_1/weight", scale_factor),
+                (".*feed_forward/linear2/weight", scale_factor),
+                (".*feed_forward/wi_0_weight", scale_factor),
+                (".*feed_forward/wi_1_weight", scale_factor),
+                (".*feed_forward/wo_weight", scale_factor),
+            ],
+            description="scale_by_mup_simple", default_scale=1.0))
+
+
+def adastar_learner_config(
+    *, peak_lr: float, max_step: int, lr_warmup_steps: int = 2000, alpha: float = 0.005,
+    weight_decay: float = 3.16e-4, b1: float = 0.95, b2: float = 0.95,
+    adam_update_transformation: Optional[Any] = None,
+) -> learner.Learner.Config:
+    """skip_and_clip_by_global_norm(drop 100, clip 1) around AdaStar in its Adafactor-like
+    setting: no gradient momentum, debiased second moment with ``eps_square``, raw updates
+    clipped per tensor, momentum on the updates without debiasing."""
+    update_schedule = config_for_function(schedule.cosine_with_linear_warmup).set(
+        peak_lr=1.0, max_step=max_step, warmup_steps=lr_warmup_steps, begin_value=0.0, alpha=alpha)
+    optimizer_cfg = config_for_function(optimizers.skip_and_clip_by_global_norm).set(
+        inner=config_for_function(optimizers.adastar_optimizer).set(
+            learning_rate=peak_lr, gradient_ema_decay=None, gradient_ema_debias=False,
+            gradient_square_ema_decay=b2, gradient_square_ema_debias=True, eps=0.0, eps_square=1e-30,
+            raw_update_clipping_threshold=1.0, update_ema_decay=b1, update_ema_debias=False,
+            weight_decay=weight_decay, update_schedule=update_schedule,
+            adam_update_transformation=adam_update_transformation),
+        drop_norm=100, max_norm=1)
+    return learner.Learner.default_config().set(optimizer=optimizer_cfg)
+
+
 def adamw_learner_config(*, peak_lr: float, max_step: int, weight_decay: float, lr_warmup_steps: int = 2000,
                          b1: float = 0.9, b2: float = 0.95, eps: float = 1e-8) -> learner.Learner.Config:
     """clip -> AdamW (decay scaled by lr) with constant lr after warm-up-free start."""
