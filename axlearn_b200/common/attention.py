@@ -426,6 +426,55 @@ class RoFormerSinusoidalPositionalEmbedding(BaseLayer):
         return torch.cat([sin, cos], dim=-1)
 
 
+class YaRNSinusoidalPositionalEmbedding(RoFormerSinusoidalPositionalEmbedding):
+    """RoPE with YaRN context extension (arXiv:2309.00071; reference: axlearn/common/
+    attention.py:1168-1298).  Dimensions that rotate fast (many periods within the original
+    context) keep their frequency, slow ones are interpolated by ``scaling_factor``, with a linear
+    ramp between the ``beta_fast`` and ``beta_slow`` rotation counts; sin / cos are multiplied by
+    ``(0.1 ln(scaling_factor) + 1) * attn_factor``."""
+
+    @config_class
+    class Config(RoFormerSinusoidalPositionalEmbedding.Config):
+        original_max_seq_length: Required[int] = REQUIRED
+        scaling_factor: float = 1.0
+        beta_slow: float = 1.0
+        beta_fast: float = 32.0
+        extrapolation_factor: float = 1.0
+        attn_factor: float = 1.0
+
+    @nowrap
+    def compute_rope_params(self) -> tuple[Tensor, float]:
+        """``(inverse frequencies [dim / 2], magnitude scale)``."""
+        cfg = self._config
+        dim, theta = cfg.dim, cfg.theta
+
+        def correction_dim(rotations: float) -> float:
+            # The dimension whose wavelength fits `rotations` times into the original context.
+            return dim * math.log(cfg.original_max_seq_length / (rotations * 2 * math.pi)) / (2 * math.log(theta))
+
+        pos_freqs = theta ** (2 * torch.arange(dim // 2, dtype=torch.float32) / dim)
+        extrapolation = 1.0 / pos_freqs
+        interpolation = 1.0 / (cfg.scaling_factor * pos_freqs)
+        low = max(0, math.floor(correction_dim(cfg.beta_fast)))
+        high = min(dim - 1, math.ceil(correction_dim(cfg.beta_slow)))
+        if low == high:
+            high += 0.001
+        ramp = ((torch.arange(dim // 2, dtype=torch.float32) - low) / (high - low)).clamp(0, 1)
+        mask = (1 - ramp) * cfg.extrapolation_factor
+        inv_freq = interpolation * (1 - mask) + extrapolation * mask
+        mscale = (0.1 * math.log(max(1.0, cfg.scaling_factor)) + 1.0) * cfg.attn_factor
+        return inv_freq, mscale
+
+    def forward(self, *, positions: Optional[Tensor] = None, max_seq_len: Optional[int] = None) -> Tensor:
+        if positions is None:
+            if max_seq_len is None:
+                raise ValueError("need positions or max_seq_len")
+            positions = self.default_query_positions(max_seq_len)
+        inv_freq, mscale = self.compute_rope_params()
+        enc = positions.float()[..., None] * inv_freq.to(positions.device)
+        return torch.cat([torch.sin(enc) * mscale, torch.cos(enc) * mscale], dim=-1)
+
+
 def apply_rotary_position_embeddings(
     *, query: Tensor, key: Tensor, value: Tensor, sinusoidal_pos: Tensor, rotary_key: bool = True,
     rotary_value: bool = False,
@@ -481,6 +530,18 @@ class RoFormerQKVLinear(BaseQKVLinear):
             query_positions = torch.arange(q.shape[1], device=q.device)
         theta = cfg.rope_pos_emb_layer.theta
         pos = query_positions
+        if type(self.rope_pos_emb_layer) is not RoFormerSinusoidalPositionalEmbedding:  # pylint: disable=unidiomatic-typecheck
+            # A scaled variant (e.g. YaRN): rotate with the layer's own sin / cos table.
+            pos2 = pos if pos.dim() == 2 else pos[None]
+            table = self.rope_pos_emb_layer(positions=pos2)[:, :, None, :]          # [B or 1, T, 1, H]
+            if kv_state is not None:
+                q, _, _ = apply_rotary_position_embeddings(
+                    query=q, key=q, value=q, sinusoidal_pos=table, rotary_key=False, rotary_value=False)
+                return self.Output(q, k, v)
+            q, k, v = apply_rotary_position_embeddings(
+                query=q, key=k, value=v, sinusoidal_pos=table, rotary_key=cfg.rotary_key,
+                rotary_value=cfg.rotary_value)
+            return self.Output(q, k, v)
         if pos.dim() == 2 and pos.shape[0] == 1:
             pos = pos[0]
         if kv_state is not None:
