@@ -772,3 +772,66 @@ def convert_dense_to_moe_parameters(dense_params: dict, *, num_experts: int, act
         if key in dense_params:
             out[key] = dense_params[key]
     return out
+
+
+class ApproximateTokenDropFreeMoE(TransformerFeedForwardMoE):
+    """Expert-parallel mixture of experts with drop-free *routing* and a generous fixed buffer
+    (reference: axlearn/common/mixture_of_experts.py:2754-2824): the router picks top-k experts
+    without any capacity limit, and every expert accepts up to ``expert_parallel_capacity`` times
+    its fair share of assignments from each routing group, so tokens are only dropped under a
+    load imbalance beyond that factor (reported as ``dropped_token_ratio``).  Everything after
+    routing -- the exchange over peer memory or all-to-all, the expert GEMMs, the combine -- is
+    the capacity-based machinery of the parent class with that buffer size."""
+
+    @config_class
+    class Config(TransformerFeedForwardMoE.Config):
+        expert_parallel_capacity: float = 1.25
+        seq_load_balance_loss_weight: Optional[float] = None
+
+    @classmethod
+    def default_config(cls):
+        cfg = super().default_config()
+        cfg.gating = TopKDropFreeGating.default_config()
+        return cfg
+
+    def _route(self, x: Tensor) -> tuple[Routing, Tensor]:
+        """``x [O, G, S, M]`` -> routing with capacity slots, and the auxiliary loss."""
+        cfg = self._config
+        o, g, s, m = x.shape
+        logits = torch.einsum("ogsm,me->ogse", x.float(), self.parameters["gate_weight"].float())
+        free = self.gating(logits.reshape(o * g, s, cfg.num_experts), cfg.seq_load_balance_loss_weight)
+        k = free.gate_assignment.shape[-1]
+        index = free.gate_assignment.reshape(o, g, s, k)
+        capacity = max(1, math.ceil(cfg.expert_parallel_capacity * s * k / cfg.num_experts))
+        slot = _slots_in_priority_order(index, cfg.num_experts, capacity)
+        kept = slot >= 0
+        self.add_summary("dropped_token_ratio", 1.0 - kept.float().mean())
+        weights = free.expert_weights.reshape(o, g, s, k) * kept.float()
+        aux = free.load_balance_loss * cfg.load_balance_loss_weight
+        if cfg.router_z_loss_weight:
+            aux = aux + free.router_z_loss * cfg.router_z_loss_weight
+        if cfg.seq_load_balance_loss_weight and free.seq_load_balance_loss is not None:
+            aux = aux + free.seq_load_balance_loss * cfg.seq_load_balance_loss_weight
+        routing = Routing(expert_index=index, slot=slot, weight=weights, num_experts=cfg.num_experts,
+                          expert_capacity=capacity, load_balance_loss=free.load_balance_loss,
+                          router_z_loss=free.router_z_loss)
+        return routing, aux
+
+    def _dispatch_and_combine(self, x: Tensor) -> Tensor:
+        cfg = self._config
+        in_dtype = x.dtype
+        token_shape = x.shape[:-1]
+        o = cfg.outer_batch
+        tokens = math.prod(token_shape) // o
+        if tokens % cfg.num_groups:
+            raise ValueError(f"{tokens} tokens per outer batch must be divisible by num_groups({cfg.num_groups}).")
+        x = x.reshape(o, cfg.num_groups, tokens // cfg.num_groups, cfg.input_dim)
+        routing, aux = self._route(x)
+        self.add_module_output("aux_loss", aux)
+        fused = self._peer_exchange(x, routing)
+        if fused is not None:
+            return fused.to(in_dtype).reshape(*token_shape, cfg.input_dim)
+        expert_in = self.gating.dispatch(x, routing)
+        expert_out = self._experts(expert_in)
+        out = self.gating.combine(expert_out, routing, dtype=in_dtype)
+        return out.reshape(*token_shape, cfg.input_dim)

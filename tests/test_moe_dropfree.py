@@ -197,3 +197,24 @@ def test_qwen3_style_model_trains_on_gpu(tmp_path):
     _, gpu_losses = _train_qwen(tmp_path / "gpu", 3, device="cuda")
     for a, b in zip(cpu_losses, gpu_losses):
         assert abs(a - b) < 0.05 * abs(a), (cpu_losses, gpu_losses)
+
+
+def test_approximate_dropfree_matches_dropfree_when_nothing_is_dropped():
+    from axlearn_b200.common.mixture_of_experts import ApproximateTokenDropFreeMoE
+
+    layer, params = _layer()
+    cfg = ApproximateTokenDropFreeMoE.default_config().set(
+        name="moe", input_dim=16, hidden_dim=32, num_experts=4, num_groups=1, activation=("nn.silu", "linear"),
+        structure="prenorm", expert_parallel_capacity=4.0)        # room for every assignment
+    cfg.gating.set(num_experts_per_token=2)
+    approx = cfg.instantiate(parent=None)
+    torch.manual_seed(5)
+    x = torch.randn(2, 12, 16)
+    want, _ = functional(layer, prng.PRNGKey(1), params, dict(inputs=x), is_training=True, drop_output_collections=())
+    got, oc = functional(approx, prng.PRNGKey(1), params, dict(inputs=x), is_training=True, drop_output_collections=())
+    torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-5)
+    assert float(oc.summaries["dropped_token_ratio"]) == 0.0
+    # A tight buffer drops the overflow and says so.
+    tight = cfg.clone(expert_parallel_capacity=0.5).instantiate(parent=None)
+    _, oc2 = functional(tight, prng.PRNGKey(1), params, dict(inputs=x), is_training=True, drop_output_collections=())
+    assert float(oc2.summaries["dropped_token_ratio"]) > 0.3
