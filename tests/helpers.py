@@ -27,3 +27,32 @@ def tiny_fuji_trainer_config(directory, *, max_step=20, save_every_n_steps=10, s
     cfg.dir = str(directory)
     cfg.device = device
     return cfg
+
+
+def to_plain(obj):
+    """Tensors -> numpy arrays, recursively: values put on a multiprocessing queue must not
+    depend on the sending process staying alive (torch shares tensor storage by file descriptor,
+    which fails when the sender has exited before the receiver unpickles)."""
+    import torch
+
+    if isinstance(obj, torch.Tensor):
+        return ("__tensor__", obj.detach().cpu().float().numpy() if obj.dtype == torch.bfloat16 else obj.detach().cpu().numpy(),
+                str(obj.dtype))
+    if isinstance(obj, dict):
+        return {k: to_plain(v) for k, v in obj.items()}
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(to_plain(v) for v in obj)
+    return obj
+
+
+def from_plain(obj):
+    import torch
+
+    if isinstance(obj, tuple) and len(obj) == 3 and obj[0] == "__tensor__":
+        t = torch.from_numpy(obj[1])
+        return t.bfloat16() if obj[2] == "torch.bfloat16" else t
+    if isinstance(obj, dict):
+        return {k: from_plain(v) for k, v in obj.items()}
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(from_plain(v) for v in obj)
+    return obj

@@ -15,6 +15,8 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, REPO)
+from tests.helpers import from_plain, to_plain  # noqa: E402  pylint: disable=wrong-import-position
 pytestmark = pytest.mark.gpu
 
 
@@ -56,7 +58,7 @@ def _run(rank, world, port, directory, fused, queue):
                 grads = {p: t.grad.float().cpu() for p, t in flatten_items(stacked)}
         torch.cuda.synchronize()
         cuda_ops.check_status()
-        queue.put((rank, losses, grads, cuda_ops.launch_count))
+        queue.put(to_plain((rank, losses, grads, cuda_ops.launch_count)))
     finally:
         dist.destroy_process_group()
 
@@ -71,7 +73,7 @@ def _launch(tmp_path, fused):
         p.start()
     results = {}
     for _ in range(world):
-        rank, losses, grads, launches = q.get(timeout=600)
+        rank, losses, grads, launches = from_plain(q.get(timeout=600))
         results[rank] = (losses, grads, launches)
     for p in procs:
         p.join(timeout=120)

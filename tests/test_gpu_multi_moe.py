@@ -11,6 +11,8 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, REPO)
+from tests.helpers import from_plain, to_plain  # noqa: E402  pylint: disable=wrong-import-position
 pytestmark = pytest.mark.gpu
 
 
@@ -51,8 +53,8 @@ def _run(rank, world, port, directory, peer, queue):
         torch.cuda.synchronize()
         cuda_ops.check_status()
         layer = trainer.trainer_state["model"]["decoder"]["transformer"]["repeat"]["layer"]["feed_forward"]
-        queue.put((rank, losses, layer["wo_weight"].float().cpu(), layer["gate_weight"].float().cpu(),
-                   cuda_ops.launch_count))
+        queue.put(to_plain((rank, losses, layer["wo_weight"].float().cpu(), layer["gate_weight"].float().cpu(),
+                            cuda_ops.launch_count)))
     finally:
         dist.destroy_process_group()
 
@@ -67,7 +69,7 @@ def _launch(tmp_path, peer):
         p.start()
     results = {}
     for _ in range(world):
-        rank, *rest = q.get(timeout=600)
+        rank, *rest = from_plain(q.get(timeout=600))
         results[rank] = rest
     for p in procs:
         p.join(timeout=120)

@@ -10,6 +10,8 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, REPO)
+from tests.helpers import from_plain, to_plain  # noqa: E402  pylint: disable=wrong-import-position
 
 
 def _free_port() -> int:
@@ -51,7 +53,7 @@ def _worker(rank, world, port, directory, mesh_axes, steps, out_queue):
         # Each rank holds half of the batch: one routing group per rank = two in total.
         trainer, losses = _train(os.path.join(directory, f"r{rank}"), mesh_axes, steps, num_groups=2 // world)
         layer = trainer.trainer_state["model"]["decoder"]["transformer"]["repeat"]["layer"]["feed_forward"]
-        out_queue.put((rank, losses, layer["wo_weight"].clone(), layer["gate_weight"].clone()))
+        out_queue.put(to_plain((rank, losses, layer["wo_weight"].clone(), layer["gate_weight"].clone())))
     finally:
         dist.destroy_process_group()
 
@@ -69,7 +71,7 @@ def test_expert_parallel_matches_single_process(tmp_path):
         p.start()
     got = {}
     for _ in range(world):
-        rank, losses, wo, gate = q.get(timeout=120)
+        rank, losses, wo, gate = from_plain(q.get(timeout=120))
         got[rank] = (losses, wo, gate)
     for p in procs:
         p.join(timeout=120)

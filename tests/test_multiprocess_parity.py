@@ -15,6 +15,8 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, REPO)
+from tests.helpers import from_plain, to_plain  # noqa: E402  pylint: disable=wrong-import-position
 
 
 def _free_port() -> int:
@@ -59,7 +61,7 @@ def _worker(rank, world, port, directory, mesh_axes, steps, out_queue):
                     full = coll.all_gather_raw(
                         full, trainer.mesh().group(axis), trainer.mesh().axis_size(axis), dim + 1)
         if rank == 0:
-            out_queue.put((losses, full.clone()))
+            out_queue.put(to_plain((losses, full.clone())))
     finally:
         dist.destroy_process_group()
 
@@ -78,7 +80,7 @@ def test_sharded_matches_single_process(tmp_path, mesh_axes):
     procs = [ctx.Process(target=_worker, args=(r, world, port, str(tmp_path), mesh_axes, steps, q)) for r in range(world)]
     for p in procs:
         p.start()
-    losses, full_w = q.get(timeout=300)
+    losses, full_w = from_plain(q.get(timeout=300))
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0

@@ -9,6 +9,8 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, REPO)
+from tests.helpers import from_plain, to_plain  # noqa: E402  pylint: disable=wrong-import-position
 
 
 def _free_port() -> int:
@@ -44,7 +46,7 @@ def _worker(rank, world, port, directory, steps, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        q.put((rank,) + _train(os.path.join(directory, f"r{rank}"), dict(pipeline=2), steps))
+        q.put(to_plain((rank,) + _train(os.path.join(directory, f"r{rank}"), dict(pipeline=2), steps)))
     finally:
         dist.destroy_process_group()
 
@@ -61,7 +63,7 @@ def test_two_stage_pipeline_matches_single_process(tmp_path):
         p.start()
     got = {}
     for _ in range(world):
-        rank, losses, w, emb = q.get(timeout=120)
+        rank, losses, w, emb = from_plain(q.get(timeout=120))
         got[rank] = (losses, w, emb)
     for p in procs:
         p.join(timeout=120)
