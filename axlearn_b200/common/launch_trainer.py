@@ -38,6 +38,9 @@ def parser() -> argparse.ArgumentParser:
     ap.add_argument("--trace_at_steps", default="", help="comma-separated steps at which to start a trace")
     ap.add_argument("--device", default=None, help="cpu | cuda[:N]; default: this rank's GPU if there is one")
     ap.add_argument("--status_port", type=int, default=None, help="serve thread stacks over HTTP on this port")
+    ap.add_argument("--recorder_type", default=None, help="goodput recorder, e.g. 'file'")
+    ap.add_argument("--recorder_spec", action="append", default=[], help="key=value for the recorder config "
+                    "(repeatable); the 'file' recorder defaults to dir=<trainer_dir>/goodput")
     ap.add_argument("--distributed", action="store_true", help="join the torch.distributed job described by "
                     "RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT")
     return ap
@@ -74,6 +77,13 @@ def get_trainer_config(args: Any):
         cfg.device = args.device
     cfg.watchdog_timeout_seconds = args.trainer_watchdog_timeout_seconds
     cfg.crash_on_hang_timeout_seconds = args.trainer_crash_on_hang_timeout_seconds
+    if getattr(args, "recorder_type", None):
+        from axlearn_b200.common import measurement
+
+        spec = list(args.recorder_spec)
+        if args.recorder_type == "file" and not any(item.startswith("dir=") for item in spec):
+            spec.append(f"dir={os.path.join(args.trainer_dir, 'goodput')}")
+        cfg.recorder = measurement.get_recorder_config(args.recorder_type, spec)
     if args.trace_at_steps:
         cfg.start_trace_steps = [int(s) for s in args.trace_at_steps.split(",") if s]
     if args.mesh_selector and getattr(cfg, "mesh_rules", None):

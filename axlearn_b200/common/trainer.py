@@ -341,26 +341,44 @@ class SpmdTrainer(Module):
         """Trains until ``max_step`` (or input exhaustion); returns the last step's outputs."""
         cfg = self._config
         output = None
-        with self._watchdog(), self._mesh, use_device(self._device), self.checkpointer:
-            if self._device_monitor is not None:
-                self._device_monitor.start_monitoring()
-            self._prepare_training(prng_key)
-            input_iter = self.input.batches(iter(self.input.dataset()))
-            for batch in input_iter:
-                if cfg.max_step is not None and self._step >= cfg.max_step:
-                    break
-                self._maybe_trace()
-                self._step += 1
-                t0 = time.perf_counter()
-                output = self._run_step(batch)
-                self._step_times.append(time.perf_counter() - t0)
-                if cfg.max_step is not None and self._step >= cfg.max_step:
-                    break
-            self._stop_trace()
-            self.checkpointer.wait_until_finished()
-            self.summary_writer.flush()
-            if self._device_monitor is not None:
-                self._device_monitor.stop_monitoring()
+        from axlearn_b200.common import measurement
+
+        def record(event, *args):
+            if self._recorder is not None:
+                self._recorder.record(event, *args)
+
+        record(measurement.Event.START_JOB)
+        if self._recorder is not None:
+            self._recorder.start_monitoring()
+        try:
+            with self._watchdog(), self._mesh, use_device(self._device), self.checkpointer:
+                if self._device_monitor is not None:
+                    self._device_monitor.start_monitoring()
+                record(measurement.Event.START_TRAINING_PREPARATION)
+                self._prepare_training(prng_key)
+                record(measurement.Event.END_TRAINING_PREPARATION)
+                input_iter = self.input.batches(iter(self.input.dataset()))
+                while True:
+                    if cfg.max_step is not None and self._step >= cfg.max_step:
+                        break
+                    record(measurement.Event.START_DATA_LOADING)
+                    batch = next(input_iter, None)
+                    record(measurement.Event.END_DATA_LOADING)
+                    if batch is None:
+                        break
+                    self._maybe_trace()
+                    self._step += 1
+                    record(measurement.Event.START_STEP, self._step)
+                    t0 = time.perf_counter()
+                    output = self._run_step(batch)
+                    self._step_times.append(time.perf_counter() - t0)
+                self._stop_trace()
+                self.checkpointer.wait_until_finished()
+                self.summary_writer.flush()
+                if self._device_monitor is not None:
+                    self._device_monitor.stop_monitoring()
+        finally:
+            record(measurement.Event.END_JOB)
         return output
 
     def _prepare_training(self, prng_key: Tensor) -> None:
