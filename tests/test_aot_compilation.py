@@ -34,5 +34,5 @@ def test_70b_does_not_fit_eight_gpus_and_cli(capsys):
     assert state > 95 * GIB
     rc = aot_compilation.main(["--module", "text.gpt.c4_trainer", "--config", "fuji-7B-v2", "--num_gpus", "8", "--per_gpu_batch", "4", "--json"])
     assert rc == 0 and '"fits": true' in capsys.readouterr().out
-    with pytest.raises(ValueError):
-        plan_training_memory(cfg, num_gpus=3)
+    with pytest.raises(ValueError):           # fsdp=8 x data=-1 cannot be laid out on 3 GPUs
+        plan_training_memory(fuji.trainer_configs()["fuji-7B-v2"](), num_gpus=3)
