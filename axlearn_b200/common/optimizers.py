@@ -589,6 +589,8 @@ def scale_by_factored_rms(factored: bool = True, decay_rate: float = 0.8, step_o
     """Adafactor second-moment estimate, factored over the two largest dims of big tensors
     (reference: axlearn/common/factorized_rms.py:73)."""
 
+    decay_fn = maybe_instantiate(decay_rate) if not isinstance(decay_rate, (int, float)) else None
+
     def factored_dims(shape):
         if not factored or len(shape) < 2:
             return None
@@ -615,7 +617,10 @@ def scale_by_factored_rms(factored: bool = True, decay_rate: float = 0.8, step_o
     def update(updates, state, params=None):
         count = _inc(state.count)
         t = float(int(count) - step_offset)
-        decay = 1.0 - t ** (-decay_rate) if t > 0 else 0.0
+        if callable(decay_fn):
+            decay = float(decay_fn(int(count)))
+        else:
+            decay = 1.0 - t ** (-decay_rate) if t > 0 else 0.0
 
         def upd(g, vr, vc, v):
             gf = g.float()

@@ -122,6 +122,16 @@ def adafactor(*, scale: float = 1.0, warmup_steps: int = 10_000, decay_power: fl
     return fn
 
 
+def adafactor_decay_rate(c: float = 0.8, step_offset: int = 0) -> ScheduleFn:
+    """Second-moment decay of Adafactor: ``1 - (step - step_offset) ** -c`` (0 at the first step)."""
+
+    def fn(step):
+        t = float(step) - step_offset
+        return 1.0 - t ** (-c) if t > 0 else 0.0
+
+    return fn
+
+
 def cosine_with_linear_warmup(*, peak_lr: float, warmup_steps: int = 500, max_step: int,
                               begin_value: float = 0.0, alpha: float = 0.0,
                               decay_begin_step: Optional[int] = None) -> ScheduleFn:

@@ -62,3 +62,23 @@ def test_all_families_list_their_configs():
         names |= set(module.trainer_configs())
     assert {"envy-Mixtral-8x7B", "qwen3-30B-A3B", "honeycrisp-3B", "gala-1B"} <= names
     assert any(n.startswith("fuji-7B") for n in names)
+
+
+def test_gspmd_pipeline_configs(tmp_path):
+    from axlearn_b200.experiments.text.gpt import gspmd
+
+    cfgs = gspmd.trainer_configs()
+    shapes = _param_shapes(cfgs["gspmd-16B-2x16x8"]().model)
+    stage = "decoder/transformer/pipeline/layer/"
+    key = next(p for p in shapes if p.startswith(stage) and p.endswith("linear1/weight"))
+    assert shapes[key] == (2, 4096, 16384)                                          # [stages, D, 4D]
+    assert sum(p.endswith("linear1/weight") for p in shapes) == 32               # layers per stage
+    total = sum(torch.Size(s).numel() for s in shapes.values())
+    assert 12e9 < total < 18e9
+    cfg = cfgs["gspmd-test"]()
+    cfg.dir, cfg.device, cfg.train_dtype = str(tmp_path), "cpu", None
+    trainer = cfg.instantiate(parent=None)
+    trainer.init(prng.PRNGKey(0))
+    batch = next(iter(trainer.input.dataset()))
+    losses = [trainer.train_step(batch)["loss"].item() for _ in range(10)]
+    assert losses[-1] < losses[0]
