@@ -90,6 +90,10 @@ class _ConvND(BaseLayer):
         # [spatial..., in, out] -> [out, in, spatial...]
         w = w.permute(nd + 1, nd, *range(nd))
         xc = x.movedim(-1, 1)
+        if not xc.is_cuda:
+            # The channels-last view is what cuDNN likes; the CPU kernels (oneDNN) have corrupted the
+            # heap on such views with few output channels and several threads, so they get NCHW.
+            xc = xc.contiguous()
         pads = self._pad()
         flat = [p for lo_hi in reversed(pads) for p in lo_hi]
         if any(flat):

@@ -128,3 +128,54 @@ def test_roi_align_on_a_linear_ramp():
     out = det.roi_align(feat, torch.tensor([[2.0, 2.0, 6.0, 6.0]]), output_size=2, sampling_ratio=2)
     want = torch.tensor([[3 + 30.0, 3 + 50.0], [5 + 30.0, 5 + 50.0]])
     torch.testing.assert_close(out[0, :, :, 0], want)
+
+
+def test_retinanet_learns_to_find_a_square():
+    from axlearn_b200.vision.retinanet import FPN, RetinaNetModel, label_anchors, sigmoid_focal_loss
+
+    # Focal loss: gamma = 0 and alpha = 0.5 is half the plain cross entropy.
+    logits, targets = torch.randn(5, 3), torch.randint(0, 2, (5, 3)).float()
+    torch.testing.assert_close(
+        sigmoid_focal_loss(logits, targets, alpha=0.5, gamma=0.0),
+        0.5 * torch.nn.functional.binary_cross_entropy_with_logits(logits, targets, reduction="none"))
+    anchors = torch.tensor([[0.0, 0, 10, 10], [0, 0, 7, 10], [30, 30, 40, 40]])
+    cls, boxes, pos = label_anchors(anchors, torch.tensor([[0.0, 0, 10, 10], [0, 0, 0, 0]]), torch.tensor([2, -1]))
+    assert cls.tolist() == [2, 2, -1] and pos.tolist() == [True, True, False]
+    cls2, _, _ = label_anchors(anchors, torch.tensor([[0.0, 0, 10, 22]]), torch.tensor([1]))
+    assert cls2.tolist() == [-2, -1, -1]                    # IoU 0.45: neither positive nor background
+
+    backbone = ResNet.default_config().set(hidden_dim=8, num_blocks_per_stage=(1, 1, 1))
+    backbone.stage.block = ResidualBlock.default_config()
+    cfg = RetinaNetModel.default_config().set(
+        name="retina", backbone=backbone, num_classes=2, num_scales=1, aspect_ratios=(1.0,), anchor_size=3.0,
+        fpn=FPN.default_config().set(hidden_dim=16, min_level=3, max_level=4))
+    cfg.head.num_layers = 1
+    model = cfg.instantiate(parent=None)
+    params = _init(model)
+    torch.manual_seed(0)
+    image = torch.zeros(2, 64, 64, 3)
+    image[0, 16:40, 16:40] = 1.0
+    image[1, 24:48, 8:32, 1] = 1.0
+    batch = {"image": image,
+             "groundtruth_boxes": torch.tensor([[[16.0, 16, 40, 40]], [[24.0, 8, 48, 32]]]),
+             "groundtruth_classes": torch.tensor([[0], [1]])}
+    out0, _ = functional(model, prng.PRNGKey(0), params, dict(input_batch=batch), is_training=False, method="predict")
+    assert out0["class_outputs"].shape == (2, 8 * 8 + 4 * 4, 2) and out0["anchors"].shape == (80, 4)
+    assert torch.sigmoid(out0["class_outputs"]).mean().item() == pytest.approx(0.01, abs=0.02)   # prior probability
+    leaves = [t.requires_grad_() for p, t in flatten_items(params) if "moving_" not in p]
+    opt = torch.optim.Adam(leaves, lr=3e-3)
+    first = None
+    for step in range(150):
+        (loss, _), oc = functional(model, prng.PRNGKey(step), params, dict(input_batch=batch), is_training=True)
+        first = first if first is not None else loss.item()
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+    assert loss.item() < 0.2 * first and float(oc.summaries["num_positive_anchors"]) >= 1
+    with torch.no_grad():
+        dets, _ = functional(model, prng.PRNGKey(0), params, dict(input_batch=batch, score_threshold=0.3),
+                             is_training=True, method="detect")
+    for i, want_cls in enumerate([0, 1]):
+        assert len(dets[i]["scores"]) >= 1 and dets[i]["classes"][0].item() == want_cls
+        iou = det.pairwise_iou(dets[i]["boxes"][:1], batch["groundtruth_boxes"][i])
+        assert iou.item() > 0.5
