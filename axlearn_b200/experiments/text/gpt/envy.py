@@ -36,6 +36,18 @@ from axlearn_b200.experiments.text.gpt.common import model_config as common_mode
 MODEL_PRESETS = {
     "test": dict(num_layers=2, hidden_dim=64, num_heads=4, num_kv_heads=2, num_experts=4, moe_ffn_dim=128,
                  vocab_size=512, num_groups=2),
+    # The reference's Switch-Transformer-style sizes: dense and sparse layers alternate, hybrid-norm
+    # feed-forward, per-head RMSNorm on queries and keys, 2 routing groups, capacity factor 2.
+    "Switch-Base": dict(num_layers=12, hidden_dim=12 * 128, num_heads=12, num_kv_heads=12, num_experts=128,
+                        moe_ffn_dim=4 * 12 * 128, vocab_size=32768, num_groups=2, ffn_layer_types=("dense", "sparse"),
+                        ffn_structure="hybridnorm", qk_norm=True, shared_lm_head=True, rope_theta=1e4),
+    "Switch-Large": dict(num_layers=24, hidden_dim=16 * 128, num_heads=16, num_kv_heads=16, num_experts=128,
+                         moe_ffn_dim=4 * 16 * 128, vocab_size=32768, num_groups=2, ffn_layer_types=("dense", "sparse"),
+                         ffn_structure="hybridnorm", qk_norm=True, shared_lm_head=True, rope_theta=1e4),
+    "Switch-XXL": dict(num_layers=24, hidden_dim=64 * 128, num_heads=64, num_kv_heads=8, num_experts=64,
+                       moe_ffn_dim=int(2.5 * 64 * 128), vocab_size=32768, num_groups=2,
+                       ffn_layer_types=("dense", "sparse"), ffn_structure="hybridnorm", qk_norm=True,
+                       shared_lm_head=True, rope_theta=1e4),
     "Mixtral-8x7B": dict(num_layers=32, hidden_dim=4096, num_heads=32, num_kv_heads=8, num_experts=8,
                          moe_ffn_dim=14336, vocab_size=32768, num_groups=1),
 }
@@ -67,6 +79,7 @@ def model_config(
     qk_norm: bool = False,
     norm_eps: float = 1e-5,
     z_loss_scale: float = 0.0,
+    ffn_structure: str = "prenorm",
 ) -> causal_lm.Model.Config:
     """RMSNorm / RoPE / SwiGLU decoder whose feed-forward layers follow ``ffn_layer_types``
     (cycled over the stack): "sparse" = MoE, "dense" = ordinary FFN.  ``drop_free`` selects the
@@ -108,7 +121,7 @@ def model_config(
         emb_cfg=TransformerTextEmbeddings.default_config().set(pos_emb=None),
         lm_head_cfg=LmHead.default_config() if not shared_lm_head else None,
         attention_cfg=atten_cfg, attention_qkv_linear=qkv, ffn_layer_types=tuple(ffn_layer_types),
-        expert_cfg=expert_cfg, moe_ffn_dim=moe_ffn_dim, scan_chunk=scan_chunk)
+        expert_cfg=expert_cfg, moe_ffn_dim=moe_ffn_dim, scan_chunk=scan_chunk, ffn_structure=ffn_structure)
     cfg.aux_loss_regex = ".*/aux_loss"
     cfg.metrics = causal_lm.metrics_config(aux_loss_regex=cfg.aux_loss_regex, z_loss_scale=z_loss_scale)
     return cfg
