@@ -47,7 +47,7 @@ from axlearn_b200.experiments.text.gpt.common import (
 )
 from axlearn_b200.experiments.text.gpt.common import model_config as common_model_config
 
-MODEL_SIZES = ("test", "1B", "3B", "7B", "8B", "70B")
+MODEL_SIZES = ("test", "1B", "3B", "7B", "8B", "70B", "405B")
 
 
 class Version(enum.Enum):
@@ -77,7 +77,15 @@ def get_trainer_kwargs(
     max_seq = MAX_SEQUENCE_LENGTH[version]
     tokens_per_batch = TOKENS_PER_BATCH[version]
     train_batch_size = tokens_per_batch // max_seq
-    max_step = 500_000 if version in (Version.V1, Version.V2) else 983_040  # 2T / 15T tokens
+    # Training budget in tokens (binary "T" = 1024^4): 1T for v1 (1.4T for 70B), 2T for v2, 15T for v3.
+    tera = 1024 ** 4
+    if version == Version.V1:
+        total_tokens = int(1.4 * tera) if model_size == "70B" else tera
+    elif version == Version.V2:
+        total_tokens = 2 * tera
+    else:
+        total_tokens = 15 * tera
+    max_step = total_tokens // tokens_per_batch
     rope_theta = ROPE_THETA[version]
     gqa = version in (Version.V3, Version.V3_TIKTOKEN)
     common = dict(vocab_size=vocab_size, rope_theta=rope_theta, flash_attention=flash_attention)
@@ -107,9 +115,10 @@ def get_trainer_kwargs(
         )
     elif model_size == "7B":
         kw = dict(
+            # The feed-forward width stays 8/3 x 4096 rounded up to 256 = 11008 in every version
+            # (only the "8B" size of the tiktoken variant widens it to 3.5 x).
             model_kwargs=dict(num_layers=32, hidden_dim=4096, num_heads=32, num_kv_heads=8 if gqa else None,
-                              ffn_dim=scaled_hidden_dim(scale=3.5, round_up_to_multiples_of=256) if gqa else None,
-                              shared_lm_head=True, **common),
+                              ffn_dim=None, shared_lm_head=True, **common),
             learner_kwargs=dict(peak_lr=3e-4, weight_decay=0.1),
             max_sequence_length=max_seq, train_batch_size=train_batch_size, max_step=max_step,
             mesh_shape=mesh_shape_from_axes(data=-1, fsdp=8),
@@ -143,6 +152,14 @@ def get_trainer_kwargs(
                 ("gpu-(a4-highgpu-8g|b200)-8",
                  MeshShapeModifier.default_config().set(mesh_shape=mesh_shape_from_axes(fsdp=4, model=2))),
             ),
+        )
+    elif model_size == "405B":
+        kw = dict(
+            model_kwargs=dict(num_layers=126, hidden_dim=16384, num_heads=128, num_kv_heads=8, ffn_dim=53248,
+                              shared_lm_head=False, **common),
+            learner_kwargs=dict(peak_lr=1.5e-4, weight_decay=0.1),
+            max_sequence_length=max_seq, train_batch_size=train_batch_size, max_step=max_step,
+            mesh_shape=mesh_shape_from_axes(fsdp=-1),
         )
     else:
         raise NotImplementedError(f"Unknown model size {model_size}")
@@ -197,26 +214,44 @@ def model_config(
     return cfg
 
 
+# Which sizes exist in which version (the reference trains no 1B / 3B / 405B on the v1 / v2 recipes
+# and names the 4096-wide tiktoken model 8B).
+SIZES_BY_VERSION = {
+    Version.V1: ("test", "7B", "70B"),
+    Version.V2: ("test", "7B", "70B"),
+    Version.V3: ("test", "1B", "3B", "7B", "70B", "405B"),
+    Version.V3_TIKTOKEN: ("test", "1B", "3B", "8B", "70B", "405B"),
+}
+
+
 def trainer_configs(
     train_input_source: Optional[Callable[..., InstantiableConfig]] = None,
     eval_input_sources: Optional[Callable[..., dict]] = None,
 ) -> dict[str, Callable[[], SpmdTrainer.Config]]:
-    """All named Fuji trainer configs: ``fuji-{size}-v{version}[-flash][-single-host]``."""
+    """All named Fuji trainer configs: ``fuji-{size}-v{version}[-flash][-fp8][-single-host]`` plus
+    ``fuji-golden-run-test-v{version}`` (the test size for a handful of steps, used to pin
+    numerics)."""
     del eval_input_sources
     config_map: dict[str, Callable[[], SpmdTrainer.Config]] = {}
-    for version, model_size, flash in itertools.product(Version, MODEL_SIZES, (False, True)):
-        if model_size == "8B" and version in (Version.V1, Version.V2):
-            continue
+    for version in Version:
         vocab_size = VOCAB_SIZE[version]
-        name = f"fuji-{model_size}-v{version.value}" + ("-flash" if flash else "")
-        config_map[name] = _make(model_size, version, vocab_size, flash, train_input_source)
-        if model_size in ("7B", "8B"):
-            config_map[name + "-single-host"] = _make(
-                model_size, version, vocab_size, flash, train_input_source, single_host=True)
+        for model_size, flash in itertools.product(SIZES_BY_VERSION[version], (False, True)):
+            name = f"fuji-{model_size}-v{version.value}" + ("-flash" if flash else "")
+            config_map[name] = _make(model_size, version, vocab_size, flash, train_input_source)
+            if model_size != "test":
+                config_map[name + "-fp8"] = _make(model_size, version, vocab_size, flash, train_input_source, fp8=True)
+            if model_size in ("1B", "3B", "7B", "8B"):
+                config_map[name + "-single-host"] = _make(
+                    model_size, version, vocab_size, flash, train_input_source, single_host=True)
+                config_map[name + "-fp8-single-host"] = _make(
+                    model_size, version, vocab_size, flash, train_input_source, single_host=True, fp8=True)
+        config_map[f"fuji-golden-run-test-v{version.value}"] = _make(
+            "test", version, vocab_size, False, train_input_source, golden_run=True)
     return config_map
 
 
-def _make(model_size, version, vocab_size, flash, train_input_source, single_host: bool = False):
+def _make(model_size, version, vocab_size, flash, train_input_source, single_host: bool = False, fp8: bool = False,
+          golden_run: bool = False):
     def fn() -> SpmdTrainer.Config:
         kw = get_trainer_kwargs(model_size, vocab_size=vocab_size, version=version, flash_attention=flash)
         mk = dict(kw["model_kwargs"])
@@ -235,6 +270,12 @@ def _make(model_size, version, vocab_size, flash, train_input_source, single_hos
             vocab_size=vocab_size, train_input_source=src, mesh_shape=kw["mesh_shape"],
             mesh_axis_names=MESH_AXIS_NAMES, mesh_rules=kw.get("mesh_rules"),
         )()
+        if fp8:
+            from axlearn_b200.common.trainer_config_modifier import FP8ConfigModifier
+
+            cfg = FP8ConfigModifier.default_config().set(fp8_amax_history_length=128).instantiate()(cfg)
+        if golden_run:
+            cfg.max_step = 5
         return cfg
 
     return fn

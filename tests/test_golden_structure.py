@@ -134,3 +134,124 @@ def test_fuji_initializers_match_reference_listing():
     assert weight_init("decoder/emb/token_emb/weight") == ("fan_out", "normal", 1.0)
     assert weight_init(layer + "feed_forward/linear1_0/weight") == ("fan_in", "normal", 1.0)
     assert weight_init(layer + "self_attention/attention/o_proj/weight") == ("fan_in", "normal", 1.0)
+
+
+def test_fuji_7b_trainer_hyperparameters_match_reference_config_dump():
+    """Scalar settings of ``fuji-7B-v2-flash`` as listed in the reference's golden config dump
+    (``fuji-7B-v2-flash.txt``, ``path: value`` lines)."""
+    cfg = fuji.trainer_configs()["fuji-7B-v2-flash"]()
+    flat = cfg.to_flat_dict(omit_default_values=set())
+    want = {
+        "max_step": 524288,
+        "checkpointer.keep_every_n_steps": 50000,
+        "checkpointer.save_policy.n": 5000,
+        "learner.optimizer.args[0].max_norm": 1,
+        "learner.optimizer.args[1].b1": 0.9,
+        "learner.optimizer.args[1].b2": 0.95,
+        "learner.optimizer.args[1].eps": 1e-8,
+        "learner.optimizer.args[1].learning_rate": 3e-4,
+        "learner.optimizer.args[1].weight_decay": 0.1,
+        "learner.optimizer.args[1].update_schedule.alpha": 0.1,
+        "learner.optimizer.args[1].update_schedule.max_step": 524288,
+        "learner.optimizer.args[1].update_schedule.peak_lr": 1.0,
+        "learner.optimizer.args[1].update_schedule.warmup_steps": 2000,
+        "mesh_axis_names[0]": "pipeline", "mesh_axis_names[3]": "fsdp", "mesh_axis_names[5]": "model",
+        "mesh_shape[1]": -1, "mesh_shape[3]": 8,
+        "model.decoder.dim": 4096,
+        "model.decoder.vocab_size": 32768,
+        "model.decoder.transformer.num_layers": 32,
+        "model.decoder.output_norm.eps": 1e-5,
+        "model.decoder.transformer.layer.feed_forward.norm.eps": 1e-5,
+        "model.decoder.transformer.layer.self_attention.norm.eps": 1e-5,
+        "model.decoder.transformer.layer.self_attention.attention.num_heads": 32,
+        "model.decoder.transformer.layer.self_attention.attention.input_linear.rope_pos_emb_layer.theta": 10000.0,
+    }
+    missing = [k for k in want if k not in flat]
+    assert not missing, missing
+    wrong = {k: (flat[k], v) for k, v in want.items() if flat[k] != v}
+    assert not wrong, wrong
+    import torch
+
+    assert flat["train_dtype"] == torch.bfloat16 and flat["model.dtype"] == torch.float32
+    assert flat["input.global_batch_size"] * flat["input.source_length"] == 4 * 2 ** 20      # 4M tokens per batch
+
+
+@pytest.mark.parametrize("name,want", [
+    ("fuji-70B-v2-flash", dict(max_step=524288, lr=1.5e-4, mesh=(1, 1, 1, -1, 1, 1), dim=8192, heads=64, kv=8, layers=80,
+                               vocab=32768, theta=1e4, seq=4096, ffn=28672, head=True)),
+    ("fuji-7B-v3-flash", dict(max_step=983040, lr=3e-4, mesh=(1, -1, 1, 8, 1, 1), dim=4096, heads=32, kv=8, layers=32,
+                              vocab=131072, theta=5e5, seq=8192, ffn=11008, head=False)),
+    ("fuji-1B-v3-flash", dict(max_step=983040, lr=3e-4, mesh=(1, -1, 1, 8, 1, 1), dim=2048, heads=32, kv=8, layers=16,
+                              vocab=131072, theta=5e5, seq=8192, ffn=8192, head=False)),
+    ("fuji-70B-v3-flash", dict(max_step=983040, lr=1.5e-4, mesh=(1, 1, 1, -1, 1, 1), dim=8192, heads=64, kv=8, layers=80,
+                               vocab=131072, theta=5e5, seq=8192, ffn=28672, head=True)),
+])
+def test_other_fuji_sizes_match_reference_config_dumps(name, want):
+    cfg = fuji.trainer_configs()[name]()
+    flat = cfg.to_flat_dict(omit_default_values=set())
+    att = "model.decoder.transformer.layer.self_attention.attention."
+    assert flat["max_step"] == want["max_step"]
+    assert flat["learner.optimizer.args[1].learning_rate"] == want["lr"]
+    assert flat["learner.optimizer.args[1].weight_decay"] == 0.1
+    assert tuple(flat[f"mesh_shape[{i}]"] for i in range(6)) == want["mesh"]
+    assert flat["model.decoder.dim"] == want["dim"] and flat["model.decoder.vocab_size"] == want["vocab"]
+    assert flat["model.decoder.transformer.num_layers"] == want["layers"]
+    assert flat[att + "num_heads"] == want["heads"]
+    assert flat[att + "input_linear.input_linear.num_kv_heads"] == want["kv"]
+    assert flat[att + "input_linear.rope_pos_emb_layer.theta"] == want["theta"]
+    assert flat["input.source_length"] == want["seq"]
+    shapes = _ours(cfg.model, want["layers"])
+    assert shapes["decoder/transformer/repeat/layer/feed_forward/linear1_0/weight"] == (want["dim"], want["ffn"])
+    assert ("decoder/lm_head/weight" in shapes) == want["head"]
+
+
+REFERENCE_FUJI_CONFIG_NAMES = """
+fuji-1B-v3 fuji-1B-v3-flash fuji-1B-v3-flash-fp8 fuji-1B-v3-flash-fp8-single-host fuji-1B-v3-flash-single-host
+fuji-1B-v3-fp8 fuji-1B-v3-fp8-single-host fuji-1B-v3-single-host fuji-1B-v3-tiktoken fuji-1B-v3-tiktoken-flash
+fuji-1B-v3-tiktoken-flash-fp8 fuji-1B-v3-tiktoken-flash-fp8-single-host fuji-1B-v3-tiktoken-flash-single-host
+fuji-1B-v3-tiktoken-fp8 fuji-1B-v3-tiktoken-fp8-single-host fuji-1B-v3-tiktoken-single-host fuji-3B-v3
+fuji-3B-v3-flash fuji-3B-v3-flash-fp8 fuji-3B-v3-flash-fp8-single-host fuji-3B-v3-flash-single-host fuji-3B-v3-fp8
+fuji-3B-v3-fp8-single-host fuji-3B-v3-single-host fuji-3B-v3-tiktoken fuji-3B-v3-tiktoken-flash
+fuji-3B-v3-tiktoken-flash-fp8 fuji-3B-v3-tiktoken-flash-fp8-single-host fuji-3B-v3-tiktoken-flash-single-host
+fuji-3B-v3-tiktoken-fp8 fuji-3B-v3-tiktoken-fp8-single-host fuji-3B-v3-tiktoken-single-host fuji-405B-v3
+fuji-405B-v3-flash fuji-405B-v3-flash-fp8 fuji-405B-v3-fp8 fuji-405B-v3-tiktoken fuji-405B-v3-tiktoken-flash
+fuji-405B-v3-tiktoken-flash-fp8 fuji-405B-v3-tiktoken-fp8 fuji-70B-v1 fuji-70B-v1-flash fuji-70B-v1-flash-fp8
+fuji-70B-v1-fp8 fuji-70B-v2 fuji-70B-v2-flash fuji-70B-v2-flash-fp8 fuji-70B-v2-fp8 fuji-70B-v3 fuji-70B-v3-flash
+fuji-70B-v3-flash-fp8 fuji-70B-v3-fp8 fuji-70B-v3-tiktoken fuji-70B-v3-tiktoken-flash fuji-70B-v3-tiktoken-flash-fp8
+fuji-70B-v3-tiktoken-fp8 fuji-7B-v1 fuji-7B-v1-flash fuji-7B-v1-flash-fp8 fuji-7B-v1-flash-fp8-single-host
+fuji-7B-v1-flash-single-host fuji-7B-v1-fp8 fuji-7B-v1-fp8-single-host fuji-7B-v1-single-host fuji-7B-v2
+fuji-7B-v2-flash fuji-7B-v2-flash-fp8 fuji-7B-v2-flash-fp8-single-host fuji-7B-v2-flash-single-host fuji-7B-v2-fp8
+fuji-7B-v2-fp8-single-host fuji-7B-v2-single-host fuji-7B-v3 fuji-7B-v3-flash fuji-7B-v3-flash-fp8
+fuji-7B-v3-flash-fp8-single-host fuji-7B-v3-flash-single-host fuji-7B-v3-fp8 fuji-7B-v3-fp8-single-host
+fuji-7B-v3-single-host fuji-8B-v3-tiktoken fuji-8B-v3-tiktoken-flash fuji-8B-v3-tiktoken-flash-fp8
+fuji-8B-v3-tiktoken-flash-fp8-single-host fuji-8B-v3-tiktoken-flash-single-host fuji-8B-v3-tiktoken-fp8
+fuji-8B-v3-tiktoken-fp8-single-host fuji-8B-v3-tiktoken-single-host fuji-golden-run-test-v1 fuji-golden-run-test-v2
+fuji-golden-run-test-v3 fuji-golden-run-test-v3-tiktoken fuji-test-v1 fuji-test-v1-flash fuji-test-v2
+fuji-test-v2-flash fuji-test-v3 fuji-test-v3-flash fuji-test-v3-tiktoken fuji-test-v3-tiktoken-flash
+""".split()
+
+
+def test_fuji_config_names_are_the_reference_set():
+    assert sorted(fuji.trainer_configs()) == sorted(REFERENCE_FUJI_CONFIG_NAMES)
+    assert len(REFERENCE_FUJI_CONFIG_NAMES) == 100
+
+
+@pytest.mark.parametrize("name,want", [
+    ("fuji-3B-v3-flash", dict(max_step=983040, dim=3072, heads=24, kv=8, layers=28, vocab=131072, ffn=8192, seq=8192)),
+    ("fuji-8B-v3-tiktoken-flash", dict(max_step=983040, dim=4096, heads=32, kv=8, layers=32, vocab=128256, ffn=14336, seq=8192)),
+    ("fuji-70B-v1-flash", dict(max_step=367001, dim=8192, heads=64, kv=None, layers=80, vocab=32768, ffn=28672, seq=2048)),
+    ("fuji-7B-v1-flash", dict(max_step=262144, dim=4096, heads=32, kv=None, layers=32, vocab=32768, ffn=11008, seq=2048)),
+    ("fuji-405B-v3-flash", dict(max_step=983040, dim=16384, heads=128, kv=8, layers=126, vocab=131072, ffn=53248, seq=8192)),
+])
+def test_more_fuji_sizes_match_reference_config_dumps(name, want):
+    cfg = fuji.trainer_configs()[name]()
+    flat = cfg.to_flat_dict(omit_default_values=set())
+    att = "model.decoder.transformer.layer.self_attention.attention."
+    assert flat["max_step"] == want["max_step"]
+    assert flat["model.decoder.dim"] == want["dim"] and flat["model.decoder.vocab_size"] == want["vocab"]
+    assert flat["model.decoder.transformer.num_layers"] == want["layers"]
+    assert flat[att + "num_heads"] == want["heads"]
+    assert flat.get(att + "input_linear.input_linear.num_kv_heads") == want["kv"]
+    assert flat["input.source_length"] == want["seq"]
+    shapes = _ours(cfg.model, want["layers"])
+    assert shapes["decoder/transformer/repeat/layer/feed_forward/linear2/weight"] == (want["ffn"], want["dim"])
