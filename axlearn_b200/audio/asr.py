@@ -156,12 +156,13 @@ class CTCDecoderModel(BaseLayer):
         return self.lm_head(x) * (1 - p)[..., None].to(x.dtype)
 
     def forward(self, input_batch: dict):
-        """``target_labels [B, U]`` uses values < 0 (or the blank id) as padding.  Loss = total
-        negative log-likelihood / number of label tokens."""
+        """``target_labels [B, U]``: values < 0 or >= vocab_size are padding.  Loss = total negative
+        log-likelihood / number of label tokens; an utterance with more labels than frames is left
+        out, one whose labels cannot be aligned (repeats without room for blanks) contributes 0."""
         cfg = self._config
         logits = self.predict(input_batch)
         labels = input_batch["target_labels"]
-        live_labels = (labels >= 0) & (labels != cfg.blank_id)
+        live_labels = (labels >= 0) & (labels < cfg.vocab_size)
         label_lengths = live_labels.sum(dim=1)
         frame_lengths = (1 - input_batch["paddings"]).sum(dim=1).long()
         # Compact the live labels to the front, as the loss expects.
@@ -171,7 +172,7 @@ class CTCDecoderModel(BaseLayer):
         per_example = F.ctc_loss(log_probs, compact, frame_lengths, label_lengths, blank=cfg.blank_id,
                                  reduction="none", zero_infinity=True)
         # An utterance with fewer frames than labels cannot be aligned: it is left out.
-        valid = (frame_lengths >= label_lengths) & (label_lengths > 0)
+        valid = frame_lengths >= label_lengths
         denom = (label_lengths * valid).sum().clamp_min(1)
         loss = (per_example * valid).sum() / denom
         self.add_summary("loss/ctc", WeightedSummary(loss.detach(), denom))

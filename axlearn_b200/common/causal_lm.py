@@ -287,3 +287,35 @@ def residual_initializer_cfg(num_layers: int, scale: float = 0.02):
                 fan=None, distribution="normal", scale=scale / math.sqrt(2 * num_layers))
         }
     )
+
+
+def gpt_decoder_config(
+    stack_cfg, num_layers: int, hidden_dim: int, num_heads: int, vocab_size: int, max_position_embeddings: int,
+    activation_function: str = "nn.relu", layer_norm_epsilon: float = 1e-8, dropout_rate: float = 0.0,
+    layer_remat=None,
+):
+    """A GPT-2-style decoder config (reference: axlearn/common/causal_lm.py:870-940): learned
+    absolute positions, pre-norm LayerNorm, separate biased q / k / v projections, a 4x
+    feed-forward with ``activation_function``, residual-scaled initialisation of the two output
+    projections, tied input / output embeddings."""
+    from axlearn_b200.common.attention import TransformerLayer
+    from axlearn_b200.common.decoder import Decoder
+    from axlearn_b200.common.embedding import LearnedPositionalEmbedding, TransformerTextEmbeddings
+    from axlearn_b200.common.layers import LayerNorm
+
+    layer_cfg = TransformerLayer.default_config()
+    layer_cfg.feed_forward.activation = activation_function
+    layer_cfg.feed_forward.norm = LayerNorm.default_config().set(eps=layer_norm_epsilon)
+    layer_cfg.feed_forward.hidden_dim = 4 * hidden_dim
+    layer_cfg.self_attention.norm = LayerNorm.default_config().set(eps=layer_norm_epsilon)
+    layer_cfg.self_attention.attention.causal = True
+    layer_cfg.self_attention.attention.num_heads = num_heads
+    layer_cfg.self_attention.attention.output_linear.param_init = residual_initializer_cfg(num_layers=num_layers)
+    layer_cfg.feed_forward.linear2.param_init = residual_initializer_cfg(num_layers=num_layers)
+    layer_cfg.remat_spec = layer_remat
+    transformer_cfg = stack_cfg.clone().set(num_layers=num_layers, layer=layer_cfg)
+    return Decoder.default_config().set(
+        transformer=transformer_cfg, dim=hidden_dim, vocab_size=vocab_size,
+        emb=TransformerTextEmbeddings.default_config().set(
+            pos_emb=LearnedPositionalEmbedding.default_config().set(shape=(max_position_embeddings,))),
+        output_norm=LayerNorm.default_config().set(eps=layer_norm_epsilon), dropout_rate=dropout_rate)
