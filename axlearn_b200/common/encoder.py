@@ -97,35 +97,103 @@ class CausalEncoder(Encoder):
 # ------------------------------------------------------------------------------------------
 
 
-class BertLMHead(BaseLayer):
-    """transform (dense + activation + norm) then logits through the tied token embedding plus
-    an output bias."""
+class NonLinear(BaseLayer):
+    """``norm(activation(linear(x)))`` (children ``linear`` and ``norm``)."""
 
     @config_class
     class Config(BaseLayer.Config):
         input_dim: Required[int] = REQUIRED
-        vocab_size: Required[int] = REQUIRED
+        output_dim: Optional[int] = None
+        linear: InstantiableConfig = Linear.default_config()
         activation: str = "nn.gelu"
         norm: InstantiableConfig = LayerNorm.default_config()
 
     def __init__(self, cfg, *, parent=None):
         super().__init__(cfg, parent=parent)
-        self._add_child("transform", Linear.default_config().set(input_dim=cfg.input_dim, output_dim=cfg.input_dim))
-        self._add_child("norm", cfg.norm.clone(input_dim=cfg.input_dim))
+        out = cfg.output_dim or cfg.input_dim
+        self._add_child("linear", cfg.linear.clone(input_dim=cfg.input_dim, output_dim=out))
+        self._add_child("norm", cfg.norm.clone(input_dim=out))
+
+    def forward(self, x: Tensor) -> Tensor:
+        return self.norm(get_activation_fn(self._config.activation)(self.linear(x)))
+
+
+class BertLMHead(BaseLayer):
+    """Masked-LM head (reference: axlearn/common/bert.py ``BertLMHead``): ``transform`` (dense +
+    activation + norm), logits through the tied token embedding plus ``output_bias``; the loss
+    ignores positions whose target equals ``ignored_target_id``."""
+
+    @config_class
+    class Config(BaseLayer.Config):
+        input_dim: Required[int] = REQUIRED
+        num_classes: Required[int] = REQUIRED          # = vocabulary size
+        transform: InstantiableConfig = NonLinear.default_config()
+        ignored_target_id: int = 0
+
+    def __init__(self, cfg, *, parent=None):
+        super().__init__(cfg, parent=parent)
+        self._add_child("transform", cfg.transform.clone(input_dim=cfg.input_dim))
 
     def _create_layer_parameter_specs(self):
-        return {"output_bias": ParameterSpec(shape=(self._config.vocab_size,), mesh_axes=(None,),
+        return {"output_bias": ParameterSpec(shape=(self._config.num_classes,), mesh_axes=(None,),
                                              initializer=gaussian_initializer(0.0))}
 
-    def forward(self, x: Tensor, *, attend) -> Tensor:
-        h = self.norm(get_activation_fn(self._config.activation)(self.transform(x)))
-        return attend(h) + self.parameters["output_bias"].to(h.dtype)
+    def forward(self, *, sequence_output: Tensor, attend, **unused) -> dict:
+        h = self.transform(sequence_output)
+        return {"logits": attend(h) + self.parameters["output_bias"].to(h.dtype)}
+
+    def loss(self, *, logits: Tensor, target_labels: Tensor):
+        live = target_labels != self._config.ignored_target_id
+        return ops.reference.cross_entropy(logits, target_labels, live_targets=live)
+
+
+class BertPooler(BaseLayer):
+    """``tanh(linear(first token))`` with dropout."""
+
+    @config_class
+    class Config(BaseLayer.Config):
+        input_dim: Required[int] = REQUIRED
+        linear: InstantiableConfig = Linear.default_config()
+        dropout: InstantiableConfig = Dropout.default_config()
+
+    def __init__(self, cfg, *, parent=None):
+        super().__init__(cfg, parent=parent)
+        self._add_child("linear", cfg.linear.clone(input_dim=cfg.input_dim, output_dim=cfg.input_dim))
+        self._add_child("dropout", cfg.dropout)
+
+    def forward(self, x: Tensor) -> Tensor:
+        return self.dropout(torch.tanh(self.linear(x[:, 0])))
+
+
+class BertSequenceClassificationHead(BaseLayer):
+    """``pooler`` + ``output`` projection to ``num_classes`` (reference: axlearn/common/bert.py
+    ``BertSequenceClassificationHead``); cross-entropy over ``target_labels [B]``."""
+
+    @config_class
+    class Config(BaseLayer.Config):
+        input_dim: Required[int] = REQUIRED
+        num_classes: Required[int] = REQUIRED
+        pooler: InstantiableConfig = BertPooler.default_config()
+        output: InstantiableConfig = Linear.default_config()
+
+    def __init__(self, cfg, *, parent=None):
+        super().__init__(cfg, parent=parent)
+        self._add_child("pooler", cfg.pooler.clone(input_dim=cfg.input_dim))
+        self._add_child("output", cfg.output.clone(input_dim=cfg.input_dim, output_dim=cfg.num_classes))
+
+    def forward(self, *, sequence_output: Tensor, **unused) -> dict:
+        pooled = self.pooler(sequence_output)
+        return {"pooled_output": pooled, "logits": self.output(pooled)}
+
+    def loss(self, *, logits: Tensor, target_labels: Tensor):
+        return ops.reference.cross_entropy(logits[:, None], target_labels.reshape(-1)[:, None])
 
 
 class BertModel(BaseModel):
-    """Masked-LM pre-training model: ``forward`` takes ``input_ids`` (with ``[MASK]`` already
-    applied), ``target_labels`` (``ignore_target_label`` where not masked) and returns the MLM
-    loss; ``predict`` also returns the pooled ``[CLS]`` representation."""
+    """``encoder`` + ``head`` (reference: axlearn/common/bert.py ``BertModel``): with the default
+    ``BertLMHead`` a masked-LM model (``input_ids`` with ``[MASK]`` applied, ``target_labels`` equal
+    to ``ignored_target_id`` where not masked); with ``BertSequenceClassificationHead`` a sequence
+    classifier.  ``predict`` returns ``sequence_output`` and the head's outputs."""
 
     @config_class
     class Config(BaseModel.Config):
@@ -133,39 +201,77 @@ class BertModel(BaseModel):
         dim: Required[int] = REQUIRED
         encoder: InstantiableConfig = Encoder.default_config()
         head: InstantiableConfig = BertLMHead.default_config()
-        ignore_target_label: int = 0
-        num_classes: Optional[int] = None    # adds a sequence-classification head on the pooled output
 
     def __init__(self, cfg, *, parent=None):
         super().__init__(cfg, parent=parent)
         self._add_child("encoder", cfg.encoder.clone(dim=cfg.dim, vocab_size=cfg.vocab_size))
-        self._add_child("head", cfg.head.clone(input_dim=cfg.dim, vocab_size=cfg.vocab_size))
-        self._add_child("pooler", Linear.default_config().set(input_dim=cfg.dim, output_dim=cfg.dim))
-        if cfg.num_classes:
-            self._add_child("classifier", Linear.default_config().set(input_dim=cfg.dim, output_dim=cfg.num_classes))
+        head = cfg.head.clone(input_dim=cfg.dim)
+        if head.klass is BertLMHead:
+            head.num_classes = cfg.vocab_size
+        self._add_child("head", head)
 
     def predict(self, input_batch: dict) -> dict:
         x = self.encoder(input_batch["input_ids"], token_type_ids=input_batch.get("token_type_ids"))
-        pooled = torch.tanh(self.pooler(x[:, 0]))
-        out = {"sequence_output": x, "pooled_output": pooled,
-               "logits": self.head(x, attend=self.encoder.attend)}
-        if "classifier" in self._children:
-            out["class_logits"] = self.classifier(pooled)
-        return out
+        return {"sequence_output": x, **self.head(sequence_output=x, attend=self.encoder.attend)}
 
     def forward(self, input_batch: dict, return_aux: bool = False):
-        cfg = self._config
         out = self.predict(input_batch)
-        labels = input_batch["target_labels"]
-        live = labels != cfg.ignore_target_label
-        loss, aux = ops.reference.cross_entropy(out["logits"], labels, live_targets=live)
-        self.add_summary("mlm_loss", loss.detach())
-        self.add_summary("mlm_accuracy", aux["accuracy"].detach())
-        if "class_logits" in out and "class_labels" in input_batch:
-            cls_loss, _ = ops.reference.cross_entropy(out["class_logits"][:, None], input_batch["class_labels"][:, None])
-            self.add_summary("class_loss", cls_loss.detach())
-            loss = loss + cls_loss
+        loss, aux = self.head.loss(logits=out["logits"], target_labels=input_batch["target_labels"])
+        self.add_summary("loss", loss.detach())
+        self.add_summary("accuracy", aux["accuracy"].detach())
         return loss, ({**out, **aux} if return_aux else {})
+
+
+def bert_embedding_config(*, max_position_embeddings: Optional[int] = 512, layer_norm_epsilon: Optional[float] = None,
+                          type_vocab_size: Optional[int] = None):
+    """token + (learned position) + (token type) embeddings followed by LayerNorm."""
+    from axlearn_b200.common.layers import Embedding
+
+    norm = LayerNorm.default_config()
+    if layer_norm_epsilon is not None:
+        norm.eps = layer_norm_epsilon
+    cfg = TransformerTextEmbeddings.default_config().set(norm=norm)
+    if max_position_embeddings is not None:
+        cfg.pos_emb = LearnedPositionalEmbedding.default_config().set(shape=(max_position_embeddings,))
+    if type_vocab_size is not None:
+        cfg.type_emb = Embedding.default_config().set(num_embeddings=type_vocab_size)
+    return cfg
+
+
+def bert_transformer_config(*, num_layers: int = 12, num_heads: int = 12, layer_norm_epsilon: float = 1e-12,
+                            base_cfg: Optional[InstantiableConfig] = None):
+    """Post-norm layers with a 4x GELU feed-forward."""
+    from axlearn_b200.common.attention import scaled_hidden_dim
+
+    base_cfg = base_cfg.clone() if base_cfg is not None else StackedTransformerLayer.default_config()
+    layer_cfg = TransformerLayer.default_config()
+    layer_cfg.feed_forward.set(activation="nn.gelu", hidden_dim=scaled_hidden_dim(4), structure="postnorm")
+    layer_cfg.feed_forward.norm.eps = layer_norm_epsilon
+    layer_cfg.self_attention.norm.eps = layer_norm_epsilon
+    layer_cfg.self_attention.attention.num_heads = num_heads
+    layer_cfg.self_attention.structure = "postnorm"
+    return base_cfg.set(num_layers=num_layers, layer=layer_cfg)
+
+
+def bert_model_config(*, vocab_size: int, hidden_dim: int = 768, num_layers: int = 12, num_heads: int = 12,
+                      max_position_embeddings: int = 512, type_vocab_size: Optional[int] = 2,
+                      layer_norm_epsilon: float = 1e-12, dropout_rate: float = 0.0,
+                      head_cfg: Optional[InstantiableConfig] = None) -> "BertModel.Config":
+    """BERT-base by default (reference: axlearn/common/bert.py ``bert_model_config``)."""
+    from axlearn_b200.common.layers import set_dropout_rate_recursively
+
+    encoder = Encoder.default_config().set(
+        pad_token_id=0,
+        emb=bert_embedding_config(max_position_embeddings=max_position_embeddings,
+                                  layer_norm_epsilon=layer_norm_epsilon, type_vocab_size=type_vocab_size),
+        transformer=bert_transformer_config(num_layers=num_layers, num_heads=num_heads,
+                                            layer_norm_epsilon=layer_norm_epsilon))
+    head = head_cfg or BertLMHead.default_config()
+    if head.klass is BertLMHead:
+        head.transform.norm.eps = layer_norm_epsilon
+    cfg = BertModel.default_config().set(vocab_size=vocab_size, dim=hidden_dim, encoder=encoder, head=head)
+    set_dropout_rate_recursively(cfg, dropout_rate)
+    return cfg
 
 
 # ------------------------------------------------------------------------------------------

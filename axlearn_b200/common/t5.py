@@ -18,7 +18,6 @@ import torch
 from axlearn_b200.common.base_layer import BaseLayer, ParameterSpec
 from axlearn_b200.common.config import REQUIRED, InstantiableConfig, Required, config_class
 from axlearn_b200.common.encoder import NEG_INF, Encoder, _padding_bias
-from axlearn_b200.common.param_init import gaussian_initializer
 
 Tensor = torch.Tensor
 
@@ -44,17 +43,24 @@ def t5_relative_position_bucket(relative_position: Tensor, *, bidirectional: boo
 
 
 class T5RelativePositionalEmbedding(BaseLayer):
+    """Per-head logit bias by bucketed relative position (child ``emb``: an embedding table
+    ``[num_buckets, dim]`` with ``dim`` = number of heads)."""
+
     @config_class
     class Config(BaseLayer.Config):
-        num_heads: Required[int] = REQUIRED
+        dim: Required[int] = REQUIRED          # number of attention heads
         num_buckets: int = 32
         max_distance: int = 128
         bidirectional: bool = True
 
-    def _create_layer_parameter_specs(self):
-        cfg = self._config
-        return {"weight": ParameterSpec(shape=(cfg.num_buckets, cfg.num_heads), mesh_axes=(None, "model"),
-                                        initializer=gaussian_initializer(1.0))}
+    def __init__(self, cfg, *, parent=None):
+        super().__init__(cfg, parent=parent)
+        from axlearn_b200.common.layers import Embedding
+        from axlearn_b200.common.param_init import DefaultInitializer, WeightInitializer
+
+        init = DefaultInitializer.default_config().set(init_by_param_name={
+            ".*weight$": WeightInitializer.default_config().set(fan="fan_avg", distribution="uniform", scale=1.0)})
+        self._add_child("emb", Embedding.default_config().set(num_embeddings=cfg.num_buckets, dim=cfg.dim, param_init=init))
 
     def forward(self, query_len: int, key_len: Optional[int] = None, *, device=None) -> Tensor:
         """``[1, num_heads, query_len, key_len]`` additive logit biases."""
@@ -64,24 +70,85 @@ class T5RelativePositionalEmbedding(BaseLayer):
         k = torch.arange(key_len, device=device)[None, :]
         buckets = t5_relative_position_bucket(k - q, bidirectional=cfg.bidirectional, num_buckets=cfg.num_buckets,
                                               max_distance=cfg.max_distance)
-        bias = self.parameters["weight"][buckets.to(self.parameters["weight"].device)]     # [T, S, N]
+        bias = self.emb(buckets)                                                           # [T, S, N]
         return bias.permute(2, 0, 1)[None]
 
 
+class EncoderOutputLayer(BaseLayer):
+    """Final norm + dropout of the encoder (children ``norm`` and ``dropout``)."""
+
+    @config_class
+    class Config(BaseLayer.Config):
+        input_dim: Required[int] = REQUIRED
+        norm: InstantiableConfig = None
+        dropout: InstantiableConfig = None
+
+    @classmethod
+    def default_config(cls):
+        from axlearn_b200.common.layers import Dropout, RMSNorm
+
+        cfg = super().default_config()
+        cfg.norm = RMSNorm.default_config()
+        cfg.dropout = Dropout.default_config()
+        return cfg
+
+    def __init__(self, cfg, *, parent=None):
+        super().__init__(cfg, parent=parent)
+        self._add_child("norm", cfg.norm.clone(input_dim=cfg.input_dim))
+        self._add_child("dropout", cfg.dropout)
+
+    def forward(self, x: Tensor) -> Tensor:
+        return self.dropout(self.norm(x))
+
+
+def t5_transformer_stack_config(arch: str = "t5-v1-1", hidden_dim=None, base_cfg=None):
+    """Pre-norm layers without biases; feed-forward by architecture: ``t5-v1-1`` gated GELU of
+    width 8/3, ``t5-v1`` ReLU of width 4, ``t5-ul2`` gated SiLU of width 8/3."""
+    from axlearn_b200.common.attention import StackedTransformerLayer, scaled_hidden_dim
+    from axlearn_b200.common.layers import set_bias_recursively
+
+    cfg = base_cfg or StackedTransformerLayer.default_config()
+    cfg.layer.feed_forward.set(structure="prenorm")
+    if arch == "t5-v1-1":
+        cfg.layer.feed_forward.set(activation=("nn.gelu", "linear"), hidden_dim=scaled_hidden_dim(8.0 / 3))
+    elif arch == "t5-v1":
+        cfg.layer.feed_forward.set(activation="nn.relu", hidden_dim=scaled_hidden_dim(4))
+    elif arch == "t5-ul2":
+        cfg.layer.feed_forward.set(activation=("nn.silu", "linear"), hidden_dim=scaled_hidden_dim(8.0 / 3))
+    else:
+        raise ValueError(f"Unsupported arch {arch}.")
+    if hidden_dim is not None:
+        cfg.layer.feed_forward.set(hidden_dim=hidden_dim)
+    set_bias_recursively(cfg, False)
+    return cfg
+
+
 class T5Encoder(Encoder):
-    """``Encoder`` whose self-attention logits get the shared relative position bias.  With
-    ``causal=True`` it is the decoder-side self-attention stack (one-sided buckets + causal mask)."""
+    """``Encoder`` whose self-attention logits get the shared relative position bias (reference:
+    axlearn/common/t5.py ``T5Encoder``).  With ``causal=True`` it is a decoder-side self-attention
+    stack (one-sided buckets + causal mask)."""
 
     @config_class
     class Config(Encoder.Config):
         relative_pos_emb: InstantiableConfig = T5RelativePositionalEmbedding.default_config()
-        num_heads: Required[int] = REQUIRED
         causal: bool = False
+
+    @classmethod
+    def default_config(cls):
+        from axlearn_b200.common.embedding import TransformerTextEmbeddings
+        from axlearn_b200.common.layers import RMSNorm, set_norm_recursively
+
+        cfg = super().default_config()
+        cfg.emb = TransformerTextEmbeddings.default_config().set(pos_emb=None)
+        cfg.transformer = t5_transformer_stack_config()
+        cfg.output = EncoderOutputLayer.default_config()
+        cfg.pad_token_id = 0
+        set_norm_recursively(cfg, RMSNorm.default_config())
+        return cfg
 
     def __init__(self, cfg, *, parent=None):
         super().__init__(cfg, parent=parent)
-        self._add_child("relative_pos_emb", cfg.relative_pos_emb.clone(
-            num_heads=cfg.num_heads, bidirectional=not cfg.causal))
+        self._add_child("relative_pos_emb", cfg.relative_pos_emb.clone(bidirectional=not cfg.causal))
 
     def forward(self, input_ids: Tensor, **kwargs) -> Tensor:
         cfg = self._config
@@ -99,24 +166,22 @@ class T5Encoder(Encoder):
         return self.output_dropout(x)
 
 
-def t5_encoder_config(*, vocab_size: int, dim: int, num_layers: int, num_heads: int, ffn_dim: Optional[int] = None,
-                      causal: bool = False, dropout_rate: float = 0.0) -> T5Encoder.Config:
-    """T5 v1.1 block structure: RMSNorm pre-norm, gated-GELU feed-forward, no biases, unscaled
-    attention logits, no absolute position embeddings."""
-    from axlearn_b200.common.attention import StackedTransformerLayer, constant_scale_fn
-    from axlearn_b200.common.config import config_for_function
-    from axlearn_b200.common.embedding import TransformerTextEmbeddings
+def t5_encoder_config(*, vocab_size: int, dim: int, num_layers: int, num_attention_heads: int,
+                      ffn_dim: Optional[int] = None, arch: str = "t5-v1-1", causal: bool = False,
+                      dropout_rate: float = 0.0, base_cfg: Optional[InstantiableConfig] = None) -> "T5Encoder.Config":
+    """RMSNorm pre-norm layers, no biases, no absolute positions, shared relative position bias.
+    (As in the reference the attention keeps its ``1 / sqrt(head_dim)`` query scale; converters
+    from T5X checkpoints fold the difference into the query weights.)"""
     from axlearn_b200.common.layers import RMSNorm, set_bias_recursively, set_dropout_rate_recursively, set_norm_recursively
 
-    cfg = T5Encoder.default_config().set(vocab_size=vocab_size, dim=dim, num_heads=num_heads, causal=causal)
-    cfg.emb = TransformerTextEmbeddings.default_config().set(pos_emb=None)
-    cfg.transformer = StackedTransformerLayer.default_config().set(num_layers=num_layers)
-    layer = cfg.transformer.layer
-    layer.self_attention.attention.num_heads = num_heads
-    layer.self_attention.attention.query_scale.scale_factor = config_for_function(constant_scale_fn).set(value=1.0)
-    layer.feed_forward.set(hidden_dim=ffn_dim or 4 * dim, activation=("nn.gelu", "linear"))
-    cfg.output = RMSNorm.default_config().set(eps=1e-6)
-    set_norm_recursively(cfg, RMSNorm.default_config().set(eps=1e-6))
+    cfg = base_cfg.clone() if base_cfg is not None else T5Encoder.default_config()
+    cfg.set(vocab_size=vocab_size, dim=dim, causal=causal)
+    cfg.transformer = t5_transformer_stack_config(arch, hidden_dim=ffn_dim, base_cfg=cfg.transformer)
+    cfg.relative_pos_emb.dim = num_attention_heads
+    cfg.transformer.set(num_layers=num_layers)
+    cfg.transformer.layer.self_attention.attention.num_heads = num_attention_heads
     set_bias_recursively(cfg, False)
-    set_dropout_rate_recursively(cfg, dropout_rate)
+    set_norm_recursively(cfg, RMSNorm.default_config())
+    if dropout_rate:
+        set_dropout_rate_recursively(cfg, dropout_rate)
     return cfg

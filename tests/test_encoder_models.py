@@ -63,20 +63,35 @@ def test_causal_encoder_has_no_lookahead():
 
 
 def test_bert_mlm_learns():
-    cfg = encoder.BertModel.default_config().set(name="bert", vocab_size=40, dim=16, num_classes=3)
+    cfg = encoder.BertModel.default_config().set(name="bert", vocab_size=40, dim=16)
     cfg.encoder.set(emb=_emb(), transformer=_stack(16))
     model = cfg.instantiate(parent=None)
     params = model.initialize_parameters_recursively(prng.PRNGKey(0))
+    assert set(params["head"]) == {"transform", "output_bias"} and set(params["head"]["transform"]) == {"linear", "norm"}
     ids = torch.randint(4, 40, (4, 8))
     labels = torch.zeros_like(ids)
     labels[:, 2] = ids[:, 2]
     masked = ids.clone()
     masked[:, 2] = 3
-    batch = {"input_ids": masked, "target_labels": labels, "class_labels": torch.tensor([0, 1, 2, 1])}
+    batch = {"input_ids": masked, "target_labels": labels}
     losses = _sgd_steps(model, params, batch)
     assert losses[-1] < 0.6 * losses[0]
     out, _ = functional(model, None, params, dict(input_batch=batch), is_training=False, method="predict")
-    assert out["logits"].shape == (4, 8, 40) and out["pooled_output"].shape == (4, 16) and out["class_logits"].shape == (4, 3)
+    assert out["logits"].shape == (4, 8, 40) and out["sequence_output"].shape == (4, 8, 16)
+
+
+def test_bert_sequence_classification_learns():
+    cfg = encoder.BertModel.default_config().set(
+        name="bert", vocab_size=40, dim=16, head=encoder.BertSequenceClassificationHead.default_config().set(num_classes=3))
+    cfg.encoder.set(emb=_emb(), transformer=_stack(16))
+    model = cfg.instantiate(parent=None)
+    params = model.initialize_parameters_recursively(prng.PRNGKey(0))
+    assert set(params["head"]) == {"pooler", "output"}
+    batch = {"input_ids": torch.randint(4, 40, (4, 8)), "target_labels": torch.tensor([0, 1, 2, 1])}
+    losses = _sgd_steps(model, params, batch)
+    assert losses[-1] < 0.6 * losses[0]
+    out, _ = functional(model, None, params, dict(input_batch=batch), is_training=False, method="predict")
+    assert out["logits"].shape == (4, 3) and out["pooled_output"].shape == (4, 16)
 
 
 def test_encoder_decoder_learns_to_copy():

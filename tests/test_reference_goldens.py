@@ -128,3 +128,58 @@ def test_bert_embeddings(golden):
     batch = {"inputs": ids, "token_type_ids": torch.zeros_like(ids), "positions": None}
     out, _ = functional(layer, prng.PRNGKey(0), g["params"], dict(input_batch=batch), is_training=False)
     torch.testing.assert_close(out, g["outputs"]["hidden_states"], rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("case", ["bert_mlm", "bert_mlm_padded"])
+def test_bert_masked_lm(golden, case):
+    """BERT (post-norm encoder + MLM head) with the reference's parameter tree reproduces the
+    hidden states, logits and loss recorded from Hugging Face's ``BertForMaskedLM``."""
+    from axlearn_b200.common import encoder
+    from axlearn_b200.common.utils import flatten_items
+
+    g = _tree(golden, case + "/")
+    cfg = encoder.bert_model_config(vocab_size=24, hidden_dim=16, num_layers=2, num_heads=4, max_position_embeddings=20,
+                                    type_vocab_size=2, layer_norm_epsilon=1e-12).set(name="bert")
+    cfg.head.ignored_target_id = -100          # Hugging Face's convention, as in the reference's test
+    model = cfg.instantiate(parent=None)
+    init = model.initialize_parameters_recursively(prng.PRNGKey(0), device="cpu")
+    assert {p: tuple(t.shape) for p, t in flatten_items(init)} == {p: tuple(t.shape) for p, t in flatten_items(g["params"])}
+    batch = {k: g["inputs"][k].long() for k in ("input_ids", "token_type_ids", "target_labels")}
+    (loss, aux), _ = functional(model, prng.PRNGKey(1), g["params"], dict(input_batch=batch, return_aux=True), is_training=False)
+    live = (batch["input_ids"] != 0)[..., None]
+    torch.testing.assert_close(aux["sequence_output"] * live, g["outputs"]["hidden_states_last"] * live, rtol=2e-4, atol=2e-5)
+    torch.testing.assert_close(aux["logits"] * live, g["outputs"]["logits"] * live, rtol=2e-4, atol=2e-5)
+    torch.testing.assert_close(loss.double(), g["outputs"]["loss"].double(), rtol=1e-4, atol=1e-5)
+
+
+def test_hf_bert_encoder(golden):
+    from axlearn_b200.common import encoder
+
+    g = _tree(golden, "hf_encoder/")
+    cfg = encoder.Encoder.default_config().set(
+        name="enc", vocab_size=24, dim=12, pad_token_id=0,
+        emb=encoder.bert_embedding_config(max_position_embeddings=11, layer_norm_epsilon=1e-12, type_vocab_size=1),
+        transformer=encoder.bert_transformer_config(num_layers=2, num_heads=4, layer_norm_epsilon=1e-12))
+    layer = cfg.instantiate(parent=None)
+    ids = g["inputs"]["input_ids"].long()
+    out, _ = functional(layer, prng.PRNGKey(1), g["params"]["encoder"], dict(input_ids=ids, token_type_ids=torch.zeros_like(ids)),
+                        is_training=False)
+    live = (ids != 0)[..., None]
+    torch.testing.assert_close(out * live, g["outputs"]["last_hidden_state"] * live, rtol=2e-4, atol=2e-5)
+
+
+def test_t5_encoder(golden):
+    """The T5 v1.1 encoder with the reference's parameter tree reproduces the hidden states the
+    reference recorded from Hugging Face's ``T5EncoderModel``."""
+    from axlearn_b200.common.t5 import t5_encoder_config
+    from axlearn_b200.common.utils import flatten_items
+
+    g = _tree(golden, "t5_encoder/")
+    cfg = t5_encoder_config(vocab_size=128, dim=12, num_layers=2, num_attention_heads=3).set(name="t5")
+    layer = cfg.instantiate(parent=None)
+    init = layer.initialize_parameters_recursively(prng.PRNGKey(0), device="cpu")
+    assert {p: tuple(t.shape) for p, t in flatten_items(init)} == {p: tuple(t.shape) for p, t in flatten_items(g["params"])}
+    ids = g["inputs"]["input_ids"].long()
+    out, _ = functional(layer, prng.PRNGKey(1), g["params"], dict(input_ids=ids), is_training=False)
+    live = (ids != 0)[..., None]
+    torch.testing.assert_close(out * live, g["outputs"]["last_hidden_state"] * live, rtol=1e-4, atol=5e-6)

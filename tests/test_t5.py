@@ -19,19 +19,19 @@ def test_buckets_match_transformers(bidirectional):
 
 
 def test_relative_bias_layer_and_encoder():
-    layer = T5RelativePositionalEmbedding.default_config().set(name="rel", num_heads=4, num_buckets=8,
+    layer = T5RelativePositionalEmbedding.default_config().set(name="rel", dim=4, num_buckets=8,
                                                                max_distance=16).instantiate(parent=None)
     params = layer.initialize_parameters_recursively(prng.PRNGKey(0), device="cpu")
     bias, _ = functional(layer, prng.PRNGKey(1), params, dict(query_len=5, key_len=7), is_training=False)
     assert bias.shape == (1, 4, 5, 7)
     # Toeplitz: the bias depends on key - query only.
     torch.testing.assert_close(bias[0, :, 1, 2], bias[0, :, 3, 4])
-    cfg = t5_encoder_config(vocab_size=50, dim=32, num_layers=2, num_heads=4, ffn_dim=64).set(name="enc")
+    cfg = t5_encoder_config(vocab_size=50, dim=32, num_layers=2, num_attention_heads=4, ffn_dim=64).set(name="enc")
     enc = cfg.instantiate(parent=None)
     p = enc.initialize_parameters_recursively(prng.PRNGKey(0), device="cpu")
     names = [n for n, _ in flatten_items(p)]
     assert not any(n.endswith("/bias") for n in names)                      # T5 has no biases
-    assert "relative_pos_emb/weight" in names and not any("pos_emb/weight" == n for n in names)
+    assert "relative_pos_emb/emb/weight" in names and "output/norm/scale" in names and not any("pos_emb/weight" == n for n in names)
     ids = torch.randint(1, 50, (2, 9))
     ids[1, 6:] = 0
     out, _ = functional(enc, prng.PRNGKey(1), p, dict(input_ids=ids), is_training=False)
@@ -41,7 +41,7 @@ def test_relative_bias_layer_and_encoder():
     out2, _ = functional(enc, prng.PRNGKey(1), p, dict(input_ids=ids2), is_training=False)
     torch.testing.assert_close(out2[1, :6], out[1, :6])
     # Causal variant: position t does not depend on later tokens.
-    dec = t5_encoder_config(vocab_size=50, dim=32, num_layers=1, num_heads=4, causal=True).set(name="dec").instantiate(parent=None)
+    dec = t5_encoder_config(vocab_size=50, dim=32, num_layers=1, num_attention_heads=4, causal=True).set(name="dec").instantiate(parent=None)
     pd = dec.initialize_parameters_recursively(prng.PRNGKey(0), device="cpu")
     a = torch.randint(1, 50, (1, 8))
     b = a.clone()
