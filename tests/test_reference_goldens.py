@@ -183,3 +183,60 @@ def test_t5_encoder(golden):
     out, _ = functional(layer, prng.PRNGKey(1), g["params"], dict(input_ids=ids), is_training=False)
     live = (ids != 0)[..., None]
     torch.testing.assert_close(out * live, g["outputs"]["last_hidden_state"] * live, rtol=1e-4, atol=5e-6)
+
+
+def test_llama_rope_attention(golden):
+    """Multi-head attention with RoPE on q / k against outputs the reference recorded from the
+    original Llama attention (weights given as ``[out, in]`` matrices)."""
+    from axlearn_b200.common.attention import MultiheadAttention, RoFormerQKVLinear
+
+    g = _tree(golden, "llama_attention/")
+    dim, heads = 32, 4
+    cfg = MultiheadAttention.default_config().set(
+        name="rope", query_dim=dim, key_dim=dim, value_dim=dim, num_heads=heads,
+        input_linear=RoFormerQKVLinear.default_config().set(rotary_value=False))
+    layer = cfg.instantiate(parent=None)
+    state = layer.initialize_parameters_recursively(prng.PRNGKey(0), device="cpu")
+    for name, key in (("q_proj", "wq"), ("k_proj", "wk"), ("v_proj", "wv")):
+        state["i_proj"]["i_proj"][name]["weight"] = g["params"][key].t().reshape(dim, heads, dim // heads).contiguous()
+        if "bias" in state["i_proj"]["i_proj"][name]:
+            state["i_proj"]["i_proj"][name]["bias"].zero_()
+    state["o_proj"]["weight"] = g["params"]["wo"].reshape(dim, heads, dim // heads).contiguous()
+    if "bias" in state["o_proj"]:
+        state["o_proj"]["bias"].zero_()
+    out, _ = functional(layer, prng.PRNGKey(0), state, dict(query=g["inputs"]["x"]), is_training=False)
+    torch.testing.assert_close(out.data, g["outputs"]["data"].reshape(4, 100, -1), rtol=1e-4, atol=1e-5)
+
+
+def test_llama_rope_frequencies(golden):
+    from axlearn_b200.common.attention import RoFormerSinusoidalPositionalEmbedding
+
+    g = _tree(golden, "llama_freqs_1e6/")
+    dim, max_len, theta = int(g["params"]["dim"]), int(g["params"]["max_len"]), float(g["params"]["theta"])
+    layer = RoFormerSinusoidalPositionalEmbedding.default_config().set(name="rope", dim=dim, theta=theta).instantiate(parent=None)
+    table, _ = functional(layer, None, {}, dict(positions=torch.arange(max_len)[None]), is_training=False)
+    sin, cos = table[0].chunk(2, dim=-1)
+    torch.testing.assert_close(cos, g["outputs"]["real"], rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(sin, g["outputs"]["imag"], rtol=1e-4, atol=1e-5)
+
+
+def test_roberta_attention_and_layer(golden):
+    from axlearn_b200.common.attention import TransformerAttentionLayer, TransformerLayer, scaled_hidden_dim
+
+    g = _tree(golden, "roberta_attention/")
+    cfg = TransformerAttentionLayer.default_config().set(name="att", target_dim=16, source_dim=16, structure="postnorm")
+    cfg.attention.set(num_heads=4)
+    layer = cfg.instantiate(parent=None)
+    out, _ = functional(layer, prng.PRNGKey(0), g["params"], dict(target=g["inputs"]["target"]), is_training=True)
+    torch.testing.assert_close(out.data, g["outputs"]["data"], rtol=1e-4, atol=1e-5)
+
+    g = _tree(golden, "roberta_layer/")
+    cfg = TransformerLayer.default_config().set(name="layer", input_dim=16)
+    cfg.self_attention.set(structure="postnorm")
+    cfg.feed_forward.set(structure="postnorm", activation="nn.silu", hidden_dim=scaled_hidden_dim(4))
+    cfg.feed_forward.linear1.set(bias=True)
+    cfg.feed_forward.linear2.set(bias=True)
+    cfg.self_attention.attention.set(num_heads=4)
+    layer = cfg.instantiate(parent=None)
+    out, _ = functional(layer, prng.PRNGKey(0), g["params"], dict(data=g["inputs"]["data"]), is_training=True)
+    torch.testing.assert_close(out.data, g["outputs"]["data"], rtol=1e-4, atol=1e-5)
