@@ -255,3 +255,24 @@ def test_more_fuji_sizes_match_reference_config_dumps(name, want):
     assert flat["input.source_length"] == want["seq"]
     shapes = _ours(cfg.model, want["layers"])
     assert shapes["decoder/transformer/repeat/layer/feed_forward/linear2/weight"] == (want["ffn"], want["dim"])
+
+
+def test_trainer_state_leaf_names_follow_the_reference_checkpoint_layout(tmp_path):
+    """``flatten_items(trainer_state)`` names = the tensor names of a checkpoint.  For
+    ``chain(clip, chain(scale_by_adam, scale_by_schedule, add_decayed_weights, scale_by_schedule,
+    scale))`` the reference stores ``learner/optimizer/1/0/{count,mu/<param>,nu/<param>}``,
+    ``learner/optimizer/1/1/count`` and ``learner/optimizer/1/3/count``; stateless links store
+    nothing (axlearn/common/state_builder_test.py:797-806, axlearn/common/optimizers.py:584-590)."""
+    from axlearn_b200.common import prng
+    from tests.helpers import tiny_fuji_trainer_config
+
+    trainer = tiny_fuji_trainer_config(str(tmp_path), max_step=2, save_every_n_steps=100).instantiate(parent=None)
+    trainer.init(prng.PRNGKey(0))
+    names = [p for p, _ in flatten_items(trainer.trainer_state)]
+    params = [n[len("model/"):] for n in names if n.startswith("model/")]
+    assert "decoder/transformer/repeat/layer/self_attention/attention/i_proj/i_proj/qkv_proj/weight" in params
+    learner = sorted(n for n in names if n.startswith("learner/"))
+    want = sorted(["learner/optimizer/1/0/count", "learner/optimizer/1/1/count", "learner/optimizer/1/3/count"]
+                  + [f"learner/optimizer/1/0/{m}/{p}" for m in ("mu", "nu") for p in params])
+    assert learner == want
+    assert "prng_key" in names and len(names) == len(params) + len(want) + 1
