@@ -40,14 +40,14 @@ MODEL_PRESETS = {
     # feed-forward, per-head RMSNorm on queries and keys, 2 routing groups, capacity factor 2.
     "Switch-Base": dict(num_layers=12, hidden_dim=12 * 128, num_heads=12, num_kv_heads=12, num_experts=128,
                         moe_ffn_dim=4 * 12 * 128, vocab_size=32768, num_groups=2, ffn_layer_types=("dense", "sparse"),
-                        ffn_structure="hybridnorm", qk_norm=True, shared_lm_head=True, rope_theta=1e4),
+                        ffn_structure="hybridnorm", qk_norm=True, shared_lm_head=True, rope_theta=5e5, z_loss_scale=1e-6),
     "Switch-Large": dict(num_layers=24, hidden_dim=16 * 128, num_heads=16, num_kv_heads=16, num_experts=128,
                          moe_ffn_dim=4 * 16 * 128, vocab_size=32768, num_groups=2, ffn_layer_types=("dense", "sparse"),
-                         ffn_structure="hybridnorm", qk_norm=True, shared_lm_head=True, rope_theta=1e4),
+                         ffn_structure="hybridnorm", qk_norm=True, shared_lm_head=True, rope_theta=5e5, z_loss_scale=1e-6),
     "Switch-XXL": dict(num_layers=24, hidden_dim=64 * 128, num_heads=64, num_kv_heads=8, num_experts=64,
                        moe_ffn_dim=int(2.5 * 64 * 128), vocab_size=32768, num_groups=2,
                        ffn_layer_types=("dense", "sparse"), ffn_structure="hybridnorm", qk_norm=True,
-                       shared_lm_head=True, rope_theta=1e4),
+                       shared_lm_head=True, rope_theta=5e5, z_loss_scale=1e-6),
     "Mixtral-8x7B": dict(num_layers=32, hidden_dim=4096, num_heads=32, num_kv_heads=8, num_experts=8,
                          moe_ffn_dim=14336, vocab_size=32768, num_groups=1),
 }
@@ -144,16 +144,29 @@ def trainer_configs() -> dict:
         def fn():
             mk = dict(MODEL_PRESETS[name])
             small = name == "test"
+            switch = name.startswith("Switch")
             max_step = 50 if small else 250_000
-            return get_trainer_config_fn(
-                model_cfg=model_config(scan_chunk=None if small else 8192, **mk),
-                learner_cfg=adamw_decoupled_learner_config(
+            seq = 64 if small else (8192 if switch else 4096)
+            if switch:
+                # The reference's recipe for these sizes: decoupled AdamW at 1e-2 with mup-simple
+                # scaling of the matrix updates (base width 768), decay to 0.5 %, 8M tokens / batch.
+                from axlearn_b200.experiments.text.gpt.common import mup_simple_adam_update_transformation
+
+                learner = adamw_decoupled_learner_config(
+                    peak_lr=0.01, max_step=max_step, weight_decay=1e-4, lr_warmup_steps=5000, alpha=0.005,
+                    adam_update_transformation=mup_simple_adam_update_transformation(768 / mk["hidden_dim"]))
+                batch = 8 * 2 ** 20 // seq
+                mesh = mesh_shape_from_axes(fsdp=-1, expert=16)
+            else:
+                learner = adamw_decoupled_learner_config(
                     peak_lr=3e-4 if not small else 3e-3, max_step=max_step, weight_decay=0.1,
-                    lr_warmup_steps=2 if small else 2000),
-                max_step=max_step, train_batch_size=8 if small else 16,
-                max_sequence_length=64 if small else 4096, vocab_size=mk["vocab_size"],
-                mesh_shape=mesh_shape_from_axes(expert=-1) if not small else mesh_shape_from_axes(),
-                mesh_axis_names=MESH_AXIS_NAMES)()
+                    lr_warmup_steps=2 if small else 2000)
+                batch = 8 if small else 16
+                mesh = mesh_shape_from_axes(expert=-1) if not small else mesh_shape_from_axes()
+            return get_trainer_config_fn(
+                model_cfg=model_config(scan_chunk=None if small else 8192, **mk), learner_cfg=learner,
+                max_step=max_step, train_batch_size=batch, max_sequence_length=seq, vocab_size=mk["vocab_size"],
+                mesh_shape=mesh, mesh_axis_names=MESH_AXIS_NAMES, keep_every_n_steps=5000 if switch else 50_000)()
 
         return fn
 

@@ -276,3 +276,32 @@ def test_trainer_state_leaf_names_follow_the_reference_checkpoint_layout(tmp_pat
                   + [f"learner/optimizer/1/0/{m}/{p}" for m in ("mu", "nu") for p in params])
     assert learner == want
     assert "prng_key" in names and len(names) == len(params) + len(want) + 1
+
+
+def test_envy_switch_base_hyperparameters_match_reference_config_dump():
+    cfg = envy.trainer_configs()["envy-Switch-Base"]()
+    flat = cfg.to_flat_dict(omit_default_values=set())
+    sparse = "model.decoder.transformer.layer.layer[1].feed_forward."
+    want = {
+        "max_step": 250000, "checkpointer.keep_every_n_steps": 5000,
+        "learner.optimizer.args[0].max_norm": 1,
+        "learner.optimizer.args[1].b1": 0.9, "learner.optimizer.args[1].b2": 0.95, "learner.optimizer.args[1].eps": 1e-8,
+        "learner.optimizer.args[1].learning_rate": 0.01, "learner.optimizer.args[1].weight_decay": 1e-4,
+        "learner.optimizer.args[1].update_schedule.alpha": 0.005,
+        "learner.optimizer.args[1].update_schedule.warmup_steps": 5000,
+        "mesh_shape[2]": 16, "mesh_shape[3]": -1,
+        "model.decoder.output_norm.eps": 1e-5,
+        "model.decoder.transformer.layer.layer[0].self_attention.attention.input_linear.rope_pos_emb_layer.theta": 5e5,
+        "model.decoder.transformer.layer.layer[0].self_attention.attention.query_scale.norm.eps": 1e-5,
+        sparse + "gating.train_capacity_factor": 2.0, sparse + "gating.eval_capacity_factor": 2.0,
+        sparse + "load_balance_loss_weight": 0.01, sparse + "router_z_loss_weight": 0.0,
+        sparse + "num_experts": 128, sparse + "num_groups": 2,
+        "model.metrics.metrics['lm'].z_loss_scale": 1e-6,
+        "input.source_length": 8192,
+    }
+    missing = [k for k in want if k not in flat]
+    assert not missing, missing
+    wrong = {k: (flat[k], v) for k, v in want.items() if flat[k] != v}
+    assert not wrong, wrong
+    assert flat["input.global_batch_size"] * flat["input.source_length"] == 8 * 2 ** 20
+    assert "scale_update_per_param" in str(flat["learner.optimizer.args[1].adam_update_transformation.fn"])
