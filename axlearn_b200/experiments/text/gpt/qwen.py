@@ -31,7 +31,8 @@ MODEL_PRESETS = {
 
 def model_config(**kwargs) -> causal_lm.Model.Config:
     defaults = dict(drop_free=True, qk_norm=True, norm_eps=QWEN3_RMS_NORM_EPS, rope_theta=QWEN3_ROPE_THETA,
-                    z_loss_scale=1e-6, shared_lm_head=False, ffn_layer_types=("sparse",), num_groups=1)
+                    z_loss_scale=1e-6, shared_lm_head=False, ffn_layer_types=("sparse",), num_groups=1,
+                    load_balance_loss_weight=1e-3)
     return envy.model_config(**{**defaults, **kwargs})
 
 
@@ -39,8 +40,14 @@ def preset(name: str, **overrides) -> causal_lm.Model.Config:
     return model_config(**{**MODEL_PRESETS[name], **overrides})
 
 
+# (tokens per batch, sequence length) variants of every size, as in the reference.
+CONFIGS = {"30B-A3B": [(8 * 1024 * 1024, 8 * 1024), (16 * 1024 * 1024, 32 * 1024)]}
+
+
 def trainer_configs() -> dict:
-    """``qwen3-{preset}`` trainer configs (synthetic input unless a source is wired)."""
+    """``qwen3-{size}-bs{tokens per batch}m-seq{length}k`` trainer configs plus ``qwen3-test``
+    (synthetic input unless a source is wired).  Learner: decoupled AdamW at 1e-2 decaying to
+    0.5 %, weight decay 1e-4, 5000 warm-up steps."""
     from axlearn_b200.experiments.text.gpt.common import (
         MESH_AXIS_NAMES,
         adamw_decoupled_learner_config,
@@ -48,21 +55,25 @@ def trainer_configs() -> dict:
         mesh_shape_from_axes,
     )
 
-    def make(name):
+    def make(size, tokens_per_batch=None, seq_len=None):
         def fn():
-            mk = dict(MODEL_PRESETS[name])
-            small = name == "test"
+            mk = dict(MODEL_PRESETS[size])
+            small = size == "test"
             max_step = 50 if small else 250_000
             return get_trainer_config_fn(
                 model_cfg=model_config(scan_chunk=None if small else 8192, **mk),
                 learner_cfg=adamw_decoupled_learner_config(
-                    peak_lr=3e-3 if small else 0.01, max_step=max_step, weight_decay=1e-4,
+                    peak_lr=3e-3 if small else 0.01, max_step=max_step, weight_decay=1e-4, alpha=1 / 200.0,
                     lr_warmup_steps=2 if small else 5000),
-                max_step=max_step, train_batch_size=8 if small else 1024,
-                max_sequence_length=64 if small else 4096, vocab_size=mk["vocab_size"],
+                max_step=max_step, train_batch_size=8 if small else tokens_per_batch // seq_len,
+                max_sequence_length=64 if small else seq_len, vocab_size=mk["vocab_size"],
                 mesh_shape=mesh_shape_from_axes() if small else mesh_shape_from_axes(fsdp=8, data=-1),
-                mesh_axis_names=MESH_AXIS_NAMES)()
+                mesh_axis_names=MESH_AXIS_NAMES, keep_every_n_steps=5000, eval_every_n_steps=25_000)()
 
         return fn
 
-    return {f"qwen3-{name}": make(name) for name in MODEL_PRESETS}
+    out = {"qwen3-test": make("test")}
+    for size, variants in CONFIGS.items():
+        for tokens, seq in variants:
+            out[f"qwen3-{size}-bs{tokens // 1024 // 1024}m-seq{seq // 1024}k"] = make(size, tokens, seq)
+    return out

@@ -60,7 +60,7 @@ def test_all_families_list_their_configs():
     names = set()
     for module in (fuji, envy, qwen, honeycrisp, gala):
         names |= set(module.trainer_configs())
-    assert {"envy-Mixtral-8x7B", "qwen3-30B-A3B", "honeycrisp-3B", "gala-1B"} <= names
+    assert {"envy-Mixtral-8x7B", "qwen3-30B-A3B-bs8m-seq8k", "honeycrisp-3B", "gala-1B"} <= names
     assert any(n.startswith("fuji-7B") for n in names)
 
 

@@ -305,3 +305,61 @@ def test_envy_switch_base_hyperparameters_match_reference_config_dump():
     assert not wrong, wrong
     assert flat["input.global_batch_size"] * flat["input.source_length"] == 8 * 2 ** 20
     assert "scale_update_per_param" in str(flat["learner.optimizer.args[1].adam_update_transformation.fn"])
+
+
+QWEN3_30B_A3B = """
+decoder/emb/token_emb/weight 151936,2048
+decoder/transformer/repeat/layer/self_attention/norm/scale
+decoder/transformer/repeat/layer/self_attention/attention/i_proj/i_proj/qkv_proj/weight 2048,40,128
+decoder/transformer/repeat/layer/self_attention/attention/o_proj/weight 2048,32,128
+decoder/transformer/repeat/layer/self_attention/attention/scale_query/norm/scale
+decoder/transformer/repeat/layer/self_attention/attention/scale_key/norm/scale
+decoder/transformer/repeat/layer/feed_forward/gate_weight 2048,128
+decoder/transformer/repeat/layer/feed_forward/wo_weight 128,768,2048
+decoder/transformer/repeat/layer/feed_forward/wi_0_weight 128,2048,768
+decoder/transformer/repeat/layer/feed_forward/wi_1_weight 128,2048,768
+decoder/transformer/repeat/layer/feed_forward/norm/scale
+decoder/output_norm/scale
+decoder/lm_head/weight 151936,2048
+"""
+
+
+def test_qwen3_matches_reference_listing_and_config_dump():
+    from axlearn_b200.experiments.text.gpt import qwen
+
+    cfgs = qwen.trainer_configs()
+    assert {"qwen3-30B-A3B-bs8m-seq8k", "qwen3-30B-A3B-bs16m-seq32k"} <= set(cfgs)
+    cfg = cfgs["qwen3-30B-A3B-bs8m-seq8k"]()
+    ours, want = _ours(cfg.model, 48), _golden(QWEN3_30B_A3B)
+    assert set(ours) == set(want), sorted(set(ours) ^ set(want))
+    for name, shape in want.items():
+        if shape is not None:
+            assert ours[name] == shape, name
+    flat = cfg.to_flat_dict(omit_default_values=set())
+    layer = "model.decoder.transformer.layer."
+    want_cfg = {
+        "max_step": 250000, "learner.optimizer.args[1].learning_rate": 0.01,
+        "learner.optimizer.args[1].update_schedule.alpha": 0.005,
+        "learner.optimizer.args[1].update_schedule.warmup_steps": 5000,
+        "learner.optimizer.args[1].weight_decay": 1e-4,
+        "mesh_shape[1]": -1, "mesh_shape[3]": 8,
+        "model.decoder.output_norm.eps": 1e-6,
+        layer + "feed_forward.gating.num_experts_per_token": 8,
+        layer + "feed_forward.hidden_dim": 768,
+        layer + "feed_forward.load_balance_loss_weight": 0.001,
+        layer + "feed_forward.num_experts": 128,
+        layer + "self_attention.attention.hidden_dim": 4096,
+        layer + "self_attention.attention.input_linear.input_linear.num_kv_heads": 4,
+        layer + "self_attention.attention.input_linear.rope_pos_emb_layer.theta": 1e6,
+        layer + "self_attention.attention.query_scale.norm.eps": 1e-6,
+        layer + "self_attention.attention.num_heads": 32,
+        "model.decoder.transformer.num_layers": 48, "model.decoder.vocab_size": 151936,
+        "model.metrics.metrics['lm'].z_loss_scale": 1e-6,
+        "input.source_length": 8192,
+    }
+    missing = [k for k in want_cfg if k not in flat]
+    assert not missing, missing
+    wrong = {k: (flat[k], v) for k, v in want_cfg.items() if flat[k] != v}
+    assert not wrong, wrong
+    assert "TopKDropFreeGating" in str(flat[layer + "feed_forward.gating.klass"])
+    assert "TransformerFeedForwardDropFreeMoE" in str(flat[layer + "feed_forward.klass"])
