@@ -22,6 +22,8 @@ Tensor = torch.Tensor
 
 
 class ConvBatchNormLayer(BaseLayer):
+    """``norm(conv(x))`` with children ``conv`` and ``norm`` (used for the shortcut projection)."""
+
     @config_class
     class Config(BaseLayer.Config):
         input_dim: Required[int] = REQUIRED
@@ -40,6 +42,14 @@ class ConvBatchNormLayer(BaseLayer):
         return get_activation_fn(self._config.activation)(x) if self._config.activation else x
 
 
+def _conv_cfg(window: int, strides: int) -> Conv2D.Config:
+    return Conv2D.default_config().set(window=(window, window), strides=(strides, strides), padding="SAME", bias=False)
+
+
+def _norm_cfg() -> BatchNorm.Config:
+    return BatchNorm.default_config().set(decay=0.9, eps=1e-5)
+
+
 def _conv_bn(window, strides, activation=None) -> ConvBatchNormLayer.Config:
     cfg = ConvBatchNormLayer.default_config().set(activation=activation)
     cfg.conv.set(window=(window, window), strides=(strides, strides))
@@ -51,7 +61,7 @@ def _max_pool_3x3_s2(x: Tensor) -> Tensor:
 
 
 class StemV0(BaseLayer):
-    """7x7 stride-2 convolution + batch norm + ReLU + 3x3 stride-2 max pool."""
+    """7x7 stride-2 convolution (``conv1``) + batch norm (``norm1``) + ReLU + 3x3 stride-2 max pool."""
 
     @config_class
     class Config(BaseLayer.Config):
@@ -60,14 +70,16 @@ class StemV0(BaseLayer):
 
     def __init__(self, cfg, *, parent=None):
         super().__init__(cfg, parent=parent)
-        self._add_child("conv1", _conv_bn(7, 2, "nn.relu").set(input_dim=cfg.input_dim, output_dim=cfg.hidden_dim))
+        self._add_child("conv1", _conv_cfg(7, 2).set(input_dim=cfg.input_dim, output_dim=cfg.hidden_dim))
+        self._add_child("norm1", _norm_cfg().set(input_dim=cfg.hidden_dim))
 
     def forward(self, x: Tensor) -> Tensor:
-        return _max_pool_3x3_s2(self.conv1(x))
+        return _max_pool_3x3_s2(F.relu(self.norm1(self.conv1(x))))
 
 
 class ResidualBlock(BaseLayer):
-    """Two 3x3 convolutions (ResNet-18 / 34)."""
+    """Two 3x3 convolutions (ResNet-18 / 34): children ``conv1, norm1, conv2, norm2`` and, where the
+    shape changes, ``downsample`` (1x1 convolution + norm on the shortcut)."""
 
     EXPANSION = 1
 
@@ -81,26 +93,34 @@ class ResidualBlock(BaseLayer):
 
     def __init__(self, cfg, *, parent=None):
         super().__init__(cfg, parent=parent)
+        self._num_convs = 0
         self._build_branch()
         if cfg.stride != 1 or cfg.input_dim != cfg.output_dim:
-            self._add_child("shortcut", _conv_bn(1, cfg.stride).set(input_dim=cfg.input_dim, output_dim=cfg.output_dim))
+            self._add_child("downsample", _conv_bn(1, cfg.stride).set(input_dim=cfg.input_dim, output_dim=cfg.output_dim))
         if cfg.squeeze_excitation is not None:
             self._add_child("squeeze_excitation", cfg.squeeze_excitation.clone(input_dim=cfg.output_dim))
         self._add_child("stochastic_depth", cfg.stochastic_depth)
 
+    def _add_conv(self, window: int, stride: int, input_dim: int, output_dim: int) -> None:
+        self._num_convs += 1
+        i = self._num_convs
+        self._add_child(f"conv{i}", _conv_cfg(window, stride).set(input_dim=input_dim, output_dim=output_dim))
+        self._add_child(f"norm{i}", _norm_cfg().set(input_dim=output_dim))
+
     def _build_branch(self):
         cfg = self._config
-        self._add_child("conv1", _conv_bn(3, cfg.stride, "nn.relu").set(input_dim=cfg.input_dim, output_dim=cfg.output_dim))
-        self._add_child("conv2", _conv_bn(3, 1).set(input_dim=cfg.output_dim, output_dim=cfg.output_dim))
-        self._branch = ["conv1", "conv2"]
+        self._add_conv(3, cfg.stride, cfg.input_dim, cfg.output_dim)
+        self._add_conv(3, 1, cfg.output_dim, cfg.output_dim)
 
     def forward(self, x: Tensor) -> Tensor:
         y = x
-        for name in self._branch:
-            y = getattr(self, name)(y)
+        for i in range(1, self._num_convs + 1):
+            y = getattr(self, f"norm{i}")(getattr(self, f"conv{i}")(y))
+            if i < self._num_convs:
+                y = F.relu(y)
         if "squeeze_excitation" in self._children:
             y = self.squeeze_excitation(y)
-        skip = self.shortcut(x) if "shortcut" in self._children else x
+        skip = self.downsample(x) if "downsample" in self._children else x
         return F.relu(skip + self.stochastic_depth(y))
 
 
@@ -112,10 +132,9 @@ class BottleneckBlock(ResidualBlock):
     def _build_branch(self):
         cfg = self._config
         mid = cfg.output_dim // self.EXPANSION
-        self._add_child("conv1", _conv_bn(1, 1, "nn.relu").set(input_dim=cfg.input_dim, output_dim=mid))
-        self._add_child("conv2", _conv_bn(3, cfg.stride, "nn.relu").set(input_dim=mid, output_dim=mid))
-        self._add_child("conv3", _conv_bn(1, 1).set(input_dim=mid, output_dim=cfg.output_dim))
-        self._branch = ["conv1", "conv2", "conv3"]
+        self._add_conv(1, 1, cfg.input_dim, mid)
+        self._add_conv(3, cfg.stride, mid, mid)
+        self._add_conv(1, 1, mid, cfg.output_dim)
 
 
 class ResNetStage(BaseLayer):

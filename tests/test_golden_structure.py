@@ -363,3 +363,111 @@ def test_qwen3_matches_reference_listing_and_config_dump():
     assert not wrong, wrong
     assert "TopKDropFreeGating" in str(flat[layer + "feed_forward.gating.klass"])
     assert "TransformerFeedForwardDropFreeMoE" in str(flat[layer + "feed_forward.klass"])
+
+
+RESNET18_WEIGHTS = """
+backbone/stem/conv1/weight 7,7,3,64
+backbone/stage0/block0/conv1/weight 3,3,64,64
+backbone/stage0/block0/conv2/weight 3,3,64,64
+backbone/stage0/block1/conv1/weight 3,3,64,64
+backbone/stage0/block1/conv2/weight 3,3,64,64
+backbone/stage1/block0/conv1/weight 3,3,64,128
+backbone/stage1/block0/conv2/weight 3,3,128,128
+backbone/stage1/block0/downsample/conv/weight 1,1,64,128
+backbone/stage1/block1/conv1/weight 3,3,128,128
+backbone/stage1/block1/conv2/weight 3,3,128,128
+backbone/stage2/block0/conv1/weight 3,3,128,256
+backbone/stage2/block0/conv2/weight 3,3,256,256
+backbone/stage2/block0/downsample/conv/weight 1,1,128,256
+backbone/stage2/block1/conv1/weight 3,3,256,256
+backbone/stage2/block1/conv2/weight 3,3,256,256
+backbone/stage3/block0/conv1/weight 3,3,256,512
+backbone/stage3/block0/conv2/weight 3,3,512,512
+backbone/stage3/block0/downsample/conv/weight 1,1,256,512
+backbone/stage3/block1/conv1/weight 3,3,512,512
+backbone/stage3/block1/conv2/weight 3,3,512,512
+classifier/weight 512,1000
+classifier/bias
+"""
+
+RESNET50_WEIGHTS = """
+backbone/stem/conv1/weight 7,7,3,64
+backbone/stage0/block0/conv1/weight 1,1,64,64
+backbone/stage0/block0/conv2/weight 3,3,64,64
+backbone/stage0/block0/conv3/weight 1,1,64,256
+backbone/stage0/block0/downsample/conv/weight 1,1,64,256
+backbone/stage0/block1/conv1/weight 1,1,256,64
+backbone/stage0/block1/conv2/weight 3,3,64,64
+backbone/stage0/block1/conv3/weight 1,1,64,256
+backbone/stage0/block2/conv1/weight 1,1,256,64
+backbone/stage0/block2/conv2/weight 3,3,64,64
+backbone/stage0/block2/conv3/weight 1,1,64,256
+backbone/stage1/block0/conv1/weight 1,1,256,128
+backbone/stage1/block0/conv2/weight 3,3,128,128
+backbone/stage1/block0/conv3/weight 1,1,128,512
+backbone/stage1/block0/downsample/conv/weight 1,1,256,512
+backbone/stage1/block1/conv1/weight 1,1,512,128
+backbone/stage1/block1/conv2/weight 3,3,128,128
+backbone/stage1/block1/conv3/weight 1,1,128,512
+backbone/stage1/block2/conv1/weight 1,1,512,128
+backbone/stage1/block2/conv2/weight 3,3,128,128
+backbone/stage1/block2/conv3/weight 1,1,128,512
+backbone/stage1/block3/conv1/weight 1,1,512,128
+backbone/stage1/block3/conv2/weight 3,3,128,128
+backbone/stage1/block3/conv3/weight 1,1,128,512
+backbone/stage2/block0/conv1/weight 1,1,512,256
+backbone/stage2/block0/conv2/weight 3,3,256,256
+backbone/stage2/block0/conv3/weight 1,1,256,1024
+backbone/stage2/block0/downsample/conv/weight 1,1,512,1024
+backbone/stage2/block1/conv1/weight 1,1,1024,256
+backbone/stage2/block1/conv2/weight 3,3,256,256
+backbone/stage2/block1/conv3/weight 1,1,256,1024
+backbone/stage2/block2/conv1/weight 1,1,1024,256
+backbone/stage2/block2/conv2/weight 3,3,256,256
+backbone/stage2/block2/conv3/weight 1,1,256,1024
+backbone/stage2/block3/conv1/weight 1,1,1024,256
+backbone/stage2/block3/conv2/weight 3,3,256,256
+backbone/stage2/block3/conv3/weight 1,1,256,1024
+backbone/stage2/block4/conv1/weight 1,1,1024,256
+backbone/stage2/block4/conv2/weight 3,3,256,256
+backbone/stage2/block4/conv3/weight 1,1,256,1024
+backbone/stage2/block5/conv1/weight 1,1,1024,256
+backbone/stage2/block5/conv2/weight 3,3,256,256
+backbone/stage2/block5/conv3/weight 1,1,256,1024
+backbone/stage3/block0/conv1/weight 1,1,1024,512
+backbone/stage3/block0/conv2/weight 3,3,512,512
+backbone/stage3/block0/conv3/weight 1,1,512,2048
+backbone/stage3/block0/downsample/conv/weight 1,1,1024,2048
+backbone/stage3/block1/conv1/weight 1,1,2048,512
+backbone/stage3/block1/conv2/weight 3,3,512,512
+backbone/stage3/block1/conv3/weight 1,1,512,2048
+backbone/stage3/block2/conv1/weight 1,1,2048,512
+backbone/stage3/block2/conv2/weight 3,3,512,512
+backbone/stage3/block2/conv3/weight 1,1,512,2048
+classifier/weight 2048,1000
+classifier/bias
+"""
+
+
+@pytest.mark.parametrize("name,listing", [("resnet18", RESNET18_WEIGHTS), ("resnet50", RESNET50_WEIGHTS)])
+def test_resnet_matches_reference_listing(name, listing):
+    """Convolution / classifier weights by name and shape; every convolution ``convN`` has its
+    ``normN`` sibling (``downsample/conv`` has ``downsample/norm``) with scale, bias and the two
+    moving statistics, as in the reference's ``ResNet-18_init.txt`` / ``ResNet-50_init.txt``."""
+    from axlearn_b200.vision.image_classification import ImageClassificationModel
+    from axlearn_b200.vision.resnet import named_resnet_config
+
+    model = ImageClassificationModel.default_config().set(
+        name="model", backbone=named_resnet_config(name), num_classes=1000).instantiate(parent=None)
+    specs = dict(flatten_items(model.create_parameter_specs_recursively(), is_leaf=lambda x: hasattr(x, "mesh_axes")))
+    want = _golden(listing)
+    ours_weights = {p: tuple(s.shape) for p, s in specs.items() if "norm" not in p}
+    assert set(ours_weights) == set(want), sorted(set(ours_weights) ^ set(want))[:10]
+    for path, shape in want.items():
+        if shape is not None:
+            assert ours_weights[path] == shape, path
+    for path in want:
+        if path.endswith("/weight") and "conv" in path.rsplit("/", 2)[-2]:
+            norm = path.rsplit("/", 2)[0] + "/" + path.rsplit("/", 2)[-2].replace("conv", "norm")
+            for leaf in ("scale", "bias", "moving_mean", "moving_variance"):
+                assert f"{norm}/{leaf}" in specs, f"{norm}/{leaf}"

@@ -28,7 +28,7 @@ def test_resnet_endpoints_and_param_counts():
                          drop_output_collections=())
     assert {k: tuple(v.shape) for k, v in out.items()} == {
         "2": (2, 16, 16, 64), "3": (2, 8, 8, 128), "4": (2, 4, 4, 256), "5": (2, 2, 2, 512), "embedding": (2, 512)}
-    assert "moving_mean" in oc.state_updates["stem"]["conv1"]["norm"]
+    assert "moving_mean" in oc.state_updates["stem"]["norm1"]
     r50 = named_resnet_config("resnet50").set(name="r50").instantiate(parent=None)
     specs = r50.create_parameter_specs_recursively()
     import math
