@@ -240,3 +240,27 @@ def test_roberta_attention_and_layer(golden):
     layer = cfg.instantiate(parent=None)
     out, _ = functional(layer, prng.PRNGKey(0), g["params"], dict(data=g["inputs"]["data"]), is_training=True)
     torch.testing.assert_close(out.data, g["outputs"]["data"], rtol=1e-4, atol=1e-5)
+
+
+def test_multihead_attention_xl(golden):
+    """Transformer-XL relative attention inside a post-norm attention layer against the
+    reference's recorded outputs (XLNet convention, scale on the logits)."""
+    from axlearn_b200.common.attention import TransformerAttentionLayer
+    from axlearn_b200.common.attention_xl import MultiheadAttentionXL, rel_pos_to_abs_pos
+
+    x = torch.tensor([[0, 0, 1, 2, 3], [0, 4, 5, 6, 0], [7, 8, 9, 0, 0]])           # the docstring's example, t = 3
+    assert rel_pos_to_abs_pos(x).tolist() == [[1, 2, 3], [4, 5, 6], [7, 8, 9]]
+    g = _tree(golden, "attention_xl/")
+    cfg = TransformerAttentionLayer.default_config().set(
+        name="xl", target_dim=6, source_dim=6, structure="postnorm",
+        attention=MultiheadAttentionXL.default_config().set(num_heads=2))
+    cfg.attention.output_linear.bias = False
+    layer = cfg.instantiate(parent=None)
+    from axlearn_b200.common.utils import flatten_items
+
+    init = layer.initialize_parameters_recursively(prng.PRNGKey(0), device="cpu")
+    assert {p: tuple(t.shape) for p, t in flatten_items(init)} == {p: tuple(t.shape) for p, t in flatten_items(g["params"])}
+    out, _ = functional(layer, prng.PRNGKey(0), g["params"],
+                        dict(target=g["inputs"]["target"], attention_logit_biases=g["inputs"]["attention_logit_biases"]),
+                        is_training=True)
+    torch.testing.assert_close(out.data, g["outputs"]["data"], rtol=1e-4, atol=6e-6)
