@@ -22,7 +22,6 @@ from axlearn_b200.audio.subsamplers import ConvSubSampler
 from axlearn_b200.common.base_layer import BaseLayer
 from axlearn_b200.common.base_model import BaseModel
 from axlearn_b200.common.config import REQUIRED, InstantiableConfig, Required, config_class
-from axlearn_b200.common.embedding import SinusoidalPositionalEmbedding
 from axlearn_b200.common.layers import Dropout, Linear
 from axlearn_b200.common.metrics import WeightedSummary
 
@@ -57,36 +56,55 @@ class SpeechFeatureLayer(BaseLayer):
         return {"outputs": x.reshape(b, t, f * c), "paddings": p}
 
 
+class SpeechContextNetwork(BaseLayer):
+    """``input_linear`` + dropout (+ positional embedding) followed by the ``context`` stack
+    (reference: axlearn/audio/encoder_asr.py ``SpeechContextNetwork``)."""
+
+    @config_class
+    class Config(BaseLayer.Config):
+        input_dim: Required[int] = REQUIRED
+        output_dim: Required[int] = REQUIRED
+        input_linear: InstantiableConfig = Linear.default_config().set(bias=True)
+        dropout: InstantiableConfig = Dropout.default_config()
+        pos_emb: Optional[InstantiableConfig] = None
+        context: InstantiableConfig = RepeatedConformerLayer.default_config()
+
+    def __init__(self, cfg, *, parent=None):
+        super().__init__(cfg, parent=parent)
+        self._add_child("input_linear", cfg.input_linear.clone(input_dim=cfg.input_dim, output_dim=cfg.output_dim))
+        self._add_child("dropout", cfg.dropout)
+        if cfg.pos_emb is not None:
+            self._add_child("pos_emb", cfg.pos_emb.clone(dim=cfg.output_dim))
+        self._add_child("context", cfg.context.clone(input_dim=cfg.output_dim))
+
+    def forward(self, inputs: Tensor, *, paddings: Tensor):
+        x = self.dropout(self.input_linear(inputs))
+        if "pos_emb" in self._children:
+            x = x + self.pos_emb(torch.arange(x.shape[1], device=x.device))[None].to(x.dtype)
+        x = x * (1 - paddings)[..., None].to(x.dtype)
+        return {"outputs": self.context(x, paddings=paddings), "paddings": paddings}
+
+
 class ASREncoder(BaseLayer):
+    """``feature`` (frontend, augmenter, subsampler) then ``context`` (input projection +
+    conformer stack)."""
+
     @config_class
     class Config(BaseLayer.Config):
         dim: Required[int] = REQUIRED
         feature: InstantiableConfig = SpeechFeatureLayer.default_config()
-        input_linear: InstantiableConfig = Linear.default_config().set(bias=True)
-        dropout: InstantiableConfig = Dropout.default_config()
-        pos_emb: Optional[InstantiableConfig] = SinusoidalPositionalEmbedding.default_config()
-        context: InstantiableConfig = RepeatedConformerLayer.default_config()
+        context: InstantiableConfig = SpeechContextNetwork.default_config()
         # Flattened (frequency x channels) size of the feature layer's output.
         feature_dim: Required[int] = REQUIRED
 
     def __init__(self, cfg, *, parent=None):
         super().__init__(cfg, parent=parent)
         self._add_child("feature", cfg.feature)
-        self._add_child("input_linear", cfg.input_linear.clone(input_dim=cfg.feature_dim, output_dim=cfg.dim))
-        self._add_child("dropout", cfg.dropout)
-        if cfg.pos_emb is not None:
-            self._add_child("pos_emb", cfg.pos_emb.clone(dim=cfg.dim))
-        self._add_child("context", cfg.context.clone(input_dim=cfg.dim))
+        self._add_child("context", cfg.context.clone(input_dim=cfg.feature_dim, output_dim=cfg.dim))
 
     def forward(self, inputs: Tensor, *, paddings: Tensor):
         feats = self.feature(inputs, paddings=paddings)
-        x, p = feats["outputs"], feats["paddings"]
-        x = self.dropout(self.input_linear(x))
-        if "pos_emb" in self._children:
-            pos = torch.arange(x.shape[1], device=x.device)
-            x = x + self.pos_emb(pos)[None].to(x.dtype)
-        x = x * (1 - p)[..., None].to(x.dtype)
-        return {"outputs": self.context(x, paddings=p), "paddings": p}
+        return self.context(feats["outputs"], paddings=feats["paddings"])
 
 
 def ctc_greedy_decode(logits: Tensor, paddings: Tensor, *, blank_id: int = 0) -> list[list[int]]:

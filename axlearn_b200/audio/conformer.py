@@ -1,10 +1,11 @@
 """Conformer blocks.
 
 Parity targets in the reference (axlearn/common/conformer.py): ``LConvLayer`` (:60-170: norm ->
-pointwise linear to 2x dim -> GLU -> depthwise conv over time -> norm -> activation -> pointwise
-linear -> dropout, residual) and ``ConformerLayer`` (:230-420: half-step feed-forward -> self
-attention -> convolution module -> half-step feed-forward -> final layer norm; paddings zeroed
-between the parts), ``RepeatedConformerLayer`` (:540).
+gated linear unit -> depthwise conv over time -> batch norm -> activation -> pointwise linear ->
+dropout, residual) and ``ConformerLayer`` (:230-420: half-step feed-forward -> relative-position
+self attention (``MultiheadAttentionXL``) -> convolution module -> half-step feed-forward -> final
+layer norm; paddings zeroed between the parts), ``RepeatedConformerLayer`` (:540, stacked
+parameters under ``repeat/layer``).
 """
 
 from __future__ import annotations
@@ -18,27 +19,33 @@ from axlearn_b200.common.base_layer import BaseLayer
 from axlearn_b200.common.config import REQUIRED, InstantiableConfig, Required, config_class
 from axlearn_b200.common.convolution import DepthwiseConv1D
 from axlearn_b200.common.layers import BatchNorm, Dropout, LayerNorm, Linear, get_activation_fn
+from axlearn_b200.common.repeat import Repeat
 
 Tensor = torch.Tensor
 NEG_INF = -1e9
 
 
 class LConvLayer(BaseLayer):
+    """The convolution module: ``linear1_norm`` -> gated linear unit (``linear1_0`` x
+    ``sigmoid(linear1_1)``) -> depthwise ``conv`` over time -> ``conv_norm`` (batch norm) ->
+    activation -> ``linear2`` -> dropout, with a residual connection."""
+
     @config_class
     class Config(BaseLayer.Config):
         input_dim: Required[int] = REQUIRED
+        linear1_norm: InstantiableConfig = LayerNorm.default_config()
+        linear1_activation: tuple = ("linear", "nn.sigmoid")
         linear1: InstantiableConfig = Linear.default_config().set(bias=True)
-        conv: InstantiableConfig = DepthwiseConv1D.default_config().set(window=15, padding="SAME", bias=False)
-        conv_norm: InstantiableConfig = LayerNorm.default_config()
+        conv: InstantiableConfig = DepthwiseConv1D.default_config().set(window=32, padding="SAME", bias=False)
+        conv_norm: InstantiableConfig = BatchNorm.default_config()
         conv_activation: str = "nn.silu"
         linear2: InstantiableConfig = Linear.default_config().set(bias=True)
-        norm: InstantiableConfig = LayerNorm.default_config()
         dropout: InstantiableConfig = Dropout.default_config()
 
     def __init__(self, cfg, *, parent=None):
         super().__init__(cfg, parent=parent)
         d = cfg.input_dim
-        self._add_child("norm", cfg.norm.clone(input_dim=d))
+        self._add_child("linear1_norm", cfg.linear1_norm.clone(input_dim=d))
         self._add_child("linear1_0", cfg.linear1.clone(input_dim=d, output_dim=d))
         self._add_child("linear1_1", cfg.linear1.clone(input_dim=d, output_dim=d))
         self._add_child("conv", cfg.conv.clone(input_dim=d))
@@ -47,13 +54,28 @@ class LConvLayer(BaseLayer):
         self._add_child("dropout", cfg.dropout)
 
     def forward(self, inputs: Tensor, *, paddings: Tensor) -> Tensor:
+        cfg = self._config
         live = (1 - paddings)[..., None].to(inputs.dtype)
-        x = self.norm(inputs)
-        x = self.linear1_0(x) * torch.sigmoid(self.linear1_1(x))          # GLU
+        x = self.linear1_norm(inputs)
+        a0, a1 = (get_activation_fn(a) for a in cfg.linear1_activation)
+        x = a0(self.linear1_0(x)) * a1(self.linear1_1(x))
         x = self.conv(x * live)
-        x = get_activation_fn(self._config.conv_activation)(self.conv_norm(x))
+        x = get_activation_fn(cfg.conv_activation)(self.conv_norm(x, paddings=paddings))
         x = self.dropout(self.linear2(x))
         return inputs + x * live
+
+
+def _xl_attention_config():
+    """Relative-position self-attention of the conformer: Transformer-XL logits, scale (with a
+    learned per-dim factor) applied to the query, fused biased QKV projection."""
+    from axlearn_b200.common.attention import FusedQKVLinear, PerDimScale
+    from axlearn_b200.common.attention_xl import MultiheadAttentionXL
+
+    cfg = MultiheadAttentionXL.default_config().set(scale_position=MultiheadAttentionXL.ScalePosition.QUERY)
+    cfg.input_linear = FusedQKVLinear.default_config()
+    cfg.input_linear.layer.bias = True
+    cfg.query_scale.per_dim_scale = PerDimScale.default_config()
+    return cfg
 
 
 class ConformerLayer(BaseLayer):
@@ -72,6 +94,12 @@ class ConformerLayer(BaseLayer):
         # Attention window (frames to the left / right); None = the whole utterance.
         left_context: Optional[int] = None
         right_context: Optional[int] = None
+
+    @classmethod
+    def default_config(cls):
+        cfg = super().default_config()
+        cfg.self_attention.attention = _xl_attention_config()
+        return cfg
 
     def __init__(self, cfg, *, parent=None):
         super().__init__(cfg, parent=parent)
@@ -109,21 +137,20 @@ class ConformerLayer(BaseLayer):
 
 
 class RepeatedConformerLayer(BaseLayer):
-    """``num_layers`` conformer layers in sequence (children ``layer{i}``)."""
+    """``num_layers`` conformer layers with parameters stacked on a leading dim (child ``repeat``
+    -> ``layer``)."""
 
     @config_class
     class Config(BaseLayer.Config):
         input_dim: Required[int] = REQUIRED
         num_layers: Required[int] = REQUIRED
         layer: InstantiableConfig = ConformerLayer.default_config()
+        repeat: InstantiableConfig = Repeat.default_config()
 
     def __init__(self, cfg, *, parent=None):
         super().__init__(cfg, parent=parent)
-        self._layers = [self._add_child(f"layer{i}", cfg.layer.clone(input_dim=cfg.input_dim))
-                        for i in range(cfg.num_layers)]
+        self._add_child("repeat", cfg.repeat.clone(layer=cfg.layer.clone(input_dim=cfg.input_dim),
+                                                   num_layers=cfg.num_layers))
 
     def forward(self, inputs: Tensor, *, paddings: Tensor) -> Tensor:
-        x = inputs
-        for layer in self._layers:
-            x = layer(x, paddings=paddings)
-        return x
+        return self.repeat(inputs, paddings=paddings)

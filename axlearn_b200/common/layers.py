@@ -281,15 +281,23 @@ class BatchNorm(BaseNormalizationLayer):
         if self.is_training:
             red = tuple(range(x.dim() - 1))
             xf = x.float()
-            mean = xf.mean(dim=red)
-            var = ((xf - mean) ** 2).mean(dim=red)
+            if paddings is not None:
+                # Statistics over the unpadded positions only.
+                w = (1 - paddings.float()).reshape(paddings.shape + (1,) * (x.dim() - paddings.dim()))
+                n = (w.sum() * (xf[..., 0].numel() / max(1, w.numel()))).clamp_min(1.0)
+                mean = (xf * w).sum(dim=red) / n
+                var = (((xf - mean) ** 2) * w).sum(dim=red) / n
+                live_mean, live_var = mean, var
+            else:
+                mean = xf.mean(dim=red)
+                var = ((xf - mean) ** 2).mean(dim=red)
+                live_mean, live_var = mean, var
             mean = coll.all_reduce_scalar(mean, ("data", "expert", "fsdp")) / coll.axis_size(("data", "expert", "fsdp"))
             var = coll.all_reduce_scalar(var, ("data", "expert", "fsdp")) / coll.axis_size(("data", "expert", "fsdp"))
             d = cfg.decay
             self.add_state_update("moving_mean", (d * p["moving_mean"] + (1 - d) * mean).detach())
             self.add_state_update("moving_variance", (d * p["moving_variance"] + (1 - d) * var).detach())
-            red_mean, red_var = xf.mean(dim=red), ((xf - xf.mean(dim=red)) ** 2).mean(dim=red)
-            y = (xf - red_mean) * torch.rsqrt(red_var + cfg.eps)
+            y = (xf - live_mean) * torch.rsqrt(live_var + cfg.eps)
         else:
             y = (x.float() - p["moving_mean"]) * torch.rsqrt(p["moving_variance"] + cfg.eps)
         return (y * p["scale"].float() + p["bias"].float()).to(x.dtype)

@@ -209,6 +209,7 @@ class Repeat(BaseLayer):
         via_function = needs_param_grads and (use_remat or gatherer.sharded or True)
 
         ys = []
+        state_updates: list = []     # per-layer non-gradient updates (e.g. batch-norm statistics)
         gatherer.prefetch(0)
         for i in range(cfg.num_layers):
             x_i = None if xs is None else tree_map(lambda t, i=i: t[i], xs)
@@ -252,8 +253,17 @@ class Repeat(BaseLayer):
             child = ctx.output_collection.get_or_add_child(f"layer{i}")
             child.summaries.update(live_oc.summaries.get("layer", {}))
             child.module_outputs.update(live_oc.module_outputs.get("layer", {}))
-            if flatten_items(live_oc.state_updates.get("layer", {})):
-                raise NotImplementedError("state updates inside Repeat are not supported")
+            updates_i = live_oc.state_updates.get("layer", {})
+            if flatten_items(updates_i):
+                state_updates.append(updates_i)
+        if state_updates:
+            # Every repetition updates the same parameters: the new values of the stacked
+            # parameters are the per-layer values stacked on the layer dim.
+            if len(state_updates) != cfg.num_layers:
+                raise NotImplementedError("state updates must come from every repetition of a Repeat")
+            stacked = tree_map(lambda *ts: torch.stack([t.detach() for t in ts], dim=0), *state_updates)
+            ctx.output_collection.state_updates.setdefault("layer", {})
+            _merge_dicts(ctx.output_collection.state_updates["layer"], stacked)
         stacked_ys = None
         if collect and ys:
             if any(t is not None for t in ys) and _flatten_tensors(ys[0])[0]:
@@ -268,6 +278,14 @@ class Repeat(BaseLayer):
 
         out, _ = self._run(body, carry=carry)
         return out
+
+
+def _merge_dicts(dst: dict, src: dict) -> None:
+    for k, v in src.items():
+        if isinstance(v, dict) and isinstance(dst.get(k), dict):
+            _merge_dicts(dst[k], v)
+        else:
+            dst[k] = v
 
 
 def _shift_fan_axes(fan_axes):

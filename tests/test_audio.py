@@ -138,8 +138,9 @@ def _asr_model():
     feature = SpeechFeatureLayer.default_config().set(
         frontend=_frontend_cfg(), augmenter=None, subsampler=ConvSubSampler.default_config().set(hidden_dim=4))
     enc = ASREncoder.default_config().set(dim=32, feature=feature.set(output_dim=4), feature_dim=4 * 4)
-    enc.context.set(num_layers=1)
-    enc.context.layer.set(num_heads=4)
+    enc.context.context.set(num_layers=1)
+    enc.context.context.layer.set(num_heads=4)
+    enc.context.context.layer.lconv.conv_norm.decay = 0.9
     dec = CTCDecoderModel.default_config().set(input_dim=32, vocab_size=6)
     return ASRModel.default_config().set(name="asr", encoder=enc, decoder=dec).instantiate(parent=None)
 
@@ -153,15 +154,22 @@ def test_asr_model_learns_a_tiny_mapping():
     params = model.initialize_parameters_recursively(prng.PRNGKey(0), device="cpu")
     from axlearn_b200.common.utils import flatten_items
 
-    leaves = [t_.requires_grad_() for _, t_ in flatten_items(params)]
+    leaves = [t_.requires_grad_() for p_, t_ in flatten_items(params) if "moving_" not in p_]
     opt = torch.optim.Adam(leaves, lr=5e-3)
     losses = []
     for step in range(200):
-        (loss, aux), _ = functional(model, prng.PRNGKey(step), params, dict(input_batch=batch), is_training=True)
+        (loss, aux), oc = functional(model, prng.PRNGKey(step), params, dict(input_batch=batch), is_training=True)
         opt.zero_grad()
         loss.backward()
         opt.step()
         losses.append(loss.item())
+        # Batch-norm statistics travel as state updates (here through the stacked conformer layers).
+        flat_params = dict(flatten_items(params))
+        updates = flatten_items(oc.state_updates)
+        assert any(p.endswith("conv_norm/moving_mean") for p, _ in updates)
+        with torch.no_grad():
+            for path, value in updates:
+                flat_params[path].copy_(value)
     assert losses[-1] < 0.1 * losses[0], (losses[0], losses[-1])
     with torch.no_grad():
         decoded, _ = functional(model, prng.PRNGKey(0), params, dict(input_batch=batch), is_training=False,

@@ -471,3 +471,87 @@ def test_resnet_matches_reference_listing(name, listing):
             norm = path.rsplit("/", 2)[0] + "/" + path.rsplit("/", 2)[-2].replace("conv", "norm")
             for leaf in ("scale", "bias", "moving_mean", "moving_variance"):
                 assert f"{norm}/{leaf}" in specs, f"{norm}/{leaf}"
+
+
+CONFORMER_TEST_CTC = """
+encoder/feature/subsampler/conv1/weight 3,3,1,4
+encoder/feature/subsampler/conv1/bias
+encoder/feature/subsampler/conv2/weight 3,3,4,4
+encoder/feature/subsampler/conv2/bias
+encoder/context/input_linear/weight 80,4
+encoder/context/input_linear/bias
+encoder/context/context/repeat/layer/ff_start/norm/scale
+encoder/context/context/repeat/layer/ff_start/norm/bias
+encoder/context/context/repeat/layer/ff_start/linear1/weight 4,16
+encoder/context/context/repeat/layer/ff_start/linear1/bias
+encoder/context/context/repeat/layer/ff_start/linear2/weight 16,4
+encoder/context/context/repeat/layer/ff_start/linear2/bias
+encoder/context/context/repeat/layer/ff_end/norm/scale
+encoder/context/context/repeat/layer/ff_end/norm/bias
+encoder/context/context/repeat/layer/ff_end/linear1/weight 4,16
+encoder/context/context/repeat/layer/ff_end/linear1/bias
+encoder/context/context/repeat/layer/ff_end/linear2/weight 16,4
+encoder/context/context/repeat/layer/ff_end/linear2/bias
+encoder/context/context/repeat/layer/self_attention/norm/scale
+encoder/context/context/repeat/layer/self_attention/norm/bias
+encoder/context/context/repeat/layer/self_attention/attention/u_bias
+encoder/context/context/repeat/layer/self_attention/attention/v_bias
+encoder/context/context/repeat/layer/self_attention/attention/i_proj/qkv_proj/weight 4,2,2
+encoder/context/context/repeat/layer/self_attention/attention/i_proj/qkv_proj/bias
+encoder/context/context/repeat/layer/self_attention/attention/o_proj/weight 4,2,2
+encoder/context/context/repeat/layer/self_attention/attention/o_proj/bias
+encoder/context/context/repeat/layer/self_attention/attention/scale_query/per_dim_scale/param
+encoder/context/context/repeat/layer/self_attention/attention/r_proj/weight 4,2,2
+encoder/context/context/repeat/layer/lconv/linear1_norm/scale
+encoder/context/context/repeat/layer/lconv/linear1_norm/bias
+encoder/context/context/repeat/layer/lconv/linear1_0/weight 4,4
+encoder/context/context/repeat/layer/lconv/linear1_0/bias
+encoder/context/context/repeat/layer/lconv/linear1_1/weight 4,4
+encoder/context/context/repeat/layer/lconv/linear1_1/bias
+encoder/context/context/repeat/layer/lconv/conv/weight 32,1,4
+encoder/context/context/repeat/layer/lconv/conv_norm/scale
+encoder/context/context/repeat/layer/lconv/conv_norm/bias
+encoder/context/context/repeat/layer/lconv/conv_norm/moving_mean
+encoder/context/context/repeat/layer/lconv/conv_norm/moving_variance
+encoder/context/context/repeat/layer/lconv/linear2/weight 4,4
+encoder/context/context/repeat/layer/lconv/linear2/bias
+encoder/context/context/repeat/layer/norm/scale
+encoder/context/context/repeat/layer/norm/bias
+decoder/lm_head/weight
+decoder/lm_head/bias
+"""
+
+
+def test_conformer_ctc_model_matches_reference_listing():
+    """Parameter names (and the shapes the listing gives) of the ``conformer-test-ctc`` speech
+    recogniser: log-mel features -> 2 x stride-2 convolutions -> input projection -> stacked
+    conformer layers with Transformer-XL attention -> CTC head."""
+    from axlearn_b200.audio.asr import ASREncoder, ASRModel, CTCDecoderModel, SpeechFeatureLayer
+    from axlearn_b200.audio.frontend import LogMelFrontend
+    from axlearn_b200.audio.subsamplers import ConvSubSampler
+
+    dim, heads, filters, layers, vocab = 4, 2, 80, 2, 1024
+    feature = SpeechFeatureLayer.default_config().set(
+        output_dim=dim, frontend=LogMelFrontend.default_config().set(
+            num_filters=filters, sample_rate=16000, frame_size_ms=25, hop_size_ms=10),
+        subsampler=ConvSubSampler.default_config())
+    enc = ASREncoder.default_config().set(dim=dim, feature=feature, feature_dim=filters // 4 * dim)
+    enc.context.context.set(num_layers=layers)
+    enc.context.context.layer.set(num_heads=heads)
+    model = ASRModel.default_config().set(
+        name="model", encoder=enc, decoder=CTCDecoderModel.default_config().set(input_dim=dim, vocab_size=vocab)
+    ).instantiate(parent=None)
+    specs = dict(flatten_items(model.create_parameter_specs_recursively(), is_leaf=lambda x: hasattr(x, "mesh_axes")))
+    want = _golden(CONFORMER_TEST_CTC)
+    assert set(specs) == set(want), sorted(set(specs) ^ set(want))
+    for path, shape in want.items():
+        if shape is None:
+            continue
+        ours = tuple(specs[path].shape)
+        if "/repeat/" in path:
+            assert ours[0] == layers
+            ours = ours[1:]
+        if path.endswith("qkv_proj/weight"):
+            assert ours[0] == 3
+            ours = ours[1:]
+        assert ours == shape, path
