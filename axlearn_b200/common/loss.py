@@ -204,13 +204,17 @@ def giou_loss(*, predictions: Tensor, targets: Tensor, eps: float = 1e-7,
 
 
 def koleo_loss(embeddings: Tensor, *, eps: float = 1e-8, normalize_embedding: bool = True) -> Tensor:
-    """Kozachenko-Leonenko differential-entropy regulariser (spreads embeddings)."""
+    """Kozachenko-Leonenko differential-entropy regulariser (spreads embeddings; reference:
+    axlearn/common/loss.py:1091-1132): ``-mean(log(distance to the nearest other embedding))``, the
+    neighbour being picked by largest dot product."""
     e = embeddings.float()
     if normalize_embedding:
-        e = F.normalize(e, dim=-1, eps=eps)
-    d = torch.cdist(e, e)
-    d = d + torch.eye(d.shape[0], device=d.device) * 1e9
-    return -torch.log(d.min(dim=-1).values + eps).mean()
+        e = l2_normalize(e, eps=eps)
+    dots = e @ e.t()
+    dots.fill_diagonal_(-1)
+    nearest = dots.argmax(dim=-1)
+    distances = torch.sqrt(((e[nearest] - e + eps) ** 2).sum(dim=-1))
+    return -torch.log(distances + eps).mean()
 
 
 def pairwise_loss(*, logits: Tensor, pair_weights: Tensor, loss_scale: float = 1.0) -> Tensor:
@@ -226,3 +230,62 @@ def ranking_pairwise_loss(*, logits: Tensor, ranks: Tensor, loss_scale: float = 
     valid = (r[..., :, None] > 0) & (r[..., None, :] > 0)
     w = ((r[..., :, None] < r[..., None, :]) & valid).float()
     return pairwise_loss(logits=logits, pair_weights=w, loss_scale=loss_scale)
+
+
+def l2_normalize(x: Tensor, eps: float = 1e-8, dim: int = -1) -> Tensor:
+    """``x / max(||x||, eps)`` (reference: axlearn/common/normalize.py ``l2_normalize``: the sum of
+    squares is floored at ``eps^2`` before the square root)."""
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.square().sum(dim=dim, keepdim=True).clamp_min(eps * eps))).to(x.dtype)
+
+
+def negative_cosine_similarity_loss(predictions: Tensor, targets: Tensor, *, normalize_embedding: bool = True,
+                                    eps: float = 1e-8, live_targets: Optional[Tensor] = None,
+                                    reduction: ReductionMethod = ReductionMethod.MEAN) -> tuple[Tensor, dict]:
+    """``-mean(cos(predictions, targets))`` over live positions (reference:
+    axlearn/common/loss.py:1007-1050); aux holds the per-position and per-element similarities."""
+    if normalize_embedding:
+        targets = l2_normalize(targets, eps=eps)
+        predictions = l2_normalize(predictions, eps=eps)
+    elementwise = targets * predictions
+    cosine = elementwise.sum(dim=-1)
+    loss = -_reduce(cosine, reduction=reduction, sample_weight=live_targets)
+    return loss, {"cosine_similarity": cosine, "elementwise_similarity": elementwise}
+
+
+def sigmoid_cross_entropy_with_logits(logits: Tensor, targets: Tensor) -> Tensor:
+    """Element-wise ``max(x, 0) - x z + log(1 + exp(-|x|))``."""
+    return F.binary_cross_entropy_with_logits(logits.float(), targets.float(), reduction="none")
+
+
+def categorical_hinge_loss(logits: Tensor, targets: Tensor) -> Tensor:
+    """``max(0, max((1 - targets) * logits) - sum(targets * logits) + 1)`` per example."""
+    pos = (targets * logits).sum(dim=-1)
+    neg = ((1.0 - targets) * logits).amax(dim=-1)
+    return torch.clamp(neg - pos + 1.0, min=0.0)
+
+
+def bilinear_mean_squared_error(preds: Tensor, targets: Tensor, *, shape: tuple, sample_weight: Optional[Tensor] = None,
+                                eps: float = 1e-7) -> Tensor:
+    """Mean squared error after bilinearly resizing ``preds - targets`` (``[B, H, W, C]``) to
+    ``shape`` (reference: :383-417)."""
+    diff = (preds - targets).float()
+    src = diff.shape
+    for d, n in zip(src, shape):
+        if not (d % n == 0 or n % d == 0):
+            raise NotImplementedError(f"dims of shape and (preds - targets).shape must divide one another: {tuple(src)} vs {shape}")
+    diff = F.interpolate(diff.permute(0, 3, 1, 2), size=tuple(shape[1:3]), mode="bilinear", align_corners=False,
+                         antialias=False).permute(0, 2, 3, 1)
+    return _reduce(diff.square(), reduction=ReductionMethod.MEAN, sample_weight=sample_weight, eps=eps)
+
+
+def asymmetric_contrastive_loss_from_features(queries: Tensor, positive_keys: Tensor, *, negative_keys: Optional[Tensor] = None,
+                                              temperature: float = 1.0, **kwargs) -> Tensor:
+    """Contrastive loss of each query against its positive key and all other (+ extra negative)
+    keys; features are expected to be normalised by the caller."""
+    keys = positive_keys if negative_keys is None else torch.cat([positive_keys, negative_keys], dim=0)
+    return asymmetric_contrastive_loss_from_logits(contrastive_logits(queries, keys) / temperature, **kwargs)
+
+
+def symmetric_contrastive_loss_from_features(x: Tensor, y: Tensor, *, temperature: float = 1.0, **kwargs) -> Tensor:
+    return symmetric_contrastive_loss_from_logits(contrastive_logits(x, y) / temperature, **kwargs)

@@ -264,3 +264,39 @@ def test_multihead_attention_xl(golden):
                         dict(target=g["inputs"]["target"], attention_logit_biases=g["inputs"]["attention_logit_biases"]),
                         is_training=True)
     torch.testing.assert_close(out.data, g["outputs"]["data"], rtol=1e-4, atol=6e-6)
+
+
+def test_losses(golden):
+    from axlearn_b200.common import loss
+
+    g = _tree(golden, "loss_negative_cosine_similarity_loss_against_torch/")
+    got, aux = loss.negative_cosine_similarity_loss(
+        g["inputs"]["predictions"], g["inputs"]["targets"], live_targets=g["inputs"]["live_targets"])
+    torch.testing.assert_close(got.double(), g["outputs"]["ref_loss"].double(), rtol=1e-5, atol=1e-6)
+    assert aux["cosine_similarity"].shape == (2, 4)
+    g = _tree(golden, "loss_koleo_loss_wo_norm/")
+    torch.testing.assert_close(loss.koleo_loss(g["inputs"]["embeddings"], eps=1e-8).double(),
+                               g["outputs"]["ref_loss"].double(), rtol=1e-5, atol=1e-6)
+    g = _tree(golden, "loss_koleo_loss_w_norm/")
+    torch.testing.assert_close(loss.koleo_loss(g["inputs"]["embeddings"], eps=1e-8, normalize_embedding=False).double(),
+                               g["outputs"]["ref_loss"].double(), rtol=1e-5, atol=1e-6)
+    logits, targets = torch.tensor([[2.0, 1.0, 0.0]]), torch.tensor([[0.0, 1.0, 0.0]])
+    assert loss.categorical_hinge_loss(logits, targets).item() == 2.0
+    torch.testing.assert_close(loss.sigmoid_cross_entropy_with_logits(torch.tensor([0.0]), torch.tensor([1.0])),
+                               torch.tensor([0.6931472]))
+    a, b = torch.randn(2, 4, 4, 3), torch.randn(2, 4, 4, 3)
+    torch.testing.assert_close(loss.bilinear_mean_squared_error(a, b, shape=(2, 4, 4, 3)), (a - b).square().mean())
+    assert loss.bilinear_mean_squared_error(a, b, shape=(2, 2, 2, 3)).item() < (a - b).square().mean().item()
+
+
+def test_giou_and_degenerate_koleo(golden):
+    from axlearn_b200.common import loss
+
+    g = _tree(golden, "loss_giou_loss/")
+    got = loss.giou_loss(predictions=g["inputs"]["predictions"], targets=g["inputs"]["targets"])
+    got = got[0] if isinstance(got, tuple) else got
+    torch.testing.assert_close(got.double().reshape(-1).mean(), g["outputs"]["ref_loss"].double().reshape(-1).mean(),
+                               rtol=1e-4, atol=1e-5)
+    g = _tree(golden, "loss_koleo_loss_zero_dist/")
+    torch.testing.assert_close(loss.koleo_loss(g["inputs"]["embeddings"], eps=1e-8).double(),
+                               g["outputs"]["ref_loss"].double(), rtol=1e-4, atol=1e-5)
