@@ -140,6 +140,20 @@ def _stateless(update_fn: Callable) -> PartitionedGradientTransformation:
     )
 
 
+def replace_with_updates() -> PartitionedGradientTransformation:
+    """The parameter's new value is its "gradient" (reference: axlearn/common/optimizers.py:202).
+
+    The learner adds the update to the parameter, so the update is ``gradient - value``.
+    """
+
+    def fn(updates, params):
+        if params is None:
+            raise ValueError("replace_with_updates needs the parameters")
+        return _map_updates(lambda u, p: u - p.value.to(u.dtype), updates, params)
+
+    return _stateless(fn)
+
+
 def scale(step_size: float) -> PartitionedGradientTransformation:
     return _stateless(lambda u, p: _map_updates(lambda g: g * step_size, u))
 
