@@ -167,16 +167,20 @@ def asymmetric_contrastive_loss_from_logits(logits: Tensor, *, key_paddings: Opt
     return -(soft_labels * torch.log_softmax(lf, -1)).sum(-1).mean()
 
 
-def flops_loss(embeddings: Tensor, paddings: Optional[Tensor] = None, sparsity_threshold: float = 0.0):
-    """FLOPs regulariser of sparse embeddings: sum_j (mean_i |e_ij|)^2."""
+def flops_loss(*, embeddings: Tensor, paddings: Optional[Tensor] = None, sparsity_threshold: float = 0.0):
+    """FLOPs regulariser of sparse embeddings ``sum_j (mean_i |e_ij|)^2`` over the live rows
+    (reference: axlearn/common/loss.py:843).  Returns ``(loss, average_sparsity_count)``: the
+    second is the mean number of entries per live row with ``|e| <= sparsity_threshold``."""
+    if embeddings.dim() == 3:
+        if embeddings.shape[1] != 1:
+            raise ValueError("expected [batch, 1, dim] or [batch, dim]")
+        embeddings = embeddings.squeeze(1)
     e = embeddings.float().abs()
-    if paddings is not None:
-        w = (1 - paddings.float()).unsqueeze(-1)
-        mean = (e * w).sum(tuple(range(e.dim() - 1))) / w.sum().clamp_min(1.0)
-    else:
-        mean = e.reshape(-1, e.shape[-1]).mean(0)
-    sparsity = (e <= sparsity_threshold).float().mean()
-    return (mean**2).sum(), sparsity
+    live = torch.ones(e.shape[0], device=e.device) if paddings is None else 1 - paddings.float().reshape(-1)
+    n = live.sum()
+    sparsity = ((e <= sparsity_threshold).float().sum(-1) * live).sum() / n
+    mean = (e * live[:, None]).sum(0) / n
+    return (mean ** 2).sum(), sparsity
 
 
 def large_margin_cosine_loss(logits: Tensor, *, labels: Tensor, alpha: float = 1.0, margin: float = 0.0):
@@ -217,18 +221,26 @@ def koleo_loss(embeddings: Tensor, *, eps: float = 1e-8, normalize_embedding: bo
     return -torch.log(distances + eps).mean()
 
 
-def pairwise_loss(*, logits: Tensor, pair_weights: Tensor, loss_scale: float = 1.0) -> Tensor:
-    diff = logits.float()[..., :, None] - logits.float()[..., None, :]
-    per = F.softplus(-diff) * pair_weights.float()
-    return loss_scale * per.sum() / pair_weights.float().sum().clamp_min(1.0)
+def pairwise_loss(*, logits: Tensor, pair_weights: Tensor, loss_scale: Optional[Tensor] = None):
+    """Weighted mean over pairs ``(i, j)`` of ``softplus(-(logit_i - logit_j))`` (reference:
+    axlearn/common/loss.py:1135).  ``pair_weights [batch, docs, docs]``; ``loss_scale [batch]``.
+    Returns ``(mean_loss, total_weight)``."""
+    lf = logits.float()
+    diff = lf[..., :, None] - lf[..., None, :]
+    w = pair_weights.float()
+    labels = (w > 0).float()
+    per = F.binary_cross_entropy_with_logits(diff, labels, reduction="none") * w
+    if loss_scale is not None:
+        per = per * torch.as_tensor(loss_scale, dtype=per.dtype, device=per.device).reshape(-1, 1, 1)
+    total = w.sum()
+    return per.sum() / (1e-8 + total), total
 
 
-def ranking_pairwise_loss(*, logits: Tensor, ranks: Tensor, loss_scale: float = 1.0) -> Tensor:
-    """Pairs (i, j) with rank_i < rank_j (and both ranked, rank > 0) should have
-    logit_i > logit_j."""
-    r = ranks.float()
-    valid = (r[..., :, None] > 0) & (r[..., None, :] > 0)
-    w = ((r[..., :, None] < r[..., None, :]) & valid).float()
+def ranking_pairwise_loss(*, logits: Tensor, ranks: Tensor, loss_scale: Optional[Tensor] = None):
+    """Pairs (i, j) with ``0 < rank_i < rank_j`` should have ``logit_i > logit_j`` (reference:
+    axlearn/common/loss.py:1164).  Returns ``(mean_loss, number of pairs)``."""
+    ranked = ranks > 0
+    w = (ranked[..., :, None] & (ranks[..., :, None] < ranks[..., None, :])).float()
     return pairwise_loss(logits=logits, pair_weights=w, loss_scale=loss_scale)
 
 

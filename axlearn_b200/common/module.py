@@ -126,7 +126,15 @@ class InvocationContext:
 
     def add_child(self, name: str, **overrides) -> "InvocationContext":
         """Context of child module ``name`` derived from this one."""
-        child_module = self.module._children[name]  # pylint: disable=protected-access
+        if "module" in overrides:
+            # A named sub-invocation of a given module (e.g. the same tower run once per input
+            # field): outputs and PRNG keys are scoped by ``name``; when the module is this
+            # context's own, it keeps this context's state.
+            child_module = overrides["module"]
+            if "state" not in overrides and child_module is self.module:
+                overrides = dict(overrides, state=self.state)
+        else:
+            child_module = self.module._children[name]  # pylint: disable=protected-access
         kwargs: dict[str, Any] = dict(
             name=name, parent=self, module=child_module, is_training=self.is_training
         )
