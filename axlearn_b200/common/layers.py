@@ -486,6 +486,13 @@ class Embedding(BaseLayer):
             raise NotImplementedError("vocab-parallel embedding lookup")
         return y
 
+    def embeddings(self) -> Tensor:
+        """The whole table ``[num_embeddings, dim]``."""
+        w = self._weight()
+        if coll.has_axis(_spec_entry(self._config.param_partition_spec, 1), "model"):
+            w = coll.all_gather(w, "model", dim=1)
+        return w
+
     def attend(self, x: Tensor) -> Tensor:
         """``logits[..., n] = sum_d x[..., d] * weight[n, d]``."""
         w = self._weight()
