@@ -430,10 +430,30 @@ def _pad_to(prefix: Tensor, max_sequence_length: int, pad_id: int) -> Tensor:
     return out
 
 
-def _decoder_step_fn(decoder, *, logits_modifier=None):
+def _cross_kwargs(cross_attention_data, cross_attention_logit_biases) -> dict:
+    if cross_attention_data is None:
+        return {}
+    return dict(cross_attention_data=cross_attention_data, cross_attention_logit_biases=cross_attention_logit_biases)
+
+
+def _decoder_step_fn(decoder, *, logits_modifier=None, cross_attention_data=None, cross_attention_logit_biases=None):
+    expanded: dict = {}
+
+    def cross(rows: int) -> dict:
+        """Encoder outputs repeated per hypothesis: decoding runs ``[batch * num_decodes]`` rows."""
+        if cross_attention_data is None:
+            return {}
+        if rows not in expanded:
+            rep = rows // cross_attention_data.shape[0]
+            bias = cross_attention_logit_biases
+            expanded[rows] = _cross_kwargs(
+                cross_attention_data.repeat_interleave(rep, dim=0),
+                None if bias is None else bias.repeat_interleave(rep, dim=0))
+        return expanded[rows]
+
     def tokens_to_scores(token_ids: Tensor, cache: Any):
         with torch.no_grad():
-            states, out = decoder.extend_step(cached_states=cache, input_ids=token_ids)
+            states, out = decoder.extend_step(cached_states=cache, input_ids=token_ids, **cross(token_ids.shape[0]))
         return log_probs_from_logits(out["logits"][:, -1, :], logits_modifier=logits_modifier), states
 
     return tokens_to_scores
@@ -441,7 +461,8 @@ def _decoder_step_fn(decoder, *, logits_modifier=None):
 
 def sample_decode_with_decoder(decoder, *, input_batch: dict, num_decodes: int, max_sequence_length: int,
                                logits_modifier=None, stop_decoding_condition=None, prng_key=None,
-                               temperature: float = 1.0, **_unused) -> SampleOutputs:
+                               temperature: float = 1.0, cross_attention_data=None,
+                               cross_attention_logit_biases=None, **_unused) -> SampleOutputs:
     """Prefills the prompt in one pass, samples the first token from the last prompt position,
     then extends one token at a time (reference: axlearn/common/decoder.py:286-372)."""
     cfg = decoder.config
@@ -456,7 +477,8 @@ def sample_decode_with_decoder(decoder, *, input_batch: dict, num_decodes: int, 
     with torch.no_grad():
         states, out = decoder.prefill_states(
             time_step=prefill_len.to(torch.int32), input_batch={**input_batch, "input_ids": input_ids},
-            max_sequence_length=max_sequence_length)
+            max_sequence_length=max_sequence_length,
+            **_cross_kwargs(cross_attention_data, cross_attention_logit_biases))
         h = out["hidden_states"]
         last = torch.gather(h, 1, (prefill_len - 1).clamp(min=0)[:, None, None].expand(-1, 1, h.shape[-1]))
         logits = decoder.compute_logits({"hidden_states": last})
@@ -474,14 +496,17 @@ def sample_decode_with_decoder(decoder, *, input_batch: dict, num_decodes: int, 
     init_scores[rows[ok], (prefill_len - 1)[ok]] = lp[rows, first][ok]
     return sample_decode(
         inputs=input_ids, time_step=prefill_len.clamp(max=max_sequence_length - 1), cache=states,
-        tokens_to_scores=_decoder_step_fn(decoder, logits_modifier=logits_modifier),
+        tokens_to_scores=_decoder_step_fn(decoder, logits_modifier=logits_modifier,
+                                          cross_attention_data=cross_attention_data,
+                                          cross_attention_logit_biases=cross_attention_logit_biases),
         stop_decoding_condition=stop_decoding_condition or StopOnSubsequence([[cfg.eos_token_id]]),
         num_decodes=num_decodes, prng_key=decode_key, max_decode_len=max_sequence_length - 1,
         pad_id=cfg.pad_token_id, input_token_scores=init_scores)
 
 
 def beam_search_decode_with_decoder(decoder, *, input_batch: dict, num_decodes: int, max_sequence_length: int,
-                                    brevity_penalty=None, **_unused) -> BeamSearchOutputs:
+                                    brevity_penalty=None, cross_attention_data=None,
+                                    cross_attention_logit_biases=None, **_unused) -> BeamSearchOutputs:
     """Prefills all prompt tokens except the last, then beam-searches from it (reference:
     axlearn/common/decoder.py:217-284)."""
     cfg = decoder.config
@@ -491,8 +516,11 @@ def beam_search_decode_with_decoder(decoder, *, input_batch: dict, num_decodes: 
     with torch.no_grad():
         states, _ = decoder.prefill_states(
             time_step=time_step.to(torch.int32), input_batch={**input_batch, "input_ids": input_ids},
-            max_sequence_length=max_sequence_length)
+            max_sequence_length=max_sequence_length,
+            **_cross_kwargs(cross_attention_data, cross_attention_logit_biases))
     return beam_search_decode(
         inputs=input_ids, time_step=time_step, cache=states,
-        tokens_to_scores=_decoder_step_fn(decoder), eos_id=cfg.eos_token_id, num_decodes=num_decodes,
+        tokens_to_scores=_decoder_step_fn(decoder, cross_attention_data=cross_attention_data,
+                                          cross_attention_logit_biases=cross_attention_logit_biases),
+        eos_id=cfg.eos_token_id, num_decodes=num_decodes,
         max_decode_len=max_sequence_length - 1, brevity_penalty=brevity_penalty, pad_id=cfg.pad_token_id)

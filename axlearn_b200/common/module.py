@@ -131,8 +131,14 @@ class InvocationContext:
             # field): outputs and PRNG keys are scoped by ``name``; when the module is this
             # context's own, it keeps this context's state.
             child_module = overrides["module"]
-            if "state" not in overrides and child_module is self.module:
-                overrides = dict(overrides, state=self.state)
+            if "state" not in overrides:
+                if child_module is self.module:
+                    overrides = dict(overrides, state=self.state)
+                else:  # a child invoked under another name keeps its own state
+                    for child_name, child in self.module._children.items():  # pylint: disable=protected-access
+                        if child is child_module and isinstance(self.state, dict):
+                            overrides = dict(overrides, state=self.state.get(child_name, {}))
+                            break
         else:
             child_module = self.module._children[name]  # pylint: disable=protected-access
         kwargs: dict[str, Any] = dict(
