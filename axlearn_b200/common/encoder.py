@@ -129,17 +129,29 @@ class BertLMHead(BaseLayer):
         num_classes: Required[int] = REQUIRED          # = vocabulary size
         transform: InstantiableConfig = NonLinear.default_config()
         ignored_target_id: int = 0
+        # Maps hidden states to logits when the caller passes no ``attend``: an own projection, or
+        # a ``RedirectToSharedModule`` onto a shared token embedding's ``attend``.
+        inner_head: Optional[InstantiableConfig] = None
 
     def __init__(self, cfg, *, parent=None):
         super().__init__(cfg, parent=parent)
         self._add_child("transform", cfg.transform.clone(input_dim=cfg.input_dim))
+        if cfg.inner_head is not None:
+            head = cfg.inner_head.clone()
+            if "input_dim" in head.keys():
+                head.set(input_dim=cfg.input_dim, output_dim=cfg.num_classes)
+            self._add_child("inner_head", head)
 
     def _create_layer_parameter_specs(self):
         return {"output_bias": ParameterSpec(shape=(self._config.num_classes,), mesh_axes=(None,),
                                              initializer=gaussian_initializer(0.0))}
 
-    def forward(self, *, sequence_output: Tensor, attend, **unused) -> dict:
+    def forward(self, *, sequence_output: Tensor, attend=None, **unused) -> dict:
         h = self.transform(sequence_output)
+        if attend is None:
+            if "inner_head" not in self._children:
+                raise ValueError("BertLMHead needs `attend` or a configured `inner_head`")
+            attend = self.inner_head
         return {"logits": attend(h) + self.parameters["output_bias"].to(h.dtype)}
 
     def loss(self, *, logits: Tensor, target_labels: Tensor):

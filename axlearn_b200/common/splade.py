@@ -3,7 +3,7 @@
 Reference: axlearn/common/splade.py:20-97.  Hidden states go through a masked-LM head into
 vocabulary logits; the embedding is ``max_t log(1 + relu(logit_t))`` (or the sum over live
 tokens).  By default the logits come from the token embedding shared by an ancestor under
-``shared_token_emb`` (``attend``); with ``shared_emb=None`` the pooler owns an output matrix.
+``shared_token_emb`` (``attend``); ``vocab_mapping.inner_head`` can be an own ``Linear`` instead.
 """
 
 from __future__ import annotations
@@ -14,7 +14,7 @@ import torch
 
 from axlearn_b200.common.config import InstantiableConfig, config_class
 from axlearn_b200.common.encoder import BertLMHead
-from axlearn_b200.common.layers import Linear, get_activation_fn
+from axlearn_b200.common.layers import RedirectToSharedModule, get_activation_fn
 from axlearn_b200.common.poolings import BasePoolingLayer
 
 NEG_INF = -1e15
@@ -28,14 +28,20 @@ class SpladePooling(BasePoolingLayer):
         splade_activation_fn: str = "nn.relu"
         splade_mode: str = "max"                         # "max" or "sum"
         vocab_mapping: InstantiableConfig = BertLMHead.default_config()
-        shared_emb: Optional[str] = "shared_token_emb"   # None: own output projection
-        inner_head: InstantiableConfig = Linear.default_config().set(bias=False)
+
+    @classmethod
+    def default_config(cls):
+        cfg = super().default_config()
+        # Logits through the token embedding that an ancestor shares (tied weights); set
+        # ``vocab_mapping.inner_head`` to a ``Linear`` config for an own output matrix.
+        cfg.vocab_mapping = BertLMHead.default_config().set(
+            inner_head=RedirectToSharedModule.default_config().set(
+                shared_module=cls.SHARED_EMB_NAME, method_map=dict(forward="attend")))
+        return cfg
 
     def __init__(self, cfg, *, parent=None):
         super().__init__(cfg, parent=parent)
         self._add_child("vocab_mapping", cfg.vocab_mapping.clone(input_dim=cfg.input_dim, num_classes=cfg.output_dim))
-        if cfg.shared_emb is None:
-            self._add_child("inner_head", cfg.inner_head.clone(input_dim=cfg.input_dim, output_dim=cfg.output_dim))
 
     def forward(self, tokens: torch.Tensor, paddings: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``[batch, length, hidden] -> [batch, 1, vocab]``."""
@@ -47,8 +53,7 @@ class SpladePooling(BasePoolingLayer):
         if paddings is None:
             paddings = torch.zeros(tokens.shape[:2], dtype=torch.bool, device=tokens.device)
         pad = paddings.bool().unsqueeze(-1)
-        attend = self.inner_head if cfg.shared_emb is None else self.get_shared_module(cfg.shared_emb).attend
-        x = self.vocab_mapping(sequence_output=tokens, attend=attend)["logits"]
+        x = self.vocab_mapping(sequence_output=tokens)["logits"]
         act = get_activation_fn(cfg.splade_activation_fn)
         if cfg.splade_mode == "max":    # pool first: log1p(act(.)) is monotone and the pooled tensor is small
             x = x.masked_fill(pad, NEG_INF).amax(dim=1, keepdim=True)

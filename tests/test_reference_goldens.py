@@ -300,3 +300,32 @@ def test_giou_and_degenerate_koleo(golden):
     g = _tree(golden, "loss_koleo_loss_zero_dist/")
     torch.testing.assert_close(loss.koleo_loss(g["inputs"]["embeddings"], eps=1e-8).double(),
                                g["outputs"]["ref_loss"].double(), rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("mode", ["max", "sum"])
+def test_splade_pooling(golden, mode):
+    from axlearn_b200.common.layers import Linear
+    from axlearn_b200.common.splade import SpladePooling
+
+    cfg = SpladePooling.default_config().set(name="splade", input_dim=32, output_dim=64, splade_mode=mode)
+    cfg.vocab_mapping.inner_head = Linear.default_config().set(bias=False)
+    layer = cfg.instantiate(parent=None)
+    for case in ("no_padding", "with_padding"):
+        g = _tree(golden, f"splade_test_splade_pooling_{mode}_{case}/")
+        paddings = None if case == "no_padding" else 1.0 - g["inputs"]["paddings"]      # stored as a validity mask
+        got, _ = functional(layer, None, g["params"], dict(tokens=g["inputs"]["tokens"], paddings=paddings),
+                            is_training=True)
+        torch.testing.assert_close(got, g["outputs"]["values"], rtol=1e-5, atol=1e-5)
+
+
+def test_distilbert(golden):
+    from axlearn_b200.common.distilbert import set_distilbert_config
+    from axlearn_b200.common.text_encoder import TEXT_EMBEDDINGS
+
+    g = _tree(golden, "distilbert_test_distilbert/")
+    vocab = g["params"]["encoder"]["emb"]["token_emb"]["weight"].shape[0]   # only the rows the inputs use are stored
+    cfg = set_distilbert_config(pad_token_id=0, max_seq_len=12, vocab_size=vocab, num_layers=1, model_dim=32,
+                                num_heads=8, feed_forward_dim=64, feed_forward_act="exact_gelu", dropout_rate=0)
+    layer = cfg.set(name="test").instantiate(parent=None)
+    got, _ = functional(layer, None, g["params"], dict(input_ids=g["inputs"]["input_ids"]), is_training=False)
+    torch.testing.assert_close(got[TEXT_EMBEDDINGS], g["outputs"]["text_embeddings"], rtol=1e-5, atol=1e-5)

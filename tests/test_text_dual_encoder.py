@@ -13,6 +13,7 @@ from axlearn_b200.common.metrics_text_dual_encoder import (
     calculate_retrieval_metrics_from_similarity_matrix,
 )
 from axlearn_b200.common.module import functional
+from axlearn_b200.common.layers import Linear
 from axlearn_b200.common.splade import SpladePooling
 from axlearn_b200.common.utils import flatten_items
 
@@ -111,7 +112,8 @@ def test_splade_pooling_max_and_sum_modes():
     x = torch.randn(2, 5, 8)
     pad = torch.tensor([[0, 0, 0, 1, 1], [0, 0, 0, 0, 0]]).bool()
     for mode in ("max", "sum"):
-        cfg = SpladePooling.default_config().set(name="s", input_dim=8, output_dim=20, splade_mode=mode, shared_emb=None)
+        cfg = SpladePooling.default_config().set(name="s", input_dim=8, output_dim=20, splade_mode=mode)
+        cfg.vocab_mapping.inner_head = Linear.default_config().set(bias=False)
         layer = cfg.instantiate(parent=None)
         params = layer.initialize_parameters_recursively(prng.PRNGKey(0), device="cpu")
         y, _ = functional(layer, None, params, dict(tokens=x, paddings=pad), is_training=False)
