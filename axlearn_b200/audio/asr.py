@@ -228,6 +228,8 @@ class ASRModel(BaseModel):
     def forward(self, input_batch: dict):
         dec_in = self._encode(input_batch)
         dec_in["target_labels"] = input_batch["target_labels"]
+        if "target" in input_batch:         # BOS-prefixed decoder inputs (transducer / LAS decoders)
+            dec_in["target"] = input_batch["target"]
         return self.decoder(dec_in)
 
     def predict(self, input_batch: dict) -> Tensor:
@@ -236,5 +238,8 @@ class ASRModel(BaseModel):
     def greedy_decode(self, input_batch: dict) -> list[list[int]]:
         return self.decoder.greedy_decode(self._encode(input_batch))
 
-    def beam_search_decode(self, input_batch: dict, *, num_decodes: int = 4):
-        return self.decoder.beam_search_decode(self._encode(input_batch), num_decodes=num_decodes)
+    def beam_search_decode(self, input_batch: dict, *, num_decodes: int = 4, **kwargs):
+        dec_in = self._encode(input_batch)
+        if "prefix" in input_batch:
+            dec_in["prefix"] = input_batch["prefix"]
+        return self.decoder.beam_search_decode(dec_in, num_decodes=num_decodes, **kwargs)

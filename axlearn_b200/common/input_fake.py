@@ -12,7 +12,7 @@ from its saved batch index.
 
 from __future__ import annotations
 
-from typing import Iterator, Optional
+from typing import Iterator, Optional, Sequence
 
 import torch
 
@@ -137,3 +137,67 @@ class FakeSeq2SeqInput(Input):
                 "target": {"input_ids": tgt[:, :-1].contiguous()},
                 "target_labels": tgt[:, 1:].contiguous(),
             }
+
+
+class FakeImageInput(Input):
+    """Random ``{"image": [B, H, W, 3], "label": [B]}`` batches (reference:
+    axlearn/vision/input_image.py ``fake_image_dataset``)."""
+
+    @config_class
+    class Config(Input.Config):
+        is_training: bool = True
+        global_batch_size: Required[int] = REQUIRED
+        image_size: Sequence[int] = (224, 224)
+        num_classes: int = 1000
+        seed: int = 0
+        total_num_batches: Optional[int] = None
+
+    def dataset(self):
+        cfg = self._config
+        base = prng.fold_in(prng.PRNGKey(cfg.seed), coll.process_index())
+        local = cfg.global_batch_size // max(1, coll.process_count())
+        i = 0
+        while cfg.total_num_batches is None or i < cfg.total_num_batches:
+            k1, k2 = prng.split(prng.fold_in(base, i), 2)
+            image = prng.normal(k1, (local, *cfg.image_size, 3))
+            label = prng.randint(k2, (local,), 0, cfg.num_classes)
+            i += 1
+            yield {"image": _pin(image), "label": _pin(label)}
+
+
+class FakeSpeechInput(Input):
+    """Random waveforms of random lengths with label sequences: ``inputs [B, samples]``,
+    ``paddings``, ``target_labels`` (labels, EOS, then -1) and ``target.input_ids`` (BOS, labels)."""
+
+    @config_class
+    class Config(Input.Config):
+        is_training: bool = True
+        global_batch_size: Required[int] = REQUIRED
+        max_source_len: int = 16000
+        max_target_len: int = 16
+        vocab_size: int = 1024
+        bos_id: int = 1
+        eos_id: int = 2
+        seed: int = 0
+        total_num_batches: Optional[int] = None
+
+    def dataset(self):
+        cfg = self._config
+        base = prng.fold_in(prng.PRNGKey(cfg.seed), coll.process_index())
+        local = cfg.global_batch_size // max(1, coll.process_count())
+        i = 0
+        while cfg.total_num_batches is None or i < cfg.total_num_batches:
+            k1, k2, k3, k4 = prng.split(prng.fold_in(base, i), 4)
+            wave = prng.normal(k1, (local, cfg.max_source_len))
+            n = prng.randint(k2, (local,), cfg.max_source_len // 2, cfg.max_source_len + 1)
+            paddings = torch.arange(cfg.max_source_len)[None] >= n[:, None]
+            u = prng.randint(k3, (local,), 1, cfg.max_target_len)
+            tokens = prng.randint(k4, (local, cfg.max_target_len), 3, cfg.vocab_size)
+            pos = torch.arange(cfg.max_target_len)[None]
+            labels = torch.where(pos < u[:, None], tokens, torch.full_like(tokens, -1))
+            labels = torch.where(pos == u[:, None], torch.full_like(tokens, cfg.eos_id), labels)
+            ids = torch.cat([torch.full((local, 1), cfg.bos_id, dtype=tokens.dtype), tokens[:, :-1]], dim=1)
+            ids = torch.where(pos <= u[:, None], ids, torch.zeros_like(ids))
+            i += 1
+            yield {"inputs": _pin(wave * (~paddings)), "paddings": _pin(paddings),
+                   "target_labels": _pin(labels), "target": {"input_ids": _pin(ids)}}

@@ -666,3 +666,78 @@ def set_layer_norm_eps_recursively(cfg: ConfigBase, eps: float, set_only_if_none
 
     _visit_configs(cfg, fn)
     return cfg
+
+
+# ------------------------------------------------------------------------------------------
+# Classification metric layers (reference: axlearn/common/layers.py:984-1110).
+# ------------------------------------------------------------------------------------------
+
+
+class BaseClassificationMetric(BaseLayer):
+    @config_class
+    class Config(BaseLayer.Config):
+        num_classes: Required[int] = REQUIRED
+
+    def forward(self, logits: Tensor, *, labels: Tensor, soft_labels: Optional[Tensor] = None) -> Tensor:
+        raise NotImplementedError(type(self))
+
+
+class ClassificationMetric(BaseClassificationMetric):
+    """Softmax cross-entropy over in-range labels; logs loss, perplexity and accuracy."""
+
+    @config_class
+    class Config(BaseClassificationMetric.Config):
+        label_smoothing: float = 0.0
+
+    def forward(self, logits: Tensor, *, labels: Tensor, soft_labels: Optional[Tensor] = None) -> Tensor:
+        from axlearn_b200.common.loss import cross_entropy
+        from axlearn_b200.common.metrics import WeightedSummary
+
+        cfg = self._config
+        live = (labels >= 0) & (labels < cfg.num_classes)
+        n = live.sum()
+        loss, aux = cross_entropy(logits, labels, live_targets=live, label_smoothing=cfg.label_smoothing,
+                                  soft_target_labels=soft_labels)
+        accuracy = ((logits.argmax(dim=-1) == labels) & live).sum() / n.clamp_min(1)
+        self.add_summary("loss", WeightedSummary(loss.detach(), n))
+        self.add_summary("z_loss", WeightedSummary(aux["z_loss"].detach(), n))
+        self.add_summary("cross_entropy_loss", WeightedSummary(aux["cross_entropy_loss"].detach(), n))
+        self.add_summary("perplexity", WeightedSummary(torch.exp(loss.detach()), n))
+        self.add_summary("accuracy", WeightedSummary(accuracy, n))
+        return loss
+
+
+class BinaryClassificationMetric(BaseClassificationMetric):
+    """Sigmoid cross-entropy on 0/1 labels (other values are padding); logs precision, recall,
+    F-score, loss and accuracy."""
+
+    @config_class
+    class Config(BaseClassificationMetric.Config):
+        num_classes: int = 2
+        prediction_threshold: float = 0.5
+
+    def forward(self, logits: Tensor, *, labels: Tensor, soft_labels: Optional[Tensor] = None) -> Tensor:
+        from axlearn_b200.common.metrics import WeightedSummary
+
+        cfg = self._config
+        if soft_labels is not None:
+            raise ValueError("soft_labels must be None for binary classification")
+        if cfg.num_classes != 2:
+            raise ValueError(f"binary classification has two classes, got {cfg.num_classes}")
+        live = (labels >= 0) & (labels < 2)
+        n = live.sum()
+        per = F.binary_cross_entropy_with_logits(logits.float(), labels.clamp(0, 1).float(), reduction="none")
+        loss = (per * live).sum() / n.clamp_min(1)
+        preds = (torch.sigmoid(logits.float()) > cfg.prediction_threshold) & live
+        truth = (labels == 1) & live
+        tp = (preds & truth).sum().float()
+        precision = tp / preds.sum().clamp_min(1)
+        recall = tp / truth.sum().clamp_min(1)
+        f_score = 2 * precision * recall / (precision + recall).clamp_min(1e-12)
+        accuracy = ((preds == truth) & live).sum() / n.clamp_min(1)
+        self.add_summary("precision", precision)
+        self.add_summary("recall", recall)
+        self.add_summary("f_score", WeightedSummary(f_score, n))
+        self.add_summary("loss", WeightedSummary(loss.detach(), n))
+        self.add_summary("accuracy", WeightedSummary(accuracy, n))
+        return loss

@@ -197,6 +197,7 @@ def per_param_scale_by_path(*, scale_by_path: Sequence[tuple[str, float]], descr
 
 
 def _weight_decay_scales(params: Any, per_param_scale: Optional[Callable]) -> Any:
+    per_param_scale = maybe_instantiate(per_param_scale)     # a config_for_function(...) is accepted too
     scales = per_param_scale(params) if per_param_scale is not None else tree_map(lambda p: 1.0, params, is_leaf=_is_opt_param)
     return tree_map(
         lambda p, s: s if p.weight_decay_scale is None else p.weight_decay_scale,
