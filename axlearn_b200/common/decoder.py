@@ -145,6 +145,9 @@ class Decoder(BaseLayer):
             self._add_child("lm_head", cfg.lm_head.clone(vocab_size=cfg.vocab_size, embedding_dim=cfg.dim))
         self._add_child("decoding", cfg.decoding)
         self._logits_modifier = maybe_instantiate(cfg.output_logits_modifier)
+        if cfg.attention_mask is not None:
+            self._add_child("attention_mask", cfg.attention_mask)
+        self._decode_key_len: Optional[int] = None
 
     # ------------------------------------------------------------------ core
     def _forward_for_mode(self, *, mode: ForwardMode, input_batch: dict, cached_states=None,
@@ -155,6 +158,10 @@ class Decoder(BaseLayer):
         segment_ids = input_batch.get("input_segment_ids")
         emb_batch = {**input_batch, "inputs": input_ids}
         x = self.emb(emb_batch)
+        if "attention_mask" in self._children and self_attention_logit_biases is None:
+            self_attention_logit_biases = self._attention_mask_biases(
+                mode=mode, input_ids=input_ids, positions=positions, segment_ids=segment_ids,
+                cached_states=cached_states, max_len=max_len)
         tkw = dict(
             self_attention_logit_biases=self_attention_logit_biases,
             cross_attention_data=cross_attention_data,
@@ -178,6 +185,25 @@ class Decoder(BaseLayer):
             h = self.output_norm(h)
         h = self.output_dropout(h)
         return states, {"hidden_states": h}
+
+    def _attention_mask_biases(self, *, mode, input_ids, positions, segment_ids, cached_states, max_len):
+        """Biases of the configured ``attention_mask`` layer (e.g. ALiBi).  Training and prefill see
+        the ``[T, T]`` bias of the given tokens; a decoding step sees its rows of the bias over the
+        whole cache, whose length was fixed when the cache was created."""
+        from axlearn_b200.common.attention_logit_bias import decode_step_bias
+
+        b, t = input_ids.shape
+        if mode == ForwardMode.EXTEND_STEP:
+            if self._decode_key_len is None:
+                raise ValueError("extend_step with an attention_mask needs init_states / prefill_states first")
+            return decode_step_bias(self.attention_mask, query_positions=positions, key_len=self._decode_key_len)
+        if mode == ForwardMode.INIT_STATES:
+            self._decode_key_len = max_len or t
+        if positions is None:
+            positions = torch.arange(t, device=input_ids.device)[None].expand(b, -1)
+        if segment_ids is None:
+            segment_ids = torch.ones_like(positions)
+        return self.attention_mask(segment_ids=segment_ids, positions=positions)
 
     def forward(self, input_batch: dict, *, cross_attention_data=None, cross_attention_logit_biases=None,
                 **kwargs) -> dict:
@@ -223,6 +249,7 @@ class Decoder(BaseLayer):
         dtype = dtype or self.dtype()
         spec = _QuerySpec((batch_size, max_sequence_length, cfg.dim), dtype, device)
         states, _ = self.transformer.init_states(time_step=None, data=spec, max_len=max_sequence_length)
+        self._decode_key_len = max_sequence_length
         return {
             "transformer_state": states,
             "time_step": torch.zeros(batch_size, dtype=torch.int32, device=device),

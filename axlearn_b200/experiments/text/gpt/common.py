@@ -23,6 +23,8 @@ from axlearn_b200.common.attention import (
     set_double_shard_weights_config,
 )
 from axlearn_b200.common.checkpointer import every_n_steps_policy
+from axlearn_b200.common.evaler import SpmdEvaler
+from axlearn_b200.common.evaler import every_n_steps_policy as eval_every_n_steps_policy
 from axlearn_b200.common.config import (
     InstantiableConfig,
     config_for_function,
@@ -231,6 +233,22 @@ def fake_lm_input_config(*, global_batch_size: int, max_sequence_length: int, vo
         vocab_size=vocab_size, seed=seed, is_training=is_training)
 
 
+def _as_input(source: InstantiableConfig, *, global_batch_size: int, is_training: bool) -> InstantiableConfig:
+    """An ``Input`` config is used as it is (with the recipe's batch size); a source config
+    ``(shard_index, shard_count) -> Stage`` is wrapped in a ``PipelineInput``."""
+    from axlearn_b200.common.input_base import Input
+    from axlearn_b200.common.input_pipeline import PipelineInput
+
+    klass = source.klass if "klass" in source.keys() else None
+    if isinstance(klass, type) and issubclass(klass, Input):
+        cfg = source.clone()
+        if "global_batch_size" in cfg.keys():
+            cfg.global_batch_size = global_batch_size
+        return cfg
+    return PipelineInput.default_config().set(source=source.clone(), global_batch_size=global_batch_size,
+                                              is_training=is_training)
+
+
 def get_trainer_config_fn(
     *,
     model_cfg: causal_lm.Model.Config,
@@ -258,10 +276,18 @@ def get_trainer_config_fn(
         cfg.learner = learner_cfg.clone()
         cfg.max_step = max_step
         cfg.train_dtype = train_dtype
-        cfg.input = (train_input_source or fake_lm_input_config(
-            global_batch_size=train_batch_size, max_sequence_length=max_sequence_length,
-            vocab_size=vocab_size)).clone()
-        cfg.evalers = {k: v.clone() for k, v in (evalers or {}).items()}
+        cfg.input = _as_input(train_input_source, global_batch_size=train_batch_size, is_training=True) \
+            if train_input_source is not None else fake_lm_input_config(
+                global_batch_size=train_batch_size, max_sequence_length=max_sequence_length, vocab_size=vocab_size)
+        cfg.evalers = {}
+        for name, ev in (evalers or {}).items():
+            klass = ev.klass if isinstance(ev, InstantiableConfig) and "klass" in ev.keys() else None
+            if isinstance(klass, type) and issubclass(klass, SpmdEvaler):
+                cfg.evalers[name] = ev.clone()
+            else:   # an input source: evaluate the model's own metrics on it
+                cfg.evalers[name] = SpmdEvaler.default_config().set(
+                    input=_as_input(ev, global_batch_size=eval_batch_size or train_batch_size, is_training=False),
+                    eval_policy=config_for_function(eval_every_n_steps_policy).set(n=eval_every_n_steps))
         cfg.checkpointer.save_policy = config_for_function(every_n_steps_policy).set(
             n=save_every_n_steps or min(eval_every_n_steps, 5_000))
         cfg.checkpointer.keep_every_n_steps = min(max_step, keep_every_n_steps)

@@ -41,7 +41,7 @@ _BASE_MODEL_HIDDEN_DIM = 768
 
 
 def get_trainer_kwargs(model_size: str, *, vocab_size: int = VOCAB_SIZE,
-                       max_sequence_length: int = MAX_SEQUENCE_LENGTH) -> dict:
+                       max_sequence_length: int = MAX_SEQUENCE_LENGTH, flash_attention: bool = False) -> dict:
     if model_size == "test":
         kw = dict(model_kwargs=dict(num_layers=4, hidden_dim=8, num_heads=4, num_kv_heads=2, vocab_size=32,
                                     ffn_dim=scaled_hidden_dim(scale=8 / 3, round_up_to_multiples_of=16)),
@@ -66,7 +66,7 @@ def get_trainer_kwargs(model_size: str, *, vocab_size: int = VOCAB_SIZE,
     factor = _BASE_MODEL_HIDDEN_DIM / model_kwargs["hidden_dim"]
     learner_kwargs["adam_update_transformation"] = mup_simple_adam_update_transformation(factor)
     kw.setdefault("max_sequence_length", max_sequence_length)
-    return dict(model_cfg=model_config(**model_kwargs),
+    return dict(model_cfg=model_config(flash_attention=flash_attention, **model_kwargs),
                 learner_cfg=adastar_learner_config(max_step=kw["max_step"], **learner_kwargs),
                 vocab_size=model_kwargs["vocab_size"], **kw)
 
@@ -100,11 +100,24 @@ def model_config(*, num_layers: int, hidden_dim: int, num_heads: int, num_kv_hea
         layer_cfg=layer_cfg, scan_chunk=scan_chunk)
 
 
-def trainer_configs() -> dict:
-    def make(size):
+def trainer_configs(train_input_source=None, eval_input_sources=None) -> dict:
+    """``honeycrisp-<size>[-flash]``; the input arguments are as in ``gala.trainer_configs``."""
+
+    def make(size, flash):
         def fn():
-            return get_trainer_config_fn(mesh_axis_names=MESH_AXIS_NAMES, **get_trainer_kwargs(size))()
+            kwargs = get_trainer_kwargs(size, flash_attention=flash)
+            extra = {}
+            if train_input_source is not None:
+                extra["train_input_source"] = train_input_source(VOCAB_SIZE, kwargs["max_sequence_length"])
+            if eval_input_sources is not None:
+                extra["evalers"] = eval_input_sources(vocab_size=VOCAB_SIZE,
+                                                      max_sequence_length=kwargs["max_sequence_length"])
+            return get_trainer_config_fn(mesh_axis_names=MESH_AXIS_NAMES, **kwargs, **extra)()
 
         return fn
 
-    return {f"honeycrisp-{size}": make(size) for size in MODEL_SIZES}
+    out = {}
+    for size in MODEL_SIZES:
+        out[f"honeycrisp-{size}"] = make(size, False)
+        out[f"honeycrisp-{size}-flash"] = make(size, True)
+    return out

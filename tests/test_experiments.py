@@ -34,9 +34,10 @@ def test_gala_sizes_and_structures():
     assert shapes[layer + "feed_forward/linear2/weight"] == (32, 11008, 4096)
     hybrid = _param_shapes(gala.get_trainer_kwargs("85M", norm_structure="hybridnorm")["model_cfg"])
     assert layer + "feed_forward/prenorm/scale" in hybrid and layer + "feed_forward/postnorm/scale" in hybrid
-    with pytest.raises(NotImplementedError):
-        gala.model_config(num_layers=1, hidden_dim=8, num_heads=2, vocab_size=8, position_encoding="alibi")
-    assert set(gala.trainer_configs()) >= {"gala-85M", "gala-7B-hybridnorm"}
+    alibi = gala.model_config(num_layers=1, hidden_dim=8, num_heads=2, vocab_size=8, position_encoding="alibi")
+    assert alibi.decoder.attention_mask.num_heads == 2
+    assert set(gala.trainer_configs()) >= {"gala-85M", "gala-7B-hybridnorm-alibi", "gala-1B-hybridnorm-alibi-flash"}
+    assert "gala-1B-hybridnorm-alibi" not in gala.trainer_configs()
 
 
 @pytest.mark.parametrize("name,module", [("honeycrisp-test", honeycrisp), ("gala-test", gala)])

@@ -154,3 +154,41 @@ def test_word_error_rate_calculator_sums_over_batches():
     assert float(summaries["word_errors/wer"].mean) == pytest.approx(3 / 6)
     assert float(summaries["word_errors/substitutions"].mean) == pytest.approx(0.5)
     assert float(summaries["word_errors/num_examples"].mean) == 3
+
+
+@pytest.mark.skipif(not os.path.isdir(_REF), reason="reference test data not mounted")
+def test_pajama_and_deterministic_trainer_names_are_the_reference_sets():
+    from axlearn_b200.experiments.text.gpt import deterministic_trainer, pajama_trainer
+
+    def names(module):
+        d = f"{_REF}/axlearn.experiments.text.gpt.{module}"
+        return {f[:-4] for f in os.listdir(d) if f.endswith(".txt") and not f.endswith(("_init.txt", "_regularizer.txt"))}
+
+    assert set(pajama_trainer.named_trainer_configs()) == names("pajama_trainer")
+    assert set(deterministic_trainer.named_trainer_configs()) == names("deterministic_trainer")
+    want = _dump(f"{_REF}/axlearn.experiments.text.gpt.pajama_trainer/gala-1B-flash-sp-rp.txt")
+    cfg = pajama_trainer.named_trainer_configs()["gala-1B-flash-sp-rp"]()
+    assert cfg.max_step == int(want["max_step"])
+    weights = [float(v) for k, v in want.items() if k.endswith("['weight']") and "data_mixture_components" in k]
+    assert [c.weight for c in cfg.input.source.data_mixture_components] == weights
+    assert cfg.input.global_batch_size == int(want["input.input_dispatcher.global_logical_batch_size"])
+    assert set(cfg.evalers) == {k.split("'")[1] for k in want if k.startswith("evalers[")}
+    det = deterministic_trainer.named_trainer_configs()["honeycrisp-test-flash-pajama-15t-49k"]()
+    assert det.save_input_iterator is True
+
+
+def test_pajama_test_config_trains_on_the_synthetic_mixture_and_resumes_its_input(tmp_path):
+    from axlearn_b200.common.utils import set_data_dir
+    from axlearn_b200.experiments.text.gpt import pajama_trainer
+
+    with set_data_dir("FAKE"):
+        cfg = pajama_trainer.named_trainer_configs()["gala-test-sp-rp"]().set(
+            dir=str(tmp_path), max_step=3, mesh_shape=(1,), mesh_axis_names=("data",), save_input_iterator=True)
+        cfg.model.decoder.vocab_size = 259                   # the byte vocabulary stands in for sentencepiece
+        cfg.evalers = {}
+        cfg.input.prefetch = 0
+        trainer = cfg.instantiate(parent=None)
+        out = trainer.run(prng.PRNGKey(0))
+        assert trainer.step == 3 and torch.isfinite(out["loss"])
+        batch = next(iter(trainer.input.dataset()))
+        assert batch["input_ids"].shape == (16, 64) and batch["input_ids"].max() < 259
