@@ -62,6 +62,9 @@ _ACTIVATIONS: dict[str, Callable[[Tensor], Tensor]] = {
     "nn.softplus": F.softplus,
     "nn.elu": F.elu,
     "nn.leaky_relu": F.leaky_relu,
+    "nn.hard_swish": F.hardswish,
+    "nn.hard_sigmoid": F.hardsigmoid,
+    "nn.hard_tanh": F.hardtanh,
     "jnp.tanh": torch.tanh,
 }
 
