@@ -133,9 +133,17 @@ class Bastion(Configurable):
         update_interval_seconds: float = 30.0
         # Seconds a pre-empted or cancelled command gets between SIGTERM and SIGKILL.
         termination_grace_seconds: float = 10.0
+        # Publish a lifecycle event per job state change to ``<root_dir>/events.jsonl``.
+        publish_events: bool = False
 
     def __init__(self, cfg):
         super().__init__(cfg)
+        self._event_client = None
+        self._published: dict[str, str] = {}
+        if cfg.publish_events:
+            from axlearn_b200.cloud.common.event_queue import FileQueueClient
+
+            self._event_client = FileQueueClient(os.path.join(cfg.root_dir, "events.jsonl"))
         self._dir = BastionDirectory.default_config().set(root_dir=cfg.root_dir).instantiate()
         self._scheduler: JobScheduler = cfg.scheduler.instantiate()
         self._cleaner = cfg.cleaner.instantiate() if cfg.cleaner is not None else None
@@ -257,6 +265,12 @@ class Bastion(Configurable):
         # 4. Persist.
         for name, job in list(self._jobs.items()):
             self._write_state(name, job)
+            if self._event_client is not None and self._published.get(name) != job.state.state.value:
+                from axlearn_b200.cloud.common.event_queue import JobLifecycleEvent
+
+                self._published[name] = job.state.state.value
+                self._event_client.publish(JobLifecycleEvent(
+                    job_name=name, state=job.state.state.value, details=json.dumps(job.state.metadata or {}, default=str)))
             if job.state.state == JobState.COMPLETED:
                 self._complete(name)
                 del self._jobs[name]

@@ -121,7 +121,7 @@ def _bastion(tmp_path, gpus=8, cleaner=False, shares=None):
         quota=config_for_function(quota.get_resource_limits).set(
             path=_quota_file(tmp_path, tiers=({"b200": gpus},), shares=shares)))
     cfg = Bastion.default_config().set(root_dir=str(tmp_path / "bastion"), scheduler=sched, update_interval_seconds=0.05,
-                                       termination_grace_seconds=2.0)
+                                       termination_grace_seconds=2.0, publish_events=True)
     if cleaner:
         cfg.cleaner = UnschedulableCleaner.default_config().set(scheduler=sched)
     return cfg.instantiate()
@@ -154,6 +154,11 @@ def test_bastion_runs_jobs_to_completion_with_cleanup(tmp_path):
     st = b.directory.get_job_state("j1")
     assert st.state == JobState.COMPLETED and st.metadata["returncode"] == 0
     assert not os.path.exists(tmp_path / "bastion" / "jobs" / "active" / "j1")
+    import json
+    events = [json.loads(l) for l in (tmp_path / "bastion" / "events.jsonl").read_text().splitlines()]
+    states = [e["state"] for e in events if e["job_name"] == "j1"]
+    assert states[0] in ("PENDING", "ACTIVE", "pending", "active") and states[-1].lower() == "completed"
+    assert len(states) == len(set(states))                      # one event per state change
     b.shutdown()
 
 
