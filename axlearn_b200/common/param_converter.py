@@ -129,3 +129,60 @@ def _contiguous(tree: Any) -> Any:
     if isinstance(tree, Mapping):
         return {k: _contiguous(v) for k, v in tree.items()}
     return tree.contiguous()
+
+
+# ------------------------------------------------------------------------------------------
+# T5 (the counterpart of the reference's T5X converter, axlearn/common/t5x_param_converter.py:
+# checkpoints of the public T5 family reach this framework through their Hugging Face form).
+# ------------------------------------------------------------------------------------------
+
+
+def t5_hf_to_encoder_decoder(state_dict: Mapping[str, Tensor], *, num_heads: int, num_encoder_layers: int,
+                             num_decoder_layers: int) -> dict:
+    """``T5ForConditionalGeneration.state_dict()`` (gated feed-forward, i.e. v1.1 / UL2 style) -> the
+    parameter tree of ``t5_encoder_decoder_config``.  T5 does not scale attention logits; this
+    framework divides by ``sqrt(head_dim)``, so the query projections are multiplied by it."""
+    sd = state_dict
+    d = sd["shared.weight"].shape[1]
+    inner = sd["encoder.block.0.layer.0.SelfAttention.q.weight"].shape[0]
+    h = inner // num_heads
+
+    def proj(w: Tensor, scale: float = 1.0) -> Tensor:       # [N*H, D] -> [D, N, H]
+        return (w.t() * scale).reshape(d, num_heads, h).contiguous()
+
+    def attention(prefix: str) -> dict:
+        return {"i_proj": {"q_proj": {"weight": proj(sd[prefix + "q.weight"], h ** 0.5)},
+                           "k_proj": {"weight": proj(sd[prefix + "k.weight"])},
+                           "v_proj": {"weight": proj(sd[prefix + "v.weight"])}},
+                "o_proj": {"weight": sd[prefix + "o.weight"].reshape(d, num_heads, h).contiguous()}}
+
+    def ffn(prefix: str, norm: str) -> dict:
+        return {"linear1_0": {"weight": sd[prefix + "wi_0.weight"].t().contiguous()},
+                "linear1_1": {"weight": sd[prefix + "wi_1.weight"].t().contiguous()},
+                "linear2": {"weight": sd[prefix + "wo.weight"].t().contiguous()},
+                "norm": {"scale": sd[norm]}}
+
+    enc_layers, dec_layers = {}, {}
+    for i in range(num_encoder_layers):
+        p = f"encoder.block.{i}.layer."
+        enc_layers[f"layer{i}"] = {
+            "self_attention": {"attention": attention(p + "0.SelfAttention."), "norm": {"scale": sd[p + "0.layer_norm.weight"]}},
+            "feed_forward": ffn(p + "1.DenseReluDense.", p + "1.layer_norm.weight")}
+    for i in range(num_decoder_layers):
+        p = f"decoder.block.{i}.layer."
+        dec_layers[f"layer{i}"] = {
+            "self_attention": {"attention": attention(p + "0.SelfAttention."), "norm": {"scale": sd[p + "0.layer_norm.weight"]}},
+            "cross_attention": {"attention": attention(p + "1.EncDecAttention."), "norm": {"scale": sd[p + "1.layer_norm.weight"]}},
+            "feed_forward": ffn(p + "2.DenseReluDense.", p + "2.layer_norm.weight")}
+    rel = "block.0.layer.0.SelfAttention.relative_attention_bias.weight"
+    out = {
+        "encoder": {"emb": {"token_emb": {"weight": sd["shared.weight"]}},
+                    "relative_pos_emb": {"emb": {"weight": sd["encoder." + rel]}},
+                    "transformer": enc_layers, "output": {"norm": {"scale": sd["encoder.final_layer_norm.weight"]}}},
+        "decoder": {"emb": {"token_emb": {"weight": sd["shared.weight"]}},
+                    "attention_mask": {"relative_pos_emb": {"emb": {"weight": sd["decoder." + rel]}}},
+                    "transformer": dec_layers, "output_norm": {"scale": sd["decoder.final_layer_norm.weight"]}},
+    }
+    if "lm_head.weight" in sd:
+        out["decoder"]["lm_head"] = {"weight": sd["lm_head.weight"]}
+    return out

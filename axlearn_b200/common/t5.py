@@ -16,7 +16,7 @@ from typing import Optional
 import torch
 
 from axlearn_b200.common.base_layer import BaseLayer, ParameterSpec
-from axlearn_b200.common.config import REQUIRED, InstantiableConfig, Required, config_class
+from axlearn_b200.common.config import REQUIRED, InstantiableConfig, Required, config_class, config_for_function
 from axlearn_b200.common.encoder import NEG_INF, Encoder, _padding_bias
 
 Tensor = torch.Tensor
@@ -185,3 +185,78 @@ def t5_encoder_config(*, vocab_size: int, dim: int, num_layers: int, num_attenti
     if dropout_rate:
         set_dropout_rate_recursively(cfg, dropout_rate)
     return cfg
+
+
+# ------------------------------------------------------------------------------------------
+# Decoder and encoder-decoder (reference: axlearn/common/t5.py ``t5_decoder_config``,
+# ``t5_encoder_decoder_config``).
+# ------------------------------------------------------------------------------------------
+
+
+class T5DecoderLogitBias(BaseLayer):
+    """The decoder's self-attention bias as a ``Decoder.attention_mask`` layer: causal and segment
+    masks plus the one-sided relative position bias shared by all layers (child
+    ``relative_pos_emb``).  Being a function of positions it serves training, prefill and
+    single-step decoding alike."""
+
+    @config_class
+    class Config(BaseLayer.Config):
+        num_heads: Required[int] = REQUIRED
+        relative_pos_emb: InstantiableConfig = T5RelativePositionalEmbedding.default_config()
+
+    def __init__(self, cfg, *, parent=None):
+        super().__init__(cfg, parent=parent)
+        self._add_child("relative_pos_emb", cfg.relative_pos_emb.clone(dim=cfg.num_heads, bidirectional=False))
+
+    def forward(self, *, segment_ids: Tensor, positions: Tensor) -> Tensor:
+        rel_cfg = self._config.relative_pos_emb
+        rel = positions[:, None, :] - positions[:, :, None]                       # key - query
+        buckets = t5_relative_position_bucket(rel, bidirectional=False, num_buckets=rel_cfg.num_buckets,
+                                              max_distance=rel_cfg.max_distance)
+        bias = self.relative_pos_emb.emb(buckets).permute(0, 3, 1, 2).float()     # [B, N, T, S]
+        ok = (rel <= 0) & (segment_ids[:, :, None] == segment_ids[:, None, :])
+        return bias + torch.where(ok, 0.0, NEG_INF)[:, None]
+
+
+def t5_decoder_config(*, vocab_size: int, dim: int, num_layers: int, num_attention_heads: int,
+                      ffn_dim: Optional[int] = None, arch: str = "t5-v1-1", dropout_rate: float = 0.0):
+    """A ``Decoder`` with cross-attention; ``t5-v1`` ties the output head to the embedding (logits
+    scaled by ``dim ** -0.5``), the later architectures have their own ``lm_head``."""
+    from axlearn_b200.common.attention import TransformerAttentionLayer
+    from axlearn_b200.common.decoder import Decoder, LmHead
+    from axlearn_b200.common.embedding import TransformerTextEmbeddings
+    from axlearn_b200.common.layers import RMSNorm, set_bias_recursively, set_dropout_rate_recursively, set_norm_recursively
+
+    cfg = Decoder.default_config().set(vocab_size=vocab_size, dim=dim, pad_token_id=0, eos_token_id=1)
+    cfg.emb = TransformerTextEmbeddings.default_config().set(pos_emb=None)
+    cfg.transformer = t5_transformer_stack_config(arch, hidden_dim=ffn_dim)
+    cfg.transformer.set(num_layers=num_layers)
+    layer = cfg.transformer.layer
+    layer.self_attention.attention.num_heads = num_attention_heads
+    layer.cross_attention = TransformerAttentionLayer.default_config().set(source_dim=dim)
+    layer.cross_attention.attention.num_heads = num_attention_heads
+    cfg.attention_mask = T5DecoderLogitBias.default_config().set(num_heads=num_attention_heads)
+    if arch == "t5-v1":
+        from axlearn_b200.common import logit_modifiers  # pylint: disable=import-outside-toplevel
+
+        cfg.output_logits_modifier = config_for_function(logit_modifiers.scale_by).set(temperature=dim ** 0.5)
+    else:
+        cfg.lm_head = LmHead.default_config()
+    set_bias_recursively(cfg, False)
+    set_norm_recursively(cfg, RMSNorm.default_config())
+    cfg.output_norm = RMSNorm.default_config()
+    if dropout_rate:
+        set_dropout_rate_recursively(cfg, dropout_rate)
+    return cfg
+
+
+def t5_encoder_decoder_config(*, vocab_size: int, dim: int, num_attention_heads: int, num_encoder_layers: int,
+                              num_decoder_layers: int, ffn_dim: Optional[int] = None, arch: str = "t5-v1-1",
+                              dropout_rate: float = 0.0):
+    from axlearn_b200.common.encoder import EncoderDecoderModel
+
+    kw = dict(vocab_size=vocab_size, dim=dim, num_attention_heads=num_attention_heads, ffn_dim=ffn_dim, arch=arch,
+              dropout_rate=dropout_rate)
+    return EncoderDecoderModel.default_config().set(
+        encoder=t5_encoder_config(num_layers=num_encoder_layers, **kw),
+        decoder=t5_decoder_config(num_layers=num_decoder_layers, **kw))

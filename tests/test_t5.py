@@ -49,3 +49,49 @@ def test_relative_bias_layer_and_encoder():
     oa, _ = functional(dec, prng.PRNGKey(1), pd, dict(input_ids=a), is_training=False)
     ob, _ = functional(dec, prng.PRNGKey(1), pd, dict(input_ids=b), is_training=False)
     torch.testing.assert_close(oa[0, :5], ob[0, :5])
+
+
+def test_t5_encoder_decoder_matches_hugging_face_and_decodes_incrementally():
+    import pytest
+
+    transformers = pytest.importorskip("transformers")
+    from axlearn_b200.common import prng, t5
+    from axlearn_b200.common.module import functional
+    from axlearn_b200.common.param_converter import t5_hf_to_encoder_decoder
+
+    hf_cfg = transformers.T5Config(
+        vocab_size=50, d_model=16, d_kv=8, d_ff=32, num_layers=2, num_decoder_layers=2, num_heads=2,
+        relative_attention_num_buckets=32, relative_attention_max_distance=128, dropout_rate=0.0,
+        feed_forward_proj="gated-gelu", tie_word_embeddings=False, layer_norm_epsilon=1e-6, decoder_start_token_id=0)
+    torch.manual_seed(0)
+    hf = transformers.T5ForConditionalGeneration(hf_cfg).eval()
+    for p in hf.parameters():
+        torch.nn.init.normal_(p, std=0.3)
+    cfg = t5.t5_encoder_decoder_config(vocab_size=50, dim=16, num_attention_heads=2, num_encoder_layers=2,
+                                       num_decoder_layers=2, ffn_dim=32).set(name="t5")
+    model = cfg.instantiate(parent=None)
+    params = t5_hf_to_encoder_decoder(hf.state_dict(), num_heads=2, num_encoder_layers=2, num_decoder_layers=2)
+    want_tree = model.initialize_parameters_recursively(prng.PRNGKey(0), device="cpu")
+    from axlearn_b200.common.utils import flatten_items
+    assert {k: tuple(v.shape) for k, v in flatten_items(params)} == {k: tuple(v.shape) for k, v in flatten_items(want_tree)}
+    src = torch.tensor([[5, 6, 7, 8, 9, 1, 0, 0], [11, 12, 13, 14, 15, 16, 17, 1]])
+    tgt = torch.tensor([[0, 21, 22, 23, 1], [0, 31, 32, 1, 0]])
+    with torch.no_grad():
+        want = hf(input_ids=src, attention_mask=(src != 0).long(), decoder_input_ids=tgt).logits
+    batch = {"source": {"input_ids": src}, "target": {"input_ids": tgt}, "target_labels": tgt}
+    out, _ = functional(model, None, params, dict(input_batch=batch), is_training=False, method="predict")
+    torch.testing.assert_close(out["logits"], want, rtol=2e-3, atol=2e-3)
+    # Incremental decoding through the decoder's attention-mask layer gives the same logits.
+    dec = model.decoder
+    enc = out["encoder_output"]
+    cross_bias = torch.where((src != 0)[:, None, None, :], 0.0, -1e9)
+    padded = torch.zeros(2, 6, dtype=tgt.dtype)
+    padded[:, :2] = tgt[:, :2]
+    (states, _), _ = functional(dec, None, params["decoder"], dict(
+        time_step=torch.full((2,), 2, dtype=torch.int32), input_batch={"input_ids": padded}, max_sequence_length=6,
+        cross_attention_data=enc, cross_attention_logit_biases=cross_bias), is_training=False, method="prefill_states")
+    for t in range(2, 4):
+        (states, step), _ = functional(dec, None, params["decoder"], dict(
+            cached_states=states, input_ids=tgt[:, t:t + 1], cross_attention_data=enc,
+            cross_attention_logit_biases=cross_bias), is_training=False, method="extend_step")
+        torch.testing.assert_close(step["logits"][:, 0], want[:, t], rtol=2e-3, atol=2e-3)
