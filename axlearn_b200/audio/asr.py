@@ -197,6 +197,18 @@ class CTCDecoderModel(BaseLayer):
         self.add_summary("loss/invalid_seq_percent", (~valid).float().mean())
         return loss, {"per_example_loss": per_example, "per_example_weight": valid.float()}
 
+    def align(self, input_batch: dict) -> dict:
+        """Forced alignment of ``target_labels`` to the frames: per frame the label id (blank between
+        labels, -1 on padding), the label index, and the path's log-probability."""
+        from axlearn_b200.audio.aligner import ctc_forced_alignment
+
+        cfg = self._config
+        labels = input_batch["target_labels"]
+        log_pos = F.log_softmax(self.predict(input_batch).float(), dim=-1)
+        return ctc_forced_alignment(
+            log_pos=log_pos, log_pos_paddings=input_batch["paddings"], labels=labels,
+            label_paddings=(labels < 0) | (labels >= cfg.vocab_size), blank_id=cfg.blank_id).asdict()
+
     def greedy_decode(self, input_batch: dict) -> list[list[int]]:
         return ctc_greedy_decode(self.predict(input_batch), input_batch["paddings"], blank_id=self._config.blank_id)
 
@@ -237,6 +249,11 @@ class ASRModel(BaseModel):
 
     def greedy_decode(self, input_batch: dict) -> list[list[int]]:
         return self.decoder.greedy_decode(self._encode(input_batch))
+
+    def align(self, input_batch: dict) -> dict:
+        dec_in = self._encode(input_batch)
+        dec_in["target_labels"] = input_batch["target_labels"]
+        return self.decoder.align(dec_in)
 
     def beam_search_decode(self, input_batch: dict, *, num_decodes: int = 4, **kwargs):
         dec_in = self._encode(input_batch)

@@ -167,8 +167,11 @@ class Stage:
     def unbatch(self) -> "Stage":
         return _Unbatch(self)
 
-    def pack(self, *, length: int, keys: Sequence[str] = ("input_ids", "target_labels"), window: int = 64) -> "Stage":
-        return _Pack(self, length, tuple(keys), window)
+    def pack(self, *, length: int, keys: Sequence[str] = ("input_ids", "target_labels"), window: int = 64,
+             method: str = "first_fit") -> "Stage":
+        """``method``: ``first_fit`` (arrival order) or ``best_fit`` (tightest open row, found with a
+        segment tree: fewer, fuller rows on long-tailed length distributions)."""
+        return _Pack(self, length, tuple(keys), window, method)
 
     def prefetch(self, buffer_size: int = 4) -> "Stage":
         return _Prefetch(self, buffer_size)
@@ -303,9 +306,11 @@ class _Pack(_Wrap):
     ``input_segment_ids`` / ``input_positions``.  ``window`` examples are drawn at a time and every
     row is completed inside its window, so the position is restorable at window boundaries."""
 
-    def __init__(self, parent, length, keys, window):
+    def __init__(self, parent, length, keys, window, method="first_fit"):
         super().__init__(parent)
-        self._len, self._keys, self._window = length, keys, window
+        if method not in ("first_fit", "best_fit"):
+            raise ValueError(f"unknown packing method {method}")
+        self._len, self._keys, self._window, self._method = length, keys, window, method
         self._ready: list[dict] = []
         self._i = 0
         self._at_window: dict = parent.state()
@@ -314,6 +319,20 @@ class _Pack(_Wrap):
         self._at_window = self._parent.state()
         bins: list[list[dict]] = []
         room: list[int] = []
+        if self._method == "best_fit":
+            from axlearn_b200.common.segment_tree import best_fit_pack
+
+            examples = []
+            for _ in range(self._window):
+                try:
+                    examples.append(next(self._parent))
+                except StopIteration:
+                    break
+            if not examples:
+                raise StopIteration
+            packed = best_fit_pack([len(ex[self._keys[0]]) for ex in examples], self._len)
+            self._ready, self._i = [self._emit([examples[i] for i in b]) for b in packed], 0
+            return
         for _ in range(self._window):
             try:
                 ex = next(self._parent)

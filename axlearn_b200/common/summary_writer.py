@@ -22,10 +22,13 @@ from axlearn_b200.common.config import REQUIRED, InstantiableConfig, Required, c
 from axlearn_b200.common.metrics import MetricSummary
 from axlearn_b200.common.module import Module
 from axlearn_b200.common.utils import flatten_items
+from axlearn_b200.common.summary import AudioSummary, CallbackSummary, ImageSummary, Summary
 from axlearn_b200.parallel import collectives as coll
 
 
 def _to_python(v: Any) -> Any:
+    if isinstance(v, Summary):
+        return v                      # written in its own form by the writer
     if isinstance(v, MetricSummary):
         v = v.value()
     if isinstance(v, torch.Tensor):
@@ -110,11 +113,26 @@ class SummaryWriter(BaseWriter):
         cfg = self._config
         if not self._enabled or step % cfg.write_every_n_steps != 0:
             return
-        flat = {p: _to_python(v) for p, v in flatten_items(values, is_leaf=lambda x: isinstance(x, MetricSummary))}
+        flat = {p: _to_python(v) for p, v in flatten_items(
+            values, is_leaf=lambda x: isinstance(x, (MetricSummary, Summary)))}
+        typed = {k: v for k, v in flat.items() if isinstance(v, Summary)}
+        for k, v in typed.items():
+            v.validate()
+            if isinstance(v, CallbackSummary):
+                flat[k] = _to_python(v.value())
+            else:                     # the JSON log records what was written, not the payload
+                flat[k] = f"<{type(v).__name__} {tuple(v.value().shape)}>"
         self._jsonl.write(json.dumps({"step": step, "time": time.time(), **flat}) + "\n")
         self._jsonl.flush()
         if self._tb is not None:
+            for k, v in typed.items():
+                if isinstance(v, ImageSummary):
+                    self._tb.add_images(k, v.value(), step, dataformats="NHWC")
+                elif isinstance(v, AudioSummary):
+                    self._tb.add_audio(k, v.value()[None], step, sample_rate=v.sample_rate)
             for k, v in flat.items():
+                if isinstance(v, list) and v and isinstance(v[0], (int, float)):
+                    self._tb.add_histogram(k, torch.tensor(v), step)
                 if isinstance(v, (int, float)):
                     self._tb.add_scalar(k, v, step)
                 elif isinstance(v, str):

@@ -140,3 +140,14 @@ def test_pipeline_input_batches_per_feed_and_resumes():
         global_batch_size=4, num_feeds=1, is_training=False, prefetch=0).instantiate(parent=None)
     batches = list(ev.dataset())
     assert len(batches) == 2 and batches[1]["is_valid"].tolist() == [True, False, False, False]
+
+
+def test_best_fit_packing_uses_fewer_rows():
+    rng = np.random.default_rng(3)
+    docs = [{"input_ids": np.ones(n, dtype=np.int32), "target_labels": np.ones(n, dtype=np.int32)}
+            for n in rng.integers(1, 33, 400)]
+    first = list(ip.read(ip.ListSource(docs)).pack(length=32, window=100))
+    best = list(ip.read(ip.ListSource(docs)).pack(length=32, window=100, method="best_fit"))
+    tokens = sum(len(d["input_ids"]) for d in docs)
+    assert sum(int((r["input_segment_ids"] > 0).sum()) for r in best) == tokens
+    assert len(best) <= len(first) and len(best) <= 1.08 * tokens / 32 + 4
