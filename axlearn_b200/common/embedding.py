@@ -82,8 +82,11 @@ class TransformerTextEmbeddings(BaseEmbedding):
     def forward(self, input_batch: dict) -> Tensor:
         inputs = input_batch["inputs"]
         x = self.token_emb(inputs)
-        if "type_emb" in self._children and input_batch.get("token_type_ids") is not None:
-            x = x + self.type_emb(input_batch["token_type_ids"])
+        if "type_emb" in self._children:
+            token_type_ids = input_batch.get("token_type_ids")
+            if token_type_ids is None:          # every token is of type 0, as in the reference
+                token_type_ids = torch.zeros_like(inputs)
+            x = x + self.type_emb(token_type_ids)
         if "pos_emb" in self._children:
             positions = input_batch.get("positions")
             if positions is None:

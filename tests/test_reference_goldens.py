@@ -329,3 +329,18 @@ def test_distilbert(golden):
     layer = cfg.set(name="test").instantiate(parent=None)
     got, _ = functional(layer, None, g["params"], dict(input_ids=g["inputs"]["input_ids"]), is_training=False)
     torch.testing.assert_close(got[TEXT_EMBEDDINGS], g["outputs"]["text_embeddings"], rtol=1e-5, atol=1e-5)
+
+
+def test_bert_text_embedding_stream_encoder(golden):
+    from axlearn_b200.common.text_dual_encoder import POSITIVE_EMBEDDINGS, POSITIVE_INPUT_IDS
+    from axlearn_b200.common.utils_text_dual_encoder import bert_text_embedding_stream_encoder_config
+
+    g = _tree(golden, "tde_test_bert_stream_encoder_config/")
+    vocab = g["params"]["encoder"]["emb"]["token_emb"]["weight"].shape[0]   # only the rows the inputs use are stored
+    cfg = bert_text_embedding_stream_encoder_config(
+        pad_token_id=0, max_seq_len=12, vocab_size=vocab, num_layers=3, hidden_dim=32, output_dim=32, num_heads=8,
+        output_proj=None, output_norm=None, remat=False)
+    layer = cfg.set(name="test").instantiate(parent=None)
+    batch = {POSITIVE_INPUT_IDS: g["inputs"]["input_ids"][:, None]}
+    got, _ = functional(layer, None, dict(text_encoder=g["params"]), dict(input_batch=batch), is_training=False)
+    torch.testing.assert_close(got[POSITIVE_EMBEDDINGS], g["outputs"]["emb"][:, None], rtol=1e-5, atol=1e-5)
