@@ -7,17 +7,16 @@ import torch
 from axlearn_b200.common import prng
 from axlearn_b200.common.utils import flatten_items
 
-_REF = "/root/reference/axlearn/experiments/testdata"
+# Hyper-parameters and config names taken from the reference's golden config dumps
+# (axlearn/experiments/testdata/<module>/<config>.txt), stored as "key: value" strings.
+with open(os.path.join(os.path.dirname(__file__), "testdata", "reference_config_values.json")) as _f:
+    _GOLDEN = __import__("json").load(_f)
+_REF = "golden"
 
 
 def _dump(path):
-    out = {}
-    with open(path) as f:
-        for line in f:
-            if ": " in line:
-                k, v = line.rstrip("\n").split(": ", 1)
-                out[k] = v
-    return out
+    module, name = path[len(_REF) + 1:-4].split("/")
+    return _GOLDEN["values"][f"{module}/{name}"]
 
 
 def test_logistic_regression_tutorial_trains_to_high_accuracy(tmp_path):
@@ -34,7 +33,6 @@ def test_logistic_regression_tutorial_trains_to_high_accuracy(tmp_path):
     assert os.path.isdir(tmp_path / "summaries" / "eval") and os.path.isdir(tmp_path / "checkpoints" / "step_00000200")
 
 
-@pytest.mark.skipif(not os.path.isdir(_REF), reason="reference test data not mounted")
 @pytest.mark.parametrize("name", ["ResNet-50-ema", "ResNet-18", "ResNet-Testb"])
 def test_imagenet_trainer_hyperparameters_match_reference_config_dump(name):
     from axlearn_b200.experiments.vision.resnet import imagenet_trainer
@@ -55,9 +53,8 @@ def test_imagenet_trainer_hyperparameters_match_reference_config_dump(name):
     assert list(cfg.model.backbone.num_blocks_per_stage) == blocks
     assert cfg.model.num_classes == int(want["model.num_classes"])
     assert set(cfg.evalers) == {k.split("'")[1] for k in want if k.startswith("evalers[")}
-    assert set(imagenet_trainer.named_trainer_configs()) == {
-        f[:-4] for f in os.listdir(f"{_REF}/axlearn.experiments.vision.resnet.imagenet_trainer")
-        if f.endswith(".txt") and "_" not in f}
+    assert set(imagenet_trainer.named_trainer_configs()) == set(
+        _GOLDEN["names"]["axlearn.experiments.vision.resnet.imagenet_trainer"])
 
 
 def test_resnet_test_config_runs_two_steps(tmp_path):
@@ -72,7 +69,6 @@ def test_resnet_test_config_runs_two_steps(tmp_path):
     assert trainer.step == 2 and torch.isfinite(out["loss"])
 
 
-@pytest.mark.skipif(not os.path.isdir(_REF), reason="reference test data not mounted")
 def test_librispeech_trainer_matches_reference_config_dump():
     from axlearn_b200.experiments.audio.conformer import librispeech_trainer as lt
 
@@ -156,13 +152,11 @@ def test_word_error_rate_calculator_sums_over_batches():
     assert float(summaries["word_errors/num_examples"].mean) == 3
 
 
-@pytest.mark.skipif(not os.path.isdir(_REF), reason="reference test data not mounted")
 def test_pajama_and_deterministic_trainer_names_are_the_reference_sets():
     from axlearn_b200.experiments.text.gpt import deterministic_trainer, pajama_trainer
 
     def names(module):
-        d = f"{_REF}/axlearn.experiments.text.gpt.{module}"
-        return {f[:-4] for f in os.listdir(d) if f.endswith(".txt") and not f.endswith(("_init.txt", "_regularizer.txt"))}
+        return set(_GOLDEN["names"][f"axlearn.experiments.text.gpt.{module}"])
 
     assert set(pajama_trainer.named_trainer_configs()) == names("pajama_trainer")
     assert set(deterministic_trainer.named_trainer_configs()) == names("deterministic_trainer")
