@@ -42,7 +42,7 @@ class Bundler(Configurable):
     @config_class
     class Config(Configurable.Config):
         # Glob patterns (relative paths) left out of the bundle.
-        exclude: Sequence[str] = (".git", "__pycache__", "*.pyc", "gpurun_out", "_work", "*.ncu-rep")
+        exclude: Sequence[str] = (".git", "__pycache__", "*.pyc", "_work", "*.ncu-rep")
         # Extra files or directories outside the tree to include (copied under their basename).
         external: Sequence[str] = ()
 

@@ -14,7 +14,7 @@ def tiny_fuji_trainer_config(directory, *, max_step=20, save_every_n_steps=10, s
                              train_dtype=None, device="cpu", num_kv_heads=None, shared_lm_head=False,
                              mesh_shape=None, batch=8, seq=64, scan_chunk=None, hidden=128, layers=4,
                              heads=4, ffn=512, vocab=32768):
-    """BASELINE config 1: 4 layers, d_model 128, 4 heads, SwiGLU 512, RMSNorm eps 1e-5, RoPE
+    """The smallest benchmark config: 4 layers, d_model 128, 4 heads, SwiGLU 512, RMSNorm eps 1e-5, RoPE
     theta 5e5, vocab 32768, untied head, batch 8 x seq 64, AdamW lr 3e-4 b1 .9 b2 .95 wd .1."""
     model = fuji.model_config(
         num_layers=layers, hidden_dim=hidden, num_heads=heads, num_kv_heads=num_kv_heads, vocab_size=vocab,

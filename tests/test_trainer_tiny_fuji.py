@@ -1,4 +1,4 @@
-"""BASELINE config 1 on CPU: 20 trainer steps of a tiny Fuji, checkpoint, restore, bit-match."""
+"""The smallest benchmark config on CPU: 20 trainer steps of a tiny Fuji, checkpoint, restore, bit-match."""
 
 import json
 import os
