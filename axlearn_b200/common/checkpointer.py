@@ -552,10 +552,16 @@ class Checkpointer(BaseCheckpointer):
         return build_step_dir(self._config.dir, step=step)
 
     def save(self, *, step: int, state: Any, specs: Optional[Any] = None,
-             evaler_summaries: Optional[dict] = None, force: bool = False) -> bool:
-        """Saves if the policy says so; returns whether a save was started."""
+             evaler_summaries: Optional[dict] = None, force: bool = False,
+             pre_save_check: Optional[Callable[[], None]] = None) -> bool:
+        """Saves if the policy says so; returns whether a save was started.  ``pre_save_check``
+        runs once the policy has decided to save and before anything is written; it may raise
+        to veto the save (the trainer uses it to refuse a state computed by a kernel that
+        reported an error)."""
         if not force and not self._save_policy(step=step, evaler_summaries=evaler_summaries):
             return False
+        if pre_save_check is not None:
+            pre_save_check()
         ckpt_dir = self.ckpt_dir(step)
         if os.path.exists(os.path.join(ckpt_dir, "index")):
             raise ValueError(f"checkpoint {ckpt_dir} already exists")

@@ -325,15 +325,26 @@ class SpmdTrainer(Module):
         specs = self.trainer_state_specs
         return tree_map(localise, specs, is_leaf=_is_spec)
 
+    def _check_device_status(self) -> None:
+        """Raises ``RuntimeError`` when a kernel reported a bounded-wait time-out since the last
+        check (its outputs may be partly unwritten, so the step must not be kept)."""
+        if self._device.type != "cuda":
+            return
+        from axlearn_b200.ops import cuda_ops
+
+        cuda_ops.check_status(self._device)
+
     def save_checkpoint(self, evaler_summaries: Optional[dict] = None, *, force: bool = False) -> bool:
         cfg = self._config
         with self._mesh:
             state = dict(self._trainer_state)
             if cfg.save_input_iterator:
                 state["input_iter"] = self.input
+            # Never persist a state that a timed-out kernel may have corrupted: the check raises,
+            # the error propagates and the supervising agent restarts from the last good checkpoint.
             saved = self.checkpointer.save(
                 step=self._step, state=state, specs=self.trainer_state_specs,
-                evaler_summaries=evaler_summaries, force=force)
+                evaler_summaries=evaler_summaries, force=force, pre_save_check=self._check_device_status)
         return saved
 
     # ------------------------------------------------------------------ run
@@ -429,6 +440,9 @@ class SpmdTrainer(Module):
         step = self._step
         if step <= 5 or step % cfg.log_every_n_steps == 0:
             loss = float(out["loss"])
+            # The loss read above synchronised the device: a bounded wait that gave up inside a
+            # kernel (late peer, lost flag) has left its code in the status word by now.
+            self._check_device_status()
             if not math.isfinite(loss):
                 raise UndefinedLossException(f"loss is {loss} at step {step}")
             if coll.process_index() == 0:

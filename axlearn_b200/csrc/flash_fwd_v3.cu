@@ -1,0 +1,573 @@
+// Flash attention forward, third generation.
+//
+// Same data flow as flash_fwd_v2.cu (two 128-row query tiles per CTA, scores and probabilities
+// in tensor memory, P*V and the next Q*K^T of one tile running while the other tile's softmax
+// works), with two changes:
+//   * every 128-row tile has EIGHT softmax warps instead of four: the two warps that share a
+//     TMEM lane quarter split the 128 score columns in halves, exchange their row maxima and
+//     row sums through shared memory and a 64-thread named barrier.  A warp's instruction
+//     stream per key tile is half as long, and each SM sub-partition always has two softmax
+//     warps of the active tile to interleave, which is what hides the latency between
+//     tcgen05.ld, the max/exp chain and tcgen05.st;
+//   * masking beyond "causal": segment ids (packed sequences), a sliding window and a tanh
+//     logit cap are applied inside the kernel, and key tiles that no row of a query tile can
+//     see (left of the window, other segments) are skipped on both sides of the range.
+//
+// Per CTA (640 threads): warp 0 TMA producer, warp 1 MMA issuer (warps 2-3 only fill up the
+// control warpgroup, which hands most of its registers to the others), warps 4..11 softmax of
+// tile A, warps 12..19 softmax of tile B.  TMEM (512 columns): S_A/P_A 0..127, S_B/P_B 128..255,
+// O_A 256.., O_B 384...  P (bf16 pairs) overlays the first 64 columns of S.
+//
+// Reference kernels being replaced: axlearn/common/flash_attention/gpu_attention.py:114-243
+// (segment ids :179-205, block skipping by mask_fn) and the cuDNN call at :792-926.
+#include "host_utils.cuh"
+#include "sm100.cuh"
+
+namespace axb {
+
+int make_bthd_map(CUtensorMap* map, const void* base, int B, int L, int N, int H, int box_rows);
+
+constexpr int kF3Threads = 640;
+constexpr uint32_t kGaveUp = 0x7fc0dead;  // NaN payload: "my wait on the score tile timed out"
+
+struct FlashFwd3Params {
+  void* out;
+  float* lse;
+  const int* q_seg;    // [B, T] or null
+  const int* k_seg;    // [B, S] or null
+  const int2* ranges;  // [B, ceil(T/128)]: key tiles [x, y) that share a segment id with the query tile
+  int B, T, S, N, Nkv, H;
+  float sc;            // multiplier applied to a (transformed) score before exp2
+  float cap_in;        // softmax_scale / cap          (logit cap: z = s * cap_in)
+  float cap_out;       // cap * log2(e); 0 = no cap    (score in log2 units = tanh(z) * cap_out)
+  int causal, q_offset, window;  // window < 0: none; else keys older than row_pos - window are hidden
+  int* status;
+};
+
+template <int H>
+struct F3Smem {
+  static constexpr int kSub = 16384;
+  static constexpr int kTile = (H / 64) * kSub;
+  static constexpr int kQ = 0;                  // two tiles
+  static constexpr int kK = kQ + 2 * kTile;     // two stages
+  static constexpr int kV = kK + 2 * kTile;     // two stages
+  static constexpr int kMax = kV + 2 * kTile;   // float [2 parity][2 tiles][2 halves][128]
+  static constexpr int kSum = kMax + 4096;      // float [2 tiles][2 halves][128]
+  static constexpr int kBar = kSum + 2048;
+  static constexpr int kTotal = kBar + 256 + 1024;
+};
+
+__device__ __forceinline__ void pair_barrier(int id) {
+  asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory");
+}
+
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// kGeneral: segment ids / sliding window / logit cap are honoured (every tile takes the masking
+// path when segment ids are present).  The plain instantiation only masks diagonal and ragged
+// tiles.
+template <int H, bool kGeneral>
+__global__ void __launch_bounds__(kF3Threads, 1)
+flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                  const __grid_constant__ CUtensorMap tmap_v, FlashFwd3Params p) {
+  using L = F3Smem<H>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBar);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;    // [2]
+  uint64_t* k_empty = bars + 3;   // [2]
+  uint64_t* v_full = bars + 5;    // [2]
+  uint64_t* v_empty = bars + 7;   // [2]
+  uint64_t* s_full = bars + 9;    // [2] per query tile
+  uint64_t* p_full = bars + 11;   // [2] per query tile, 8 arrivals
+  uint64_t* pv_done = bars + 13;  // [2] per query tile, completes once
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  float* ex_max = reinterpret_cast<float*>(smem + L::kMax);
+  float* ex_sum = reinterpret_cast<float*>(smem + L::kSum);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pair = gridDim.x - 1 - blockIdx.x;  // heavy (late) query tiles first
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int kv_head = head / (p.N / p.Nkv);
+  const int t0 = pair * 256;
+  const int n_qt = (p.T + 127) / 128;
+
+  // Key tiles [lo, hi) each query tile needs.
+  int lo[2], hi[2];
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    const int tx = t0 + x * 128;
+    int l = 0, h = 0;
+    if (tx < p.T) {
+      int kv_len = p.S;
+      if (p.causal) kv_len = min(p.S, tx + 128 + p.q_offset);
+      h = kv_len > 0 ? (kv_len + 127) / 128 : 0;
+      if (kGeneral) {
+        if (p.window >= 0) l = max(0, tx + p.q_offset - p.window) / 128;
+        if (p.ranges != nullptr) {
+          const int2 r = p.ranges[batch * n_qt + pair * 2 + x];
+          l = max(l, r.x);
+          h = min(h, r.y);
+        }
+      }
+      if (l >= h) l = h = 0;
+    }
+    lo[x] = l, hi[x] = h;
+  }
+  const bool act0 = hi[0] > lo[0], act1 = hi[1] > lo[1];
+  const int g_lo = act0 ? (act1 ? min(lo[0], lo[1]) : lo[0]) : lo[1];
+  const int g_hi = max(hi[0], hi[1]);
+  const bool any = act0 || act1;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 8);
+      mbar_init(&pv_done[i], 1);
+    }
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one() && any) {
+      mbar_arrive_expect_tx(q_full, 2 * L::kTile);
+#pragma unroll
+      for (int x = 0; x < 2; ++x)
+#pragma unroll
+        for (int j = 0; j < H / 64; ++j)
+          tma_load_4d(smem + L::kQ + x * L::kTile + j * L::kSub, &tmap_q, q_full, j * 64, head,
+                      t0 + x * 128, batch);
+      for (int it = g_lo; it < g_hi; ++it) {
+        const int g = it - g_lo;
+        const int st = g & 1;
+        const uint32_t ph = (g >> 1) & 1;
+        if (!mbar_wait(&k_empty[st], ph ^ 1, p.status, kStatusWaitTimeoutProducer)) break;
+        mbar_arrive_expect_tx(&k_full[st], L::kTile);
+#pragma unroll
+        for (int j = 0; j < H / 64; ++j)
+          tma_load_4d(smem + L::kK + st * L::kTile + j * L::kSub, &tmap_k, &k_full[st], j * 64, kv_head,
+                      it * 128, batch);
+        if (!mbar_wait(&v_empty[st], ph ^ 1, p.status, kStatusWaitTimeoutProducer)) break;
+        mbar_arrive_expect_tx(&v_full[st], L::kTile);
+#pragma unroll
+        for (int j = 0; j < H / 64; ++j)
+          tma_load_4d(smem + L::kV + st * L::kTile + j * L::kSub, &tmap_v, &v_full[st], j * 64, kv_head,
+                      it * 128, batch);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one() && any) {
+      constexpr uint32_t idesc_qk = umma_idesc_f16(128, 128, 1, 1, 0, 0);
+      constexpr uint32_t idesc_pv = umma_idesc_f16(128, H, 1, 1, 0, 1);
+      bool ok = mbar_wait(q_full, 0, p.status, kStatusWaitTimeoutMma);
+      auto issue_qk = [&](int x, int st) {
+        const uint32_t q_addr = smem_u32(smem + L::kQ + x * L::kTile);
+        const uint32_t k_addr = smem_u32(smem + L::kK + st * L::kTile);
+#pragma unroll
+        for (int kk = 0; kk < H / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
+          tc_mma_f16(tmem_base + x * 128, umma_smem_desc(q_addr + off, 16, 1024),
+                     umma_smem_desc(k_addr + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+        }
+        tc_commit(&s_full[x]);
+      };
+      auto issue_pv = [&](int x, int st, bool first) {
+        const uint32_t v_addr = smem_u32(smem + L::kV + st * L::kTile);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          // 16 keys per step: 8 TMEM columns of packed bf16 pairs; 16 V rows = 2048 B.
+          tc_mma_f16_ts(tmem_base + 256 + x * 128, tmem_base + x * 128 + kk * 8,
+                        umma_smem_desc(v_addr + kk * 2048, L::kSub, 1024), idesc_pv,
+                        (!first || kk > 0) ? 1u : 0u);
+        }
+      };
+      // Prologue: scores of the first key tile for the query tiles that start there.
+      if (ok) ok = mbar_wait(&k_full[0], 0, p.status, kStatusWaitTimeoutMma);
+      if (ok) {
+        tc_fence_after_sync();
+        for (int x = 0; x < 2; ++x)
+          if (hi[x] > lo[x] && lo[x] == g_lo) issue_qk(x, 0);
+        tc_commit(&k_empty[0]);
+      }
+      for (int it = g_lo; it < g_hi && ok; ++it) {
+        const int g = it - g_lo;
+        const int st = g & 1;
+        const uint32_t ph = (g >> 1) & 1;
+        const bool has_next = it + 1 < g_hi;
+        if (!mbar_wait(&v_full[st], ph, p.status, kStatusWaitTimeoutMma)) break;
+        if (has_next) {
+          if (!mbar_wait(&k_full[st ^ 1], ((g + 1) >> 1) & 1, p.status, kStatusWaitTimeoutMma)) break;
+        }
+        tc_fence_after_sync();
+        for (int x = 0; x < 2 && ok; ++x) {
+          if (it >= lo[x] && it < hi[x]) {
+            if (!mbar_wait(&p_full[x], (it - lo[x]) & 1, p.status, kStatusWaitTimeoutMma)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            issue_pv(x, st, it == lo[x]);
+            if (it + 1 < hi[x]) issue_qk(x, st ^ 1);
+            else tc_commit(&pv_done[x]);
+          } else if (it + 1 == lo[x] && it + 1 < hi[x]) {
+            issue_qk(x, st ^ 1);  // first score tile of a query tile that starts later
+          }
+        }
+        if (!ok) break;
+        tc_commit(&v_empty[st]);
+        if (has_next) tc_commit(&k_empty[st ^ 1]);
+      }
+    }
+  }
+  } else {
+    // ------------------------------------------------------------------ softmax / epilogue
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
+    const int idx = warp - 4;
+    const int x = idx >> 3;               // query tile
+    const int half = (idx >> 2) & 1;      // which 64 score columns / which half of the O columns
+    const int quarter = warp & 3;         // TMEM lane quarter accessible to this warp
+    const int r_in = quarter * 32 + lane;
+    const int row = t0 + x * 128 + r_in;
+    const int row_pos = row + p.q_offset;
+    const int bar_id = 1 + x * 4 + quarter;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_base + x * 128 + half * 64;
+    const uint32_t p_addr = tmem_base + lane_base + x * 128 + half * 32;
+    const uint32_t o_addr = tmem_base + lane_base + 256 + x * 128 + half * (H / 2);
+    float* my_max = ex_max + (x * 2 + half) * 128 + r_in;
+    float* other_max = ex_max + (x * 2 + (half ^ 1)) * 128 + r_in;
+    const int my_lo = lo[x], my_hi = hi[x];
+    // Visible key range of this row (general mode) and its segment id.
+    int c_lo = 0, c_hi = p.S - 1, seg = 0;
+    if (p.causal) c_hi = min(c_hi, row_pos);
+    const int* kseg_row = nullptr;
+    if (kGeneral) {
+      if (p.window >= 0) c_lo = max(0, row_pos - p.window);
+      if (p.q_seg != nullptr) {
+        seg = row < p.T ? p.q_seg[static_cast<int64_t>(batch) * p.T + row] : -1;
+        kseg_row = p.k_seg + static_cast<int64_t>(batch) * p.S;
+      }
+    }
+    const uint32_t c_span = static_cast<uint32_t>(c_hi - c_lo);
+    float m_ref = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    for (int it = my_lo; it < my_hi && ok; ++it) {
+      const int kpar = (it - my_lo) & 1;
+      // A wait that gives up must not leave the partner warp alone at the named barrier: both
+      // halves always reach it, and a failed wait travels through the exchange slot.
+      const bool got = __all_sync(0xffffffffu, mbar_wait(&s_full[x], kpar, p.status, kStatusWaitTimeoutEpilogue));
+      uint32_t ra[32], rb[32];
+      float tmax = -INFINITY;
+      if (got) {
+        tc_fence_after_sync();
+        tmem_ld_32x32(s_addr, ra);
+        tmem_ld_32x32(s_addr + 32, rb);
+        tmem_ld_wait();
+        const int s0 = it * 128 + half * 64;  // first key column of this thread
+        const uint32_t ninf = __float_as_uint(-INFINITY);
+        if (kGeneral) {
+          if (p.cap_out != 0.f) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              ra[j] = __float_as_uint(tanh_approx(__uint_as_float(ra[j]) * p.cap_in) * p.cap_out);
+              rb[j] = __float_as_uint(tanh_approx(__uint_as_float(rb[j]) * p.cap_in) * p.cap_out);
+            }
+          }
+          const bool edge = (s0 < c_lo) || (s0 + 63 > c_hi);
+          if (edge) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (static_cast<uint32_t>(s0 + j - c_lo) > c_span || c_hi < c_lo) ra[j] = ninf;
+              if (static_cast<uint32_t>(s0 + 32 + j - c_lo) > c_span || c_hi < c_lo) rb[j] = ninf;
+            }
+          }
+          if (kseg_row != nullptr) {
+#pragma unroll
+            for (int j4 = 0; j4 < 8; ++j4) {
+              int ka[4], kb[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int ca = s0 + 4 * j4 + e, cb = ca + 32;
+                ka[e] = ca < p.S ? __ldg(kseg_row + ca) : -2;
+                kb[e] = cb < p.S ? __ldg(kseg_row + cb) : -2;
+              }
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                if (ka[e] != seg) ra[4 * j4 + e] = ninf;
+                if (kb[e] != seg) rb[4 * j4 + e] = ninf;
+              }
+            }
+          }
+        } else {
+          const int tile_t0 = t0 + x * 128;
+          const bool need_mask = (p.causal && s0 + 63 > tile_t0 + p.q_offset) || (s0 + 64 > p.S);
+          if (need_mask) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (s0 + j > c_hi) ra[j] = ninf;
+              if (s0 + 32 + j > c_hi) rb[j] = ninf;
+            }
+          }
+        }
+        // Row maximum: four independent chains over this half, then the other half's value.
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          mx0 = fmaxf(mx0, __uint_as_float(ra[j]));
+          mx1 = fmaxf(mx1, __uint_as_float(ra[j + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(rb[j]));
+          mx3 = fmaxf(mx3, __uint_as_float(rb[j + 1]));
+        }
+        tmax = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      }
+      my_max[kpar * 512] = got ? tmax : __uint_as_float(kGaveUp);
+      pair_barrier(bar_id);  // both halves have their scores in registers: P may overwrite S now
+      const float other = other_max[kpar * 512];
+      if (!got || __any_sync(0xffffffffu, __float_as_uint(other) == kGaveUp)) {
+        ok = false;
+        break;
+      }
+      tmax = fmaxf(tmax, other) * p.sc;  // sc > 0, so max commutes with scaling
+      float alpha = 1.f;
+      bool rescale = false;
+      if (tmax > m_ref + 8.f) {
+        if (m_ref != -INFINITY) {
+          alpha = exp2f(m_ref - tmax);
+          rescale = true;
+        }
+        m_ref = tmax;
+      }
+      if (__any_sync(0xffffffffu, rescale)) {
+        // s_full of this tile was committed after the previous P*V of this query tile, so O is
+        // quiescent; each half rescales its own O columns.
+#pragma unroll 1
+        for (int c = 0; c < H / 2; c += 32) {
+          uint32_t o[32];
+          tmem_ld_32x32(o_addr + c, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+          tmem_st_32x32(o_addr + c, o);
+        }
+        l_sum *= alpha;
+      }
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+      // Probabilities rounded to bf16 and packed two per register: q[j] = (p[2j], p[2j+1]).
+      uint32_t q[32];
+      float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float e0 = exp2f(__uint_as_float(ra[2 * j]) * p.sc - m_use);
+        const float e1 = exp2f(__uint_as_float(ra[2 * j + 1]) * p.sc - m_use);
+        q[j] = pack_bf16x2(e0, e1);
+        l0 += e0;
+        l1 += e1;
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float e0 = exp2f(__uint_as_float(rb[2 * j]) * p.sc - m_use);
+        const float e1 = exp2f(__uint_as_float(rb[2 * j + 1]) * p.sc - m_use);
+        q[16 + j] = pack_bf16x2(e0, e1);
+        l0 += e0;
+        l1 += e1;
+      }
+      l_sum += l0 + l1;
+      tmem_st_32x32(p_addr, q);
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[x]);
+    }
+    const int nt = my_hi - my_lo;
+    if (ok && nt > 0) {
+      ok = mbar_wait(&pv_done[x], 0, p.status, kStatusWaitTimeoutEpilogue);
+      tc_fence_after_sync();
+    }
+    // Total row sum = the two halves' partial sums.
+    ex_sum[(x * 2 + half) * 128 + r_in] = l_sum;
+    pair_barrier(bar_id);
+    l_sum += ex_sum[(x * 2 + (half ^ 1)) * 128 + r_in];
+    if (ok && row < p.T) {
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) +
+                            ((static_cast<int64_t>(batch) * p.T + row) * p.N + head) * H + half * (H / 2);
+      if (half == 0) {
+        p.lse[(static_cast<int64_t>(batch) * p.N + head) * p.T + row] =
+            (l_sum > 0.f) ? (m_ref * 0.6931471805599453f + logf(l_sum)) : -INFINITY;
+      }
+      if (nt == 0) {
+        for (int c = 0; c < H / 2; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    if (ok && nt > 0) {
+      const float inv_l = l_sum > 0.f ? 1.f / l_sum : 0.f;
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) +
+                            ((static_cast<int64_t>(batch) * p.T + row) * p.N + head) * H + half * (H / 2);
+#pragma unroll 1
+      for (int c = 0; c < H / 2; c += 32) {
+        uint32_t o[32];
+        tmem_ld_32x32(o_addr + c, o);
+        tmem_ld_wait();
+        if (row < p.T) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(o[8 * g + 0]) * inv_l, __uint_as_float(o[8 * g + 1]) * inv_l);
+            v.y = pack_bf16x2(__uint_as_float(o[8 * g + 2]) * inv_l, __uint_as_float(o[8 * g + 3]) * inv_l);
+            v.z = pack_bf16x2(__uint_as_float(o[8 * g + 4]) * inv_l, __uint_as_float(o[8 * g + 5]) * inv_l);
+            v.w = pack_bf16x2(__uint_as_float(o[8 * g + 6]) * inv_l, __uint_as_float(o[8 * g + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + c + 8 * g) = v;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) {
+      for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// For every (batch, 128-row query tile): the range [x, y) of 128-key tiles that contain at least
+// one key whose segment id lies within [min, max] of the query tile's ids.  One CTA per batch
+// row; key-tile minima / maxima are staged in shared memory (up to 2048 tiles = 256K keys).
+__global__ void seg_tile_ranges_kernel(const int* __restrict__ q_seg, const int* __restrict__ k_seg, int2* ranges,
+                                       int T, int S) {
+  __shared__ int kmin[2048], kmax[2048];
+  const int b = blockIdx.x;
+  const int n_kt = (S + 127) / 128, n_qt = (T + 127) / 128;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  for (int t = warp; t < n_kt; t += n_warps) {
+    int mn = INT_MAX, mx = INT_MIN;
+    for (int i = lane; i < 128; i += 32) {
+      const int c = t * 128 + i;
+      if (c < S) {
+        const int v = k_seg[static_cast<int64_t>(b) * S + c];
+        mn = min(mn, v), mx = max(mx, v);
+      }
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+      mn = min(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    }
+    if (lane == 0) kmin[t] = mn, kmax[t] = mx;
+  }
+  __syncthreads();
+  for (int t = warp; t < n_qt; t += n_warps) {
+    int mn = INT_MAX, mx = INT_MIN;
+    for (int i = lane; i < 128; i += 32) {
+      const int r = t * 128 + i;
+      if (r < T) {
+        const int v = q_seg[static_cast<int64_t>(b) * T + r];
+        mn = min(mn, v), mx = max(mx, v);
+      }
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+      mn = min(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+      mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    }
+    int first = INT_MAX, last = -1;
+    for (int kt = lane; kt < n_kt; kt += 32) {
+      if (kmax[kt] >= mn && kmin[kt] <= mx) first = min(first, kt), last = max(last, kt);
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+      first = min(first, __shfl_xor_sync(0xffffffffu, first, off));
+      last = max(last, __shfl_xor_sync(0xffffffffu, last, off));
+    }
+    if (lane == 0) ranges[b * n_qt + t] = last >= 0 ? make_int2(first, last + 1) : make_int2(0, 0);
+  }
+}
+
+template <int H, bool kGeneral>
+static int launch_flash_fwd3(const void* q, const void* k, const void* v, FlashFwd3Params p, cudaStream_t stream) {
+  CUtensorMap tq, tk, tv;
+  if (make_bthd_map(&tq, q, p.B, p.T, p.N, H, 128)) return -2;
+  if (make_bthd_map(&tk, k, p.B, p.S, p.Nkv, H, 128)) return -2;
+  if (make_bthd_map(&tv, v, p.B, p.S, p.Nkv, H, 128)) return -2;
+  auto kernel = flash_fwd3_kernel<H, kGeneral>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F3Smem<H>::kTotal) != cudaSuccess)
+      return -3;
+    configured = true;
+  }
+  dim3 grid((p.T + 255) / 256, p.N, p.B);
+  kernel<<<grid, kF3Threads, F3Smem<H>::kTotal, stream>>>(tq, tk, tv, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace axb
+
+// Writes, for every batch row and 128-row query tile, the range of 128-key tiles that can hold a
+// key of one of the tile's segments (see seg_tile_ranges_kernel).  ranges: int32 [B, ceil(T/128), 2].
+extern "C" int axb_seg_tile_ranges(const int* q_seg, const int* k_seg, int* ranges, int B, int T, int S,
+                                   cudaStream_t stream) {
+  if ((S + 127) / 128 > 2048) return -10;
+  axb::seg_tile_ranges_kernel<<<B, 256, 0, stream>>>(q_seg, k_seg, reinterpret_cast<int2*>(ranges), T, S);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// q: [B, T, N, H], k/v: [B, S, Nkv, H], out: [B, T, N, H] (bf16, contiguous); lse: [B, N, T] fp32.
+// causal: key s is visible to query t iff s <= t + (S - T).  window >= 0 additionally hides keys
+// with s < t + (S - T) - window.  q_seg [B, T] / k_seg [B, S] int32 (both or neither): a key is
+// visible only when the ids match; `ranges` (from axb_seg_tile_ranges) lets whole key tiles be
+// skipped.  logit_cap > 0 replaces a scaled score z by cap * tanh(z / cap).
+extern "C" int axb_flash_fwd_v3(const void* q, const void* k, const void* v, void* out, float* lse,
+                                const int* q_seg, const int* k_seg, const int* ranges, int B, int T, int S, int N,
+                                int Nkv, int H, float softmax_scale, int causal, int window, float logit_cap,
+                                int* status, cudaStream_t stream) {
+  using namespace axb;
+  if (N % Nkv != 0 || (H != 64 && H != 128)) return -10;
+  if ((q_seg == nullptr) != (k_seg == nullptr)) return -11;
+  FlashFwd3Params p;
+  p.out = out, p.lse = lse;
+  p.q_seg = q_seg, p.k_seg = k_seg, p.ranges = reinterpret_cast<const int2*>(ranges);
+  p.B = B, p.T = T, p.S = S, p.N = N, p.Nkv = Nkv, p.H = H;
+  const float log2e = 1.4426950408889634f;
+  if (logit_cap > 0.f) {
+    p.sc = 1.f, p.cap_in = softmax_scale / logit_cap, p.cap_out = logit_cap * log2e;
+  } else {
+    p.sc = softmax_scale * log2e, p.cap_in = 0.f, p.cap_out = 0.f;
+  }
+  p.causal = causal;
+  p.q_offset = S - T;
+  p.window = window;
+  p.status = status;
+  const bool general = q_seg != nullptr || window >= 0 || logit_cap > 0.f;
+  if (H == 128) {
+    return general ? launch_flash_fwd3<128, true>(q, k, v, p, stream) : launch_flash_fwd3<128, false>(q, k, v, p, stream);
+  }
+  return general ? launch_flash_fwd3<64, true>(q, k, v, p, stream) : launch_flash_fwd3<64, false>(q, k, v, p, stream);
+}

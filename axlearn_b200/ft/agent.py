@@ -55,6 +55,13 @@ class TrainerProcess:
     def __init__(self, command: Sequence[str], *, env: Optional[dict] = None, log_path: Optional[str] = None,
                  on_line: Optional[Callable[[str], None]] = None):
         self._log = open(log_path, "a", encoding="utf-8") if log_path else None  # pylint: disable=consider-using-with
+        # A supervised trainer may be killed at any moment (kill() below).  A rank that dies while
+        # its memory is bound to an NVLink multicast object raises NVLink faults on its peers'
+        # GPUs, so supervised runs keep NCCL's in-switch reduction and symmetric-memory multicast
+        # off unless the caller's environment says otherwise.
+        env = dict(os.environ if env is None else env)
+        env.setdefault("NCCL_NVLS_ENABLE", "0")
+        env.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         self.proc = subprocess.Popen(  # pylint: disable=consider-using-with
             list(command), stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env,
             start_new_session=True)

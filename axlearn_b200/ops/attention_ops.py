@@ -23,33 +23,54 @@ def _has(symbol: str) -> bool:
     return hasattr(cuda_ops.lib(), symbol)
 
 
-def flash_supported(q, k, v, segment_ids) -> bool:
+def flash_supported(q, k, v, segment_ids=None) -> bool:
+    """Head dims 64 / 128 with grouped KV heads; causal, segment-id, sliding-window and
+    logit-cap masks all run inside the kernels."""
     h = q.shape[-1]
-    return h in (64, 128) and q.shape[2] % k.shape[2] == 0 and segment_ids is None
+    if segment_ids is not None and (segment_ids.dim() != 2 or segment_ids.shape[1] != q.shape[1]):
+        return False
+    return h in (64, 128) and q.shape[2] % k.shape[2] == 0
 
 
 class _FlashAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, causal, scale):
+    def forward(ctx, q, k, v, causal, scale, q_seg, k_seg, window, logit_cap):
         from axlearn_b200.ops import flash_sm100
 
-        out, lse = flash_sm100.forward(q, k, v, causal=causal, scale=scale)
-        ctx.save_for_backward(q, k, v, out, lse)
-        ctx.causal, ctx.scale = causal, scale
+        ranges = flash_sm100.segment_tile_ranges(q_seg, k_seg) if q_seg is not None else None
+        out, lse = flash_sm100.forward(q, k, v, causal=causal, scale=scale, q_seg=q_seg, k_seg=k_seg,
+                                       ranges=ranges, window=window, logit_cap=logit_cap)
+        ctx.save_for_backward(q, k, v, out, lse, q_seg, k_seg)
+        ctx.causal, ctx.scale, ctx.window, ctx.logit_cap = causal, scale, window, logit_cap
         return out
 
     @staticmethod
     def backward(ctx, dout):
         from axlearn_b200.ops import flash_sm100
 
-        q, k, v, out, lse = ctx.saved_tensors
-        dq, dk, dv = flash_sm100.backward(q, k, v, out, lse, dout.contiguous(), causal=ctx.causal, scale=ctx.scale)
-        return dq, dk, dv, None, None
+        q, k, v, out, lse, q_seg, k_seg = ctx.saved_tensors
+        k_ranges = flash_sm100.segment_tile_ranges(k_seg, q_seg) if q_seg is not None else None
+        dq, dk, dv = flash_sm100.backward(
+            q, k, v, out, lse, dout.contiguous(), causal=ctx.causal, scale=ctx.scale, q_seg=q_seg, k_seg=k_seg,
+            k_ranges=k_ranges, window=ctx.window, logit_cap=ctx.logit_cap)
+        return dq, dk, dv, None, None, None, None, None, None
 
 
-def flash_attention(q, k, v, *, causal: bool, softmax_scale: Optional[float], segment_ids=None):
+def flash_attention(q, k, v, *, causal: bool, softmax_scale: Optional[float], segment_ids=None,
+                    kv_segment_ids=None, sliding_window: Optional[int] = None, logit_cap: Optional[float] = None):
+    """``segment_ids [B, T]`` (and ``kv_segment_ids [B, S]``, default the same tensor): a query
+    sees only keys of its own segment.  ``sliding_window``: keys more than that many positions
+    before the query are hidden.  ``logit_cap``: scaled scores become ``cap * tanh(s / cap)``."""
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(q.shape[-1])
-    return _FlashAttention.apply(q.contiguous(), k.contiguous(), v.contiguous(), bool(causal), float(scale))
+    q_seg = k_seg = None
+    if segment_ids is not None:
+        q_seg = segment_ids.to(torch.int32).contiguous()
+        k_seg = q_seg if kv_segment_ids is None else kv_segment_ids.to(torch.int32).contiguous()
+        if k_seg.shape[1] != k.shape[1]:
+            raise ValueError("kv_segment_ids must be given when the key length differs from the query length")
+    return _FlashAttention.apply(
+        q.contiguous(), k.contiguous(), v.contiguous(), bool(causal), float(scale), q_seg, k_seg,
+        None if sliding_window is None else int(sliding_window), None if not logit_cap else float(logit_cap))
 
 
 def paged_kv_append(pages: torch.Tensor, new: torch.Tensor, page_ids: torch.Tensor, offsets: torch.Tensor):

@@ -532,10 +532,11 @@ def flash_supported(q, k, v, segment_ids) -> bool:
     return attention_ops.flash_supported(q, k, v, segment_ids)
 
 
-def flash_attention(q, k, v, *, causal: bool, softmax_scale: Optional[float], segment_ids=None):
+def flash_attention(q, k, v, *, causal: bool, softmax_scale: Optional[float], segment_ids=None, **masks):
     from axlearn_b200.ops import attention_ops
 
-    return attention_ops.flash_attention(q, k, v, causal=causal, softmax_scale=softmax_scale, segment_ids=segment_ids)
+    return attention_ops.flash_attention(q, k, v, causal=causal, softmax_scale=softmax_scale, segment_ids=segment_ids,
+                                         **masks)
 
 
 def paged_kv_append(pages, new, page_ids, offsets):

@@ -136,6 +136,10 @@ class OneShotAllReduce:
                  rank: int = 0):
         from axlearn_b200.parallel import symm
 
+        # With one site a rank that has finished step k could push step k+1 into a peer's slot
+        # while that peer still reads it in step k's finish kernel; two sites alternate.
+        if sites < 2:
+            raise ValueError("OneShotAllReduce needs sites >= 2 (staging is reused across steps)")
         self.numel, self.sites = numel, sites
         if peers is not None:
             # Single-process emulation: `peers[r]` is another instance whose buffers stand in

@@ -87,13 +87,15 @@ def attention(
         _cuda(q, k, v)
         and q.dtype == torch.bfloat16
         and bias is None
-        and logit_cap is None
         and dropout_mask is None
-        and sliding_window is None
+        and (segment_ids is None or q.shape[1] == k.shape[1])
         and _ops().flash_supported(q, k, v, segment_ids)
     ):
+        # Segment ids, the sliding window and the logit cap are masks of the kernel itself; only an
+        # arbitrary additive bias or a dropout mask needs the materialised [T, S] path below.
         return _ops().flash_attention(
-            q, k, v, causal=causal, softmax_scale=softmax_scale, segment_ids=segment_ids
+            q, k, v, causal=causal, softmax_scale=softmax_scale, segment_ids=segment_ids,
+            sliding_window=sliding_window, logit_cap=logit_cap
         )
     return reference.attention(
         q,

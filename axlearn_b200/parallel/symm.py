@@ -14,7 +14,7 @@ In single-process tests ``FakePeers`` stands in: "peers" are just other local te
 from __future__ import annotations
 
 import bisect
-import ctypes
+import os
 from typing import Optional, Sequence
 
 import torch
@@ -27,6 +27,10 @@ class SymmetricBuffer:
     """One symmetric allocation of ``numel`` elements of ``dtype`` on every rank of ``group``."""
 
     def __init__(self, numel: int, dtype: torch.dtype, group, device: torch.device):
+        # The kernels use unicast peer pointers only.  Without this switch the rendezvous also
+        # binds every allocation to an NVLink multicast object, which buys nothing here and turns
+        # a rank that exits abruptly (watchdog or supervisor kill) into NVLink faults on its peers.
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
 
         self.group = group
@@ -41,7 +45,7 @@ class SymmetricBuffer:
         self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
         self.nbytes = numel * self.tensor.element_size()
         start = self.tensor.data_ptr()
-        bisect.insort(_registry, (start, start + self.nbytes, self))
+        bisect.insort(_registry, (start, start + self.nbytes, self), key=lambda e: e[0])
 
     def peer_addresses(self, t: torch.Tensor) -> list[int]:
         """Addresses of the peers' copies of ``t`` (a view into this buffer)."""
@@ -56,9 +60,7 @@ class SymmetricBuffer:
 
 def find(t: torch.Tensor) -> Optional[SymmetricBuffer]:
     ptr = t.data_ptr()
-    i = bisect.bisect_right(_registry, (ptr, float("inf"), None)) - 1 if _registry else -1
-    # bisect on tuples with a None tail can fail to compare; scan instead (few buffers exist).
-    for start, end, buf in _registry:
+    for start, end, buf in _registry:  # few buffers exist: a scan is enough
         if start <= ptr < end:
             return buf
     return None

@@ -99,7 +99,7 @@ def test_gemm_with_all_reduce_push_epilogue_emulated():
     from axlearn_b200.ops import cuda_ops, decode_ops
 
     world, m, k, n = 2, 64, 256, 512
-    ranks = [decode_ops.OneShotAllReduce(m * n, 1, device="cuda", peers=[None] * world, rank=r) for r in range(world)]
+    ranks = [decode_ops.OneShotAllReduce(m * n, 2, device="cuda", peers=[None] * world, rank=r) for r in range(world)]
     for r in ranks:
         r.connect(ranks)
     a = [torch.randn(m, k, device="cuda").bfloat16() for _ in range(world)]
