@@ -29,6 +29,7 @@ import torch
 
 from axlearn_b200 import ops
 from axlearn_b200.common import attention_bias as ab
+from axlearn_b200.common import remat
 from axlearn_b200.common.attention_bias import (
     NEG_INF,
     BaseAttentionBias,
@@ -816,7 +817,8 @@ class MultiheadAttention(BaseLayer):
             time_step = cached_states["time_step"]
             query_positions = query_positions + time_step[:, None]
             key_positions = key_positions + time_step[:, None] if key is None else key_positions
-        q_proj, k_proj, v_proj = self.i_proj(query, query_positions=query_positions, **kv_kwargs)
+        with remat.tagged(self, ("q_proj", "k_proj", "v_proj")):
+            q_proj, k_proj, v_proj = self.i_proj(query, query_positions=query_positions, **kv_kwargs)
         q_proj = self._remat_name(q_proj, "q_proj")
         k_proj = self._remat_name(k_proj, "k_proj")
         v_proj = self._remat_name(v_proj, "v_proj")
@@ -879,21 +881,25 @@ class MultiheadAttention(BaseLayer):
         # self-attention called without explicit positions.
         plain_positions = mode == ForwardMode.FORWARD and is_self_attention and default_positions
         want_probs = return_aux is not None and "probs" in return_aux
+        # Causal, sliding-window, segment-id and logit-cap masking all happen inside the attention
+        # kernel; an arbitrary bias, a logit sink, dropout or a request for the probabilities need
+        # the materialised path.
         fast = (
             plain_positions
             and not user_bias.has_value()
             and generic_fn is None
-            and window is None
-            and cfg.atten_logit_cap is None
+            and (window is None or causal)
             and not cfg.logit_sink
             and not want_probs
             and not (self.is_training and cfg.dropout.rate)
         )
         if fast:
-            context = ops.attention(
-                q_proj, dense_kv.k_proj, dense_kv.v_proj, causal=causal,
-                softmax_scale=softmax_scale, segment_ids=segment_ids,
-            )
+            with remat.tagged(self, "context"):
+                context = ops.attention(
+                    q_proj, dense_kv.k_proj, dense_kv.v_proj, causal=causal,
+                    softmax_scale=softmax_scale, segment_ids=segment_ids,
+                    sliding_window=window, logit_cap=cfg.atten_logit_cap,
+                )
             probs = None
         else:
             biases: list[BaseAttentionBias] = [user_bias]
@@ -918,7 +924,8 @@ class MultiheadAttention(BaseLayer):
         if sp > 1:
             context = coll.all_to_all(context, "seq", split_dim=1, concat_dim=2)
         context = self._remat_name(context, "context")
-        o = self.o_proj(context)
+        with remat.tagged(self, "o_proj"):
+            o = self.o_proj(context)
         o = self._remat_name(o, "o_proj")
         out_kv = None
         if return_aux is not None and "kv_state" in return_aux:
@@ -1275,8 +1282,10 @@ class TransformerFeedForwardLayer(BaseLayer):
     def _mlp(self, x: Tensor) -> Tensor:
         cfg = self._config
         if isinstance(cfg.activation, (tuple, list)):
-            a0 = self._remat_name(self.linear1_0(x), "linear1_0")
-            a1 = self._remat_name(self.linear1_1(x), "linear1_1")
+            with remat.tagged(self, "linear1_0"):
+                a0 = self._remat_name(self.linear1_0(x), "linear1_0")
+            with remat.tagged(self, "linear1_1"):
+                a1 = self._remat_name(self.linear1_1(x), "linear1_1")
             if tuple(cfg.activation) == ("nn.silu", "linear"):
                 h = ops.swiglu(a0, a1)
             elif tuple(cfg.activation) == ("linear", "nn.silu"):
@@ -1284,11 +1293,13 @@ class TransformerFeedForwardLayer(BaseLayer):
             else:
                 h = get_activation_fn(cfg.activation[0])(a0) * get_activation_fn(cfg.activation[1])(a1)
         else:
-            h = get_activation_fn(cfg.activation)(self._remat_name(self.linear1(x), "linear1_0"))
+            with remat.tagged(self, "linear1_0"):
+                h = get_activation_fn(cfg.activation)(self._remat_name(self.linear1(x), "linear1_0"))
         if cfg.add_dead_neuron_summary:
             self.add_summary("dead_neurons", (h.detach() <= 0).float().mean())
         h = self.dropout1(h)
-        return self._remat_name(self.linear2(h), "linear2")
+        with remat.tagged(self, "linear2"):
+            return self._remat_name(self.linear2(h), "linear2")
 
     def forward(self, inputs: Tensor) -> Tensor:
         cfg = self._config
@@ -1553,15 +1564,8 @@ class RematRegexSavePatterns(enum.Enum):
     FLASH_ATTENTION = "|".join([FLASH_CONTEXT, QKV_PROJ, O_PROJ])
 
 
-def save_only_these_names_regex(pattern: str):
-    """Policy object recording the save pattern (kept for config parity; the eager runtime
-    keeps inputs only)."""
-
-    def policy(*_, **__):
-        return False
-
-    policy.pattern = pattern
-    return policy
+save_only_these_names_regex = remat.save_only_these_names_regex
+save_and_offload_only_these_names_regex = remat.save_and_offload_only_these_names_regex
 
 
 def build_remat_spec(
@@ -1570,11 +1574,16 @@ def build_remat_spec(
     offload_pattern: Any = None,
     offload_dst: str = "pinned_host",
 ) -> Optional[RematSpec]:
-    """Remat spec for the layers of ``stack_cfg``; None for pipelined stacks."""
-    del offload_pattern, offload_dst
+    """Remat spec for the layers of ``stack_cfg``: tensors tagged with a name matching
+    ``save_pattern`` are kept on the device between the first pass and the replay, those matching
+    ``offload_pattern`` in pinned host memory, everything else is recomputed (reference:
+    axlearn/common/attention.py:4574-4653).  None for pipelined stacks."""
     if getattr(stack_cfg, "klass", None) is not None and stack_cfg.klass.__name__ == "PipelinedTransformerLayer":
         return None
-    return RematSpec(prevent_cse=False, policy=config_for_function(save_only_these_names_regex).set(pattern=save_pattern))
+    policy = config_for_function(save_and_offload_only_these_names_regex).set(
+        names_which_can_be_saved=save_pattern, names_which_can_be_offloaded=offload_pattern,
+        offload_src="device", offload_dst=offload_dst)
+    return RematSpec(prevent_cse=False, policy=policy)
 
 
 def set_double_shard_weights_config(

@@ -91,8 +91,9 @@ class ParameterSpec(TensorSpec):
 NestedParameterSpec = Union[ParameterSpec, dict]
 
 
-# Remat policies. Only the distinction "keep everything" vs "keep inputs only" is
-# observable in an eager runtime; the names match the reference's policy vocabulary.
+# Remat policies.  ``everything_saveable`` switches rematerialisation off, ``nothing_saveable``
+# keeps only a layer's inputs; the selective policies (by tagged name, all projection GEMMs, with
+# or without offload to pinned host memory) live in ``axlearn_b200.common.remat``.
 def everything_saveable(*_, **__):
     return True
 
@@ -101,8 +102,13 @@ def nothing_saveable(*_, **__):
     return False
 
 
-def dots_saveable(*_, **__):
-    return False
+from axlearn_b200.common.remat import (  # noqa: E402  pylint: disable=wrong-import-position
+    dots_saveable,
+    offload_dots_saveable,
+    save_and_offload_only_these_names_regex,
+    save_only_these_names,
+    save_only_these_names_regex,
+)
 
 
 @dataclasses.dataclass
@@ -117,6 +123,13 @@ class RematSpec:
     def saves_everything(self) -> bool:
         pol = maybe_instantiate(self.policy) if isinstance(self.policy, InstantiableConfig) else self.policy
         return pol is everything_saveable
+
+    def selective_policy(self):
+        """The ``remat.RematPolicy`` that names what a replayed layer keeps, or None (keep inputs
+        only)."""
+        from axlearn_b200.common import remat
+
+        return remat.as_policy(self.policy)
 
 
 @dataclasses.dataclass
@@ -183,15 +196,18 @@ class _Remat(torch.autograd.Function):
     """Runs ``run(tensors) -> tuple[Tensor]`` keeping only ``tensors`` for backward."""
 
     @staticmethod
-    def forward(ctx, run, *tensors):  # pylint: disable=arguments-differ
+    def forward(ctx, run, policy, *tensors):  # pylint: disable=arguments-differ
+        from axlearn_b200.common import remat
         from axlearn_b200.parallel.mesh import current_mesh
+
+        ctx.stash = remat.LayerStash(policy) if policy is not None else None
 
         ctx.run = run
         ctx.needs = [t.requires_grad for t in tensors]
         # The replay runs on an autograd worker thread, whose thread-local mesh stack is empty.
         ctx.mesh = current_mesh()
         ctx.save_for_backward(*tensors)
-        with torch.no_grad():
+        with torch.no_grad(), remat.recording(ctx.stash):
             outs = run(tensors, first_pass=True)
         return tuple(outs)
 
@@ -211,12 +227,16 @@ class _Remat(torch.autograd.Function):
             t.detach().requires_grad_(need) if t.is_floating_point() else t.detach()
             for t, need in zip(tensors, ctx.needs)
         ]
-        with torch.enable_grad():
+        from axlearn_b200.common import remat
+
+        with torch.enable_grad(), remat.replaying(ctx.stash):
             outs = ctx.run(replay, first_pass=False)
+        if ctx.stash is not None:
+            ctx.stash.clear()
         pairs = [(o, g) for o, g in zip(outs, grads) if g is not None and o.requires_grad]
         if pairs:
             torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
-        return (None,) + tuple(
+        return (None, None) + tuple(
             (r.grad if need and r.is_floating_point() else None)
             for r, need in zip(replay, ctx.needs)
         )
@@ -250,9 +270,10 @@ class _Slot:
     i: int
 
 
-def remat_call(fn: Callable, *, state: Any, args: tuple, kwargs: dict) -> Any:
+def remat_call(fn: Callable, *, state: Any, args: tuple, kwargs: dict, policy: Any = None) -> Any:
     """Calls ``fn(*args, **kwargs)`` in the current invocation context with
-    rematerialisation: only the tensor leaves of (state, args, kwargs) are kept."""
+    rematerialisation: only the tensor leaves of (state, args, kwargs) are kept, plus what the
+    selective ``policy`` (a ``remat.RematPolicy``) names."""
     ctx = current_context()
     in_tensors, rebuild_inputs = _flatten_tensors({"state": state, "args": args, "kwargs": kwargs})
     out_box: dict[str, Any] = {}
@@ -269,7 +290,7 @@ def remat_call(fn: Callable, *, state: Any, args: tuple, kwargs: dict) -> Any:
             out_box["rebuild"] = rebuild_out
         return out_tensors
 
-    outs = _Remat.apply(run, *in_tensors)
+    outs = _Remat.apply(run, policy, *in_tensors)
     return out_box["rebuild"](list(outs))
 
 
@@ -351,7 +372,7 @@ class BaseLayer(Module):
             and not getattr(fn, "__no_remat__", False)
         ):
             bound = lambda *a, **k: fn(self, *a, **k)
-            return remat_call(bound, state=ctx.state, args=args, kwargs=kwargs)
+            return remat_call(bound, state=ctx.state, args=args, kwargs=kwargs, policy=spec.selective_policy())
         return fn(self, *args, **kwargs)
 
     # ------------------------------------------------------------------ parameter specs

@@ -62,6 +62,12 @@ class _LayerCall(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, run, gatherer, i, n_inputs, remat, *tensors):  # pylint: disable=arguments-differ
+        # `remat`: False (keep the graph), True (keep the inputs only) or a remat.RematPolicy
+        # (keep the inputs and what the policy names; the replay skips what was kept).
+        from axlearn_b200.common import remat as remat_lib
+
+        ctx.stash = remat_lib.LayerStash(remat) if isinstance(remat, remat_lib.RematPolicy) else None
+        remat = bool(remat)
         ctx.run, ctx.gatherer, ctx.i, ctx.n_inputs, ctx.remat = run, gatherer, i, n_inputs, remat
         # Backward runs on an autograd worker thread, where the thread-local mesh stack is empty.
         ctx.mesh = current_mesh()
@@ -72,7 +78,7 @@ class _LayerCall(torch.autograd.Function):
         gatherer.prefetch(i + 1)
         if remat:
             ctx.save_for_backward(*inputs)
-            with torch.no_grad():
+            with torch.no_grad(), remat_lib.recording(ctx.stash):
                 outs = run(inputs, params, first_pass=True)
             return tuple(outs)
         # No remat: build and keep an inner graph.
@@ -97,10 +103,14 @@ class _LayerCall(torch.autograd.Function):
             inputs = ctx.saved_tensors
             params = gatherer.get(i)
             gatherer.prefetch(i - 1)
-            with torch.enable_grad():
+            from axlearn_b200.common import remat as remat_lib
+
+            with torch.enable_grad(), remat_lib.replaying(ctx.stash):
                 in_d = [t.detach().requires_grad_(n) if t.is_floating_point() else t.detach() for t, n in zip(inputs, ctx.needs)]
                 p_d = [p.detach().requires_grad_(n) for p, n in zip(params, ctx.param_needs)]
                 outs = ctx.run(in_d, p_d, first_pass=False)
+            if ctx.stash is not None:
+                ctx.stash.clear()
         else:
             in_d, p_d, outs = ctx.inner
             ctx.inner = None
@@ -204,6 +214,8 @@ class Repeat(BaseLayer):
         remat_spec = getattr(layer_cfg, "remat_spec", None)
         training = ctx.is_training and torch.is_grad_enabled()
         use_remat = bool(training and remat_spec is not None and not remat_spec.saves_everything())
+        # A selective policy (names to keep / offload) rides along in place of the plain flag.
+        remat_arg = (remat_spec.selective_policy() or True) if use_remat else False
         gatherer = self._gatherer(stacked_params, remat=use_remat or not training)
         needs_param_grads = training and any(t.requires_grad for t in param_leaves)
         via_function = needs_param_grads and (use_remat or gatherer.sharded or True)
@@ -235,7 +247,7 @@ class Repeat(BaseLayer):
 
             if via_function:
                 outs = _LayerCall.apply(
-                    run, gatherer, i, len(in_tensors), use_remat, *in_tensors, *param_leaves
+                    run, gatherer, i, len(in_tensors), remat_arg, *in_tensors, *param_leaves
                 )
             else:
                 params = gatherer.get(i)

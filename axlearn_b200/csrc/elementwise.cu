@@ -7,6 +7,7 @@
 // 374-417 (RMSNorm), axlearn/common/attention.py:1301-1349 (RoPE), :3354-3370 (SwiGLU),
 // axlearn/common/loss.py:234-327 (cross entropy) and axlearn/common/optimizers.py:741-856,
 // 1149-1184 (AdamW chain, global-norm clip).
+#include "no_alloc.h"
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
@@ -637,7 +638,9 @@ extern "C" int axb_rmsnorm_fwd(const void* x, const void* residual, const void* 
 
 // Number of CTAs (= rows of the fp32 `partial` workspace [ctas, D]) the backward will use.
 extern "C" int axb_rmsnorm_bwd_ctas(int64_t rows) {
-  return static_cast<int>(rows < 148 * 2 ? rows : 148 * 2);
+  // The allocation-free variant (no_alloc.cu) sizes its built-in workspace with the same constant
+  // and promises bit-equal results, which needs the same grid: keep both on the one definition.
+  return static_cast<int>(rows < AXB_NOALLOC_RMSNORM_MAX_CTAS ? rows : AXB_NOALLOC_RMSNORM_MAX_CTAS);
 }
 
 extern "C" int axb_rmsnorm_bwd(const void* x, const void* scale, const float* rstd, const void* dy,

@@ -41,6 +41,9 @@ namespace axb {
 int make_bthd_map(CUtensorMap* map, const void* base, int B, int L, int N, int H, int box_rows);
 
 constexpr int kFbThreads = 512;
+// Register budget: 512 threads launch with 128 registers each; setmaxnreg only redistributes that
+// launch-time allocation (control 4 warps x 80, exponential / dS 8 warps x 160, drain 4 warps x 112).
+static_assert(128 * 80 + 256 * 160 + 128 * 112 <= 512 * 128, "setmaxnreg split exceeds the launch allocation");
 constexpr int kFbSub = 16384;  // [128 x 64] bf16
 
 struct FlashBwdFusedParams {
@@ -401,8 +404,8 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       const bool need_mask = c_min > half * 64 || c_max < half * 64 + 63;
       const float* lse_s = reinterpret_cast<const float*>(smem + L::kLse + st * 1024) + half * 64;
       const float* delta_s = lse_s + 128;
-      if (!mbar_wait(&q_full[st], (it >> 1) & 1, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
-      if (!mbar_wait(s_full, it & 1, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
+      if (!mbar_wait_warp(&q_full[st], (it >> 1) & 1, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
+      if (!mbar_wait_warp(s_full, it & 1, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
       tc_fence_after_sync();
       float pf[64];  // P (times 1 - tanh^2 under a logit cap): the factor of dS
       {
@@ -449,10 +452,10 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
       // dS^T = P^T (dP^T - delta): needs dP^T of this pair and the shared-memory tile free.
-      if (!mbar_wait(dp_full, it & 1, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
+      if (!mbar_wait_warp(dp_full, it & 1, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
       tc_fence_after_sync();
       if (it > 0) {
-        if (!mbar_wait(ds_free, (it - 1) & 1, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
+        if (!mbar_wait_warp(ds_free, (it - 1) & 1, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
       }
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
@@ -476,8 +479,9 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       if (lane == 0) mbar_arrive(ds_full);
     }
     // Epilogue: lane = key; each half stores half of the columns of dK (scaled) and dV.
-    if (ok) ok = mbar_wait(acc_done, 0, p.status, kStatusWaitTimeoutEpilogue);
-    if ((ok || (aligned && n_iters == 0)) && key < p.S) {
+    if (ok) ok = mbar_wait_warp(acc_done, 0, p.status, kStatusWaitTimeoutEpilogue);
+    if (ok || (aligned && n_iters == 0)) {
+      // tcgen05.ld is warp-collective: every lane runs the loads, only lanes with a real key store.
       tc_fence_after_sync();
       const int64_t orow = ((static_cast<int64_t>(batch) * p.S + key) * p.Nkv + kv_head) * H;
 #pragma unroll 1
@@ -495,14 +499,16 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 #pragma unroll
             for (int j = 0; j < 32; ++j) r[j] = 0;
           }
+          if (key < p.S) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(r[8 * g + 0]) * mul, __uint_as_float(r[8 * g + 1]) * mul);
-            o.y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * mul, __uint_as_float(r[8 * g + 3]) * mul);
-            o.z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * mul, __uint_as_float(r[8 * g + 5]) * mul);
-            o.w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * mul, __uint_as_float(r[8 * g + 7]) * mul);
-            *reinterpret_cast<uint4*>(dst + c + 8 * g) = o;
+            for (int g = 0; g < 4; ++g) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r[8 * g + 0]) * mul, __uint_as_float(r[8 * g + 1]) * mul);
+              o.y = pack_bf16x2(__uint_as_float(r[8 * g + 2]) * mul, __uint_as_float(r[8 * g + 3]) * mul);
+              o.z = pack_bf16x2(__uint_as_float(r[8 * g + 4]) * mul, __uint_as_float(r[8 * g + 5]) * mul);
+              o.w = pack_bf16x2(__uint_as_float(r[8 * g + 6]) * mul, __uint_as_float(r[8 * g + 7]) * mul);
+              *reinterpret_cast<uint4*>(dst + c + 8 * g) = o;
+            }
           }
         }
       }
@@ -518,7 +524,7 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       const int head = kv_head * group + it / tiles_per_head;
       const int qt = i_lo + it % tiles_per_head;
       float* tile = p.dq_acc + ((static_cast<int64_t>(batch) * p.N + head) * n_qt + qt) * (H * 128) + r_in * 4;
-      if (!mbar_wait(dq_full, it & 1, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
+      if (!mbar_wait_warp(dq_full, it & 1, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
       tc_fence_after_sync();
 #pragma unroll
       for (int c = 0; c < H; c += 64) {

@@ -28,6 +28,11 @@ namespace axb {
 int make_bthd_map(CUtensorMap* map, const void* base, int B, int L, int N, int H, int box_rows);
 
 constexpr int kF3Threads = 640;
+// Register budget.  640 threads launch with 96 registers each (61440 in all); setmaxnreg only moves
+// registers around INSIDE that launch-time allocation (an increase that asks for more than the
+// decreases released waits forever), so control (4 warps x 64) + softmax (16 warps x 104) must
+// not exceed it.
+static_assert(128 * 64 + 512 * 104 <= 640 * 96, "setmaxnreg split exceeds the launch allocation");
 constexpr uint32_t kGaveUp = 0x7fc0dead;  // NaN payload: "my wait on the score tile timed out"
 
 struct FlashFwd3Params {
@@ -67,6 +72,25 @@ __device__ __forceinline__ float tanh_approx(float x) {
   return y;
 }
 
+// 2^x for x <= 0 (x = -inf allowed) on the FMA and integer pipes: the exponential unit is the
+// scarcest resource of the softmax (16 results per clock and SM), so a fixed share of the
+// exponentials is evaluated here instead.  Round-to-nearest split x = n + f with f in
+// [-0.5, 0.5] through the 1.5 * 2^23 trick, a degree-3 minimax polynomial for 2^f (relative
+// error 7.5e-5, far below the bf16 rounding of the result) and n added into the exponent field.
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -126.f);
+  const float r = __fadd_rn(x, 12582912.f);
+  const float f = __fsub_rn(x, __fsub_rn(r, 12582912.f));
+  float p = fmaf(0.0551716685f, f, 0.2426111251f);
+  p = fmaf(p, f, 0.6932609677f);
+  p = fmaf(p, f, 0.9999280572f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(r) << 23));
+}
+
+// Of every 8 probability pairs, this many are evaluated with exp2_poly (the rest on the
+// exponential unit).
+constexpr int kPolyOf8 = 3;
+
 // kGeneral: segment ids / sliding window / logit cap are honoured (every tile takes the masking
 // path when segment ids are present).  The plain instantiation only masks diagonal and ragged
 // tiles.
@@ -81,9 +105,10 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBar);
   uint64_t* q_full = bars + 0;
   uint64_t* k_full = bars + 1;    // [2]
-  uint64_t* k_empty = bars + 3;   // [2]
+  uint64_t* it_done = bars + 3;   // [2]: MMA iteration g (ring index) releases V stage g & 1 and
+                                  //      K stage (g + 1) & 1 with ONE commit on it_done[g & 1];
+                                  //      the prologue counts as iteration -1
   uint64_t* v_full = bars + 5;    // [2]
-  uint64_t* v_empty = bars + 7;   // [2]
   uint64_t* s_full = bars + 9;    // [2] per query tile
   uint64_t* p_full = bars + 11;   // [2] per query tile, 8 arrivals
   uint64_t* pv_done = bars + 13;  // [2] per query tile, completes once
@@ -132,9 +157,8 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], 1);
+      mbar_init(&it_done[i], 1);
       mbar_init(&v_full[i], 1);
-      mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 8);
       mbar_init(&pv_done[i], 1);
@@ -166,14 +190,22 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       for (int it = g_lo; it < g_hi; ++it) {
         const int g = it - g_lo;
         const int st = g & 1;
-        const uint32_t ph = (g >> 1) & 1;
-        if (!mbar_wait(&k_empty[st], ph ^ 1, p.status, kStatusWaitTimeoutProducer)) break;
+        // K(g) reuses the stage of K(g - 2), last read by the scores issued in iteration g - 3;
+        // V(g) reuses the stage of V(g - 2), last read in iteration g - 2.  Completion number k
+        // of it_done[1] belongs to iteration 2k - 1, of it_done[0] to iteration 2k.
+        if (g >= 2) {
+          const int k_need = (g & 1) ? (g - 3) / 2 : (g - 2) / 2;
+          if (!mbar_wait(&it_done[(g + 1) & 1], k_need & 1, p.status, kStatusWaitTimeoutProducer)) break;
+        }
         mbar_arrive_expect_tx(&k_full[st], L::kTile);
 #pragma unroll
         for (int j = 0; j < H / 64; ++j)
           tma_load_4d(smem + L::kK + st * L::kTile + j * L::kSub, &tmap_k, &k_full[st], j * 64, kv_head,
                       it * 128, batch);
-        if (!mbar_wait(&v_empty[st], ph ^ 1, p.status, kStatusWaitTimeoutProducer)) break;
+        if (g >= 2) {
+          const int v_need = (g & 1) ? (g - 1) / 2 : (g - 2) / 2;
+          if (!mbar_wait(&it_done[g & 1], v_need & 1, p.status, kStatusWaitTimeoutProducer)) break;
+        }
         mbar_arrive_expect_tx(&v_full[st], L::kTile);
 #pragma unroll
         for (int j = 0; j < H / 64; ++j)
@@ -214,7 +246,7 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         tc_fence_after_sync();
         for (int x = 0; x < 2; ++x)
           if (hi[x] > lo[x] && lo[x] == g_lo) issue_qk(x, 0);
-        tc_commit(&k_empty[0]);
+        tc_commit(&it_done[1]);
       }
       for (int it = g_lo; it < g_hi && ok; ++it) {
         const int g = it - g_lo;
@@ -241,14 +273,13 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           }
         }
         if (!ok) break;
-        tc_commit(&v_empty[st]);
-        if (has_next) tc_commit(&k_empty[st ^ 1]);
+        tc_commit(&it_done[st]);
       }
     }
   }
   } else {
     // ------------------------------------------------------------------ softmax / epilogue
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
     const int idx = warp - 4;
     const int x = idx >> 3;               // query tile
     const int half = (idx >> 2) & 1;      // which 64 score columns / which half of the O columns
@@ -282,7 +313,7 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       const int kpar = (it - my_lo) & 1;
       // A wait that gives up must not leave the partner warp alone at the named barrier: both
       // halves always reach it, and a failed wait travels through the exchange slot.
-      const bool got = __all_sync(0xffffffffu, mbar_wait(&s_full[x], kpar, p.status, kStatusWaitTimeoutEpilogue));
+      const bool got = mbar_wait_warp(&s_full[x], kpar, p.status, kStatusWaitTimeoutEpilogue);
       uint32_t ra[32], rb[32];
       float tmax = -INFINITY;
       if (got) {
@@ -380,26 +411,35 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       }
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
       // Probabilities rounded to bf16 and packed two per register: q[j] = (p[2j], p[2j+1]).
-      uint32_t q[32];
+      uint32_t qa[16], qb[16];
       float l0 = 0.f, l1 = 0.f;
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
-        const float e0 = exp2f(__uint_as_float(ra[2 * j]) * p.sc - m_use);
-        const float e1 = exp2f(__uint_as_float(ra[2 * j + 1]) * p.sc - m_use);
-        q[j] = pack_bf16x2(e0, e1);
+        const float a0 = __uint_as_float(ra[2 * j]) * p.sc - m_use;
+        const float a1 = __uint_as_float(ra[2 * j + 1]) * p.sc - m_use;
+        const bool poly = (j & 7) < kPolyOf8;
+        const float e0 = poly ? exp2_poly(a0) : exp2f(a0);
+        const float e1 = poly ? exp2_poly(a1) : exp2f(a1);
+        qa[j] = pack_bf16x2(e0, e1);
         l0 += e0;
         l1 += e1;
       }
+      // The first half of this thread's probabilities travels to tensor memory while the second
+      // half is computed.
+      tmem_st_32x16(p_addr, qa);
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
-        const float e0 = exp2f(__uint_as_float(rb[2 * j]) * p.sc - m_use);
-        const float e1 = exp2f(__uint_as_float(rb[2 * j + 1]) * p.sc - m_use);
-        q[16 + j] = pack_bf16x2(e0, e1);
+        const float a0 = __uint_as_float(rb[2 * j]) * p.sc - m_use;
+        const float a1 = __uint_as_float(rb[2 * j + 1]) * p.sc - m_use;
+        const bool poly = (j & 7) < kPolyOf8;
+        const float e0 = poly ? exp2_poly(a0) : exp2f(a0);
+        const float e1 = poly ? exp2_poly(a1) : exp2f(a1);
+        qb[j] = pack_bf16x2(e0, e1);
         l0 += e0;
         l1 += e1;
       }
       l_sum += l0 + l1;
-      tmem_st_32x32(p_addr, q);
+      tmem_st_32x16(p_addr + 16, qb);
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
@@ -407,7 +447,7 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     }
     const int nt = my_hi - my_lo;
     if (ok && nt > 0) {
-      ok = mbar_wait(&pv_done[x], 0, p.status, kStatusWaitTimeoutEpilogue);
+      ok = mbar_wait_warp(&pv_done[x], 0, p.status, kStatusWaitTimeoutEpilogue);
       tc_fence_after_sync();
     }
     // Total row sum = the two halves' partial sums.

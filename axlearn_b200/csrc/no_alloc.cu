@@ -139,13 +139,20 @@ extern "C" int axb_rmsnorm_bwd_noalloc(const void* x, const void* scale, const f
   float* partial = workspace_for_current_device(&dev);
   if (partial == nullptr) return -21;
   if (!g_kernel_configured[dev]) {
-    cudaFuncSetAttribute(rmsnorm_bwd_noalloc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         AXB_NOALLOC_RMSNORM_MAX_D * static_cast<int>(sizeof(float)));
+    if (cudaFuncSetAttribute(rmsnorm_bwd_noalloc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             AXB_NOALLOC_RMSNORM_MAX_D * static_cast<int>(sizeof(float))) != cudaSuccess)
+      return -4;
     g_kernel_configured[dev] = true;
   }
-  // Same grid rule as axb_rmsnorm_bwd_ctas(), so the summation order (and the result) match.
+  // Same grid rule as axb_rmsnorm_bwd_ctas() (one shared constant), so the summation order, and
+  // with it the result, match the regular entry point bit for bit.
   const int grid = static_cast<int>(rows < AXB_NOALLOC_RMSNORM_MAX_CTAS ? rows : AXB_NOALLOC_RMSNORM_MAX_CTAS);
-  if (grid <= 0) return 0;
+  if (grid <= 0) {
+    // No rows: the gradient of the scale is exactly zero.
+    if (dscale_bf16 != nullptr && cudaMemsetAsync(dscale_bf16, 0, D * sizeof(bf16), stream) != cudaSuccess) return -4;
+    if (dscale_f32 != nullptr && cudaMemsetAsync(dscale_f32, 0, D * sizeof(float), stream) != cudaSuccess) return -4;
+    return 0;
+  }
   rmsnorm_bwd_noalloc_kernel<<<grid, 256, D * sizeof(float), stream>>>(
       static_cast<const bf16*>(x), static_cast<const bf16*>(scale), rstd, static_cast<const bf16*>(dy),
       static_cast<const bf16*>(dres), static_cast<bf16*>(dx), partial, rows, D);

@@ -20,6 +20,10 @@
 //     holds until the process exits.
 //   * The first call on a device looks up the array's device address (once per device, with
 //     that device current).  Make this first call before starting any stream capture.
+//   * On EVERY call the device that `stream` belongs to must be the current device: the
+//     workspace is chosen from the current device, not from the stream.
+//   * rows == 0 is allowed: dx is untouched and the scale gradients that were passed are set
+//     to zero.
 //   * No cudaMalloc, cudaFree or allocating library routine is called, on any call.
 //   * All calls share the one workspace and it keeps the previous call's contents.  Every
 //     element that a call reads is written by that same call first, so nothing has to be

@@ -88,6 +88,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   return false;
 }
 
+// The same wait for a whole warp: every lane gets the same answer, so the warp stays converged
+// for the warp-collective tcgen05.ld / tcgen05.st that follow (a lane that alone gave up at the
+// edge of the poll budget would otherwise leave the others in a collective it never joins).
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int* status, int code) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, status, code));
+}
+
 // ------------------------------------------------------------------------------ TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");

@@ -35,11 +35,19 @@ def flash_supported(q, k, v, segment_ids=None) -> bool:
 class _FlashAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, causal, scale, q_seg, k_seg, window, logit_cap):
+        from axlearn_b200.common import remat
         from axlearn_b200.ops import flash_sm100
 
-        ranges = flash_sm100.segment_tile_ranges(q_seg, k_seg) if q_seg is not None else None
-        out, lse = flash_sm100.forward(q, k, v, causal=causal, scale=scale, q_seg=q_seg, k_seg=k_seg,
+        def run():
+            ranges = flash_sm100.segment_tile_ranges(q_seg, k_seg) if q_seg is not None else None
+            return flash_sm100.forward(q, k, v, causal=causal, scale=scale, q_seg=q_seg, k_seg=k_seg,
                                        ranges=ranges, window=window, logit_cap=logit_cap)
+
+        # Under a remat policy that keeps the context, the first pass stores (out, lse) and the
+        # replay finds them here instead of launching the forward kernel again.
+        (out, lse), replayed = remat.operator_outputs(run, is_dot=False)
+        if replayed:
+            out = out.view_as(out)
         ctx.save_for_backward(q, k, v, out, lse, q_seg, k_seg)
         ctx.causal, ctx.scale, ctx.window, ctx.logit_cap = causal, scale, window, logit_cap
         return out

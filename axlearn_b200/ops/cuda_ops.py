@@ -294,6 +294,29 @@ def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return _Linear.apply(x, w)
 
 
+class _LinearKept(_Linear):
+    """``_Linear`` whose forward result ``y`` is already known (kept by a remat policy): no GEMM
+    in forward; the backward GEMMs are those of ``_Linear``."""
+
+    @staticmethod
+    def forward(ctx, x, w, y):  # pylint: disable=arguments-differ
+        ctx.save_for_backward(x, w)
+        return y.view_as(y)
+
+    @staticmethod
+    def backward(ctx, dy):
+        return _Linear.backward(ctx, dy) + (None,)
+
+
+def linear_kept(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    return _LinearKept.apply(x, w, y)
+
+
+def carries_gather(w: torch.Tensor) -> bool:
+    """True when the forward GEMM on ``w`` also gathers parameters (fused FSDP)."""
+    return _fused_fsdp_info(w) is not None
+
+
 # ------------------------------------------------------------------------------------------
 # RMSNorm.
 # ------------------------------------------------------------------------------------------

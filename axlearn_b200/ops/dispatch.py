@@ -63,11 +63,50 @@ def rope(x, positions, theta: float = 10000.0):
     return reference.rope(x, positions, theta)
 
 
-def linear(x, w):
-    """``x[..., K] @ w[K, N]`` with fp32 accumulation."""
+class _LinearKept(torch.autograd.Function):
+    """``x @ w`` whose forward result was kept from the first pass of a replayed layer: nothing
+    is computed in forward, and the backward of a matrix product never needs its result."""
+
+    @staticmethod
+    def forward(ctx, x, w, y):
+        ctx.save_for_backward(x, w)
+        return y.view_as(y)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.matmul(dy, w.t())
+        if ctx.needs_input_grad[1]:
+            dw = torch.matmul(x.reshape(-1, x.shape[-1]).t(), dy.reshape(-1, dy.shape[-1]))
+        return dx, dw, None
+
+
+def _linear_impl(x, w):
     if _cuda(x, w) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         return _ops().linear(x, w)
     return torch.matmul(x, w)
+
+
+def linear(x, w):
+    """``x[..., K] @ w[K, N]`` with fp32 accumulation.  Inside a replayed layer whose remat
+    policy keeps this product (``axlearn_b200.common.remat``), the replay reuses the kept result
+    instead of running the GEMM again."""
+    from axlearn_b200.common import remat
+
+    if remat.active() is None:
+        return _linear_impl(x, w)
+    on_kernel = _cuda(x, w) and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    # A GEMM that carries a parameter gather for a neighbouring layer has to run even when its
+    # own result is known.
+    can_skip = not (on_kernel and _ops().carries_gather(w))
+    (y,), replayed = remat.operator_outputs(lambda: (_linear_impl(x, w),), is_dot=True, can_skip=can_skip)
+    if not replayed:
+        return y
+    if on_kernel:
+        return _ops().linear_kept(x, w, y)
+    return _LinearKept.apply(x, w, y)
 
 
 def attention(
@@ -93,6 +132,7 @@ def attention(
     ):
         # Segment ids, the sliding window and the logit cap are masks of the kernel itself; only an
         # arbitrary additive bias or a dropout mask needs the materialised [T, S] path below.
+        # (Under a remat policy that keeps the context, the replay skips the forward kernel.)
         return _ops().flash_attention(
             q, k, v, causal=causal, softmax_scale=softmax_scale, segment_ids=segment_ids,
             sliding_window=sliding_window, logit_cap=logit_cap

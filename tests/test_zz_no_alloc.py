@@ -81,6 +81,65 @@ def test_noalloc_matches_regular_entry_point_on_two_calls_in_a_row():
             assert torch.equal(w, g)  # same math, same summation order
 
 
+def _fp32_reference(x, scale, rstd, dy, dres):
+    """RMSNorm backward written out in fp32 PyTorch: y = x * rstd * scale."""
+    xf, dyf, sf = x.float(), dy.float(), scale.float()
+    xhat = xf * rstd[:, None]
+    g = dyf * sf
+    dx = rstd[:, None] * (g - xhat * (g * xhat).mean(-1, keepdim=True))
+    if dres is not None:
+        dx = dx + dres.float()
+    return dx, (dyf * xhat).sum(0)
+
+
+def _assert_close(got, want, atol, rtol, what):
+    diff = (got.float() - want.float()).abs()
+    bound = atol + rtol * want.float().abs()
+    assert bool((diff <= bound).all()), (what, diff.max().item())
+
+
+@pytest.mark.parametrize("rows,d,with_dres,with_f32,with_bf16", [
+    (513, 4096, True, True, True),
+    (64, MAX_D, True, True, False),   # the largest width the built-in workspace holds
+    (300, 1024, False, False, True),  # no residual gradient, no fp32 scale gradient
+    (40, 512, False, True, False),
+])
+def test_noalloc_against_fp32_pytorch(rows, d, with_dres, with_f32, with_bf16):
+    _, fn = _entry_points()
+    x, scale, rstd, dy, dres = _inputs(rows, d, 3)
+    dx = torch.empty_like(x)
+    ds16 = torch.full((d,), 7.0, device="cuda", dtype=torch.bfloat16)
+    ds32 = torch.full((d,), 7.0, device="cuda")
+    for _ in range(2):  # the second call reuses the workspace the first one left behind
+        rc = fn(x.data_ptr(), scale.data_ptr(), rstd.data_ptr(), dy.data_ptr(), dres.data_ptr() if with_dres else None,
+                dx.data_ptr(), ds16.data_ptr() if with_bf16 else None, ds32.data_ptr() if with_f32 else None, rows, d,
+                torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+    torch.cuda.synchronize()
+    want_dx, want_ds = _fp32_reference(x, scale, rstd, dy, dres if with_dres else None)
+    _assert_close(dx, want_dx, 2e-2, 2e-2, "dx")
+    if with_f32:
+        _assert_close(ds32, want_ds, 1e-2 * want_ds.abs().max().item(), 1e-3, "dscale fp32")
+    else:
+        assert torch.all(ds32 == 7.0)  # a null output is not written
+    if with_bf16:
+        _assert_close(ds16, want_ds, 2e-2 * want_ds.abs().max().item(), 2e-2, "dscale bf16")
+    else:
+        assert torch.all(ds16 == 7.0)
+
+
+def test_noalloc_with_no_rows_zeroes_the_scale_gradient():
+    _, fn = _entry_points()
+    d = 256
+    x, scale, rstd, dy, dres = _inputs(1, d, 4)
+    ds32 = torch.full((d,), 7.0, device="cuda")
+    rc = fn(x.data_ptr(), scale.data_ptr(), rstd.data_ptr(), dy.data_ptr(), None, x.data_ptr(), None, ds32.data_ptr(),
+            0, d, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert rc == 0
+    assert torch.all(ds32 == 0.0)
+
+
 def test_noalloc_rejects_sizes_beyond_its_workspace():
     _, fn = _entry_points()
     d = MAX_D + 8
