@@ -87,9 +87,25 @@ __device__ __forceinline__ float exp2_poly(float x) {
   return __int_as_float(__float_as_int(p) + (__float_as_int(r) << 23));
 }
 
-// Of every 8 probability pairs, this many are evaluated with exp2_poly (the rest on the
-// exponential unit).
-constexpr int kPolyOf8 = 3;
+// Of the eight batches of eight exponentials per thread and key tile, this many use exp2_poly
+// (the rest the exponential unit).  Measured on B200: with scalar FMA instructions the
+// polynomial costs more issue slots than the exponential unit saves, so the share is zero; the
+// routine stays for experiments with packed two-wide FMA.
+constexpr int kPolyBatches = 0;
+
+// e[u] = 2^(s[u] * sc - m) for eight scores.
+__device__ __forceinline__ void exp2_batch8(const uint32_t* s, float sc, float m, float (&e)[8], bool poly) {
+  float a[8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u) a[u] = fmaf(__uint_as_float(s[u]), sc, -m);
+  if (poly) {
+#pragma unroll
+    for (int u = 0; u < 8; ++u) e[u] = exp2_poly(a[u]);
+  } else {
+#pragma unroll
+    for (int u = 0; u < 8; ++u) e[u] = exp2f(a[u]);
+  }
+}
 
 // kGeneral: segment ids / sliding window / logit cap are honoured (every tile takes the masking
 // path when segment ids are present).  The plain instantiation only masks diagonal and ragged
@@ -413,30 +429,27 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       // Probabilities rounded to bf16 and packed two per register: q[j] = (p[2j], p[2j+1]).
       uint32_t qa[16], qb[16];
       float l0 = 0.f, l1 = 0.f;
+      // Exponentials in batches of eight independent values.
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float a0 = __uint_as_float(ra[2 * j]) * p.sc - m_use;
-        const float a1 = __uint_as_float(ra[2 * j + 1]) * p.sc - m_use;
-        const bool poly = (j & 7) < kPolyOf8;
-        const float e0 = poly ? exp2_poly(a0) : exp2f(a0);
-        const float e1 = poly ? exp2_poly(a1) : exp2f(a1);
-        qa[j] = pack_bf16x2(e0, e1);
-        l0 += e0;
-        l1 += e1;
+      for (int j0 = 0; j0 < 32; j0 += 8) {
+        float e[8];
+        exp2_batch8(ra + j0, p.sc, m_use, e, (j0 >> 3) < kPolyBatches);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) qa[(j0 >> 1) + u] = pack_bf16x2(e[2 * u], e[2 * u + 1]);
+        l0 += (e[0] + e[1]) + (e[2] + e[3]);
+        l1 += (e[4] + e[5]) + (e[6] + e[7]);
       }
       // The first half of this thread's probabilities travels to tensor memory while the second
       // half is computed.
       tmem_st_32x16(p_addr, qa);
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float a0 = __uint_as_float(rb[2 * j]) * p.sc - m_use;
-        const float a1 = __uint_as_float(rb[2 * j + 1]) * p.sc - m_use;
-        const bool poly = (j & 7) < kPolyOf8;
-        const float e0 = poly ? exp2_poly(a0) : exp2f(a0);
-        const float e1 = poly ? exp2_poly(a1) : exp2f(a1);
-        qb[j] = pack_bf16x2(e0, e1);
-        l0 += e0;
-        l1 += e1;
+      for (int j0 = 0; j0 < 32; j0 += 8) {
+        float e[8];
+        exp2_batch8(rb + j0, p.sc, m_use, e, false);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) qb[(j0 >> 1) + u] = pack_bf16x2(e[2 * u], e[2 * u + 1]);
+        l0 += (e[0] + e[1]) + (e[2] + e[3]);
+        l1 += (e[4] + e[5]) + (e[6] + e[7]);
       }
       l_sum += l0 + l1;
       tmem_st_32x16(p_addr + 16, qb);

@@ -75,12 +75,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe of the same condition (no suspend machinery: the cheap path for a phase
+// that completed long ago, e.g. a TMA load that landed an iteration earlier).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Poll budget of one wait. try_wait itself blocks for a hardware-defined slice per call, so
 // this bounds a wait to the order of a second.
 constexpr uint32_t kMaxPolls = 1u << 22;
 
 // Returns false (after recording `code`) if the phase did not complete within the budget.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+  if (mbar_test_wait(bar, parity)) return true;
   for (uint32_t i = 0; i < kMaxPolls; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
   }

@@ -50,6 +50,7 @@ class _FlashAttention(torch.autograd.Function):
             out = out.view_as(out)
         ctx.save_for_backward(q, k, v, out, lse, q_seg, k_seg)
         ctx.causal, ctx.scale, ctx.window, ctx.logit_cap = causal, scale, window, logit_cap
+        ctx.bwd_variant = flash_sm100.BACKWARD_VARIANT  # the selection in force when the forward ran
         return out
 
     @staticmethod
@@ -60,7 +61,7 @@ class _FlashAttention(torch.autograd.Function):
         k_ranges = flash_sm100.segment_tile_ranges(k_seg, q_seg) if q_seg is not None else None
         dq, dk, dv = flash_sm100.backward(
             q, k, v, out, lse, dout.contiguous(), causal=ctx.causal, scale=ctx.scale, q_seg=q_seg, k_seg=k_seg,
-            k_ranges=k_ranges, window=ctx.window, logit_cap=ctx.logit_cap)
+            k_ranges=k_ranges, window=ctx.window, logit_cap=ctx.logit_cap, variant=ctx.bwd_variant)
         return dq, dk, dv, None, None, None, None, None, None
 
 

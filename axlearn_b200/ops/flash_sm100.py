@@ -88,7 +88,7 @@ def forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool, 
 
 
 def backward(q, k, v, out, lse, dout, *, causal: bool, scale: float, q_seg=None, k_seg=None, k_ranges=None,
-             window: Optional[int] = None, logit_cap: Optional[float] = None):
+             window: Optional[int] = None, logit_cap: Optional[float] = None, variant: Optional[str] = None):
     """Gradients ``(dq, dk, dv)``.  ``k_ranges`` is ``segment_tile_ranges(k_seg, q_seg)`` (indexed by
     key tile)."""
     b, t, n, h = q.shape
@@ -96,7 +96,7 @@ def backward(q, k, v, out, lse, dout, *, causal: bool, scale: float, q_seg=None,
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     general = q_seg is not None or window is not None or logit_cap is not None
     status = cuda_ops.status_word(q.device).data_ptr()
-    if BACKWARD_VARIANT == "fused" or general:
+    if (variant or BACKWARD_VARIANT) == "fused" or general:
         tp = (t + 127) // 128 * 128
         lse2 = torch.empty((b, n, tp), dtype=torch.float32, device=q.device)
         delta = torch.empty_like(lse2)

@@ -1,6 +1,6 @@
 """Headline benchmark: Fuji-7B training throughput (tokens/s) on N B200 GPUs of one node.
 
-Config (BASELINE.json config 2): 32 layers, d_model 4096, 32 heads (MHA), SwiGLU hidden 11008,
+Config (the reference's single-host Fuji-7B-v2 training configuration): 32 layers, d_model 4096, 32 heads (MHA), SwiGLU hidden 11008,
 vocab 32768, RoPE, RMSNorm; sequence length 4096; 4 sequences per GPU (32 at 8 GPUs, weak
 scaling); mesh fsdp=N; bf16 compute with fp32 master weights and AdamW moments; full
 rematerialisation per layer; synthetic uniform-random tokens from seed 0; random-init weights.
@@ -114,7 +114,7 @@ def main():
     if args.impl == "reference":
         print(json.dumps({
             "impl": "reference",
-            "unavailable": "apple/axlearn needs jax/jaxlib(cuda12)/tensorstore/absl/optax wheels and the hatchling "
+            "unavailable": "apple/axlearn needs jax/jaxlib(cuda12)/tensorstore/optax wheels and the hatchling "
                            "build backend; none are in the offline wheelhouse, so it cannot be installed",
         }))
         return
