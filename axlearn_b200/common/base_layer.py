@@ -32,6 +32,7 @@ import torch
 from axlearn_b200.common import prng
 from axlearn_b200.common.config import (
     REQUIRED,
+    Configurable,
     ConfigOr,
     InstantiableConfig,
     Required,
@@ -185,6 +186,40 @@ class DefaultTensorStats(CompositeTensorStats):
         }
 
 
+class ParameterNoise(Configurable):
+    """Interface for perturbing a layer's parameters during training (reference:
+    axlearn/common/base_layer.py:263-269).  ``apply`` returns a tree of the same structure;
+    it must not modify ``params`` in place."""
+
+    def apply(self, prng_key: Tensor, params: Any) -> Any:
+        raise NotImplementedError(type(self))
+
+
+class GaussianParameterNoise(ParameterNoise):
+    """Adds ``std * N(0, 1)`` to every floating-point parameter whose name matches ``regex``."""
+
+    @config_class
+    class Config(Configurable.Config):
+        std: float = 0.0
+        regex: str = ".*"
+
+    def apply(self, prng_key: Tensor, params: Any) -> Any:
+        import re
+
+        cfg = self._config
+        items = flatten_items(params)
+        keys = prng.split(prng_key, max(1, len(items)))
+        out = []
+        for (path, value), key in zip(items, keys):
+            if isinstance(value, Tensor) and value.is_floating_point() and re.fullmatch(cfg.regex, path):
+                noise = prng.normal(key, value.shape, dtype=value.dtype, device=value.device, std=cfg.std)
+                value = value + noise  # differentiable: the gradient reaches the clean parameter
+            out.append((path, value))
+        from axlearn_b200.common.utils import unflatten_items
+
+        return unflatten_items(out) if out else params
+
+
 # --------------------------------------------------------------------------------------
 # Remat machinery.
 # --------------------------------------------------------------------------------------
@@ -330,10 +365,14 @@ class BaseLayer(Module):
         # Mesh axes of this layer's parameters (per-dim); layer-specific defaults apply.
         param_partition_spec: Optional[Sequence[Any]] = None
         remat_spec: Optional[RematSpec] = None
+        # Parameter perturbation, applied by the trainer through
+        # apply_parameter_noise_recursively() (never implicitly inside forward).
+        param_noise: Optional[InstantiableConfig] = None
         tensor_stats: Optional[InstantiableConfig] = None
 
     def __init__(self, cfg: "BaseLayer.Config", *, parent: Optional[Module] = None):
         super().__init__(cfg, parent=parent)
+        self._param_noise = cfg.param_noise.instantiate() if cfg.param_noise is not None else None
         self._param_init: Optional[Initializer] = (
             cfg.param_init.instantiate() if cfg.param_init is not None else None
         )
@@ -374,6 +413,31 @@ class BaseLayer(Module):
             bound = lambda *a, **k: fn(self, *a, **k)
             return remat_call(bound, state=ctx.state, args=args, kwargs=kwargs, policy=spec.selective_policy())
         return fn(self, *args, **kwargs)
+
+    # ------------------------------------------------------------------ parameter noise
+    @nowrap
+    def has_parameter_noise(self) -> bool:
+        if self._param_noise is not None:
+            return True
+        return any(isinstance(c, BaseLayer) and c.has_parameter_noise() for c in self._children.values())
+
+    @nowrap
+    def apply_parameter_noise_recursively(self, prng_key: Tensor, params: Any) -> Any:
+        """Returns ``params`` with every configured ``param_noise`` applied: children first (one
+        key split per BaseLayer child, in declaration order), then this layer's own noise on the
+        result.  The input tree is not modified (reference: axlearn/common/base_layer.py:747-771)."""
+        if not self.has_parameter_noise():
+            return params
+        params = type(params)(**params) if isinstance(params, dict) else params
+        for name, child in self._children.items():
+            if not isinstance(child, BaseLayer):
+                continue
+            prng_key, child_key = prng.split(prng_key, 2)
+            if isinstance(params, dict) and name in params:
+                params[name] = child.apply_parameter_noise_recursively(child_key, params[name])
+        if self._param_noise is not None:
+            params = self._param_noise.apply(prng_key, params)
+        return params
 
     # ------------------------------------------------------------------ parameter specs
     def _create_layer_parameter_specs(self) -> dict[str, ParameterSpec]:

@@ -27,6 +27,7 @@ from __future__ import annotations
 
 import ast
 import json
+import math
 import os
 import re
 import shutil
@@ -313,14 +314,70 @@ class BestMetricPolicy(Configurable):
 # ------------------------------------------------------------------------------------------
 
 
+class _ByteBudget:
+    """Bounds the bytes that sit in host staging buffers waiting to be written."""
+
+    def __init__(self, limit: Optional[int]):
+        self._limit = limit
+        self._used = 0
+        self._cv = threading.Condition()
+
+    def acquire(self, n: int) -> None:
+        if self._limit is None:
+            return
+        with self._cv:
+            # A single array larger than the whole budget is admitted once nothing else is in flight.
+            while self._used > 0 and self._used + n > self._limit:
+                self._cv.wait()
+            self._used += n
+
+    def release(self, n: int) -> None:
+        if self._limit is None:
+            return
+        with self._cv:
+            self._used -= n
+            self._cv.notify_all()
+
+
+def _data_shard(local_shape: Sequence[int], replicas: int, replica: int, max_degree: Optional[int]):
+    """How replica ``replica`` of ``replicas`` holders of the same shard takes part in writing it:
+    ``(dim, degree, index)`` = it writes slice ``index`` of ``degree`` along ``dim``; or None
+    when it writes nothing.  The first dim divisible by the degree is split (reference:
+    axlearn/common/array_serialization.py:189-240); without ``max_degree`` only replica 0 writes."""
+    if not max_degree or replicas <= 1:
+        return (0, 1, 0) if replica == 0 else None
+    degree = replicas if max_degree < 0 else min(replicas, max_degree)
+    while degree > 1:
+        for dim, size in enumerate(local_shape):
+            if size % degree == 0 and size >= degree:
+                return (dim, degree, replica) if replica < degree else None
+        degree -= 1
+    return (0, 1, 0) if replica == 0 else None
+
+
 class TensorStoreStateStorage(Configurable):
-    """Writes/reads a state tree in the layout described in the module docstring."""
+    """Writes/reads a state tree in the layout described in the module docstring.
+
+    Saving is asynchronous in every process (reference: ``BoundedDataShardedAsyncCheckpointManager``,
+    axlearn/common/array_serialization.py:1199-1337): ``save_to_dir`` only *enqueues* the
+    device-to-host copies on the current stream (so the next training step, queued behind them,
+    cannot overwrite what is being copied) and returns; worker threads wait for each copy and
+    write the chunk; host staging is bounded by ``max_concurrent_gb`` (the call blocks while the
+    budget is exhausted); replicated arrays are written in slices by up to
+    ``max_data_shard_degree`` of their holders.  Commit needs no collective: every process drops
+    a marker file once its chunks are on disk and process 0 writes ``index`` when all markers
+    are there, so the index-last rule holds across processes without a barrier on a helper thread.
+    """
 
     @config_class
     class Config(Configurable.Config):
         timeout_secs: float = 3600
+        # Upper bound on host staging memory in flight (GiB); None = unbounded.
         max_concurrent_gb: Optional[float] = None
         max_concurrent_restore_gb: Optional[float] = 32
+        # Up to this many holders of a replicated array each write a slice of it (-1 = all of
+        # them, None / 0 = only the first holder writes).
+        max_data_shard_degree: Optional[int] = None
         num_io_threads: int = 8
 
     def __init__(self, cfg):
@@ -328,49 +385,77 @@ class TensorStoreStateStorage(Configurable):
         self._pool = ThreadPoolExecutor(max_workers=cfg.num_io_threads, thread_name_prefix="ckpt-io")
         self._pending: Optional[threading.Thread] = None
         self._error: Optional[BaseException] = None
+        self.peak_staged_bytes = 0  # observed high-water mark of host staging (tests, summaries)
 
     # ---------------------------------------------------------------- save
     def save_to_dir(self, *, step: int, state: Any, ckpt_dir: str, specs: Optional[Any] = None,
                     on_commit_callback: Optional[Callable[..., None]] = None) -> None:
+        cfg = self._config
         self.wait_until_finished()
         mesh = current_mesh()
-        rank = coll.process_index()
+        rank, nproc = coll.process_index(), coll.process_count()
         if rank == 0:
             os.makedirs(ckpt_dir, exist_ok=True)
         coll.barrier("ckpt-mkdir")
         spec_map = dict(flatten_items(specs, is_leaf=lambda x: isinstance(x, TensorSpec))) if specs is not None else {}
         entries: list[tuple[str, Any]] = []
-        shards: list[_Shard] = []
         python_items: list[tuple[str, Any]] = []
+        budget = _ByteBudget(int(cfg.max_concurrent_gb * (1 << 30)) if cfg.max_concurrent_gb else None)
+        futures = []
+        staged = {"now": 0, "peak": 0}
+        lock = threading.Lock()
+
+        def write_when_copied(shard: _Shard, event, nbytes: int):
+            try:
+                if event is not None:
+                    event.synchronize()  # this array's device-to-host copy has landed
+                _write_shard(ckpt_dir, shard)
+            finally:
+                with lock:
+                    staged["now"] -= nbytes
+                budget.release(nbytes)
+
         for path, value in flatten_items(state):
             if isinstance(value, torch.Tensor):
                 spec = spec_map.get(path)
                 mesh_axes = getattr(spec, "mesh_axes", None)
                 if mesh is not None and mesh.size > 1 and mesh_axes is not None and len(mesh_axes) == value.dim():
-                    gshape = tuple(
-                        d * mesh.axis_size(mesh.present_axes(ax)) for d, ax in zip(value.shape, mesh_axes))
-                    coords = tuple(mesh.axis_index(mesh.present_axes(ax)) for ax in mesh_axes)
-                    writer = mesh.replica_id(mesh_axes) == 0
+                    sizes = [mesh.axis_size(mesh.present_axes(ax)) for ax in mesh_axes]
+                    gshape = tuple(d * n for d, n in zip(value.shape, sizes))
+                    coords = [mesh.axis_index(mesh.present_axes(ax)) for ax in mesh_axes]
+                    replicas = mesh.size // max(1, math.prod(sizes))
+                    part = _data_shard(value.shape, replicas, mesh.replica_id(mesh_axes), cfg.max_data_shard_degree)
                 else:
-                    gshape, coords = tuple(value.shape), tuple(0 for _ in value.shape)
-                    writer = rank == 0
+                    gshape, coords = tuple(value.shape), [0 for _ in value.shape]
+                    part = _data_shard(value.shape, nproc, rank, cfg.max_data_shard_degree)
                 entries.append((path, {"dtype": _DTYPE_NAMES[value.dtype], "shape": str(gshape)}))
-                if writer:
-                    host = self._to_host(value)
-                    shards.append(_Shard(path, host, gshape, coords, True, all(c == 0 for c in coords)))
+                if part is None:
+                    continue
+                dim, degree, index = part
+                piece = value
+                if degree > 1:
+                    width = value.shape[dim] // degree
+                    piece = value.narrow(dim, index * width, width)
+                    coords[dim] = coords[dim] * degree + index
+                nbytes = piece.numel() * piece.element_size()
+                budget.acquire(nbytes)  # blocks the caller while too much is staged already
+                with lock:
+                    staged["now"] += nbytes
+                    staged["peak"] = max(staged["peak"], staged["now"])
+                host, event = self._to_host(piece)
+                shard = _Shard(path, host, gshape, tuple(coords), True, all(c == 0 for c in coords))
+                futures.append(self._pool.submit(write_when_copied, shard, event, nbytes))
             elif hasattr(value, "get_state"):
                 entries.append((path, str(type(value))))
                 python_items.append((path, value.get_state()))
             else:
                 entries.append((path, _leaf_entry(value)))
-        if torch.cuda.is_available():
-            torch.cuda.current_stream().synchronize()  # D2H copies have landed.
 
         def commit():
             try:
-                futures = [self._pool.submit(_write_shard, ckpt_dir, s) for s in shards]
                 for f in futures:
                     f.result()
+                self.peak_staged_bytes = staged["peak"]
                 if python_items:
                     pdir = os.path.join(ckpt_dir, f"python_{rank}")
                     for path, st in python_items:
@@ -378,30 +463,30 @@ class TensorStoreStateStorage(Configurable):
                         os.makedirs(os.path.dirname(fp), exist_ok=True)
                         with open(fp, "w") as f:
                             json.dump(st, f)
-                coll_barrier_from_thread()
+                _commit_across_processes(ckpt_dir, rank=rank, nproc=nproc, timeout_secs=cfg.timeout_secs)
                 if rank == 0:
                     if on_commit_callback is not None:
                         on_commit_callback(ckpt_dir=ckpt_dir, step=step, entries=entries)
                     else:
                         write_index_file(ckpt_dir, step=step, entries=entries)
+                    _clear_commit_markers(ckpt_dir)
             except BaseException as e:  # pylint: disable=broad-except
                 self._error = e
 
-        if coll.process_count() > 1:
-            # Cross-process barriers must run on the main thread: write synchronously.
-            commit()
-            self._raise_if_failed()
-        else:
-            self._pending = threading.Thread(target=commit, name="ckpt-commit", daemon=True)
-            self._pending.start()
+        self._pending = threading.Thread(target=commit, name="ckpt-commit", daemon=True)
+        self._pending.start()
 
-    def _to_host(self, t: torch.Tensor) -> torch.Tensor:
+    def _to_host(self, t: torch.Tensor):
+        """``(host copy, event)``: the copy is enqueued on the current stream; ``event`` (None for
+        CPU tensors) fires when it has landed."""
         t = t.detach()
         if not t.is_cuda:
-            return t.clone()
+            return t.clone(), None
         host = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
         host.copy_(t, non_blocking=True)
-        return host
+        event = torch.cuda.Event()
+        event.record(torch.cuda.current_stream(t.device))
+        return host, event
 
     def wait_until_finished(self) -> None:
         if self._pending is not None:
@@ -467,14 +552,57 @@ class TensorStoreStateStorage(Configurable):
                 return tgt
             return entry
 
-        futures = {p: self._pool.submit(restore_leaf, p, t) for p, t in target}
+        # Host memory held by arrays that were read but not yet handed over is bounded by
+        # max_concurrent_restore_gb (reference: axlearn/common/array_serialization.py:549-720).
+        cfg = self._config
+        budget = _ByteBudget(int(cfg.max_concurrent_restore_gb * (1 << 30)) if cfg.max_concurrent_restore_gb else None)
+
+        def bounded(path: str, tgt: Any, nbytes: int):
+            try:
+                return restore_leaf(path, tgt)
+            finally:
+                budget.release(nbytes)
+
+        futures = {}
+        for p, t in target:
+            nbytes = 0
+            if isinstance(t, (torch.Tensor, TensorSpec)):
+                elem = torch.empty((), dtype=t.dtype).element_size() if t.dtype is not None else 4
+                nbytes = math.prod(tuple(t.shape)) * elem
+            budget.acquire(nbytes)
+            futures[p] = self._pool.submit(bounded, p, t, nbytes)
         restored = {p: f.result() for p, f in futures.items()}
         return _fill_like(state, restored)
 
 
-def coll_barrier_from_thread() -> None:
-    if coll.process_count() > 1:
-        coll.barrier("ckpt-commit")
+def _commit_across_processes(ckpt_dir: str, *, rank: int, nproc: int, timeout_secs: float) -> None:
+    """Index-last commit without a collective: every process drops ``.done.<rank>`` once its
+    chunks are on disk; process 0 returns when all ``nproc`` markers exist (the others return at
+    once).  Runs on a helper thread, where a process-group barrier must not be issued."""
+    if nproc <= 1:
+        return
+    marker = os.path.join(ckpt_dir, f".done.{rank}")
+    with open(marker + ".tmp", "w") as f:
+        f.write(str(time.time()))
+    os.replace(marker + ".tmp", marker)
+    if rank != 0:
+        return
+    deadline = time.time() + timeout_secs
+    while True:
+        if all(os.path.exists(os.path.join(ckpt_dir, f".done.{r}")) for r in range(nproc)):
+            return
+        if time.time() > deadline:
+            raise TimeoutError(f"not every process finished writing {ckpt_dir} within {timeout_secs} s")
+        time.sleep(0.02)
+
+
+def _clear_commit_markers(ckpt_dir: str) -> None:
+    for name in os.listdir(ckpt_dir):
+        if name.startswith(".done."):
+            try:
+                os.remove(os.path.join(ckpt_dir, name))
+            except FileNotFoundError:
+                pass
 
 
 def _fill_like(structure: Any, values: dict[str, Any], prefix: str = "") -> Any:

@@ -145,6 +145,7 @@ class SpmdTrainer(Module):
         self._step = 0
         self._trainer_state: Optional[dict] = None
         self._shadows: Optional[Any] = None
+        self._has_param_noise = False
         self._device = torch.device(cfg.device) if cfg.device else _default_device()
         self._mesh = mesh or create_mesh(cfg.mesh_shape, cfg.mesh_axis_names)
         self._step_times = collections.deque(maxlen=100)
@@ -159,6 +160,7 @@ class SpmdTrainer(Module):
                 cfg.summary_writer.clone(dir=cfg.summary_writer.dir or os.path.join(cfg.dir, "summaries", "train_train")),
             )
             self._add_child("model", cfg.model)
+            self._has_param_noise = bool(getattr(self.model, "has_parameter_noise", lambda: False)())
             self._add_child("learner", cfg.learner)
             self._add_child(
                 "checkpointer",
@@ -472,8 +474,13 @@ class SpmdTrainer(Module):
 
                 # Cross-rank ordering of the gradient staging buffers (once per micro-batch).
                 fsdp_fused.begin_step_all(accumulate=micro is not micro_batches[0])
+            # Parameter noise (if any layer configures it) perturbs what the model reads; gradients
+            # still land on the clean shadows (reference: axlearn/common/trainer.py:1305-1307).
+            step_params = self._shadows
+            if self._has_param_noise:
+                step_params = self.model.apply_parameter_noise_recursively(_noise_key, self._shadows)
             (micro_loss, aux), oc = functional(
-                self.model, key, self._shadows, [micro], is_training=True, method="forward")
+                self.model, key, step_params, [micro], is_training=True, method="forward")
             # Micro-batch gradients are averaged (reference: gradient_accumulation.py:96-351).
             # Pipeline ranks each hold 1/num_stages of the loss gradient (see common/pipeline.py).
             (micro_loss * (pipeline_scale / steps)).backward()

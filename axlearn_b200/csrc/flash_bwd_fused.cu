@@ -135,18 +135,9 @@ struct FbSmem {
   static constexpr int kQ = kV + kTile;            // 2 stages
   static constexpr int kDO = kQ + 2 * kTile;       // 2 stages
   static constexpr int kDS = kDO + 2 * kTile;      // [128 keys x 128 queries]
-  static constexpr int kLse = kDS + 2 * kFbSub;    // 2 stages x (128 lse2 + 128 delta) floats
-  static constexpr int kBar = kLse + 2048;
+  static constexpr int kBar = kDS + 2 * kFbSub;
   static constexpr int kTotal = kBar + 256;
 };
-
-__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-          smem_u32(smem_dst)),
-      "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
-      : "memory");
-}
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
@@ -271,14 +262,11 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           const int st = it & 1;
           const uint32_t ph = (it >> 1) & 1;
           if (!mbar_wait(&q_empty[st], ph ^ 1, p.status, kStatusWaitTimeoutProducer)) break;
-          mbar_arrive_expect_tx(&q_full[st], L::kTile + 1024);
+          mbar_arrive_expect_tx(&q_full[st], L::kTile);
 #pragma unroll
           for (int j = 0; j < H / 64; ++j)
             tma_load_4d(smem + L::kQ + st * L::kTile + j * kFbSub, &tmap_q, &q_full[st], j * 64, head, qt * 128,
                         batch);
-          const int64_t row0 = (static_cast<int64_t>(batch) * p.N + head) * p.Tp + qt * 128;
-          bulk_load_1d(smem + L::kLse + st * 1024, p.lse2 + row0, 512, &q_full[st]);
-          bulk_load_1d(smem + L::kLse + st * 1024 + 512, p.delta + row0, 512, &q_full[st]);
           if (!mbar_wait(&do_empty[st], ph ^ 1, p.status, kStatusWaitTimeoutProducer)) break;
           mbar_arrive_expect_tx(&do_full[st], L::kTile);
 #pragma unroll
@@ -393,18 +381,28 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     }
     bool ok = run;
     for (int it = 0; it < n_iters && ok; ++it) {
+      const int head = kv_head * group + it / tiles_per_head;
       const int qt = i_lo + it % tiles_per_head;
-      const int st = it & 1;
       const int t0 = qt * 128;
+      // Per-query values of this thread's 64 columns.  Shared memory is saturated by the operand
+      // reads of the shared-memory GEMMs, so they do not come from there: lane l keeps the values
+      // of columns l and l + 32 (two coalesced global loads per quantity, issued before the wait
+      // on the scores) and the loops fetch column c from lane c & 31 with a register shuffle.
+      const int64_t row0 = (static_cast<int64_t>(batch) * p.N + head) * p.Tp + t0 + half * 64;
+      const float lse_lo = __ldg(p.lse2 + row0 + lane), lse_hi = __ldg(p.lse2 + row0 + 32 + lane);
+      const float del_lo = __ldg(p.delta + row0 + lane), del_hi = __ldg(p.delta + row0 + 32 + lane);
+      int qs_lo = -1, qs_hi = -1;
+      if (kGeneral && qseg_row != nullptr) {
+        const int ta = t0 + half * 64 + lane, tb = ta + 32;
+        qs_lo = ta < p.T ? __ldg(qseg_row + ta) : -1;
+        qs_hi = tb < p.T ? __ldg(qseg_row + tb) : -1;
+      }
       // Visible query columns of this key: c_min <= c <= c_max (tile-relative).
       int c_min = 0, c_max = 127;
       if (p.causal) c_min = key - p.q_offset - t0;
       if (kGeneral && p.window >= 0) c_max = key - p.q_offset + p.window - t0;
       if (key >= p.S) c_min = 1 << 20;
-      const bool need_mask = c_min > half * 64 || c_max < half * 64 + 63;
-      const float* lse_s = reinterpret_cast<const float*>(smem + L::kLse + st * 1024) + half * 64;
-      const float* delta_s = lse_s + 128;
-      if (!mbar_wait_warp(&q_full[st], (it >> 1) & 1, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
+      const bool need_mask = __any_sync(0xffffffffu, c_min > half * 64 || c_max < half * 64 + 63);
       if (!mbar_wait_warp(s_full, it & 1, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
       tc_fence_after_sync();
       float pf[64];  // P (times 1 - tanh^2 under a logit cap): the factor of dS
@@ -413,39 +411,41 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         tmem_ld_32x32(s_addr, rs[0]);
         tmem_ld_32x32(s_addr + 32, rs[1]);
         tmem_ld_wait();
-        uint32_t pk[32];
 #pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(lse_s + 4 * c4);
-          const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
-          float e[4];
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t pk[16];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int c = 4 * c4 + u;
-            float val = __uint_as_float(rs[c >> 5][c & 31]);
+          for (int j = 0; j < 32; ++j) {
+            const int c = hh * 32 + j;
+            const float ls = __shfl_sync(0xffffffffu, hh ? lse_hi : lse_lo, j);
+            float val = __uint_as_float(rs[hh][j]);
             float w = 1.f;
             if (kGeneral && p.cap_out != 0.f) {
               const float th = tanh_approx_b(val * p.cap_in);
               val = th * p.cap_out;
               w = 1.f - th * th;
             }
-            float pr = exp2f(val * p.sc - ls[u]);
+            float pr = exp2f(val * p.sc - ls);
             if (need_mask) {
               const int cc = half * 64 + c;
               if (cc < c_min || cc > c_max) pr = 0.f;
             }
             if (kGeneral && qseg_row != nullptr) {
-              const int t = t0 + half * 64 + c;
-              const int qs = t < p.T ? __ldg(qseg_row + t) : -1;
+              const int qs = __shfl_sync(0xffffffffu, hh ? qs_hi : qs_lo, j);
               if (qs != kseg) pr = 0.f;
             }
-            e[u] = pr;
             pf[c] = (kGeneral && p.cap_out != 0.f) ? pr * w : pr;
+            // Pack pairs as they complete (the bf16 rounding happens here; pf keeps fp32).
+            if (j & 1) {
+              const float prev = (kGeneral && p.cap_out != 0.f) ? __uint_as_float(rs[hh][j - 1]) : pf[c - 1];
+              pk[j >> 1] = pack_bf16x2(prev, pr);
+            } else if (kGeneral && p.cap_out != 0.f) {
+              rs[hh][j] = __float_as_uint(pr);  // the unweighted probability, for the pair above
+            }
           }
-          pk[2 * c4] = pack_bf16x2(e[0], e[1]);
-          pk[2 * c4 + 1] = pack_bf16x2(e[2], e[3]);
+          // The first 32 columns travel to tensor memory while the other 32 are computed.
+          tmem_st_32x16(s_addr + hh * 16, pk);
         }
-        tmem_st_32x32(s_addr, pk);
         tmem_st_wait();
       }
       tc_fence_before_sync();
@@ -464,12 +464,9 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         tmem_ld_wait();
         float dsv[32];
 #pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4) {
-          const float4 d4 = *reinterpret_cast<const float4*>(delta_s + ch * 32 + 4 * c4);
-          dsv[4 * c4 + 0] = pf[ch * 32 + 4 * c4 + 0] * (__uint_as_float(rd[4 * c4 + 0]) - d4.x);
-          dsv[4 * c4 + 1] = pf[ch * 32 + 4 * c4 + 1] * (__uint_as_float(rd[4 * c4 + 1]) - d4.y);
-          dsv[4 * c4 + 2] = pf[ch * 32 + 4 * c4 + 2] * (__uint_as_float(rd[4 * c4 + 2]) - d4.z);
-          dsv[4 * c4 + 3] = pf[ch * 32 + 4 * c4 + 3] * (__uint_as_float(rd[4 * c4 + 3]) - d4.w);
+        for (int j = 0; j < 32; ++j) {
+          const float dl = __shfl_sync(0xffffffffu, ch ? del_hi : del_lo, j);
+          dsv[j] = pf[ch * 32 + j] * (__uint_as_float(rd[j]) - dl);
         }
         fb_store_row_chunk(smem + L::kDS, r_in, half * 64 + ch * 32, dsv);
       }
