@@ -1,18 +1,25 @@
 """Quantised contractions for dense layers.
 
 Parity target in the reference: ``QuantizedDotGeneral`` (axlearn/common/quantized_dot_general/
-layers.py): a child layer that dense layers call instead of a plain einsum, configured by
-``quantization_type`` (fp8 / int8) and, for fp8, ``fp8_amax_history_length``.  The reference
-quantises per tensor with delayed scaling (scales from a history of amax values kept as
-parameters whose "gradients" overwrite them in place).
+layers.py:69-203, 282-323; fp8_ops.py:15-257): a child layer that dense layers call instead of a
+plain einsum, configured by ``quantization_type`` (fp8 / int8) and, for fp8,
+``fp8_amax_history_length``.
 
-Two fp8 schemes are offered here:
+Two fp8 schemes:
 
-* ``scaling="block"`` (default): 1x128 activation / 128x128 weight scale blocks computed from the
-  current tensors (``ops/fp8_ops.py``) -- no state, and the form the tcgen05 kernel runs;
-* ``scaling="tensor"``: one scale per tensor from the current amax, with the amax histories kept
-  as state (``*_amax_history`` parameters updated through state updates) for parity of the
-  parameter tree and for monitoring.
+* ``scaling="tensor"``: the reference's per-tensor scaling.  Every dense layer owns six extra
+  parameters -- ``input_scale``, ``kernel_scale``, ``output_grad_scale`` (fp32 scalars, initial
+  1) and, with a history length > 0 (*delayed* scaling), ``input_amax_history``,
+  ``kernel_amax_history``, ``output_grad_amax_history`` (``[length]``, initial 0).  A forward pass
+  quantises with the scale derived from the *stored* history, and the new scales / histories
+  come back from ``backward`` **as the gradients of those parameters**; the learner applies
+  them as in-place overrides (``OverrideInplaceUpdateTransformation`` with rules
+  ``.*/<name>``, installed by ``FP8ConfigModifier``), so they are part of the checkpointed
+  state under the reference's names.  With history length 0 / None the scale comes from the
+  current tensor (in-batch scaling) and only the three scale parameters exist.
+* ``scaling="block"`` (default here): 1x128 activation / 128x128 weight scale blocks computed
+  from the current tensors (``ops/fp8_ops.py``) -- no state, and the form the tcgen05 fp8 kernel
+  runs.
 """
 
 from __future__ import annotations
@@ -31,37 +38,71 @@ from axlearn_b200.ops import fp8_ops
 
 Tensor = torch.Tensor
 
+FP8_SCALE_PARAMS = ("input_scale", "kernel_scale", "output_grad_scale")
+FP8_AMAX_HISTORY_PARAMS = ("input_amax_history", "kernel_amax_history", "output_grad_amax_history")
+
+
+def get_all_fp8_param_names() -> list[str]:
+    return list(FP8_SCALE_PARAMS) + list(FP8_AMAX_HISTORY_PARAMS)
+
 
 class DotGeneralQuantizationType(enum.Enum):
     INT_8 = "int8"
     FP_8 = "fp8"
 
 
+def compute_scale(amax: Tensor, scale: Tensor, fp8_max: float) -> Tensor:
+    """New dequantisation scale from an amax (reference math: flax ``fp8_ops.compute_scale`` with
+    margin 0): ``amax / fp8_max`` where amax is positive and finite, else the old scale."""
+    ok = torch.isfinite(amax) & (amax > 0)
+    return torch.where(ok, amax / fp8_max, scale)
+
+
+def update_amax_history(x: Tensor, history: Tensor) -> Tensor:
+    """Rolls the history by one and stores ``max|x|`` in slot 0."""
+    new = torch.roll(history, shifts=-1, dims=0).clone()
+    new[0] = x.detach().abs().amax().to(history.dtype)
+    return new
+
+
+def _quantize(x: Tensor, scale: Tensor, history: Optional[Tensor], *, e5m2: bool):
+    """``(dequantised fp8 value of x, new_scale, new_history)``; delayed scaling when ``history``
+    is given (the scale comes from the stored history, which then takes the current amax)."""
+    fmax = fp8_ops.E5M2_MAX if e5m2 else fp8_ops.E4M3_MAX
+    if history is None:
+        amax, new_history = x.detach().abs().amax().float(), None
+    else:
+        amax, new_history = history.max(), update_amax_history(x, history)
+    new_scale = compute_scale(amax, scale.float(), fmax)
+    dt = torch.float8_e5m2 if e5m2 else torch.float8_e4m3fn
+    q = (x.float() / new_scale).clamp(-fmax, fmax).to(dt)
+    return q.float() * new_scale, new_scale.to(scale.dtype), new_history
+
+
 class _TensorScaledFp8(torch.autograd.Function):
-    """Per-tensor current scaling: e4m3 forward operands, e5m2 gradients, fp32 accumulation."""
+    """Per-tensor scaled fp8 matmul: e4m3 forward operands, e5m2 output gradient, fp32
+    accumulation.  The gradients returned for the scale / history inputs are their NEW VALUES."""
 
     @staticmethod
-    def forward(ctx, x, w):
-        def q(t, e5m2=False):
-            amax = t.detach().abs().amax().float().clamp_min(1e-12)
-            s = amax / (fp8_ops.E5M2_MAX if e5m2 else fp8_ops.E4M3_MAX)
-            return (t.float() / s).to(torch.float8_e5m2 if e5m2 else torch.float8_e4m3fn).float() * s
-
-        ctx.q = q
-        ctx.save_for_backward(x, w)
-        return (q(x) @ q(w)).to(x.dtype)
+    def forward(ctx, x, w, in_scale, k_scale, og_scale, in_hist, k_hist, og_hist):
+        xq, new_in_scale, new_in_hist = _quantize(x, in_scale, in_hist, e5m2=False)
+        wq, new_k_scale, new_k_hist = _quantize(w, k_scale, k_hist, e5m2=False)
+        ctx.save_for_backward(xq, wq, og_scale, og_hist if og_hist is not None else og_scale.new_zeros(0))
+        ctx.has_hist = og_hist is not None
+        ctx.new = (new_in_scale, new_k_scale, new_in_hist, new_k_hist)
+        ctx.dtypes = (x.dtype, w.dtype)
+        return (xq @ wq).to(x.dtype)
 
     @staticmethod
     def backward(ctx, dy):
-        x, w = ctx.saved_tensors
-        q = ctx.q
-        dyq = q(dy, e5m2=True)
-        dx = (dyq @ q(w).t()).to(x.dtype) if ctx.needs_input_grad[0] else None
+        xq, wq, og_scale, og_hist = ctx.saved_tensors
+        dyq, new_og_scale, new_og_hist = _quantize(dy, og_scale, og_hist if ctx.has_hist else None, e5m2=True)
+        new_in_scale, new_k_scale, new_in_hist, new_k_hist = ctx.new
+        dx = (dyq @ wq.t()).to(ctx.dtypes[0]) if ctx.needs_input_grad[0] else None
         dw = None
         if ctx.needs_input_grad[1]:
-            x2 = q(x).reshape(-1, x.shape[-1])
-            dw = (x2.t() @ dyq.reshape(-1, dy.shape[-1])).to(w.dtype)
-        return dx, dw
+            dw = (xq.reshape(-1, xq.shape[-1]).t() @ dyq.reshape(-1, dy.shape[-1])).to(ctx.dtypes[1])
+        return dx, dw, new_in_scale, new_k_scale, new_og_scale, new_in_hist, new_k_hist, new_og_hist
 
 
 class QuantizedDotGeneral(BaseLayer):
@@ -77,16 +118,15 @@ class QuantizedDotGeneral(BaseLayer):
         cfg = self._config
         if cfg.quantization_type != DotGeneralQuantizationType.FP_8 or cfg.scaling != "tensor":
             return {}
-        hist = lambda: ParameterSpec(shape=(cfg.fp8_amax_history_length,), dtype=torch.float32, mesh_axes=(None,),
-                                     initializer=constant_initializer(0.0), weight_decay_scale=0.0)
-        return {"input_amax_history": hist(), "kernel_amax_history": hist(), "output_grad_amax_history": hist()}
-
-    @nowrap
-    def _record_amax(self, name: str, t: Tensor) -> None:
-        hist = self.parameters[name].detach()
-        new = torch.roll(hist, 1)
-        new[0] = t.detach().abs().amax().float()
-        self.add_state_update(name, new)
+        scale = lambda: ParameterSpec(shape=(), dtype=torch.float32, mesh_axes=(),
+                                      initializer=constant_initializer(1.0), weight_decay_scale=0.0)
+        specs = {name: scale() for name in FP8_SCALE_PARAMS}
+        if cfg.fp8_amax_history_length and cfg.fp8_amax_history_length > 0:
+            hist = lambda: ParameterSpec(shape=(cfg.fp8_amax_history_length,), dtype=torch.float32,
+                                         mesh_axes=(None,), initializer=constant_initializer(0.0),
+                                         weight_decay_scale=0.0)
+            specs.update({name: hist() for name in FP8_AMAX_HISTORY_PARAMS})
+        return specs
 
     def matmul(self, x: Tensor, w: Tensor) -> Tensor:
         cfg = self._config
@@ -95,9 +135,14 @@ class QuantizedDotGeneral(BaseLayer):
         if cfg.quantization_type == DotGeneralQuantizationType.INT_8:
             return _int8_matmul(x, w)
         if cfg.scaling == "tensor":
-            self._record_amax("input_amax_history", x)
-            self._record_amax("kernel_amax_history", w)
-            return _TensorScaledFp8.apply(x, w.to(x.dtype))
+            params = self.parameters
+            delayed = "input_amax_history" in params
+            # The trainer's bf16 working copies of these fp32 parameters would lose the scales'
+            # precision: they are read (and their new values returned) in fp32.
+            f32 = lambda name: params[name] if params[name].dtype == torch.float32 else params[name].float()
+            scales = [f32(n) for n in FP8_SCALE_PARAMS]
+            hists = [f32(n) for n in FP8_AMAX_HISTORY_PARAMS] if delayed else [None, None, None]
+            return _TensorScaledFp8.apply(x, w.to(x.dtype), *scales, *hists)
         if cfg.scaling != "block":
             raise NotImplementedError(cfg.scaling)
         w = w.to(x.dtype)

@@ -183,4 +183,13 @@ class FP8ConfigModifier(ConfigModifier):
                     visit(x)
 
         visit(cfg.model)
+        if self._config.scaling == "tensor":
+            # The new scales and amax histories arrive as the "gradients" of those parameters:
+            # they overwrite the parameters instead of going through the optimizer (reference:
+            # axlearn/common/trainer_config_modifier.py:362-370).
+            from axlearn_b200.common.quantized_dot_general.layers import get_all_fp8_param_names
+            from axlearn_b200.common.update_transformation import OverrideInplaceUpdateTransformation
+
+            cfg.learner.optimizer = OverrideInplaceUpdateTransformation.default_config().set(
+                rules=[f".*/{name}" for name in get_all_fp8_param_names()], transformation=cfg.learner.optimizer)
         return cfg

@@ -88,7 +88,15 @@ def override_inplace_update(inner: Any, *, rules: Sequence[str]) -> PartitionedG
                 out.append((path, flat_rest.get(path)))
         return unflatten_items(out), new_state
 
-    return PartitionedGradientTransformation(inner.init, update, inner.partition)
+    # No optimizer state exists for the overridden parameters (reference:
+    # axlearn/common/update_transformation.py:415-424).
+    def init(params):
+        return inner.init(split(params))
+
+    def partition(specs):
+        return inner.partition(split(specs))
+
+    return PartitionedGradientTransformation(init, update, partition)
 
 
 class UpdateTransformation(Configurable):
