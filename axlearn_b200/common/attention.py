@@ -683,6 +683,13 @@ class MultiheadAttention(BaseLayer):
         kv_cache: BaseKVCache.Config = KVCache.default_config()
         scale_kv_before_cache_update: Optional[bool] = None
         logit_sink: Optional[bool] = None
+        # What to do with a ``seq`` mesh axis in self-attention: "ulysses" re-partitions q/k/v from
+        # sequence-sharded to head-sharded with all-to-alls (reference: axlearn/common/
+        # flash_attention/layer.py:165-216); "allgather_kv" keeps the queries sequence-sharded and
+        # gathers K/V over the axis (context parallelism, reference: axlearn/common/
+        # flash_attention/tpu_attention.py:1096-1283) -- the choice when there are fewer KV heads
+        # than ranks or the head count does not divide.
+        seq_parallel_mode: str = "ulysses"
         q_partition_spec: Optional[Sequence[Any]] = None
         k_partition_spec: Optional[Sequence[Any]] = None
         v_partition_spec: Optional[Sequence[Any]] = None
@@ -836,7 +843,21 @@ class MultiheadAttention(BaseLayer):
             else:
                 k_proj = self.scale_key(k_proj)
 
-        if sp > 1:
+        cp_kv = None  # context parallelism: (gathered K, gathered V, key segment ids, first query position)
+        if sp > 1 and cfg.seq_parallel_mode == "allgather_kv":
+            if not default_positions:
+                raise NotImplementedError("sequence parallelism needs default (contiguous) positions")
+            rank = coll.axis_index("seq")
+            k_all = coll.all_gather(k_proj.contiguous(), "seq", dim=1)   # backward: reduce-scatter of dK
+            v_all = coll.all_gather(v_proj.contiguous(), "seq", dim=1)
+            kv_seg = None
+            if segment_ids is not None:
+                kv_seg = coll.all_gather_raw(segment_ids.contiguous(), coll.current_group("seq"), sp, 1)
+            cp_kv = (k_all, v_all, kv_seg, rank * t)
+            sp = 1  # everything after the attention stays sequence-sharded
+        elif sp > 1:
+            if cfg.seq_parallel_mode != "ulysses":
+                raise ValueError(f"unknown seq_parallel_mode {cfg.seq_parallel_mode!r}")
             if not default_positions:
                 raise NotImplementedError("sequence parallelism needs default (contiguous) positions")
             q_proj, k_proj, v_proj = (_seq_to_heads(x, sp) for x in (q_proj, k_proj, v_proj))
@@ -893,7 +914,25 @@ class MultiheadAttention(BaseLayer):
             and not want_probs
             and not (self.is_training and cfg.dropout.rate)
         )
-        if fast:
+        if cp_kv is not None:
+            if not fast:
+                raise NotImplementedError("allgather_kv context parallelism supports the kernel masks only "
+                                          "(causal, sliding window, segment ids, logit cap)")
+            k_all, v_all, kv_seg, q_start = cp_kv
+            if causal:
+                # Queries are positions [q_start, q_start + t): keys beyond the last query are never
+                # visible, and dropping them makes the queries the LAST t positions of the keys,
+                # which is the offset convention of the attention op.
+                k_all, v_all = k_all[:, : q_start + t], v_all[:, : q_start + t]
+                kv_seg = None if kv_seg is None else kv_seg[:, : q_start + t]
+            with remat.tagged(self, "context"):
+                context = ops.attention(
+                    q_proj, k_all, v_all, causal=causal, softmax_scale=softmax_scale,
+                    segment_ids=segment_ids, kv_segment_ids=kv_seg, sliding_window=window,
+                    logit_cap=cfg.atten_logit_cap, q_offset=(q_start if causal else None),
+                )
+            probs = None
+        elif fast:
             with remat.tagged(self, "context"):
                 context = ops.attention(
                     q_proj, dense_kv.k_proj, dense_kv.v_proj, causal=causal,

@@ -198,6 +198,28 @@ def _flat_destinations(routing: Routing) -> Tensor:
     return torch.where(routing.slot >= 0, dest, torch.full_like(dest, -1)).reshape(o * g * s, k)
 
 
+def _fused_routing_ok(layer, logits: Tensor, k: int) -> bool:
+    """The routing kernel covers plain top-k selection (subclasses that pick experts differently
+    keep the step-by-step path)."""
+    from axlearn_b200.ops import moe_ops
+
+    default_index = type(layer)._compute_index in (Top2Gating._compute_index, TopKGating._compute_index)
+    return default_index and moe_ops.gate_kernel_ok(logits, k)
+
+
+def _fused_routing(layer, logits: Tensor, *, k: int, capacity: int):
+    """``(index, gates, slot [O,G,S,K], counts [O,G,K,E], score_sums [O,G,E], lse [O,G,S])`` from
+    the routing kernel, or None when it does not apply.  ``logits`` are already capped."""
+    if not _fused_routing_ok(layer, logits, k):
+        return None
+    from axlearn_b200.ops import moe_ops
+
+    o, g, s, e = logits.shape
+    index, gates, slot, counts, sums, lse = moe_ops.topk_gate(logits.reshape(o * g, s, e), k, capacity)
+    return (index.reshape(o, g, s, k), gates.reshape(o, g, s, k), slot.reshape(o, g, s, k),
+            counts.reshape(o, g, k, e), sums.reshape(o, g, e), lse.reshape(o, g, s))
+
+
 class Top2Gating(BaseGating):
     """Top-2 routing with capacity (GShard).  The second choice is the best expert other than
     the first; gate weights are renormalised over the two."""
@@ -221,30 +243,40 @@ class Top2Gating(BaseGating):
     def forward(self, logits: Tensor) -> Routing:
         cfg = self._config
         logits = _cap_logits(logits.float(), cfg.gating_logit_cap)
-        raw_gates = torch.softmax(logits, dim=-1)
         e = cfg.num_experts
         capacity = _compute_expert_capacity(
             expert_capacity=cfg.expert_capacity,
             capacity_factor=cfg.train_capacity_factor if self.is_training else cfg.eval_capacity_factor,
             group_size=logits.shape[-2], num_experts=e)
-        index = self._compute_index(raw_gates, k=2)                          # [O, G, S, 2]
-        gate_1 = torch.gather(raw_gates, -1, index[..., :1]).squeeze(-1)
-        gate_2 = torch.gather(raw_gates, -1, index[..., 1:]).squeeze(-1)
-        gate_2 = torch.where(index[..., 0] == index[..., 1], torch.zeros_like(gate_2), gate_2)
-        denom = gate_1 + gate_2 + 1e-9
-        weights = torch.stack([gate_1 / denom, gate_2 / denom], dim=-1)
+        raw_gates = None if _fused_routing_ok(self, logits, 2) else torch.softmax(logits, dim=-1)
+        fused = _fused_routing(self, logits, k=2, capacity=capacity)
+        if fused is not None:
+            # One routing kernel: scores, top-2, capacity positions, per-expert counts and score sums.
+            index, gates, slot, counts, score_sums, lse = fused
+            weights = gates / (gates.sum(dim=-1, keepdim=True) + 1e-9)
+            first, second = counts[:, :, 0], counts[:, :, 1]
+            density_proxy = score_sums / index.shape[2]
+            z = lse.square().mean()
+        else:
+            index = self._compute_index(raw_gates, k=2)                          # [O, G, S, 2]
+            gate_1 = torch.gather(raw_gates, -1, index[..., :1]).squeeze(-1)
+            gate_2 = torch.gather(raw_gates, -1, index[..., 1:]).squeeze(-1)
+            gate_2 = torch.where(index[..., 0] == index[..., 1], torch.zeros_like(gate_2), gate_2)
+            denom = gate_1 + gate_2 + 1e-9
+            weights = torch.stack([gate_1 / denom, gate_2 / denom], dim=-1)
+            first = _expert_counts(index[..., 0], e)                            # [O, G, E]
+            second = _expert_counts(index[..., 1], e)
+            density_proxy = raw_gates.mean(dim=-2)
+            slot = _slots_in_priority_order(index, e, capacity)
+            z = _router_z_loss(logits)
         # Load balance: fraction of tokens whose first choice is e, times the mean gate of e.
-        first = _expert_counts(index[..., 0], e)                            # [O, G, E]
         density_1 = first.float() / index.shape[2]
-        density_proxy = raw_gates.mean(dim=-2)
         aux = (density_1 * density_proxy).mean() * e * e
-        slot = _slots_in_priority_order(index, e, capacity)
         kept = slot >= 0
         weights = weights * kept.float()
         over_1 = (first - capacity).clamp(min=0).sum() / first.sum().clamp(min=1)
-        second_total = _expert_counts(index[..., 1], e) + first
+        second_total = second + first
         over_2 = (second_total - capacity).clamp(min=0).sum() / second_total.sum().clamp(min=1)
-        z = _router_z_loss(logits)
         counts = kept.sum(dim=-1)
         for i in range(3):
             self.add_summary(f"dispatch_{i}", (counts == i).sum())
@@ -312,16 +344,24 @@ class TopKGating(BaseGating):
 
             u = prng.uniform(self.prng_key, logits.shape, device=logits.device).clamp(1e-20, 1.0)
             logits = logits - torch.log(-torch.log(u))
-        z = _router_z_loss(logits)
-        raw_gates = self._score(logits)
         capacity = self._expert_capacity(logits.shape[-2])
-        index = self._compute_index(raw_gates, k=k)
-        gate_w = torch.gather(raw_gates, -1, index)
-        normalized = raw_gates if cfg.score_fn is None else raw_gates / raw_gates.sum(dim=-1, keepdim=True)
-        # top-k indices of a token are distinct, so "assigned" counts are plain counts.
-        totals = sum(_expert_counts(index[..., j], e) for j in range(k))      # [O, G, E]
-        aux = (totals.float() / index.shape[2] * normalized.mean(dim=-2)).mean() * e * e / k
-        slot = _slots_in_priority_order(index, e, capacity)
+        fused = _fused_routing(self, logits, k=k, capacity=capacity) if cfg.score_fn is None else None
+        if fused is not None:
+            index, gate_w, slot, counts, score_sums, lse = fused
+            z = lse.square().mean()
+            totals = counts.sum(dim=2)                                        # [O, G, E]
+            mean_scores = score_sums / index.shape[2]
+        else:
+            z = _router_z_loss(logits)
+            raw_gates = self._score(logits)
+            index = self._compute_index(raw_gates, k=k)
+            gate_w = torch.gather(raw_gates, -1, index)
+            normalized = raw_gates if cfg.score_fn is None else raw_gates / raw_gates.sum(dim=-1, keepdim=True)
+            # top-k indices of a token are distinct, so "assigned" counts are plain counts.
+            totals = sum(_expert_counts(index[..., j], e) for j in range(k))      # [O, G, E]
+            mean_scores = normalized.mean(dim=-2)
+            slot = _slots_in_priority_order(index, e, capacity)
+        aux = (totals.float() / index.shape[2] * mean_scores).mean() * e * e / k
         kept = slot >= 0
         weights = gate_w / gate_w.sum(dim=-1, keepdim=True) * kept.float()
         over = (totals - capacity).clamp(min=0).sum() / totals.sum().clamp(min=1)

@@ -42,8 +42,8 @@ int make_bthd_map(CUtensorMap* map, const void* base, int B, int L, int N, int H
 
 constexpr int kFbThreads = 512;
 // Register budget: 512 threads launch with 128 registers each; setmaxnreg only redistributes that
-// launch-time allocation (control 4 warps x 80, exponential / dS 8 warps x 160, drain 4 warps x 112).
-static_assert(128 * 80 + 256 * 160 + 128 * 112 <= 512 * 128, "setmaxnreg split exceeds the launch allocation");
+// launch-time allocation (control 4 warps x 96, exponential / dS 8 warps x 168, drain 4 warps x 80).
+static_assert(128 * 96 + 256 * 168 + 128 * 80 <= 512 * 128, "setmaxnreg split exceeds the launch allocation");
 constexpr int kFbSub = 16384;  // [128 x 64] bf16
 
 struct FlashBwdFusedParams {
@@ -135,9 +135,18 @@ struct FbSmem {
   static constexpr int kQ = kV + kTile;            // 2 stages
   static constexpr int kDO = kQ + 2 * kTile;       // 2 stages
   static constexpr int kDS = kDO + 2 * kTile;      // [128 keys x 128 queries]
-  static constexpr int kBar = kDS + 2 * kFbSub;
+  static constexpr int kLse = kDS + 2 * kFbSub;    // 2 stages x (128 lse2 + 128 delta) floats
+  static constexpr int kBar = kLse + 2048;
   static constexpr int kTotal = kBar + 256;
 };
+
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
@@ -246,7 +255,7 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dv = tmem_base + 256, tm_dk = tmem_base + 256 + H;
 
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
     if (warp == 0) {
       // ---------------------------------------------------------------- TMA producer
       if (elect_one() && run) {
@@ -262,11 +271,14 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           const int st = it & 1;
           const uint32_t ph = (it >> 1) & 1;
           if (!mbar_wait(&q_empty[st], ph ^ 1, p.status, kStatusWaitTimeoutProducer)) break;
-          mbar_arrive_expect_tx(&q_full[st], L::kTile);
+          mbar_arrive_expect_tx(&q_full[st], L::kTile + 1024);
 #pragma unroll
           for (int j = 0; j < H / 64; ++j)
             tma_load_4d(smem + L::kQ + st * L::kTile + j * kFbSub, &tmap_q, &q_full[st], j * 64, head, qt * 128,
                         batch);
+          const int64_t row0 = (static_cast<int64_t>(batch) * p.N + head) * p.Tp + qt * 128;
+          bulk_load_1d(smem + L::kLse + st * 1024, p.lse2 + row0, 512, &q_full[st]);
+          bulk_load_1d(smem + L::kLse + st * 1024 + 512, p.delta + row0, 512, &q_full[st]);
           if (!mbar_wait(&do_empty[st], ph ^ 1, p.status, kStatusWaitTimeoutProducer)) break;
           mbar_arrive_expect_tx(&do_full[st], L::kTile);
 #pragma unroll
@@ -365,7 +377,7 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     }
   } else if (warp < 12) {
     // ------------------------------------------------------------------ exponential / dS
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 160;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
     const int quarter = warp & 3;
     const int half = (warp - 4) >> 2;  // which 64 query columns
     const int r_in = quarter * 32 + lane;
@@ -381,71 +393,76 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     }
     bool ok = run;
     for (int it = 0; it < n_iters && ok; ++it) {
-      const int head = kv_head * group + it / tiles_per_head;
       const int qt = i_lo + it % tiles_per_head;
+      const int st = it & 1;
       const int t0 = qt * 128;
-      // Per-query values of this thread's 64 columns.  Shared memory is saturated by the operand
-      // reads of the shared-memory GEMMs, so they do not come from there: lane l keeps the values
-      // of columns l and l + 32 (two coalesced global loads per quantity, issued before the wait
-      // on the scores) and the loops fetch column c from lane c & 31 with a register shuffle.
-      const int64_t row0 = (static_cast<int64_t>(batch) * p.N + head) * p.Tp + t0 + half * 64;
-      const float lse_lo = __ldg(p.lse2 + row0 + lane), lse_hi = __ldg(p.lse2 + row0 + 32 + lane);
-      const float del_lo = __ldg(p.delta + row0 + lane), del_hi = __ldg(p.delta + row0 + 32 + lane);
-      int qs_lo = -1, qs_hi = -1;
-      if (kGeneral && qseg_row != nullptr) {
-        const int ta = t0 + half * 64 + lane, tb = ta + 32;
-        qs_lo = ta < p.T ? __ldg(qseg_row + ta) : -1;
-        qs_hi = tb < p.T ? __ldg(qseg_row + tb) : -1;
-      }
       // Visible query columns of this key: c_min <= c <= c_max (tile-relative).
       int c_min = 0, c_max = 127;
       if (p.causal) c_min = key - p.q_offset - t0;
       if (kGeneral && p.window >= 0) c_max = key - p.q_offset + p.window - t0;
       if (key >= p.S) c_min = 1 << 20;
-      const bool need_mask = __any_sync(0xffffffffu, c_min > half * 64 || c_max < half * 64 + 63);
+      const bool need_mask = c_min > half * 64 || c_max < half * 64 + 63;
+      const float* lse_s = reinterpret_cast<const float*>(smem + L::kLse + st * 1024) + half * 64;
+      const float* delta_s = lse_s + 128;
+      if (!mbar_wait_warp(&q_full[st], (it >> 1) & 1, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
       if (!mbar_wait_warp(s_full, it & 1, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
       tc_fence_after_sync();
-      float pf[64];  // P (times 1 - tanh^2 under a logit cap): the factor of dS
+      // P^T as bf16 pairs: written to tensor memory for dV and kept in registers (32 instead of
+      // 64 for fp32) as the factor of dS; under a logit cap the factor is P (1 - tanh^2), kept
+      // the same way in a second array.
+      uint32_t pk[32], pw[kGeneral ? 32 : 1];
       {
         uint32_t rs[2][32];
         tmem_ld_32x32(s_addr, rs[0]);
         tmem_ld_32x32(s_addr + 32, rs[1]);
         tmem_ld_wait();
+        const bool capped = kGeneral && p.cap_out != 0.f;
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          uint32_t pk[16];
+        for (int c4 = 0; c4 < 16; ++c4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(lse_s + 4 * c4);
+          const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+          float e[4], ew[4];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int c = hh * 32 + j;
-            const float ls = __shfl_sync(0xffffffffu, hh ? lse_hi : lse_lo, j);
-            float val = __uint_as_float(rs[hh][j]);
+          for (int u = 0; u < 4; ++u) {
+            const int c = 4 * c4 + u;
+            float val = __uint_as_float(rs[c >> 5][c & 31]);
             float w = 1.f;
-            if (kGeneral && p.cap_out != 0.f) {
+            if (capped) {
               const float th = tanh_approx_b(val * p.cap_in);
               val = th * p.cap_out;
               w = 1.f - th * th;
             }
-            float pr = exp2f(val * p.sc - ls);
+            float pr = exp2f(val * p.sc - ls[u]);
             if (need_mask) {
               const int cc = half * 64 + c;
               if (cc < c_min || cc > c_max) pr = 0.f;
             }
             if (kGeneral && qseg_row != nullptr) {
-              const int qs = __shfl_sync(0xffffffffu, hh ? qs_hi : qs_lo, j);
+              const int t = t0 + half * 64 + c;
+              const int qs = t < p.T ? __ldg(qseg_row + t) : -1;
               if (qs != kseg) pr = 0.f;
             }
-            pf[c] = (kGeneral && p.cap_out != 0.f) ? pr * w : pr;
-            // Pack pairs as they complete (the bf16 rounding happens here; pf keeps fp32).
-            if (j & 1) {
-              const float prev = (kGeneral && p.cap_out != 0.f) ? __uint_as_float(rs[hh][j - 1]) : pf[c - 1];
-              pk[j >> 1] = pack_bf16x2(prev, pr);
-            } else if (kGeneral && p.cap_out != 0.f) {
-              rs[hh][j] = __float_as_uint(pr);  // the unweighted probability, for the pair above
-            }
+            e[u] = pr;
+            ew[u] = pr * w;
           }
-          // The first 32 columns travel to tensor memory while the other 32 are computed.
-          tmem_st_32x16(s_addr + hh * 16, pk);
+          pk[2 * c4] = pack_bf16x2(e[0], e[1]);
+          pk[2 * c4 + 1] = pack_bf16x2(e[2], e[3]);
+          if (kGeneral) {
+            pw[2 * c4] = capped ? pack_bf16x2(ew[0], ew[1]) : pk[2 * c4];
+            pw[2 * c4 + 1] = capped ? pack_bf16x2(ew[2], ew[3]) : pk[2 * c4 + 1];
+          }
+          if (c4 == 7) {
+            // The first 32 columns travel to tensor memory while the other 32 are computed.
+            uint32_t lo[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) lo[i] = pk[i];
+            tmem_st_32x16(s_addr, lo);
+          }
         }
+        uint32_t hi[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) hi[i] = pk[16 + i];
+        tmem_st_32x16(s_addr + 16, hi);
         tmem_st_wait();
       }
       tc_fence_before_sync();
@@ -464,9 +481,14 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         tmem_ld_wait();
         float dsv[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float dl = __shfl_sync(0xffffffffu, ch ? del_hi : del_lo, j);
-          dsv[j] = pf[ch * 32 + j] * (__uint_as_float(rd[j]) - dl);
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const float4 d4 = *reinterpret_cast<const float4*>(delta_s + ch * 32 + 4 * c4);
+          const uint32_t f01 = kGeneral ? pw[ch * 16 + 2 * c4] : pk[ch * 16 + 2 * c4];
+          const uint32_t f23 = kGeneral ? pw[ch * 16 + 2 * c4 + 1] : pk[ch * 16 + 2 * c4 + 1];
+          dsv[4 * c4 + 0] = __uint_as_float(f01 << 16) * (__uint_as_float(rd[4 * c4 + 0]) - d4.x);
+          dsv[4 * c4 + 1] = __uint_as_float(f01 & 0xffff0000u) * (__uint_as_float(rd[4 * c4 + 1]) - d4.y);
+          dsv[4 * c4 + 2] = __uint_as_float(f23 << 16) * (__uint_as_float(rd[4 * c4 + 2]) - d4.z);
+          dsv[4 * c4 + 3] = __uint_as_float(f23 & 0xffff0000u) * (__uint_as_float(rd[4 * c4 + 3]) - d4.w);
         }
         fb_store_row_chunk(smem + L::kDS, r_in, half * 64 + ch * 32, dsv);
       }
@@ -512,7 +534,7 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     }
   } else {
     // ------------------------------------------------------------------ dQ drain
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 112;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
     const int quarter = warp & 3;
     const int r_in = quarter * 32 + lane;  // query row within the tile
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
@@ -524,12 +546,11 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       if (!mbar_wait_warp(dq_full, it & 1, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
       tc_fence_after_sync();
 #pragma unroll
-      for (int c = 0; c < H; c += 64) {
-        uint32_t r0[32], r1[32];
+      for (int c = 0; c < H; c += 32) {
+        uint32_t r0[32];
         tmem_ld_32x32(tm_dp + lane_base + c, r0);
-        tmem_ld_32x32(tm_dp + lane_base + c + 32, r1);
         tmem_ld_wait();
-        if (c + 64 >= H) {
+        if (c + 32 >= H) {
           // Everything is in registers: the MMA issuer may overwrite these columns.
           tc_fence_before_sync();
           __syncwarp();
@@ -539,11 +560,6 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         for (int g = 0; g < 8; ++g) {
           red_add_v4(tile + ((c >> 2) + g) * 512, __uint_as_float(r0[4 * g]), __uint_as_float(r0[4 * g + 1]),
                      __uint_as_float(r0[4 * g + 2]), __uint_as_float(r0[4 * g + 3]));
-        }
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          red_add_v4(tile + ((c >> 2) + 8 + g) * 512, __uint_as_float(r1[4 * g]), __uint_as_float(r1[4 * g + 1]),
-                     __uint_as_float(r1[4 * g + 2]), __uint_as_float(r1[4 * g + 3]));
         }
       }
     }

@@ -13,10 +13,10 @@
 //     logit cap are applied inside the kernel, and key tiles that no row of a query tile can
 //     see (left of the window, other segments) are skipped on both sides of the range.
 //
-// Per CTA (640 threads): warp 0 TMA producer, warp 1 MMA issuer (warps 2-3 only fill up the
-// control warpgroup, which hands most of its registers to the others), warps 4..11 softmax of
-// tile A, warps 12..19 softmax of tile B.  TMEM (512 columns): S_A/P_A 0..127, S_B/P_B 128..255,
-// O_A 256.., O_B 384...  P (bf16 pairs) overlays the first 64 columns of S.
+// Per CTA (640 threads): warp 0 TMA producer, warp 1 MMA issuer (warps 2-3 idle: they keep the
+// softmax warps aligned to warpgroups), warps 4..11 softmax of tile A, warps 12..19 of tile B.  TMEM (512 columns): S_A/P_A 0..127, S_B/P_B 128..255,
+// O_A 256.., O_B 384...  P (bf16 pairs): keys 0-63 overlay score columns 0-31, keys 64-127
+// score columns 64-95 (each softmax warp writes over columns it read itself).
 //
 // Reference kernels being replaced: axlearn/common/flash_attention/gpu_attention.py:114-243
 // (segment ids :179-205, block skipping by mask_fn) and the cuDNN call at :792-926.
@@ -28,11 +28,9 @@ namespace axb {
 int make_bthd_map(CUtensorMap* map, const void* base, int B, int L, int N, int H, int box_rows);
 
 constexpr int kF3Threads = 640;
-// Register budget.  640 threads launch with 96 registers each (61440 in all); setmaxnreg only moves
-// registers around INSIDE that launch-time allocation (an increase that asks for more than the
-// decreases released waits forever), so control (4 warps x 64) + softmax (16 warps x 104) must
-// not exceed it.
-static_assert(128 * 64 + 512 * 104 <= 640 * 96, "setmaxnreg split exceeds the launch allocation");
+// 640 threads launch with 96 registers each.  The softmax warps hold at most 32 scores at a time
+// (scores are re-read from tensor memory for the second pass), which fits without spills, so no
+// register redistribution (setmaxnreg) is needed.
 constexpr uint32_t kGaveUp = 0x7fc0dead;  // NaN payload: "my wait on the score tile timed out"
 
 struct FlashFwd3Params {
@@ -192,7 +190,6 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp < 4) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one() && any) {
@@ -251,7 +248,8 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           // 16 keys per step: 8 TMEM columns of packed bf16 pairs; 16 V rows = 2048 B.
-          tc_mma_f16_ts(tmem_base + 256 + x * 128, tmem_base + x * 128 + kk * 8,
+          // keys 0-63 (first half's probabilities) at columns 0-31, keys 64-127 at columns 64-95
+          tc_mma_f16_ts(tmem_base + 256 + x * 128, tmem_base + x * 128 + (kk >> 2) * 64 + (kk & 3) * 8,
                         umma_smem_desc(v_addr + kk * 2048, L::kSub, 1024), idesc_pv,
                         (!first || kk > 0) ? 1u : 0u);
         }
@@ -295,7 +293,6 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   }
   } else {
     // ------------------------------------------------------------------ softmax / epilogue
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
     const int idx = warp - 4;
     const int x = idx >> 3;               // query tile
     const int half = (idx >> 2) & 1;      // which 64 score columns / which half of the O columns
@@ -306,7 +303,7 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     const int bar_id = 1 + x * 4 + quarter;
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t s_addr = tmem_base + lane_base + x * 128 + half * 64;
-    const uint32_t p_addr = tmem_base + lane_base + x * 128 + half * 32;
+    const uint32_t p_addr = tmem_base + lane_base + x * 128 + half * 64;  // P pairs over the own scores
     const uint32_t o_addr = tmem_base + lane_base + 256 + x * 128 + half * (H / 2);
     float* my_max = ex_max + (x * 2 + half) * 128 + r_in;
     float* other_max = ex_max + (x * 2 + (half ^ 1)) * 128 + r_in;
@@ -330,72 +327,65 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       // A wait that gives up must not leave the partner warp alone at the named barrier: both
       // halves always reach it, and a failed wait travels through the exchange slot.
       const bool got = mbar_wait_warp(&s_full[x], kpar, p.status, kStatusWaitTimeoutEpilogue);
-      uint32_t ra[32], rb[32];
-      float tmax = -INFINITY;
-      if (got) {
-        tc_fence_after_sync();
-        tmem_ld_32x32(s_addr, ra);
-        tmem_ld_32x32(s_addr + 32, rb);
+      const int s0 = it * 128 + half * 64;  // first key column of this thread
+      // Scores are read from tensor memory twice, 32 columns at a time (once for the row maximum,
+      // once for the exponentials): a TMEM read is cheap, while keeping all 64 scores of the row
+      // in registers next to the packed probabilities does not fit the register budget and
+      // spilled into the hot loop.  Masks and the logit cap are part of the load.
+      auto load_scores = [&](int hh, uint32_t (&r)[32]) {
+        tmem_ld_32x32(s_addr + hh * 32, r);
         tmem_ld_wait();
-        const int s0 = it * 128 + half * 64;  // first key column of this thread
+        const int c0 = s0 + hh * 32;
         const uint32_t ninf = __float_as_uint(-INFINITY);
         if (kGeneral) {
           if (p.cap_out != 0.f) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              ra[j] = __float_as_uint(tanh_approx(__uint_as_float(ra[j]) * p.cap_in) * p.cap_out);
-              rb[j] = __float_as_uint(tanh_approx(__uint_as_float(rb[j]) * p.cap_in) * p.cap_out);
-            }
+            for (int j = 0; j < 32; ++j)
+              r[j] = __float_as_uint(tanh_approx(__uint_as_float(r[j]) * p.cap_in) * p.cap_out);
           }
-          const bool edge = (s0 < c_lo) || (s0 + 63 > c_hi);
-          if (edge) {
+          if ((c0 < c_lo) || (c0 + 31 > c_hi)) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (static_cast<uint32_t>(s0 + j - c_lo) > c_span || c_hi < c_lo) ra[j] = ninf;
-              if (static_cast<uint32_t>(s0 + 32 + j - c_lo) > c_span || c_hi < c_lo) rb[j] = ninf;
-            }
+            for (int j = 0; j < 32; ++j)
+              if (static_cast<uint32_t>(c0 + j - c_lo) > c_span || c_hi < c_lo) r[j] = ninf;
           }
           if (kseg_row != nullptr) {
 #pragma unroll
-            for (int j4 = 0; j4 < 8; ++j4) {
-              int ka[4], kb[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const int ca = s0 + 4 * j4 + e, cb = ca + 32;
-                ka[e] = ca < p.S ? __ldg(kseg_row + ca) : -2;
-                kb[e] = cb < p.S ? __ldg(kseg_row + cb) : -2;
-              }
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                if (ka[e] != seg) ra[4 * j4 + e] = ninf;
-                if (kb[e] != seg) rb[4 * j4 + e] = ninf;
-              }
+            for (int j = 0; j < 32; ++j) {
+              const int c = c0 + j;
+              const int ks = c < p.S ? __ldg(kseg_row + c) : -2;
+              if (ks != seg) r[j] = ninf;
             }
           }
         } else {
           const int tile_t0 = t0 + x * 128;
-          const bool need_mask = (p.causal && s0 + 63 > tile_t0 + p.q_offset) || (s0 + 64 > p.S);
-          if (need_mask) {
+          if ((p.causal && c0 + 31 > tile_t0 + p.q_offset) || (c0 + 32 > p.S)) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (s0 + j > c_hi) ra[j] = ninf;
-              if (s0 + 32 + j > c_hi) rb[j] = ninf;
-            }
+            for (int j = 0; j < 32; ++j)
+              if (c0 + j > c_hi) r[j] = ninf;
           }
         }
-        // Row maximum: four independent chains over this half, then the other half's value.
-        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      };
+      float tmax = -INFINITY;
+      if (got) {
+        tc_fence_after_sync();
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          mx0 = fmaxf(mx0, __uint_as_float(ra[j]));
-          mx1 = fmaxf(mx1, __uint_as_float(ra[j + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(rb[j]));
-          mx3 = fmaxf(mx3, __uint_as_float(rb[j + 1]));
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t r[32];
+          load_scores(hh, r);
+          // Row maximum: four independent chains.
+          float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            mx0 = fmaxf(mx0, __uint_as_float(r[j]));
+            mx1 = fmaxf(mx1, __uint_as_float(r[j + 1]));
+            mx2 = fmaxf(mx2, __uint_as_float(r[j + 2]));
+            mx3 = fmaxf(mx3, __uint_as_float(r[j + 3]));
+          }
+          tmax = fmaxf(tmax, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
         }
-        tmax = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       }
       my_max[kpar * 512] = got ? tmax : __uint_as_float(kGaveUp);
-      pair_barrier(bar_id);  // both halves have their scores in registers: P may overwrite S now
+      pair_barrier(bar_id);
       const float other = other_max[kpar * 512];
       if (!got || __any_sync(0xffffffffu, __float_as_uint(other) == kGaveUp)) {
         ok = false;
@@ -426,33 +416,28 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         l_sum *= alpha;
       }
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-      // Probabilities rounded to bf16 and packed two per register: q[j] = (p[2j], p[2j+1]).
-      uint32_t qa[16], qb[16];
+      // Probabilities rounded to bf16, packed two per register, 32 columns (16 registers) at a
+      // time; each chunk travels to tensor memory while the next one is computed.  This thread's
+      // probabilities overlay the first 32 columns of its OWN 64 score columns (the chunk being
+      // written was consumed just before, the other chunk lies beyond), so the two halves of a
+      // row never touch each other's columns.
       float l0 = 0.f, l1 = 0.f;
-      // Exponentials in batches of eight independent values.
 #pragma unroll
-      for (int j0 = 0; j0 < 32; j0 += 8) {
-        float e[8];
-        exp2_batch8(ra + j0, p.sc, m_use, e, (j0 >> 3) < kPolyBatches);
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t r[32], q[16];
+        load_scores(hh, r);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) qa[(j0 >> 1) + u] = pack_bf16x2(e[2 * u], e[2 * u + 1]);
-        l0 += (e[0] + e[1]) + (e[2] + e[3]);
-        l1 += (e[4] + e[5]) + (e[6] + e[7]);
-      }
-      // The first half of this thread's probabilities travels to tensor memory while the second
-      // half is computed.
-      tmem_st_32x16(p_addr, qa);
+        for (int j0 = 0; j0 < 32; j0 += 8) {
+          float e[8];
+          exp2_batch8(r + j0, p.sc, m_use, e, (hh * 4 + (j0 >> 3)) < kPolyBatches);
 #pragma unroll
-      for (int j0 = 0; j0 < 32; j0 += 8) {
-        float e[8];
-        exp2_batch8(rb + j0, p.sc, m_use, e, false);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) qb[(j0 >> 1) + u] = pack_bf16x2(e[2 * u], e[2 * u + 1]);
-        l0 += (e[0] + e[1]) + (e[2] + e[3]);
-        l1 += (e[4] + e[5]) + (e[6] + e[7]);
+          for (int u = 0; u < 4; ++u) q[(j0 >> 1) + u] = pack_bf16x2(e[2 * u], e[2 * u + 1]);
+          l0 += (e[0] + e[1]) + (e[2] + e[3]);
+          l1 += (e[4] + e[5]) + (e[6] + e[7]);
+        }
+        tmem_st_32x16(p_addr + hh * 16, q);
       }
       l_sum += l0 + l1;
-      tmem_st_32x16(p_addr + 16, qb);
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();

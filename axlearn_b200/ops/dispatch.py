@@ -118,16 +118,23 @@ def attention(
     causal: bool = False,
     softmax_scale: Optional[float] = None,
     segment_ids=None,
+    kv_segment_ids=None,
     sliding_window: Optional[int] = None,
     logit_cap: Optional[float] = None,
     dropout_mask=None,
+    q_offset: Optional[int] = None,
 ):
+    """``q_offset``: position of the first query among the keys; only ``len(keys) - len(queries)``
+    (queries are the last positions: decoding, context parallelism) or None / 0 with equal lengths
+    are supported."""
+    if q_offset is not None and q_offset != k.shape[1] - q.shape[1]:
+        raise NotImplementedError("q_offset must equal len(keys) - len(queries)")
     if (
         _cuda(q, k, v)
         and q.dtype == torch.bfloat16
         and bias is None
         and dropout_mask is None
-        and (segment_ids is None or q.shape[1] == k.shape[1])
+        and (segment_ids is None or q.shape[1] == k.shape[1] or kv_segment_ids is not None)
         and _ops().flash_supported(q, k, v, segment_ids)
     ):
         # Segment ids, the sliding window and the logit cap are masks of the kernel itself; only an
@@ -135,7 +142,7 @@ def attention(
         # (Under a remat policy that keeps the context, the replay skips the forward kernel.)
         return _ops().flash_attention(
             q, k, v, causal=causal, softmax_scale=softmax_scale, segment_ids=segment_ids,
-            sliding_window=sliding_window, logit_cap=logit_cap
+            kv_segment_ids=kv_segment_ids, sliding_window=sliding_window, logit_cap=logit_cap
         )
     return reference.attention(
         q,
@@ -145,9 +152,11 @@ def attention(
         causal=causal,
         softmax_scale=softmax_scale,
         segment_ids=segment_ids,
+        kv_segment_ids=kv_segment_ids,
         sliding_window=sliding_window,
         logit_cap=logit_cap,
         dropout_mask=dropout_mask,
+        q_offset=(None if not q_offset else torch.full((q.shape[0],), q_offset, device=q.device)),
     )
 
 

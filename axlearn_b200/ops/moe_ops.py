@@ -459,3 +459,107 @@ def ep_combine(y: torch.Tensor, weight: torch.Tensor, dest: torch.Tensor, ex: Ex
     dest = dest.to(torch.int32).contiguous()
     rows = ex.world * ex.experts_per_rank * ex.slots
     return _EpCombine.apply(y, weight, dest, inverse_pairs(dest, rows), ex)
+
+
+# ------------------------------------------------------------------------------------------
+# Routing (csrc/moe_gate.cu): scores, top-k, capacity positions and aux-loss sums.
+# ------------------------------------------------------------------------------------------
+
+_gate_configured = False
+
+
+def _gate_lib():
+    global _gate_configured
+    h = cuda_ops.lib()
+    if not _gate_configured:
+        c_float = ctypes.c_float
+        h.axb_moe_gate_parts.argtypes = [c_int]
+        h.axb_moe_gate_parts.restype = c_int
+        h.axb_moe_gate_fwd.argtypes = [c_void_p] * 8 + [c_int] * 5 + [c_float, c_int, c_void_p]
+        h.axb_moe_gate_fwd.restype = c_int
+        h.axb_moe_gate_bwd.argtypes = [c_void_p] * 7 + [c_int] * 4 + [c_float, c_int, c_void_p]
+        h.axb_moe_gate_bwd.restype = c_int
+        _gate_configured = True
+    return h
+
+
+def gate_kernel_ok(logits: torch.Tensor, k: int) -> bool:
+    from axlearn_b200.ops import dispatch as op_dispatch
+
+    return (logits.is_cuda and logits.shape[-1] <= 256 and 1 <= k <= min(8, logits.shape[-1])
+            and not op_dispatch._flags.force_reference)  # pylint: disable=protected-access
+
+
+def topk_gate_reference(logits: torch.Tensor, k: int, capacity: int, logit_cap: float = 0.0, sigmoid: bool = False):
+    """The same routing in PyTorch statements (oracle; ``logits [G, S, E]``)."""
+    g, s, e = logits.shape
+    x = logits.float()
+    if logit_cap > 0:
+        x = logit_cap * torch.tanh(x / logit_cap)
+    lse = torch.logsumexp(x, dim=-1)
+    score = torch.sigmoid(x) if sigmoid else torch.softmax(x, dim=-1)
+    gate, index = score.topk(k, dim=-1)
+    flat = index.permute(0, 2, 1).reshape(g, k * s)                      # choice-major priority
+    keys = (torch.arange(g, device=x.device)[:, None] * e + flat).reshape(-1)
+    order = torch.sort(keys, stable=True).indices
+    cnt = torch.bincount(keys, minlength=g * e)
+    starts = cnt.cumsum(0) - cnt
+    pos = torch.empty_like(keys)
+    pos[order] = torch.arange(keys.numel(), device=x.device) - starts[keys[order]]
+    slot = torch.where(pos < capacity, pos, torch.full_like(pos, -1)).reshape(g, k, s).permute(0, 2, 1).contiguous()
+    counts = torch.stack([torch.nn.functional.one_hot(index[..., j], e).sum(dim=1) for j in range(k)], dim=1)
+    return index, gate, slot, counts, score.sum(dim=1), lse
+
+
+class _TopkGate(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, k, capacity, logit_cap, sigmoid):
+        g, s, e = logits.shape
+        dev = logits.device
+        logits = logits.contiguous()
+        h = _gate_lib()
+        index = torch.empty((g, s, k), dtype=torch.int32, device=dev)
+        gate = torch.empty((g, s, k), dtype=torch.float32, device=dev)
+        slot = torch.empty((g, s, k), dtype=torch.int32, device=dev)
+        counts = torch.empty((g, k, e), dtype=torch.int32, device=dev)
+        proxy = torch.empty((g, e), dtype=torch.float32, device=dev)
+        lse = torch.empty((g, s), dtype=torch.float32, device=dev)
+        part = torch.empty((g, h.axb_moe_gate_parts(s), e), dtype=torch.float32, device=dev)
+        rc = h.axb_moe_gate_fwd(logits.data_ptr(), index.data_ptr(), gate.data_ptr(), slot.data_ptr(),
+                                counts.data_ptr(), proxy.data_ptr(), lse.data_ptr(), part.data_ptr(), g, s, e, k,
+                                int(capacity), float(logit_cap), 1 if sigmoid else 0, cuda_ops._stream())  # pylint: disable=protected-access
+        cuda_ops._check(rc, "axb_moe_gate_fwd")  # pylint: disable=protected-access
+        cuda_ops.launch_count += 1
+        ctx.save_for_backward(logits, index, lse)
+        ctx.args = (k, float(logit_cap), bool(sigmoid))
+        index64, slot64, counts64 = index.long(), slot.long(), counts.long()
+        ctx.mark_non_differentiable(index64, slot64, counts64)
+        return index64, gate, slot64, counts64, proxy, lse
+
+    @staticmethod
+    def backward(ctx, _di, d_gate, _ds, _dc, d_proxy, d_lse):
+        logits, index, lse = ctx.saved_tensors
+        k, cap, sigmoid = ctx.args
+        g, s, e = logits.shape
+        d_logits = torch.empty_like(logits)
+        opt = lambda t: None if t is None else t.float().contiguous()
+        d_gate, d_proxy, d_lse = opt(d_gate), opt(d_proxy), opt(d_lse)
+        if d_gate is None:
+            d_gate = torch.zeros((g, s, k), dtype=torch.float32, device=logits.device)
+        rc = _gate_lib().axb_moe_gate_bwd(
+            logits.data_ptr(), index.data_ptr(), lse.data_ptr(), d_gate.data_ptr(), cuda_ops._p(d_proxy),  # pylint: disable=protected-access
+            cuda_ops._p(d_lse), d_logits.data_ptr(), g, s, e, k, cap, 1 if sigmoid else 0, cuda_ops._stream())  # pylint: disable=protected-access
+        cuda_ops._check(rc, "axb_moe_gate_bwd")  # pylint: disable=protected-access
+        return d_logits, None, None, None, None
+
+
+def topk_gate(logits: torch.Tensor, k: int, capacity: int, *, logit_cap: float = 0.0, sigmoid: bool = False):
+    """Routing of ``logits [G, S, E]`` (fp32): ``(index [G,S,K], gate [G,S,K], slot [G,S,K],
+    counts [G,K,E], score_sums [G,E], lse [G,S])``.  ``gate`` are the chosen experts' scores,
+    ``slot`` the capacity positions in choice-major priority order (-1 = dropped), ``counts`` the
+    tokens per (choice, expert), ``score_sums`` the per-expert sums of the scores over the group's
+    tokens and ``lse`` the per-token log-sum-exp of the (capped) logits; ``gate``, ``score_sums`` and
+    ``lse`` are differentiable."""
+    if gate_kernel_ok(logits, k):
+        return _TopkGate.apply(logits.float(), int(k), int(capacity), float(logit_cap), bool(sigmoid))
+    return topk_gate_reference(logits, k, capacity, logit_cap, sigmoid)

@@ -115,3 +115,72 @@ def test_peer_exchange_on_one_gpu_matches_local_dispatch(monkeypatch):
     assert torch.equal(dx, ref_dx)
     for name in ("wi_0_weight", "wo_weight", "gate_weight"):
         assert torch.equal(p[name].grad, ref_p[name].grad), name
+
+
+@pytest.mark.parametrize("g,s,e,k,cap,logit_cap,sigmoid", [
+    (2, 300, 8, 2, 60, 0.0, False),       # Mixtral-like: 8 experts, top-2, some tokens dropped
+    (1, 4096, 8, 2, 2048, 0.0, False),
+    (3, 1111, 16, 1, 50, 5.0, False),     # top-1 with a logit cap
+    (2, 700, 128, 8, 64, 0.0, False),     # Qwen3-like: 128 experts, top-8
+    (1, 513, 40, 4, 1000, 0.0, True),     # sigmoid scores, nothing dropped
+    (1, 37, 5, 3, 7, 0.0, False),         # tiny, fewer tokens than one chunk
+])
+def test_routing_kernel_matches_torch_statements(g, s, e, k, cap, logit_cap, sigmoid):
+    """Scores, top-k, capacity positions (choice-major priority), counts, score sums and the
+    log-sum-exp from one kernel, and the gradient of the logits from its backward kernel."""
+    from axlearn_b200.ops import moe_ops
+
+    torch.manual_seed(0)
+    logits = (torch.randn(g, s, e, device="cuda") * 2).requires_grad_()
+    index, gate, slot, counts, sums, lse = moe_ops.topk_gate(logits, k, cap, logit_cap=logit_cap, sigmoid=sigmoid)
+    ref_logits = logits.detach().clone().requires_grad_()
+    r_index, r_gate, r_slot, r_counts, r_sums, r_lse = moe_ops.topk_gate_reference(ref_logits, k, cap, logit_cap, sigmoid)
+    # Ties between equal scores are vanishingly rare with random floats: indices must agree.
+    assert torch.equal(index, r_index)
+    assert torch.equal(slot, r_slot)
+    assert torch.equal(counts, r_counts)
+    # (the kernel's tanh of the logit cap is the fast approximation)
+    tol = 2e-3 if logit_cap > 0 else 1e-6
+    assert torch.allclose(gate, r_gate, atol=tol, rtol=1e-5)
+    assert torch.allclose(sums, r_sums, atol=1e-3 + s * tol, rtol=1e-5)
+    assert torch.allclose(lse, r_lse, atol=max(tol, 1e-5), rtol=1e-5)
+    # Every expert's kept positions are exactly 0 .. min(count, capacity) - 1.
+    for gi in range(g):
+        for ei in range(min(e, 4)):
+            pos = slot[gi][index[gi] == ei]
+            kept = pos[pos >= 0].sort().values
+            assert torch.equal(kept, torch.arange(kept.numel(), device="cuda"))
+            assert kept.numel() == min(int(counts[gi, :, ei].sum()), cap)
+    w_gate = torch.randn_like(gate)
+    w_sums = torch.randn_like(sums)
+    w_lse = torch.randn_like(lse)
+    ((gate * w_gate).sum() + (sums * w_sums).sum() + (lse * w_lse).sum()).backward()
+    ((r_gate * w_gate).sum() + (r_sums * w_sums).sum() + (r_lse * w_lse).sum()).backward()
+    assert torch.allclose(logits.grad, ref_logits.grad, atol=2e-5 if logit_cap == 0 else 5e-3, rtol=1e-4)
+
+
+def test_gating_layers_use_the_routing_kernel_and_match_the_step_by_step_path():
+    from axlearn_b200.common import prng
+    from axlearn_b200.common.mixture_of_experts import Top2Gating, TopKGating
+    from axlearn_b200.common.module import functional
+    from axlearn_b200.ops import dispatch
+
+    torch.manual_seed(1)
+    for cfg in (Top2Gating.default_config().set(name="g", num_experts=8, train_capacity_factor=1.0),
+                TopKGating.default_config().set(name="g", num_experts=16, num_experts_per_token=4,
+                                                train_capacity_factor=2.0)):
+        layer = cfg.instantiate(parent=None)
+        logits = torch.randn(1, 2, 512, cfg.num_experts, device="cuda")
+        a = logits.clone().requires_grad_()
+        out_a, _ = functional(layer, prng.PRNGKey(0), {}, [a], is_training=True)
+        b = logits.clone().requires_grad_()
+        with dispatch.use_reference_ops():
+            out_b, _ = functional(layer, prng.PRNGKey(0), {}, [b], is_training=True)
+        assert torch.equal(out_a.expert_index, out_b.expert_index) and torch.equal(out_a.slot, out_b.slot)
+        assert torch.allclose(out_a.weight, out_b.weight, atol=1e-5)
+        assert torch.allclose(out_a.load_balance_loss, out_b.load_balance_loss, rtol=1e-4)
+        assert torch.allclose(out_a.router_z_loss, out_b.router_z_loss, rtol=1e-4)
+        wa = torch.randn_like(out_a.weight)
+        ((out_a.weight * wa).sum() + out_a.load_balance_loss + out_a.router_z_loss).backward()
+        ((out_b.weight * wa).sum() + out_b.load_balance_loss + out_b.router_z_loss).backward()
+        assert torch.allclose(a.grad, b.grad, atol=2e-5, rtol=1e-3)

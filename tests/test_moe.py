@@ -170,3 +170,25 @@ def test_moe_layer_structures_run(structure):
     x = torch.randn(2, 8, 16)
     _, _, out, _ = _run(cfg, [x])
     assert out.shape == x.shape and torch.isfinite(out).all()
+
+
+def test_routing_reference_function_matches_the_layer_statements():
+    """``moe_ops.topk_gate_reference`` (the oracle of the routing kernel) agrees with the slot /
+    count helpers the gating layers use."""
+    import torch
+
+    from axlearn_b200.common import mixture_of_experts as moe
+    from axlearn_b200.ops import moe_ops
+
+    torch.manual_seed(0)
+    g, s, e, k, cap = 3, 200, 8, 2, 30
+    logits = torch.randn(g, s, e)
+    index, gate, slot, counts, sums, lse = moe_ops.topk_gate_reference(logits, k, cap)
+    probs = torch.softmax(logits, -1)
+    assert torch.equal(index, probs.topk(k, -1).indices)
+    assert torch.allclose(gate, torch.gather(probs, -1, index))
+    want_slot = moe._slots_in_priority_order(index.reshape(1, g, s, k), e, cap)  # pylint: disable=protected-access
+    assert torch.equal(slot, want_slot.reshape(g, s, k))
+    for j in range(k):
+        assert torch.equal(counts[:, j], moe._expert_counts(index[..., j].reshape(1, g, s), e).reshape(g, e))  # pylint: disable=protected-access
+    assert torch.allclose(sums, probs.sum(1)) and torch.allclose(lse, torch.logsumexp(logits, -1))

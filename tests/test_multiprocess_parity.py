@@ -26,6 +26,8 @@ def _free_port() -> int:
 
 
 def _train(directory, mesh_axes: dict, steps: int, num_kv_heads=None):
+    mesh_axes = dict(mesh_axes)
+    seq_mode = mesh_axes.pop("seq_parallel_mode", None)
     sys.path.insert(0, REPO)
     from axlearn_b200.common import prng
     from axlearn_b200.experiments.text.gpt.common import mesh_shape_from_axes
@@ -34,6 +36,8 @@ def _train(directory, mesh_axes: dict, steps: int, num_kv_heads=None):
     cfg = tiny_fuji_trainer_config(
         directory, max_step=steps, save_every_n_steps=1000, mesh_shape=mesh_shape_from_axes(**mesh_axes),
         hidden=64, heads=4, ffn=128, vocab=512, seq=32, batch=4, layers=2, num_kv_heads=num_kv_heads)
+    if seq_mode is not None:
+        cfg.model.decoder.transformer.layer.self_attention.attention.seq_parallel_mode = seq_mode
     trainer = cfg.instantiate(parent=None)
     trainer.init(prng.PRNGKey(0))
     losses = []
@@ -66,12 +70,16 @@ def _worker(rank, world, port, directory, mesh_axes, steps, out_queue):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mesh_axes", [dict(fsdp=2), dict(model=2), dict(fsdp=2, model=2), dict(data=2), dict(seq=2)])
+@pytest.mark.parametrize("mesh_axes", [
+    dict(fsdp=2), dict(model=2), dict(fsdp=2, model=2), dict(data=2), dict(seq=2),
+    # Context parallelism: queries stay sequence-sharded, K / V are gathered over the seq axis.
+    dict(seq=2, seq_parallel_mode="allgather_kv"),
+])
 def test_sharded_matches_single_process(tmp_path, mesh_axes):
     steps = 3
     world = 1
     for v in mesh_axes.values():
-        world *= v
+        world *= v if isinstance(v, int) else 1
     ref_trainer, ref_losses = _train(tmp_path / "single", {}, steps)
     ref_w = ref_trainer.trainer_state["model"]["decoder"]["transformer"]["repeat"]["layer"]["feed_forward"]["linear2"]["weight"]
     ctx = mp.get_context("spawn")
