@@ -33,7 +33,7 @@ import torch.distributed as dist
 
 from axlearn_b200.common import prng
 from axlearn_b200.common.base_layer import BaseLayer, ParameterSpec
-from axlearn_b200.common.config import REQUIRED, InstantiableConfig, Required, config_class
+from axlearn_b200.common.config import REQUIRED, Configurable, InstantiableConfig, Required, config_class
 from axlearn_b200.common.module import current_context, new_output_collection, nowrap, set_current_context
 from axlearn_b200.common.utils import VDict, flatten_items, tree_map
 from axlearn_b200.parallel import collectives as coll
@@ -50,39 +50,78 @@ def _pipeline_group():
     return mesh.group("pipeline"), mesh.shape["pipeline"], mesh.coords["pipeline"], mesh.ranks_along("pipeline")
 
 
-class _Send(torch.autograd.Function):
-    """Sends ``x`` to global rank ``dst``; returns a token that keeps the node in the graph.
-    Backward receives the gradient of ``x`` from ``dst``."""
+class _Transfers:
+    """The point-to-point operations of one pipeline pass (forward and its backward).
+
+    Every transfer is posted asynchronously (``isend`` / ``irecv``: on NCCL they run on the
+    process group's own streams, beside the compute stream) and waited for only where its data is
+    needed, so a stage computes micro-batch ``i`` while micro-batch ``i + 1`` arrives and
+    micro-batch ``i - 1`` leaves.  With ``overlap=False`` every operation is waited for at once
+    (the plain blocking schedule; kept for debugging).
+    """
+
+    def __init__(self, group, overlap: bool):
+        self.group = group
+        self.overlap = overlap
+        self._sends: list = []          # (work, tensor): tensors stay alive until the pass ends
+        self._grad_recvs: dict = {}     # micro-batch -> (work, buffer)
+
+    def send(self, x: Tensor, dst: int) -> None:
+        x = x.detach().contiguous()
+        work = dist.isend(x, dst=dst, group=self.group)
+        if self.overlap:
+            self._sends.append((work, x))
+        else:
+            work.wait()
+
+    def post_recv(self, shape, dtype, device, src: int):
+        buf = torch.empty(shape, dtype=dtype, device=device)
+        return dist.irecv(buf, src=src, group=self.group), buf
+
+    def grad_from(self, i: int, src: int, meta) -> Tensor:
+        """Gradient of micro-batch ``i`` from the next stage.  Backward visits micro-batches in
+        reverse order, so the receive for ``i - 1`` is posted before waiting for ``i``."""
+        for j in ((i, i - 1) if self.overlap else (i,)):
+            if j >= 0 and j not in self._grad_recvs:
+                self._grad_recvs[j] = self.post_recv(*meta, src)
+        work, buf = self._grad_recvs.pop(i)
+        work.wait()
+        return buf
+
+    def drain(self) -> None:
+        for work, _ in self._sends:
+            work.wait()
+        self._sends.clear()
+
+
+class _Sent(torch.autograd.Function):
+    """Sends ``x`` (micro-batch ``i``) to global rank ``dst``; returns a token that keeps the node
+    in the graph.  Backward receives the gradient of ``x`` from ``dst``."""
 
     @staticmethod
-    def forward(ctx, x, dst, group):
-        ctx.dst, ctx.group, ctx.meta = dst, group, (x.shape, x.dtype, x.device)
-        dist.send(x.contiguous(), dst=dst, group=group)
+    def forward(ctx, x, dst, transfers, i):
+        ctx.dst, ctx.transfers, ctx.i, ctx.meta = dst, transfers, i, (x.shape, x.dtype, x.device)
+        transfers.send(x, dst)
         return x.new_zeros(())
 
     @staticmethod
     def backward(ctx, _token_grad):
-        shape, dtype, device = ctx.meta
-        g = torch.empty(shape, dtype=dtype, device=device)
-        dist.recv(g, src=ctx.dst, group=ctx.group)
-        return g, None, None
+        return ctx.transfers.grad_from(ctx.i, ctx.dst, ctx.meta), None, None, None
 
 
-class _Recv(torch.autograd.Function):
-    """Receives a tensor like ``like`` from global rank ``src``; backward sends the gradient
-    back.  ``anchor`` (a tensor that requires grad) ties the node into the graph."""
+class _Received(torch.autograd.Function):
+    """Puts a received buffer into the graph; backward sends its gradient back to ``src``.
+    ``anchor`` (a tensor that requires grad) ties the node into the graph."""
 
     @staticmethod
-    def forward(ctx, anchor, src, group, shape, dtype):
-        ctx.src, ctx.group = src, group
-        out = torch.empty(shape, dtype=dtype, device=anchor.device)
-        dist.recv(out, src=src, group=group)
-        return out
+    def forward(ctx, anchor, buf, src, transfers):
+        ctx.src, ctx.transfers = src, transfers
+        return buf
 
     @staticmethod
     def backward(ctx, g):
-        dist.send(g.contiguous(), dst=ctx.src, group=ctx.group)
-        return None, None, None, None, None
+        ctx.transfers.send(g, ctx.src)
+        return None, None, None, None
 
 
 class _BroadcastFromLast(torch.autograd.Function):
@@ -90,8 +129,9 @@ class _BroadcastFromLast(torch.autograd.Function):
     onto the last stage.  ``tokens`` are the send tokens of this rank (kept alive in the graph)."""
 
     @staticmethod
-    def forward(ctx, y, src, group, is_last, *tokens):
-        ctx.src, ctx.group, ctx.is_last, ctx.n = src, group, is_last, len(tokens)
+    def forward(ctx, y, src, group, is_last, transfers, *tokens):
+        ctx.src, ctx.group, ctx.is_last, ctx.n, ctx.transfers = src, group, is_last, len(tokens), transfers
+        transfers.drain()
         out = y.detach().clone().contiguous()
         dist.broadcast(out, src=src, group=group)
         return out
@@ -101,7 +141,122 @@ class _BroadcastFromLast(torch.autograd.Function):
         g = g.contiguous().clone()
         dist.reduce(g, dst=ctx.src, op=dist.ReduceOp.SUM, group=ctx.group)
         zero = g.new_zeros(())
-        return (g if ctx.is_last else torch.zeros_like(g)), None, None, None, *([zero] * ctx.n)
+        return (g if ctx.is_last else torch.zeros_like(g)), None, None, None, None, *([zero] * ctx.n)
+
+
+class _CollectStreams(torch.autograd.Function):
+    """The output side of the stream schedule.
+
+    Micro-batch ``i`` belongs to stream ``i // (M / N)``, owned by the stage of that index.  The
+    last stage has already posted a send of every finished micro-batch to its owner (inside the
+    micro-batch loop, so those transfers overlap the remaining compute); here the owners receive
+    their streams and one all-gather gives every rank the whole output.  Backward: a
+    reduce-scatter sums the ranks' output gradients onto the owners, which return them to the last
+    stage -- every rank sends and receives ``1 / N`` of the output instead of the last stage
+    serving everything.
+    """
+
+    @staticmethod
+    def forward(ctx, anchor, group, ranks, index, m, transfers, meta, *outs_or_tokens):
+        size = len(ranks)
+        per = m // size
+        is_last = index == size - 1
+        ctx.group, ctx.ranks, ctx.index, ctx.m, ctx.transfers, ctx.meta = group, ranks, index, m, transfers, meta
+        ctx.n_inputs = len(outs_or_tokens)
+        shape, dtype, device = meta
+        if is_last:
+            mine = [outs_or_tokens[i].detach() for i in range(index * per, (index + 1) * per)]
+        else:
+            pending = [transfers.post_recv(shape, dtype, device, ranks[-1]) for _ in range(per)]
+            mine = []
+            for work, buf in pending:
+                work.wait()
+                mine.append(buf)
+        transfers.drain()
+        stream = torch.cat(mine, dim=0).contiguous()
+        full = torch.empty((size,) + tuple(stream.shape), dtype=dtype, device=device)
+        dist.all_gather_into_tensor(full.view(-1, *stream.shape[1:]), stream, group=group)
+        return full.view(-1, *stream.shape[1:])
+
+    @staticmethod
+    def backward(ctx, g):
+        size, per, index = len(ctx.ranks), ctx.m // len(ctx.ranks), ctx.index
+        is_last = index == size - 1
+        g = g.contiguous()
+        mine = torch.empty((g.shape[0] // size,) + tuple(g.shape[1:]), dtype=g.dtype, device=g.device)
+        dist.reduce_scatter_tensor(mine, g, op=dist.ReduceOp.SUM, group=ctx.group)
+        head = (None,) * 7
+        if not is_last:
+            for piece in mine.chunk(per, dim=0):
+                ctx.transfers.send(piece, ctx.ranks[-1])
+            ctx.transfers.drain()
+            return head + tuple(g.new_zeros(()) for _ in range(ctx.n_inputs))
+        grads: list = [None] * ctx.m
+        pending = {}
+        for owner in range(size - 1):
+            for i in range(owner * per, (owner + 1) * per):
+                pending[i] = ctx.transfers.post_recv(*ctx.meta, ctx.ranks[owner])
+        for j, piece in enumerate(mine.chunk(per, dim=0)):
+            grads[index * per + j] = piece
+        for i, (work, buf) in pending.items():
+            work.wait()
+            grads[i] = buf
+        return head + tuple(grads)
+
+
+class BaseSchedule(Configurable):
+    """How micro-batches enter and leave the stages (axlearn/common/pipeline.py:197-661)."""
+
+    @config_class
+    class Config(Configurable.Config):
+        num_stages: Optional[int] = None         # filled in by ``Pipeline``
+        num_microbatches: Optional[int] = None
+
+    @property
+    def num_stages(self) -> int:
+        return self._config.num_stages
+
+    @property
+    def num_microbatches(self) -> int:
+        return self._config.num_microbatches
+
+    @property
+    def num_iterations(self) -> int:
+        """Ticks until the pipeline is flushed."""
+        return self.num_microbatches + self.num_stages - 1
+
+    def bubble_fraction(self) -> float:
+        return (self.num_stages - 1) / self.num_iterations
+
+    def stage_and_microbatch_at(self, t: int) -> list:
+        """``(stage, micro-batch)`` pairs that are busy at tick ``t`` of the forward pass."""
+        return [(s, t - s) for s in range(self.num_stages) if 0 <= t - s < self.num_microbatches]
+
+    def output_owner(self, microbatch: int) -> int:
+        raise NotImplementedError(type(self))
+
+
+class GPipeSchedule(BaseSchedule):
+    """All inputs live on every stage; all outputs come from the last stage (one broadcast)."""
+
+    def output_owner(self, microbatch: int) -> int:
+        return self.num_stages - 1
+
+
+class StreamSchedule(BaseSchedule):
+    """Outputs are kept as ``num_stages`` streams of ``M / N`` micro-batches, one per stage
+    (axlearn/common/pipeline.py:421-661): finished micro-batches leave the last stage for their
+    owner while later ones are still being computed, and the gradient of the output returns the
+    same way, so no stage carries the whole output traffic."""
+
+    def __init__(self, cfg):
+        super().__init__(cfg)
+        if cfg.num_stages and cfg.num_microbatches and cfg.num_microbatches % cfg.num_stages:
+            raise ValueError(f"num_microbatches ({cfg.num_microbatches}) must be divisible by num_stages "
+                             f"({cfg.num_stages}) for the stream schedule")
+
+    def output_owner(self, microbatch: int) -> int:
+        return microbatch // (self.num_microbatches // self.num_stages)
 
 
 class Pipeline(BaseLayer):
@@ -113,10 +268,18 @@ class Pipeline(BaseLayer):
         layer: Required[InstantiableConfig] = REQUIRED
         num_layers: Required[int] = REQUIRED          # number of stages (the reference's name)
         num_microbatches: Required[int] = REQUIRED
+        schedule: InstantiableConfig = GPipeSchedule.default_config()
+        # Post transfers asynchronously and wait where the data is needed (False: blocking).
+        overlap_transfers: bool = True
 
     def __init__(self, cfg, *, parent=None):
         super().__init__(cfg, parent=parent)
         self._add_child("layer", cfg.layer)
+        self._schedule = cfg.schedule.clone(num_stages=cfg.num_layers, num_microbatches=cfg.num_microbatches).instantiate()
+
+    @property
+    def schedule(self) -> BaseSchedule:
+        return self._schedule
 
     # ------------------------------------------------------------------ parameters
     @nowrap
@@ -170,24 +333,52 @@ class Pipeline(BaseLayer):
             {k: (v.chunk(m, dim=0)[i] if isinstance(v, Tensor) and v.dim() > 0 and v.shape[0] == data.shape[0] else v)
              for k, v in kwargs.items()} for i in range(m)]
         is_first, is_last = index == 0, index == size - 1
+        stream = size > 1 and isinstance(self._schedule, StreamSchedule)
+        if stream and m % size:
+            raise ValueError(f"{m} micro-batches cannot be kept as {size} equal streams")
+        per_stream = m // size if stream else m
+        transfers = _Transfers(group, cfg.overlap_transfers)
         outs, tokens = [], []
         anchor = next((t for _, t in flatten_items(current_context().state["layer"]) if t.requires_grad), None)
+        meta = (micro[0].shape, micro[0].dtype, micro[0].device)
+        incoming = None
         for i in range(m):
             if is_first:
                 x = micro[i]
             else:
-                recv_anchor = anchor if anchor is not None else micro[i]
-                x = _Recv.apply(recv_anchor, ranks[index - 1], group, micro[i].shape, micro[i].dtype)
+                work, buf = incoming if incoming is not None else transfers.post_recv(*meta, ranks[index - 1])
+                work.wait()
+                # The next micro-batch travels while this one is computed.
+                incoming = transfers.post_recv(*meta, ranks[index - 1]) if cfg.overlap_transfers and i + 1 < m else None
+                x = _Received.apply(anchor if anchor is not None else micro[i], buf, ranks[index - 1], transfers)
             for j in range(per_rank):
                 x = self._run_stage(j, index * per_rank + j, x, kw_micro[i])
             if is_last:
                 outs.append(x)
+                owner = i // per_stream
+                if stream and owner != index:
+                    transfers.send(x, ranks[owner])
             else:
-                tokens.append(_Send.apply(x, ranks[index + 1], group))
+                tokens.append(_Sent.apply(x, ranks[index + 1], transfers, i))
         if size == 1:
             return torch.cat(outs, dim=0)
+        if stream:
+            out_meta = (outs[0].shape, outs[0].dtype, outs[0].device) if is_last else None
+            out_meta = _share_meta(out_meta, ranks[-1], group, meta)
+            link = anchor if anchor is not None else data
+            return _CollectStreams.apply(link, group, ranks, index, m, transfers, out_meta, *(outs if is_last else tokens))
         y = torch.cat(outs, dim=0) if is_last else torch.zeros_like(data)
-        return _BroadcastFromLast.apply(y, ranks[-1], group, is_last, *tokens)
+        return _BroadcastFromLast.apply(y, ranks[-1], group, is_last, transfers, *tokens)
+
+
+def _share_meta(out_meta, src: int, group, in_meta):
+    """Shape / dtype of one output micro-batch on every rank.  Stages map ``[b, ...] -> [b, ...]``
+    of the same shape in every use here, so the input's description is the output's; the last
+    stage checks that."""
+    del src, group
+    if out_meta is not None and (tuple(out_meta[0]) != tuple(in_meta[0]) or out_meta[1] != in_meta[1]):
+        raise ValueError(f"the stream schedule needs stages that keep shape and dtype: {in_meta[:2]} -> {out_meta[:2]}")
+    return in_meta
 
 
 def loss_scale_for_pipeline() -> float:

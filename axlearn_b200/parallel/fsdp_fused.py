@@ -248,6 +248,11 @@ def register(gatherer: "FusedLayerGatherer") -> None:
     _active.append(gatherer)
 
 
+def reset() -> None:
+    """Forgets every registered gatherer (a new trainer in the same process starts clean)."""
+    _active.clear()
+
+
 def begin_step_all(accumulate: bool = False) -> None:
     """Called by the trainer before every forward/backward pass: at the start of a step (after
     the previous optimizer update) and, with ``accumulate``, before each further micro-batch."""

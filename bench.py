@@ -48,6 +48,7 @@ def _args():
     ap.add_argument("--per_gpu_batch", type=int, default=4)
     ap.add_argument("--layers", type=int, default=None, help="debug only: override layer count")
     ap.add_argument("--skip_e2e", action="store_true")
+    ap.add_argument("--skip_parity", action="store_true", help="N>1: skip the one-step fused-vs-library parity record")
     return ap.parse_args()
 
 
@@ -138,50 +139,14 @@ def main():
             dist.init_process_group("gloo")
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
 
-    from axlearn_b200.common import prng
-    from axlearn_b200.common.base_layer import RematSpec, nothing_saveable
-    from axlearn_b200.experiments.text.gpt import fuji
-    from axlearn_b200.experiments.text.gpt.common import (
-        MESH_AXIS_NAMES,
-        adamw_decoupled_learner_config,
-        get_trainer_config_fn,
-        mesh_shape_from_axes,
-    )
     from axlearn_b200.ops import cuda_ops
 
     moe = args.family == "envy"
-    kw = fuji.get_trainer_kwargs("7B" if moe else args.model, vocab_size=32768, version=fuji.Version.V2)
-    if moe:
-        from axlearn_b200.experiments.text.gpt import envy
-
-        mk = dict(envy.MODEL_PRESETS[args.model])
-        if args.layers:
-            mk["num_layers"] = args.layers
-        model_cfg = envy.model_config(scan_chunk=8192, **mk)
-    else:
-        mk = dict(kw["model_kwargs"])
-        if args.layers:
-            mk["num_layers"] = args.layers
-        model_cfg = fuji.model_config(scan_chunk=8192, **mk)
-    # Full remat per layer: only each layer's input is kept.
-    model_cfg.decoder.transformer.layer.remat_spec = RematSpec(prevent_cse=False, policy=nothing_saveable)
+    parity = None
+    if world > 1 and use_cuda and not moe and not args.skip_parity:
+        parity = _fused_vs_library_parity(args, world, local_rank)
+    trainer, mk = _build_trainer(args, world, local_rank, use_cuda, layers=args.layers, per_gpu_batch=args.per_gpu_batch)
     global_batch = args.per_gpu_batch * world
-    cfg = get_trainer_config_fn(
-        model_cfg=model_cfg,
-        learner_cfg=adamw_decoupled_learner_config(max_step=kw["max_step"], **kw["learner_kwargs"]),
-        max_step=kw["max_step"], train_batch_size=global_batch, max_sequence_length=args.seq,
-        vocab_size=mk.get("vocab_size", 32768),
-        mesh_shape=mesh_shape_from_axes(**({"expert": world} if moe else {"fsdp": world})),
-        mesh_axis_names=MESH_AXIS_NAMES,
-        train_dtype=torch.bfloat16)()
-    if args.fp8:
-        from axlearn_b200.common.trainer_config_modifier import FP8ConfigModifier
-
-        cfg = FP8ConfigModifier.default_config().set(scaling="block").instantiate()(cfg)
-    cfg.dir = tempfile.mkdtemp(prefix="axb200_bench_")
-    cfg.device = f"cuda:{local_rank}" if use_cuda else "cpu"
-    trainer = cfg.instantiate(parent=None)
-    trainer.init(prng.PRNGKey(0))
     num_params = sum(t.numel() for t in _leaves(trainer.trainer_state["model"]))
     data = iter(trainer.input.dataset())
     dev = torch.device("cuda", local_rank) if use_cuda else torch.device("cpu")
@@ -286,6 +251,7 @@ def main():
             "clocks": clocks,
             "e2e": e2e,
             "gpu_launches": launches,
+            "multi_gpu_parity": parity,
             "loss": loss_value,
             "mfu_model_flops_nominal_peak": value * flops_per_token / (peak * world),
             "local_params": num_params,
@@ -293,6 +259,105 @@ def main():
         print(json.dumps(result))
     if world > 1:
         dist.destroy_process_group()
+
+
+def _build_trainer(args, world, local_rank, use_cuda, *, layers, per_gpu_batch):
+    """The benchmark's trainer (optionally a slice with fewer layers); returns (trainer, model kwargs)."""
+    import torch
+
+    from axlearn_b200.common import prng
+    from axlearn_b200.common.base_layer import RematSpec, nothing_saveable
+    from axlearn_b200.experiments.text.gpt import fuji
+    from axlearn_b200.experiments.text.gpt.common import (
+        MESH_AXIS_NAMES,
+        adamw_decoupled_learner_config,
+        get_trainer_config_fn,
+        mesh_shape_from_axes,
+    )
+
+    moe = args.family == "envy"
+    kw = fuji.get_trainer_kwargs("7B" if moe else args.model, vocab_size=32768, version=fuji.Version.V2)
+    if moe:
+        from axlearn_b200.experiments.text.gpt import envy
+
+        mk = dict(envy.MODEL_PRESETS[args.model])
+        if layers:
+            mk["num_layers"] = layers
+        model_cfg = envy.model_config(scan_chunk=8192, **mk)
+    else:
+        mk = dict(kw["model_kwargs"])
+        if layers:
+            mk["num_layers"] = layers
+        model_cfg = fuji.model_config(scan_chunk=8192, **mk)
+    # Full remat per layer: only each layer's input is kept.
+    model_cfg.decoder.transformer.layer.remat_spec = RematSpec(prevent_cse=False, policy=nothing_saveable)
+    cfg = get_trainer_config_fn(
+        model_cfg=model_cfg,
+        learner_cfg=adamw_decoupled_learner_config(max_step=kw["max_step"], **kw["learner_kwargs"]),
+        max_step=kw["max_step"], train_batch_size=per_gpu_batch * world, max_sequence_length=args.seq,
+        vocab_size=mk.get("vocab_size", 32768),
+        mesh_shape=mesh_shape_from_axes(**({"expert": world} if moe else {"fsdp": world})),
+        mesh_axis_names=MESH_AXIS_NAMES,
+        train_dtype=torch.bfloat16)()
+    if args.fp8:
+        from axlearn_b200.common.trainer_config_modifier import FP8ConfigModifier
+
+        cfg = FP8ConfigModifier.default_config().set(scaling="block").instantiate()(cfg)
+    cfg.dir = tempfile.mkdtemp(prefix="axb200_bench_")
+    cfg.device = f"cuda:{local_rank}" if use_cuda else "cpu"
+    trainer = cfg.instantiate(parent=None)
+    trainer.init(prng.PRNGKey(0))
+    return trainer, mk
+
+
+def _fused_vs_library_parity(args, world, local_rank) -> dict:
+    """Multi-GPU correctness record carried by the benchmark line: a 2-layer slice of the same
+    architecture (same widths, sequence length and mesh) takes ONE training step from the same
+    initial state and batch, first with library collectives (all-gather / reduce-scatter through
+    NCCL), then with the fused gather-GEMM / GEMM-reduce-scatter kernels; reports both losses and
+    the largest gradient-shard difference relative to the largest gradient, max over ranks."""
+    import gc
+
+    import torch
+    import torch.distributed as dist
+
+    from axlearn_b200.common.utils import flatten_items
+    from axlearn_b200.ops import cuda_ops
+    from axlearn_b200.parallel import fsdp_fused
+
+    was_enabled = fsdp_fused.ENABLED
+    record = {}
+    grads = {}
+    for name, fused in (("library", False), ("fused", True)):
+        fsdp_fused.ENABLED = fused and was_enabled
+        fsdp_fused.reset()
+        trainer, _ = _build_trainer(args, world, local_rank, True, layers=2, per_gpu_batch=1)
+        out = trainer.train_step(next(iter(trainer.input.dataset())))
+        record[f"loss_{name}"] = float(out["loss"])
+        stacked = trainer._shadows["decoder"]["transformer"]["repeat"]["layer"]  # pylint: disable=protected-access
+        grads[name] = {p: t.grad.float().clone() for p, t in flatten_items(stacked) if t.grad is not None}
+        torch.cuda.synchronize()
+        cuda_ops.check_status()
+        del trainer, out, stacked
+        fsdp_fused.reset()
+        gc.collect()
+        torch.cuda.empty_cache()
+    fsdp_fused.ENABLED = was_enabled
+    worst = torch.zeros(2, device="cuda")
+    for p, g in grads["fused"].items():
+        r = grads["library"][p]
+        worst[0] = torch.maximum(worst[0], (g - r).abs().max())
+        worst[1] = torch.maximum(worst[1], r.abs().max())
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    record["max_grad_shard_abs_diff"] = worst[0].item()
+    record["max_grad_abs"] = worst[1].item()
+    record["max_grad_shard_rel_diff"] = worst[0].item() / max(worst[1].item(), 1e-30)
+    record["fused_path_active"] = bool(was_enabled)
+    record["slice"] = f"2 layers of the benchmark architecture, 1x{args.seq} tokens per GPU, fsdp{world}, one step"
+    del grads
+    gc.collect()
+    torch.cuda.empty_cache()
+    return record
 
 
 def _leaves(tree):
