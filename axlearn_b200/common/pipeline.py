@@ -66,10 +66,12 @@ class _Transfers:
         self._sends: list = []          # (work, tensor): tensors stay alive until the pass ends
         self._grad_recvs: dict = {}     # micro-batch -> (work, buffer)
 
-    def send(self, x: Tensor, dst: int) -> None:
+    def send(self, x: Tensor, dst: int, *, deferred: bool = False) -> None:
+        """``deferred``: never wait here, whatever the mode (the receiver posts its side only after
+        its own loop, so waiting would stall both ranks)."""
         x = x.detach().contiguous()
         work = dist.isend(x, dst=dst, group=self.group)
-        if self.overlap:
+        if self.overlap or deferred:
             self._sends.append((work, x))
         else:
             work.wait()
@@ -357,7 +359,7 @@ class Pipeline(BaseLayer):
                 outs.append(x)
                 owner = i // per_stream
                 if stream and owner != index:
-                    transfers.send(x, ranks[owner])
+                    transfers.send(x, ranks[owner], deferred=True)
             else:
                 tokens.append(_Sent.apply(x, ranks[index + 1], transfers, i))
         if size == 1:
