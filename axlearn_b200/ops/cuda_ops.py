@@ -29,6 +29,8 @@ launch_count = 0  # Kernels launched through this module (bench.py reports it).
 # peer-memory copy kernels). The persistent GEMM launches at most (SM count - this) CTAs, so
 # that all of its CTAs stay resident and its static tile schedule has no second wave.
 COMM_RESERVED_SMS = int(os.environ.get("AXB200_COMM_SMS", "0"))
+# "2cta": large GEMMs run on CTA pairs (256 x 256 tiles); "1cta": always the single-CTA kernel.
+GEMM_VARIANT = os.environ.get("AXB200_GEMM", "2cta")
 
 
 def reserve_sms_for_comm(n: int) -> None:
@@ -61,6 +63,8 @@ def lib() -> ctypes.CDLL:
 class _Sigs:
     axb_gemm_bf16 = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
                      c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
+    axb_gemm_bf16_2cta = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
+                          c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
     axb_gemm_splitk_plan = [c_int, c_int, c_int]
     axb_gemm_bf16_splitk = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
                             c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
@@ -217,6 +221,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = None
                 1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0, split, ws.data_ptr(),
                 counters.data_ptr(), status_word(a.device).data_ptr(), max_ctas, _stream())
             _check(rc, "axb_gemm_bf16_splitk")
+            return out
+    if GEMM_VARIANT == "2cta" and m >= 512 and n >= 256 and ((m + 255) // 256) * ((n + 255) // 256) >= 64:
+        # Large problems: CTA pairs on 256 x 256 tiles.
+        rc = lib().axb_gemm_bf16_2cta(a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k, lda, ldb, out.stride(0),
+                                      a_mn, b_mn, 1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0,
+                                      status_word(a.device).data_ptr(), max_ctas, _stream())
+        if rc != -20:
+            _check(rc, "axb_gemm_bf16_2cta")
             return out
     rc = lib().axb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k, lda, ldb, out.stride(0),
                              a_mn, b_mn, 1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0,
