@@ -25,6 +25,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include "gemm_fused.cuh"
 #include "host_utils.cuh"
 #include "sm100.cuh"
 
@@ -35,21 +36,31 @@ constexpr int k2TileM = 256;
 constexpr int k2TileN = 256;
 constexpr int k2HalfN = 128;
 constexpr int k2BlockK = 64;
-constexpr int k2Stages = 6;
 constexpr int k2Threads = 192;
+constexpr int k2FusedThreads = k2Threads + 32;  // + one copy warp per CTA
 constexpr int k2GroupM = 8;
 
+// The fused variants give one stage of the ring to the copy warp's two chunk buffers.
+template <bool FUSED>
 struct Gemm2Smem {
+  static constexpr int kStages = FUSED ? 5 : 6;
   static constexpr int kABytes = k2RowsPerCta * k2BlockK * 2;
   static constexpr int kBBytes = k2HalfN * k2BlockK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;  // 32 KB
-  static constexpr int kRingBytes = k2Stages * kStageBytes;
+  static constexpr int kRingBytes = kStages * kStageBytes;
   static constexpr int kStagingPerWarp = 2 * 4096;  // two 32-row x 128-byte tiles
   static constexpr int kStagingBytes = 4 * kStagingPerWarp;
+  static constexpr int kCopyBytes = FUSED ? kCopyBufs * static_cast<int>(kCopyChunk) : 0;
   static constexpr int kBarrierBytes = 1024;
-  static constexpr int kTotal = kRingBytes + kStagingBytes + kBarrierBytes + 1024;  // + align slack
+  static constexpr int kTotal = kRingBytes + kStagingBytes + kCopyBytes + kBarrierBytes + 1024;  // + align slack
 };
-static_assert(Gemm2Smem::kTotal <= 227 * 1024, "shared memory budget");
+static_assert(Gemm2Smem<false>::kTotal <= 227 * 1024 && Gemm2Smem<true>::kTotal <= 227 * 1024, "shared memory budget");
+
+// One store map per owner of the reduce-scatter: its staging buffer seen as a
+// [world * rows_per_rank, N] matrix.
+struct PeerMaps {
+  CUtensorMap m[kMaxPeers];
+};
 
 struct Gemm2Params {
   int M, N, K;
@@ -127,23 +138,32 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const 
                : "memory");
 }
 
-template <bool A_MN, bool B_MN, typename OutT>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(k2Threads, 1)
+// FUSED adds what the single-CTA fused kernel has (same `FusedParams` contract): a copy warp that
+// carries parameter gathers, consumption of a gathered B behind per-slab flags (every CTA of the
+// pair waits for the slabs ITS half of B touches), and a reduce-scatter epilogue whose TMA stores
+// go to the row owner's staging buffer (peer memory over NVLink: plain stores, full lines).
+template <bool A_MN, bool B_MN, typename OutT, bool FUSED>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(FUSED ? k2FusedThreads : k2Threads, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                  const __grid_constant__ CUtensorMap tmap_c, Gemm2Params p) {
-  using S = Gemm2Smem;
+                  const __grid_constant__ CUtensorMap tmap_c, Gemm2Params p,
+                  const __grid_constant__ CUtensorMap tmap_b_local, const __grid_constant__ FusedParams f,
+                  const __grid_constant__ PeerMaps rs_maps) {
+  using S = Gemm2Smem<FUSED>;
+  constexpr int k2Stages = S::kStages;
   extern __shared__ uint8_t smem_raw[];
   // The dynamic shared-memory window starts at the same offset in both CTAs, so rounding up to
   // 1024 bytes (required by the 128-byte swizzle) gives the same layout in both.
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw + 1023u) & ~1023u) - raw);
   uint8_t* staging = smem + S::kRingBytes;
-  uint8_t* bar_base = staging + S::kStagingBytes;
+  uint8_t* copy_bufs = staging + S::kStagingBytes;
+  uint8_t* bar_base = copy_bufs + S::kCopyBytes;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_base);
   uint64_t* empty_bar = full_bar + k2Stages;
   uint64_t* tmem_full = empty_bar + k2Stages;
   uint64_t* tmem_empty = tmem_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  uint64_t* copy_full = reinterpret_cast<uint64_t*>(bar_base + 512);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -160,6 +180,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
     tma_prefetch_desc(&tmap_c);
+    if constexpr (FUSED) {
+      tma_prefetch_desc(&tmap_b_local);
+      for (int b = 0; b < kCopyBufs; ++b) mbar_init(&copy_full[b], 1);
+    }
     for (int s = 0; s < k2Stages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -181,6 +205,16 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  const bool copy_on = FUSED && (f.ag[0].world > 1 || f.ag[1].world > 1);  // carries gathers
+  const bool ag_on = FUSED && f.ag_consume && f.ag[0].world > 1;           // ... one of its own B
+  // Rows [own_lo, own_hi) of the split dim are this rank's own slab: tiles inside it are read
+  // straight from the shard (`tmap_b_local`), without waiting for any copy.
+  const int own_lo = ag_on ? f.ag[0].rank * f.ag_shard_extent : 0;
+  const int own_hi = own_lo + (ag_on ? f.ag_shard_extent : 0);
+  // Rotation that makes every rank start on the first tile fully inside its own slab.
+  const int n_rot = (ag_on && !f.ag_along_k) ? ((own_lo + k2TileN - 1) / k2TileN) % n_blocks : 0;
+  const int kb_rot = (ag_on && f.ag_along_k) ? ((own_lo + k2BlockK - 1) / k2BlockK) % num_kb : 0;
+
   auto tile_coords = [&](int t, int& m_blk, int& n_blk) {
     const int per_group = k2GroupM * n_blocks;
     const int g = t / per_group;
@@ -189,20 +223,54 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     const int r = t % per_group;
     m_blk = first_m + r % gsize;
     n_blk = r / gsize;
+    if (FUSED && n_rot) n_blk = (n_blk + n_rot) % n_blocks;
   };
 
-  if (warp == 0) {
+  if (warp == 6) {
+    // ------------------------------------------------------------------ copy warp (fused only)
+    if constexpr (FUSED) {
+      if (copy_on && elect_one()) {
+        int64_t seq = 0;
+        bool ok = true;
+        for (int j = 0; j < 2 && ok; ++j)
+          if (f.ag[j].world > 1) ok = ag_copy_warp(copy_bufs, copy_full, f.ag[j], seq, p.status);
+      }
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ producer (both CTAs)
     if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      uint32_t slab_ready = 0;  // bit r: slab r of the gathered operand has landed
+      auto need_slab = [&](int r) -> bool {
+        if (slab_ready >> r & 1u) return true;
+        if (!wait_flag(&f.ag[0].flags[r], f.ag[0].epoch, p.status)) return false;
+        // Later TMA reads (async proxy) must observe the copy CTAs' writes.
+        asm volatile("fence.proxy.async;" ::: "memory");
+        slab_ready |= 1u << r;
+        return true;
+      };
       for (int t = pair; t < num_tiles && ok; t += num_pairs) {
         int m_blk, n_blk;
         tile_coords(t, m_blk, n_blk);
         const int m0 = m_blk * k2TileM + static_cast<int>(rank) * k2RowsPerCta;
         const int n0 = n_blk * k2TileN + static_cast<int>(rank) * k2HalfN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        bool local = false;  // read this CTA's half of the B tile from the own shard
+        if (FUSED && ag_on && !f.ag_along_k && n0 < p.N) {
+          const int last = min(n0 + k2HalfN, p.N) - 1;
+          local = n0 >= own_lo && last < own_hi;
+          for (int r = n0 / f.ag_shard_extent; !local && r <= last / f.ag_shard_extent && ok; ++r) ok = need_slab(r);
+          if (!ok) break;
+        }
+        for (int kbi = 0; kbi < num_kb; ++kbi) {
+          const int kb = FUSED ? (kbi + kb_rot) % num_kb : kbi;
+          if (FUSED && ag_on && f.ag_along_k) {
+            const int k_lo = kb * k2BlockK, k_hi = min(k_lo + k2BlockK, p.K) - 1;
+            local = k_lo >= own_lo && k_hi < own_hi;
+            for (int r = k_lo / f.ag_shard_extent; !local && r <= k_hi / f.ag_shard_extent && ok; ++r) ok = need_slab(r);
+            if (!ok) break;
+          }
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kStatusWaitTimeoutProducer)) {
             ok = false;
             break;
@@ -219,7 +287,16 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 #pragma unroll
             for (int j = 0; j < k2RowsPerCta / 64; ++j) tma_load_2d_pair(sa + j * 8192, &tmap_a, bar, m0 + j * 64, k0);
           }
-          if constexpr (!B_MN) {
+          if (FUSED && local) {
+            // B_MN: slabs split K (rows of the stored [K, N]); otherwise they split N.
+            if constexpr (!B_MN) {
+              tma_load_2d_pair(sb, &tmap_b_local, bar, k0, n0 - own_lo);
+            } else {
+#pragma unroll
+              for (int j = 0; j < k2HalfN / 64; ++j)
+                tma_load_2d_pair(sb + j * 8192, &tmap_b_local, bar, n0 + j * 64, k0 - own_lo);
+            }
+          } else if constexpr (!B_MN) {
             tma_load_2d_pair(sb, &tmap_b, bar, k0, n0);
           } else {
 #pragma unroll
@@ -245,7 +322,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.status, kStatusWaitTimeoutMma)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * k2TileN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = 0; kb < num_kb; ++kb) {  // the producer's k order (rotated or not) is irrelevant here
           if (!mbar_wait(&full_bar[stage], phase, p.status, kStatusWaitTimeoutMma)) {
             ok = false;
             break;
@@ -297,6 +374,15 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       const int row0 = m_blk * k2TileM + static_cast<int>(rank) * k2RowsPerCta + quarter * 32;
       const int n0 = n_blk * k2TileN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * k2TileN;
+      // Reduce-scatter: these 32 rows go to their owner's staging slot for this rank (the host
+      // checks that a 32-row block never straddles two owners).
+      const CUtensorMap* out_map = &tmap_c;
+      int out_row = row0;
+      if (FUSED && f.rs_world > 1 && row0 < p.M) {
+        const int owner = row0 / f.rs_rows_per_rank;
+        out_map = &rs_maps.m[owner];
+        out_row = f.rs_rank * f.rs_rows_per_rank + (row0 - owner * f.rs_rows_per_rank);
+      }
 #pragma unroll 1
       for (int ch = 0; ch < kChunks; ++ch) {
         uint32_t r[32];
@@ -341,9 +427,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         __syncwarp();
         if (lane == 0 && row0 < p.M && n0 + ch * kChunkCols < p.N) {
           if (p.accumulate)
-            tma_reduce_add_2d(&tmap_c, tile, n0 + ch * kChunkCols, row0);
+            tma_reduce_add_2d(out_map, tile, n0 + ch * kChunkCols, out_row);
           else
-            tma_store_2d(&tmap_c, tile, n0 + ch * kChunkCols, row0);
+            tma_store_2d(out_map, tile, n0 + ch * kChunkCols, out_row);
         }
         if (lane == 0) tma_store_commit();
         ++store_seq;
@@ -353,7 +439,12 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         acc_phase ^= 1;
       }
     }
-    if (lane == 0) tma_store_wait<0>();
+    if (lane == 0) {
+      tma_store_wait<0>();
+      // Stores to peer memory: visible system-wide before the kernel can complete, so the flag
+      // raised by the next launch cannot overtake them.
+      if (FUSED && f.rs_world > 1) __threadfence_system();
+    }
     __syncwarp();
   }
 
@@ -372,9 +463,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   }
 }
 
-template <bool A_MN, bool B_MN, typename OutT>
+template <bool A_MN, bool B_MN, typename OutT, bool FUSED = false>
 static int launch_gemm2(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
-                        int64_t ldc, int accumulate, int* status, int max_ctas, cudaStream_t stream) {
+                        int64_t ldc, int accumulate, int* status, int max_ctas, cudaStream_t stream,
+                        const FusedParams* fused = nullptr) {
   CUtensorMap ta, tb, tc;
   int rc;
   {
@@ -384,25 +476,49 @@ static int launch_gemm2(const void* A, const void* B, void* C, int M, int N, int
     rc = make_tensor_map(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != 0) return rc;
   }
+  const uint32_t b_box[2] = {64, static_cast<uint32_t>(B_MN ? k2BlockK : k2HalfN)};
   {
     uint64_t dims[2] = {static_cast<uint64_t>(B_MN ? N : K), static_cast<uint64_t>(B_MN ? K : N)};
     uint64_t strides[1] = {static_cast<uint64_t>(ldb) * 2};
-    uint32_t box[2] = {64, static_cast<uint32_t>(B_MN ? k2BlockK : k2HalfN)};
-    rc = make_tensor_map(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    rc = make_tensor_map(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, dims, strides, b_box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != 0) return rc;
   }
-  {
+  const CUtensorMapDataType c_type = sizeof(OutT) == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  const uint32_t c_box[2] = {static_cast<uint32_t>(128 / sizeof(OutT)), 32};
+  const uint64_t c_strides[1] = {static_cast<uint64_t>(ldc) * sizeof(OutT)};
+  FusedParams fp;
+  memset(&fp, 0, sizeof(fp));
+  if (FUSED && fused != nullptr) fp = *fused;
+  const bool scatter = FUSED && fp.rs_world > 1;
+  if (!scatter) {
     uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)};
-    uint64_t strides[1] = {static_cast<uint64_t>(ldc) * sizeof(OutT)};
-    uint32_t box[2] = {static_cast<uint32_t>(128 / sizeof(OutT)), 32};
-    rc = make_tensor_map(&tc, sizeof(OutT) == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
-                         C, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    rc = make_tensor_map(&tc, c_type, 2, C, dims, c_strides, c_box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != 0) return rc;
   }
-  auto kernel = gemm2_bf16_kernel<A_MN, B_MN, OutT>;
+  // The own shard as a tensor of its own (consume mode): same row pitch, one slab of rows.
+  CUtensorMap tl = tb;
+  if (FUSED && fp.ag[0].world > 1 && fp.ag_consume) {
+    const void* own = fp.ag[0].src[fp.ag[0].rank];
+    uint64_t dims[2] = {static_cast<uint64_t>(B_MN ? N : K), static_cast<uint64_t>(fp.ag_shard_extent)};
+    uint64_t strides[1] = {static_cast<uint64_t>(ldb) * 2};
+    rc = make_tensor_map(&tl, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, own, dims, strides, b_box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != 0) return rc;
+  }
+  static PeerMaps no_maps;  // zero-initialised; unused unless scattering
+  PeerMaps maps = no_maps;
+  if (scatter) {
+    for (int r = 0; r < fp.rs_world; ++r) {
+      uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(fp.rs_world) * fp.rs_rows_per_rank};
+      rc = make_tensor_map(&maps.m[r], c_type, 2, fp.rs_dst[r], dims, c_strides, c_box, CU_TENSOR_MAP_SWIZZLE_128B);
+      if (rc != 0) return rc;
+    }
+    tc = maps.m[fp.rs_rank];
+  }
+  using S = Gemm2Smem<FUSED>;
+  auto kernel = gemm2_bf16_kernel<A_MN, B_MN, OutT, FUSED>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Gemm2Smem::kTotal);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
     if (e != cudaSuccess) {
       fprintf(stderr, "axb gemm2: cudaFuncSetAttribute: %s\n", cudaGetErrorString(e));
       return -3;
@@ -415,7 +531,7 @@ static int launch_gemm2(const void* A, const void* B, void* C, int M, int N, int
   if (tiles < pairs) pairs = tiles;
   if (pairs < 1) return -12;
   Gemm2Params p{M, N, K, accumulate, status};
-  kernel<<<2 * pairs, k2Threads, Gemm2Smem::kTotal, stream>>>(ta, tb, tc, p);
+  kernel<<<2 * pairs, FUSED ? k2FusedThreads : k2Threads, S::kTotal, stream>>>(ta, tb, tc, p, tl, fp, maps);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     fprintf(stderr, "axb gemm2: launch failed: %s\n", cudaGetErrorString(e));
@@ -449,5 +565,27 @@ extern "C" int axb_gemm_bf16_2cta(const void* A, const void* B, void* C, int M, 
   AXB_GEMM2_CASE(true, false)
   AXB_GEMM2_CASE(true, true)
 #undef AXB_GEMM2_CASE
+  return -11;
+}
+
+// Fused compute+collective form on CTA pairs; same arguments as axb_gemm_bf16_fused.  Returns -20
+// when the problem is not one this kernel takes (small problems, the all-reduce-push epilogue,
+// owner slabs that are no multiple of 32 rows): the caller then uses the single-CTA kernel.
+extern "C" int axb_gemm_bf16_fused_2cta(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda,
+                                        int64_t ldb, int64_t ldc, int a_mn_major, int b_mn_major, int* status,
+                                        int max_ctas, const void* fused, cudaStream_t stream) {
+  using namespace axb;
+  const FusedParams* fp = static_cast<const FusedParams*>(fused);
+  if (M < 2 * k2TileM || N < k2TileN || ((M + k2TileM - 1) / k2TileM) * ((N + k2TileN - 1) / k2TileN) < 64) return -20;
+  if (fp->rs_world > 1 && (fp->rs_mode != 0 || (fp->rs_rows_per_rank % 32) != 0)) return -20;
+  if (fp->rs_world <= 1 && (reinterpret_cast<uintptr_t>(C) & 15)) return -10;
+#define AXB_FUSED2_CASE(AM, BM)                                                                                  \
+  if (a_mn_major == (AM ? 1 : 0) && b_mn_major == (BM ? 1 : 0))                                                  \
+    return launch_gemm2<AM, BM, __nv_bfloat16, true>(A, B, C, M, N, K, lda, ldb, ldc, 0, status, max_ctas, stream, fp);
+  AXB_FUSED2_CASE(false, false)
+  AXB_FUSED2_CASE(false, true)
+  AXB_FUSED2_CASE(true, false)
+  AXB_FUSED2_CASE(true, true)
+#undef AXB_FUSED2_CASE
   return -11;
 }

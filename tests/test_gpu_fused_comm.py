@@ -106,3 +106,65 @@ def test_wait_flags_times_out_cleanly():
         cuda_ops.check_status()
     cuda_ops.check_status()  # cleared
     assert torch.ones(4, device="cuda").sum().item() == 4.0
+
+
+@pytest.mark.parametrize("variant", ["2cta", "1cta"])
+@pytest.mark.parametrize("world", [2, 8])
+def test_large_fused_gemms_on_cta_pairs(world, variant, monkeypatch):
+    """Problems large enough for the CTA-pair kernel (>= 64 tiles of 256 x 256): gather consumed
+    by the GEMM in both weight layouts, a gather carried by an unrelated GEMM, and the
+    reduce-scatter epilogue; the single-CTA kernel on the same problems is the cross-check."""
+    import subprocess
+    import sys
+
+    if variant == "1cta":
+        # The choice is read once per process by the library: run this variant in a child.
+        code = ("import os, sys, pytest; os.environ['AXB200_GEMM'] = '1cta'; "
+                f"sys.exit(pytest.main(['-q', '-x', '{__file__}', '-k', 'test_large_fused_gemms_on_cta_pairs and 2cta and {world}', '-p', 'no:cacheprovider']))")
+        env = dict(__import__("os").environ, AXB200_GEMM="1cta")
+        assert subprocess.run([sys.executable, "-c", code], env=env, timeout=600).returncode == 0
+        return
+    from axlearn_b200.ops import cuda_ops, fused_comm
+
+    torch.manual_seed(5)
+    m, k, n = 4096, 1024, 4096
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    for weight_is_nk in (False, True):
+        w = (torch.randn(n, k, device="cuda") if weight_is_nk else torch.randn(k, n, device="cuda")).bfloat16()
+        shards = [s.contiguous() for s in w.chunk(world, dim=0)]
+        ref = x.float() @ (w.float().t() if weight_is_nk else w.float())
+        for rank in (0, world - 1):
+            state = fused_comm.GatherState(w.shape, world, "cuda")
+            state.full.fill_(float("nan"))
+            for _ in range(2):
+                out = fused_comm.ag_gemm(x, shard_ptrs=[s.data_ptr() for s in shards], state=state, rank=rank,
+                                         weight_is_nk=weight_is_nk)
+                torch.cuda.synchronize()
+                cuda_ops.check_status()
+                _close(out, ref)
+            assert torch.equal(state.full, w)
+    # A gather carried by an unrelated GEMM.
+    w = torch.randn(k, n, device="cuda").bfloat16()
+    other = torch.randn(4096, 1000 + 8 * world, device="cuda").bfloat16()
+    shards = [s.contiguous() for s in other.chunk(world, dim=0)]
+    state = fused_comm.GatherState(other.shape, world, "cuda")
+    state.full.fill_(float("nan"))
+    out = fused_comm.gemm_carrying_gather(x, w, shard_ptrs=[s.data_ptr() for s in shards], state=state, rank=1)
+    torch.cuda.synchronize()
+    cuda_ops.check_status()
+    _close(out, x.float() @ w.float())
+    assert torch.equal(state.full, other)
+    # Reduce-scatter epilogue: dW[m, n] = x^T dy, rows scattered over `world` owners.
+    tokens = 512
+    xs = [torch.randn(tokens, m, device="cuda").bfloat16() for _ in range(world)]
+    dys = [torch.randn(tokens, n, device="cuda").bfloat16() for _ in range(world)]
+    staging = [torch.full((world, m // world, n), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    for rank in range(world):
+        fused_comm.gemm_rs(xs[rank].t(), dys[rank], staging_ptrs=[s.data_ptr() for s in staging], rank=rank)
+    torch.cuda.synchronize()
+    cuda_ops.check_status()
+    rows = m // world
+    for owner in range(world):
+        for rank in range(world):
+            ref = (xs[rank].float().t() @ dys[rank].float())[owner * rows:(owner + 1) * rows]
+            _close(staging[owner][rank], ref)
