@@ -369,7 +369,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     for (int t = pair; t < num_tiles; t += num_pairs) {
       int m_blk, n_blk;
       tile_coords(t, m_blk, n_blk);
-      if (!mbar_wait_warp(&tmem_full[acc], acc_phase, p.status, kStatusWaitTimeoutEpilogue)) break;
+      if (!mbar_wait_warp_relaxed(&tmem_full[acc], acc_phase, p.status, kStatusWaitTimeoutEpilogue)) break;
       tc_fence_after_sync();
       const int row0 = m_blk * k2TileM + static_cast<int>(rank) * k2RowsPerCta + quarter * 32;
       const int n0 = n_blk * k2TileN;

@@ -110,6 +110,31 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, i
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, status, code));
 }
 
+// A whole-warp wait for something that is long in coming and not urgent (an epilogue waiting for
+// the next accumulator while the main loop runs): one lane polls, sleeping between polls, so the
+// other 31 lanes issue nothing meanwhile; afterwards every lane makes its own (immediately
+// successful) observation of the phase so that each has acquired it.
+__device__ __forceinline__ bool mbar_wait_warp_relaxed(uint64_t* bar, uint32_t parity, int* status, int code) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0 && !mbar_test_wait(bar, parity)) {
+    ok = 0;
+    for (uint32_t i = 0; i < kMaxPolls; ++i) {
+      if (mbar_try_wait(bar, parity)) {
+        ok = 1;
+        break;
+      }
+      __nanosleep(128);
+    }
+    if (!ok && status != nullptr) atomicCAS(status, 0, code);
+  }
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  if (ok) {
+    for (int i = 0; i < 1024 && !mbar_test_wait(bar, parity); ++i) {
+    }
+  }
+  return ok != 0;
+}
+
 // ------------------------------------------------------------------------------ TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
