@@ -1187,7 +1187,7 @@ class TransformerAttentionLayer(BaseLayer):
 
     def _forward_for_mode(self, *, mode, target, source=None, attention_logit_biases=None,
                           segment_ids=None, target_positions=None, cached_states=None,
-                          return_aux=None, page_pool=None, max_len=None):
+                          return_aux=None, page_pool=None, max_len=None, defer_residual=False):
         cfg = self._config
         kv_kwargs: dict[str, Any] = {}
         if isinstance(source, KVState):
@@ -1213,9 +1213,14 @@ class TransformerAttentionLayer(BaseLayer):
             states, _ = self.attention.init_states(time_step=None, query=target, page_pool=page_pool, **kv_kwargs)
             return {"attention": states}, None
         if cfg.structure == "prenorm":
-            skip = target
-            states, out = attend(self.norm(target))
-            data = skip + self.stochastic_depth(self.dropout(out.data))
+            if mode == ForwardMode.FORWARD and hasattr(self.norm, "forward_keep_input"):
+                normed, skip = self.norm.forward_keep_input(target)
+            else:
+                normed, skip = self.norm(target), target
+            states, out = attend(normed)
+            branch = self.stochastic_depth(self.dropout(out.data))
+            # With `defer_residual` the caller adds the branch (fused into its next norm).
+            data = (skip, branch) if defer_residual else skip + branch
         elif cfg.structure == "postnorm":
             states, out = attend(target)
             data = self.norm(target + self.stochastic_depth(self.dropout(out.data)))
@@ -1226,11 +1231,16 @@ class TransformerAttentionLayer(BaseLayer):
         return {"attention": states}, self.Output(data=data, probs=out.probs, kv_state=out.kv_state)
 
     def forward(self, *, target, source=None, attention_logit_biases=None, segment_ids=None,
-                target_positions=None, return_aux=None):
+                target_positions=None, return_aux=None, defer_residual: bool = False):
+        """``defer_residual`` (pre-norm structure only): ``Output.data`` is the pair
+        ``(skip, branch)`` instead of their sum, for a caller that fuses the addition into the
+        next normalisation."""
+        if defer_residual and self._config.structure != "prenorm":
+            raise ValueError("defer_residual needs the prenorm structure")
         _, out = self._forward_for_mode(
             mode=ForwardMode.FORWARD, target=target, source=source,
             attention_logit_biases=attention_logit_biases, segment_ids=segment_ids,
-            target_positions=target_positions, return_aux=return_aux)
+            target_positions=target_positions, return_aux=return_aux, defer_residual=defer_residual)
         return out
 
     def init_states(self, *, time_step, target, source=None, attention_logit_biases=None,
@@ -1340,11 +1350,26 @@ class TransformerFeedForwardLayer(BaseLayer):
         with remat.tagged(self, "linear2"):
             return self._remat_name(self.linear2(h), "linear2")
 
-    def forward(self, inputs: Tensor) -> Tensor:
+    ACCEPTS_PENDING_RESIDUAL = True
+
+    def forward(self, inputs: Tensor, *, pending_residual: Optional[Tensor] = None) -> Tensor:
+        """``pending_residual`` (pre-norm structure only): a branch output that still has to be
+        added to ``inputs``; the addition is fused into this layer's normalisation."""
         cfg = self._config
         rw = cfg.residual_weight
+        if pending_residual is not None and cfg.structure != "prenorm":
+            inputs, pending_residual = inputs + pending_residual, None
         if cfg.structure == "prenorm":
-            x = self._mlp(self.norm(inputs))
+            if pending_residual is not None and hasattr(self.norm, "forward_add"):
+                inputs, normed = self.norm.forward_add(inputs, pending_residual)
+            else:
+                if pending_residual is not None:
+                    inputs = inputs + pending_residual
+                if hasattr(self.norm, "forward_keep_input"):
+                    normed, inputs = self.norm.forward_keep_input(inputs)
+                else:
+                    normed = self.norm(inputs)
+            x = self._mlp(normed)
             x = self.stochastic_depth(self.dropout2(x))
             return inputs + (x if rw == 1.0 else x * rw)
         if cfg.structure == "postnorm":
@@ -1399,9 +1424,14 @@ class TransformerLayer(BaseTransformerLayer):
         data = self._remat_name(data, "input") if isinstance(data, Tensor) else data
         sa_kwargs = dict(target=data, source=self_attention_kv_state,
                          attention_logit_biases=self_attention_logit_biases, return_aux=return_aux)
+        # Pre-norm blocks hand the attention branch to the feed-forward layer unsummed: its
+        # normalisation adds it (one pass instead of an add and a norm).
+        defer = (mode == ForwardMode.FORWARD and self.self_attention.config.structure == "prenorm"
+                 and getattr(self.feed_forward, "ACCEPTS_PENDING_RESIDUAL", False)
+                 and not (cross_attention_data is not None and "cross_attention" in self._children))
         if mode == ForwardMode.FORWARD:
             states, sa = None, self.self_attention(
-                segment_ids=target_segment_ids, target_positions=target_positions, **sa_kwargs)
+                segment_ids=target_segment_ids, target_positions=target_positions, defer_residual=defer, **sa_kwargs)
         elif mode == ForwardMode.INIT_STATES:
             states, sa = self.self_attention.init_states(
                 time_step=cached_states["self_attention"], segment_ids=target_segment_ids,
@@ -1418,7 +1448,10 @@ class TransformerLayer(BaseTransformerLayer):
                                       attention_logit_biases=cross_attention_logit_biases,
                                       return_aux=return_aux)
             x, cross_probs = ca.data, ca.probs
-        x = self.feed_forward(x)
+        if isinstance(x, tuple):
+            x = self.feed_forward(x[0], pending_residual=x[1])
+        else:
+            x = self.feed_forward(x)
         return {"self_attention": states}, self.Output(
             data=x, self_attention_probs=sa.probs, self_attention_kv_state=sa.kv_state,
             cross_attention_probs=cross_probs)

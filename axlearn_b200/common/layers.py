@@ -205,6 +205,18 @@ class RMSNorm(RMSNormStateless):
             x, self.parameters["scale"], cfg.eps, upcast=cfg.forward_dtype == torch.float32
         )
 
+    def forward_keep_input(self, x: Tensor) -> tuple[Tensor, Tensor]:
+        """``(norm(x), x)`` for a pre-norm block: use the second output for the residual branch
+        and its gradient is added inside the norm's backward pass."""
+        cfg = self._config
+        return ops.rms_norm_keep_input(x, self.parameters["scale"], cfg.eps, upcast=cfg.forward_dtype == torch.float32)
+
+    def forward_add(self, x: Tensor, residual: Tensor) -> tuple[Tensor, Tensor]:
+        """``(x + residual, norm(x + residual))`` in one pass."""
+        cfg = self._config
+        return ops.add_rms_norm(x, residual, self.parameters["scale"], cfg.eps,
+                                upcast=cfg.forward_dtype == torch.float32)
+
 
 class L2Norm(BaseLayer):
     @config_class

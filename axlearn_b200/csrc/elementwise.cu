@@ -164,6 +164,187 @@ __global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ x, const bf16* __res
     partial[static_cast<int64_t>(blockIdx.x) * D + i] = dscale_acc[i];
 }
 
+// ------------------------------------------------------------------------------ RMSNorm, one warp per row
+// The row (D = 256 * VPL elements) lives in registers: every lane issues all of its 16-byte loads
+// up front and the statistics need only warp shuffles, so a CTA of eight warps keeps eight rows
+// (tens of KB) in flight with no block-wide barrier per row.  Same arithmetic as the kernels above.
+// Keeps the compiler from hoisting the next group's loads above this group's stores (which would
+// hold several more vectors per lane live than the register file has room for).
+#define AXB_SCHED_FENCE() asm volatile("" ::: "memory")
+
+// A 16-byte read-only load that the compiler neither merges with an identical earlier load nor
+// moves: each use re-reads (from L1) instead of keeping the vector in registers between loops.
+__device__ __forceinline__ Bf16x8 ld_again(const Bf16x8* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return *reinterpret_cast<Bf16x8*>(&v);
+}
+
+template <int VPL>
+__global__ void __launch_bounds__(256, VPL >= 16 ? 1 : 2)
+rmsnorm_fwd_warp_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual,
+                        const bf16* __restrict__ scale, bf16* __restrict__ y, bf16* __restrict__ sum_out,
+                        float* __restrict__ rstd_out, int64_t rows, float eps) {
+  constexpr int D = VPL * 256;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * 8;
+  const Bf16x8* sc = reinterpret_cast<const Bf16x8*>(scale);
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); row < rows; row += warps) {
+    const Bf16x8* xr = reinterpret_cast<const Bf16x8*>(x + row * D);
+    Bf16x8 a[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) a[i] = xr[i * 32 + lane];
+    if (residual != nullptr) {
+      const Bf16x8* rr = reinterpret_cast<const Bf16x8*>(residual + row * D);
+      Bf16x8* sr = reinterpret_cast<Bf16x8*>(sum_out + row * D);
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const Bf16x8 b = rr[i * 32 + lane];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) a[i].v[j] = __hadd2(a[i].v[j], b.v[j]);
+        sr[i * 32 + lane] = a[i];
+        if ((i & 7) == 7) AXB_SCHED_FENCE();
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(a[i].v[j]);
+        ss += f.x * f.x + f.y * f.y;
+      }
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / D + eps);
+    if (lane == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+    Bf16x8* yr = reinterpret_cast<Bf16x8*>(y + row * D);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const Bf16x8 s = sc[i * 32 + lane];
+      Bf16x8 o;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(a[i].v[j]);
+        const float2 g = __bfloat1622float2(s.v[j]);
+        // Match the unfused definition: normalise, round to bf16, then scale.
+        const float2 nf = __bfloat1622float2(__floats2bfloat162_rn(f.x * rstd, f.y * rstd));
+        o.v[j] = __floats2bfloat162_rn(nf.x * g.x, nf.y * g.y);
+      }
+      yr[i * 32 + lane] = o;
+      if ((i & 3) == 3) AXB_SCHED_FENCE();
+    }
+  }
+}
+
+// Backward, WPR warps per row (each owns a contiguous 256 * VPL-element part of it; two warps
+// for the widest rows, whose halves would not fit one lane's registers).  The per-column sums for
+// dscale are kept per warp in shared memory (each lane owns its columns, so nothing races), summed
+// over the CTA's warps in a fixed order at the end and written to partial[blockIdx.x, :].  Shared
+// layout of a warp's part: float4 slot ((i * 2 + h) * 32 + lane) holds its columns
+// (i * 32 + lane) * 8 + h * 4 .. + 3 (conflict-free for a warp).
+template <int VPL, int WPR>
+__global__ void __launch_bounds__(256, 1)
+rmsnorm_bwd_warp_kernel(const bf16* __restrict__ x, const bf16* __restrict__ scale, const float* __restrict__ rstd_in,
+                        const bf16* __restrict__ dy, const bf16* __restrict__ dres, bf16* __restrict__ dx,
+                        float* __restrict__ partial, int64_t rows) {
+  constexpr int P = VPL * 256;  // elements per warp
+  constexpr int D = P * WPR;
+  constexpr int kRowsPerCta = 8 / WPR;
+  extern __shared__ float4 acc_all[];  // [8 warps][P / 4]
+  __shared__ float dot_part[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int part = warp % WPR, slot = warp / WPR;
+  float4* acc = acc_all + warp * (P / 4);
+  for (int i = lane; i < P / 4; i += 32) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  __syncwarp();
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kRowsPerCta;
+  const Bf16x8* sc = reinterpret_cast<const Bf16x8*>(scale + part * P);
+  // Every warp of a row makes the same number of trips, so the pair barrier below always matches.
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + slot; row < rows; row += stride) {
+    const Bf16x8* xr = reinterpret_cast<const Bf16x8*>(x + row * D + part * P);
+    const Bf16x8* gr = reinterpret_cast<const Bf16x8*>(dy + row * D + part * P);
+    Bf16x8 a[VPL], g[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      a[i] = xr[i * 32 + lane];
+      g[i] = gr[i * 32 + lane];
+    }
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const Bf16x8 s = ld_again(sc + i * 32 + lane);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 xf = __bfloat1622float2(a[i].v[j]), gf = __bfloat1622float2(g[i].v[j]),
+                     sf = __bfloat1622float2(s.v[j]);
+        dot += gf.x * sf.x * xf.x * rstd + gf.y * sf.y * xf.y * rstd;
+      }
+    }
+    dot = warp_sum(dot);
+    if constexpr (WPR > 1) {
+      // Exchange the parts' sums between the warps of this row (a named barrier per row slot).
+      if (lane == 0) dot_part[warp] = dot;
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + slot), "r"(32 * WPR) : "memory");
+      dot = 0.f;
+#pragma unroll
+      for (int w = 0; w < WPR; ++w) dot += dot_part[slot * WPR + w];
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + slot), "r"(32 * WPR) : "memory");  // before the next row overwrites
+    }
+    dot /= D;
+    const Bf16x8* rr = dres != nullptr ? reinterpret_cast<const Bf16x8*>(dres + row * D + part * P) : nullptr;
+    Bf16x8* dxr = reinterpret_cast<Bf16x8*>(dx + row * D + part * P);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const Bf16x8 s = ld_again(sc + i * 32 + lane);
+      Bf16x8 r, o;
+      if (rr != nullptr) r = ld_again(rr + i * 32 + lane);
+      float ds[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 xf = __bfloat1622float2(a[i].v[j]), gf = __bfloat1622float2(g[i].v[j]),
+                     sf = __bfloat1622float2(s.v[j]);
+        const float xh0 = xf.x * rstd, xh1 = xf.y * rstd;
+        float d0 = rstd * (gf.x * sf.x - xh0 * dot);
+        float d1 = rstd * (gf.y * sf.y - xh1 * dot);
+        if (rr != nullptr) {
+          const float2 rf = __bfloat1622float2(r.v[j]);
+          d0 += rf.x;
+          d1 += rf.y;
+        }
+        o.v[j] = __floats2bfloat162_rn(d0, d1);
+        ds[2 * j] = gf.x * xh0;
+        ds[2 * j + 1] = gf.y * xh1;
+      }
+      dxr[i * 32 + lane] = o;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float4 v = acc[(i * 2 + h) * 32 + lane];
+        v.x += ds[4 * h];
+        v.y += ds[4 * h + 1];
+        v.z += ds[4 * h + 2];
+        v.w += ds[4 * h + 3];
+        acc[(i * 2 + h) * 32 + lane] = v;
+      }
+    }
+  }
+  __syncthreads();
+  // Column c of part q: cc = c - q * P = (i * 32 + l) * 8 + h * 4 + e  <->  float index
+  // ((i * 2 + h) * 32 + l) * 4 + e of every warp with warp % WPR == q.
+  const float* flat = reinterpret_cast<const float*>(acc_all);
+  for (int c = threadIdx.x; c < D; c += 256) {
+    const int q = c / P, cc = c - q * P;
+    const int vec = cc >> 3, h = (cc >> 2) & 1, e = cc & 3;
+    const int i = vec >> 5, l = vec & 31;
+    const int idx = ((i * 2 + h) * 32 + l) * 4 + e;
+    float sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < kRowsPerCta; ++w) sum += flat[(w * WPR + q) * P + idx];
+    partial[static_cast<int64_t>(blockIdx.x) * D + c] = sum;
+  }
+}
+
 __global__ void reduce_partials_kernel(const float* __restrict__ partial, bf16* __restrict__ out_bf16,
                                        float* __restrict__ out_f32, int nparts, int D) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -659,6 +840,80 @@ extern "C" int axb_rmsnorm_bwd(const void* x, const void* scale, const float* rs
       rows, D);
   reduce_partials_kernel<<<(D + 255) / 256, 256, 0, stream>>>(
       partial, static_cast<bf16*>(dscale_bf16), dscale_f32, grid, D);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+template <int VPL>
+static int launch_rmsnorm_fwd_warp(const void* x, const void* residual, const void* scale, void* y, void* sum_out,
+                                   float* rstd, int64_t rows, float eps, cudaStream_t stream) {
+  const int64_t want = (rows + 7) / 8;
+  const int grid = static_cast<int>(want < 148 * 2 ? want : 148 * 2);
+  rmsnorm_fwd_warp_kernel<VPL><<<grid, 256, 0, stream>>>(
+      static_cast<const bf16*>(x), static_cast<const bf16*>(residual), static_cast<const bf16*>(scale),
+      static_cast<bf16*>(y), static_cast<bf16*>(sum_out), rstd, rows, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+template <int VPL, int WPR>
+static int launch_rmsnorm_bwd_warp(const void* x, const void* scale, const float* rstd, const void* dy,
+                                   const void* dres, void* dx, float* partial, int cap, int64_t rows,
+                                   cudaStream_t stream) {
+  constexpr int kSmem = 8 * VPL * 256 * static_cast<int>(sizeof(float));
+  const int64_t want = (rows + 8 / WPR - 1) / (8 / WPR);
+  const int grid = static_cast<int>(want < cap ? want : cap);
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(rmsnorm_bwd_warp_kernel<VPL, WPR>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
+        cudaSuccess)
+      return -3;
+    configured = true;
+  }
+  rmsnorm_bwd_warp_kernel<VPL, WPR><<<grid, 256, kSmem, stream>>>(
+      static_cast<const bf16*>(x), static_cast<const bf16*>(scale), rstd, static_cast<const bf16*>(dy),
+      static_cast<const bf16*>(dres), static_cast<bf16*>(dx), partial, rows);
+  return cudaGetLastError() == cudaSuccess ? grid : -4;
+}
+
+// 1 when the warp-per-row kernels take this width (rows of 512, 1024, 2048 or 4096 elements).
+extern "C" int axb_rmsnorm_fast_supported(int D) { return (D == 512 || D == 1024 || D == 2048 || D == 4096) ? 1 : 0; }
+
+// Same contract as axb_rmsnorm_fwd, on the warp-per-row kernel (D must be a supported width).
+extern "C" int axb_rmsnorm_fwd_fast(const void* x, const void* residual, const void* scale, void* y, void* sum_out,
+                                    float* rstd, int64_t rows, int D, float eps, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (residual != nullptr && sum_out == nullptr) return -10;
+  switch (D) {
+    case 512: return launch_rmsnorm_fwd_warp<2>(x, residual, scale, y, sum_out, rstd, rows, eps, stream);
+    case 1024: return launch_rmsnorm_fwd_warp<4>(x, residual, scale, y, sum_out, rstd, rows, eps, stream);
+    case 2048: return launch_rmsnorm_fwd_warp<8>(x, residual, scale, y, sum_out, rstd, rows, eps, stream);
+    case 4096: return launch_rmsnorm_fwd_warp<16>(x, residual, scale, y, sum_out, rstd, rows, eps, stream);
+    default: return -10;
+  }
+}
+
+// Same contract as axb_rmsnorm_bwd (`partial` has axb_rmsnorm_bwd_ctas(rows) rows), on the
+// warp-per-row kernel.  The order of the dscale summation differs from axb_rmsnorm_bwd, so the two
+// agree to rounding, not bit for bit.
+extern "C" int axb_rmsnorm_bwd_fast(const void* x, const void* scale, const float* rstd, const void* dy,
+                                    const void* dres, void* dx, float* partial, void* dscale_bf16, float* dscale_f32,
+                                    int64_t rows, int D, cudaStream_t stream) {
+  if (rows <= 0) {
+    if (dscale_bf16 != nullptr) cudaMemsetAsync(dscale_bf16, 0, D * sizeof(bf16), stream);
+    if (dscale_f32 != nullptr) cudaMemsetAsync(dscale_f32, 0, D * sizeof(float), stream);
+    return 0;
+  }
+  const int cap = axb_rmsnorm_bwd_ctas(rows) < 148 ? axb_rmsnorm_bwd_ctas(rows) : 148;
+  int grid;  // the launcher returns the number of CTAs (= rows of `partial`) it used
+  switch (D) {
+    case 512: grid = launch_rmsnorm_bwd_warp<2, 1>(x, scale, rstd, dy, dres, dx, partial, cap, rows, stream); break;
+    case 1024: grid = launch_rmsnorm_bwd_warp<4, 1>(x, scale, rstd, dy, dres, dx, partial, cap, rows, stream); break;
+    case 2048: grid = launch_rmsnorm_bwd_warp<4, 2>(x, scale, rstd, dy, dres, dx, partial, cap, rows, stream); break;
+    case 4096: grid = launch_rmsnorm_bwd_warp<8, 2>(x, scale, rstd, dy, dres, dx, partial, cap, rows, stream); break;
+    default: return -10;
+  }
+  if (grid < 0) return grid;
+  reduce_partials_kernel<<<(D + 255) / 256, 256, 0, stream>>>(partial, static_cast<bf16*>(dscale_bf16), dscale_f32,
+                                                              grid, D);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -12,7 +12,9 @@ from axlearn_b200.ops.dispatch import (  # noqa: F401
     cross_entropy,
     linear,
     lm_head_cross_entropy,
+    add_rms_norm,
     rms_norm,
+    rms_norm_keep_input,
     rope,
     swiglu,
     use_reference_ops,

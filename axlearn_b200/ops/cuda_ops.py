@@ -70,6 +70,10 @@ class _Sigs:
                             c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     axb_rmsnorm_fwd = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p]
     axb_rmsnorm_bwd_ctas = [c_int64]
+    axb_rmsnorm_fast_supported = [c_int]
+    axb_rmsnorm_fwd_fast = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p]
+    axb_rmsnorm_bwd_fast = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_void_p, c_int64, c_int, c_void_p]
     axb_rmsnorm_bwd = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                        c_void_p, c_int64, c_int, c_void_p]
     axb_swiglu_fwd = [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]
@@ -334,19 +338,43 @@ def carries_gather(w: torch.Tensor) -> bool:
 # ------------------------------------------------------------------------------------------
 
 
+def _rmsnorm_forward(x2, residual2, scale_b, eps):
+    """``(y, sum, rstd)``; ``sum`` is ``x + residual`` (None without a residual)."""
+    rows, d = x2.shape
+    y = torch.empty_like(x2)
+    total = torch.empty_like(x2) if residual2 is not None else None
+    rstd = torch.empty(rows, dtype=torch.float32, device=x2.device)
+    fn = lib().axb_rmsnorm_fwd_fast if lib().axb_rmsnorm_fast_supported(d) else lib().axb_rmsnorm_fwd
+    _check(fn(x2.data_ptr(), None if residual2 is None else residual2.data_ptr(), scale_b.data_ptr(), y.data_ptr(),
+              None if total is None else total.data_ptr(), rstd.data_ptr(), rows, d, eps, _stream()), "axb_rmsnorm_fwd")
+    return y, total, rstd
+
+
+def _rmsnorm_backward(x2, scale_b, rstd, dy2, dres2):
+    """``(dx [+ dres], dscale fp32)`` in one pass over the rows."""
+    rows, d = x2.shape
+    dx = torch.empty_like(x2)
+    ctas = lib().axb_rmsnorm_bwd_ctas(rows)
+    partial = torch.empty((max(ctas, 1), d), dtype=torch.float32, device=x2.device)
+    dscale = torch.empty(d, dtype=torch.float32, device=x2.device)
+    fn = lib().axb_rmsnorm_bwd_fast if lib().axb_rmsnorm_fast_supported(d) else lib().axb_rmsnorm_bwd
+    _check(fn(x2.data_ptr(), scale_b.data_ptr(), rstd.data_ptr(), dy2.data_ptr(),
+              None if dres2 is None else dres2.data_ptr(), dx.data_ptr(), partial.data_ptr(), None, dscale.data_ptr(),
+              rows, d, _stream()), "axb_rmsnorm_bwd")
+    return dx, dscale
+
+
+def _rows(t: torch.Tensor) -> torch.Tensor:
+    t2 = t.reshape(-1, t.shape[-1])
+    return t2 if t2.is_contiguous() else t2.contiguous()
+
+
 class _RmsNorm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, scale, eps):
-        d = x.shape[-1]
-        x2 = x.reshape(-1, d)
-        if not x2.is_contiguous():
-            x2 = x2.contiguous()
+        x2 = _rows(x)
         scale_b = scale.to(torch.bfloat16).contiguous()
-        rows = x2.shape[0]
-        y = torch.empty_like(x2)
-        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
-        _check(lib().axb_rmsnorm_fwd(x2.data_ptr(), None, scale_b.data_ptr(), y.data_ptr(), None,
-                                     rstd.data_ptr(), rows, d, eps, _stream()), "axb_rmsnorm_fwd")
+        y, _, rstd = _rmsnorm_forward(x2, None, scale_b, eps)
         ctx.save_for_backward(x2, scale_b, rstd)
         ctx.scale_dtype = scale.dtype
         ctx.x_shape = x.shape
@@ -355,19 +383,56 @@ class _RmsNorm(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x2, scale_b, rstd = ctx.saved_tensors
-        d = x2.shape[-1]
-        rows = x2.shape[0]
-        dy2 = dy.reshape(-1, d)
-        if not dy2.is_contiguous():
-            dy2 = dy2.contiguous()
-        dx = torch.empty_like(x2)
-        ctas = lib().axb_rmsnorm_bwd_ctas(rows)
-        partial = torch.empty((ctas, d), dtype=torch.float32, device=x2.device)
-        dscale = torch.empty(d, dtype=torch.float32, device=x2.device)
-        _check(lib().axb_rmsnorm_bwd(x2.data_ptr(), scale_b.data_ptr(), rstd.data_ptr(), dy2.data_ptr(),
-                                     None, dx.data_ptr(), partial.data_ptr(), None, dscale.data_ptr(),
-                                     rows, d, _stream()), "axb_rmsnorm_bwd")
+        dx, dscale = _rmsnorm_backward(x2, scale_b, rstd, _rows(dy), None)
         return dx.reshape(ctx.x_shape), dscale.to(ctx.scale_dtype), None
+
+
+class _RmsNormKeepInput(torch.autograd.Function):
+    """``(rms_norm(x), x)``: the second output is the input itself, for the residual branch of a
+    pre-norm block.  The gradient arriving through that branch is added inside the backward
+    kernel, so no separate add runs."""
+
+    @staticmethod
+    def forward(ctx, x, scale, eps):
+        x2 = _rows(x)
+        scale_b = scale.to(torch.bfloat16).contiguous()
+        y, _, rstd = _rmsnorm_forward(x2, None, scale_b, eps)
+        ctx.save_for_backward(x2, scale_b, rstd)
+        ctx.scale_dtype = scale.dtype
+        ctx.x_shape = x.shape
+        return y.reshape(x.shape), x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dy, dskip):
+        x2, scale_b, rstd = ctx.saved_tensors
+        if dy is None:
+            return dskip, None, None
+        dx, dscale = _rmsnorm_backward(x2, scale_b, rstd, _rows(dy), None if dskip is None else _rows(dskip))
+        return dx.reshape(ctx.x_shape), dscale.to(ctx.scale_dtype), None
+
+
+class _AddRmsNorm(torch.autograd.Function):
+    """``s = x + r`` and ``rms_norm(s)`` in one pass; backward gives ``ds + d rms_norm`` (one
+    tensor, the gradient of both ``x`` and ``r``) in one pass."""
+
+    @staticmethod
+    def forward(ctx, x, r, scale, eps):
+        x2, r2 = _rows(x), _rows(r)
+        scale_b = scale.to(torch.bfloat16).contiguous()
+        y, total, rstd = _rmsnorm_forward(x2, r2, scale_b, eps)
+        ctx.save_for_backward(total, scale_b, rstd)
+        ctx.scale_dtype = scale.dtype
+        ctx.x_shape = x.shape
+        return total.reshape(x.shape), y.reshape(x.shape)
+
+    @staticmethod
+    def backward(ctx, dsum, dy):
+        total, scale_b, rstd = ctx.saved_tensors
+        if dy is None:
+            return dsum, dsum, None, None
+        dx, dscale = _rmsnorm_backward(total, scale_b, rstd, _rows(dy), None if dsum is None else _rows(dsum))
+        dx = dx.reshape(ctx.x_shape)
+        return dx, dx, dscale.to(ctx.scale_dtype), None
 
 
 def rms_norm(x: torch.Tensor, scale: torch.Tensor, eps: float) -> torch.Tensor:
@@ -376,6 +441,16 @@ def rms_norm(x: torch.Tensor, scale: torch.Tensor, eps: float) -> torch.Tensor:
 
         return reference.rms_norm(x, scale, eps, upcast=True)
     return _RmsNorm.apply(x, scale, float(eps))
+
+
+def rms_norm_keep_input(x: torch.Tensor, scale: torch.Tensor, eps: float):
+    """``(rms_norm(x), x)`` with the residual-branch gradient folded into the backward kernel."""
+    return _RmsNormKeepInput.apply(x, scale, float(eps))
+
+
+def add_rms_norm(x: torch.Tensor, r: torch.Tensor, scale: torch.Tensor, eps: float):
+    """``(x + r, rms_norm(x + r))`` in one pass each way."""
+    return _AddRmsNorm.apply(x, r, scale, float(eps))
 
 
 # ------------------------------------------------------------------------------------------

@@ -51,6 +51,26 @@ def rms_norm(x, scale, eps: float, *, upcast: bool = False):
     return reference.rms_norm(x, scale, eps, upcast=upcast)
 
 
+def _fused_norm_ok(x, scale) -> bool:
+    return _cuda(x, scale) and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0
+
+
+def rms_norm_keep_input(x, scale, eps: float, *, upcast: bool = False):
+    """``(rms_norm(x), x)``: on the kernel path the gradient that arrives through the second
+    output (the residual branch of a pre-norm block) is added inside the norm's backward kernel."""
+    if _fused_norm_ok(x, scale):
+        return _ops().rms_norm_keep_input(x, scale, eps)
+    return rms_norm(x, scale, eps, upcast=upcast), x
+
+
+def add_rms_norm(x, r, scale, eps: float, *, upcast: bool = False):
+    """``(x + r, rms_norm(x + r))``; one pass forward and one backward on the kernel path."""
+    if _fused_norm_ok(x, scale) and r.dtype == x.dtype and r.shape == x.shape:
+        return _ops().add_rms_norm(x, r, scale, eps)
+    total = x + r
+    return total, rms_norm(total, scale, eps, upcast=upcast)
+
+
 def swiglu(gate, up):
     if _cuda(gate, up) and gate.dtype == torch.bfloat16:
         return _ops().swiglu(gate, up)

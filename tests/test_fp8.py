@@ -69,9 +69,11 @@ def test_quantized_dot_general_layer(scaling):
     ref = x.float() @ w.float()
     assert (y.float() - ref).abs().max() < 0.1 * ref.abs().max()
     if scaling == "tensor":
-        assert set(params) == {"input_amax_history", "kernel_amax_history", "output_grad_amax_history"}
-        upd = oc.state_updates["input_amax_history"]
-        assert upd[0] == x.abs().amax().float() and upd.shape == (4,)
+        # Scales and amax histories are parameters; their new values come back as gradients
+        # (tests/test_fp8_training.py covers the update through the learner).
+        assert set(params) == {"input_scale", "kernel_scale", "output_grad_scale",
+                               "input_amax_history", "kernel_amax_history", "output_grad_amax_history"}
+        assert params["input_amax_history"].shape == (4,) and params["input_scale"].shape == ()
     else:
         assert params == {}
 

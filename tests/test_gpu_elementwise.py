@@ -12,7 +12,59 @@ def _close(a, b, tol):
     assert err / scale < tol, f"err {err} scale {scale}"
 
 
-@pytest.mark.parametrize("rows,d", [(64, 128), (1000, 4096), (37, 1024)])
+def _close_elementwise(out, ref, atol, rtol):
+    diff = (out.float() - ref.float()).abs()
+    bad = diff > atol + rtol * ref.float().abs()
+    assert not bad.any(), f"{int(bad.sum())} elements off; worst {diff.max().item():.4g}"
+
+
+@pytest.mark.parametrize("rows,d", [(333, 512), (100, 1024), (257, 2048), (1000, 4096), (9, 4096), (64, 768), (50, 8192)])
+def test_fused_residual_rmsnorm_ops(rows, d):
+    """``rms_norm_keep_input`` and ``add_rms_norm`` (warp-per-row kernels for the widths they take,
+    the general kernel otherwise) against fp32 PyTorch, values and all gradients."""
+    from axlearn_b200.ops import cuda_ops
+
+    torch.manual_seed(4)
+    eps = 1e-5
+
+    def ref_norm(t, sc):
+        return t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps) * sc
+
+    x = torch.randn(rows, d, device="cuda").bfloat16().requires_grad_()
+    r = torch.randn(rows, d, device="cuda").bfloat16().requires_grad_()
+    scale = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16().requires_grad_()
+    g_y, g_s = torch.randn(rows, d, device="cuda").bfloat16(), torch.randn(rows, d, device="cuda").bfloat16()
+
+    # (x + r, norm(x + r)); loss takes both outputs.
+    total, y = cuda_ops.add_rms_norm(x, r, scale, eps)
+    (total.float() * g_s.float()).sum().backward(retain_graph=True)
+    (y.float() * g_y.float()).sum().backward()
+    xf, rf, sf = (t.detach().float().requires_grad_() for t in (x, r, scale))
+    tf = (xf + rf).detach().bfloat16().float() + (xf + rf - (xf + rf).detach())   # value rounded to bf16, gradient of x + r
+    yf = ref_norm(tf, sf)
+    ((tf * g_s.float()).sum() + (yf * g_y.float()).sum()).backward()
+    _close_elementwise(total, tf, 1e-6, 1e-6)
+    _close_elementwise(y, yf, 0.03, 2e-2)
+    _close_elementwise(x.grad, xf.grad, 0.06, 2e-2)
+    assert torch.equal(x.grad, r.grad)
+    _close(scale.grad, sf.grad, 2e-2)
+
+    # (norm(x), x): the residual-branch gradient is added inside the backward kernel.
+    x2 = x.detach().clone().requires_grad_()
+    scale2 = scale.detach().clone().requires_grad_()
+    y2, skip = cuda_ops.rms_norm_keep_input(x2, scale2, eps)
+    ((y2.float() * g_y.float()).sum() + (skip.float() * g_s.float()).sum()).backward()
+    x2f, s2f = x2.detach().float().requires_grad_(), scale2.detach().float().requires_grad_()
+    ((ref_norm(x2f, s2f) * g_y.float()).sum() + (x2f * g_s.float()).sum()).backward()
+    assert torch.equal(skip, x2)
+    _close_elementwise(y2, ref_norm(x2f, s2f), 0.03, 2e-2)
+    _close_elementwise(x2.grad, x2f.grad, 0.06, 2e-2)
+    _close(scale2.grad, s2f.grad, 2e-2)
+    torch.cuda.synchronize()
+    cuda_ops.check_status()
+
+
+@pytest.mark.parametrize("rows,d", [(64, 128), (1000, 4096), (37, 1024), (5000, 2048), (7, 512)])
 def test_rmsnorm_fwd_bwd(rows, d):
     from axlearn_b200.ops import cuda_ops
 
