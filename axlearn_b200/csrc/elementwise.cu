@@ -180,30 +180,37 @@ __device__ __forceinline__ Bf16x8 ld_again(const Bf16x8* p) {
   return *reinterpret_cast<Bf16x8*>(&v);
 }
 
-template <int VPL>
-__global__ void __launch_bounds__(256, VPL >= 16 ? 1 : 2)
+// WPR warps share a row (each a contiguous 256 * VPL-element part); wide rows are split so that a
+// lane holds at most eight vectors and three CTAs fit an SM (more rows, hence bytes, in flight).
+template <int VPL, int WPR>
+__global__ void __launch_bounds__(256, 3)
 rmsnorm_fwd_warp_kernel(const bf16* __restrict__ x, const bf16* __restrict__ residual,
                         const bf16* __restrict__ scale, bf16* __restrict__ y, bf16* __restrict__ sum_out,
                         float* __restrict__ rstd_out, int64_t rows, float eps) {
-  constexpr int D = VPL * 256;
-  const int lane = threadIdx.x & 31;
-  const int64_t warps = static_cast<int64_t>(gridDim.x) * 8;
-  const Bf16x8* sc = reinterpret_cast<const Bf16x8*>(scale);
-  for (int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); row < rows; row += warps) {
-    const Bf16x8* xr = reinterpret_cast<const Bf16x8*>(x + row * D);
+  constexpr int P = VPL * 256;
+  constexpr int D = P * WPR;
+  constexpr int kRowsPerCta = 8 / WPR;
+  __shared__ float ss_part[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int part = warp % WPR, slot = warp / WPR;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kRowsPerCta;
+  const Bf16x8* sc = reinterpret_cast<const Bf16x8*>(scale + part * P);
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + slot; row < rows; row += stride) {
+    const Bf16x8* xr = reinterpret_cast<const Bf16x8*>(x + row * D + part * P);
     Bf16x8 a[VPL];
 #pragma unroll
     for (int i = 0; i < VPL; ++i) a[i] = xr[i * 32 + lane];
     if (residual != nullptr) {
-      const Bf16x8* rr = reinterpret_cast<const Bf16x8*>(residual + row * D);
-      Bf16x8* sr = reinterpret_cast<Bf16x8*>(sum_out + row * D);
+      const Bf16x8* rr = reinterpret_cast<const Bf16x8*>(residual + row * D + part * P);
+      Bf16x8* sr = reinterpret_cast<Bf16x8*>(sum_out + row * D + part * P);
+      Bf16x8 b[VPL];
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) b[i] = rr[i * 32 + lane];
 #pragma unroll
       for (int i = 0; i < VPL; ++i) {
-        const Bf16x8 b = rr[i * 32 + lane];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) a[i].v[j] = __hadd2(a[i].v[j], b.v[j]);
+        for (int j = 0; j < 4; ++j) a[i].v[j] = __hadd2(a[i].v[j], b[i].v[j]);
         sr[i * 32 + lane] = a[i];
-        if ((i & 7) == 7) AXB_SCHED_FENCE();
       }
     }
     float ss = 0.f;
@@ -216,9 +223,17 @@ rmsnorm_fwd_warp_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res
       }
     }
     ss = warp_sum(ss);
+    if constexpr (WPR > 1) {
+      if (lane == 0) ss_part[warp] = ss;
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + slot), "r"(32 * WPR) : "memory");
+      ss = 0.f;
+#pragma unroll
+      for (int w = 0; w < WPR; ++w) ss += ss_part[slot * WPR + w];
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + slot), "r"(32 * WPR) : "memory");
+    }
     const float rstd = rsqrtf(ss / D + eps);
-    if (lane == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
-    Bf16x8* yr = reinterpret_cast<Bf16x8*>(y + row * D);
+    if (lane == 0 && part == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+    Bf16x8* yr = reinterpret_cast<Bf16x8*>(y + row * D + part * P);
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
       const Bf16x8 s = sc[i * 32 + lane];
@@ -232,7 +247,6 @@ rmsnorm_fwd_warp_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res
         o.v[j] = __floats2bfloat162_rn(nf.x * g.x, nf.y * g.y);
       }
       yr[i * 32 + lane] = o;
-      if ((i & 3) == 3) AXB_SCHED_FENCE();
     }
   }
 }
@@ -243,16 +257,16 @@ rmsnorm_fwd_warp_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res
 // over the CTA's warps in a fixed order at the end and written to partial[blockIdx.x, :].  Shared
 // layout of a warp's part: float4 slot ((i * 2 + h) * 32 + lane) holds its columns
 // (i * 32 + lane) * 8 + h * 4 .. + 3 (conflict-free for a warp).
-template <int VPL, int WPR>
-__global__ void __launch_bounds__(256, 1)
+template <int VPL, int WPR, int NW>
+__global__ void __launch_bounds__(NW * 32, 1)
 rmsnorm_bwd_warp_kernel(const bf16* __restrict__ x, const bf16* __restrict__ scale, const float* __restrict__ rstd_in,
                         const bf16* __restrict__ dy, const bf16* __restrict__ dres, bf16* __restrict__ dx,
                         float* __restrict__ partial, int64_t rows) {
   constexpr int P = VPL * 256;  // elements per warp
   constexpr int D = P * WPR;
-  constexpr int kRowsPerCta = 8 / WPR;
-  extern __shared__ float4 acc_all[];  // [8 warps][P / 4]
-  __shared__ float dot_part[8];
+  constexpr int kRowsPerCta = NW / WPR;
+  extern __shared__ float4 acc_all[];  // [NW warps][P / 4]
+  __shared__ float dot_part[NW];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int part = warp % WPR, slot = warp / WPR;
   float4* acc = acc_all + warp * (P / 4);
@@ -333,7 +347,7 @@ rmsnorm_bwd_warp_kernel(const bf16* __restrict__ x, const bf16* __restrict__ sca
   // Column c of part q: cc = c - q * P = (i * 32 + l) * 8 + h * 4 + e  <->  float index
   // ((i * 2 + h) * 32 + l) * 4 + e of every warp with warp % WPR == q.
   const float* flat = reinterpret_cast<const float*>(acc_all);
-  for (int c = threadIdx.x; c < D; c += 256) {
+  for (int c = threadIdx.x; c < D; c += NW * 32) {
     const int q = c / P, cc = c - q * P;
     const int vec = cc >> 3, h = (cc >> 2) & 1, e = cc & 3;
     const int i = vec >> 5, l = vec & 31;
@@ -843,32 +857,32 @@ extern "C" int axb_rmsnorm_bwd(const void* x, const void* scale, const float* rs
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-template <int VPL>
+template <int VPL, int WPR>
 static int launch_rmsnorm_fwd_warp(const void* x, const void* residual, const void* scale, void* y, void* sum_out,
                                    float* rstd, int64_t rows, float eps, cudaStream_t stream) {
-  const int64_t want = (rows + 7) / 8;
-  const int grid = static_cast<int>(want < 148 * 2 ? want : 148 * 2);
-  rmsnorm_fwd_warp_kernel<VPL><<<grid, 256, 0, stream>>>(
+  const int64_t want = (rows + 8 / WPR - 1) / (8 / WPR);
+  const int grid = static_cast<int>(want < 148 * 3 ? want : 148 * 3);
+  rmsnorm_fwd_warp_kernel<VPL, WPR><<<grid, 256, 0, stream>>>(
       static_cast<const bf16*>(x), static_cast<const bf16*>(residual), static_cast<const bf16*>(scale),
       static_cast<bf16*>(y), static_cast<bf16*>(sum_out), rstd, rows, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-template <int VPL, int WPR>
+template <int VPL, int WPR, int NW>
 static int launch_rmsnorm_bwd_warp(const void* x, const void* scale, const float* rstd, const void* dy,
                                    const void* dres, void* dx, float* partial, int cap, int64_t rows,
                                    cudaStream_t stream) {
-  constexpr int kSmem = 8 * VPL * 256 * static_cast<int>(sizeof(float));
-  const int64_t want = (rows + 8 / WPR - 1) / (8 / WPR);
+  constexpr int kSmem = NW * VPL * 256 * static_cast<int>(sizeof(float));
+  const int64_t want = (rows + NW / WPR - 1) / (NW / WPR);
   const int grid = static_cast<int>(want < cap ? want : cap);
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(rmsnorm_bwd_warp_kernel<VPL, WPR>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
+    if (cudaFuncSetAttribute(rmsnorm_bwd_warp_kernel<VPL, WPR, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
         cudaSuccess)
       return -3;
     configured = true;
   }
-  rmsnorm_bwd_warp_kernel<VPL, WPR><<<grid, 256, kSmem, stream>>>(
+  rmsnorm_bwd_warp_kernel<VPL, WPR, NW><<<grid, NW * 32, kSmem, stream>>>(
       static_cast<const bf16*>(x), static_cast<const bf16*>(scale), rstd, static_cast<const bf16*>(dy),
       static_cast<const bf16*>(dres), static_cast<bf16*>(dx), partial, rows);
   return cudaGetLastError() == cudaSuccess ? grid : -4;
@@ -883,10 +897,10 @@ extern "C" int axb_rmsnorm_fwd_fast(const void* x, const void* residual, const v
   if (rows <= 0) return 0;
   if (residual != nullptr && sum_out == nullptr) return -10;
   switch (D) {
-    case 512: return launch_rmsnorm_fwd_warp<2>(x, residual, scale, y, sum_out, rstd, rows, eps, stream);
-    case 1024: return launch_rmsnorm_fwd_warp<4>(x, residual, scale, y, sum_out, rstd, rows, eps, stream);
-    case 2048: return launch_rmsnorm_fwd_warp<8>(x, residual, scale, y, sum_out, rstd, rows, eps, stream);
-    case 4096: return launch_rmsnorm_fwd_warp<16>(x, residual, scale, y, sum_out, rstd, rows, eps, stream);
+    case 512: return launch_rmsnorm_fwd_warp<2, 1>(x, residual, scale, y, sum_out, rstd, rows, eps, stream);
+    case 1024: return launch_rmsnorm_fwd_warp<4, 1>(x, residual, scale, y, sum_out, rstd, rows, eps, stream);
+    case 2048: return launch_rmsnorm_fwd_warp<8, 1>(x, residual, scale, y, sum_out, rstd, rows, eps, stream);
+    case 4096: return launch_rmsnorm_fwd_warp<8, 2>(x, residual, scale, y, sum_out, rstd, rows, eps, stream);
     default: return -10;
   }
 }
@@ -905,10 +919,10 @@ extern "C" int axb_rmsnorm_bwd_fast(const void* x, const void* scale, const floa
   const int cap = axb_rmsnorm_bwd_ctas(rows) < 148 ? axb_rmsnorm_bwd_ctas(rows) : 148;
   int grid;  // the launcher returns the number of CTAs (= rows of `partial`) it used
   switch (D) {
-    case 512: grid = launch_rmsnorm_bwd_warp<2, 1>(x, scale, rstd, dy, dres, dx, partial, cap, rows, stream); break;
-    case 1024: grid = launch_rmsnorm_bwd_warp<4, 1>(x, scale, rstd, dy, dres, dx, partial, cap, rows, stream); break;
-    case 2048: grid = launch_rmsnorm_bwd_warp<4, 2>(x, scale, rstd, dy, dres, dx, partial, cap, rows, stream); break;
-    case 4096: grid = launch_rmsnorm_bwd_warp<8, 2>(x, scale, rstd, dy, dres, dx, partial, cap, rows, stream); break;
+    case 512: grid = launch_rmsnorm_bwd_warp<2, 1, 8>(x, scale, rstd, dy, dres, dx, partial, cap, rows, stream); break;
+    case 1024: grid = launch_rmsnorm_bwd_warp<4, 1, 8>(x, scale, rstd, dy, dres, dx, partial, cap, rows, stream); break;
+    case 2048: grid = launch_rmsnorm_bwd_warp<4, 2, 16>(x, scale, rstd, dy, dres, dx, partial, cap, rows, stream); break;
+    case 4096: grid = launch_rmsnorm_bwd_warp<4, 4, 16>(x, scale, rstd, dy, dres, dx, partial, cap, rows, stream); break;
     default: return -10;
   }
   if (grid < 0) return grid;
