@@ -70,7 +70,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
         for _, log in results:
             if log:
                 print(log)
-    stale = force or not os.path.exists(LIB_PATH) or any(
+    # The list of linked objects is recorded beside the library: a source that was removed (or
+    # added) changes the list and forces a new link even when no object is newer than the library.
+    manifest = LIB_PATH + ".objects"
+    listing = "\n".join(os.path.basename(o) for o in objs)
+    previous = open(manifest, encoding="utf-8").read() if os.path.exists(manifest) else None
+    stale = force or not os.path.exists(LIB_PATH) or previous != listing or any(
         os.path.getmtime(o) > os.path.getmtime(LIB_PATH) for o in objs)
     if stale:
         cmd = [_nvcc(), "-shared", "-o", LIB_PATH, *objs, "-gencode", "arch=compute_100a,code=sm_100a",
@@ -78,6 +83,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError(f"link failed:\n{proc.stdout}\n{proc.stderr}")
+        with open(manifest, "w", encoding="utf-8") as f:
+            f.write(listing)
     return LIB_PATH
 
 

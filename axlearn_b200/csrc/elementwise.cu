@@ -17,8 +17,17 @@ namespace axb {
 
 using bf16 = __nv_bfloat16;
 
+// Eight bf16 values moved as ONE 16-byte access: the copy operations are written out, because a
+// member-wise copy of the four bf16 pairs compiles to four 4-byte accesses (four times the
+// load / store instructions and cache sectors touched per warp).
 struct alignas(16) Bf16x8 {
   __nv_bfloat162 v[4];
+  Bf16x8() = default;
+  __device__ __forceinline__ Bf16x8(const Bf16x8& o) { *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(o.v); }
+  __device__ __forceinline__ Bf16x8& operator=(const Bf16x8& o) {
+    *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(o.v);
+    return *this;
+  }
 };
 
 __device__ __forceinline__ float warp_sum(float x) {

@@ -13,8 +13,17 @@ namespace {
 
 using bf16 = __nv_bfloat16;
 
+// Eight bf16 values moved as ONE 16-byte access: the copy operations are written out, because a
+// member-wise copy of the four bf16 pairs compiles to four 4-byte accesses (four times the
+// load / store instructions and cache sectors touched per warp).
 struct alignas(16) Vec8 {
   __nv_bfloat162 v[4];
+  Vec8() = default;
+  __device__ __forceinline__ Vec8(const Vec8& o) { *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(o.v); }
+  __device__ __forceinline__ Vec8& operator=(const Vec8& o) {
+    *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(o.v);
+    return *this;
+  }
 };
 
 // The library-owned workspace: [AXB_NOALLOC_RMSNORM_MAX_CTAS][AXB_NOALLOC_RMSNORM_MAX_D] fp32.

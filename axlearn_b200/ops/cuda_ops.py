@@ -31,6 +31,8 @@ launch_count = 0  # Kernels launched through this module (bench.py reports it).
 COMM_RESERVED_SMS = int(os.environ.get("AXB200_COMM_SMS", "0"))
 # "2cta": large GEMMs run on CTA pairs (256 x 256 tiles); "1cta": always the single-CTA kernel.
 GEMM_VARIANT = os.environ.get("AXB200_GEMM", "2cta")
+# RMSNorm kernels: "warp" (rows in registers, one or more warps per row) or "plain" (one CTA per row).
+RMSNORM_VARIANT = os.environ.get("AXB200_RMSNORM", "warp")
 
 
 def reserve_sms_for_comm(n: int) -> None:
@@ -344,9 +346,12 @@ def _rmsnorm_forward(x2, residual2, scale_b, eps):
     y = torch.empty_like(x2)
     total = torch.empty_like(x2) if residual2 is not None else None
     rstd = torch.empty(rows, dtype=torch.float32, device=x2.device)
-    fn = lib().axb_rmsnorm_fwd_fast if lib().axb_rmsnorm_fast_supported(d) else lib().axb_rmsnorm_fwd
-    _check(fn(x2.data_ptr(), None if residual2 is None else residual2.data_ptr(), scale_b.data_ptr(), y.data_ptr(),
-              None if total is None else total.data_ptr(), rstd.data_ptr(), rows, d, eps, _stream()), "axb_rmsnorm_fwd")
+    args = (x2.data_ptr(), None if residual2 is None else residual2.data_ptr(), scale_b.data_ptr(), y.data_ptr(),
+            None if total is None else total.data_ptr(), rstd.data_ptr(), rows, d, eps)
+    if RMSNORM_VARIANT != "plain" and lib().axb_rmsnorm_fast_supported(d):
+        _check(lib().axb_rmsnorm_fwd_fast(*args, _stream()), "axb_rmsnorm_fwd_fast")
+    else:
+        _check(lib().axb_rmsnorm_fwd(*args, _stream()), "axb_rmsnorm_fwd")
     return y, total, rstd
 
 
@@ -357,10 +362,12 @@ def _rmsnorm_backward(x2, scale_b, rstd, dy2, dres2):
     ctas = lib().axb_rmsnorm_bwd_ctas(rows)
     partial = torch.empty((max(ctas, 1), d), dtype=torch.float32, device=x2.device)
     dscale = torch.empty(d, dtype=torch.float32, device=x2.device)
-    fn = lib().axb_rmsnorm_bwd_fast if lib().axb_rmsnorm_fast_supported(d) else lib().axb_rmsnorm_bwd
-    _check(fn(x2.data_ptr(), scale_b.data_ptr(), rstd.data_ptr(), dy2.data_ptr(),
-              None if dres2 is None else dres2.data_ptr(), dx.data_ptr(), partial.data_ptr(), None, dscale.data_ptr(),
-              rows, d, _stream()), "axb_rmsnorm_bwd")
+    args = (x2.data_ptr(), scale_b.data_ptr(), rstd.data_ptr(), dy2.data_ptr(),
+            None if dres2 is None else dres2.data_ptr(), dx.data_ptr(), partial.data_ptr(), None, dscale.data_ptr(), rows, d)
+    if RMSNORM_VARIANT != "plain" and lib().axb_rmsnorm_fast_supported(d):
+        _check(lib().axb_rmsnorm_bwd_fast(*args, _stream()), "axb_rmsnorm_bwd_fast")
+    else:
+        _check(lib().axb_rmsnorm_bwd(*args, _stream()), "axb_rmsnorm_bwd")
     return dx, dscale
 
 

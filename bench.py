@@ -48,6 +48,8 @@ def _args():
     ap.add_argument("--per_gpu_batch", type=int, default=4)
     ap.add_argument("--layers", type=int, default=None, help="debug only: override layer count")
     ap.add_argument("--skip_e2e", action="store_true")
+    ap.add_argument("--kernel_table", default=None, help="after the timed regions, profile two more steps with the "
+                    "torch profiler and write per-kernel device-time shares to this file (rank 0)")
     ap.add_argument("--skip_parity", action="store_true", help="N>1: skip the one-step fused-vs-library parity record")
     return ap.parse_args()
 
@@ -222,6 +224,9 @@ def main():
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
         }
 
+    if args.kernel_table and use_cuda:
+        _write_kernel_table(args.kernel_table, trainer, step_fn, device_batches, rank)
+
     if rank == 0:
         # 6 * params * tokens (fwd+bwd) + attention; remat adds one more forward (reported
         # MFU counts model FLOPs only, i.e. without the recompute).
@@ -358,6 +363,37 @@ def _fused_vs_library_parity(args, world, local_rank) -> dict:
     gc.collect()
     torch.cuda.empty_cache()
     return record
+
+
+def _write_kernel_table(path, trainer, step_fn, batches, rank) -> None:
+    """Device time per kernel over two profiled steps (outside every timed region)."""
+    import collections
+
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    with trainer.mesh():
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for i in range(2):
+                step_fn(batches[i % len(batches)])
+            torch.cuda.synchronize()
+    total, count = collections.Counter(), collections.Counter()
+    first = last = None
+    for e in prof.events():
+        if e.device_type != torch.autograd.DeviceType.CUDA:
+            continue
+        total[e.name[:100]] += e.device_time
+        count[e.name[:100]] += 1
+        first = e.time_range.start if first is None else min(first, e.time_range.start)
+        last = e.time_range.end if last is None else max(last, e.time_range.end)
+    if rank != 0 or not total:
+        return
+    busy = sum(total.values())
+    with open(path, "w", encoding="utf-8") as f:
+        f.write(f"span_ms_per_step {(last - first) / 2e3:.1f} busy_ms_per_step {busy / 2e3:.1f} "
+                f"launches_per_step {sum(count.values()) // 2}\n")
+        for name, t in total.most_common(40):
+            f.write(f"{100 * t / busy:5.1f}% {count[name] // 2:5d} {t / count[name]:9.1f}us  {name}\n")
 
 
 def _leaves(tree):
