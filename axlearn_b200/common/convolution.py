@@ -26,21 +26,28 @@ Padding = Union[str, Sequence[tuple]]
 
 def _explicit_padding(padding: Padding, window: Sequence[int], strides: Sequence[int],
                       dilation: Sequence[int]) -> list[tuple[int, int]]:
+    """Explicit ``(lo, hi)`` per spatial dim (axlearn/common/convolution.py:119-217), with
+    ``w`` the dilated window: SAME = ``((w - 1) // 2, w - 1 - (w - 1) // 2)`` whatever the stride,
+    VALID = ``(0, 0)``, CAUSAL = ``(w - stride, stride - 1)`` on the first (time) dim and SAME on
+    the others."""
     if not isinstance(padding, str):
         return [tuple(p) for p in padding]
-    out = []
-    for w, s, d in zip(window, strides, dilation):
-        eff = (w - 1) * d + 1
-        if padding == "VALID":
-            out.append((0, 0))
-        elif padding == "CAUSAL":
-            out.append((eff - 1, 0))
-        elif padding == "SAME":
-            total = max(eff - 1, 0) if s == 1 else max(eff - s, 0)
-            out.append((total // 2, total - total // 2))
-        else:
-            raise NotImplementedError(padding)
-    return out
+    eff = [(w - 1) * d + 1 for w, d in zip(window, dilation)]
+
+    def same(w):
+        total = w - 1
+        return (total // 2, total - total // 2)
+
+    if padding == "VALID":
+        return [(0, 0)] * len(eff)
+    if padding == "SAME":
+        return [same(w) for w in eff]
+    if padding == "CAUSAL":
+        return [(eff[0] - strides[0], strides[0] - 1)] + [same(w) for w in eff[1:]]
+    raise NotImplementedError(padding)
+
+
+conv_explicit_padding = _explicit_padding
 
 
 def conv_output_length(length: int, *, window: int, stride: int, padding: tuple[int, int], dilation: int = 1) -> int:
