@@ -82,3 +82,83 @@ def ctc_forced_alignment(*, log_pos: Tensor, log_pos_paddings: Tensor, labels: T
     indices = torch.where(is_label & frame_live, path // 2, torch.full_like(path, -1))
     return AlignmentOutput(alignment=alignment, alignment_indices=indices,
                            alignment_score=torch.where(ok, final_score, torch.full_like(final_score, float("-inf"))))
+
+
+def alignment_to_segments(alignment: Tensor, blank_id: int) -> Tensor:
+    """``[B, T]`` frame labels (negative = padding) -> ``[B, T, 2]`` segments: row ``l`` holds the
+    start frame (inclusive) and end frame (exclusive) of the l-th emitted label, ``-1`` beyond the
+    last label.  A label's segment runs to the start of the next label (trailing blanks belong to
+    it); the last one runs to the number of frames (axlearn/audio/aligner/ctc_aligner.py:611)."""
+    b, t = alignment.shape
+    dev = alignment.device
+    prev = torch.cat([alignment.new_full((b, 1), -1), alignment[:, :-1]], dim=1)
+    starts_here = (alignment != prev) & (alignment != blank_id) & (alignment >= 0)
+    frame = torch.arange(t, device=dev)[None].expand(b, -1)
+    starts = torch.where(starts_here, frame, torch.full_like(frame, t + 1)).sort(dim=-1).values
+    starts = torch.where(starts == t + 1, torch.full_like(starts, -1), starts)
+    ends = torch.cat([starts[:, 1:], starts.new_full((b, 1), -1)], dim=1)
+    count = (starts >= 0).sum(-1)
+    frames = (alignment >= 0).sum(-1)
+    rows = torch.arange(b, device=dev)
+    has = count > 0
+    last = (count - 1).clamp_min(0)
+    ends[rows[has], last[has]] = frames[has]
+    return torch.stack([starts, ends], dim=-1)
+
+
+class CtcAligner:
+    """Forced alignment of ONE utterance on the host (numpy in, numpy out): the offline tool form of
+    ``ctc_forced_alignment`` (axlearn/audio/aligner/ctc_aligner.py:31-188)."""
+
+    def __init__(self, vocab_size: int, blank_id: int = 0):
+        if blank_id != 0:
+            raise ValueError("Only blank_id == 0 is supported.")
+        self.blank_id = blank_id
+        self.vocab_size = vocab_size
+
+    def _check_input(self, log_posterior, ground_truth) -> None:
+        import numpy as np
+
+        if log_posterior.ndim != 2:
+            raise ValueError(f"Expecting log_posterior is a 2-D tensor, but got {log_posterior.shape}.")
+        if log_posterior.shape[1] != self.vocab_size:
+            raise ValueError(f"Expecting vocab_size to be {self.vocab_size}, but got {log_posterior.shape[1]}.")
+        if ground_truth.ndim != 1:
+            raise ValueError(f"Expecting ground_truth is a 1-D tensor, but got {ground_truth.shape}.")
+        if ground_truth.dtype != np.int32:
+            raise ValueError(f"Ground_truth must have a int32 dtype, got {ground_truth.dtype}")
+        if ground_truth.size and (ground_truth.max() >= self.vocab_size or ground_truth.min() < 0):
+            raise ValueError(f"Ground truth label must be in range [0, {self.vocab_size}), "
+                             f"but we got [{ground_truth.min()}, {ground_truth.max()}].")
+
+    def align(self, log_posterior, ground_truth):
+        """``log_posterior [T, V]``, ``ground_truth [W]`` int32 -> ``[T]`` int32 frame labels, or
+        None when the labels do not fit the frames."""
+        import numpy as np
+
+        self._check_input(log_posterior, ground_truth)
+        t, w = log_posterior.shape[0], ground_truth.shape[0]
+        out = ctc_forced_alignment(
+            log_pos=torch.from_numpy(np.asarray(log_posterior, dtype=np.float32))[None],
+            log_pos_paddings=torch.zeros(1, t, dtype=torch.bool),
+            labels=torch.from_numpy(ground_truth.astype(np.int64))[None].reshape(1, w),
+            label_paddings=torch.zeros(1, w, dtype=torch.bool), blank_id=self.blank_id)
+        if not torch.isfinite(out.alignment_score[0]):
+            return None
+        return out.alignment[0].numpy().astype(np.int32)
+
+    def alignment_to_boundary(self, alignment, ground_truth):
+        """``[2, W]``: row 0 the first frame of every label, row 1 the frame after its last one (a
+        label's span includes the blanks that follow it)."""
+        import numpy as np
+
+        ext = np.concatenate([alignment, np.array([self.blank_id], dtype=np.int32)])
+        shifted = np.roll(ext, 1)
+        mask = (shifted != ext) & (ext != self.blank_id)
+        if not np.array_equal(ext[mask], ground_truth):
+            raise ValueError(f"{alignment} is not a valid alignment for {ground_truth}")
+        start = np.where(mask)[0].astype(np.int32)
+        end = np.roll(start, -1)
+        if end.size:
+            end[-1] = alignment.shape[0]
+        return np.stack([start, end], axis=0)

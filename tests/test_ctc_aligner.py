@@ -73,3 +73,34 @@ def test_decoder_model_align_and_typed_summaries(tmp_path):
     import pytest
     with pytest.raises(ValueError):
         writer(2, {"bad": ImageSummary(torch.rand(8, 8))})
+
+
+def test_alignment_to_segments_and_host_aligner():
+    import numpy as np
+
+    from axlearn_b200.audio.aligner import CtcAligner, alignment_to_segments
+
+    seg = alignment_to_segments(torch.tensor([[0, 1, 1, 2, -1], [0, 0, 0, 0, 0], [3, 0, 3, 3, -1]]), blank_id=0)
+    assert seg[0].tolist() == [[1, 3], [3, 4], [-1, -1], [-1, -1], [-1, -1]]
+    assert seg[1].tolist() == [[-1, -1]] * 5
+    assert seg[2].tolist() == [[0, 2], [2, 4], [-1, -1], [-1, -1], [-1, -1]]
+
+    aligner = CtcAligner(vocab_size=4)
+    rng = np.random.default_rng(0)
+    logits = rng.normal(size=(8, 4)).astype(np.float32)
+    truth = np.array([2, 2, 1], dtype=np.int32)
+    # Make the intended path clearly the best one.
+    path = [2, 2, 0, 2, 1, 1, 0, 0]
+    for t, s in enumerate(path):
+        logits[t, s] += 10
+    log_post = logits - np.log(np.exp(logits).sum(-1, keepdims=True))
+    got = aligner.align(log_post, truth)
+    assert got.tolist() == path
+    boundary = aligner.alignment_to_boundary(got, truth)
+    assert boundary.tolist() == [[0, 3, 4], [3, 4, 8]]
+    assert aligner.align(log_post[:2], np.array([1, 2, 3], dtype=np.int32)) is None     # too few frames
+    import pytest as _pytest
+    with _pytest.raises(ValueError):
+        aligner.align(log_post, truth.astype(np.int64))
+    with _pytest.raises(ValueError):
+        aligner.alignment_to_boundary(got, np.array([1, 2], dtype=np.int32))
