@@ -95,3 +95,68 @@ def test_t5_encoder_decoder_matches_hugging_face_and_decodes_incrementally():
             cached_states=states, input_ids=tgt[:, t:t + 1], cross_attention_data=enc,
             cross_attention_logit_biases=cross_bias), is_training=False, method="extend_step")
         torch.testing.assert_close(step["logits"][:, 0], want[:, t], rtol=2e-3, atol=2e-3)
+
+
+def test_t5x_tree_converts_to_the_same_parameters_as_hugging_face():
+    """A T5X-layout tree built from a Hugging Face model's weights must convert to exactly the
+    parameters the Hugging Face converter gives (which is checked against ``transformers`` above)."""
+    import numpy as np
+    import pytest
+
+    transformers = pytest.importorskip("transformers")
+    from axlearn_b200.common.param_converter import t5_hf_to_encoder_decoder
+    from axlearn_b200.common.t5x_param_converter import parameters_from_t5x_encoder_decoder, t5x_to_hf_state_dict
+    from axlearn_b200.common.utils import flatten_items
+
+    hf_cfg = transformers.T5Config(vocab_size=40, d_model=16, d_kv=8, d_ff=24, num_layers=2, num_decoder_layers=3,
+                                   num_heads=2, feed_forward_proj="gated-gelu", tie_word_embeddings=False)
+    torch.manual_seed(1)
+    sd = transformers.T5ForConditionalGeneration(hf_cfg).state_dict()
+
+    def kernel(key):                    # HF Linear weight [out, in] -> T5X kernel [in, out], as numpy
+        return sd[key].t().contiguous().numpy()
+
+    def attention(prefix):
+        return {name: {"kernel": kernel(prefix + short + ".weight")}
+                for name, short in (("query", "q"), ("key", "k"), ("value", "v"), ("out", "o"))}
+
+    def mlp(prefix):
+        return {n: {"kernel": kernel(prefix + n + ".weight")} for n in ("wi_0", "wi_1", "wo")}
+
+    rel = "block.0.layer.0.SelfAttention.relative_attention_bias.weight"
+    t5x = {"token_embedder": {"embedding": sd["shared.weight"].numpy()},
+           "encoder": {"relpos_bias": {"rel_embedding": sd["encoder." + rel].t().numpy()},
+                       "encoder_norm": {"scale": sd["encoder.final_layer_norm.weight"].numpy()}},
+           "decoder": {"relpos_bias": {"rel_embedding": sd["decoder." + rel].t().numpy()},
+                       "decoder_norm": {"scale": sd["decoder.final_layer_norm.weight"].numpy()},
+                       "logits_dense": {"kernel": kernel("lm_head.weight")}}}
+    for i in range(2):
+        p = f"encoder.block.{i}.layer."
+        t5x["encoder"][f"layers_{i}"] = {
+            "attention": attention(p + "0.SelfAttention."), "pre_attention_layer_norm": {"scale": sd[p + "0.layer_norm.weight"].numpy()},
+            "mlp": mlp(p + "1.DenseReluDense."), "pre_mlp_layer_norm": {"scale": sd[p + "1.layer_norm.weight"].numpy()}}
+    for i in range(3):
+        p = f"decoder.block.{i}.layer."
+        t5x["decoder"][f"layers_{i}"] = {
+            "self_attention": attention(p + "0.SelfAttention."),
+            "pre_self_attention_layer_norm": {"scale": sd[p + "0.layer_norm.weight"].numpy()},
+            "encoder_decoder_attention": attention(p + "1.EncDecAttention."),
+            "pre_cross_attention_layer_norm": {"scale": sd[p + "1.layer_norm.weight"].numpy()},
+            "mlp": mlp(p + "2.DenseReluDense."), "pre_mlp_layer_norm": {"scale": sd[p + "2.layer_norm.weight"].numpy()}}
+    got = parameters_from_t5x_encoder_decoder(t5x, num_heads=2)
+    want = t5_hf_to_encoder_decoder(sd, num_heads=2, num_encoder_layers=2, num_decoder_layers=3)
+    got_flat, want_flat = dict(flatten_items(got)), dict(flatten_items(want))
+    assert set(got_flat) == set(want_flat)
+    for k, v in want_flat.items():
+        assert torch.equal(got_flat[k], v), k
+    # The query kernels carry the sqrt(head_dim) that T5X folds into their initialisation.
+    q = got["encoder"]["transformer"]["layer0"]["self_attention"]["attention"]["i_proj"]["q_proj"]["weight"]
+    np.testing.assert_allclose(q.reshape(16, 16).numpy(), t5x["encoder"]["layers_0"]["attention"]["query"]["kernel"] * 8 ** 0.5, rtol=1e-6)
+    state_dict, n_enc, n_dec = t5x_to_hf_state_dict(t5x)
+    assert (n_enc, n_dec) == (2, 3)
+    assert set(state_dict) == {k for k in sd if "embed_tokens" not in k}          # the embedding is stored once, as "shared"
+    with pytest.raises(ValueError, match="Unsupported layer"):
+        parameters_from_t5x_encoder_decoder({**t5x, "extra": {}}, num_heads=2)
+    bad = {**t5x, "encoder": {**t5x["encoder"], "layers_0": {**t5x["encoder"]["layers_0"], "mlp": {"wi": {}}}}}
+    with pytest.raises(ValueError, match="Unsupported layer"):
+        parameters_from_t5x_encoder_decoder(bad, num_heads=2)
