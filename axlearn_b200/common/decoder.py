@@ -286,6 +286,11 @@ class Decoder(BaseLayer):
     def sample_decode(self, *, input_batch: dict, **kwargs):
         return self.decoding.sample_decode(input_batch=input_batch, **kwargs)
 
+    def parameter_tree(self) -> dict:
+        """This decoder's parameters (for callers that run in a child's context, such as the decode
+        engine built behind ``sample_decode``)."""
+        return self.state
+
     def beam_search_decode(self, *, input_batch: dict, **kwargs):
         return self.decoding.beam_search_decode(input_batch=input_batch, **kwargs)
 

@@ -474,6 +474,13 @@ def sample_decode_with_decoder(decoder, *, input_batch: dict, num_decodes: int, 
         logits_modifier = scale if logits_modifier is None else logit_modifiers.chain(scale, logits_modifier)
     input_ids = _pad_to(prefix, max_sequence_length, cfg.pad_token_id)
     prefill_len = infer_initial_time_step(prefix, pad_id=cfg.pad_token_id) + 1
+    if cross_attention_data is None and prefix.is_cuda:
+        fast = _sample_decode_on_engine(
+            decoder, input_ids=input_ids, prefill_len=prefill_len, num_decodes=num_decodes,
+            max_sequence_length=max_sequence_length, logits_modifier=logits_modifier,
+            stop_decoding_condition=stop_decoding_condition, prng_key=prng_key)
+        if fast is not None:
+            return fast
     with torch.no_grad():
         states, out = decoder.prefill_states(
             time_step=prefill_len.to(torch.int32), input_batch={**input_batch, "input_ids": input_ids},
@@ -499,6 +506,46 @@ def sample_decode_with_decoder(decoder, *, input_batch: dict, num_decodes: int, 
         tokens_to_scores=_decoder_step_fn(decoder, logits_modifier=logits_modifier,
                                           cross_attention_data=cross_attention_data,
                                           cross_attention_logit_biases=cross_attention_logit_biases),
+        stop_decoding_condition=stop_decoding_condition or StopOnSubsequence([[cfg.eos_token_id]]),
+        num_decodes=num_decodes, prng_key=decode_key, max_decode_len=max_sequence_length - 1,
+        pad_id=cfg.pad_token_id, input_token_scores=init_scores)
+
+
+def _sample_decode_on_engine(decoder, *, input_ids: Tensor, prefill_len: Tensor, num_decodes: int,
+                             max_sequence_length: int, logits_modifier, stop_decoding_condition, prng_key):
+    """The same sampling loop with the CUDA-graph decode engine as its ``tokens -> scores``
+    function (paged KV cache inside the engine, one graph replay per token): used when the decoder
+    is the Fuji shape the engine implements, on one GPU.  Returns None otherwise."""
+    from axlearn_b200.inference import decode_engine
+
+    cfg = decoder.config
+    b = input_ids.shape[0]
+    engine = decode_engine.engine_for_decoder(decoder, batch=b * num_decodes, max_len=max_sequence_length)
+    if engine is None:
+        return None
+    longest = int(prefill_len.max().item())
+    prompts = input_ids[:, :max(longest, 1)].repeat_interleave(num_decodes, dim=0)
+    engine.prefill(prompts, lengths=prefill_len.repeat_interleave(num_decodes))
+    logits = engine.logits[::num_decodes].clone()                       # one row per prompt
+    lp = log_probs_from_logits(logits[:, None, :], logits_modifier=logits_modifier)[:, 0, :]
+    key = prng_key if prng_key is not None else prng.PRNGKey(0)
+    first_key, decode_key = prng.split(key, 2)
+    first = _categorical(first_key, lp)
+    rows = torch.arange(b, device=input_ids.device)
+    can_write = prefill_len < input_ids.shape[1]
+    input_ids = input_ids.clone()
+    input_ids[rows[can_write], prefill_len[can_write]] = first[can_write].to(input_ids.dtype)
+    init_scores = torch.zeros((b, max_sequence_length - 1), dtype=torch.float32, device=input_ids.device)
+    ok = can_write & (prefill_len - 1 < init_scores.shape[1])
+    init_scores[rows[ok], (prefill_len - 1)[ok]] = lp[rows, first][ok]
+
+    def tokens_to_scores(token_ids: Tensor, cache: Any):
+        step_logits = engine.step_logits(token_ids[:, 0])
+        return log_probs_from_logits(step_logits[:, None, :], logits_modifier=logits_modifier)[:, 0, :], cache
+
+    return sample_decode(
+        inputs=input_ids, time_step=prefill_len.clamp(max=max_sequence_length - 1), cache={},
+        tokens_to_scores=tokens_to_scores,
         stop_decoding_condition=stop_decoding_condition or StopOnSubsequence([[cfg.eos_token_id]]),
         num_decodes=num_decodes, prng_key=decode_key, max_decode_len=max_sequence_length - 1,
         pad_id=cfg.pad_token_id, input_token_scores=init_scores)

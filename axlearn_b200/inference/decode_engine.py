@@ -141,6 +141,9 @@ class DecodeEngine:
             batch, self.max_pages)
         self.lengths = torch.zeros(batch, dtype=torch.int32, device=self.device)
         self.tokens = torch.zeros(batch, dtype=torch.int64, device=self.device)
+        # Logits of the latest position (a fixed buffer: the captured step writes into it, and a
+        # sampler outside the graph reads it).
+        self.logits = torch.zeros(batch, dims.vocab_size, dtype=torch.float32, device=self.device)
         self.splits = decode_ops.default_splits(batch, self.nkv_l, self.nq_l // self.nkv_l, self.max_len, page_size)
         self._scratch = torch.empty(
             max(1, decode_ops._lib().axb_decode_attn_scratch_floats(batch, self.nq_l, self.splits)),  # pylint: disable=protected-access
@@ -175,9 +178,11 @@ class DecodeEngine:
 
     # ------------------------------------------------------------------ prefill
     @torch.no_grad()
-    def prefill(self, prompt_ids: Tensor) -> Tensor:
-        """Runs the prompts ``[batch, T]`` (all of length T), fills the caches and returns the
-        first generated token of every sequence ``[batch]``."""
+    def prefill(self, prompt_ids: Tensor, lengths: Optional[Tensor] = None) -> Tensor:
+        """Runs the prompts ``[batch, T]``, fills the caches and returns the greedy first token of
+        every sequence ``[batch]`` (its logits stay in ``self.logits``).  ``lengths [batch]``:
+        right-padded prompts of different lengths (the padding's cache entries are overwritten
+        as decoding proceeds); None = all of length T."""
         d = self.dims
         b, t = prompt_ids.shape
         assert b == self.batch and t <= self.max_len
@@ -212,10 +217,19 @@ class DecodeEngine:
                 if self.world > 1:
                     dist.all_reduce(dn, group=self.group)
                 x = x + dn
-            last_hidden[b0:b1] = x[:, -1]
-        self.lengths.fill_(t)
-        logits = self._logits(last_hidden)
-        self.tokens.copy_(logits.argmax(dim=-1))
+            if lengths is None:
+                last_hidden[b0:b1] = x[:, -1]
+            else:
+                idx = (lengths[b0:b1].long() - 1).clamp(min=0)
+                last_hidden[b0:b1] = x[torch.arange(b1 - b0, device=self.device), idx]
+        if lengths is None:
+            self.lengths.fill_(t)
+        else:
+            self.lengths.copy_(lengths.to(self.lengths.dtype))
+        self.logits.copy_(self._logits(last_hidden))
+        self.tokens.copy_(self.logits.argmax(dim=-1))
+        if self.device.type == "cuda":
+            cuda_ops.check_status(self.device)
         return self.tokens.clone()
 
     def _logits(self, hidden: Tensor) -> Tensor:
@@ -228,7 +242,7 @@ class DecodeEngine:
         its K/V, and leaves the next token in ``self.tokens``."""
         d = self.dims
         before = cuda_ops.launch_count
-        self.lengths.add_(1)
+        self.lengths.add_(1).clamp_(max=self.max_len)   # rows that ran out of room rewrite their last slot
         if self._allreduce is not None:
             self._allreduce.begin_step()
         x = self.w["emb"][self.tokens]                                        # [B, D]
@@ -252,8 +266,8 @@ class DecodeEngine:
                 x = self._gemm_reduce(act, lw.wdown, x, 2 * li + 1)
             else:
                 cuda_ops.gemm(act, lw.wdown, out=x, accumulate=True)
-        logits = self._logits(x)
-        self.tokens.copy_(logits.argmax(dim=-1))
+        self.logits.copy_(self._logits(x))
+        self.tokens.copy_(self.logits.argmax(dim=-1))
         self.launches_per_step = cuda_ops.launch_count - before
 
     @torch.no_grad()
@@ -261,6 +275,17 @@ class DecodeEngine:
         """Generates ``steps`` further tokens per sequence (after ``prefill``); returns them
         ``[batch, steps]``.  The first call captures the step in a CUDA graph."""
         out = torch.empty((self.batch, steps), dtype=torch.int64, device=self.device)
+        self._ensure_graph()
+        for i in range(steps):
+            if self._graph is not None:
+                self._graph.replay()
+            else:
+                self._step()
+            out[:, i] = self.tokens
+        cuda_ops.check_status(self.device)
+        return out
+
+    def _ensure_graph(self) -> None:
         if self._use_graph and self._graph is None:
             # Warm up on a side stream (lazy module loading, tensor-map encoding), restoring
             # the state the warm-up steps consumed, then capture.
@@ -279,16 +304,86 @@ class DecodeEngine:
                 self._step()
             self.lengths.copy_(saved[0])
             self.tokens.copy_(saved[1])
-        for i in range(steps):
-            if self._graph is not None:
-                self._graph.replay()
-            else:
-                self._step()
-            out[:, i] = self.tokens
-        return out
+
+    @torch.no_grad()
+    def step_logits(self, tokens: Tensor) -> Tensor:
+        """Feeds one token per sequence (``[batch]``: the token at each sequence's current end),
+        appends its K/V and returns the fp32 logits of the next position ``[batch, vocab]`` -- the
+        engine as a ``tokens -> scores`` function for samplers and searches that live outside."""
+        self._ensure_graph()
+        self.tokens.copy_(tokens.reshape(-1))
+        if self._graph is not None:
+            self._graph.replay()
+        else:
+            self._step()
+        return self.logits
 
     @torch.no_grad()
     def generate(self, prompt_ids: Tensor, max_new_tokens: int) -> Tensor:
         first = self.prefill(prompt_ids)
         rest = self.decode(max_new_tokens - 1) if max_new_tokens > 1 else first[:, :0]
         return torch.cat([first[:, None], rest], dim=1)
+
+
+# ------------------------------------------------------------------------------------------
+# The engine behind the framework's decoding API.
+# ------------------------------------------------------------------------------------------
+
+_ENGINES: dict = {}
+
+
+def dims_from_decoder(decoder) -> Optional[FujiDims]:
+    """``FujiDims`` of a ``Decoder`` whose stack is the Fuji / Llama shape this engine implements
+    (repeated pre-norm layers, RMSNorm, RoPE on q / k, fused QKV, SwiGLU, no biases); None for
+    anything else."""
+    try:
+        cfg = decoder.config
+        stack = cfg.transformer
+        layer = stack.layer
+        attn = layer.self_attention.attention
+        ff = layer.feed_forward
+        qkv = attn.input_linear
+        rope = qkv.rope_pos_emb_layer
+        inner = qkv.input_linear
+        if layer.self_attention.structure != "prenorm" or ff.structure != "prenorm":
+            return None
+        if tuple(ff.activation) != ("nn.silu", "linear") or getattr(layer, "cross_attention", None) is not None:
+            return None
+        if "RMSNorm" not in layer.self_attention.norm.klass.__name__ or cfg.output_norm is None:
+            return None
+        num_heads = attn.num_heads
+        num_kv = getattr(inner, "num_kv_heads", None) or num_heads
+        state = decoder.parameter_tree()
+        w_gate = _get(state, "transformer/repeat/layer/feed_forward/linear1_0/weight")
+        return FujiDims(num_layers=stack.num_layers, hidden_dim=cfg.dim, num_heads=num_heads, num_kv_heads=num_kv,
+                        head_dim=cfg.dim // num_heads, ffn_dim=w_gate.shape[-1], vocab_size=cfg.vocab_size,
+                        rope_theta=float(rope.theta), norm_eps=float(layer.self_attention.norm.eps))
+    except (AttributeError, KeyError, TypeError):
+        return None
+
+
+def engine_for_decoder(decoder, *, batch: int, max_len: int) -> Optional["DecodeEngine"]:
+    """A (cached) engine over the decoder's current parameters, or None when the decoder, its
+    placement or its shapes are outside what the engine implements."""
+    from axlearn_b200.parallel.mesh import current_mesh
+
+    if os.environ.get("AXB200_DECODE_ENGINE", "1") == "0":
+        return None
+    mesh = current_mesh()
+    if mesh is not None and mesh.size > 1:
+        return None
+    dims = dims_from_decoder(decoder)
+    if dims is None or dims.head_dim != 128:
+        return None
+    state = decoder.parameter_tree()
+    emb = _get(state, "emb/token_emb/weight")
+    if not emb.is_cuda or emb.dtype != torch.bfloat16:
+        return None
+    key = (id(decoder), batch, max_len, emb.data_ptr())
+    engine = _ENGINES.get(key)
+    if engine is None:
+        _ENGINES.clear()          # one resident engine: its caches and weight copies are large
+        weights = weights_from_fuji_state({"decoder": state}, dims, device=emb.device)
+        engine = DecodeEngine(weights, dims, batch=batch, max_len=max_len, device=emb.device)
+        _ENGINES[key] = engine
+    return engine

@@ -160,3 +160,60 @@ def test_decode_engine_matches_model_forward(num_kv_heads, use_graph):
             row = logits[b, t + i - 1].float().cpu()
             # The engine's pick is the reference argmax up to bf16 noise between near-ties.
             assert row.max() - row[tokens[b, i]] < 0.1 * max(1.0, row.std().item()), (b, i)
+
+
+def test_sample_decode_api_runs_on_the_engine_and_matches_the_eager_path(monkeypatch):
+    """``Model.sample_decode`` on a Fuji-shaped bf16 model on one GPU goes through the CUDA-graph
+    engine; with deterministic sampling (top-k = 1) its tokens are those of the eager
+    ``prefill_states`` / ``extend_step`` path, ragged prompts and two decodes per prompt included."""
+    from axlearn_b200.common import decoding, logit_modifiers, prng
+    from axlearn_b200.common.module import functional
+    from axlearn_b200.common.utils import tree_map
+    from axlearn_b200.inference import decode_engine
+    from axlearn_b200.ops import cuda_ops
+
+    model, params = _tiny_model(1)
+    params = tree_map(lambda t: t.cuda().bfloat16() if t.is_floating_point() else t.cuda(), params)
+    g = torch.Generator().manual_seed(3)
+    prefix = torch.randint(2, 512, (3, 24), generator=g)
+    prefix[1, 17:] = 0            # shorter prompts are right-padded with the pad id
+    prefix[2, 9:] = 0
+    calls = {"n": 0}
+    real = decode_engine.DecodeEngine.step_logits
+
+    def counted(self, tokens):
+        calls["n"] += 1
+        return real(self, tokens)
+
+    monkeypatch.setattr(decode_engine.DecodeEngine, "step_logits", counted)
+    kwargs = dict(input_batch={"prefix": prefix.cuda()}, num_decodes=2, max_sequence_length=40,
+                  logits_modifier=logit_modifiers.top_k_logits(1),
+                  stop_decoding_condition=decoding.StopOnSubsequence([[511]]))
+    fast, _ = functional(model, prng.PRNGKey(5), params, kwargs, is_training=False, method="sample_decode")
+    assert calls["n"] > 0, "the engine was not used"
+    torch.cuda.synchronize()
+    cuda_ops.check_status()
+    monkeypatch.setenv("AXB200_DECODE_ENGINE", "0")
+    before = calls["n"]
+    slow, _ = functional(model, prng.PRNGKey(5), params, kwargs, is_training=False, method="sample_decode")
+    assert calls["n"] == before
+    assert fast.sequences.shape == slow.sequences.shape == (3, 2, 39)
+    assert torch.equal(fast.sequences[:, :, :8], slow.sequences[:, :, :8])          # the prompts
+    # With top-k = 1 every generated token must be the argmax of the model's own logits for the
+    # sequence so far, up to bf16 noise between near-ties (a random model has many of those, so
+    # the two paths may part ways at a tie and are therefore not compared token by token).
+    lengths = (prefix != 0).sum(-1)
+    for out in (fast, slow):
+        full = torch.cat([prefix[:, :1].cuda().repeat_interleave(2, dim=0), out.sequences.reshape(6, 39)], dim=1)
+        logits, _ = functional(model, prng.PRNGKey(1), params, dict(input_batch={"input_ids": full}),
+                               is_training=False, method="extract_logits")
+        for row in range(6):
+            start = int(lengths[row // 2])
+            for t in range(start, 40):
+                tok = int(full[row, t])
+                if tok == 0:
+                    break
+                ref = logits[row, t - 1].float()
+                assert ref.max() - ref[tok] < 0.15 * max(1.0, ref.std().item()), (row, t)
+    same = (fast.sequences == slow.sequences).float().mean().item()
+    assert same > 0.5, same
