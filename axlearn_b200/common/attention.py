@@ -312,6 +312,7 @@ class _FusedQKVProj(DenseGeneralBaseLayer):
         w = coll.unshard_param(self.parameters["weight"], spec, compute_shape=cshape)
         if coll.has_axis(spec[2] if spec else None, "model"):
             x = coll.psum_grad(x, "model")
+        x = ops.share_input_grad(x)      # the three projections sum their input gradients in place
         outs = []
         for p in range(3):
             y = self._matmul(x, w[p].reshape(cshape[1], -1).to(x.dtype))
@@ -1276,6 +1277,13 @@ def scaled_hidden_dim(scale: float = 4, *, round_up_to_multiples_of: Optional[in
     return config_for_function(scale_fn).set(scale=scale, round_up_to_multiples_of=round_up_to_multiples_of)
 
 
+def _first_model_axis(linear) -> Any:
+    """Output-dim entry of a linear's partition spec (tensor parallel layers route their input
+    through a gradient all-reduce, which makes a new tensor per linear)."""
+    spec = getattr(linear.config, "param_partition_spec", None)
+    return spec[-1] if spec else None
+
+
 class TransformerFeedForwardLayer(BaseLayer):
     """Norm + MLP + residual.  ``activation`` is a name, or a pair of names for a gated MLP
     (children ``linear1_0`` / ``linear1_1``): SwiGLU = ("nn.silu", "linear")."""
@@ -1331,6 +1339,8 @@ class TransformerFeedForwardLayer(BaseLayer):
     def _mlp(self, x: Tensor) -> Tensor:
         cfg = self._config
         if isinstance(cfg.activation, (tuple, list)):
+            if not coll.has_axis(_first_model_axis(self.linear1_0), "model"):
+                x = ops.share_input_grad(x)  # both halves sum their input gradients in place
             with remat.tagged(self, "linear1_0"):
                 a0 = self._remat_name(self.linear1_0(x), "linear1_0")
             with remat.tagged(self, "linear1_1"):

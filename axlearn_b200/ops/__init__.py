@@ -15,6 +15,7 @@ from axlearn_b200.ops.dispatch import (  # noqa: F401
     add_rms_norm,
     rms_norm,
     rms_norm_keep_input,
+    share_input_grad,
     rope,
     swiglu,
     use_reference_ops,

@@ -256,10 +256,33 @@ def _is_nk_view(w: torch.Tensor) -> bool:
     return w.stride(0) == 1 and w.stride(1) != 1
 
 
+class _SharedInputGrad:
+    """Input-gradient buffer shared by the linears that read the same activation (q / k / v, the
+    two halves of a gated feed-forward): the first backward allocates it, the others add their
+    ``dy @ w^T`` into it from the GEMM epilogue, and only the first returns it to autograd -- no
+    separate add kernels.  Valid only when the marked tensor feeds nothing but such linears."""
+
+    __slots__ = ("buf",)
+
+    def __init__(self):
+        self.buf = None
+
+
+def share_input_grad(x: torch.Tensor) -> torch.Tensor:
+    """Marks ``x`` (a fresh alias of it) as the common input of several kernel linears; see
+    ``_SharedInputGrad``.  A no-op for tensors the GEMM kernel does not take."""
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and x.requires_grad and x.shape[-1] % 8 == 0):
+        return x
+    y = x.view_as(x)
+    y._axb_shared_dx = _SharedInputGrad()  # pylint: disable=protected-access
+    return y
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w):  # x: [..., K], w: [K, N] (any strides)
         ctx.save_for_backward(x, w)
+        ctx.shared_dx = getattr(x, "_axb_shared_dx", None)
         x2 = x.reshape(-1, x.shape[-1])
         info = _fused_fsdp_info(w)
         if info is not None and not (info.gathered and info.carry is None):
@@ -286,7 +309,14 @@ class _Linear(torch.autograd.Function):
         x2 = x.reshape(-1, x.shape[-1])
         dx = dw = None
         if ctx.needs_input_grad[0]:
-            dx = gemm(dy2, w.t()).reshape(x.shape)
+            shared = getattr(ctx, "shared_dx", None)
+            if shared is None:
+                dx = gemm(dy2, w.t()).reshape(x.shape)
+            elif shared.buf is None:
+                shared.buf = gemm(dy2, w.t())
+                dx = shared.buf.reshape(x.shape)
+            else:
+                gemm(dy2, w.t(), out=shared.buf, accumulate=True)   # autograd already holds the buffer
         if ctx.needs_input_grad[1]:
             info = _fused_fsdp_info(w)
             if info is not None:
@@ -319,6 +349,7 @@ class _LinearKept(_Linear):
     @staticmethod
     def forward(ctx, x, w, y):  # pylint: disable=arguments-differ
         ctx.save_for_backward(x, w)
+        ctx.shared_dx = getattr(x, "_axb_shared_dx", None)
         return y.view_as(y)
 
     @staticmethod

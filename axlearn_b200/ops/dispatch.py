@@ -71,6 +71,15 @@ def add_rms_norm(x, r, scale, eps: float, *, upcast: bool = False):
     return total, rms_norm(total, scale, eps, upcast=upcast)
 
 
+def share_input_grad(x):
+    """Marks ``x`` as the common input of several linears whose input gradients the kernels then
+    sum in the GEMM epilogue (no add kernels); identity elsewhere.  Use only where ``x`` feeds
+    nothing but those linears."""
+    if _cuda(x) and x.dtype == torch.bfloat16 and x.requires_grad:
+        return _ops().share_input_grad(x)
+    return x
+
+
 def swiglu(gate, up):
     if _cuda(gate, up) and gate.dtype == torch.bfloat16:
         return _ops().swiglu(gate, up)

@@ -48,6 +48,8 @@ def _args():
     ap.add_argument("--per_gpu_batch", type=int, default=4)
     ap.add_argument("--layers", type=int, default=None, help="debug only: override layer count")
     ap.add_argument("--skip_e2e", action="store_true")
+    ap.add_argument("--mesh", default=None, help="non-headline: mesh axes instead of fsdp=N, e.g. 'fsdp=4,model=2' "
+                    "(the product of the sizes must be --gpus; the batch is per data-parallel rank)")
     ap.add_argument("--kernel_table", default=None, help="after the timed regions, profile two more steps with the "
                     "torch profiler and write per-kernel device-time shares to this file (rank 0)")
     ap.add_argument("--skip_parity", action="store_true", help="N>1: skip the one-step fused-vs-library parity record")
@@ -145,10 +147,10 @@ def main():
 
     moe = args.family == "envy"
     parity = None
-    if world > 1 and use_cuda and not moe and not args.skip_parity:
+    if world > 1 and use_cuda and not moe and not args.skip_parity and not args.mesh:
         parity = _fused_vs_library_parity(args, world, local_rank)
     trainer, mk = _build_trainer(args, world, local_rank, use_cuda, layers=args.layers, per_gpu_batch=args.per_gpu_batch)
-    global_batch = args.per_gpu_batch * world
+    global_batch = args.per_gpu_batch * _data_ranks(args, world, moe)
     num_params = sum(t.numel() for t in _leaves(trainer.trainer_state["model"]))
     data = iter(trainer.input.dataset())
     dev = torch.device("cuda", local_rank) if use_cuda else torch.device("cpu")
@@ -249,7 +251,8 @@ def main():
                 "model": (f"envy-{args.model}" if moe else f"fuji-{args.model}-v2") + (
                     f"-{args.layers}layers-DEBUG" if args.layers else ""),
                 "global_batch": global_batch, "seq_len": args.seq,
-                "parallelism": f"expert{world} (dense parameters sharded over the same axis)" if moe else f"fsdp{world}",
+                "parallelism": (args.mesh.replace("=", "").replace(",", "x") + " (non-headline mesh)") if args.mesh else (
+                    f"expert{world} (dense parameters sharded over the same axis)" if moe else f"fsdp{world}"),
                 "remat": "full per layer", "optimizer": "clip_by_global_norm(1)+adamw_decoupled, fp32 master+moments",
                 "l2": "per-step working set (>100 GB of parameters, moments and activations) exceeds the 126 MB L2",
             },
@@ -299,9 +302,10 @@ def _build_trainer(args, world, local_rank, use_cuda, *, layers, per_gpu_batch):
     cfg = get_trainer_config_fn(
         model_cfg=model_cfg,
         learner_cfg=adamw_decoupled_learner_config(max_step=kw["max_step"], **kw["learner_kwargs"]),
-        max_step=kw["max_step"], train_batch_size=per_gpu_batch * world, max_sequence_length=args.seq,
+        max_step=kw["max_step"], train_batch_size=per_gpu_batch * _data_ranks(args, world, moe),
+        max_sequence_length=args.seq,
         vocab_size=mk.get("vocab_size", 32768),
-        mesh_shape=mesh_shape_from_axes(**({"expert": world} if moe else {"fsdp": world})),
+        mesh_shape=mesh_shape_from_axes(**_mesh_axes(args, world, moe)),
         mesh_axis_names=MESH_AXIS_NAMES,
         train_dtype=torch.bfloat16)()
     if args.fp8:
@@ -313,6 +317,27 @@ def _build_trainer(args, world, local_rank, use_cuda, *, layers, per_gpu_batch):
     trainer = cfg.instantiate(parent=None)
     trainer.init(prng.PRNGKey(0))
     return trainer, mk
+
+
+def _mesh_axes(args, world: int, moe: bool) -> dict:
+    if args.mesh:
+        axes = {k: int(v) for k, v in (item.split("=") for item in args.mesh.split(","))}
+        size = 1
+        for v in axes.values():
+            size *= v
+        assert size == world, f"--mesh {args.mesh} has {size} ranks but --gpus is {world}"
+        return axes
+    return {"expert": world} if moe else {"fsdp": world}
+
+
+def _data_ranks(args, world: int, moe: bool) -> int:
+    """Ranks that hold different data (everything but the model / pipeline / seq axes)."""
+    axes = _mesh_axes(args, world, moe)
+    n = 1
+    for k, v in axes.items():
+        if k in ("data", "expert", "fsdp"):
+            n *= v
+    return n
 
 
 def _fused_vs_library_parity(args, world, local_rank) -> dict:
