@@ -176,9 +176,13 @@ class MultiheadOutputLinear(DenseGeneralBaseLayer):
         cshape = coll.compute_shape(full, spec)
         w = coll.unshard_param(self.parameters["weight"], spec, compute_shape=cshape)
         w2 = w.reshape(cshape[0], -1).to(x.dtype)  # [D, N*H]
-        y = self._matmul(x.reshape(x.shape[:-2] + (-1,)), w2.t())
-        if coll.has_axis(spec[1] if spec else None, "model"):
-            y = coll.psum(y, "model")
+        x2 = x.reshape(x.shape[:-2] + (-1,))
+        row_parallel = coll.has_axis(spec[1] if spec else None, "model")
+        y = coll.row_parallel_linear(x2, w2.t(), "model") if row_parallel and self._plain_matmul() else None
+        if y is None:
+            y = self._matmul(x2, w2.t())
+            if row_parallel:
+                y = coll.psum(y, "model")
         if cfg.bias:
             y = y + self.parameters["bias"].to(y.dtype)
         return y

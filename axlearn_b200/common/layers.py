@@ -342,6 +342,11 @@ class DenseGeneralBaseLayer(BaseLayer):
         if cfg.quantized_dot_general is not None:
             self._add_child("quantized_dot_general", cfg.quantized_dot_general)
 
+    @nowrap
+    def _plain_matmul(self) -> bool:
+        """True when products of this layer are ordinary bf16 GEMMs (no quantised path)."""
+        return "quantized_dot_general" not in self._children
+
     def _matmul(self, x: Tensor, w: Tensor) -> Tensor:
         """``x[..., K] @ w[K, N]`` routed through the quantised path when configured."""
         if "quantized_dot_general" in self._children:
@@ -391,9 +396,12 @@ class Linear(DenseGeneralBaseLayer):
         row_parallel = coll.has_axis(_spec_entry(spec, 0), "model")
         if col_parallel:
             x = coll.psum_grad(x, "model")
-        y = self._matmul(x, w.to(x.dtype) if w.dtype != x.dtype else w)
-        if row_parallel:
-            y = coll.psum(y, "model")
+        wx = w.to(x.dtype) if w.dtype != x.dtype else w
+        y = coll.row_parallel_linear(x, wx, "model") if row_parallel and self._plain_matmul() else None
+        if y is None:
+            y = self._matmul(x, wx)
+            if row_parallel:
+                y = coll.psum(y, "model")
         if cfg.bias:
             b = self.parameters["bias"]
             b = coll.unshard_param(b, (_spec_entry(spec, -1),) if spec else None,

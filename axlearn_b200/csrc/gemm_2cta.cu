@@ -378,10 +378,16 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       // checks that a 32-row block never straddles two owners).
       const CUtensorMap* out_map = &tmap_c;
       int out_row = row0;
+      // rs_mode 1 (all-reduce push): the tile goes to slot `rs_rank` of EVERY peer's staging.
+      const int n_dst = (FUSED && f.rs_world > 1 && f.rs_mode == 1) ? f.rs_world : 1;
       if (FUSED && f.rs_world > 1 && row0 < p.M) {
-        const int owner = row0 / f.rs_rows_per_rank;
-        out_map = &rs_maps.m[owner];
-        out_row = f.rs_rank * f.rs_rows_per_rank + (row0 - owner * f.rs_rows_per_rank);
+        if (f.rs_mode == 1) {
+          out_row = f.rs_rank * p.M + row0;
+        } else {
+          const int owner = row0 / f.rs_rows_per_rank;
+          out_map = &rs_maps.m[owner];
+          out_row = f.rs_rank * f.rs_rows_per_rank + (row0 - owner * f.rs_rows_per_rank);
+        }
       }
 #pragma unroll 1
       for (int ch = 0; ch < kChunks; ++ch) {
@@ -426,10 +432,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         fence_proxy_async();
         __syncwarp();
         if (lane == 0 && row0 < p.M && n0 + ch * kChunkCols < p.N) {
-          if (p.accumulate)
+          if (n_dst > 1) {
+            for (int d = 0; d < n_dst; ++d) tma_store_2d(&rs_maps.m[d], tile, n0 + ch * kChunkCols, out_row);
+          } else if (p.accumulate) {
             tma_reduce_add_2d(out_map, tile, n0 + ch * kChunkCols, out_row);
-          else
+          } else {
             tma_store_2d(out_map, tile, n0 + ch * kChunkCols, out_row);
+          }
         }
         if (lane == 0) tma_store_commit();
         ++store_seq;
@@ -446,6 +455,19 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       if (FUSED && f.rs_world > 1) __threadfence_system();
     }
     __syncwarp();
+    if (FUSED && f.rs_world > 1 && f.rs_mode == 1) {
+      // All four epilogue warps of this CTA are past their fences; the last CTA of the grid raises
+      // this rank's flag on every peer.
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) {
+        if (atomicAdd(f.rs_counter, 1) == static_cast<int>(gridDim.x) - 1) {
+          *f.rs_counter = 0;
+          __threadfence_system();
+          const int epoch = *reinterpret_cast<const volatile int*>(f.rs_epoch_ptr);
+          for (int r = 0; r < f.rs_world; ++r) st_release_sys(f.rs_flags[r] + f.rs_site * f.rs_world + f.rs_rank, epoch);
+        }
+      }
+    }
   }
 
   // ---------------------------------------------------------------------- tear-down
@@ -508,7 +530,8 @@ static int launch_gemm2(const void* A, const void* B, void* C, int M, int N, int
   PeerMaps maps = no_maps;
   if (scatter) {
     for (int r = 0; r < fp.rs_world; ++r) {
-      uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(fp.rs_world) * fp.rs_rows_per_rank};
+      const uint64_t slot_rows = fp.rs_mode == 1 ? static_cast<uint64_t>(M) : static_cast<uint64_t>(fp.rs_rows_per_rank);
+      uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(fp.rs_world) * slot_rows};
       rc = make_tensor_map(&maps.m[r], c_type, 2, fp.rs_dst[r], dims, c_strides, c_box, CU_TENSOR_MAP_SWIZZLE_128B);
       if (rc != 0) return rc;
     }
@@ -577,7 +600,9 @@ extern "C" int axb_gemm_bf16_fused_2cta(const void* A, const void* B, void* C, i
   using namespace axb;
   const FusedParams* fp = static_cast<const FusedParams*>(fused);
   if (M < 2 * k2TileM || N < k2TileN || ((M + k2TileM - 1) / k2TileM) * ((N + k2TileN - 1) / k2TileN) < 64) return -20;
-  if (fp->rs_world > 1 && (fp->rs_mode != 0 || (fp->rs_rows_per_rank % 32) != 0)) return -20;
+  if (fp->rs_world > 1 && fp->rs_mode == 0 && (fp->rs_rows_per_rank % 32) != 0) return -20;
+  if (fp->rs_world > 1 && fp->rs_mode == 1 && ((M % 32) != 0 || fp->rs_counter == nullptr || fp->rs_epoch_ptr == nullptr))
+    return -20;
   if (fp->rs_world <= 1 && (reinterpret_cast<uintptr_t>(C) & 15)) return -10;
 #define AXB_FUSED2_CASE(AM, BM)                                                                                  \
   if (a_mn_major == (AM ? 1 : 0) && b_mn_major == (BM ? 1 : 0))                                                  \

@@ -175,6 +175,10 @@ def psum(x: torch.Tensor, axes: AxisSpec) -> torch.Tensor:
     group, world, _ = _group(axes)
     if world == 1:
         return x
+    from axlearn_b200.parallel import peer_allreduce
+
+    if peer_allreduce.usable(x, group, world):
+        return peer_allreduce.psum(x, group)
     return _AllReduce.apply(x, group)
 
 
@@ -183,7 +187,22 @@ def psum_grad(x: torch.Tensor, axes: AxisSpec) -> torch.Tensor:
     group, world, _ = _group(axes)
     if world == 1:
         return x
+    from axlearn_b200.parallel import peer_allreduce
+
+    if peer_allreduce.usable(x, group, world):
+        return peer_allreduce.psum_grad(x, group)
     return _IdentityFwdAllReduceBwd.apply(x, group)
+
+
+def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, axes: AxisSpec) -> Optional[torch.Tensor]:
+    """``psum(x @ w, axes)`` with the reduction's stores fused into the GEMM epilogue (peer
+    memory), or None when that path does not apply."""
+    group, world, _ = _group(axes)
+    if world == 1:
+        return None
+    from axlearn_b200.parallel import peer_allreduce
+
+    return peer_allreduce.row_parallel_linear(x, w, group, world)
 
 
 def all_gather(x: torch.Tensor, axes: AxisSpec, *, dim: int = 0) -> torch.Tensor:

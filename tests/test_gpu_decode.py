@@ -93,12 +93,13 @@ def test_one_shot_all_reduce_emulated():
     cuda_ops.check_status()
 
 
-def test_gemm_with_all_reduce_push_epilogue_emulated():
-    """Two emulated ranks: each rank's GEMM stores its rows into both staging buffers and raises
-    the flags itself; the finish kernels then see residual + the sum of both products."""
+@pytest.mark.parametrize("world,m,k,n", [(2, 64, 256, 512), (2, 4096, 512, 1024), (4, 2048, 256, 2048)])
+def test_gemm_with_all_reduce_push_epilogue_emulated(world, m, k, n):
+    """Emulated ranks: each rank's GEMM stores its rows into every staging buffer and raises the
+    flags itself; the finish kernels then see residual + the sum of the products.  The small case
+    runs on the single-CTA kernel, the large ones on the CTA-pair kernel (TMA stores per peer)."""
     from axlearn_b200.ops import cuda_ops, decode_ops
 
-    world, m, k, n = 2, 64, 256, 512
     ranks = [decode_ops.OneShotAllReduce(m * n, 2, device="cuda", peers=[None] * world, rank=r) for r in range(world)]
     for r in ranks:
         r.connect(ranks)

@@ -98,3 +98,70 @@ def test_fused_fsdp_matches_library_collectives(tmp_path):
             if max(per_layer) >= 3e-2:
                 bad.append((path, per_layer))
         assert not bad, (rank, bad)
+
+
+def _run_tp(rank, world, port, directory, peer, big, queue):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), AXB200_TP_PEER="1" if peer else "0", NCCL_NVLS_ENABLE="0")
+    sys.path.insert(0, REPO)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from axlearn_b200.common import prng
+        from axlearn_b200.common.base_layer import RematSpec, nothing_saveable
+        from axlearn_b200.common.utils import flatten_items
+        from axlearn_b200.experiments.text.gpt.common import mesh_shape_from_axes
+        from axlearn_b200.ops import cuda_ops
+        from tests.helpers import tiny_fuji_trainer_config
+
+        dims = dict(hidden=1024, heads=8, ffn=2048, seq=1024) if big else dict(hidden=512, heads=4, ffn=1024, seq=256)
+        cfg = tiny_fuji_trainer_config(
+            os.path.join(directory, f"tp_{'peer' if peer else 'nccl'}_{rank}"), max_step=4, save_every_n_steps=1000,
+            train_dtype=torch.bfloat16, device=f"cuda:{rank}", mesh_shape=mesh_shape_from_axes(model=world),
+            vocab=4096, batch=4, layers=2, scan_chunk=512, shared_lm_head=True, **dims)
+        cfg.model.decoder.transformer.layer.remat_spec = RematSpec(prevent_cse=False, policy=nothing_saveable)
+        trainer = cfg.instantiate(parent=None)
+        trainer.init(prng.PRNGKey(0))
+        data = iter(trainer.input.dataset())
+        losses = []
+        for _ in range(3):
+            losses.append(trainer.train_step(next(data))["loss"].item())
+        torch.cuda.synchronize()
+        cuda_ops.check_status()
+        stacked = trainer.trainer_state["model"]["decoder"]["transformer"]["repeat"]["layer"]
+        w = {p: t.float().cpu() for p, t in flatten_items(stacked) if "linear2" in p or "o_proj" in p}
+        queue.put(to_plain((rank, losses, w, cuda_ops.launch_count)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("big", [False, True])
+def test_tensor_parallel_peer_reductions_match_library_all_reduce(tmp_path, big):
+    """model=2: reductions over peer memory (GEMM-epilogue stores + one summing kernel) against NCCL
+    all-reduces, three training steps from the same initial state."""
+    world = 2
+    results = {}
+    for peer in (False, True):
+        ctx = mp.get_context("spawn")
+        q = ctx.Queue()
+        port = _free_port()
+        procs = [ctx.Process(target=_run_tp, args=(r, world, port, str(tmp_path), peer, big, q)) for r in range(world)]
+        for p in procs:
+            p.start()
+        got = {}
+        for _ in range(world):
+            rank, losses, w, launches = from_plain(q.get(timeout=600))
+            got[rank] = (losses, w, launches)
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0
+        results[peer] = got
+    for rank in range(world):
+        ref_losses, ref_w, ref_launches = results[False][rank]
+        losses, w, launches = results[True][rank]
+        assert launches > ref_launches, "the peer path must launch its own push / sum kernels"
+        for a, b in zip(losses, ref_losses):
+            assert abs(a - b) < 5e-3 * abs(b), (losses, ref_losses)
+        for path, t in w.items():
+            assert (t - ref_w[path]).abs().max() < 2e-2 * ref_w[path].abs().max() + 1e-6, path
