@@ -64,37 +64,52 @@ struct FlashBwdFusedParams {
 };
 
 // delta = rowsum(dO * O) and lse2 = lse * log2(e), both padded to Tp rows per (batch, head).
+// H / 8 lanes share a row (one 16-byte load of O and of dO each), so a warp covers 32 / (H / 8) rows
+// per trip with full-width loads.  H / 8 must be a power of two not above 32.
 __global__ void flash_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                       const float* __restrict__ lse, float* __restrict__ lse2,
                                       float* __restrict__ delta, int B, int T, int Tp, int N, int H) {
   const int64_t rows = static_cast<int64_t>(B) * Tp * N;
   const int lane = threadIdx.x & 31;
-  for (int64_t r = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5; r < rows;
-       r += (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5) {
-    const int n = r % N;
-    const int64_t bt = r / N;
-    const int t = bt % Tp;
+  const int lpr = H / 8;                 // lanes per row
+  const int rpw = 32 / lpr;              // rows per warp and trip
+  const int sub = lane / lpr, col = lane % lpr;
+  const int64_t warp = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+  const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  for (int64_t base = warp * rpw; base < rows; base += warps * rpw) {
+    const int64_t r = base + sub;
+    const bool live = r < rows;
+    const int n = live ? static_cast<int>(r % N) : 0;
+    const int64_t bt = live ? r / N : 0;
+    const int t = static_cast<int>(bt % Tp);
     const int64_t b_ = bt / Tp;
     const int64_t dst = (b_ * N + n) * Tp + t;
-    if (t >= T) {
-      if (lane == 0) lse2[dst] = INFINITY, delta[dst] = 0.f;
-      continue;
-    }
-    const int64_t src_row = (b_ * T + t) * N + n;
-    const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(o + src_row * H);
-    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(d_o + src_row * H);
+    const bool real = live && t < T;
     float s = 0.f;
-    for (int i = lane; i < H / 2; i += 32) {
-      const float2 x = __bfloat1622float2(a[i]), y = __bfloat1622float2(b[i]);
-      s += x.x * y.x + x.y * y.y;
-    }
+    if (real) {
+      const int64_t src_row = (b_ * T + t) * N + n;
+      const uint4 x = *(reinterpret_cast<const uint4*>(o + src_row * H) + col);
+      const uint4 y = *(reinterpret_cast<const uint4*>(d_o + src_row * H) + col);
+      const __nv_bfloat162* xa = reinterpret_cast<const __nv_bfloat162*>(&x);
+      const __nv_bfloat162* ya = reinterpret_cast<const __nv_bfloat162*>(&y);
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-    if (lane == 0) {
-      const float l = lse[(b_ * N + n) * T + t];
-      // A row that saw no key has lse = -inf; +inf here makes its probabilities exactly zero.
-      lse2[dst] = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
-      delta[dst] = s;
+      for (int j = 0; j < 4; ++j) {
+        const float2 xf = __bfloat1622float2(xa[j]), yf = __bfloat1622float2(ya[j]);
+        s += xf.x * yf.x + xf.y * yf.y;
+      }
+    }
+    // Sum over the lanes of the row (every lane takes part; the offsets stay inside the row's lanes).
+    for (int off = lpr >> 1; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    if (live && col == 0) {
+      if (!real) {
+        lse2[dst] = INFINITY;
+        delta[dst] = 0.f;
+      } else {
+        const float l = lse[(b_ * N + n) * T + t];
+        // A row that saw no key has lse = -inf; +inf here makes its probabilities exactly zero.
+        lse2[dst] = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
+        delta[dst] = s;
+      }
     }
   }
 }

@@ -27,8 +27,16 @@
 
 namespace axb {
 
+// Eight bf16 values moved as ONE 16-byte access (a member-wise copy of the four pairs compiles to
+// four 4-byte accesses).
 struct alignas(16) Bf8 {
   __nv_bfloat162 v[4];
+  Bf8() = default;
+  __device__ __forceinline__ Bf8(const Bf8& o) { *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(o.v); }
+  __device__ __forceinline__ Bf8& operator=(const Bf8& o) {
+    *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(o.v);
+    return *this;
+  }
 };
 
 __global__ void gather_rows_kernel(const Bf8* __restrict__ src, const int* __restrict__ idx,

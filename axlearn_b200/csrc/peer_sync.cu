@@ -42,8 +42,16 @@ __global__ void wait_flags_kernel(const int* flags, int count, int value, int* s
   }
 }
 
+// Eight bf16 values moved as ONE 16-byte access (a member-wise copy of the four pairs compiles to
+// four 4-byte accesses).
 struct alignas(16) V8 {
   __nv_bfloat162 v[4];
+  V8() = default;
+  __device__ __forceinline__ V8(const V8& o) { *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(o.v); }
+  __device__ __forceinline__ V8& operator=(const V8& o) {
+    *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(o.v);
+    return *this;
+  }
 };
 
 __global__ void reduce_slots_kernel(const __nv_bfloat16* __restrict__ staging, __nv_bfloat16* __restrict__ out,
@@ -237,8 +245,11 @@ extern "C" int axb_allreduce_push(const void* src, void* const* peer_staging_dev
                                   int64_t n, cudaStream_t stream) {
   if (n % 8 || world > 32) return -10;
   const int64_t nvec = n / 8;
+  // Decode-sized messages stay on a few CTAs (launch latency matters, not bandwidth); large
+  // activations (tensor-parallel training) get enough CTAs to fill the memory system.
   int ctas = static_cast<int>((nvec + 255) / 256);
-  if (ctas > 32) ctas = 32;
+  const int cap = nvec > (1 << 20) ? 592 : 32;
+  if (ctas > cap) ctas = cap;
   axb::allreduce_push_kernel<<<ctas, 256, 0, stream>>>(
       static_cast<const uint4*>(src), reinterpret_cast<uint4* const*>(peer_staging_dev), peer_flags_dev,
       done_counter, epoch_ptr, world, rank, site, nvec);
@@ -251,7 +262,8 @@ extern "C" int axb_allreduce_finish(const void* staging, const void* residual, v
   if (n % 8 || world > 32) return -10;
   const int64_t nvec = n / 8;
   int ctas = static_cast<int>((nvec + 255) / 256);
-  if (ctas > 32) ctas = 32;
+  const int cap = nvec > (1 << 20) ? 592 : 32;
+  if (ctas > cap) ctas = cap;
   axb::allreduce_finish_kernel<<<ctas, 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(staging), static_cast<const __nv_bfloat16*>(residual),
       static_cast<__nv_bfloat16*>(out), flags, epoch_ptr, world, site, n, status);
