@@ -38,7 +38,6 @@ constexpr int k2HalfN = 128;
 constexpr int k2BlockK = 64;
 constexpr int k2Threads = 192;
 constexpr int k2FusedThreads = k2Threads + 32;  // + one copy warp per CTA
-constexpr int k2GroupM = 8;
 
 // The fused variants give one stage of the ring to the copy warp's two chunk buffers.
 template <bool FUSED>
@@ -66,6 +65,7 @@ struct Gemm2Params {
   int M, N, K;
   int accumulate;
   int* status;
+  int group_m;  // row blocks per rasterisation group
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -216,10 +216,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const int kb_rot = (ag_on && f.ag_along_k) ? ((own_lo + k2BlockK - 1) / k2BlockK) % num_kb : 0;
 
   auto tile_coords = [&](int t, int& m_blk, int& n_blk) {
-    const int per_group = k2GroupM * n_blocks;
+    const int per_group = p.group_m * n_blocks;
     const int g = t / per_group;
-    const int first_m = g * k2GroupM;
-    const int gsize = min(m_blocks - first_m, k2GroupM);
+    const int first_m = g * p.group_m;
+    const int gsize = min(m_blocks - first_m, p.group_m);
     const int r = t % per_group;
     m_blk = first_m + r % gsize;
     n_blk = r / gsize;
@@ -485,6 +485,26 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   }
 }
 
+// Tiles are visited in groups of `group_m` row blocks x all column blocks (row block fastest), so
+// that the group's rows of A stay in L2 while B streams past once per group: more row blocks per
+// group mean fewer passes over B, as long as the group's A (group_m x 256 x K x 2 bytes) leaves room
+// in the 126 MB L2 for the streams.  AXB_GEMM2_GROUP_M overrides the choice (experiments).
+static int raster_group_m(int M, int N, int K) {
+  static int forced = -1;
+  if (forced < 0) {
+    const char* e = getenv("AXB_GEMM2_GROUP_M");
+    forced = e != nullptr ? atoi(e) : 0;
+  }
+  if (forced > 0) return forced;
+  (void)M;
+  (void)N;
+  const int64_t bytes_per_block = static_cast<int64_t>(k2TileM) * K * 2;
+  int g = static_cast<int>((32ll << 20) / bytes_per_block);   // about 32 MB of A per group
+  if (g < 4) g = 4;
+  if (g > 32) g = 32;
+  return g;
+}
+
 template <bool A_MN, bool B_MN, typename OutT, bool FUSED = false>
 static int launch_gemm2(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
                         int64_t ldc, int accumulate, int* status, int max_ctas, cudaStream_t stream,
@@ -553,7 +573,7 @@ static int launch_gemm2(const void* A, const void* B, void* C, int M, int N, int
   if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2;
   if (tiles < pairs) pairs = tiles;
   if (pairs < 1) return -12;
-  Gemm2Params p{M, N, K, accumulate, status};
+  Gemm2Params p{M, N, K, accumulate, status, raster_group_m(M, N, K)};
   kernel<<<2 * pairs, FUSED ? k2FusedThreads : k2Threads, S::kTotal, stream>>>(ta, tb, tc, p, tl, fp, maps);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
