@@ -485,24 +485,22 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   }
 }
 
-// Tiles are visited in groups of `group_m` row blocks x all column blocks (row block fastest), so
-// that the group's rows of A stay in L2 while B streams past once per group: more row blocks per
-// group mean fewer passes over B, as long as the group's A (group_m x 256 x K x 2 bytes) leaves room
-// in the 126 MB L2 for the streams.  AXB_GEMM2_GROUP_M overrides the choice (experiments).
+// Tiles are visited in groups of `group_m` row blocks x all column blocks (row block fastest): a
+// wave of 74 pairs then covers about 8 x 9 tiles, and the group's rows of A are reused by the next
+// wave.  Measured DRAM reads on the Fuji shapes (ncu, one launch): 16384 x 4096 x 4096: 215 / 322 /
+// 343 / 624 MB for groups of 4 / 8 / 16 / 32; 16384 x 4096 x 11008: 2.81 / 2.24 / 2.43 / 3.65 GB (a
+// wave's operand panels, (8 + 9) x 256 x K x 2 bytes, no longer fit the L2 at this K); times within
+// 2 % of each other up to 16 and worse beyond.  Eight is the choice; AXB_GEMM2_GROUP_M overrides it.
 static int raster_group_m(int M, int N, int K) {
   static int forced = -1;
   if (forced < 0) {
     const char* e = getenv("AXB_GEMM2_GROUP_M");
     forced = e != nullptr ? atoi(e) : 0;
   }
-  if (forced > 0) return forced;
   (void)M;
   (void)N;
-  const int64_t bytes_per_block = static_cast<int64_t>(k2TileM) * K * 2;
-  int g = static_cast<int>((32ll << 20) / bytes_per_block);   // about 32 MB of A per group
-  if (g < 4) g = 4;
-  if (g > 32) g = 32;
-  return g;
+  (void)K;
+  return forced > 0 ? forced : 8;
 }
 
 template <bool A_MN, bool B_MN, typename OutT, bool FUSED = false>
