@@ -67,6 +67,56 @@ def _cmd_bundle(args) -> int:
     return 0
 
 
+def _cmd_gcp(args, rest: Sequence[str]) -> int:
+    """``gcp launch|delete|status|manifest|config``: GKE JobSets through kubectl, settings from the
+    ``[gcp]`` tables of the settings files (axlearn/cloud/gcp/jobs/launch.py, .../config.py)."""
+    from axlearn_b200.cloud.common import config as settings
+    from axlearn_b200.cloud.gcp.job import GKEJob
+    from axlearn_b200.cloud.gcp.jobset_utils import A3UltraReplicatedJob, A4HighReplicatedJob, GCSFuseMount
+
+    if args.action == "config":
+        if args.activate:
+            _, gcp = settings.load_configs("gcp")
+            if args.activate not in gcp:
+                raise SystemExit(f"no [gcp.\"{args.activate}\"] table; known: {[k for k in gcp if k != '_active']}")
+            gcp["_active"] = args.activate
+            print(settings.update_configs("gcp", gcp))
+        else:
+            path, gcp = settings.load_configs("gcp")
+            print(json.dumps({"file": path, "gcp": gcp}, indent=1))
+        return 0
+    if not args.name:
+        raise SystemExit(f"gcp {args.action} needs --name")
+
+    def setting(key, default=None, required=False):
+        return settings.gcp_settings(key, project=args.project, env_id=args.env_id, default=default, required=required)
+
+    builder_cls = {"a4-highgpu-8g": A4HighReplicatedJob, "a3-ultragpu-8g": A3UltraReplicatedJob}[args.machine_type]
+    command = " ".join(rest) if rest else (args.command or "true")
+    builder = builder_cls.default_config().set(
+        command=command, image=args.image or setting("docker_image"), num_nodes=args.num_nodes,
+        reservation=args.reservation or setting("reservation"), service_account=setting("k8s_service_account"),
+        priority_class=args.priority_class, disable_nvls=args.fault_tolerant,
+        env_vars=dict(item.split("=", 1) for item in args.env))
+    if args.output_dir and args.output_dir.startswith("gs://"):
+        builder.gcsfuse_mount = GCSFuseMount(gcs_path=args.output_dir)
+        builder.output_dir = "/output"
+    job = GKEJob.default_config().set(name=args.name, builder=builder, namespace=args.namespace,
+                                      max_restarts=args.max_tries - 1, queue=setting("kueue_queue")).instantiate()
+    if args.action == "manifest":
+        import yaml  # pylint: disable=import-outside-toplevel
+
+        print(yaml.safe_dump(job.build_jobset(), sort_keys=False))
+    elif args.action == "launch":
+        print(job.execute())
+    elif args.action == "delete":
+        job._delete()  # pylint: disable=protected-access
+        print(f"deleted {args.name}")
+    else:
+        print(job.status().value)
+    return 0
+
+
 def _cmd_train(args, rest: Sequence[str]) -> int:
     cmd = [sys.executable, "-m", "axlearn_b200.common.launch_trainer_main", *rest]
     if args.gpus > 1:
@@ -103,6 +153,24 @@ def build_parser() -> argparse.ArgumentParser:
     bastion.add_argument("--resources", nargs="*", default=[], help="e.g. b200=8")
     bastion.add_argument("--env", nargs="*", default=[], help="KEY=VALUE")
 
+    gcp = groups.add_parser("gcp", help="GKE JobSets; everything after the flags is the worker command")
+    gcp.add_argument("action", choices=["launch", "delete", "status", "manifest", "config"])
+    gcp.add_argument("--name")
+    gcp.add_argument("--project")
+    gcp.add_argument("--env_id")
+    gcp.add_argument("--namespace", default="default")
+    gcp.add_argument("--machine_type", default="a4-highgpu-8g", choices=["a4-highgpu-8g", "a3-ultragpu-8g"])
+    gcp.add_argument("--num_nodes", type=int, default=1)
+    gcp.add_argument("--image")
+    gcp.add_argument("--command")
+    gcp.add_argument("--reservation")
+    gcp.add_argument("--priority_class")
+    gcp.add_argument("--output_dir")
+    gcp.add_argument("--max_tries", type=int, default=1)
+    gcp.add_argument("--fault_tolerant", action="store_true", help="restartable job: no NVLink multicast binding")
+    gcp.add_argument("--env", nargs="*", default=[], help="KEY=VALUE")
+    gcp.add_argument("--activate", help="config: make this \"project:env_id\" table the active one")
+
     bundle = groups.add_parser("bundle")
     bundle.add_argument("--name", required=True)
     bundle.add_argument("--remote_dir", required=True)
@@ -117,6 +185,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         return _cmd_train(args, rest)
     if args.group == "bench":
         return _cmd_bench(args, rest)
+    if args.group == "gcp":
+        return _cmd_gcp(args, rest)
     if rest:
         raise SystemExit(f"unknown arguments: {rest}")
     if args.group == "bastion":

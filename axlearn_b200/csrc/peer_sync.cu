@@ -9,6 +9,12 @@
 //                       is bit-reproducible), written as bf16; optionally accumulates the sum
 //                       of squares of the result into per-CTA partials for global-norm clipping.
 //
+//   axb_multimem_allreduce   the reduction half of an in-switch (NVLS) all-reduce: this rank's slice
+//                       of a multicast-bound symmetric buffer is read with multimem.ld_reduce
+//                       (the NVSwitch sums all ranks' copies, fp32 accumulation) and the sums are
+//                       written back to every rank's copy with multimem.st.  The callers order
+//                       it between two flag barriers (signal + wait above).
+//
 // Waiting kernels never wait on a kernel that might not be resident: flags are written by
 // kernels of *other* GPUs (or, in single-GPU tests, by an earlier launch on the same stream).
 #include <cuda_bf16.h>
@@ -106,7 +112,40 @@ __global__ void reduce_slots_kernel(const __nv_bfloat16* __restrict__ staging, _
   }
 }
 
+// One 16-byte vector (eight bf16) per thread and trip.  `mc` is the multicast address of the buffer;
+// vectors [first, first + count) are this rank's share.
+__global__ void multimem_allreduce_kernel(uint64_t mc, int64_t first, int64_t count) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < count;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const uint64_t addr = mc + static_cast<uint64_t>(first + i) * 16;
+    uint32_t a, b, c, d;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
+                 : "l"(addr)
+                 : "memory");
+    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(a), "r"(b),
+                 "r"(c), "r"(d)
+                 : "memory");
+  }
+  // The stores travel through the switch to every peer: ordered before this kernel can complete,
+  // so the flag raised by the next launch cannot overtake them.
+  __threadfence_system();
+}
+
 }  // namespace axb
+
+// Reduces vectors [rank * nvec / world, (rank + 1) * nvec / world) of a buffer of `nvec` 16-byte
+// vectors (bf16) bound to the multicast address `mc_ptr`, in place on every rank.
+extern "C" int axb_multimem_allreduce(uint64_t mc_ptr, int64_t nvec, int world, int rank, cudaStream_t stream) {
+  if (mc_ptr == 0 || (mc_ptr & 15) || world < 1 || rank < 0 || rank >= world) return -10;
+  const int64_t first = nvec * rank / world, last = nvec * (rank + 1) / world;
+  const int64_t count = last - first;
+  if (count <= 0) return 0;
+  int64_t ctas = (count + 255) / 256;
+  if (ctas > 296) ctas = 296;
+  axb::multimem_allreduce_kernel<<<static_cast<int>(ctas), 256, 0, stream>>>(mc_ptr, first, count);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
 
 extern "C" int axb_signal_peers(int* const* peer_flags_dev, int world, int slot, int value, cudaStream_t stream) {
   if (world > 32) return -10;

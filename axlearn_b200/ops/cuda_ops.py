@@ -68,6 +68,7 @@ class _Sigs:
     axb_gemm_bf16_2cta = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
                           c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
     axb_gemm_splitk_plan = [c_int, c_int, c_int]
+    axb_multimem_allreduce = [ctypes.c_uint64, c_int64, c_int, c_int, c_void_p]
     axb_gemm_bf16_splitk = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64,
                             c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     axb_rmsnorm_fwd = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p]

@@ -159,6 +159,13 @@ def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, group, world: int) -> 
         return None
     if w.dtype != torch.bfloat16 or x.shape[-1] % 8 or w.shape[1] % 8:
         return None
+    from axlearn_b200.ops import cuda_ops
+
+    if x.is_cuda and cuda_ops.carries_gather(w):
+        # The weight is also storage-sharded by the fused FSDP runtime, whose linear gathers it
+        # and scatters its gradient from inside its own GEMMs: that linear runs, and the
+        # reduction over the tensor-parallel group follows as a separate peer all-reduce.
+        return None
     rows = x.numel() // x.shape[-1]
     if not (x.is_cuda and x.dtype == torch.bfloat16 and ENABLED and group is not None and 2 <= world <= 8):
         return None

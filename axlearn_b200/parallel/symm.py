@@ -30,7 +30,11 @@ class SymmetricBuffer:
         # The kernels use unicast peer pointers only.  Without this switch the rendezvous also
         # binds every allocation to an NVLink multicast object, which buys nothing here and turns
         # a rank that exits abruptly (watchdog or supervisor kill) into NVLink faults on its peers.
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        # AXB200_NVLS=1 opts in to the binding (parallel/nvls.py: in-switch reductions).
+        if os.environ.get("AXB200_NVLS", "0") == "1":
+            os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "0"
+        else:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
 
         self.group = group
@@ -43,6 +47,7 @@ class SymmetricBuffer:
         self.rank = self.handle.rank
         self.world = self.handle.world_size
         self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         self.nbytes = numel * self.tensor.element_size()
         start = self.tensor.data_ptr()
         bisect.insort(_registry, (start, start + self.nbytes, self), key=lambda e: e[0])

@@ -243,3 +243,51 @@ def test_goodput_recorder_with_fake_client(tmp_path):
     file_rec = measurement.get_recorder_config("goodput", ["name=run2", f"upload_dir={tmp_path}"]).instantiate()
     file_rec.record(measurement.Event.START_JOB)
     assert (tmp_path / "goodput_run2.jsonl").read_text().count("START_JOB") == 1
+
+
+def test_settings_files_and_gcp_cli(tmp_path, monkeypatch, capsys):
+    import json
+    import os
+
+    from axlearn_b200.cli import main as cli
+    from axlearn_b200.cloud.common import config as settings
+
+    root = tmp_path / "repo"
+    (root / ".axlearn").mkdir(parents=True)
+    (root / ".axlearn" / "axlearn.default.config").write_text(
+        '[gcp]\n_active = "proj:us-central1-b"\n\n[gcp."proj:us-central1-b"]\nproject = "proj"\nzone = "us-central1-b"\n'
+        'docker_image = "gcr.io/proj/img:1"\nreservation = "res-b200"\n\n[gcp."other:europe-west4-a"]\nproject = "other"\n'
+        'zone = "europe-west4-a"\ndocker_image = "gcr.io/other/img:2"\n')
+    monkeypatch.chdir(root)
+    monkeypatch.setenv("HOME", str(tmp_path / "home"))
+    path, gcp = settings.load_configs("gcp")
+    assert path.endswith("axlearn.default.config") and gcp["_active"] == "proj:us-central1-b"
+    assert settings.gcp_settings("docker_image") == "gcr.io/proj/img:1"
+    assert settings.gcp_settings("env_id") == "us-central1-b"                       # falls back to the zone
+    assert settings.gcp_settings("docker_image", project="other", env_id="europe-west4-a") == "gcr.io/other/img:2"
+    assert settings.gcp_settings("missing", required=False) is None
+    with pytest.raises(SystemExit):
+        settings.gcp_settings("missing")
+    # A user file overrides the default file key by key.
+    user = settings.update_configs("gcp", {**gcp, "_active": "other:europe-west4-a"})
+    assert user == str(root / ".axlearn" / ".axlearn.config")
+    assert settings.gcp_settings("project") == "other"
+    assert settings.load_configs("gcp")[1]["proj:us-central1-b"]["reservation"] == "res-b200"
+    os.remove(user)
+    # The command line builds the JobSet from those settings.
+    assert cli.main(["gcp", "manifest", "--name", "run1", "--num_nodes", "2", "--output_dir", "gs://b/out",
+                     "--fault_tolerant", "python", "-m", "train", "--x=1"]) == 0
+    out = capsys.readouterr().out
+    import yaml
+
+    jobset = yaml.safe_load(out)
+    pod = jobset["spec"]["replicatedJobs"][0]["template"]["spec"]["template"]["spec"]
+    assert jobset["metadata"]["name"] == "run1" and pod["containers"][0]["image"] == "gcr.io/proj/img:1"
+    assert pod["nodeSelector"]["cloud.google.com/reservation-name"] == "res-b200"
+    assert "-m train --x=1" in pod["containers"][0]["command"][2]
+    env = {e["name"]: e.get("value") for e in pod["containers"][0]["env"]}
+    assert env["NCCL_NVLS_ENABLE"] == "0" and env["OUTPUT_DIR"] == "/output"
+    assert cli.main(["gcp", "config", "--activate", "other:europe-west4-a"]) == 0
+    assert settings.gcp_settings("project") == "other"
+    assert cli.main(["gcp", "config"]) == 0
+    assert json.loads(capsys.readouterr().out.split("\n", 1)[1])["gcp"]["_active"] == "other:europe-west4-a"

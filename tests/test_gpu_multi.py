@@ -165,3 +165,55 @@ def test_tensor_parallel_peer_reductions_match_library_all_reduce(tmp_path, big)
             assert abs(a - b) < 5e-3 * abs(b), (losses, ref_losses)
         for path, t in w.items():
             assert (t - ref_w[path]).abs().max() < 2e-2 * ref_w[path].abs().max() + 1e-6, path
+
+
+def _run_nvls(rank, world, port, queue):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), AXB200_NVLS="1")
+    sys.path.insert(0, REPO)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from axlearn_b200.ops import cuda_ops
+        from axlearn_b200.parallel import nvls
+
+        dev = torch.device("cuda", rank)
+        try:
+            reducer = nvls.MultimemAllReduce(1 << 22, group=dist.group.WORLD, device=dev)
+        except RuntimeError as e:
+            queue.put((rank, "unavailable", str(e)))
+            return
+        worst = 0.0
+        for n, seed in ((1 << 22, 0), (8 * 1000, 1), (1 << 20, 2)):
+            g = torch.Generator(device=dev).manual_seed(seed * 10 + rank)
+            x = torch.randn(n, device=dev, generator=g).bfloat16()
+            got = reducer.all_reduce(x)
+            ref = x.float().clone()
+            dist.all_reduce(ref)
+            torch.cuda.synchronize()
+            cuda_ops.check_status()
+            worst = max(worst, ((got.float() - ref).abs() / (ref.abs() + 1.0)).max().item())
+        queue.put((rank, "ok", worst))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_multimem_all_reduce_matches_library():
+    """In-switch all-reduce (multimem.ld_reduce / multimem.st on a multicast-bound symmetric buffer)
+    against NCCL; skipped where the system offers no multicast address."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_run_nvls, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    if any(status == "unavailable" for _, status, _ in results):
+        pytest.skip(f"no multicast: {results[0][2]}")
+    for _, status, worst in results:
+        assert status == "ok" and worst < 2e-2, results
