@@ -718,12 +718,12 @@ class TransformerFeedForwardDropFreeMoE(TransformerFeedForwardMoE):
 
     The (token, choice) pairs are sorted by expert -- choice-major, so that every token's first
     choice precedes any second choice inside an expert's run, as in the reference -- and laid
-    out in one ``[R, M]`` buffer in which each expert's run starts on a 128-row boundary.  The
+    out in one ``[R, M]`` buffer in which each expert's run starts on a block boundary (256 rows).  The
     three projections are then grouped GEMMs over that buffer (one tcgen05 kernel launch each;
-    the expert of every 128-row block selects the weight matrix), the activation is the usual
+    the expert of every row block selects the weight matrix), the activation is the usual
     fused elementwise kernel, and the outputs are gathered back and summed over the K choices
     with the routing weights in fp32.  Nothing synchronises with the host: ``R`` is the static
-    bound ``pairs + E * 127`` rounded up to 128.
+    bound ``pairs + E * (block - 1)`` rounded up to the block.
     """
 
     @config_class

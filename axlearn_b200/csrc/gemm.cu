@@ -53,8 +53,8 @@ struct GemmParams {
   float* ws;
   int* counters;
   // Grouped problems (mixture-of-experts), rows sorted by group and every group padded to whole
-  // 128-row blocks.  Mode 1: row block m uses B matrix number `group_index[m]` (-1 = unused
-  // block, skipped); the B tensor map stacks the groups along its outer dim, `b_group_rows`
+  // blocks of `group_block_rows` rows (a multiple of 128).  Mode 1: the rows of block b use B
+  // matrix number `group_index[b]` (-1 = unused block, skipped); the B tensor map stacks the groups along its outer dim, `b_group_rows`
   // apart.  Mode 2: one output [M, N] per group g (`c_group_stride` elements apart), contracting
   // rows [group_index[g], group_index[g + 1]) of the (MN-major) operands; an empty group's
   // output is zero.
@@ -63,6 +63,7 @@ struct GemmParams {
   const int* group_index;
   int b_group_rows;
   int64_t c_group_stride;
+  int group_block_rows;
 };
 
 constexpr int kFusedThreads = kNumThreads + 32;  // + one copy warp per CTA
@@ -193,7 +194,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         kb_range(ks, kb_lo, kb_hi);
         int b_off = 0;  // grouped mode 1: outer-dim offset of this row block's B matrix
         if (gmode == 1) {
-          const int g = p.group_index[m_blk];
+          const int g = p.group_index[m_blk / (p.group_block_rows / kBlockM)];
           if (g < 0) continue;
           b_off = g * p.b_group_rows;
         }
@@ -267,7 +268,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (gmode == 1) {
           int m_blk, n_blk;
           tile_coords(t - ks * num_tiles, m_blk, n_blk);
-          if (p.group_index[m_blk] < 0) continue;
+          if (p.group_index[m_blk / (p.group_block_rows / kBlockM)] < 0) continue;
         }
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.status, kStatusWaitTimeoutMma)) break;
         tc_fence_after_sync();
@@ -316,7 +317,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int ks = t / num_tiles;
       const int tile = t - ks * num_tiles;
       tile_coords(tile, m_blk, n_blk);
-      if (gmode == 1 && p.group_index[m_blk] < 0) continue;
+      if (gmode == 1 && p.group_index[m_blk / (p.group_block_rows / kBlockM)] < 0) continue;
       if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, kStatusWaitTimeoutEpilogue)) break;
       tc_fence_after_sync();
       const int row = m_blk * kBlockM + quarter * 32 + lane;
@@ -545,7 +546,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
                        cudaStream_t stream, const FusedParams* fused = nullptr, int split_k = 1,
                        float* ws = nullptr, int* counters = nullptr, int group_mode = 0,
                        int num_groups = 1, const int* group_index = nullptr,
-                       int64_t c_group_stride = 0) {
+                       int64_t c_group_stride = 0, int group_block_rows = kBlockM) {
   // Grouped mode 1 stacks the groups' B matrices along the outer dim of one tensor map.
   const uint64_t b_stack = group_mode == 1 ? static_cast<uint64_t>(num_groups) : 1;
   CUtensorMap ta, tb;
@@ -621,7 +622,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   if (grid > cap) grid = cap;
   if (grid < 1) return -12;
   GemmParams p{M, N, K, C, ldc, status, accumulate, split_k, ws, counters,
-               group_mode, num_groups, group_index, B_MN ? K : N, c_group_stride};
+               group_mode, num_groups, group_index, B_MN ? K : N, c_group_stride, group_block_rows};
   kernel<<<grid, FUSED ? kFusedThreads : kNumThreads, kSmem, stream>>>(ta, tb, tl, p, fp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -716,21 +717,40 @@ extern "C" int axb_gemm_bf16_splitk(const void* A, const void* B, void* C, int M
   return -11;
 }
 
+// AXB200_GEMM=1cta keeps every problem on the single-CTA kernels (for comparisons).
+static bool cta_pairs_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("AXB200_GEMM");
+    on = (e != nullptr && strcmp(e, "1cta") == 0) ? 0 : 1;
+  }
+  return on != 0;
+}
+
+extern "C" int axb_gemm_bf16_grouped_2cta(const void* A, const void* B, void* C, int M, int N, int K,
+                                          int64_t lda, int64_t ldb, int64_t ldc, int a_mn_major,
+                                          int b_mn_major, int mode, int num_groups,
+                                          const int* group_index, int64_t c_group_stride,
+                                          int block_rows, int* status, int max_ctas, cudaStream_t stream);
+
 // Grouped GEMMs for mixture-of-experts layers whose token rows are sorted by expert, each expert's
-// run padded to a whole number of 128-row blocks.
+// run padded to a whole number of `block_rows`-row blocks (a multiple of 128; multiples of 256 run
+// on CTA pairs).
 //   mode 1: C[M, N] = A[M, K] * B[g(m)]  with B stacked [G, K, N] (b_mn_major = 1) or [G, N, K]
-//           (b_mn_major = 0) and `group_index[M / 128]` = the group of each row block (-1 = unused
-//           block: its rows of C are not written).  With b_mn_major = 1, K must be a multiple of 64.
+//           (b_mn_major = 0) and `group_index[M / block_rows]` = the group of each row block (-1 =
+//           unused block: its rows of C are not written).  With b_mn_major = 1, K must be a multiple
+//           of 64.
 //   mode 2: C[g] [M, N] = sum over rows r in [group_index[g], group_index[g + 1]) of
 //           A[r, :M]^T * B[r, :N]  (both operands stored row-major over the token rows, i.e.
-//           a_mn_major = b_mn_major = 1; K = total rows); offsets are multiples of 128.
+//           a_mn_major = b_mn_major = 1; K = total rows); offsets are multiples of `block_rows`.
 extern "C" int axb_gemm_bf16_grouped(const void* A, const void* B, void* C, int M, int N, int K,
                                      int64_t lda, int64_t ldb, int64_t ldc, int a_mn_major,
                                      int b_mn_major, int out_fp32, int mode, int num_groups,
-                                     const int* group_index, int64_t c_group_stride, int* status,
-                                     int max_ctas, cudaStream_t stream) {
+                                     const int* group_index, int64_t c_group_stride, int block_rows,
+                                     int* status, int max_ctas, cudaStream_t stream) {
   using namespace axb;
   if (M <= 0 || N <= 0 || K <= 0 || num_groups <= 0) return 0;
+  if (block_rows < kBlockM || (block_rows % kBlockM) != 0) return -16;
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
       (reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(C) & 15) ||
       (ldc % (out_fp32 ? 4 : 8)) || group_index == nullptr)
@@ -738,15 +758,21 @@ extern "C" int axb_gemm_bf16_grouped(const void* A, const void* B, void* C, int 
   if (mode == 1 && (a_mn_major || (M % kBlockM) || (b_mn_major && (K % kBlockK)))) return -16;
   if (mode == 2 && (!a_mn_major || !b_mn_major || (c_group_stride % 8))) return -16;
   if (mode != 1 && mode != 2) return -16;
+  if (cta_pairs_enabled() && !out_fp32) {
+    const int rc = axb_gemm_bf16_grouped_2cta(A, B, C, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, mode,
+                                              num_groups, group_index, c_group_stride, block_rows, status,
+                                              max_ctas, stream);
+    if (rc != -20) return rc;
+  }
 #define AXB_GROUPED_CASE(AM, BM, T)                                                                \
   if (a_mn_major == (AM ? 1 : 0) && b_mn_major == (BM ? 1 : 0) && out_fp32 == (sizeof(T) == 4)) { \
     if (N >= 256)                                                                                  \
       return launch_gemm<256, 4, AM, BM, T>(A, B, C, M, N, K, lda, ldb, ldc, 0, status, max_ctas,  \
                                             stream, nullptr, 1, nullptr, nullptr, mode,           \
-                                            num_groups, group_index, c_group_stride);              \
+                                            num_groups, group_index, c_group_stride, block_rows);  \
     return launch_gemm<128, 6, AM, BM, T>(A, B, C, M, N, K, lda, ldb, ldc, 0, status, max_ctas,    \
                                           stream, nullptr, 1, nullptr, nullptr, mode, num_groups, \
-                                          group_index, c_group_stride);                            \
+                                          group_index, c_group_stride, block_rows);                \
   }
   AXB_GROUPED_CASE(false, false, __nv_bfloat16)
   AXB_GROUPED_CASE(false, true, __nv_bfloat16)
@@ -764,15 +790,6 @@ extern "C" int axb_gemm_bf16_fused_2cta(const void* A, const void* B, void* C, i
                                         int b_mn_major, int* status, int max_ctas, const void* fused,
                                         cudaStream_t stream);
 
-// AXB200_GEMM=1cta keeps every problem on the single-CTA kernels (for comparisons).
-static bool cta_pairs_enabled() {
-  static int on = -1;
-  if (on < 0) {
-    const char* e = getenv("AXB200_GEMM");
-    on = (e != nullptr && strcmp(e, "1cta") == 0) ? 0 : 1;
-  }
-  return on != 0;
-}
 
 extern "C" int axb_gemm_bf16_fused(const void* A, const void* B, void* C, int M, int N, int K,
                                    int64_t lda, int64_t ldb, int64_t ldc, int a_mn_major,

@@ -66,6 +66,17 @@ struct Gemm2Params {
   int accumulate;
   int* status;
   int group_m;  // row blocks per rasterisation group
+  // Grouped problems (mixture-of-experts; plain kernel only), rows sorted by group and every group
+  // padded to whole blocks of `group_block_rows` rows (a multiple of 256).  Mode 1: the rows of
+  // block b use B matrix number `group_index[b]` (-1 = unused block, skipped); the B tensor map
+  // stacks the groups along its outer dim, `b_group_rows` apart.  Mode 2: one output [M, N] per
+  // group g (third coordinate of the C map), contracting rows [group_index[g], group_index[g + 1])
+  // of the MN-major operands; an empty group's output is zero.
+  int group_mode;
+  int num_groups;
+  const int* group_index;
+  int b_group_rows;
+  int group_block_rows;
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -138,6 +149,13 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const 
                : "memory");
 }
 
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* smem_src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+
 // FUSED adds what the single-CTA fused kernel has (same `FusedParams` contract): a copy warp that
 // carries parameter gathers, consumption of a gathered B behind per-slab flags (every CTA of the
 // pair waits for the slabs ITS half of B touches), and a reduce-scatter epilogue whose TMA stores
@@ -175,6 +193,20 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   const int n_blocks = (p.N + k2TileN - 1) / k2TileN;
   const int num_tiles = m_blocks * n_blocks;
   const int num_kb = (p.K + k2BlockK - 1) / k2BlockK;
+  const int gmode = FUSED ? 0 : p.group_mode;
+  // item = (group, tile) in grouped mode 2, a tile otherwise.
+  const int num_items = num_tiles * (gmode == 2 ? p.num_groups : 1);
+  auto kb_range = [&](int g, int& kb_lo, int& kb_hi) {
+    if (gmode == 2) {
+      kb_lo = p.group_index[g] / k2BlockK;
+      kb_hi = p.group_index[g + 1] / k2BlockK;
+    } else {
+      kb_lo = 0;
+      kb_hi = num_kb;
+    }
+  };
+  // Grouped mode 1: the group of a 256-row tile (every block of the index covers whole tiles).
+  auto tile_group = [&](int m_blk) { return p.group_index[m_blk / (p.group_block_rows / k2TileM)]; };
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmap_a);
@@ -251,9 +283,18 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         slab_ready |= 1u << r;
         return true;
       };
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+      for (int t = pair; t < num_items && ok; t += num_pairs) {
         int m_blk, n_blk;
-        tile_coords(t, m_blk, n_blk);
+        const int grp = t / num_tiles;
+        tile_coords(t - grp * num_tiles, m_blk, n_blk);
+        int kb_lo, kb_hi;
+        kb_range(grp, kb_lo, kb_hi);
+        int b_off = 0;  // grouped mode 1: outer-dim offset of this tile's B matrix
+        if (gmode == 1) {
+          const int g = tile_group(m_blk);
+          if (g < 0) continue;
+          b_off = g * p.b_group_rows;
+        }
         const int m0 = m_blk * k2TileM + static_cast<int>(rank) * k2RowsPerCta;
         const int n0 = n_blk * k2TileN + static_cast<int>(rank) * k2HalfN;
         bool local = false;  // read this CTA's half of the B tile from the own shard
@@ -263,7 +304,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           for (int r = n0 / f.ag_shard_extent; !local && r <= last / f.ag_shard_extent && ok; ++r) ok = need_slab(r);
           if (!ok) break;
         }
-        for (int kbi = 0; kbi < num_kb; ++kbi) {
+        for (int kbi = kb_lo; kbi < kb_hi; ++kbi) {
           const int kb = FUSED ? (kbi + kb_rot) % num_kb : kbi;
           if (FUSED && ag_on && f.ag_along_k) {
             const int k_lo = kb * k2BlockK, k_hi = min(k_lo + k2BlockK, p.K) - 1;
@@ -297,10 +338,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 tma_load_2d_pair(sb + j * 8192, &tmap_b_local, bar, n0 + j * 64, k0 - own_lo);
             }
           } else if constexpr (!B_MN) {
-            tma_load_2d_pair(sb, &tmap_b, bar, k0, n0);
+            tma_load_2d_pair(sb, &tmap_b, bar, k0, n0 + b_off);
           } else {
 #pragma unroll
-            for (int j = 0; j < k2HalfN / 64; ++j) tma_load_2d_pair(sb + j * 8192, &tmap_b, bar, n0 + j * 64, k0);
+            for (int j = 0; j < k2HalfN / 64; ++j)
+              tma_load_2d_pair(sb + j * 8192, &tmap_b, bar, n0 + j * 64, k0 + b_off);
           }
           if (++stage == k2Stages) {
             stage = 0;
@@ -318,11 +360,19 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+      for (int t = pair; t < num_items && ok; t += num_pairs) {
+        const int grp = t / num_tiles;
+        if (gmode == 1) {
+          int m_blk, n_blk;
+          tile_coords(t - grp * num_tiles, m_blk, n_blk);
+          if (tile_group(m_blk) < 0) continue;
+        }
+        int kb_lo, kb_hi;
+        kb_range(grp, kb_lo, kb_hi);
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.status, kStatusWaitTimeoutMma)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * k2TileN;
-        for (int kb = 0; kb < num_kb; ++kb) {  // the producer's k order (rotated or not) is irrelevant here
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {  // the producer's k order (rotated or not) is irrelevant here
           if (!mbar_wait(&full_bar[stage], phase, p.status, kStatusWaitTimeoutMma)) {
             ok = false;
             break;
@@ -334,7 +384,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           for (int k = 0; k < k2BlockK / 16; ++k) {
             const uint64_t da = A_MN ? umma_smem_desc(sa + k * 2048, 8192, 1024) : umma_smem_desc(sa + k * 32, 16, 1024);
             const uint64_t db = B_MN ? umma_smem_desc(sb + k * 2048, 8192, 1024) : umma_smem_desc(sb + k * 32, 16, 1024);
-            tc_mma_f16_pair(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            tc_mma_f16_pair(d_tmem, da, db, idesc, (kb > kb_lo || k > 0) ? 1u : 0u);
           }
           // The stage is free in BOTH CTAs once these MMAs retire.
           const uint32_t eb = smem_u32(&empty_bar[stage]);
@@ -366,9 +416,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     int acc = 0;
     uint32_t acc_phase = 0;
     uint32_t store_seq = 0;
-    for (int t = pair; t < num_tiles; t += num_pairs) {
+    for (int t = pair; t < num_items; t += num_pairs) {
       int m_blk, n_blk;
-      tile_coords(t, m_blk, n_blk);
+      const int grp = t / num_tiles;
+      tile_coords(t - grp * num_tiles, m_blk, n_blk);
+      if (gmode == 1 && tile_group(m_blk) < 0) continue;
+      // Grouped mode 2: nothing was accumulated for an empty group, its result is zero.
+      const bool empty_group = gmode == 2 && p.group_index[grp] / k2BlockK == p.group_index[grp + 1] / k2BlockK;
       if (!mbar_wait_warp_relaxed(&tmem_full[acc], acc_phase, p.status, kStatusWaitTimeoutEpilogue)) break;
       tc_fence_after_sync();
       const int row0 = m_blk * k2TileM + static_cast<int>(rank) * k2RowsPerCta + quarter * 32;
@@ -415,6 +469,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 #pragma unroll
           for (int v = 0; v < 8; ++v) o[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
         }
+        if (empty_group) {
+#pragma unroll
+          for (int v = 0; v < 8; ++v) o[v] = make_uint4(0u, 0u, 0u, 0u);
+        }
         if (ch == kChunks - 1) {
           // All of this warp's reads of the accumulator are done: hand it back early.
           tc_fence_before_sync();
@@ -434,6 +492,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         if (lane == 0 && row0 < p.M && n0 + ch * kChunkCols < p.N) {
           if (n_dst > 1) {
             for (int d = 0; d < n_dst; ++d) tma_store_2d(&rs_maps.m[d], tile, n0 + ch * kChunkCols, out_row);
+          } else if (gmode == 2) {
+            tma_store_3d(out_map, tile, n0 + ch * kChunkCols, out_row, grp);
           } else if (p.accumulate) {
             tma_reduce_add_2d(out_map, tile, n0 + ch * kChunkCols, out_row);
           } else {
@@ -506,8 +566,11 @@ static int raster_group_m(int M, int N, int K) {
 template <bool A_MN, bool B_MN, typename OutT, bool FUSED = false>
 static int launch_gemm2(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
                         int64_t ldc, int accumulate, int* status, int max_ctas, cudaStream_t stream,
-                        const FusedParams* fused = nullptr) {
+                        const FusedParams* fused = nullptr, int group_mode = 0, int num_groups = 1,
+                        const int* group_index = nullptr, int64_t c_group_stride = 0, int group_block_rows = k2TileM) {
   CUtensorMap ta, tb, tc;
+  // Grouped mode 1 stacks the groups' B matrices along the outer dim of one tensor map.
+  const uint64_t b_stack = group_mode == 1 ? static_cast<uint64_t>(num_groups) : 1;
   int rc;
   {
     uint64_t dims[2] = {static_cast<uint64_t>(A_MN ? M : K), static_cast<uint64_t>(A_MN ? K : M)};
@@ -518,7 +581,7 @@ static int launch_gemm2(const void* A, const void* B, void* C, int M, int N, int
   }
   const uint32_t b_box[2] = {64, static_cast<uint32_t>(B_MN ? k2BlockK : k2HalfN)};
   {
-    uint64_t dims[2] = {static_cast<uint64_t>(B_MN ? N : K), static_cast<uint64_t>(B_MN ? K : N)};
+    uint64_t dims[2] = {static_cast<uint64_t>(B_MN ? N : K), b_stack * static_cast<uint64_t>(B_MN ? K : N)};
     uint64_t strides[1] = {static_cast<uint64_t>(ldb) * 2};
     rc = make_tensor_map(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, B, dims, strides, b_box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != 0) return rc;
@@ -530,7 +593,15 @@ static int launch_gemm2(const void* A, const void* B, void* C, int M, int N, int
   memset(&fp, 0, sizeof(fp));
   if (FUSED && fused != nullptr) fp = *fused;
   const bool scatter = FUSED && fp.rs_world > 1;
-  if (!scatter) {
+  if (group_mode == 2) {
+    // One [M, N] output per group: the group is the third coordinate, so rows past M are clipped
+    // instead of running into the next group's matrix.
+    uint64_t dims[3] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M), static_cast<uint64_t>(num_groups)};
+    uint64_t strides[2] = {c_strides[0], static_cast<uint64_t>(c_group_stride) * sizeof(OutT)};
+    uint32_t box[3] = {c_box[0], c_box[1], 1};
+    rc = make_tensor_map(&tc, c_type, 3, C, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != 0) return rc;
+  } else if (!scatter) {
     uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)};
     rc = make_tensor_map(&tc, c_type, 2, C, dims, c_strides, c_box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != 0) return rc;
@@ -566,12 +637,17 @@ static int launch_gemm2(const void* A, const void* B, void* C, int M, int N, int
     }
     configured = true;
   }
-  const int tiles = ((M + k2TileM - 1) / k2TileM) * ((N + k2TileN - 1) / k2TileN);
+  const int tiles = ((M + k2TileM - 1) / k2TileM) * ((N + k2TileN - 1) / k2TileN) * (group_mode == 2 ? num_groups : 1);
   int pairs = sm_count() / 2;
   if (max_ctas > 0 && max_ctas / 2 < pairs) pairs = max_ctas / 2;
   if (tiles < pairs) pairs = tiles;
   if (pairs < 1) return -12;
-  Gemm2Params p{M, N, K, accumulate, status, raster_group_m(M, N, K)};
+  // Grouped mode 1: sixteen row blocks per rasterisation group, so that a wave mostly stays inside
+  // one group's B matrix (measured at 32768 pairs, 8 groups, 4096 -> 14336: 3.07 / 2.85 / 2.78 ms for
+  // 4 / 8 / 16).
+  const int raster = group_mode == 1 && getenv("AXB_GEMM2_GROUP_M") == nullptr ? 16 : raster_group_m(M, N, K);
+  Gemm2Params p{M,          N,          K,           accumulate,     status,          raster,
+                group_mode, num_groups, group_index, B_MN ? K : N, group_block_rows};
   kernel<<<2 * pairs, FUSED ? k2FusedThreads : k2Threads, S::kTotal, stream>>>(ta, tb, tc, p, tl, fp, maps);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -606,6 +682,28 @@ extern "C" int axb_gemm_bf16_2cta(const void* A, const void* B, void* C, int M, 
   AXB_GEMM2_CASE(true, false)
   AXB_GEMM2_CASE(true, true)
 #undef AXB_GEMM2_CASE
+  return -11;
+}
+
+// Grouped form on CTA pairs (same contract as axb_gemm_bf16_grouped, bf16 output).  `block_rows`
+// is the padding unit of the row groups: every group starts on a multiple of it, and mode 1's
+// `group_index` has one entry per block.  Returns -20 for what this kernel does not take.
+extern "C" int axb_gemm_bf16_grouped_2cta(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda,
+                                          int64_t ldb, int64_t ldc, int a_mn_major, int b_mn_major, int mode,
+                                          int num_groups, const int* group_index, int64_t c_group_stride,
+                                          int block_rows, int* status, int max_ctas, cudaStream_t stream) {
+  using namespace axb;
+  if (block_rows < k2TileM || (block_rows % k2TileM) != 0 || M < k2TileM || N < k2TileN) return -20;
+  if (mode == 1 && (a_mn_major || (M % block_rows) != 0)) return -20;
+  if (mode == 2 && (!a_mn_major || !b_mn_major)) return -20;
+#define AXB_GROUPED2_CASE(AM, BM)                                                                              \
+  if (a_mn_major == (AM ? 1 : 0) && b_mn_major == (BM ? 1 : 0))                                                \
+    return launch_gemm2<AM, BM, __nv_bfloat16>(A, B, C, M, N, K, lda, ldb, ldc, 0, status, max_ctas, stream,   \
+                                               nullptr, mode, num_groups, group_index, c_group_stride, block_rows);
+  AXB_GROUPED2_CASE(false, false)
+  AXB_GROUPED2_CASE(false, true)
+  AXB_GROUPED2_CASE(true, true)
+#undef AXB_GROUPED2_CASE
   return -11;
 }
 

@@ -137,17 +137,21 @@ def combine(y: torch.Tensor, weight: torch.Tensor, dest: torch.Tensor) -> torch.
 # Grouped GEMM over expert-sorted, block-padded rows (drop-free mixture of experts).
 # ------------------------------------------------------------------------------------------
 
-GROUP_BLOCK = 128  # every expert's run of rows starts on a multiple of this
+# Every expert's run of rows starts on a multiple of this.  256 rows is one output tile of the
+# CTA-pair GEMM; AXB200_MOE_GROUP_BLOCK=128 keeps the single-CTA kernel's tile (less padding).
+GROUP_BLOCK = int(os.environ.get("AXB200_MOE_GROUP_BLOCK", "256"))
+if GROUP_BLOCK < 128 or GROUP_BLOCK % 128:
+    raise ValueError(f"AXB200_MOE_GROUP_BLOCK must be a multiple of 128, got {GROUP_BLOCK}")
 
 
 def padded_group_layout(expert_of_pair: torch.Tensor, num_experts: int):
     """Sorted, block-padded placement of ``P`` (token, choice) pairs.
 
-    Returns ``(dest [P] int32, offsets [E + 1] int32, block_expert [R / 128] int32, R)``: pair
-    ``p`` goes to row ``dest[p]`` of an ``[R, M]`` buffer in which expert ``e`` owns rows
-    ``[offsets[e], offsets[e + 1])`` (a multiple of 128 each, its pairs first -- in pair order --
-    and zero rows after them); ``block_expert`` names the owner of every 128-row block (-1 for
-    the unused tail).  ``R`` is a static bound, so nothing here synchronises with the host.
+    Returns ``(dest [P] int32, offsets [E + 1] int32, block_expert [R / GROUP_BLOCK] int32, R)``:
+    pair ``p`` goes to row ``dest[p]`` of an ``[R, M]`` buffer in which expert ``e`` owns rows
+    ``[offsets[e], offsets[e + 1])`` (a multiple of ``GROUP_BLOCK`` each, its pairs first -- in pair
+    order -- and zero rows after them); ``block_expert`` names the owner of every block of
+    ``GROUP_BLOCK`` rows (-1 for the unused tail).  ``R`` is a static bound, so nothing here synchronises with the host.
     """
     p = expert_of_pair.numel()
     flat = expert_of_pair.reshape(-1).long()
@@ -173,7 +177,7 @@ def _grouped_argtypes():
     if not getattr(h, "_axb_grouped_configured", False):
         h.axb_gemm_bf16_grouped.argtypes = [
             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int,
-            c_int, c_int, c_void_p, c_int64, c_void_p, c_int, c_void_p]
+            c_int, c_int, c_void_p, c_int64, c_int, c_void_p, c_int, c_void_p]
         h.axb_gemm_bf16_grouped.restype = c_int
         h._axb_grouped_configured = True  # pylint: disable=protected-access
     return h
@@ -187,7 +191,7 @@ def _gmm_kernel(x, w, block_expert, transpose_w: bool):
     out = torch.zeros((rows, n), dtype=torch.bfloat16, device=x.device)
     rc = _grouped_argtypes().axb_gemm_bf16_grouped(
         x.data_ptr(), w.data_ptr(), out.data_ptr(), rows, n, k, x.stride(0), w.stride(1), out.stride(0),
-        0, 0 if transpose_w else 1, 0, 1, e, block_expert.data_ptr(), 0,
+        0, 0 if transpose_w else 1, 0, 1, e, block_expert.data_ptr(), 0, GROUP_BLOCK,
         cuda_ops.status_word(x.device).data_ptr(), 0, cuda_ops._stream())  # pylint: disable=protected-access
     cuda_ops._check(rc, "axb_gemm_bf16_grouped")  # pylint: disable=protected-access
     return out
@@ -200,7 +204,7 @@ def _tgmm_kernel(x, dy, offsets, num_experts: int):
     dw = torch.empty((num_experts, k, n), dtype=torch.bfloat16, device=x.device)
     rc = _grouped_argtypes().axb_gemm_bf16_grouped(
         x.data_ptr(), dy.data_ptr(), dw.data_ptr(), k, n, rows, x.stride(0), dy.stride(0), n,
-        1, 1, 0, 2, num_experts, offsets.data_ptr(), k * n,
+        1, 1, 0, 2, num_experts, offsets.data_ptr(), k * n, GROUP_BLOCK,
         cuda_ops.status_word(x.device).data_ptr(), 0, cuda_ops._stream())  # pylint: disable=protected-access
     cuda_ops._check(rc, "axb_gemm_bf16_grouped")  # pylint: disable=protected-access
     return dw

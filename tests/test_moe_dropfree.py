@@ -48,8 +48,9 @@ def test_padded_layout_properties():
     experts = torch.randint(0, 6, (3, 50))
     experts[experts == 4] = 1                      # an empty expert
     dest, offsets, block_expert, rows = moe_ops.padded_group_layout(experts, 6)
-    assert rows % 128 == 0 and offsets[-1] <= rows
-    assert (offsets % 128 == 0).all() and offsets[4] == offsets[5]
+    blk = moe_ops.GROUP_BLOCK
+    assert rows % blk == 0 and offsets[-1] <= rows
+    assert (offsets % blk == 0).all() and offsets[4] == offsets[5]
     flat, d = experts.reshape(-1), dest.long()
     assert d.unique().numel() == flat.numel()
     assert ((d >= offsets[flat.long()]) & (d < offsets[flat.long() + 1])).all()
@@ -59,9 +60,9 @@ def test_padded_layout_properties():
         assert (mine[1:] > mine[:-1]).all()
     for b, e in enumerate(block_expert.tolist()):
         if e >= 0:
-            assert offsets[e] <= b * 128 < offsets[e + 1]
+            assert offsets[e] <= b * blk < offsets[e + 1]
         else:
-            assert b * 128 >= offsets[-1]
+            assert b * blk >= offsets[-1]
 
 
 def test_dropfree_layer_matches_per_token_loop():
@@ -107,7 +108,7 @@ def test_convert_dense_to_moe():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("num_experts,k_dim,n_dim", [(4, 256, 512), (8, 128, 192), (3, 512, 64)])
+@pytest.mark.parametrize("num_experts,k_dim,n_dim", [(4, 256, 512), (8, 128, 192), (3, 512, 64), (8, 1024, 640)])
 def test_grouped_linear_kernel_matches_reference(num_experts, k_dim, n_dim):
     from axlearn_b200.ops import cuda_ops
 
