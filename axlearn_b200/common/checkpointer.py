@@ -465,11 +465,13 @@ class TensorStoreStateStorage(Configurable):
                             json.dump(st, f)
                 _commit_across_processes(ckpt_dir, rank=rank, nproc=nproc, timeout_secs=cfg.timeout_secs)
                 if rank == 0:
+                    # Markers go first: the callback may move the directory, and a crash between
+                    # the two leaves an uncommitted checkpoint either way.
+                    _clear_commit_markers(ckpt_dir)
                     if on_commit_callback is not None:
                         on_commit_callback(ckpt_dir=ckpt_dir, step=step, entries=entries)
                     else:
                         write_index_file(ckpt_dir, step=step, entries=entries)
-                    _clear_commit_markers(ckpt_dir)
             except BaseException as e:  # pylint: disable=broad-except
                 self._error = e
 

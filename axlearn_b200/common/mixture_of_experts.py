@@ -724,11 +724,22 @@ class TransformerFeedForwardDropFreeMoE(TransformerFeedForwardMoE):
     fused elementwise kernel, and the outputs are gathered back and summed over the K choices
     with the routing weights in fp32.  Nothing synchronises with the host: ``R`` is the static
     bound ``pairs + E * (block - 1)`` rounded up to the block.
+
+    With an ``expert`` mesh axis every rank keeps ``E / ep`` experts: tokens and routing decisions
+    are all-gathered over the axis, each rank runs the pairs of its own experts, and a
+    reduce-scatter sums the partial outputs back (the counterpart of the reference's ragged
+    all-to-all pair, :2139-2178, with static sizes: per token the gather moves ``M`` values in
+    and the scatter ``M`` values out per rank of the axis, independent of ``K``).
     """
 
     @config_class
     class Config(TransformerFeedForwardMoE.Config):
         seq_load_balance_loss_weight: Optional[float] = None
+        # With experts sharded over the ``expert`` mesh axis: None sizes every rank's row buffer
+        # for the worst case (all pairs of the axis choose this rank's experts; nothing is ever
+        # dropped); a number caps it at that multiple of the fair share (``tokens * K`` rows),
+        # and pairs beyond the cap are dropped as in the reference's approximate variant.
+        expert_parallel_capacity: Optional[float] = None
         # Accepted for config compatibility with the reference (Pallas tile sizes / backend
         # choice); the grouped kernel has one tiling.
         tiling: Any = None
@@ -761,13 +772,34 @@ class TransformerFeedForwardDropFreeMoE(TransformerFeedForwardMoE):
         k = routing.gate_assignment.shape[-1]
         tokens = x3.shape[0] * x3.shape[1]
         assignment = routing.gate_assignment.reshape(tokens, k)
+        weights = routing.expert_weights.reshape(tokens, k)
+        xt = x3.reshape(tokens, m)
+        ep = self._expert_parallel_size()
+        num_local, max_rows = cfg.num_experts, None
+        if ep > 1:
+            # Expert parallelism without a capacity: every rank of the expert axis sees the tokens
+            # and routing decisions of the whole axis (all-gather), runs the pairs that chose ITS
+            # experts through the grouped GEMMs, and the partial outputs are summed back to the
+            # tokens' owners (reduce-scatter).  All sizes are static, so nothing waits for the
+            # host; the blocks of the row buffer that stay unused are skipped by the kernels.
+            num_local = cfg.num_experts // ep
+            xt = coll.all_gather(xt, "expert", dim=0)
+            weights = coll.all_gather(weights, "expert", dim=0)
+            assignment = coll.all_gather_raw(assignment.contiguous(), current_mesh().group("expert"), ep, dim=0)
+            local = assignment - coll.axis_index("expert") * num_local
+            assignment = torch.where((local >= 0) & (local < num_local), local, torch.full_like(local, -1))
+            if cfg.expert_parallel_capacity is not None:
+                max_rows = int(math.ceil(cfg.expert_parallel_capacity * tokens * k))
+        all_tokens = xt.shape[0]
         # Choice-major pair order decides the order inside an expert's run.
         dest_km, offsets, block_expert, rows = moe_ops.padded_group_layout(
-            assignment.t().contiguous(), cfg.num_experts)
-        dest = dest_km.reshape(k, tokens).t().contiguous()                        # [T, K]
-        xs = moe_ops.dispatch(x3.reshape(tokens, m), dest, rows)                 # [R, M]
+            assignment.t().contiguous(), num_local, max_rows=max_rows)
+        dest = dest_km.reshape(k, all_tokens).t().contiguous()                    # [T, K]
+        xs = moe_ops.dispatch(xt, dest, rows)                                     # [R, M]
         ys = self._grouped_ffn(xs, offsets, block_expert)
-        out = moe_ops.combine(ys, routing.expert_weights.reshape(tokens, k), dest)
+        out = moe_ops.combine(ys, weights, dest)
+        if ep > 1:
+            out = coll.reduce_scatter(out, "expert", dim=0)
         return out.to(in_dtype).reshape(*token_shape, m)
 
     def _grouped_ffn(self, xs: Tensor, offsets: Tensor, block_expert: Tensor) -> Tensor:

@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+from typing import Optional
 
 import torch
 
@@ -144,28 +145,43 @@ if GROUP_BLOCK < 128 or GROUP_BLOCK % 128:
     raise ValueError(f"AXB200_MOE_GROUP_BLOCK must be a multiple of 128, got {GROUP_BLOCK}")
 
 
-def padded_group_layout(expert_of_pair: torch.Tensor, num_experts: int):
+def padded_group_layout(expert_of_pair: torch.Tensor, num_experts: int, max_rows: Optional[int] = None):
     """Sorted, block-padded placement of ``P`` (token, choice) pairs.
 
     Returns ``(dest [P] int32, offsets [E + 1] int32, block_expert [R / GROUP_BLOCK] int32, R)``:
     pair ``p`` goes to row ``dest[p]`` of an ``[R, M]`` buffer in which expert ``e`` owns rows
     ``[offsets[e], offsets[e + 1])`` (a multiple of ``GROUP_BLOCK`` each, its pairs first -- in pair
     order -- and zero rows after them); ``block_expert`` names the owner of every block of
-    ``GROUP_BLOCK`` rows (-1 for the unused tail).  ``R`` is a static bound, so nothing here synchronises with the host.
+    ``GROUP_BLOCK`` rows (-1 for the unused tail).  ``R`` is a static bound, so nothing here
+    synchronises with the host.
+
+    Pairs whose expert is negative (an expert that lives on another rank) get ``dest = -1``.  With
+    ``max_rows`` the buffer is capped at that many rows (rounded up to the block): runs are cut at
+    the cap and the pairs beyond it get ``dest = -1`` as well.
     """
     p = expert_of_pair.numel()
     flat = expert_of_pair.reshape(-1).long()
-    counts = torch.bincount(flat, minlength=num_experts)
+    absent = flat < 0
+    flat = torch.where(absent, torch.full_like(flat, num_experts), flat)      # bucket E = "not here"
+    counts = torch.bincount(flat, minlength=num_experts + 1)[:num_experts + 1]
     padded = (counts + GROUP_BLOCK - 1) // GROUP_BLOCK * GROUP_BLOCK
-    offsets = torch.zeros(num_experts + 1, dtype=torch.long, device=flat.device)
+    padded[num_experts] = 0
+    offsets = torch.zeros(num_experts + 2, dtype=torch.long, device=flat.device)
     offsets[1:] = torch.cumsum(padded, 0)
+    rows = (p + num_experts * (GROUP_BLOCK - 1) + GROUP_BLOCK - 1) // GROUP_BLOCK * GROUP_BLOCK
+    if max_rows is not None:
+        rows = min(rows, (max_rows + GROUP_BLOCK - 1) // GROUP_BLOCK * GROUP_BLOCK)
+        offsets = offsets.clamp(max=rows)
     order = torch.argsort(flat, stable=True)
     start_unpadded = torch.cumsum(counts, 0) - counts
     sorted_expert = flat[order]
     rank_in_expert = torch.arange(p, device=flat.device) - start_unpadded[sorted_expert]
+    dest_sorted = offsets[:-1][sorted_expert] + rank_in_expert
+    dest_sorted = torch.where((sorted_expert < num_experts) & (dest_sorted < offsets[1:][sorted_expert]),
+                              dest_sorted, torch.full_like(dest_sorted, -1))
     dest = torch.empty(p, dtype=torch.long, device=flat.device)
-    dest[order] = offsets[:-1][sorted_expert] + rank_in_expert
-    rows = (p + num_experts * (GROUP_BLOCK - 1) + GROUP_BLOCK - 1) // GROUP_BLOCK * GROUP_BLOCK
+    dest[order] = dest_sorted
+    offsets = offsets[:num_experts + 1]
     block_start = torch.arange(rows // GROUP_BLOCK, device=flat.device) * GROUP_BLOCK
     block_expert = torch.searchsorted(offsets[1:].contiguous(), block_start, right=True)
     block_expert = torch.where(block_start < offsets[-1], block_expert, torch.full_like(block_expert, -1))
