@@ -31,7 +31,8 @@ import torch
 
 from axlearn_b200 import ops
 from axlearn_b200.common.base_layer import BaseLayer, ParameterSpec
-from axlearn_b200.common.config import config_class
+from axlearn_b200.common import prng
+from axlearn_b200.common.config import InstantiableConfig, config_class
 from axlearn_b200.common.module import nowrap
 from axlearn_b200.common.param_init import constant_initializer
 from axlearn_b200.ops import fp8_ops
@@ -49,6 +50,13 @@ def get_all_fp8_param_names() -> list[str]:
 class DotGeneralQuantizationType(enum.Enum):
     INT_8 = "int8"
     FP_8 = "fp8"
+
+
+class ClippingChoice(enum.Enum):
+    """Which tensor the activation-clipping child is applied to."""
+
+    INPUT_ACTIVATION = 0
+    OUTPUT_ACTIVATION = 1
 
 
 def compute_scale(amax: Tensor, scale: Tensor, fp8_max: float) -> Tensor:
@@ -113,6 +121,14 @@ class QuantizedDotGeneral(BaseLayer):
         quantization_type: Optional[DotGeneralQuantizationType] = DotGeneralQuantizationType.FP_8
         fp8_amax_history_length: int = 128
         scaling: str = "block"   # "block" | "tensor"
+        # int8 only: a BaseActivationClippingLayer config applied to the input or the output.
+        activation_clipping: Optional[InstantiableConfig] = None
+        clipping_choice: ClippingChoice = ClippingChoice.INPUT_ACTIVATION
+
+    def __init__(self, cfg, *, parent=None):
+        super().__init__(cfg, parent=parent)
+        if self._config.activation_clipping is not None:
+            self._add_child("activation_clipping", self._config.activation_clipping)
 
     def _create_layer_parameter_specs(self):
         cfg = self._config
@@ -133,7 +149,19 @@ class QuantizedDotGeneral(BaseLayer):
         if cfg.quantization_type is None:
             return ops.linear(x, w)
         if cfg.quantization_type == DotGeneralQuantizationType.INT_8:
-            return _int8_matmul(x, w)
+            clip = self._children.get("activation_clipping")
+            if clip is not None and cfg.clipping_choice == ClippingChoice.INPUT_ACTIVATION:
+                x = clip(x)
+            # Stochastic rounding of the output gradient draws from this layer's PRNG stream
+            # while training (deterministic round-to-nearest otherwise).
+            seed = None
+            key = self.get_invocation_context().prng_key
+            if self.is_training and key is not None:
+                seed = prng.seed_of(key) % (2**31 - 1)
+            y = _Int8DotGeneral.apply(x, w.to(x.dtype), seed)
+            if clip is not None and cfg.clipping_choice == ClippingChoice.OUTPUT_ACTIVATION:
+                y = clip(y)
+            return y
         if cfg.scaling == "tensor":
             params = self.parameters
             delayed = "input_amax_history" in params
@@ -151,14 +179,50 @@ class QuantizedDotGeneral(BaseLayer):
         return fp8_ops.fp8_linear(x, w)
 
 
-def _int8_matmul(x: Tensor, w: Tensor) -> Tensor:
-    """Symmetric per-row (activations) / per-column (weights) int8 with a straight-through
-    gradient."""
-    sx = x.detach().abs().amax(dim=-1, keepdim=True).float().clamp_min(1e-12) / 127.0
-    sw = w.detach().abs().amax(dim=0, keepdim=True).float().clamp_min(1e-12) / 127.0
-    xq = torch.round(x.float() / sx).clamp(-127, 127) * sx
-    wq = torch.round(w.float() / sw).clamp(-127, 127) * sw
-    # Straight-through: forward uses the quantised values, backward the identity.
-    xs = x.float() + (xq - x.float()).detach()
-    ws = w.float() + (wq - w.float()).detach()
-    return (xs @ ws).to(x.dtype)
+def _quantize_int8(t: Tensor, dim: int, *, noise: Optional[Tensor] = None) -> tuple[Tensor, Tensor]:
+    """Symmetric int8 along ``dim`` (the contraction dim): returns the integer-valued tensor (in
+    ``t``'s dtype; every integer in [-127, 127] is exact in bf16) and the fp32 scales.  With
+    ``noise`` (uniform in [0, 1)) the rounding is stochastic: ``floor(v + u)``, unbiased."""
+    scale = t.detach().abs().amax(dim=dim, keepdim=True).float().clamp_min(1e-30) / 127.0
+    v = t.float() / scale
+    q = torch.floor(v + noise) if noise is not None else torch.round(v)
+    return q.clamp(-127, 127).to(t.dtype), scale
+
+
+class _Int8DotGeneral(torch.autograd.Function):
+    """``x [..., K] @ w [K, N]`` on the int8 grid, the reference's default recipe (AQT ``config_v3``
+    through ``lhs_activation_aqt_config``, axlearn/common/quantized_dot_general/utils.py:26-48):
+
+    * forward: activations quantised per row, weights per output column (both over K), products
+      accumulated exactly, result rescaled by the two scales;
+    * input gradient: the output gradient quantised per row over N with STOCHASTIC rounding and
+      the weights re-quantised per input row (over N);
+    * weight gradient: not quantised.
+
+    The integer-valued operands travel as bf16 (exact) through the framework's tensor-core GEMM
+    with fp32 accumulation; an int32 accumulator would differ only where a sum exceeds 2^24."""
+
+    @staticmethod
+    def forward(ctx, x, w, seed):
+        xq, sx = _quantize_int8(x, -1)
+        wq, sw = _quantize_int8(w, 0)
+        ctx.save_for_backward(x, w)
+        ctx.seed = seed
+        y = ops.linear(xq, wq).float() * sx * sw
+        return y.to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            noise = None
+            if ctx.seed is not None:
+                gen = torch.Generator(device=dy.device).manual_seed(ctx.seed)
+                noise = torch.rand(dy.shape, generator=gen, device=dy.device, dtype=torch.float32)
+            gq, sg = _quantize_int8(dy, -1, noise=noise)
+            wq, sw = _quantize_int8(w, 1)                                  # per input row, over N
+            dx = (ops.linear(gq, wq.t().contiguous()).float() * sg * sw.reshape(-1)).to(x.dtype)
+        if ctx.needs_input_grad[1]:
+            dw = (x.reshape(-1, x.shape[-1]).t().float() @ dy.reshape(-1, dy.shape[-1]).float()).to(w.dtype)
+        return dx, dw, None
