@@ -113,7 +113,7 @@ def test_tar_bundler(tmp_path):
         assert tar.getnames() == ["pkg/mod.py"]
     assert "tar -xzf" in TarBundler.install_command(out, dest="/tmp/x")
     with pytest.raises(NotImplementedError):
-        get_bundler_config(bundler_type="docker")
+        get_bundler_config(bundler_type="no-such-bundler")
 
 
 def _bastion(tmp_path, gpus=8, cleaner=False, shares=None):
