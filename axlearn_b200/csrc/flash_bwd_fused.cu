@@ -447,7 +447,7 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
               val = th * p.cap_out;
               w = 1.f - th * th;
             }
-            float pr = exp2f(val * p.sc - ls[u]);
+            float pr = ex2_approx(val * p.sc - ls[u]);
             if (need_mask) {
               const int cc = half * 64 + c;
               if (cc < c_min || cc > c_max) pr = 0.f;

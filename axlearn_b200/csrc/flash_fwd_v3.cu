@@ -20,6 +20,8 @@
 //
 // Reference kernels being replaced: axlearn/common/flash_attention/gpu_attention.py:114-243
 // (segment ids :179-205, block skipping by mask_fn) and the cuDNN call at :792-926.
+#include <stdlib.h>
+
 #include "host_utils.cuh"
 #include "sm100.cuh"
 
@@ -28,9 +30,13 @@ namespace axb {
 int make_bthd_map(CUtensorMap* map, const void* base, int B, int L, int N, int H, int box_rows);
 
 constexpr int kF3Threads = 640;
-// 640 threads launch with 96 registers each.  The softmax warps hold at most 32 scores at a time
-// (scores are re-read from tensor memory for the second pass), which fits without spills, so no
-// register redistribution (setmaxnreg) is needed.
+// 640 threads launch with 96 registers each.  The first warpgroup (producer, MMA issuer, two idle
+// warps) gives registers back and the sixteen softmax warps take them, so that a softmax thread
+// can hold all 64 scores of its half row at once: both tensor-memory loads of a key tile are in
+// flight together, and the exponentials are computed from registers instead of a second load.
+constexpr int kF3LaunchRegs = 96, kF3LightRegs = 64, kF3SoftmaxRegs = 104;
+static_assert(128 * kF3LightRegs + 512 * kF3SoftmaxRegs <= kF3Threads * kF3LaunchRegs,
+              "setmaxnreg split exceeds the launch allocation");
 constexpr uint32_t kGaveUp = 0x7fc0dead;  // NaN payload: "my wait on the score tile timed out"
 
 struct FlashFwd3Params {
@@ -70,39 +76,46 @@ __device__ __forceinline__ float tanh_approx(float x) {
   return y;
 }
 
-// 2^x for x <= 0 (x = -inf allowed) on the FMA and integer pipes: the exponential unit is the
-// scarcest resource of the softmax (16 results per clock and SM), so a fixed share of the
-// exponentials is evaluated here instead.  Round-to-nearest split x = n + f with f in
-// [-0.5, 0.5] through the 1.5 * 2^23 trick, a degree-3 minimax polynomial for 2^f (relative
-// error 7.5e-5, far below the bf16 rounding of the result) and n added into the exponent field.
-__device__ __forceinline__ float exp2_poly(float x) {
-  x = fmaxf(x, -126.f);
-  const float r = __fadd_rn(x, 12582912.f);
-  const float f = __fsub_rn(x, __fsub_rn(r, 12582912.f));
-  float p = fmaf(0.0551716685f, f, 0.2426111251f);
-  p = fmaf(p, f, 0.6932609677f);
-  p = fmaf(p, f, 0.9999280572f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(r) << 23));
+// Two-wide fp32 arithmetic (one issue slot for two lanes of work on the FMA pipe).
+__device__ __forceinline__ uint64_t f32x2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void f32x2_split(uint64_t v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
 }
 
-// Of the eight batches of eight exponentials per thread and key tile, this many use exp2_poly
-// (the rest the exponential unit).  Measured on B200: with scalar FMA instructions the
-// polynomial costs more issue slots than the exponential unit saves, so the share is zero; the
-// routine stays for experiments with packed two-wide FMA.
-constexpr int kPolyBatches = 0;
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 
-// e[u] = 2^(s[u] * sc - m) for eight scores.
-__device__ __forceinline__ void exp2_batch8(const uint32_t* s, float sc, float m, float (&e)[8], bool poly) {
+// e[u] = 2^(s[u] * sc - m) for eight scores; the scaling runs two values per instruction.
+//
+// Evaluating a share of the exponentials with a polynomial on the FMA pipe (round-to-nearest
+// split, degree-3 minimax, exponent add; two-wide FMAs, about 5.5 issue slots per value) was
+// measured on B200 at 25 % / 37 % / 50 % of the values: 886 / 836 / 831 TFLOP/s against 910 with
+// the exponential unit alone (b4, T 4096, 32 heads, d 128).  The softmax warps are short of issue
+// slots and latency, not of exponential throughput, so every exponential stays on the unit.
+__device__ __forceinline__ void exp2_batch8(const uint32_t* s, uint64_t sc2, uint64_t nm2, float (&e)[8]) {
   float a[8];
 #pragma unroll
-  for (int u = 0; u < 8; ++u) a[u] = fmaf(__uint_as_float(s[u]), sc, -m);
-  if (poly) {
+  for (int u = 0; u < 8; u += 2)
+    f32x2_split(fma2(f32x2(__uint_as_float(s[u]), __uint_as_float(s[u + 1])), sc2, nm2), a[u], a[u + 1]);
 #pragma unroll
-    for (int u = 0; u < 8; ++u) e[u] = exp2_poly(a[u]);
-  } else {
-#pragma unroll
-    for (int u = 0; u < 8; ++u) e[u] = exp2f(a[u]);
-  }
+  for (int u = 0; u < 8; ++u) e[u] = ex2_approx(a[u]);
 }
 
 // kGeneral: segment ids / sliding window / logit cap are honoured (every tile takes the masking
@@ -190,6 +203,7 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");  // kF3LightRegs
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one() && any) {
@@ -232,26 +246,34 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       constexpr uint32_t idesc_qk = umma_idesc_f16(128, 128, 1, 1, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_f16(128, H, 1, 1, 0, 1);
       bool ok = mbar_wait(q_full, 0, p.status, kStatusWaitTimeoutMma);
+      // Descriptors are assembled from a per-operand low word plus an immediate: the high word
+      // (stride between 8-row groups, version, swizzle mode) is the same constant for every
+      // operand, so the issuer keeps a handful of registers instead of one 64-bit value per MMA.
+      constexpr uint32_t kDescHi = ((1024u >> 4) & 0x3FFF) | (1u << 14) | (2u << 29);
+      auto desc_lo = [](uint32_t addr, uint32_t lbo) { return ((addr >> 4) & 0x3FFFu) | (((lbo >> 4) & 0x3FFFu) << 16); };
+      auto desc = [](uint32_t lo) {
+        uint64_t d;
+        asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(kDescHi));
+        return d;
+      };
       auto issue_qk = [&](int x, int st) {
-        const uint32_t q_addr = smem_u32(smem + L::kQ + x * L::kTile);
-        const uint32_t k_addr = smem_u32(smem + L::kK + st * L::kTile);
+        const uint32_t q_lo = desc_lo(smem_u32(smem + L::kQ + x * L::kTile), 16);
+        const uint32_t k_lo = desc_lo(smem_u32(smem + L::kK + st * L::kTile), 16);
 #pragma unroll
         for (int kk = 0; kk < H / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * L::kSub + (kk & 3) * 32;
-          tc_mma_f16(tmem_base + x * 128, umma_smem_desc(q_addr + off, 16, 1024),
-                     umma_smem_desc(k_addr + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+          const uint32_t off = ((kk >> 2) * L::kSub + (kk & 3) * 32) >> 4;
+          tc_mma_f16(tmem_base + x * 128, desc(q_lo + off), desc(k_lo + off), idesc_qk, kk > 0 ? 1u : 0u);
         }
         tc_commit(&s_full[x]);
       };
       auto issue_pv = [&](int x, int st, bool first) {
-        const uint32_t v_addr = smem_u32(smem + L::kV + st * L::kTile);
+        const uint32_t v_lo = desc_lo(smem_u32(smem + L::kV + st * L::kTile), L::kSub);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           // 16 keys per step: 8 TMEM columns of packed bf16 pairs; 16 V rows = 2048 B.
           // keys 0-63 (first half's probabilities) at columns 0-31, keys 64-127 at columns 64-95
           tc_mma_f16_ts(tmem_base + 256 + x * 128, tmem_base + x * 128 + (kk >> 2) * 64 + (kk & 3) * 8,
-                        umma_smem_desc(v_addr + kk * 2048, L::kSub, 1024), idesc_pv,
-                        (!first || kk > 0) ? 1u : 0u);
+                        desc(v_lo + ((kk * 2048) >> 4)), idesc_pv, (!first || kk > 0) ? 1u : 0u);
         }
       };
       // Prologue: scores of the first key tile for the query tiles that start there.
@@ -293,6 +315,7 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   }
   } else {
     // ------------------------------------------------------------------ softmax / epilogue
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");  // kF3SoftmaxRegs
     const int idx = warp - 4;
     const int x = idx >> 3;               // query tile
     const int half = (idx >> 2) & 1;      // which 64 score columns / which half of the O columns
@@ -328,13 +351,10 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       // halves always reach it, and a failed wait travels through the exchange slot.
       const bool got = mbar_wait_warp(&s_full[x], kpar, p.status, kStatusWaitTimeoutEpilogue);
       const int s0 = it * 128 + half * 64;  // first key column of this thread
-      // Scores are read from tensor memory twice, 32 columns at a time (once for the row maximum,
-      // once for the exponentials): a TMEM read is cheap, while keeping all 64 scores of the row
-      // in registers next to the packed probabilities does not fit the register budget and
-      // spilled into the hot loop.  Masks and the logit cap are part of the load.
-      auto load_scores = [&](int hh, uint32_t (&r)[32]) {
-        tmem_ld_32x32(s_addr + hh * 32, r);
-        tmem_ld_wait();
+      // All 64 scores of this thread's half row are loaded at once (two loads in flight, one
+      // wait) and stay in registers for both passes.  Masks and the logit cap are applied once.
+      uint32_t r0[32], r1[32];
+      auto mask_scores = [&](int hh, uint32_t (&r)[32]) {
         const int c0 = s0 + hh * 32;
         const uint32_t ninf = __float_as_uint(-INFINITY);
         if (kGeneral) {
@@ -365,24 +385,27 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           }
         }
       };
+      auto row_max = [&](const uint32_t (&r)[32]) {
+        // Four independent chains of three-input maxima.
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          mx0 = max3(mx0, __uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+          mx1 = max3(mx1, __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+          mx2 = max3(mx2, __uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+          mx3 = max3(mx3, __uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+        }
+        return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      };
       float tmax = -INFINITY;
       if (got) {
         tc_fence_after_sync();
-#pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          uint32_t r[32];
-          load_scores(hh, r);
-          // Row maximum: four independent chains.
-          float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            mx0 = fmaxf(mx0, __uint_as_float(r[j]));
-            mx1 = fmaxf(mx1, __uint_as_float(r[j + 1]));
-            mx2 = fmaxf(mx2, __uint_as_float(r[j + 2]));
-            mx3 = fmaxf(mx3, __uint_as_float(r[j + 3]));
-          }
-          tmax = fmaxf(tmax, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
-        }
+        tmem_ld_32x32(s_addr, r0);
+        tmem_ld_32x32(s_addr + 32, r1);
+        tmem_ld_wait();
+        mask_scores(0, r0);
+        mask_scores(1, r1);
+        tmax = fmaxf(row_max(r0), row_max(r1));
       }
       my_max[kpar * 512] = got ? tmax : __uint_as_float(kGaveUp);
       pair_barrier(bar_id);
@@ -405,13 +428,13 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         // s_full of this tile was committed after the previous P*V of this query tile, so O is
         // quiescent; each half rescales its own O columns.
 #pragma unroll 1
-        for (int c = 0; c < H / 2; c += 32) {
-          uint32_t o[32];
-          tmem_ld_32x32(o_addr + c, o);
+        for (int c = 0; c < H / 2; c += 16) {  // 16 columns at a time: the 64 scores stay in registers
+          uint32_t o[16];
+          tmem_ld_32x16(o_addr + c, o);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-          tmem_st_32x32(o_addr + c, o);
+          for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+          tmem_st_32x16(o_addr + c, o);
         }
         l_sum *= alpha;
       }
@@ -421,22 +444,28 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       // probabilities overlay the first 32 columns of its OWN 64 score columns (the chunk being
       // written was consumed just before, the other chunk lies beyond), so the two halves of a
       // row never touch each other's columns.
-      float l0 = 0.f, l1 = 0.f;
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        uint32_t r[32], q[16];
-        load_scores(hh, r);
+      const uint64_t sc2 = f32x2(p.sc, p.sc), nm2 = f32x2(-m_use, -m_use);
+      uint64_t acc0 = f32x2(0.f, 0.f), acc1 = acc0;   // row sums, two lanes each
+      auto write_probs = [&](int hh, const uint32_t (&r)[32]) {
+        uint32_t q[16];
 #pragma unroll
         for (int j0 = 0; j0 < 32; j0 += 8) {
           float e[8];
-          exp2_batch8(r + j0, p.sc, m_use, e, (hh * 4 + (j0 >> 3)) < kPolyBatches);
+          exp2_batch8(r + j0, sc2, nm2, e);
 #pragma unroll
           for (int u = 0; u < 4; ++u) q[(j0 >> 1) + u] = pack_bf16x2(e[2 * u], e[2 * u + 1]);
-          l0 += (e[0] + e[1]) + (e[2] + e[3]);
-          l1 += (e[4] + e[5]) + (e[6] + e[7]);
+          acc0 = add2(acc0, add2(f32x2(e[0], e[1]), f32x2(e[2], e[3])));
+          acc1 = add2(acc1, add2(f32x2(e[4], e[5]), f32x2(e[6], e[7])));
         }
         tmem_st_32x16(p_addr + hh * 16, q);
-      }
+      };
+      write_probs(0, r0);
+      write_probs(1, r1);
+      float l0, l1, l2, l3;
+      f32x2_split(acc0, l0, l1);
+      f32x2_split(acc1, l2, l3);
+      l0 += l2;
+      l1 += l3;
       l_sum += l0 + l1;
       tmem_st_wait();
       tc_fence_before_sync();
@@ -559,6 +588,15 @@ static int launch_flash_fwd3(const void* q, const void* k, const void* v, FlashF
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F3Smem<H>::kTotal) != cudaSuccess)
       return -3;
+    // The in-kernel register redistribution only balances if the launch allocates exactly the
+    // assumed count per thread; refuse to launch a build for which it does not.
+    cudaFuncAttributes attr;
+    if (cudaFuncGetAttributes(&attr, kernel) != cudaSuccess) return -3;
+    if (attr.numRegs != kF3LaunchRegs) {
+      fprintf(stderr, "axb flash fwd: built with %d registers per thread, the kernel assumes %d\n", attr.numRegs,
+              kF3LaunchRegs);
+      return -5;
+    }
     configured = true;
   }
   dim3 grid((p.T + 255) / 256, p.N, p.B);

@@ -195,6 +195,15 @@ __device__ __forceinline__ void tma_store_wait() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// 2^x on the special-function unit in ONE instruction (results below 2^-126 flush to zero;
+// 2^-inf = 0).  `exp2f` without fast-math wraps the same instruction in a denormal-preserving
+// range fix-up (compare, scale, multiply back), which triples the issue slots of a softmax loop.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // ------------------------------------------------------------------------------ TMEM
 // Must be executed by all 32 lanes of one warp. ncols: power of two in [32, 512].
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {
