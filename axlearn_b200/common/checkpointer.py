@@ -201,10 +201,62 @@ class _Shard(NamedTuple):
     write_meta: bool
 
 
-def _zarray_meta(global_shape: Sequence[int], chunk_shape: Sequence[int], dtype_name: str) -> dict:
+def _compressor_meta(name: Optional[str]) -> Optional[dict]:
+    """``None`` (raw chunks, the default here) or the zarr-v2 compressor entry.  ``"zstd"`` is what
+    the reference's writer puts into its tensorstore spec (level 1)."""
+    if name in (None, "", "none"):
+        return None
+    if name == "zstd":
+        return {"id": "zstd", "level": 1}
+    if name in ("zlib", "gzip"):
+        return {"id": name, "level": 1}
+    raise ValueError(f"unknown chunk compressor {name!r}")
+
+
+def _encode_chunk(raw: bytes, compressor: Optional[dict]) -> bytes:
+    if compressor is None:
+        return raw
+    cid, level = compressor.get("id"), int(compressor.get("level", 1))
+    if cid == "zstd":
+        import pyarrow as pa
+
+        return pa.Codec("zstd", compression_level=level).compress(raw, asbytes=True)
+    if cid == "zlib":
+        import zlib
+
+        return zlib.compress(raw, level)
+    if cid == "gzip":
+        import gzip
+
+        return gzip.compress(raw, compresslevel=level)
+    raise ValueError(f"cannot write chunks with compressor {compressor!r}")
+
+
+def _decode_chunk(raw: bytes, compressor: Optional[dict], nbytes: int) -> bytes:
+    """Undoes the zarr-v2 ``compressor`` of one chunk (``nbytes`` = size of the decoded chunk)."""
+    if compressor is None:
+        return raw
+    cid = compressor.get("id")
+    if cid == "zstd":
+        import pyarrow as pa
+
+        return pa.Codec("zstd").decompress(raw, decompressed_size=nbytes, asbytes=True)
+    if cid == "zlib":
+        import zlib
+
+        return zlib.decompress(raw)
+    if cid == "gzip":
+        import gzip
+
+        return gzip.decompress(raw)
+    raise ValueError(f"chunks compressed with {compressor!r} cannot be read here (supported: none, zstd, zlib, gzip)")
+
+
+def _zarray_meta(global_shape: Sequence[int], chunk_shape: Sequence[int], dtype_name: str,
+                 compressor: Optional[dict] = None) -> dict:
     return {
         "chunks": list(chunk_shape) if len(chunk_shape) else [],
-        "compressor": None,
+        "compressor": compressor,
         "dimension_separator": ".",
         "dtype": _ZARR_DTYPE[dtype_name],
         "fill_value": None,
@@ -215,18 +267,18 @@ def _zarray_meta(global_shape: Sequence[int], chunk_shape: Sequence[int], dtype_
     }
 
 
-def _write_shard(ckpt_dir: str, s: _Shard) -> int:
+def _write_shard(ckpt_dir: str, s: _Shard, compressor: Optional[dict] = None) -> int:
     adir = os.path.join(ckpt_dir, "gda", s.path)
     os.makedirs(adir, exist_ok=True)
     if s.write_meta:
-        meta = _zarray_meta(s.global_shape, tuple(s.host.shape), _DTYPE_NAMES[s.host.dtype])
+        meta = _zarray_meta(s.global_shape, tuple(s.host.shape), _DTYPE_NAMES[s.host.dtype], compressor)
         with open(os.path.join(adir, ".zarray"), "w") as f:
             json.dump(meta, f)
     if s.write_chunk:
         name = ".".join(str(c) for c in s.coords) if s.coords else "0"
         arr = _to_numpy_bytes(s.host)
         with open(os.path.join(adir, name), "wb") as f:
-            f.write(arr.tobytes())
+            f.write(_encode_chunk(arr.tobytes(), compressor))
         return arr.nbytes
     return 0
 
@@ -238,9 +290,28 @@ def _read_array(ckpt_dir: str, path: str, *, want: tuple[slice, ...], dtype: Opt
         meta = json.load(f)
     stored = _NAME_TO_DTYPE[_ZARR_TO_NAME[meta["dtype"]]]
     shape, chunks = tuple(meta["shape"]), tuple(meta["chunks"])
+    compressor = meta.get("compressor")
+    if meta.get("filters"):
+        raise ValueError(f"{path}: zarr filters are not supported")
+    if meta.get("order", "C") != "C":
+        raise ValueError(f"{path}: only C-order chunks are supported")
+    sep = meta.get("dimension_separator", ".")
+    itemsize = torch.empty((), dtype=stored).element_size()
+
+    def load_chunk(name: str, chunk_shape: tuple) -> Optional[torch.Tensor]:
+        file = os.path.join(adir, name)
+        if not os.path.exists(file):
+            return None                      # never written: every element is the fill value
+        with open(file, "rb") as f:
+            raw = f.read()
+        return _from_bytes(_decode_chunk(raw, compressor, int(np.prod(chunk_shape, dtype=np.int64)) * itemsize),
+                           stored, chunk_shape)
+
+    fill = meta.get("fill_value") or 0
     if not shape:
-        with open(os.path.join(adir, "0"), "rb") as f:
-            t = _from_bytes(f.read(), stored, ())
+        t = load_chunk("0", ())
+        if t is None:
+            t = torch.full((), fill, dtype=stored)
         return t if dtype is None or dtype == stored else t.to(dtype)
     out_shape = tuple(s.stop - s.start for s in want)
     out = torch.empty(out_shape, dtype=stored)
@@ -249,14 +320,17 @@ def _read_array(ckpt_dir: str, path: str, *, want: tuple[slice, ...], dtype: Opt
         ranges.append(range(s.start // c, (s.stop - 1) // c + 1) if s.stop > s.start else range(0))
     for coords in np.ndindex(*[len(r) for r in ranges]):
         cidx = tuple(r[i] for r, i in zip(ranges, coords))
-        with open(os.path.join(adir, ".".join(str(c) for c in cidx)), "rb") as f:
-            chunk = _from_bytes(f.read(), stored, chunks)
+        # A chunk file always holds a whole chunk; at the array's edge the part beyond `shape` is padding.
+        chunk = load_chunk(sep.join(str(c) for c in cidx), chunks)
         src, dst = [], []
         for d, (ci, c, s) in enumerate(zip(cidx, chunks, want)):
             lo, hi = max(s.start, ci * c), min(s.stop, (ci + 1) * c)
             src.append(slice(lo - ci * c, hi - ci * c))
             dst.append(slice(lo - s.start, hi - s.start))
-        out[tuple(dst)] = chunk[tuple(src)]
+        if chunk is None:
+            out[tuple(dst)] = fill
+        else:
+            out[tuple(dst)] = chunk[tuple(src)]
     return out if dtype is None or dtype == stored else out.to(dtype)
 
 
@@ -379,6 +453,10 @@ class TensorStoreStateStorage(Configurable):
         # them, None / 0 = only the first holder writes).
         max_data_shard_degree: Optional[int] = None
         num_io_threads: int = 8
+        # Chunk compression: None (raw, the fastest to write from pinned host memory) or "zstd"
+        # (what the reference's tensorstore writer uses, level 1), "zlib", "gzip".  The reader
+        # handles all of them whatever this says.
+        compressor: Optional[str] = None
 
     def __init__(self, cfg):
         super().__init__(cfg)
@@ -409,7 +487,7 @@ class TensorStoreStateStorage(Configurable):
             try:
                 if event is not None:
                     event.synchronize()  # this array's device-to-host copy has landed
-                _write_shard(ckpt_dir, shard)
+                _write_shard(ckpt_dir, shard, _compressor_meta(cfg.compressor))
             finally:
                 with lock:
                     staged["now"] -= nbytes
