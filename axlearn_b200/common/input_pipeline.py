@@ -650,13 +650,17 @@ class PipelineInput(Input):
         axes = mesh.present_axes(("data", "expert", "fsdp"))
         return mesh.axis_size(axes), mesh.axis_index(axes)
 
+    def _make_source(self) -> Callable[[int, int], Stage]:
+        """``(shard_index, shard_count) -> Stage`` of examples; subclasses add per-example stages."""
+        cfg = self._config
+        return maybe_instantiate(cfg.source) if isinstance(cfg.source, InstantiableConfig) else cfg.source
+
     def _build(self) -> Stage:
         cfg = self._config
         feeds, index = self._feeds()
         if cfg.global_batch_size % feeds:
             raise ValueError(f"global batch {cfg.global_batch_size} is not divisible by {feeds} feeds")
-        make = maybe_instantiate(cfg.source) if isinstance(cfg.source, InstantiableConfig) else cfg.source
-        ds = make(index, feeds)
+        ds = self._make_source()(index, feeds)
         per_feed = cfg.global_batch_size // feeds
         if cfg.is_training:
             ds = ds.batch(per_feed, drop_remainder=True)
