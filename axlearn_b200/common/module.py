@@ -35,6 +35,7 @@ from typing import Any, Callable, NamedTuple, Optional, Sequence, TypeVar, Union
 import torch
 
 from axlearn_b200.common import prng
+from axlearn_b200.common import debug_utils, traceback_util
 from axlearn_b200.common.config import REQUIRED, Configurable, Required, config_class
 
 NestedTensor = Union[torch.Tensor, dict[str, Any]]
@@ -266,8 +267,16 @@ def _wrap_method(fn: Callable) -> Callable:
                     return self._call_in_context(fn, args, kwargs)
             finally:
                 torch.cuda.nvtx.range_pop()
-        with set_current_context(target):
-            return self._call_in_context(fn, args, kwargs)
+        try:
+            with set_current_context(target):
+                out = self._call_in_context(fn, args, kwargs)
+            if debug_utils.active_checks():
+                debug_utils.check_outputs(out, where=f"{self.path()} [{type(self).__name__}.{fn.__name__}]")
+            return out
+        except Exception as e:  # pylint: disable=broad-except
+            # One line per module on the way out: the traceback then names WHICH layer failed.
+            traceback_util.add_module_note(e, path=self.path(), cls=type(self).__name__, method=fn.__name__)
+            raise
 
     wrapped.__wrapped_module_method__ = True
     return wrapped
