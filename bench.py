@@ -43,6 +43,8 @@ def _args():
     ap.add_argument("--model", default="7B", help="Fuji size (7B is the benchmark; others for debugging), or an "
                     "envy preset with --family envy (Mixtral-8x7B: the MoE training configuration)")
     ap.add_argument("--family", default="fuji", choices=["fuji", "envy"])
+    ap.add_argument("--drop_free", action="store_true", help="--family envy: capacity-free routing on the grouped GEMM "
+                    "(TransformerFeedForwardDropFreeMoE) instead of the capacity-based layer")
     ap.add_argument("--fp8", action="store_true", help="block-scaled fp8 projection GEMMs (FP8ConfigModifier)")
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--per_gpu_batch", type=int, default=4)
@@ -249,7 +251,7 @@ def main():
             "impl": "ours",
             "config": {
                 "model": (f"envy-{args.model}" if moe else f"fuji-{args.model}-v2") + (
-                    f"-{args.layers}layers-DEBUG" if args.layers else ""),
+                    f"-{args.layers}layers-DEBUG" if args.layers else "") + ("-dropfree" if args.drop_free else ""),
                 "global_batch": global_batch, "seq_len": args.seq,
                 "parallelism": (args.mesh.replace("=", "").replace(",", "x") + " (non-headline mesh)") if args.mesh else (
                     f"expert{world} (dense parameters sharded over the same axis)" if moe else f"fsdp{world}"),
@@ -291,6 +293,8 @@ def _build_trainer(args, world, local_rank, use_cuda, *, layers, per_gpu_batch):
         mk = dict(envy.MODEL_PRESETS[args.model])
         if layers:
             mk["num_layers"] = layers
+        if args.drop_free:
+            mk["drop_free"] = True
         model_cfg = envy.model_config(scan_chunk=8192, **mk)
     else:
         mk = dict(kw["model_kwargs"])
