@@ -77,11 +77,13 @@ def test_gemm_deterministic():
     assert torch.equal(cuda_ops.gemm(a, b), cuda_ops.gemm(a, b))
 
 
-@pytest.mark.parametrize("m,n,k", [(64, 1536, 4096), (16, 2752, 4096), (8, 4096, 1376), (128, 4096, 11008), (1, 1536, 512)])
+@pytest.mark.parametrize("m,n,k", [(64, 1536, 4096), (16, 2752, 4096), (8, 4096, 1376), (128, 4096, 11008), (1, 1536, 512),
+                                   (8, 12288, 4096), (16, 22016, 4096), (48, 4096, 4096), (8, 32768, 4096), (5, 9504, 2112)])
 @pytest.mark.parametrize("b_t", [False, True])
 def test_skinny_gemm_split_k(m, n, k, b_t):
-    """Decode-shaped problems (one row block): 64-column tiles, split over K where the plan says
-    so; bf16 and fp32 outputs, with and without accumulation, repeated to exercise the counters."""
+    """Decode-shaped problems (one row block): 64-column tiles, split over K or cut into equal
+    runs of (tile, k-block) units per SM (stream-K) where the plan says so; bf16 and fp32 outputs,
+    with and without accumulation, repeated to exercise the counters."""
     from axlearn_b200.ops import cuda_ops
 
     torch.manual_seed(2)
