@@ -443,27 +443,47 @@ __global__ void rope_table_kernel(const int64_t* __restrict__ pos, float2* __res
   table[idx] = make_float2(s, c);
 }
 
+// One block handles `rows` (batch, position) rows of [N heads x H]; within a row a thread owns one
+// 16-byte vector position of the head (`pv`) and every `lanes`-th head, so the sines and cosines
+// of its four pairs are loaded once and reused over N / lanes heads, no index needs a division
+// beyond the row's position, and a thread keeps several independent 16-byte loads in flight.
+template <int kHeadsInFlight>
 __global__ void rope_apply_kernel(const Bf16x8* __restrict__ x, Bf16x8* __restrict__ y,
-                                  const float2* __restrict__ table, int64_t total_vec, int T, int N, int hp,
-                                  float sign) {
+                                  const float2* __restrict__ table, int64_t num_rows, int T, int N, int hp,
+                                  float sign, int lanes, int rows) {
   const int vec_per_head = hp / 4;  // 4 pairs (8 elements) per 16-byte vector
-  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total_vec;
-       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int pv = idx % vec_per_head;
-    const int64_t bt = idx / (static_cast<int64_t>(vec_per_head) * N);
-    const int t = bt % T;
+  const int per_row = vec_per_head * lanes;
+  const int r_in = threadIdx.x / per_row, j = threadIdx.x - r_in * per_row;
+  const int pv = j % vec_per_head, n0 = j / vec_per_head;
+  if (r_in >= rows) return;
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * rows + r_in; row < num_rows;
+       row += static_cast<int64_t>(gridDim.x) * rows) {
+    const int t = static_cast<int>(row % T);
     const float4* tab = reinterpret_cast<const float4*>(table + static_cast<int64_t>(t) * hp + pv * 4);
     const float4 sc0 = __ldg(tab), sc1 = __ldg(tab + 1);  // (s0, c0, s1, c1), (s2, c2, s3, c3)
     const float sn[4] = {sc0.x * sign, sc0.z * sign, sc1.x * sign, sc1.z * sign};
     const float cs[4] = {sc0.y, sc0.w, sc1.y, sc1.w};
-    const Bf16x8 v = x[idx];
-    Bf16x8 o;
+    const int64_t base = row * (static_cast<int64_t>(N) * vec_per_head) + pv;
+    for (int n = n0; n < N; n += lanes * kHeadsInFlight) {
+      Bf16x8 v[kHeadsInFlight];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = __bfloat1622float2(v.v[j]);
-      o.v[j] = __floats2bfloat162_rn(f.x * cs[j] - f.y * sn[j], f.y * cs[j] + f.x * sn[j]);
+      for (int u = 0; u < kHeadsInFlight; ++u) {
+        const int nn = n + u * lanes;
+        if (nn < N) v[u] = x[base + static_cast<int64_t>(nn) * vec_per_head];
+      }
+#pragma unroll
+      for (int u = 0; u < kHeadsInFlight; ++u) {
+        const int nn = n + u * lanes;
+        if (nn >= N) continue;
+        Bf16x8 o;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 f = __bfloat1622float2(v[u].v[q]);
+          o.v[q] = __floats2bfloat162_rn(f.x * cs[q] - f.y * sn[q], f.y * cs[q] + f.x * sn[q]);
+        }
+        y[base + static_cast<int64_t>(nn) * vec_per_head] = o;
+      }
     }
-    y[idx] = o;
   }
 }
 
@@ -965,13 +985,24 @@ extern "C" int axb_rope(const void* x, void* y, const int64_t* positions, int64_
   const int hp = H / 2;
   const int64_t total = B * T * static_cast<int64_t>(N) * hp;
   if (total <= 0) return 0;
-  if (table != nullptr && hp % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+  if (table != nullptr && hp % 4 == 0 && hp / 4 <= 256 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
       (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
     rope_table_kernel<<<(T * hp + 255) / 256, 256, 0, stream>>>(positions, reinterpret_cast<float2*>(table), T, hp,
                                                                 H, log2f(theta));
-    rope_apply_kernel<<<grid_for(total / 4, 256, 148 * 16), 256, 0, stream>>>(
-        static_cast<const Bf16x8*>(x), static_cast<Bf16x8*>(y), reinterpret_cast<const float2*>(table), total / 4, T,
-        N, hp, backward ? -1.f : 1.f);
+    // 64 threads' worth of (vector position, head lane) per row where the head allows it.
+    const int vec_per_head = hp / 4;
+    int lanes = 64 / vec_per_head;
+    if (lanes < 1) lanes = 1;
+    if (lanes > N) lanes = N;
+    int rows = 256 / (vec_per_head * lanes);
+    if (rows < 1) rows = 1;
+    const int64_t num_rows = B * static_cast<int64_t>(T);
+    const int threads = rows * vec_per_head * lanes;
+    int64_t blocks = (num_rows + rows - 1) / rows;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    rope_apply_kernel<4><<<static_cast<int>(blocks), threads, 0, stream>>>(
+        static_cast<const Bf16x8*>(x), static_cast<Bf16x8*>(y), reinterpret_cast<const float2*>(table), num_rows, T,
+        N, hp, backward ? -1.f : 1.f, lanes, rows);
   } else {
     rope_kernel<<<grid_for(total, 256, 148 * 16), 256, 0, stream>>>(
         static_cast<const bf16*>(x), static_cast<bf16*>(y), positions, B, T, N, H, log2f(theta),

@@ -99,12 +99,14 @@ def test_swiglu_fwd_bwd():
     _close(b.grad, bf.grad, 2e-2)
 
 
-def test_rope_fwd_bwd():
+@pytest.mark.parametrize("b,t,n,h", [(2, 300, 4, 128), (3, 257, 32, 128), (1, 65, 5, 64), (2, 33, 3, 256), (1, 17, 2, 32),
+                                     (1, 9, 1, 2048)])
+def test_rope_fwd_bwd(b, t, n, h):
     from axlearn_b200.ops import cuda_ops, reference
 
     torch.manual_seed(0)
-    x = torch.randn(2, 300, 4, 128, device="cuda").bfloat16().requires_grad_()
-    pos = torch.arange(300, device="cuda")
+    x = torch.randn(b, t, n, h, device="cuda").bfloat16().requires_grad_()
+    pos = torch.arange(t, device="cuda") + 3
     y = cuda_ops.rope(x, pos, 5e5)
     g = torch.randn_like(y)
     y.backward(g)
