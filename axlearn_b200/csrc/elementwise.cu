@@ -287,11 +287,16 @@ rmsnorm_bwd_warp_kernel(const bf16* __restrict__ x, const bf16* __restrict__ sca
   for (int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + slot; row < rows; row += stride) {
     const Bf16x8* xr = reinterpret_cast<const Bf16x8*>(x + row * D + part * P);
     const Bf16x8* gr = reinterpret_cast<const Bf16x8*>(dy + row * D + part * P);
-    Bf16x8 a[VPL], g[VPL];
+    // Everything the row needs from global memory is requested up front (x, dy and, when
+    // present, the residual branch's gradient): one exposed round trip per row instead of one
+    // per use.
+    const Bf16x8* rr = dres != nullptr ? reinterpret_cast<const Bf16x8*>(dres + row * D + part * P) : nullptr;
+    Bf16x8 a[VPL], g[VPL], r[VPL];
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
       a[i] = xr[i * 32 + lane];
       g[i] = gr[i * 32 + lane];
+      if (rr != nullptr) r[i] = rr[i * 32 + lane];
     }
     const float rstd = rstd_in[row];
     float dot = 0.f;
@@ -316,13 +321,11 @@ rmsnorm_bwd_warp_kernel(const bf16* __restrict__ x, const bf16* __restrict__ sca
       asm volatile("bar.sync %0, %1;" ::"r"(1 + slot), "r"(32 * WPR) : "memory");  // before the next row overwrites
     }
     dot /= D;
-    const Bf16x8* rr = dres != nullptr ? reinterpret_cast<const Bf16x8*>(dres + row * D + part * P) : nullptr;
     Bf16x8* dxr = reinterpret_cast<Bf16x8*>(dx + row * D + part * P);
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
       const Bf16x8 s = ld_again(sc + i * 32 + lane);
-      Bf16x8 r, o;
-      if (rr != nullptr) r = ld_again(rr + i * 32 + lane);
+      Bf16x8 o;
       float ds[8];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -332,7 +335,7 @@ rmsnorm_bwd_warp_kernel(const bf16* __restrict__ x, const bf16* __restrict__ sca
         float d0 = rstd * (gf.x * sf.x - xh0 * dot);
         float d1 = rstd * (gf.y * sf.y - xh1 * dot);
         if (rr != nullptr) {
-          const float2 rf = __bfloat1622float2(r.v[j]);
+          const float2 rf = __bfloat1622float2(r[i].v[j]);
           d0 += rf.x;
           d1 += rf.y;
         }

@@ -189,6 +189,29 @@ def bench_memory_bound(args) -> dict:
         ours = _time(lambda: cuda_ops.rms_norm(x, scale, 1e-5), args.iters)
         lib = _time(lambda: torch.nn.functional.rms_norm(x, (d,), scale, 1e-5), args.iters)
         nbytes = 2 * x.numel() * 2
+    elif args.op in ("rmsnorm_add", "rmsnorm_bwd", "rmsnorm_bwd_add"):
+        # The fused forms of the training step: forward with the residual add (reads two rows,
+        # writes the sum and the normalised row), backward without / with the residual branch's
+        # gradient added in (reads x, dy [, dres], writes dx; dscale partials are small).
+        scale = torch.ones(d, device="cuda").bfloat16()
+        other = torch.randn_like(x)
+        y, _, rstd = cuda_ops._rmsnorm_forward(x, None, scale, 1e-5)  # pylint: disable=protected-access
+        if args.op == "rmsnorm_add":
+            ours = _time(lambda: cuda_ops._rmsnorm_forward(x, other, scale, 1e-5), args.iters)  # pylint: disable=protected-access
+            lib = _time(lambda: torch.nn.functional.rms_norm(x + other, (d,), scale, 1e-5), args.iters)
+            nbytes = 4 * x.numel() * 2
+        else:
+            dres = other if args.op == "rmsnorm_bwd_add" else None
+            ours = _time(lambda: cuda_ops._rmsnorm_backward(x, scale, rstd, y, dres), args.iters)  # pylint: disable=protected-access
+            xg = x.clone().requires_grad_()
+
+            def lib_fn():
+                out = torch.nn.functional.rms_norm(xg, (d,), scale, 1e-5)
+                (gx,) = torch.autograd.grad(out, xg, y)
+                return gx if dres is None else gx + dres
+
+            lib = _time(lib_fn, args.iters)
+            nbytes = (4 if dres is not None else 3) * x.numel() * 2
     elif args.op == "swiglu":
         y = torch.randn_like(x)
         ours = _time(lambda: cuda_ops.swiglu(x, y), args.iters)
@@ -229,7 +252,7 @@ def bench_memory_bound(args) -> dict:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--op", required=True,
-                    choices=["gemm", "gemm_fp8", "grouped_gemm", "flash_fwd", "flash_bwd", "decode_attn", "rmsnorm", "swiglu", "rope", "ce",
+                    choices=["gemm", "gemm_fp8", "grouped_gemm", "flash_fwd", "flash_bwd", "decode_attn", "rmsnorm", "rmsnorm_add", "rmsnorm_bwd", "rmsnorm_bwd_add", "swiglu", "rope", "ce",
                              "adamw"])
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
