@@ -687,36 +687,46 @@ ce_fwd_bwd_bf16_vec_kernel(bf16* __restrict__ logits, const int64_t* __restrict_
         mi = oi;
       }
     }
-    float se = 0.f;
-    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
-      const Bf16x8 v = cache[i];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __bfloat1622float2(v.v[j]);
-        se += __expf(f.x - m) + __expf(f.y - m);
-      }
-    }
-    se = block_sum(se, red);
-    const float lse = m + logf(se);
     const int64_t tgt_raw = targets[row];
     const bool is_live = live[row] != 0;
     const int tgt = static_cast<int>(tgt_raw < 0 ? 0 : (tgt_raw >= V ? V - 1 : tgt_raw));
+    // The target's logit is read before the staged row is overwritten below (every thread's own
+    // copy: the value is the same and nobody has to wait for a broadcast).
+    const float picked = __bfloat162float(reinterpret_cast<const bf16*>(cache)[tgt]);
+    __syncthreads();
+    // Each exponential is evaluated ONCE: exp(x - max) feeds the sum and, rounded to bf16, replaces
+    // the staged logit; the gradient pass then only scales it by coef / sum.  (Two exponentials
+    // per element made the special-function unit as busy as the memory system.)
+    float se = 0.f;
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      const Bf16x8 v = cache[i];
+      Bf16x8 e;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(v.v[j]);
+        const float e0 = __expf(f.x - m), e1 = __expf(f.y - m);
+        se += e0 + e1;
+        e.v[j] = __floats2bfloat162_rn(e0, e1);
+      }
+      if (write_grad) cache[i] = e;
+    }
+    se = block_sum(se, red);
+    const float lse = m + logf(se);
     if (threadIdx.x == 0) {
-      const float picked = __bfloat162float(reinterpret_cast<const bf16*>(cache)[tgt]);
       ce_out[row] = is_live ? (lse - picked) : 0.f;
       z_out[row] = is_live ? lse * lse : 0.f;
       correct_out[row] = (is_live && mi == tgt) ? 1.f : 0.f;
     }
     if (write_grad) {
       const float g = is_live ? inv_denom : 0.f;
-      const float coef = g * (1.f + 2.f * z_scale * lse);
+      const float coef = g * (1.f + 2.f * z_scale * lse) / se;   // exp(x - lse) = exp(x - max) / sum
       for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
         const Bf16x8 v = cache[i];
         Bf16x8 o;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const float2 f = __bfloat1622float2(v.v[j]);
-          float d0 = coef * __expf(f.x - lse), d1 = coef * __expf(f.y - lse);
+          float d0 = coef * f.x, d1 = coef * f.y;
           if (i * 8 + 2 * j == tgt) d0 -= g;
           if (i * 8 + 2 * j + 1 == tgt) d1 -= g;
           o.v[j] = __floats2bfloat162_rn(d0, d1);
