@@ -130,7 +130,7 @@ class MultiheadInputLinear(DenseGeneralBaseLayer):
         cshape = coll.compute_shape(full, spec)
         w = coll.unshard_param(self.parameters["weight"], spec, compute_shape=cshape)
         if coll.has_axis(spec[1] if spec else None, "model"):
-            x = coll.psum_grad(x, "model")
+            x = coll.tp_enter(x, "model")
         y = self._matmul(x, w.reshape(cshape[0], -1).to(x.dtype))
         y = y.reshape(x.shape[:-1] + (cshape[1], cshape[2]))
         if cfg.bias:
@@ -182,7 +182,7 @@ class MultiheadOutputLinear(DenseGeneralBaseLayer):
         if y is None:
             y = self._matmul(x2, w2.t())
             if row_parallel:
-                y = coll.psum(y, "model")
+                y = coll.tp_exit(y, "model")
         if cfg.bias:
             y = y + self.parameters["bias"].to(y.dtype)
         return y
@@ -315,7 +315,7 @@ class _FusedQKVProj(DenseGeneralBaseLayer):
         cshape = coll.compute_shape(full, spec)
         w = coll.unshard_param(self.parameters["weight"], spec, compute_shape=cshape)
         if coll.has_axis(spec[2] if spec else None, "model"):
-            x = coll.psum_grad(x, "model")
+            x = coll.tp_enter(x, "model")
         x = ops.share_input_grad(x)      # the three projections sum their input gradients in place
         outs = []
         for p in range(3):
@@ -811,6 +811,10 @@ class MultiheadAttention(BaseLayer):
             kv_kwargs.update(key=key, value=value)
         is_self_attention = key is None and kv_state is None
         b, t = query.shape[:2]
+        if coll.tp_sequence_parallel_dim() is not None and is_self_attention:
+            # Sequence-sharded tensor-parallel region: `query` is this rank's slice; the projections
+            # all-gather it, so everything below sees the whole sequence.
+            t = t * coll.axis_size("model")
         dev = query.device
         default_positions = query_positions is None
         # Ulysses sequence parallelism: activations hold this rank's contiguous slice of the
@@ -1422,6 +1426,12 @@ class TransformerLayer(BaseTransformerLayer):
         self_attention: InstantiableConfig = TransformerAttentionLayer.default_config()
         cross_attention: Optional[InstantiableConfig] = None
         feed_forward: InstantiableConfig = TransformerFeedForwardLayer.default_config()
+        # With a `model` mesh axis: the layer's input and output are 1 / tp slices of the
+        # sequence (dim 1); norms and residual adds work on the slice, column-parallel linears
+        # all-gather their input and row-parallel linears reduce-scatter their output.  Set by
+        # the stack (``BaseStackedTransformerLayer.Config.tp_sequence_parallel``), which also
+        # slices the stack's input and gathers its output.
+        tp_sequence_parallel: bool = False
 
     def __init__(self, cfg, *, parent=None):
         super().__init__(cfg, parent=parent)
@@ -1471,7 +1481,11 @@ class TransformerLayer(BaseTransformerLayer):
             cross_attention_probs=cross_probs)
 
     def forward(self, data, **kwargs):
-        _, out = self._forward_for_mode(mode=ForwardMode.FORWARD, data=data, **kwargs)
+        # The flag is raised here, inside the (possibly rematerialised) forward, so that the
+        # recomputation in the backward pass issues the same collectives.
+        sp = self._config.tp_sequence_parallel and coll.axis_size("model") > 1
+        with coll.tp_sequence_parallel(sp):
+            _, out = self._forward_for_mode(mode=ForwardMode.FORWARD, data=data, **kwargs)
         return out
 
     def init_states(self, *, time_step, data, page_pool=None, max_len=None, **kwargs):
@@ -1501,6 +1515,20 @@ class BaseStackedTransformerLayer(BaseTransformerLayer):
         num_layers: Required[int] = REQUIRED
         layer: Union[InstantiableConfig, Sequence[InstantiableConfig]] = TransformerLayer.default_config()
         peak_stochastic_depth_rate: Optional[float] = None
+        # Sequence-sharded activations between the tensor-parallel blocks (training forward only;
+        # see ``TransformerLayer.Config.tp_sequence_parallel``).
+        tp_sequence_parallel: bool = False
+
+    def _tp_seq_on(self) -> bool:
+        return bool(self._config.tp_sequence_parallel) and coll.axis_size("model") > 1
+
+    def _tp_seq_wrap(self, run, data):
+        """Slices the replicated input over the `model` axis, runs the stack on the slice and
+        gathers the output (``run(data) -> Output``)."""
+        if not self._tp_seq_on():
+            return run(data)
+        out = run(coll.scatter_replicated(data, "model", dim=1))
+        return out._replace(data=coll.gather_replicated(out.data, "model", dim=1))
 
 
 def _update_data(kwargs: dict, data: Tensor) -> dict:
@@ -1523,6 +1551,8 @@ class StackedTransformerLayer(BaseStackedTransformerLayer):
             raise ValueError("number of layer configs must equal num_layers")
         for i, lc in enumerate(layer_cfgs):
             lc = lc.clone(input_dim=cfg.input_dim)
+            if cfg.tp_sequence_parallel and "tp_sequence_parallel" in lc.keys():
+                lc.tp_sequence_parallel = True
             if cfg.peak_stochastic_depth_rate:
                 rate = cfg.peak_stochastic_depth_rate * (i + 1) / cfg.num_layers
                 lc.self_attention.stochastic_depth.rate = rate
@@ -1557,8 +1587,8 @@ class StackedTransformerLayer(BaseStackedTransformerLayer):
         )
 
     def forward(self, data, **kwargs):
-        _, out = self._forward_for_mode(mode=ForwardMode.FORWARD, data=data, **kwargs)
-        return out
+        return self._tp_seq_wrap(
+            lambda d: self._forward_for_mode(mode=ForwardMode.FORWARD, data=d, **kwargs)[1], data)
 
     def init_states(self, *, time_step, data, **kwargs):
         return self._forward_for_mode(mode=ForwardMode.INIT_STATES, data=data, cached_states=time_step, **kwargs)
@@ -1612,15 +1642,16 @@ class RepeatedTransformerLayer(BaseStackedTransformerLayer):
 
     def __init__(self, cfg, *, parent=None):
         super().__init__(cfg, parent=parent)
-        repeat_cfg = cfg.repeat.clone(
-            layer=cfg.layer.clone(input_dim=cfg.input_dim), num_layers=cfg.num_layers
-        )
+        layer_cfg = cfg.layer.clone(input_dim=cfg.input_dim)
+        if cfg.tp_sequence_parallel and "tp_sequence_parallel" in layer_cfg.keys():
+            layer_cfg.tp_sequence_parallel = True
+        repeat_cfg = cfg.repeat.clone(layer=layer_cfg, num_layers=cfg.num_layers)
         self._add_child("repeat", repeat_cfg)
 
     def forward(self, data, *, return_aux=None, **kwargs):
         if return_aux:
             raise NotImplementedError("return_aux is not supported by RepeatedTransformerLayer")
-        return BaseTransformerLayer.Output(data=self.repeat(data, **kwargs))
+        return self._tp_seq_wrap(lambda d: BaseTransformerLayer.Output(data=self.repeat(d, **kwargs)), data)
 
     def init_states(self, *, time_step, data, **kwargs):
         kwargs.pop("return_aux", None)

@@ -395,13 +395,13 @@ class Linear(DenseGeneralBaseLayer):
         col_parallel = coll.has_axis(_spec_entry(spec, 1), "model")
         row_parallel = coll.has_axis(_spec_entry(spec, 0), "model")
         if col_parallel:
-            x = coll.psum_grad(x, "model")
+            x = coll.tp_enter(x, "model")
         wx = w.to(x.dtype) if w.dtype != x.dtype else w
         y = coll.row_parallel_linear(x, wx, "model") if row_parallel and self._plain_matmul() else None
         if y is None:
             y = self._matmul(x, wx)
             if row_parallel:
-                y = coll.psum(y, "model")
+                y = coll.tp_exit(y, "model")
         if cfg.bias:
             b = self.parameters["bias"]
             b = coll.unshard_param(b, (_spec_entry(spec, -1),) if spec else None,

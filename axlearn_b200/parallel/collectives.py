@@ -14,6 +14,8 @@ the explicit ones it does write are in axlearn/common/mixture_of_experts.py:2139
 
 from __future__ import annotations
 
+import contextlib
+import threading
 from typing import Any, Optional, Sequence
 
 import torch
@@ -198,7 +200,7 @@ def row_parallel_linear(x: torch.Tensor, w: torch.Tensor, axes: AxisSpec) -> Opt
     """``psum(x @ w, axes)`` with the reduction's stores fused into the GEMM epilogue (peer
     memory), or None when that path does not apply."""
     group, world, _ = _group(axes)
-    if world == 1:
+    if world == 1 or _tp_seq.dim is not None:
         return None
     from axlearn_b200.parallel import peer_allreduce
 
@@ -210,6 +212,98 @@ def all_gather(x: torch.Tensor, axes: AxisSpec, *, dim: int = 0) -> torch.Tensor
     if world == 1:
         return x
     return _AllGather.apply(x, group, world, dim % x.dim())
+
+
+# ------------------------------------------------------------------------------------------
+# Sequence-sharded tensor-parallel regions ("Megatron sequence parallelism").
+#
+# Between the tensor-parallel blocks of a transformer layer (norms, residual adds, dropout) every
+# rank of the `model` axis would otherwise hold and process the same [B, T, D] activations.  With
+# the mode on, those regions work on a 1 / tp slice of the sequence: a column-parallel linear
+# all-gathers its input (backward: reduce-scatter of the input gradient) and a row-parallel linear
+# reduce-scatters its output (backward: all-gather) -- the same bytes as the all-reduce pair they
+# replace.  The mode is a thread-local flag set INSIDE a layer's forward, so that a rematerialised
+# forward in the backward pass sees it too.
+# ------------------------------------------------------------------------------------------
+
+
+class _TpSeqState(threading.local):
+    def __init__(self):
+        self.dim: Optional[int] = None
+
+
+_tp_seq = _TpSeqState()
+
+
+@contextlib.contextmanager
+def tp_sequence_parallel(enabled: bool = True, *, dim: int = 1):
+    prev, _tp_seq.dim = _tp_seq.dim, (dim if enabled else None)
+    try:
+        yield
+    finally:
+        _tp_seq.dim = prev
+
+
+def tp_sequence_parallel_dim() -> Optional[int]:
+    return _tp_seq.dim
+
+
+def tp_enter(x: torch.Tensor, axes: AxisSpec) -> torch.Tensor:
+    """Input of a column-parallel linear: the full activations, gradient summed over ``axes``."""
+    if _tp_seq.dim is not None:
+        return all_gather(x.contiguous(), axes, dim=_tp_seq.dim)
+    return psum_grad(x, axes)
+
+
+def tp_exit(y: torch.Tensor, axes: AxisSpec) -> torch.Tensor:
+    """Output of a row-parallel linear: summed over ``axes`` (and sequence-sharded when the mode is on)."""
+    if _tp_seq.dim is not None:
+        return reduce_scatter(y.contiguous(), axes, dim=_tp_seq.dim)
+    return psum(y, axes)
+
+
+class _ScatterReplicated(torch.autograd.Function):
+    """Takes this rank's slice of a tensor that is REPLICATED over the group; the gradient of
+    the replicated tensor is the concatenation of the slices' gradients."""
+
+    @staticmethod
+    def forward(ctx, x, group, world, dim):
+        ctx.group, ctx.world, ctx.dim = group, world, dim
+        return x.chunk(world, dim=dim)[dist.get_rank(group)].contiguous()
+
+    @staticmethod
+    def backward(ctx, g):
+        return all_gather_raw(g.contiguous(), ctx.group, ctx.world, ctx.dim), None, None, None
+
+
+class _GatherReplicated(torch.autograd.Function):
+    """All-gathers slices into a tensor whose consumers are replicated over the group: every rank
+    computes the same gradient for the whole tensor, so the slice's gradient is just its part."""
+
+    @staticmethod
+    def forward(ctx, x, group, world, dim):
+        ctx.group, ctx.world, ctx.dim = group, world, dim
+        return all_gather_raw(x.contiguous(), group, world, dim)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g.chunk(ctx.world, dim=ctx.dim)[dist.get_rank(ctx.group)].contiguous(), None, None, None
+
+
+def scatter_replicated(x: torch.Tensor, axes: AxisSpec, *, dim: int) -> torch.Tensor:
+    group, world, _ = _group(axes)
+    if world == 1:
+        return x
+    if x.shape[dim] % world:
+        raise ValueError(f"dim {dim} of size {x.shape[dim]} is not divisible by the {world} ranks of {axes}")
+    return _ScatterReplicated.apply(x, group, world, dim % x.dim())
+
+
+def gather_replicated(x: torch.Tensor, axes: AxisSpec, *, dim: int) -> torch.Tensor:
+    group, world, _ = _group(axes)
+    if world == 1:
+        return x
+    return _GatherReplicated.apply(x, group, world, dim % x.dim())
 
 
 def reduce_scatter(x: torch.Tensor, axes: AxisSpec, *, dim: int = 0) -> torch.Tensor:

@@ -28,6 +28,7 @@ def _free_port() -> int:
 def _train(directory, mesh_axes: dict, steps: int, num_kv_heads=None):
     mesh_axes = dict(mesh_axes)
     seq_mode = mesh_axes.pop("seq_parallel_mode", None)
+    tp_seq = mesh_axes.pop("tp_sequence_parallel", False)
     sys.path.insert(0, REPO)
     from axlearn_b200.common import prng
     from axlearn_b200.experiments.text.gpt.common import mesh_shape_from_axes
@@ -38,6 +39,8 @@ def _train(directory, mesh_axes: dict, steps: int, num_kv_heads=None):
         hidden=64, heads=4, ffn=128, vocab=512, seq=32, batch=4, layers=2, num_kv_heads=num_kv_heads)
     if seq_mode is not None:
         cfg.model.decoder.transformer.layer.self_attention.attention.seq_parallel_mode = seq_mode
+    if tp_seq:
+        cfg.model.decoder.transformer.tp_sequence_parallel = True
     trainer = cfg.instantiate(parent=None)
     trainer.init(prng.PRNGKey(0))
     losses = []
@@ -74,12 +77,15 @@ def _worker(rank, world, port, directory, mesh_axes, steps, out_queue):
     dict(fsdp=2), dict(model=2), dict(fsdp=2, model=2), dict(data=2), dict(seq=2),
     # Context parallelism: queries stay sequence-sharded, K / V are gathered over the seq axis.
     dict(seq=2, seq_parallel_mode="allgather_kv"),
+    # Tensor parallelism with sequence-sharded norm / residual regions (all-gather into the
+    # column-parallel linears, reduce-scatter out of the row-parallel ones).
+    dict(model=2, tp_sequence_parallel=True), dict(fsdp=2, model=2, tp_sequence_parallel=True),
 ])
 def test_sharded_matches_single_process(tmp_path, mesh_axes):
     steps = 3
     world = 1
     for v in mesh_axes.values():
-        world *= v if isinstance(v, int) else 1
+        world *= v if isinstance(v, int) and not isinstance(v, bool) else 1
     ref_trainer, ref_losses = _train(tmp_path / "single", {}, steps)
     ref_w = ref_trainer.trainer_state["model"]["decoder"]["transformer"]["repeat"]["layer"]["feed_forward"]["linear2"]["weight"]
     ctx = mp.get_context("spawn")
