@@ -45,6 +45,8 @@ def _args():
     ap.add_argument("--family", default="fuji", choices=["fuji", "envy"])
     ap.add_argument("--drop_free", action="store_true", help="--family envy: capacity-free routing on the grouped GEMM "
                     "(TransformerFeedForwardDropFreeMoE) instead of the capacity-based layer")
+    ap.add_argument("--ep_capacity", type=float, default=None, help="--drop_free with an expert axis: cap every rank's row "
+                    "buffer at this multiple of the fair share (default: sized for the worst case, nothing dropped)")
     ap.add_argument("--fp8", action="store_true", help="block-scaled fp8 projection GEMMs (FP8ConfigModifier)")
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--per_gpu_batch", type=int, default=4)
@@ -296,6 +298,10 @@ def _build_trainer(args, world, local_rank, use_cuda, *, layers, per_gpu_batch):
         if args.drop_free:
             mk["drop_free"] = True
         model_cfg = envy.model_config(scan_chunk=8192, **mk)
+        if args.drop_free and args.ep_capacity is not None:
+            ff = model_cfg.decoder.transformer.layer.feed_forward
+            if "expert_parallel_capacity" in ff.keys():
+                ff.expert_parallel_capacity = args.ep_capacity
     else:
         mk = dict(kw["model_kwargs"])
         if layers:
