@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from typing import Optional
 
 import torch
@@ -52,6 +53,8 @@ def default_splits(batch: int, num_kv_heads: int, group: int, max_len: int, page
     """KV splits so that the grid has a few CTAs per SM without splitting below 8 pages."""
     gt = 4 if group % 4 == 0 else 2 if group % 2 == 0 else 1
     ctas = batch * num_kv_heads * (group // gt)
+    if num_kv_heads % 4 == 0 and group in (2, 4) and os.environ.get("AXB_DECODE_ATTN") != "head":
+        ctas = batch * (num_kv_heads // 4)      # the row-contiguous kernel: four KV heads per CTA
     want = max(1, (4 * sms + ctas - 1) // ctas)
     pages = max(1, max_len // page_size)
     return max(1, min(want, pages // 8 if pages >= 8 else 1, 32))

@@ -18,7 +18,7 @@ def _pools(b, max_pages, page_size, nkv, h, seed=0):
     return k, v, perm.reshape(b, max_pages).contiguous()
 
 
-@pytest.mark.parametrize("nq,nkv", [(4, 4), (8, 2), (8, 1), (6, 3)])
+@pytest.mark.parametrize("nq,nkv", [(4, 4), (8, 2), (8, 1), (6, 3), (8, 4), (16, 4), (32, 8)])
 @pytest.mark.parametrize("splits", [1, 3])
 def test_paged_decode_attention_matches_reference(nq, nkv, splits):
     from axlearn_b200.ops import cuda_ops, decode_ops
