@@ -192,3 +192,33 @@ def test_validators_and_mutators():
     assert out["spec"]["priorityClassName"] == "high" and pod["spec"]["hostNetwork"] is False   # input untouched
     p = PrefixCommandPatcher.default_config().set(prefix="python -m axlearn_b200.ft.agent --").instantiate()
     assert p.patch("python train.py") == "python -m axlearn_b200.ft.agent -- python train.py"
+
+
+def test_gcs_storage_helpers():
+    from axlearn_b200.cloud.gcp import storage
+
+    assert storage.split_url("gs://b/x/y") == ("b", "x/y")
+    with pytest.raises(ValueError):
+        storage.split_url("/local/path")
+    listing = "gs://b/run/:\ngs://b/run/a.txt\ngs://b/run/sub/\ngs://b/run/sub/c.bin\n"
+    rec = Recorder(outputs=[listing])
+    assert storage.list_blobs("gs://b/run", runner=rec) == ["gs://b/run/a.txt", "gs://b/run/sub/c.bin"]
+    assert rec.calls[0] == ["gcloud", "storage", "ls", "gs://b/run/**"]
+
+    def missing(args, **kwargs):
+        return types.SimpleNamespace(stdout="", stderr="matched no objects", returncode=1)
+
+    assert storage.list_blobs("gs://b/none", runner=missing) == [] and not storage.blob_exists("gs://b/x", runner=missing)
+    assert storage.blob_exists("gs://b/x", runner=Recorder(outputs=["gs://b/x\n"]))
+    rec = Recorder()
+    storage.upload_blob("/tmp/f", "gs://b/f", runner=rec)
+    storage.download_blob("gs://b/f", "/tmp/g", runner=rec)
+    storage.delete_blob("gs://b/dir", recursive=True, runner=rec)
+    storage.sync_directory("/tmp/out", "gs://b/out", delete_unmatched=True, runner=rec)
+    assert rec.calls == [["gcloud", "storage", "cp", "/tmp/f", "gs://b/f"],
+                         ["gcloud", "storage", "cp", "gs://b/f", "/tmp/g"],
+                         ["gcloud", "storage", "rm", "--recursive", "gs://b/dir"],
+                         ["gcloud", "storage", "rsync", "--recursive", "--delete-unmatched-destination-objects",
+                          "/tmp/out", "gs://b/out"]]
+    with pytest.raises(RuntimeError, match="upload"):
+        storage.upload_blob("/tmp/f", "gs://b/f", runner=missing)
