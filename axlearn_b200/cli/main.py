@@ -91,8 +91,35 @@ def _cmd_gcp(args, rest: Sequence[str]) -> int:
     def setting(key, default=None, required=False):
         return settings.gcp_settings(key, project=args.project, env_id=args.env_id, default=default, required=required)
 
-    builder_cls = {"a4-highgpu-8g": A4HighReplicatedJob, "a3-ultragpu-8g": A3UltraReplicatedJob}[args.machine_type]
     command = " ".join(rest) if rest else (args.command or "true")
+    if args.action == "serve-manifest":
+        # A multi-host serving deployment: --num_nodes hosts per replica, leader Service, probes,
+        # optionally a Gateway route and an autoscaler (axlearn/cloud/gcp/lws_utils.py, k8s_*.py).
+        import yaml  # pylint: disable=import-outside-toplevel
+
+        from axlearn_b200.cloud.gcp import serving
+
+        lws = serving.LeaderWorkerSet.default_config().set(
+            name=args.name, namespace=args.namespace, image=args.image or setting("docker_image", required=True),
+            command=command, replicas=args.replicas, hosts_per_replica=args.num_nodes, machine_type=args.machine_type,
+            service_account=setting("k8s_service_account"), port=args.port,
+            env_vars=dict(item.split("=", 1) for item in args.env),
+            probes=[serving.StartupProbe.default_config().set(port=args.port),
+                    serving.ReadinessProbe.default_config().set(port=args.port),
+                    serving.LivenessProbe.default_config().set(port=args.port)])
+        dep = serving.ServingDeployment.default_config().set(lws=lws, gke_policies=bool(args.gateway),
+                                                             monitoring=args.max_replicas > args.replicas)
+        if args.gateway:
+            dep.route = serving.LWSHTTPRoute.default_config().set(gateway_name=args.gateway)
+        if args.max_replicas > args.replicas:
+            metric, _, target = args.scale_metric.partition("=")
+            dep.hpa = serving.HPA.default_config().set(
+                min_replicas=args.replicas, max_replicas=args.max_replicas,
+                metrics=[serving.HPAMetric.default_config().set(metric_name=metric, average_value=target or "1")])
+        objs = [lws.instantiate().build()] + dep.instantiate().manifests()
+        print(yaml.safe_dump_all(objs, sort_keys=False))
+        return 0
+    builder_cls = {"a4-highgpu-8g": A4HighReplicatedJob, "a3-ultragpu-8g": A3UltraReplicatedJob}[args.machine_type]
     builder = builder_cls.default_config().set(
         command=command, image=args.image or setting("docker_image"), num_nodes=args.num_nodes,
         reservation=args.reservation or setting("reservation"), service_account=setting("k8s_service_account"),
@@ -154,7 +181,7 @@ def build_parser() -> argparse.ArgumentParser:
     bastion.add_argument("--env", nargs="*", default=[], help="KEY=VALUE")
 
     gcp = groups.add_parser("gcp", help="GKE JobSets; everything after the flags is the worker command")
-    gcp.add_argument("action", choices=["launch", "delete", "status", "manifest", "config"])
+    gcp.add_argument("action", choices=["launch", "delete", "status", "manifest", "config", "serve-manifest"])
     gcp.add_argument("--name")
     gcp.add_argument("--project")
     gcp.add_argument("--env_id")
@@ -170,6 +197,12 @@ def build_parser() -> argparse.ArgumentParser:
     gcp.add_argument("--fault_tolerant", action="store_true", help="restartable job: no NVLink multicast binding")
     gcp.add_argument("--env", nargs="*", default=[], help="KEY=VALUE")
     gcp.add_argument("--activate", help="config: make this \"project:env_id\" table the active one")
+    gcp.add_argument("--replicas", type=int, default=1, help="serve-manifest: LeaderWorkerSet replicas")
+    gcp.add_argument("--max_replicas", type=int, default=0, help="serve-manifest: > replicas adds an autoscaler")
+    gcp.add_argument("--scale_metric", default="requests_in_flight=16",
+                     help="serve-manifest: pod metric and its per-pod target for the autoscaler")
+    gcp.add_argument("--port", type=int, default=8000, help="serve-manifest: the leader's HTTP port")
+    gcp.add_argument("--gateway", help="serve-manifest: route requests from this Gateway to the deployment")
 
     bundle = groups.add_parser("bundle")
     bundle.add_argument("--name", required=True)

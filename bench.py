@@ -47,6 +47,8 @@ def _args():
                     "(TransformerFeedForwardDropFreeMoE) instead of the capacity-based layer")
     ap.add_argument("--ep_capacity", type=float, default=None, help="--drop_free with an expert axis: cap every rank's row "
                     "buffer at this multiple of the fair share (default: sized for the worst case, nothing dropped)")
+    ap.add_argument("--tp_seq", action="store_true", help="non-headline, with a model axis in --mesh: sequence-sharded "
+                    "norm / residual regions (all-gather into column-parallel, reduce-scatter out of row-parallel linears)")
     ap.add_argument("--fp8", action="store_true", help="block-scaled fp8 projection GEMMs (FP8ConfigModifier)")
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--per_gpu_batch", type=int, default=4)
@@ -309,6 +311,8 @@ def _build_trainer(args, world, local_rank, use_cuda, *, layers, per_gpu_batch):
         model_cfg = fuji.model_config(scan_chunk=8192, **mk)
     # Full remat per layer: only each layer's input is kept.
     model_cfg.decoder.transformer.layer.remat_spec = RematSpec(prevent_cse=False, policy=nothing_saveable)
+    if args.tp_seq:
+        model_cfg.decoder.transformer.tp_sequence_parallel = True
     cfg = get_trainer_config_fn(
         model_cfg=model_cfg,
         learner_cfg=adamw_decoupled_learner_config(max_step=kw["max_step"], **kw["learner_kwargs"]),

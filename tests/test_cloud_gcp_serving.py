@@ -102,3 +102,19 @@ def test_deployment_applies_set_first_and_owns_the_rest():
     assert api.applied[3]["spec"]["default"]["config"]["httpHealthCheck"]["port"] == 9000
     dep.delete(api)
     assert api.deleted == [("LeaderWorkerSet", "serving", "fuji-70b")]
+
+
+def test_cli_serve_manifest(capsys):
+    import yaml
+
+    from axlearn_b200.cli.main import main
+
+    rc = main(["gcp", "serve-manifest", "--name", "m7", "--image", "reg/serve:v1", "--num_nodes", "2", "--replicas", "1",
+               "--max_replicas", "3", "--gateway", "gw", "--", "python", "-m", "server"])
+    assert rc == 0
+    objs = [o for o in yaml.safe_load_all(capsys.readouterr().out) if o]
+    assert [o["kind"] for o in objs] == ["LeaderWorkerSet", "Service", "HTTPRoute", "HealthCheckPolicy",
+                                         "GCPBackendPolicy", "PodMonitoring", "HorizontalPodAutoscaler"]
+    lws = objs[0]["spec"]["leaderWorkerTemplate"]
+    assert lws["size"] == 2 and lws["leaderTemplate"]["spec"]["containers"][0]["command"][-1] == "python -m server"
+    assert objs[-1]["spec"]["maxReplicas"] == 3 and objs[2]["spec"]["parentRefs"][0]["name"] == "gw"
