@@ -91,6 +91,8 @@ def _cmd_gcp(args, rest: Sequence[str]) -> int:
     def setting(key, default=None, required=False):
         return settings.gcp_settings(key, project=args.project, env_id=args.env_id, default=default, required=required)
 
+    if rest and rest[0] == "--":
+        rest = rest[1:]          # the separator in front of the worker command is not part of it
     command = " ".join(rest) if rest else (args.command or "true")
     if args.action == "serve-manifest":
         # A multi-host serving deployment: --num_nodes hosts per replica, leader Service, probes,
