@@ -33,7 +33,6 @@ from axlearn_b200 import ops
 from axlearn_b200.common.base_layer import BaseLayer, ParameterSpec
 from axlearn_b200.common import prng
 from axlearn_b200.common.config import InstantiableConfig, config_class
-from axlearn_b200.common.module import nowrap
 from axlearn_b200.common.param_init import constant_initializer
 from axlearn_b200.ops import fp8_ops
 

@@ -16,7 +16,7 @@ from __future__ import annotations
 
 import contextlib
 import threading
-from typing import Any, Optional, Sequence
+from typing import Optional, Sequence
 
 import torch
 import torch.distributed as dist

@@ -11,7 +11,7 @@ batches reach the GPU through the pinned-tensor path of ``PipelineInput``.
 from __future__ import annotations
 
 import zlib
-from typing import Any, Callable, Optional, Sequence
+from typing import Callable, Optional, Sequence
 
 import numpy as np
 
