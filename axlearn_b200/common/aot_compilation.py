@@ -138,6 +138,100 @@ def plan_training_memory(trainer_cfg, *, num_gpus: int, hbm_gb: float = 180.0, m
                       hbm_bytes=hbm_gb * 1e9)
 
 
+@dataclasses.dataclass
+class CostAnalysis:
+    """What a training step costs per GPU, from the config alone (the counterpart of the compiled
+    executable's cost analysis the reference prints without hardware,
+    axlearn/common/aot_compilation.py): matrix FLOPs, attention FLOPs, bytes the optimizer streams,
+    bytes every collective moves, and a step-time estimate from given peak rates."""
+
+    tokens_per_gpu: int
+    gemm_flops: float            # projections + LM head, forward + backward (+ recomputed forward)
+    attention_flops: float       # causal QK^T / PV, forward + backward (+ recomputed forward)
+    optimizer_bytes: float       # fp32 master + moments read and written, gradient read, bf16 copy written
+    collective_bytes: dict       # name -> bytes received per GPU and step
+    gemm_tflops: float
+    attention_tflops: float
+    hbm_gbs: float
+    link_gbs: float
+
+    @property
+    def compute_ms(self) -> float:
+        return 1e3 * (self.gemm_flops / (self.gemm_tflops * 1e12) + self.attention_flops / (self.attention_tflops * 1e12)
+                      + self.optimizer_bytes / (self.hbm_gbs * 1e9))
+
+    @property
+    def collective_ms(self) -> float:
+        return 1e3 * sum(self.collective_bytes.values()) / (self.link_gbs * 1e9)
+
+    def table(self) -> str:
+        lines = [f"per GPU and step: {self.tokens_per_gpu} tokens",
+                 f"  GEMM work                   {self.gemm_flops / 1e12:10.1f} TFLOP  ({self.gemm_tflops:.0f} TFLOP/s assumed)",
+                 f"  attention work              {self.attention_flops / 1e12:10.1f} TFLOP  ({self.attention_tflops:.0f} TFLOP/s assumed)",
+                 f"  optimizer traffic           {self.optimizer_bytes / 1e9:10.1f} GB     ({self.hbm_gbs:.0f} GB/s assumed)"]
+        for name, b in self.collective_bytes.items():
+            lines.append(f"  {name:<27} {b / 1e9:10.2f} GB received over NVLink ({self.link_gbs:.0f} GB/s assumed)")
+        lines.append(f"  compute estimate            {self.compute_ms:10.1f} ms; collectives {self.collective_ms:.1f} ms "
+                     f"(hidden when they overlap the GEMMs)")
+        lines.append(f"  tokens/s per GPU at the compute estimate: {self.tokens_per_gpu / self.compute_ms * 1e3:,.0f}")
+        return "\n".join(lines)
+
+
+def analyze_training_cost(trainer_cfg, *, num_gpus: int, per_gpu_batch: Optional[int] = None,
+                          seq_len: Optional[int] = None, full_remat: bool = True, gemm_tflops: float = 1377.0,
+                          attention_tflops: float = 800.0, hbm_gbs: float = 6551.0, link_gbs: float = 770.0,
+                          moment_count: int = 2) -> CostAnalysis:
+    """Defaults: the sustained library GEMM rate, copy bandwidth and peer-copy bandwidth measured on
+    B200, and this framework's attention kernels' rate."""
+    names = tuple(trainer_cfg.mesh_axis_names)
+    shape = infer_mesh_shape(tuple(trainer_cfg.mesh_shape), num_devices=num_gpus)
+    mesh = dict(zip(names, shape))
+    model = trainer_cfg.model.clone(name="model").instantiate(parent=None)
+    specs = flatten_items(model.create_parameter_specs_recursively(), is_leaf=lambda x: hasattr(x, "mesh_axes"))
+    dec = trainer_cfg.model.decoder
+    d, layers = dec.dim, dec.transformer.num_layers
+    tp, sp = mesh.get("model", 1), mesh.get("seq", 1)
+    batch_axes = math.prod(mesh.get(a, 1) for a in ("data", "expert", "fsdp"))
+    if per_gpu_batch is None:
+        global_batch = getattr(trainer_cfg.input, "global_batch_size", None) or batch_axes
+        per_gpu_batch = max(1, global_batch // batch_axes)
+    seq_len = seq_len or getattr(trainer_cfg.input, "source_length", None) or 4096
+    tokens = per_gpu_batch * seq_len // sp
+    # Every matrix parameter (>= 2 dims, embeddings excluded: a lookup, not a product) costs
+    # 2 FLOPs per element and token forward and 4 backward; full remat repeats the forward of the
+    # layer stack.
+    # (Stacked parameters carry a leading layer dim: a stacked norm scale is [L, D], not a matrix.)
+    matrix_stack = sum(math.prod(sp_.shape) for path, sp_ in specs if len(sp_.shape) >= 3 and "/repeat/" in path)
+    matrix_rest = sum(math.prod(sp_.shape) for path, sp_ in specs
+                      if len(sp_.shape) >= 2 and "/repeat/" not in path and "emb" not in path.split("/")[-2:][0])
+    shared_head = not any("lm_head" in path for path, _ in specs)
+    if shared_head:
+        matrix_rest += dec.vocab_size * d        # the embedding doubles as the output projection
+    passes_stack = 8.0 if full_remat else 6.0
+    gemm = tokens * (passes_stack * matrix_stack + 6.0 * matrix_rest) / tp
+    # Causal attention: 4 * T * T * d / 2 FLOPs per sequence forward, 2.5x that backward.
+    per_seq = 4.0 * seq_len * seq_len * d * 0.5
+    attention = per_gpu_batch * layers * per_seq * ((2.0 if full_remat else 1.0) + 2.5) / (tp * sp)
+    local = sum(math.prod(s_.shape) * _shard_fraction(s_, mesh) for _, s_ in specs)
+    optimizer = local * (4.0 * 2 * (1 + moment_count) + 2.0 + 2.0)
+    coll: dict = {}
+    storage = math.prod(mesh.get(a, 1) for a in ("fsdp", "expert", "seq")) or 1
+    if storage > 1:
+        sharded = sum(math.prod(s_.shape) for _, s_ in specs if _shard_fraction(s_, mesh) < 1.0) / tp
+        frac = (storage - 1) / storage
+        coll["parameter all-gathers"] = 2.0 * sharded * frac * (3.0 if full_remat else 2.0)
+        coll["gradient reduce-scatters"] = 2.0 * sharded * frac
+    if tp > 1:
+        # Two all-reduces forward (attention output, FFN output) and two backward per layer pass.
+        per_layer = 2.0 * tokens * d * 2.0 * (tp - 1) / tp
+        coll["tensor-parallel all-reduces"] = per_layer * layers * ((2.0 if full_remat else 1.0) + 1.0) * 2.0
+    if mesh.get("data", 1) > 1:
+        coll["data-parallel gradient all-reduce"] = 2.0 * 2.0 * local * (mesh["data"] - 1) / mesh["data"]
+    return CostAnalysis(tokens_per_gpu=tokens, gemm_flops=gemm, attention_flops=attention, optimizer_bytes=optimizer,
+                        collective_bytes=coll, gemm_tflops=gemm_tflops, attention_tflops=attention_tflops,
+                        hbm_gbs=hbm_gbs, link_gbs=link_gbs)
+
+
 def main(argv: Optional[Sequence[str]] = None) -> int:
     from axlearn_b200.common.launch_trainer import _import
 
@@ -149,15 +243,25 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--per_gpu_batch", type=int, default=None)
     ap.add_argument("--seq_len", type=int, default=None)
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--cost", action="store_true", help="also print FLOPs, collective bytes and a step-time estimate")
     args = ap.parse_args(argv)
     cfg = _import(args.module).named_trainer_configs()[args.config]()
     plan = plan_training_memory(cfg, num_gpus=args.num_gpus, hbm_gb=args.hbm_gb, per_gpu_batch=args.per_gpu_batch,
                                 seq_len=args.seq_len)
+    cost = analyze_training_cost(cfg, num_gpus=args.num_gpus, per_gpu_batch=args.per_gpu_batch,
+                                 seq_len=args.seq_len) if args.cost else None
     if args.json:
-        print(json.dumps({"mesh": plan.mesh, "bytes_per_gpu": plan.bytes_per_gpu, "total_bytes": plan.total_bytes,
-                          "fits": plan.fits}))
+        out = {"mesh": plan.mesh, "bytes_per_gpu": plan.bytes_per_gpu, "total_bytes": plan.total_bytes,
+               "fits": plan.fits}
+        if cost is not None:
+            out["cost"] = {"gemm_flops": cost.gemm_flops, "attention_flops": cost.attention_flops,
+                           "optimizer_bytes": cost.optimizer_bytes, "collective_bytes": cost.collective_bytes,
+                           "compute_ms": cost.compute_ms, "collective_ms": cost.collective_ms}
+        print(json.dumps(out))
     else:
         print(plan.table())
+        if cost is not None:
+            print(cost.table())
     return 0 if plan.fits else 1
 
 

@@ -36,3 +36,26 @@ def test_70b_does_not_fit_eight_gpus_and_cli(capsys):
     assert rc == 0 and '"fits": true' in capsys.readouterr().out
     with pytest.raises(ValueError):           # fsdp=8 x data=-1 cannot be laid out on 3 GPUs
         plan_training_memory(fuji.trainer_configs()["fuji-7B-v2"](), num_gpus=3)
+
+
+def test_cost_analysis_matches_hand_counts():
+    from axlearn_b200.common.aot_compilation import analyze_training_cost
+    from axlearn_b200.experiments.text.gpt import c4_trainer
+
+    cfg = c4_trainer.named_trainer_configs()["fuji-7B-v2"]()
+    cost = analyze_training_cost(cfg, num_gpus=8, per_gpu_batch=4, seq_len=4096)
+    assert cost.tokens_per_gpu == 4 * 4096
+    # 6.48 B matrix parameters in the layer stack (8 passes with full remat) + the 134 M LM head (6).
+    stack = 32 * (3 * 4096 * 4096 + 4096 * 4096 + 3 * 4096 * 11008)
+    expect = 16384 * (8.0 * stack + 6.0 * 32768 * 4096)
+    assert abs(cost.gemm_flops - expect) / expect < 1e-6
+    per_pass = 4 * 32 * (4.0 * 4096 * 4096 * 4096 * 0.5)
+    assert abs(cost.attention_flops - 4.5 * per_pass) / cost.attention_flops < 1e-6
+    assert set(cost.collective_bytes) == {"parameter all-gathers", "gradient reduce-scatters"}
+    # One bf16 copy of the model is gathered three times (forward, recomputation, backward) and
+    # scattered once, 7/8 of it over the links.
+    assert abs(cost.collective_bytes["gradient reduce-scatters"] - 2.0 * 6.61e9 * 7 / 8) / 1.2e10 < 0.05
+    assert abs(cost.collective_bytes["parameter all-gathers"] / cost.collective_bytes["gradient reduce-scatters"] - 3.0) < 1e-6
+    assert 600 < cost.compute_ms < 900 and "tokens/s per GPU" in cost.table()
+    tp = analyze_training_cost(cfg.clone(mesh_shape=(1, 1, 1, 4, 1, 2)), num_gpus=8, per_gpu_batch=4, seq_len=4096)
+    assert "tensor-parallel all-reduces" in tp.collective_bytes and abs(tp.gemm_flops * 2 - cost.gemm_flops) / cost.gemm_flops < 1e-6
