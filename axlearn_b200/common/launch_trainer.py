@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import argparse
 import importlib
+import json
 import os
 from typing import Any, Optional, Sequence
 
@@ -95,9 +96,25 @@ def get_trainer_config(args: Any):
     return cfg
 
 
-def run_trainer(cfg, *, seed: int = 0) -> Optional[dict]:
+def run_trainer(cfg, *, seed: int = 0, flags: Optional[dict] = None) -> Optional[dict]:
+    """Records what is about to run -- ``{dir}/trainer_config`` (the config's debug string) and
+    ``{dir}/launch_trainer_flags`` (the launch flags as JSON), written by process 0 -- then
+    instantiates the trainer and runs it (reference: axlearn/common/launch_trainer.py:192-217)."""
+    trainer_dir = getattr(cfg, "dir", None)
+    if trainer_dir and _process_index() == 0:
+        os.makedirs(trainer_dir, exist_ok=True)
+        with open(os.path.join(trainer_dir, "trainer_config"), "w", encoding="utf-8") as f:
+            f.write(cfg.debug_string())
+        with open(os.path.join(trainer_dir, "launch_trainer_flags"), "w", encoding="utf-8") as f:
+            json.dump(flags or {}, f, default=str, sort_keys=True)
     trainer = cfg.instantiate(parent=None)
     return trainer.run(prng.PRNGKey(seed))
+
+
+def _process_index() -> int:
+    import torch.distributed as dist
+
+    return dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
 
 
 def main(argv: Optional[Sequence[str]] = None) -> None:
@@ -116,7 +133,7 @@ def main(argv: Optional[Sequence[str]] = None) -> None:
         server.start()
     try:
         os.makedirs(args.trainer_dir, exist_ok=True)
-        run_trainer(get_trainer_config(args), seed=args.trainer_prng_seed)
+        run_trainer(get_trainer_config(args), seed=args.trainer_prng_seed, flags=vars(args))
     finally:
         if server is not None:
             server.stop()
