@@ -221,6 +221,12 @@ class SpmdEvaler(Module):
         # Cap on the number of batches per evaluation (None = the whole eval input).
         max_batches: Optional[int] = None
         dir: Optional[str] = None
+        # Batch indices at which a profiler trace of ONE forward is written under
+        # ``{summary dir}/traces`` (at most three evaluations are traced, so that a long run does
+        # not fill the disk; reference: axlearn/common/evaler.py:577, :699).
+        trace_at_iters: Sequence[int] = ()
+        # Writes every batch's inputs and per-example outputs (e.g. ``JsonlOutputWriter``).
+        output_writer: Optional[InstantiableConfig] = None
 
     def __init__(self, cfg, *, parent=None, model=None, model_param_partition_specs=None):
         super().__init__(cfg, parent=parent)
@@ -234,6 +240,10 @@ class SpmdEvaler(Module):
         self._add_child("metric_calculator", cfg.metric_calculator.clone(eval_dtype=cfg.eval_dtype), model=model,
                         model_param_partition_specs=model_param_partition_specs)
         self._add_child("summary_writer", sw)
+        if cfg.output_writer is not None:
+            self._add_child("output_writer", cfg.output_writer)
+        self._trace_dir = os.path.join(sw.dir, "traces")
+        self._traced_evals = 0
         self._policy: EvalPolicy = cfg.eval_policy.instantiate()
         self.last_eval_seconds: Optional[float] = None
 
@@ -248,16 +258,40 @@ class SpmdEvaler(Module):
         calc = self.metric_calculator
         state = calc.init_state(prng_key=eval_key, model_params=model_params)
         outputs = []
+        traced_any = False
         device = next((t.device for _, t in flatten_items(model_params) if isinstance(t, Tensor)), None)
         for i, batch in enumerate(self.input.batches(iter(self.input.dataset()))):
             if cfg.max_batches is not None and i >= cfg.max_batches:
                 break
             batch = tree_map(lambda t: t.to(device) if isinstance(t, Tensor) and device is not None else t, batch)
-            r = calc.forward(batch, model_params=model_params, state=state)
+            if i in cfg.trace_at_iters and self._traced_evals < 3:
+                traced_any = True
+                r = self._traced_forward(calc, batch, model_params, state, step=step, batch_index=i)
+            else:
+                r = calc.forward(batch, model_params=model_params, state=state)
             state = r["state"]
             if return_aux or isinstance(calc, (GlobalMetricCalculator, CompositeMetricCalculator)):
                 outputs.append(r["output"])
+            if "output_writer" in self._children:
+                self.output_writer.write(input_batch=batch, output_batch=r["output"])
+        if traced_any:
+            self._traced_evals += 1
+        if "output_writer" in self._children:
+            self.output_writer.flush()
         summaries = calc.get_summaries(model_params=model_params, state=state, all_forward_outputs=outputs)
         self.last_eval_seconds = time.perf_counter() - t0
         self.summary_writer(step, {**summaries, "eval_time_secs": self.last_eval_seconds})
         return prng_key, summaries, (outputs if return_aux else None)
+
+    def _traced_forward(self, calc, batch, model_params, state, *, step: int, batch_index: int):
+        """One forward under the torch profiler; the Chrome trace lands in ``traces/``."""
+        from torch.profiler import ProfilerActivity, profile
+
+        activities = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if torch.cuda.is_available() else [])
+        os.makedirs(self._trace_dir, exist_ok=True)
+        with profile(activities=activities) as prof:
+            r = calc.forward(batch, model_params=model_params, state=state)
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+        prof.export_chrome_trace(os.path.join(self._trace_dir, f"eval_step{step:08d}_batch{batch_index}.json"))
+        return r

@@ -88,6 +88,10 @@ class FakeLmInput(Input):
             raise ValueError(f"global batch {cfg.global_batch_size} not divisible by {feeds} feeds")
         local = cfg.global_batch_size // feeds
         base = prng.PRNGKey(cfg.seed)
+        if not cfg.is_training:
+            # An evaluation input is iterated from the start every time (each evaluation sees the
+            # same batches); a training input continues where its state says.
+            self._batch_index = 0
         while cfg.total_num_batches is None or self._batch_index < cfg.total_num_batches:
             # The global batch is a function of (seed, batch index) only; each feed takes its
             # rows, so the data does not depend on how many ranks share the batch.

@@ -77,3 +77,27 @@ def test_trainer_runs_evalers_and_best_metric_policy_sees_them(tmp_path):
     assert trainer.heldout.last_eval_seconds is not None
     files = list((tmp_path / "summaries" / "heldout").iterdir())
     assert files
+
+
+def test_evaler_traces_chosen_batches_and_writes_outputs(tmp_path):
+    import json
+    import os
+
+    from axlearn_b200.common.inference import JsonlOutputWriter
+
+    model, params = _model()
+    cfg = evaler.SpmdEvaler.default_config().set(
+        name="eval", input=_input(3), dir=str(tmp_path), trace_at_iters=[1],
+        output_writer=JsonlOutputWriter.default_config().set(output_dir=str(tmp_path / "out"), include_inputs=True),
+        eval_policy=config_for_function(evaler.every_n_steps_policy).set(n=1))
+    ev = cfg.instantiate(parent=None, model=model)
+    key = prng.PRNGKey(1)
+    for step in range(1, 6):
+        ev.eval_step(step, prng_key=key, model_params=params)
+    traces = sorted(os.listdir(tmp_path / "summaries" / "eval" / "traces"))
+    # Batch 1 of the first THREE evaluations only.
+    assert traces == [f"eval_step{s:08d}_batch1.json" for s in (1, 2, 3)]
+    with open(tmp_path / "summaries" / "eval" / "traces" / traces[0]) as f:
+        assert "traceEvents" in json.load(f)
+    rows = [json.loads(line) for line in open(ev.output_writer.path)]
+    assert len(rows) == 5 * 3 * 4 and "inputs/input_ids" in rows[0]          # 5 evals x 3 batches x 4 examples
