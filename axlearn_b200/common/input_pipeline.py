@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import bisect
 import json
+import os
 import queue
 import threading
 from typing import Any, Callable, Iterable, Iterator, Optional, Sequence
@@ -108,6 +109,58 @@ class TokenFileSource(Source):
         lo = index * self._stride
         window = np.asarray(self._tokens[lo:lo + self._length + 1], dtype=np.int32)
         return {"input_ids": window[:-1], "target_labels": window[1:]}
+
+
+class TFRecordSource(Source):
+    """``tf.train.Example`` records of TFRecord files (the format of the reference's tfds datasets,
+    axlearn/common/input_tf_data.py:204-330).  The frame offsets of every file are indexed once
+    from the length headers, so access is random; ``features`` optionally maps a feature name to
+    ``"bytes"`` / ``"str"`` / ``"int"`` / ``"float"`` (scalar: first value) -- unnamed features
+    come back as the arrays / byte lists that ``tfrecord.decode_example`` produces."""
+
+    def __init__(self, paths: Sequence[str], features: Optional[dict[str, str]] = None, *, check_crc: bool = False):
+        import struct
+
+        self._paths, self._features, self._check_crc = list(paths), features, check_crc
+        self._offsets: list[np.ndarray] = []
+        for p in self._paths:
+            offs, pos, size = [], 0, os.path.getsize(p)
+            with open(p, "rb") as f:
+                while pos + 12 <= size:
+                    f.seek(pos)
+                    (length,) = struct.unpack("<Q", f.read(8))
+                    offs.append(pos)
+                    pos += 12 + length + 4
+            if pos != size:
+                raise ValueError(f"{p}: truncated TFRecord file")
+            self._offsets.append(np.asarray(offs, dtype=np.int64))
+        self._starts = np.cumsum([0] + [len(o) for o in self._offsets])
+
+    def __len__(self):
+        return int(self._starts[-1])
+
+    def __getitem__(self, index):
+        from axlearn_b200.common import tfrecord
+
+        f = bisect.bisect_right(self._starts, index) - 1
+        with open(self._paths[f], "rb") as fh:
+            fh.seek(int(self._offsets[f][index - self._starts[f]]))
+            record = next(tfrecord.read_tfrecords(fh, check_crc=self._check_crc))
+        ex = tfrecord.decode_example(record)
+        if self._features is None:
+            return ex
+        out = {}
+        for name, kind in self._features.items():
+            v = ex[name]
+            if kind == "bytes":
+                out[name] = v[0]
+            elif kind == "str":
+                out[name] = v[0].decode("utf-8")
+            elif kind in ("int", "float"):
+                out[name] = v[0].item()
+            else:
+                out[name] = v
+        return out
 
 
 class ParquetSource(Source):
