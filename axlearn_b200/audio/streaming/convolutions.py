@@ -21,6 +21,7 @@ import torch.nn.functional as F
 from axlearn_b200.common.base_layer import BaseLayer, FanAxes, ParameterSpec
 from axlearn_b200.common.config import REQUIRED, Required, config_class
 from axlearn_b200.common.convolution import Conv1D, Conv2DWith1DPadding, conv_explicit_padding
+from axlearn_b200.audio.streaming.streaming_base import StreamingBase, config_method
 from axlearn_b200.common.module import nowrap
 
 Tensor = torch.Tensor
@@ -40,7 +41,7 @@ def _strided_paddings(paddings: Tensor, *, stride: int, pad_left: int, pad_right
     return p[:, anchor::stride][:, :n_out]
 
 
-class CausalConv1D(Conv1D):
+class CausalConv1D(StreamingBase, Conv1D):
     """``[B, T, C] -> [B, T / stride, C']`` with CAUSAL padding and ``extend_step``."""
 
     @classmethod
@@ -52,23 +53,26 @@ class CausalConv1D(Conv1D):
         if cfg.padding != "CAUSAL":
             raise ValueError(f"Only CAUSAL padding is supported (got {cfg.padding}).")
 
+    @staticmethod
+    def _cfg_time_padding(cfg) -> tuple:
+        return tuple(conv_explicit_padding("CAUSAL", (cfg.window,), (cfg.strides,), (cfg.dilation or 1,))[0])
+
     @nowrap
     def _time_padding(self) -> tuple:
-        cfg = self._config
-        return tuple(conv_explicit_padding("CAUSAL", (cfg.window,), (cfg.strides,), (cfg.dilation or 1,))[0])
+        return self._cfg_time_padding(self._config)
 
     @nowrap
     def cache_size(self) -> int:
         return self._time_padding()[0]
 
-    @nowrap
-    def in_stride(self) -> int:
-        return self._config.strides
+    @config_method
+    def in_stride(cls, cfg) -> int:  # pylint: disable=no-self-argument
+        return cfg.strides
 
-    @nowrap
-    def segment_pad(self) -> int:
+    @config_method
+    def segment_pad(cls, cfg) -> int:  # pylint: disable=no-self-argument
         """Padding frames needed between packed segments so that no window spans two of them."""
-        return max(self._time_padding())
+        return max(cls._cfg_time_padding(cfg))
 
     @nowrap
     def init_states(self, *, batch_size: int, dtype: torch.dtype = torch.float32, device=None) -> dict:
@@ -138,7 +142,7 @@ class CausalConv1DWithPadding(CausalConv1D):
         return states, {"x": out["x"] * _keep(out_p, out["x"]), "paddings": out_p}
 
 
-class CausalConv2DWith1DPadding(Conv2DWith1DPadding):
+class CausalConv2DWith1DPadding(StreamingBase, Conv2DWith1DPadding):
     """``[B, T, F, C]`` convolution, causal in time (SAME in frequency), with ``extend_step``."""
 
     @classmethod
@@ -158,13 +162,14 @@ class CausalConv2DWith1DPadding(Conv2DWith1DPadding):
     def cache_size(self) -> int:
         return self._time_padding()[0]
 
-    @nowrap
-    def in_stride(self) -> int:
-        return self._config.strides[0]
+    @config_method
+    def in_stride(cls, cfg) -> int:  # pylint: disable=no-self-argument
+        return cfg.strides[0]
 
-    @nowrap
-    def segment_pad(self) -> int:
-        return max(self._time_padding())
+    @config_method
+    def segment_pad(cls, cfg) -> int:  # pylint: disable=no-self-argument
+        dil = cfg.dilation or (1,) * len(cfg.window)
+        return max(conv_explicit_padding(cfg.padding, cfg.window, cfg.strides, dil)[0])
 
     def forward(self, x: Tensor, *, paddings: Tensor):
         cfg = self._config
@@ -280,7 +285,7 @@ class Conv1DTranspose(BaseLayer):
         return [input_shape[0], n, self._config.output_dim]
 
 
-class CausalConv1DTranspose(Conv1DTranspose):
+class CausalConv1DTranspose(StreamingBase, Conv1DTranspose):
     """Causal up-sampling with ``extend_step``: output frames ``[t * s, (t + 1) * s)`` depend on
     inputs ``t, t - 1, ..., t - ceil((w - 1) / s)``; the state holds those past input frames."""
 
@@ -299,9 +304,15 @@ class CausalConv1DTranspose(Conv1DTranspose):
         eff = (cfg.window - 1) * cfg.dilation + 1
         return math.ceil((eff - 1) / cfg.strides)
 
-    @nowrap
-    def out_stride(self) -> int:
-        return self._config.strides
+    @config_method
+    def out_stride(cls, cfg) -> int:  # pylint: disable=no-self-argument
+        return cfg.strides
+
+    @config_method
+    def segment_pad(cls, cfg) -> int:  # pylint: disable=no-self-argument
+        # Output frame o sees input frames t with t * s <= o <= t * s + (w - 1) * d; the zeros that
+        # up-sampling puts between inputs count as padding, so floor, not ceil.
+        return max((cfg.window - 1) * cfg.dilation, cfg.strides - 1) // cfg.strides
 
     @nowrap
     def init_states(self, *, batch_size: int, dtype: torch.dtype = torch.float32, device=None) -> dict:
