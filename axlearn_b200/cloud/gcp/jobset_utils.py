@@ -18,6 +18,7 @@ import dataclasses
 from typing import Any, Optional, Sequence
 
 from axlearn_b200.cloud.gcp.jobset import A4_HIGH_NCCL_ENV, GPUS_PER_NODE
+from axlearn_b200.common import runtime_options
 from axlearn_b200.common.config import REQUIRED, Configurable, InstantiableConfig, Required, config_class
 
 # Machine type -> GKE accelerator label.
@@ -239,7 +240,11 @@ class GPUReplicatedJob(BaseReplicatedJob):
 
     def _env(self) -> list:
         cfg = self._config
-        env = dict(self.NCCL_ENV)
+        # Framework defaults for this topology first; the fabric's NCCL settings and the user's
+        # own variables override them.
+        env = runtime_options.env_from_options(runtime_options.default_runtime_options(
+            instance_type="b200", num_gpus=GPUS_PER_NODE, num_nodes=cfg.num_nodes))
+        env.update(self.NCCL_ENV)
         env.update({"MASTER_ADDR": self._coordinator(), "MASTER_PORT": str(cfg.rendezvous_port),
                     "NUM_NODES": str(cfg.num_nodes), "GPUS_PER_NODE": str(GPUS_PER_NODE),
                     "NUM_PROCESSES": str(cfg.num_nodes * GPUS_PER_NODE)})
