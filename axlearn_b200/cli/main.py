@@ -52,6 +52,14 @@ def _cmd_bastion(args) -> int:
         st = directory.get_job_state(args.name)
         print(json.dumps(None if st is None else {"state": st.state.value, "metadata": st.metadata}))
         return 0
+    if args.format == "table":
+        from axlearn_b200.cloud.common import utils as cloud_utils
+
+        jobs = directory.list_jobs()
+        print(cloud_utils.jobs_table(jobs))
+        print("Usage by project:", cloud_utils.project_usage_table(jobs))
+        print("Usage by user:", cloud_utils.user_usage_table(jobs))
+        return 0
     rows = [{"name": n, "state": j.state.state.value, "user": j.spec.metadata.user_id,
              "project": j.spec.metadata.project_id, "resources": j.spec.metadata.resources}
             for n, j in directory.list_jobs().items()]
@@ -181,6 +189,7 @@ def build_parser() -> argparse.ArgumentParser:
     bastion.add_argument("--priority", type=int, default=5)
     bastion.add_argument("--resources", nargs="*", default=[], help="e.g. b200=8")
     bastion.add_argument("--env", nargs="*", default=[], help="KEY=VALUE")
+    bastion.add_argument("--format", default="json", choices=["json", "table"], help="list: output form")
 
     gcp = groups.add_parser("gcp", help="GKE JobSets; everything after the flags is the worker command")
     gcp.add_argument("action", choices=["launch", "delete", "status", "manifest", "config", "serve-manifest"])
