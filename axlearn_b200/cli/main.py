@@ -102,6 +102,21 @@ def _cmd_gcp(args, rest: Sequence[str]) -> int:
     if rest and rest[0] == "--":
         rest = rest[1:]          # the separator in front of the worker command is not part of it
     command = " ".join(rest) if rest else (args.command or "true")
+    if args.action == "logs":
+        # Direct route: the cluster's own log stream.  (Cloud Logging: ``cloud.gcp.logs.print_logs``
+        # with an authorised client.)
+        from axlearn_b200.cloud.gcp import logs  # pylint: disable=import-outside-toplevel
+
+        cmd = list(logs.kubectl_logs_command(name=args.name, worker=args.worker, replica=args.replica,
+                                             namespace=args.namespace, num_lines=args.num_lines, follow=args.follow))
+        print(" ".join(cmd))
+        print("Cloud logging url: " + logs.logs_url(name=args.name, worker=args.worker, replica=args.replica,
+                                                     namespace=args.namespace))
+        if args.dry_run:
+            return 0
+        import subprocess  # pylint: disable=import-outside-toplevel
+
+        return subprocess.run(cmd, check=False).returncode
     if args.action == "serve-manifest":
         # A multi-host serving deployment: --num_nodes hosts per replica, leader Service, probes,
         # optionally a Gateway route and an autoscaler (axlearn/cloud/gcp/lws_utils.py, k8s_*.py).
@@ -192,7 +207,12 @@ def build_parser() -> argparse.ArgumentParser:
     bastion.add_argument("--format", default="json", choices=["json", "table"], help="list: output form")
 
     gcp = groups.add_parser("gcp", help="GKE JobSets; everything after the flags is the worker command")
-    gcp.add_argument("action", choices=["launch", "delete", "status", "manifest", "config", "serve-manifest"])
+    gcp.add_argument("action", choices=["launch", "delete", "status", "manifest", "config", "serve-manifest", "logs"])
+    gcp.add_argument("--worker", type=int, default=0, help="logs: worker (completion index) within the replica")
+    gcp.add_argument("--replica", type=int, default=0, help="logs: replicated-job index")
+    gcp.add_argument("--num_lines", "-n", type=int, default=1000, help="logs: lines to show")
+    gcp.add_argument("--follow", action="store_true", help="logs: keep streaming")
+    gcp.add_argument("--dry_run", action="store_true", help="logs: print the command and the URL only")
     gcp.add_argument("--name")
     gcp.add_argument("--project")
     gcp.add_argument("--env_id")
