@@ -38,7 +38,7 @@ KNOBS: dict[str, tuple[str, str]] = {
     "AXB200_FLASH_FWD": ("v3", "Flash-attention forward kernel: v3 (scores in registers), v2 or v1."),
     "AXB200_FLASH_BWD": ("fused", "Flash-attention backward: fused (one kernel, 5 GEMMs) or split (dK/dV + dQ kernels)."),
     "AXB200_RMSNORM": ("warp", "RMSNorm kernels: warp (rows held in registers, where the width allows) or plain."),
-    "AXB_DECODE_ATTN": ("", "head: one CTA per query head in decode attention even for grouped-query layouts."),
+    "AXB_DECODE_ATTN": ("", "head: the per-head decode-attention kernel for every layout (no row-contiguous kernel); head1 / head2: also at most 1 / 2 query heads per CTA."),
     "AXB200_MOE_GROUP_BLOCK": ("256", "Rows to which each expert's token run is padded (256: CTA-pair grouped GEMM; 128: single CTA)."),
     "AXB_MOE_PEER_EXCHANGE": ("1", "0: NCCL all-to-all for expert parallelism; 1: peer-memory exchange kernels; force: also when sizes are small."),
     "AXB200_FUSED_FSDP": ("1", "0: NCCL all-gather / reduce-scatter for FSDP instead of the GEMM-fused peer-memory paths."),

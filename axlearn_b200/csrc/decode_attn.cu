@@ -59,8 +59,10 @@ __device__ __forceinline__ void unpack8(const uint4& u, float* f) {
 }
 
 // GT query heads of one KV head per CTA (GT = 1, 2 or 4).
+// One query head per CTA (GT == 1) fits 64 registers without spills: eight CTAs per SM instead of
+// six, i.e. 1184 resident CTAs, so that a 32 x 32-head batch is one wave instead of 1.15.
 template <int GT>
-__global__ void __launch_bounds__(kDecodeThreads)
+__global__ void __launch_bounds__(kDecodeThreads, GT == 1 ? 8 : 1)
 decode_attn_kernel(DecodeParams p) {
   const int split = blockIdx.x;
   const int groups_per_kv = (p.num_q_heads / p.num_kv_heads) / GT;
@@ -425,28 +427,33 @@ extern "C" int axb_decode_attn(const void* q, const void* k_pool, const void* v_
   p.splits = splits;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   // AXB_DECODE_ATTN=head keeps the per-head kernel for every shape (for comparisons).
-  static int rows_ok = -1;
+  // head1 / head2 additionally cap the query heads per CTA at 1 / 2.
+  static int rows_ok = -1, gt_cap = 4;
   if (rows_ok < 0) {
     const char* e = getenv("AXB_DECODE_ATTN");
-    rows_ok = (e != nullptr && strcmp(e, "head") == 0) ? 0 : 1;
+    if (e != nullptr && strcmp(e, "head1") == 0) gt_cap = 1;
+    if (e != nullptr && strcmp(e, "head2") == 0) gt_cap = 2;
+    rows_ok = (e != nullptr && strncmp(e, "head", 4) == 0) ? 0 : 1;
   }
-  // Measured (16 x 2048 cached tokens, 32 query heads): with 8 KV heads the row-contiguous kernel
-  // reaches 1747 GB/s against 1298 for the per-head one; with one query head per KV head the two are
-  // equal at 32 heads (3618 / 3616) and the per-head kernel wins at 4 heads (3799 / 2945), so that
-  // case stays on it.
-  if (rows_ok && num_kv_heads % 4 == 0 && (g == 2 || g == 4)) {
+  // Measured (2048 cached tokens, 32 query heads, bytes of K and V counted once):
+  //   * four query heads per KV head, 8 KV heads: the row-contiguous kernel reaches 2250 GB/s at
+  //     batch 64 and 1845 at batch 16 against 2073 / 1579 for one query head per CTA (which re-reads
+  //     K and V through the L2 four times); at batch 4 the latter wins (1057 against 840) because
+  //     the row kernel has too few CTAs to cover the machine;
+  //   * two query heads per KV head (16 KV heads, batch 64): one query head per CTA 3870, row kernel
+  //     3531 -- eight resident CTAs per SM at 64 registers beat two at 221;
+  //   * one query head per KV head: the per-head kernel throughout.
+  const bool few_row_ctas = static_cast<int64_t>(B) * (num_kv_heads / 4) <= 8;
+  if (rows_ok && num_kv_heads % 4 == 0 && g == 4 && !few_row_ctas) {
     dim3 rgrid(splits, num_kv_heads / 4, B);
-    if (g == 4)
-      decode_attn_rows_kernel<4><<<rgrid, kDecodeThreads, 0, stream>>>(p);
-    else if (g == 2)
-      decode_attn_rows_kernel<2><<<rgrid, kDecodeThreads, 0, stream>>>(p);
-    else
-      decode_attn_rows_kernel<1><<<rgrid, kDecodeThreads, 0, stream>>>(p);
+    decode_attn_rows_kernel<4><<<rgrid, kDecodeThreads, 0, stream>>>(p);
     if (splits > 1)
       decode_combine_kernel<<<B * num_q_heads, kHeadDim, 0, stream>>>(p.part_out, p.part_ml, p.out, splits);
     return cudaGetLastError() == cudaSuccess ? 0 : -4;
   }
-  const int gt = (g % 4 == 0) ? 4 : (g % 2 == 0) ? 2 : 1;
+  int gt = (g % 4 == 0) ? 4 : (g % 2 == 0) ? 2 : 1;
+  if (rows_ok && (g == 2 || (g == 4 && num_kv_heads % 4 == 0))) gt = 1;
+  if (gt > gt_cap) gt = gt_cap;
   dim3 grid(splits, num_kv_heads * (g / gt), B);
   if (gt == 4)
     decode_attn_kernel<4><<<grid, kDecodeThreads, 0, stream>>>(p);

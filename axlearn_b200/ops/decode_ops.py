@@ -49,15 +49,41 @@ def _lib():
     return h
 
 
+def _kernel_shape(batch: int, num_kv_heads: int, group: int) -> tuple[int, int]:
+    """``(CTAs of one split, CTAs that fit one SM)`` of the kernel that the launcher picks (mirrors
+    ``axb_decode_attn``): 128 threads each, residency limited by registers -- 64 with the occupancy
+    bound / 125 / 193 for the per-head kernel with 1 / 2 / 4 query heads per CTA, 225 for the
+    row-contiguous kernel of four KV heads x four query heads."""
+    mode = os.environ.get("AXB_DECODE_ATTN", "")
+    natural = 4 if group % 4 == 0 else 2 if group % 2 == 0 else 1
+    if mode.startswith("head"):
+        gt = min(natural, {"head1": 1, "head2": 2}.get(mode, 4))
+    elif group == 4 and num_kv_heads % 4 == 0 and batch * (num_kv_heads // 4) > 8:
+        return batch * (num_kv_heads // 4), 2
+    else:
+        gt = 1 if group == 2 or (group == 4 and num_kv_heads % 4 == 0) else natural
+    return batch * num_kv_heads * (group // gt), {1: 8, 2: 4, 4: 2}[gt]
+
+
 def default_splits(batch: int, num_kv_heads: int, group: int, max_len: int, page_size: int, sms: int = 148) -> int:
-    """KV splits so that the grid has a few CTAs per SM without splitting below 8 pages."""
-    gt = 4 if group % 4 == 0 else 2 if group % 2 == 0 else 1
-    ctas = batch * num_kv_heads * (group // gt)
-    if num_kv_heads % 4 == 0 and group in (2, 4) and os.environ.get("AXB_DECODE_ATTN") != "head":
-        ctas = batch * (num_kv_heads // 4)      # the row-contiguous kernel: four KV heads per CTA
-    want = max(1, (4 * sms + ctas - 1) // ctas)
+    """KV splits: enough CTAs for up to four per SM without splitting below 8 pages; once that grid
+    is more than one wave of resident CTAs, the nearby split count whose last wave is fullest (the
+    CTAs of a decode step all run about equally long, so a grid of 1.15 waves takes the time of 2)."""
+    ctas, resident = _kernel_shape(batch, num_kv_heads, group)
     pages = max(1, max_len // page_size)
-    return max(1, min(want, pages // 8 if pages >= 8 else 1, 32))
+    smax = max(1, min(pages // 8 if pages >= 8 else 1, 32))
+    base = max(1, min((min(4, resident) * sms + ctas - 1) // ctas, smax))
+    slots = sms * resident
+    if ctas * base <= slots:
+        return base
+
+    def fill(s: int) -> float:
+        x = ctas * s / slots
+        return x / math.ceil(x)
+
+    candidates = range(max(1, base - 4), min(smax, base + 7) + 1)
+    best = max(fill(s) for s in candidates)
+    return next(s for s in candidates if fill(s) >= 0.95 * best)
 
 
 def paged_decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,

@@ -166,7 +166,7 @@ def bench_decode_attn(args) -> dict:
     table = torch.randperm(b * pages, device="cuda").to(torch.int32).reshape(b, pages).contiguous()
     lengths = torch.full((b,), t, dtype=torch.int32, device="cuda")
     q = torch.randn(b, nq, h, device="cuda").bfloat16()
-    splits = decode_ops.default_splits(b, nkv, nq // nkv, t, ps)
+    splits = args.splits or decode_ops.default_splits(b, nkv, nq // nkv, t, ps)
     scratch = torch.empty(decode_ops._lib().axb_decode_attn_scratch_floats(b, nq, splits), device="cuda")  # pylint: disable=protected-access
     out = torch.empty_like(q)
     ours = _time(lambda: decode_ops.paged_decode_attention(q, k, v, table, lengths, splits=splits, out=out,
@@ -266,6 +266,7 @@ def main() -> None:
     ap.add_argument("--head_dim", type=int, default=128)
     ap.add_argument("--full", action="store_true", help="non-causal attention")
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--splits", type=int, default=0, help="decode_attn: KV splits (0 = the default heuristic)")
     args = ap.parse_args()
     peaks = _peaks()
     if args.op == "gemm":
