@@ -16,6 +16,31 @@ ProjectResourceMap = dict
 
 
 @dataclasses.dataclass
+class Topology:
+    """``replicas`` copies of an accelerator topology (e.g. ``"8x8"`` GPUs x nodes of one NVLink domain)."""
+
+    topology: str
+    replicas: int
+
+
+# Stands in for ``ScalingSpec.name`` when that is not set.
+DEFAULT_SCALING_SPEC_NAME = "default"
+
+
+@dataclasses.dataclass
+class ScalingSpec:
+    """Scaling bounds of one scaling group of an elastic job: it runs with any replica count in
+    ``[min_replicas, max_replicas]``, each replica needing ``resources_per_replica``."""
+
+    min_replicas: int
+    max_replicas: int
+    init_replicas: Optional[int] = None
+    resources_per_replica: dict = dataclasses.field(default_factory=dict)
+    topology_per_replica: Optional[str] = None
+    name: Optional[str] = None
+
+
+@dataclasses.dataclass
 class JobMetadata:
     user_id: str
     project_id: str
@@ -23,6 +48,7 @@ class JobMetadata:
     resources: dict
     priority: int = 5            # 1 = highest
     job_id: Optional[str] = None
+    scaling_specs: Optional[list] = None     # list[ScalingSpec] of an elastic job
 
     def to_json(self) -> dict:
         d = dataclasses.asdict(self)
@@ -33,6 +59,8 @@ class JobMetadata:
     def from_json(cls, d: dict) -> "JobMetadata":
         d = dict(d)
         d["creation_time"] = datetime.datetime.fromisoformat(d["creation_time"])
+        if d.get("scaling_specs"):
+            d["scaling_specs"] = [ScalingSpec(**spec) if isinstance(spec, dict) else spec for spec in d["scaling_specs"]]
         return cls(**d)
 
 
