@@ -21,6 +21,7 @@ from __future__ import annotations
 
 import collections
 import dataclasses
+import logging
 import datetime
 from typing import Any, Mapping, Optional, Sequence
 
@@ -170,20 +171,82 @@ class JobScheduler(Configurable):
         self._sorter = cfg.sorter.instantiate()
         self._scheduler = cfg.scheduler.instantiate()
 
-    def schedule(self, jobs: Mapping[str, JobMetadata], *, dry_run: Optional[bool] = None, verbosity: int = 0):
+    def schedule(self, jobs: Mapping[str, JobMetadata], *, dry_run: Optional[bool] = None, verbosity: int = 0,
+                 desired_replicas: Optional[Mapping[str, Mapping[str, int]]] = None):
+        """``desired_replicas``: ``{job: {scaling group: replicas}}`` for elastic jobs (what a
+        ``ReplicaManager`` reports); without an entry an elastic job asks for its ``min_replicas``.
+
+        An elastic job is scheduled as its base job (``metadata.resources``: the minimum it runs
+        with) plus one expansion slot per replica beyond ``min_replicas``; the slots inherit the
+        job's priority and age and compete with every other job.  Admitted slots are folded back
+        into the parent's verdict as ``metadata["granted_replicas"]`` (always present for an
+        admitted elastic job, so that a scale-down is observed too); a slot whose parent was not
+        admitted is dropped."""
         # The quota file is read afresh on every pass, so edits take effect without a restart.
         source = self._config.quota
         if isinstance(source, InstantiableConfig):
             info = source.instantiate()
         else:
             info = source() if callable(source) else source
+        expanded, slot_info = _expand_elastic_jobs(jobs, desired_replicas or {})
         by_project = collections.defaultdict(dict)
-        for job_id, meta in jobs.items():
+        for job_id, meta in expanded.items():
             by_project[meta.project_id][job_id] = meta
         project_jobs = {p: self._sorter.sort(js) for p, js in by_project.items()}
         results = self._scheduler.schedule(
             resource_limits=info.total_resources, project_quotas=info.project_resources,
             project_jobs=project_jobs, verbosity=verbosity)
+        results = _collapse_expansion_verdicts(results, slot_info, jobs)
         if self._config.dry_run if dry_run is None else dry_run:
             results.job_verdicts = {j: JobVerdict() for j in results.job_verdicts}
         return results
+
+
+GRANTED_REPLICAS_KEY = "granted_replicas"
+
+
+def expansion_slot_name(job_name: str, spec_name: str, index: int) -> str:
+    return f"{job_name}--exp-{spec_name}-{index}"
+
+
+def _expand_elastic_jobs(jobs: Mapping[str, JobMetadata], desired: Mapping[str, Mapping[str, int]]):
+    """``(jobs plus expansion slots, {slot: (parent job, scaling group)})``.  Stateless: every pass
+    builds all slots from ``min_replicas`` up to the target afresh."""
+    from axlearn_b200.cloud.common.job_types import DEFAULT_SCALING_SPEC_NAME
+
+    expanded, slot_info = dict(jobs), {}
+    for job_name, meta in jobs.items():
+        for spec in getattr(meta, "scaling_specs", None) or []:
+            spec_name = spec.name or DEFAULT_SCALING_SPEC_NAME
+            target = min(int(desired.get(job_name, {}).get(spec_name, spec.min_replicas)), spec.max_replicas)
+            for i in range(spec.min_replicas, target):
+                slot = expansion_slot_name(job_name, spec_name, i)
+                expanded[slot] = dataclasses.replace(meta, resources=dict(spec.resources_per_replica), scaling_specs=None)
+                slot_info[slot] = (job_name, spec_name)
+    return expanded, slot_info
+
+
+def _collapse_expansion_verdicts(results, slot_info: Mapping[str, tuple], jobs: Mapping[str, JobMetadata]):
+    from axlearn_b200.cloud.common.job_types import DEFAULT_SCALING_SPEC_NAME
+
+    for job_name, meta in jobs.items():
+        verdict = results.job_verdicts.get(job_name)
+        if getattr(meta, "scaling_specs", None) and verdict:
+            verdict.metadata[GRANTED_REPLICAS_KEY] = {(spec.name or DEFAULT_SCALING_SPEC_NAME): spec.min_replicas
+                                                      for spec in meta.scaling_specs}
+    collapsed = {}
+    for name, verdict in results.job_verdicts.items():
+        if name not in slot_info:
+            collapsed[name] = verdict
+            continue
+        parent, spec_name = slot_info[name]
+        parent_verdict = results.job_verdicts.get(parent)
+        if not parent_verdict:
+            if verdict:
+                logging.warning("Expansion slot %s admitted but its parent %s is not; dropping the slot.", name, parent)
+            continue
+        if verdict:
+            granted = parent_verdict.metadata.setdefault(GRANTED_REPLICAS_KEY, {})
+            granted[spec_name] = granted.get(spec_name, 0) + 1
+    results.job_verdicts = collapsed
+    return results

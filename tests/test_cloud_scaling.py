@@ -46,3 +46,37 @@ def test_env_prefix_patcher():
     p = EnvPrefixPatcher.default_config().set(env_vars={"A": "1"}).instantiate()
     assert p.patch("python x.py", env_vars={"B": "two words"}) == "A=1 B='two words' python x.py"
     assert EnvPrefixPatcher.default_config().instantiate().patch("cmd") == "cmd"
+
+
+def test_elastic_jobs_get_replicas_as_quota_allows():
+    from axlearn_b200.cloud.common.quota import QuotaInfo
+    from axlearn_b200.cloud.common.scheduler import JobScheduler
+
+    def meta(project, t, resources, specs=None, priority=5):
+        return JobMetadata(user_id="u", project_id=project, creation_time=datetime.datetime(2024, 1, 1, 0, t),
+                           resources=resources, priority=priority, scaling_specs=specs)
+
+    quota = QuotaInfo(total_resources=[{"b200": 40}], project_resources={"a": {"b200": 0.5}, "b": {"b200": 0.5}},
+                      project_membership={})
+    sched = JobScheduler.default_config().set(quota=lambda: quota).instantiate()
+    elastic = [ScalingSpec(min_replicas=1, max_replicas=4, resources_per_replica={"b200": 8}, name="train")]
+    jobs = {"el": meta("a", 0, {"b200": 8}, elastic), "fixed": meta("b", 1, {"b200": 16})}
+    # Nothing asked beyond the minimum: one replica granted, no slots in the verdicts.
+    r = sched.schedule(jobs)
+    assert set(r.job_verdicts) == {"el", "fixed"} and r.job_verdicts["el"].metadata["granted_replicas"] == {"train": 1}
+    assert "granted_replicas" not in r.job_verdicts["fixed"].metadata
+    # Four replicas wanted: 8 (base) + 16 (fixed) leave 16 of 40, i.e. two more replicas.
+    r = sched.schedule(jobs, desired_replicas={"el": {"train": 4}})
+    assert set(r.job_verdicts) == {"el", "fixed"}
+    assert r.job_verdicts["el"].metadata["granted_replicas"] == {"train": 3} and r.job_verdicts["fixed"]
+    assert r.project_usages["a"]["b200"] == 24
+    # A request beyond max_replicas is capped.
+    big = QuotaInfo(total_resources=[{"b200": 400}], project_resources={"a": {"b200": 1.0}}, project_membership={})
+    r = JobScheduler.default_config().set(quota=lambda: big).instantiate().schedule(
+        {"el": jobs["el"]}, desired_replicas={"el": {"train": 9}})
+    assert r.job_verdicts["el"].metadata["granted_replicas"] == {"train": 4}
+    # A parent that does not fit drops its slots.
+    tiny = QuotaInfo(total_resources=[{"b200": 4}], project_resources={"a": {"b200": 1.0}}, project_membership={})
+    r = JobScheduler.default_config().set(quota=lambda: tiny).instantiate().schedule(
+        {"el": jobs["el"]}, desired_replicas={"el": {"train": 2}})
+    assert set(r.job_verdicts) == {"el"} and not r.job_verdicts["el"]
