@@ -135,6 +135,9 @@ class Bastion(Configurable):
         termination_grace_seconds: float = 10.0
         # Publish a lifecycle event per job state change to ``<root_dir>/events.jsonl``.
         publish_events: bool = False
+        # Where elastic jobs' desired replica counts come from and granted counts go to
+        # (``cloud.common.replica_manager``); None: elastic jobs run at their minimum.
+        replica_manager: Optional[InstantiableConfig] = None
 
     def __init__(self, cfg):
         super().__init__(cfg)
@@ -147,6 +150,7 @@ class Bastion(Configurable):
         self._dir = BastionDirectory.default_config().set(root_dir=cfg.root_dir).instantiate()
         self._scheduler: JobScheduler = cfg.scheduler.instantiate()
         self._cleaner = cfg.cleaner.instantiate() if cfg.cleaner is not None else None
+        self._replica_manager = cfg.replica_manager.instantiate() if cfg.replica_manager is not None else None
         self._jobs: dict[str, BastionJob] = {}
 
     @property
@@ -244,9 +248,19 @@ class Bastion(Configurable):
         # 2. Schedule the schedulable ones.
         candidates = {n: j.spec.metadata for n, j in self._jobs.items()
                       if j.state.state in (JobState.PENDING, JobState.ACTIVE)}
-        verdicts = self._scheduler.schedule(candidates).job_verdicts if candidates else {}
+        desired = {}
+        if self._replica_manager is not None:
+            self._replica_manager.refresh()
+            for n, meta in candidates.items():
+                if getattr(meta, "scaling_specs", None):
+                    want = self._replica_manager.get_desired_replicas(n)
+                    if want:
+                        desired[n] = want
+        verdicts = self._scheduler.schedule(candidates, desired_replicas=desired).job_verdicts if candidates else {}
         for name, verdict in verdicts.items():
             job = self._jobs[name]
+            if self._replica_manager is not None and verdict and "granted_replicas" in verdict.metadata:
+                self._replica_manager.set_granted_replicas(name, verdict.metadata["granted_replicas"])
             if verdict and job.state.state == JobState.PENDING:
                 job.state = JobStatus(JobState.ACTIVE, dict(verdict.metadata))
                 job.command_proc = self._start(job, job.spec.command, name)

@@ -80,3 +80,29 @@ def test_elastic_jobs_get_replicas_as_quota_allows():
     r = JobScheduler.default_config().set(quota=lambda: tiny).instantiate().schedule(
         {"el": jobs["el"]}, desired_replicas={"el": {"train": 2}})
     assert set(r.job_verdicts) == {"el"} and not r.job_verdicts["el"]
+
+
+def test_bastion_reports_granted_replicas(tmp_path):
+    import json
+
+    from axlearn_b200.cloud.common.bastion import Bastion, BastionDirectory
+    from axlearn_b200.cloud.common.scheduler import JobScheduler
+    from axlearn_b200.common.config import config_for_function
+    from axlearn_b200.cloud.common import quota as quota_lib
+
+    quota_file = tmp_path / "quota.json"
+    quota_file.write_text(json.dumps({"total_resources": {"b200": 24}, "project_resources": {"p": {"b200": 1.0}}}))
+    root = str(tmp_path / "bastion")
+    replicas_dir = str(tmp_path / "replicas")
+    manager_cfg = FileReplicaManager.default_config().set(root_dir=replicas_dir)
+    manager_cfg.instantiate().set_desired_replicas("el", {"default": 4})
+    sched = JobScheduler.default_config().set(quota=config_for_function(quota_lib.get_resource_limits).set(path=str(quota_file)))
+    bastion = Bastion.default_config().set(root_dir=root, scheduler=sched, update_interval_seconds=0.01,
+                                           replica_manager=manager_cfg).instantiate()
+    meta = JobMetadata(user_id="u", project_id="p", creation_time=datetime.datetime(2024, 1, 1), resources={"b200": 8},
+                       scaling_specs=[ScalingSpec(min_replicas=1, max_replicas=8, resources_per_replica={"b200": 8})])
+    BastionDirectory.default_config().set(root_dir=root).instantiate().submit_job(
+        "el", job_spec=JobSpec(version=1, name="el", command="sleep 0.2", cleanup_command=None, env_vars=None, metadata=meta))
+    bastion.execute(max_iterations=2)
+    # 24 GPUs: the base replica and two more of the four wanted.
+    assert manager_cfg.instantiate().get_granted_replicas("el") == {"default": 3}
