@@ -238,13 +238,24 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--module", required=True)
     ap.add_argument("--config", required=True)
-    ap.add_argument("--num_gpus", type=int, required=True)
-    ap.add_argument("--hbm_gb", type=float, default=180.0)
+    ap.add_argument("--num_gpus", type=int, default=None)
+    ap.add_argument("--topology", default=None,
+                    help="instead of --num_gpus / --hbm_gb: an instance type such as gpu-b200-64 or b200-8")
+    ap.add_argument("--hbm_gb", type=float, default=None)
     ap.add_argument("--per_gpu_batch", type=int, default=None)
     ap.add_argument("--seq_len", type=int, default=None)
     ap.add_argument("--json", action="store_true")
     ap.add_argument("--cost", action="store_true", help="also print FLOPs, collective bytes and a step-time estimate")
     args = ap.parse_args(argv)
+    if args.topology:
+        from axlearn_b200.cloud.gcp.system_characteristics import parse_gpu_instance_type
+
+        vm, num_vms = parse_gpu_instance_type(args.topology)
+        args.num_gpus = args.num_gpus or vm.chips_per_vm * num_vms
+        args.hbm_gb = args.hbm_gb or float(vm.memory_gb_per_chip)
+    if not args.num_gpus:
+        ap.error("one of --num_gpus or --topology is required")
+    args.hbm_gb = args.hbm_gb or 180.0
     cfg = _import(args.module).named_trainer_configs()[args.config]()
     plan = plan_training_memory(cfg, num_gpus=args.num_gpus, hbm_gb=args.hbm_gb, per_gpu_batch=args.per_gpu_batch,
                                 seq_len=args.seq_len)

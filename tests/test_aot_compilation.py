@@ -59,3 +59,14 @@ def test_cost_analysis_matches_hand_counts():
     assert 600 < cost.compute_ms < 900 and "tokens/s per GPU" in cost.table()
     tp = analyze_training_cost(cfg.clone(mesh_shape=(1, 1, 1, 4, 1, 2)), num_gpus=8, per_gpu_batch=4, seq_len=4096)
     assert "tensor-parallel all-reduces" in tp.collective_bytes and abs(tp.gemm_flops * 2 - cost.gemm_flops) / cost.gemm_flops < 1e-6
+
+
+def test_topology_flag_and_reference_entry_point(capsys):
+    import json
+
+    from axlearn_b200.experiments import run_aot_compilation
+
+    rc = run_aot_compilation.main(["--module", "text.gpt.c4_trainer", "--config", "fuji-7B-v2", "--topology", "gpu-b200-16",
+                                   "--json"])
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rc == 0 and out["fits"] and out["mesh"]["fsdp"] * out["mesh"]["data"] == 16
